@@ -1,0 +1,196 @@
+"""Collective sweep: bus bandwidth of the fused collectives against plain NCCL.
+
+Method (the reference's, scripts/gpu/bench_all_reduce.py:125-197): per size 5 warm-ups, then
+up to ``--trials`` timed calls (or ``--seconds``), each bracketed by CUDA events on the
+current stream; a trial's latency is the slowest rank's; the median over trials is reported;
+``algbw = bytes / t`` and, as nccl-tests does, ``busbw = algbw * 2 (n-1) / n`` for
+all_reduce, ``algbw * (n-1) / n`` for all_gather and reduce_scatter, ``algbw`` for broadcast.
+
+Run under torchrun, one process per GPU, e.g.::
+
+    GPUBRIDGE_ISLANDS=4,4 python -m torch.distributed.run --nproc-per-node 8 \
+        --master-addr 127.0.0.1 -m gpubridge_b200.bench.bench_all_reduce --max 1G
+
+Targets: ``ours`` (the active policy), ``nccl`` (one NCCL communicator of every rank),
+``policy:<name>`` and ``compression:<mode>[:<format>]`` (a policy instance of their own).
+``--write-thresholds PATH`` writes an auto-tuned thresholds file from the measured winners.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+import warnings
+
+import torch
+import torch.distributed as dist
+
+import gpubridge_b200 as gb
+from gpubridge_b200 import policies as _policies
+from gpubridge_b200.config import parse_size
+
+BUS = {"all_reduce": lambda n: 2 * (n - 1) / n, "all_gather": lambda n: (n - 1) / n,
+       "reduce_scatter": lambda n: (n - 1) / n, "broadcast": lambda n: 1.0}
+
+
+def sizes(lo: int, hi: int) -> list[int]:
+    out, s = [], lo
+    while s <= hi:
+        out.append(s)
+        s *= 2
+    return out
+
+
+def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5) -> float:
+    """Median over trials of the slowest rank's device time, in milliseconds."""
+    dev = topology.device
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(dev)
+    topology.world_group.barrier()
+    times, started = [], time.monotonic()
+    for _ in range(trials):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        end.synchronize()
+        slowest = torch.tensor([start.elapsed_time(end)], dtype=torch.float64)
+        topology.world_group.all_reduce(slowest, "max")
+        times.append(float(slowest))
+        stop = torch.tensor([1.0 if time.monotonic() - started > seconds else 0.0])
+        topology.world_group.all_reduce(stop, "max")
+        if float(stop) > 0:
+            break
+    return statistics.median(times)
+
+
+def make_target(name: str, op: str, topology, dtype, nbytes: int):
+    """A zero-argument callable running ``op`` once on ``nbytes`` of ``dtype``."""
+    dev, world = topology.device, topology.world_size
+    n = max(1, nbytes // torch.empty(0, dtype=dtype).element_size())
+    gen = torch.Generator(device="cpu").manual_seed(1234 + topology.rank)
+    full = torch.randn(n, generator=gen).to(dtype).to(dev)
+    if name == "nccl":
+        comm = topology.p2p_group
+        if op == "all_reduce":
+            return lambda: comm.all_reduce(full), nbytes
+        if op == "broadcast":
+            return lambda: comm.broadcast(full, topology.layout.members[0]), nbytes
+        part = full[: n // world]
+        if op == "all_gather":
+            out = torch.empty(part.numel() * world, dtype=dtype, device=dev)
+            return lambda: comm.all_gather_into(out, part), out.nbytes
+        out = torch.empty(n // world, dtype=dtype, device=dev)
+        src = full[: out.numel() * world]
+        return lambda: comm.reduce_scatter_into(out, src), src.nbytes
+    policy = topology.policy
+    if name.startswith("policy:"):
+        cls = _policies.choose_policy(_policies.resolve_policy(name.split(":", 1)[1]),
+                                      topology.layout)
+        policy = cls()
+        policy.setup(topology)
+    elif name.startswith("compression:"):
+        parts = name.split(":")
+        policy = type(topology.policy)(compression=parts[1]) if hasattr(
+            topology.policy, "compression") else topology.policy
+        policy.setup(topology)
+        if len(parts) > 2:
+            policy._fmt = parts[2]
+    if op == "all_reduce":
+        return lambda: policy.all_reduce(full, topology), nbytes
+    if op == "broadcast":
+        return lambda: policy.broadcast(full, topology.layout.members[0], topology), nbytes
+    part = full[: n // world]
+    if op == "all_gather":
+        out = torch.empty(part.numel() * world, dtype=dtype, device=dev)
+        return lambda: policy.all_gather_into_tensor(out, part, topology), out.nbytes
+    out = torch.empty(n // world, dtype=dtype, device=dev)
+    src = full[: out.numel() * world]
+    return lambda: policy.reduce_scatter_tensor(out, src, topology), src.nbytes
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--min", default="4K")
+    ap.add_argument("--max", default="64M")
+    ap.add_argument("--ops", default="all_reduce")
+    ap.add_argument("--targets", default="ours,nccl")
+    ap.add_argument("--dtypes", default="float32")
+    ap.add_argument("--trials", type=int, default=20)
+    ap.add_argument("--seconds", type=float, default=20.0)
+    ap.add_argument("--json", default="")
+    ap.add_argument("--write-thresholds", default="")
+    args = ap.parse_args(argv)
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", gb.SplitTestWarning)
+        topology = gb.init()
+    rank, world = topology.rank, topology.world_size
+    rows = []
+    try:
+        for op in args.ops.split(","):
+            for dtype_name in args.dtypes.split(","):
+                dtype = getattr(torch, dtype_name)
+                for nbytes in sizes(parse_size(args.min), parse_size(args.max)):
+                    for target in args.targets.split(","):
+                        if target == "nccl" and topology.p2p_group is None:
+                            continue
+                        fn, moved = make_target(target, op, topology, dtype, nbytes)
+                        # the fused kernels are timed on the stream they run on, as the async
+                        # (DDP / FSDP) path uses them; NCCL is timed on the current stream
+                        fused = target != "nccl" and topology.fabric is not None
+                        stream = (topology.fabric.comm_stream if fused
+                                  else torch.cuda.current_stream(topology.device))
+                        with torch.cuda.stream(stream):
+                            ms = time_calls(fn, topology, args.trials, args.seconds)
+                        algbw = moved / (ms * 1e-3) / 1e9
+                        row = {"op": op, "dtype": dtype_name, "bytes": moved, "target": target,
+                               "ms": round(ms, 5), "algbw_gbs": round(algbw, 3),
+                               "busbw_gbs": round(algbw * BUS[op](world), 3), "world": world,
+                               "islands": [len(i.ranks) for i in topology.layout.islands],
+                               "policy": topology.policy_name}
+                        rows.append(row)
+                        if rank == 0:
+                            print(json.dumps(row), flush=True)
+        if topology.fabric is not None:
+            topology.fabric.check()
+    finally:
+        gb.destroy()
+    if rank == 0 and args.json:
+        with open(args.json, "w") as fh:
+            json.dump(rows, fh, indent=1)
+    if rank == 0 and args.write_thresholds:
+        write_thresholds(rows, args.write_thresholds)
+    return 0
+
+
+def write_thresholds(rows: list[dict], path: str) -> None:
+    """The fastest ``policy:*`` target per size becomes a rule; neighbouring sizes with the
+    same winner are merged; the last rule covers every size."""
+    best: dict[int, tuple[float, str]] = {}
+    for row in rows:
+        if row["op"] != "all_reduce" or not row["target"].startswith("policy:"):
+            continue
+        name = row["target"].split(":", 1)[1]
+        if row["bytes"] not in best or row["ms"] < best[row["bytes"]][0]:
+            best[row["bytes"]] = (row["ms"], name)
+    rules: list[dict] = []
+    for size in sorted(best):
+        name = best[size][1]
+        if rules and rules[-1]["policy"] == name:
+            rules[-1]["max_bytes"] = size
+        else:
+            rules.append({"max_bytes": size, "policy": name})
+    if not rules:
+        rules = [{"max_bytes": None, "policy": "auto"}]
+    rules[-1]["max_bytes"] = None
+    _policies.write_thresholds(path, rules, _policies.PipelinedReduceBridgeBroadcast
+                               .DEFAULT_CHUNK_BYTES)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,647 @@
+// Fused collectives over NVLink peer memory (sm_100a).
+//
+// Every kernel here is persistent (one wave of blocks), moves data with 16-byte loads and
+// stores to and from the peers' symmetric workspaces, and separates its steps with
+// gb_sync_all().  Summation order is fixed and the same on every rank: members of an
+// island in rank order, the island result rounded to the tensor's dtype, island results in
+// island order - so every rank ends with identical bits and integer-valued data is exact.
+//
+//   allreduce_oneshot  small tensors: every rank stores its tensor into a slot of every
+//                      peer, one barrier, every rank reduces the slots locally.
+//   allreduce_hier     the three-phase hierarchical all-reduce in one launch, software
+//                      pipelined over chunks.  A chunk is k stripes (k = size of the smallest
+//                      island); island member j owns stripe j.  Per chunk:
+//                        A  every rank stores stripe j of its input into a slot of its
+//                           island's owner j                            (island reduce)
+//                        B  owner j reduces its island's slots and stores the island result
+//                           - raw, bf16 or block-scaled fp8 with error feedback - into
+//                           owner j of every island                     (bridge, send)
+//                        C  owner j adds the island results in island order, applies AVG and
+//                           rounds once                                 (bridge, reduce)
+//                        D  every rank loads stripe j from its island's owner j into its
+//                           output                                      (island broadcast)
+//                      Iteration t runs A(t), B(t-1), C(t-2), D(t-3) and then one barrier, so
+//                      the steps of neighbouring chunks share the links.  With one island B
+//                      writes the result directly and C is skipped.
+//   allgather          every rank stages its input, barrier, every rank loads every peer's.
+//   reduce_scatter     every rank stores slice r into rank r, barrier, rank r reduces.
+//   broadcast          the source scatters stripes over the ranks, barrier, all-gather.
+//   barrier            gb_sync_all() alone.
+//
+// Buffer reuse.  A region written before a kernel's first barrier (one-shot slots, all-gather
+// staging, reduce-scatter slots, broadcast stripes) has two copies selected by the parity of
+// the team's collective counter; everything else is written only after a barrier of the same
+// kernel, when every peer has left the previous collective.  Inside a pipelined kernel the
+// two buffers of a region alternate with the chunk index.
+#include "gb_codec.cuh"
+
+// Byte offsets are into a workspace; every offset and length is a multiple of 16.
+struct GbArgs {
+    const void* in;
+    void* out;
+    size_t n;                 // elements (all-reduce, reduce-scatter: per slice) or bytes (copies)
+    size_t chunk;             // elements / bytes per chunk
+    size_t stripe;            // elements per stripe of a chunk (a multiple of 256)
+    int k;                    // stripes per chunk
+    int divide;               // > 0: divide the sum by it (AVG)
+    int root;                 // broadcast source (team rank)
+    int pad;
+    size_t off_a, off_b, off_c;   // regions
+    size_t len_a, len_b, len_c;   // bytes of one buffer of each region
+    float* residual;          // error feedback of this rank's stripes (compressed all-reduce)
+};
+
+namespace {
+
+constexpr int THREADS = 512;
+
+template <typename T> struct Vec {
+    static constexpr int N = 16 / sizeof(T);
+    union { uint4 u; T e[16 / sizeof(T)]; };
+};
+
+__device__ __forceinline__ size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+
+// Values of stripe j of the chunk starting at c0 that lie inside the tensor.
+__device__ __forceinline__ size_t stripe_valid(const GbArgs& a, size_t c0, int j) {
+    const size_t s0 = c0 + (size_t)j * a.stripe;
+    if (s0 >= a.n) return 0;
+    const size_t left = a.n - s0;
+    return left < a.stripe ? left : a.stripe;
+}
+
+// Reduce local slots in hierarchical order into out[0 .. count).
+//   slot s lives at slots + s * slot_bytes; island g is slot_of[bounds[g] .. bounds[g+1]).
+template <typename T, int OP>
+__device__ __forceinline__ void reduce_slots(const char* slots, size_t slot_bytes,
+                                             const int* slot_of, const int* bounds, int n_groups,
+                                             size_t count, T* out, int divide) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = Vec<T>::N;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    const size_t nvec = count / V;
+    const bool out_aligned = ((uintptr_t)out & 15u) == 0;
+    for (size_t v = tid; v < nvec; v += nth) {
+        A total[V];
+        for (int g = 0; g < n_groups; ++g) {
+            A part[V];
+            for (int s = bounds[g]; s < bounds[g + 1]; ++s) {
+                Vec<T> w;
+                w.u = gb_ld16(slots + (size_t)slot_of[s] * slot_bytes + v * 16);
+                #pragma unroll
+                for (int j = 0; j < V; ++j)
+                    part[j] = (s == bounds[g]) ? gb_up<T>(w.e[j])
+                                               : GbFold<OP, A>::run(part[j], gb_up<T>(w.e[j]));
+            }
+            #pragma unroll
+            for (int j = 0; j < V; ++j) {
+                A rounded = gb_up<T>(gb_down<T>(part[j]));      // the island result, in T
+                total[j] = (g == 0) ? rounded : GbFold<OP, A>::run(total[j], rounded);
+            }
+        }
+        Vec<T> r;
+        #pragma unroll
+        for (int j = 0; j < V; ++j)
+            r.e[j] = gb_down<T>(divide > 0 ? gb_divide<A>(total[j], divide) : total[j]);
+        if (out_aligned) gb_st16(out + v * V, r.u);
+        else {
+            #pragma unroll
+            for (int j = 0; j < V; ++j) out[v * V + j] = r.e[j];
+        }
+    }
+    // ragged tail: count is not a multiple of a 16-byte vector
+    for (size_t i = nvec * V + tid; i < count; i += nth) {
+        A total = A();
+        for (int g = 0; g < n_groups; ++g) {
+            A part = A();
+            for (int s = bounds[g]; s < bounds[g + 1]; ++s) {
+                const volatile unsigned char* p = reinterpret_cast<const volatile unsigned char*>(
+                    slots + (size_t)slot_of[s] * slot_bytes + i * sizeof(T));
+                union { T t; unsigned char b[sizeof(T)]; } cell;
+                #pragma unroll
+                for (unsigned q = 0; q < sizeof(T); ++q) cell.b[q] = p[q];
+                A x = gb_up<T>(cell.t);
+                part = (s == bounds[g]) ? x : GbFold<OP, A>::run(part, x);
+            }
+            A rounded = gb_up<T>(gb_down<T>(part));
+            total = (g == 0) ? rounded : GbFold<OP, A>::run(total, rounded);
+        }
+        out[i] = gb_down<T>(divide > 0 ? gb_divide<A>(total, divide) : total);
+    }
+}
+
+// Zero [lo, hi) bytes of a 16-byte aligned buffer with the whole grid.
+__device__ __forceinline__ void zero_range(char* base, size_t lo, size_t hi) {
+    if (hi <= lo) return;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    size_t head = round_up(lo, 16);
+    if (head > hi) head = hi;
+    if (tid < head - lo) base[lo + tid] = 0;
+    const size_t nv = (hi - head) >> 4;
+    for (size_t i = tid; i < nv; i += nth) gb_st16(base + head + (i << 4), make_uint4(0, 0, 0, 0));
+    for (size_t b = head + (nv << 4) + tid; b < hi; b += nth) base[b] = 0;
+}
+
+// ---- one-shot all-reduce ----------------------------------------------------------------------
+// Region A: [2 parities][world slots] of len_a / world bytes each.
+template <typename T, int OP>
+__global__ void __launch_bounds__(THREADS)
+allreduce_oneshot_kernel(GbTeam tm, GbArgs a) {
+    const unsigned parity = gb_ld_volatile(&tm.ctrl->epoch) & 1u;
+    const size_t nbytes = a.n * sizeof(T);
+    const size_t base = a.off_a + parity * a.len_a;
+    const size_t slot = a.len_a / (size_t)tm.world;
+    for (int d = 0; d < tm.world; ++d) {
+        const int peer = (tm.rank + d) % tm.world;
+        gb_copy_bytes(tm.ws[peer] + base + (size_t)tm.rank * slot, a.in, nbytes, false);
+    }
+    if (!gb_sync_all(tm, 0, true)) return;
+    reduce_slots<T, OP>(tm.ws[tm.rank] + base, slot, tm.order, tm.island_off, tm.n_islands,
+                        a.n, static_cast<T*>(a.out), a.divide);
+}
+
+// ---- hierarchical all-reduce ------------------------------------------------------------------
+// Region A: [2][island slots] of stripe bytes     (step A targets, on the owner)
+// Region B: [2][n_islands] of payload bytes       (step B targets, on the owner)
+// Region C: [2] of stripe bytes                   (step C output, on the owner)
+template <typename T, int CODEC> __host__ __device__ inline size_t payload_bytes(size_t stripe) {
+    if (CODEC == GB_RAW) return stripe * sizeof(T);
+    if (CODEC == GB_C_BF16) return stripe * 2;
+    return (stripe + 4 * (stripe / GbBlock<CODEC>::size) + 15) / 16 * 16;   // codes, then scales
+}
+
+template <typename T> __device__ __forceinline__ T coded_out(float v) { return (T)v; }
+template <> __device__ __forceinline__ float coded_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ double coded_out<double>(float v) { return (double)v; }
+template <> __device__ __forceinline__ __half coded_out<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 coded_out<__nv_bfloat16>(float v) {
+    __nv_bfloat16_raw raw;
+    raw.x = (unsigned short)gb_bf16_bits(v);
+    return __nv_bfloat16(raw);
+}
+
+template <typename T> __device__ __forceinline__ float as_float_sat(T v, bool& finite) {
+    float x = (float)gb_up<T>(v);
+    finite = isfinite(x);
+    return x;
+}
+template <> __device__ __forceinline__ float as_float_sat<double>(double v, bool& finite) {
+    finite = isfinite(v);
+    if (!finite) return (float)v;
+    return __double2float_rn(fmin(fmax(v, -(double)GB_FLT_MAX), (double)GB_FLT_MAX));
+}
+
+// Step B without compression: reduce the island's slots, round to T, store into every owner
+// (or, with a single island, straight into the result buffer with AVG applied).
+template <typename T, int OP>
+__device__ __forceinline__ void island_reduce_raw(const GbTeam& tm, const GbArgs& a,
+                                                  const char* slots, size_t count, int buf) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = Vec<T>::N;
+    const int m = tm.island_off[tm.my_island + 1] - tm.island_off[tm.my_island];
+    const bool bridged = tm.n_islands > 1;
+    const size_t sbytes = a.stripe * sizeof(T);
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    const size_t nvec = count / V;                       // count is a multiple of 256
+    for (size_t v = tid; v < nvec; v += nth) {
+        A part[V];
+        for (int p = 0; p < m; ++p) {
+            Vec<T> w;
+            w.u = gb_ld16(slots + (size_t)p * sbytes + v * 16);
+            #pragma unroll
+            for (int j = 0; j < V; ++j)
+                part[j] = (p == 0) ? gb_up<T>(w.e[j]) : GbFold<OP, A>::run(part[j], gb_up<T>(w.e[j]));
+        }
+        Vec<T> r;
+        #pragma unroll
+        for (int j = 0; j < V; ++j) r.e[j] = gb_down<T>(part[j]);
+        if (!bridged) {
+            if (a.divide > 0) {
+                #pragma unroll
+                for (int j = 0; j < V; ++j)
+                    r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
+            }
+            gb_st16(tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c + v * 16, r.u);
+        } else {
+            for (int d = 0; d < tm.n_islands; ++d) {
+                const int isl = (tm.my_island + d) % tm.n_islands;
+                const int owner = tm.order[tm.island_off[isl] + tm.my_pos];
+                gb_st16(tm.ws[owner] + a.off_b + (size_t)buf * a.len_b
+                        + (size_t)tm.my_island * sbytes + v * 16, r.u);
+            }
+        }
+    }
+}
+
+// EPL consecutive values of type T, read past L1, as floats (saturated for double).
+template <typename T, int EPL>
+__device__ __forceinline__ void load_run(const T* src, float (&x)[EPL], bool (&fin)[EPL], bool first,
+                                         float (&acc)[EPL]) {
+    constexpr int BYTES = EPL * (int)sizeof(T);
+    union { uint4 q[(BYTES + 15) / 16]; uint2 d; T e[EPL]; } w;
+    if (BYTES >= 16) {
+        #pragma unroll
+        for (int g = 0; g < BYTES / 16; ++g) w.q[g] = gb_ld16(reinterpret_cast<const char*>(src) + 16 * g);
+    } else {
+        asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];"
+                     : "=r"(w.d.x), "=r"(w.d.y) : "l"(src) : "memory");
+    }
+    #pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        x[j] = as_float_sat<T>(w.e[j], fin[j]);
+        acc[j] = first ? x[j] : __fadd_rn(acc[j], x[j]);
+    }
+}
+
+// Step B with compression: one warp per quantisation block; payload = codes, then scales.
+template <typename T, int CODEC>
+__device__ __forceinline__ void island_reduce_coded(const GbTeam& tm, const GbArgs& a,
+                                                    const char* slots, size_t count, int buf,
+                                                    float* residual) {
+    constexpr int BS = GbBlock<CODEC>::size;
+    constexpr int EPL = BS / 32;
+    const int m = tm.island_off[tm.my_island + 1] - tm.island_off[tm.my_island];
+    const size_t sbytes = a.stripe * sizeof(T);
+    const size_t pbytes = payload_bytes<T, CODEC>(a.stripe);
+    const int lane = threadIdx.x & 31;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t nblk = count / BS;
+    for (size_t blk = warp; blk < nblk; blk += nwarps) {
+        const size_t i0 = blk * BS + (size_t)lane * EPL;
+        float v[EPL], acc[EPL]; bool fin[EPL];
+        for (int p = 0; p < m; ++p)
+            load_run<T, EPL>(reinterpret_cast<const T*>(slots + (size_t)p * sbytes) + i0, v, fin,
+                             p == 0, acc);
+        float amax = 0.0f;
+        #pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            // the island result in T, as the uncompressed path would hand it to the bridge
+            bool xf;
+            float x = as_float_sat<T>(gb_down<T>((typename GbAcc<T>::type)acc[j]), xf);
+            bool f;
+            v[j] = gb_prepare(x, xf, residual[i0 + j], f);
+            fin[j] = f;
+            if (f) amax = fmaxf(amax, fabsf(v[j]));
+        }
+        if (CODEC == GB_C_BF16) {
+            unsigned words[EPL / 2];
+            #pragma unroll
+            for (int j = 0; j < EPL; ++j) {
+                unsigned code = gb_bf16_code(v[j], fin[j]);
+                residual[i0 + j] = fin[j] ? __fsub_rn(v[j], gb_from_bf16_bits(code)) : 0.0f;
+                if (j & 1) words[j / 2] |= code << 16; else words[j / 2] = code;
+            }
+            for (int d = 0; d < tm.n_islands; ++d) {
+                const int isl = (tm.my_island + d) % tm.n_islands;
+                const int owner = tm.order[tm.island_off[isl] + tm.my_pos];
+                char* dst = tm.ws[owner] + a.off_b + (size_t)buf * a.len_b
+                            + (size_t)tm.my_island * pbytes + i0 * 2;
+                gb_st16(dst, make_uint4(words[0], words[1], words[2], words[3]));
+            }
+        } else {
+            amax = gb_warp_max(amax);
+            float scale, mult;
+            gb_block_scale<CODEC>(amax, scale, mult);
+            unsigned words[2] = {0u, 0u};
+            #pragma unroll
+            for (int j = 0; j < EPL; ++j) {
+                unsigned code = fin[j] ? gb_e4m3_encode(__fmul_rn(v[j], mult)) : 0x7Fu;
+                float sent = __fmul_rn(gb_e4m3_decode(code), scale);
+                residual[i0 + j] = fin[j] ? __fsub_rn(v[j], sent) : 0.0f;
+                words[j / 4] |= code << (8 * (j & 3));
+            }
+            for (int d = 0; d < tm.n_islands; ++d) {
+                const int isl = (tm.my_island + d) % tm.n_islands;
+                const int owner = tm.order[tm.island_off[isl] + tm.my_pos];
+                char* dst = tm.ws[owner] + a.off_b + (size_t)buf * a.len_b
+                            + (size_t)tm.my_island * pbytes;
+                if (EPL == 8) *reinterpret_cast<uint2*>(dst + i0) = make_uint2(words[0], words[1]);
+                else *reinterpret_cast<unsigned*>(dst + i0) = words[0];
+                if (lane == 0) reinterpret_cast<float*>(dst + a.stripe)[blk] = scale;
+            }
+        }
+    }
+}
+
+// Step C: add the island results in island order, AVG, round once, into region C.
+template <typename T, int OP, int CODEC>
+__device__ __forceinline__ void bridge_reduce(const GbTeam& tm, const GbArgs& a, size_t count,
+                                              int buf) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = Vec<T>::N;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    const size_t pbytes = payload_bytes<T, CODEC>(a.stripe);
+    const char* parts = tm.ws[tm.rank] + a.off_b + (size_t)buf * a.len_b;
+    char* result = tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c;
+    const size_t nvec = count / V;
+    for (size_t v = tid; v < nvec; v += nth) {
+        Vec<T> r;
+        if (CODEC == GB_RAW) {
+            A total[V];
+            for (int g = 0; g < tm.n_islands; ++g) {
+                Vec<T> w;
+                w.u = gb_ld16(parts + (size_t)g * pbytes + v * 16);
+                #pragma unroll
+                for (int j = 0; j < V; ++j)
+                    total[j] = (g == 0) ? gb_up<T>(w.e[j])
+                                        : GbFold<OP, A>::run(total[j], gb_up<T>(w.e[j]));
+            }
+            #pragma unroll
+            for (int j = 0; j < V; ++j)
+                r.e[j] = gb_down<T>(a.divide > 0 ? gb_divide<A>(total[j], a.divide) : total[j]);
+        } else {
+            float acc[V];
+            #pragma unroll
+            for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+            const size_t e0 = v * V;
+            for (int g = 0; g < tm.n_islands; ++g) {
+                const char* row = parts + (size_t)g * pbytes;
+                if (CODEC == GB_C_BF16) {
+                    #pragma unroll
+                    for (int j = 0; j < V; j += 2) {
+                        unsigned w = *reinterpret_cast<const volatile unsigned*>(row + (e0 + j) * 2);
+                        acc[j] = gb_flush(__fadd_rn(acc[j], gb_from_bf16_bits(w & 0xFFFFu)));
+                        acc[j + 1] = gb_flush(__fadd_rn(acc[j + 1], gb_from_bf16_bits(w >> 16)));
+                    }
+                } else {
+                    const float scale = reinterpret_cast<const volatile float*>(row + a.stripe)
+                        [e0 / GbBlock<CODEC>::size];
+                    if (V >= 4) {
+                        #pragma unroll
+                        for (int j = 0; j < V; j += 4) {
+                            unsigned w = *reinterpret_cast<const volatile unsigned*>(row + e0 + j);
+                            #pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                if (j + q < V) {
+                                    float d = __fmul_rn(gb_e4m3_decode((w >> (8 * q)) & 0xFFu), scale);
+                                    acc[j + q] = gb_flush(__fadd_rn(acc[j + q], d));
+                                }
+                            }
+                        }
+                    } else {                              // double: two codes per vector
+                        #pragma unroll
+                        for (int j = 0; j < V; ++j) {
+                            unsigned c = *reinterpret_cast<const volatile unsigned char*>(row + e0 + j);
+                            float d = __fmul_rn(gb_e4m3_decode(c), scale);
+                            acc[j] = gb_flush(__fadd_rn(acc[j], d));
+                        }
+                    }
+                }
+            }
+            #pragma unroll
+            for (int j = 0; j < V; ++j)
+                r.e[j] = coded_out<T>(a.divide > 0 ? __fdiv_rn(acc[j], (float)a.divide) : acc[j]);
+        }
+        gb_st16(result + v * 16, r.u);
+    }
+}
+
+template <typename T, int OP, int CODEC>
+__global__ void __launch_bounds__(THREADS)
+allreduce_hier_kernel(GbTeam tm, GbArgs a) {
+    const T* in = static_cast<const T*>(a.in);
+    T* out = static_cast<T*>(a.out);
+    const bool owner = tm.my_pos < a.k;
+    const bool bridged = tm.n_islands > 1;
+    const size_t sbytes = a.stripe * sizeof(T);
+    const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    const int depth = bridged ? 3 : 2;                   // iterations between A and D
+    const long iters = nchunks + depth;
+    for (long t = 0; t < iters; ++t) {
+        if (t < nchunks) {                               // A(t)
+            const size_t c0 = (size_t)t * a.chunk;
+            for (int dj = 0; dj < a.k; ++dj) {
+                const int j = (tm.my_pos + dj) % a.k;
+                const int own = tm.order[tm.island_off[tm.my_island] + j];
+                char* dst = tm.ws[own] + a.off_a + (size_t)(t & 1) * a.len_a
+                            + (size_t)tm.my_pos * sbytes;
+                const size_t valid = stripe_valid(a, c0, j);
+                if (valid)
+                    gb_copy_bytes(dst, in + c0 + (size_t)j * a.stripe, valid * sizeof(T), false);
+                // zeros up to the next quantisation block: padding reduces only with padding
+                zero_range(dst, valid * sizeof(T), round_up(valid, 256) * sizeof(T));
+            }
+        }
+        if (owner && t >= 1 && t - 1 < nchunks) {        // B(t-1)
+            const long c = t - 1;
+            const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
+            const char* slots = tm.ws[tm.rank] + a.off_a + (size_t)(c & 1) * a.len_a;
+            if (CODEC == GB_RAW)
+                island_reduce_raw<T, OP>(tm, a, slots, need, (int)(c & 1));
+            else
+                island_reduce_coded<T, CODEC>(tm, a, slots, need, (int)(c & 1),
+                                              a.residual + (size_t)c * a.stripe);
+        }
+        if (bridged && owner && t >= 2 && t - 2 < nchunks) {   // C(t-2)
+            const long c = t - 2;
+            const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
+            bridge_reduce<T, OP, CODEC>(tm, a, need, (int)(c & 1));
+        }
+        if (t >= depth) {                                // D(t-depth)
+            const long c = t - depth;
+            const size_t c0 = (size_t)c * a.chunk;
+            for (int dj = 0; dj < a.k; ++dj) {
+                const int j = (tm.my_pos + dj) % a.k;
+                const int own = tm.order[tm.island_off[tm.my_island] + j];
+                const size_t valid = stripe_valid(a, c0, j);
+                if (valid)
+                    gb_copy_bytes(out + c0 + (size_t)j * a.stripe,
+                                  tm.ws[own] + a.off_c + (size_t)(c & 1) * a.len_c,
+                                  valid * sizeof(T), true);
+            }
+        }
+        if (t + 1 < iters && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
+    }
+}
+
+// ---- all-gather ---------------------------------------------------------------------------------
+// Region A: [2 parities][2 chunk buffers] of len_a bytes.  n and chunk are bytes.
+__global__ void __launch_bounds__(THREADS)
+allgather_kernel(GbTeam tm, GbArgs a) {
+    const unsigned parity = gb_ld_volatile(&tm.ctrl->epoch) & 1u;
+    const char* in = static_cast<const char*>(a.in);
+    char* out = static_cast<char*>(a.out);
+    const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    for (long t = 0; t <= nchunks; ++t) {
+        if (t < nchunks) {
+            const size_t c0 = (size_t)t * a.chunk;
+            const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
+            gb_copy_bytes(tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
+                          in + c0, len, false);
+        }
+        if (t >= 1) {
+            const long c = t - 1;
+            const size_t c0 = (size_t)c * a.chunk;
+            const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
+            for (int d = 0; d < tm.world; ++d) {
+                const int peer = (tm.rank + d) % tm.world;
+                gb_copy_bytes(out + (size_t)peer * a.n + c0,
+                              tm.ws[peer] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
+                              len, true);
+            }
+        }
+        if (t < nchunks && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
+    }
+}
+
+// ---- reduce-scatter -------------------------------------------------------------------------------
+// Region A: [2 parities][2 chunk buffers][world slots] ; len_a = world * chunk bytes.
+// n: elements of one slice; chunk: elements per step.
+template <typename T, int OP>
+__global__ void __launch_bounds__(THREADS)
+reduce_scatter_kernel(GbTeam tm, GbArgs a) {
+    const unsigned parity = gb_ld_volatile(&tm.ctrl->epoch) & 1u;
+    const T* in = static_cast<const T*>(a.in);
+    T* out = static_cast<T*>(a.out);
+    const size_t slot = a.chunk * sizeof(T);
+    const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    for (long t = 0; t <= nchunks; ++t) {
+        if (t < nchunks) {
+            const size_t c0 = (size_t)t * a.chunk;
+            const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
+            for (int d = 0; d < tm.world; ++d) {
+                const int owner = (tm.rank + d) % tm.world;
+                gb_copy_bytes(tm.ws[owner] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a
+                              + (size_t)tm.rank * slot,
+                              in + (size_t)owner * a.n + c0, len * sizeof(T), false);
+            }
+        }
+        if (t >= 1) {
+            const long c = t - 1;
+            const size_t c0 = (size_t)c * a.chunk;
+            const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
+            reduce_slots<T, OP>(tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
+                                slot, tm.order, tm.island_off, tm.n_islands, len, out + c0, a.divide);
+        }
+        if (t < nchunks && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
+    }
+}
+
+// ---- broadcast --------------------------------------------------------------------------------------
+// Region A: [2 parities][2 chunk buffers] of len_a = stripe bytes.  n, chunk, stripe are bytes
+// (chunk = world * stripe).  `out` is the tensor on every rank (the data on the source).
+__global__ void __launch_bounds__(THREADS)
+broadcast_kernel(GbTeam tm, GbArgs a) {
+    const unsigned parity = gb_ld_volatile(&tm.ctrl->epoch) & 1u;
+    char* data = static_cast<char*>(a.out);
+    const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    for (long t = 0; t <= nchunks; ++t) {
+        if (t < nchunks && tm.rank == a.root) {
+            const size_t c0 = (size_t)t * a.chunk;
+            for (int d = 0; d < tm.world; ++d) {
+                const int j = (tm.rank + d) % tm.world;
+                const size_t s0 = c0 + (size_t)j * a.stripe;
+                if (s0 >= a.n) continue;
+                const size_t len = a.n - s0 < a.stripe ? a.n - s0 : a.stripe;
+                gb_copy_bytes(tm.ws[j] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
+                              data + s0, len, false);
+            }
+        }
+        if (t >= 1 && tm.rank != a.root) {
+            const long c = t - 1;
+            const size_t c0 = (size_t)c * a.chunk;
+            for (int d = 0; d < tm.world; ++d) {
+                const int j = (tm.rank + d) % tm.world;
+                const size_t s0 = c0 + (size_t)j * a.stripe;
+                if (s0 >= a.n) continue;
+                const size_t len = a.n - s0 < a.stripe ? a.n - s0 : a.stripe;
+                gb_copy_bytes(data + s0,
+                              tm.ws[j] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
+                              len, true);
+            }
+        }
+        if (t < nchunks && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
+    }
+}
+
+__global__ void __launch_bounds__(THREADS)
+barrier_kernel(GbTeam tm) {
+    gb_sync_all(tm, 0, true);
+}
+
+// ---- dispatch -----------------------------------------------------------------------------------------
+template <typename T, int OP>
+cudaError_t launch_plain(int kind, const GbTeam& tm, const GbArgs& a, int grid, cudaStream_t s) {
+    if (kind == 0) allreduce_oneshot_kernel<T, OP><<<grid, THREADS, 0, s>>>(tm, a);
+    else if (kind == 1) allreduce_hier_kernel<T, OP, GB_RAW><<<grid, THREADS, 0, s>>>(tm, a);
+    else if (kind == 2) reduce_scatter_kernel<T, OP><<<grid, THREADS, 0, s>>>(tm, a);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_op(int kind, int op, const GbTeam& tm, const GbArgs& a, int grid, cudaStream_t s) {
+    if (op == GB_SUM) return launch_plain<T, GB_SUM>(kind, tm, a, grid, s);
+    if (kind == 2) return cudaErrorInvalidValue;            // reduce-scatter: SUM only
+    if (op == GB_MAX) return launch_plain<T, GB_MAX>(kind, tm, a, grid, s);
+    if (op == GB_MIN) return launch_plain<T, GB_MIN>(kind, tm, a, grid, s);
+    return cudaErrorInvalidValue;
+}
+
+template <typename T>
+cudaError_t launch_coded(int codec, const GbTeam& tm, const GbArgs& a, int grid, cudaStream_t s) {
+    if (codec == GB_C_FP8_REF)
+        allreduce_hier_kernel<T, GB_SUM, GB_C_FP8_REF><<<grid, THREADS, 0, s>>>(tm, a);
+    else if (codec == GB_C_FP8_B200)
+        allreduce_hier_kernel<T, GB_SUM, GB_C_FP8_B200><<<grid, THREADS, 0, s>>>(tm, a);
+    else if (codec == GB_C_BF16 && sizeof(T) >= 4)
+        allreduce_hier_kernel<T, GB_SUM, GB_C_BF16><<<grid, THREADS, 0, s>>>(tm, a);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// kind: 0 one-shot all-reduce, 1 hierarchical all-reduce, 2 reduce-scatter.
+// codec (kind 1, SUM, floating point only): GbCodec.  Returns a cudaError_t.
+extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const GbTeam* team,
+                                const GbArgs* args, int grid, cudaStream_t stream) {
+    const GbTeam& tm = *team;
+    const GbArgs& a = *args;
+    if (codec != GB_RAW) {
+        if (kind != 1 || op != GB_SUM) return cudaErrorInvalidValue;
+        switch (dtype) {
+            case GB_F32: return launch_coded<float>(codec, tm, a, grid, stream);
+            case GB_F64: return launch_coded<double>(codec, tm, a, grid, stream);
+            case GB_BF16: return launch_coded<__nv_bfloat16>(codec, tm, a, grid, stream);
+            case GB_F16: return launch_coded<__half>(codec, tm, a, grid, stream);
+        }
+        return cudaErrorInvalidValue;
+    }
+    switch (dtype) {
+        case GB_F32: return launch_op<float>(kind, op, tm, a, grid, stream);
+        case GB_BF16: return launch_op<__nv_bfloat16>(kind, op, tm, a, grid, stream);
+        case GB_F16: return launch_op<__half>(kind, op, tm, a, grid, stream);
+        case GB_F64: return launch_op<double>(kind, op, tm, a, grid, stream);
+        case GB_I8: return launch_op<signed char>(kind, op, tm, a, grid, stream);
+        case GB_U8: return launch_op<unsigned char>(kind, op, tm, a, grid, stream);
+        case GB_I32: return launch_op<int>(kind, op, tm, a, grid, stream);
+        case GB_I64: return launch_op<long long>(kind, op, tm, a, grid, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// kind: 0 all-gather, 1 broadcast, 2 barrier.
+extern "C" int gb_launch_copy(int kind, const GbTeam* team, const GbArgs* args, int grid,
+                              cudaStream_t stream) {
+    if (kind == 0) allgather_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
+    else if (kind == 1) broadcast_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
+    else if (kind == 2) barrier_kernel<<<1, THREADS, 0, stream>>>(*team);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+extern "C" size_t gb_sizeof_team() { return sizeof(GbTeam); }
+extern "C" size_t gb_sizeof_args() { return sizeof(GbArgs); }
+extern "C" size_t gb_sizeof_ctrl() { return sizeof(GbCtrl); }
+extern "C" size_t gb_payload_bytes(int codec, int elem_size, size_t stripe) {
+    if (codec == GB_RAW) return stripe * (size_t)elem_size;
+    if (codec == GB_C_BF16) return stripe * 2;
+    const size_t bs = codec == GB_C_FP8_B200 ? 128 : 256;
+    return (stripe + 4 * (stripe / bs) + 15) / 16 * 16;
+}

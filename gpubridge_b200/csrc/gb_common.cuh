@@ -1,0 +1,258 @@
+// Shared device-side definitions of the fabric kernels (sm_100a).
+//
+// A "team" is the group of ranks one collective runs over.  Every rank owns a symmetric
+// workspace that is mapped into every peer (CUDA IPC or cuMem handles), so a kernel can
+// store into and load from any peer's workspace over NVLink.  All synchronisation between
+// GPUs goes through one primitive, gb_sync_all(): a grid barrier on this GPU whose last
+// arriving block also runs a barrier with every peer (a release store of a sequence number
+// into each peer's flag row, an acquire poll of the own row).  Every wait is bounded by a
+// spin limit and a globaltimer deadline; when one runs out the kernel records
+// {code, peer, sequence, phase} in a host-mapped status block, raises the abort word and
+// returns normally - it never traps and never spins forever.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#define GB_MAX_RANKS 16
+#define GB_FLAG_BYTES 4096          // start of every workspace: the flag rows
+#define GB_STATUS_WORDS 8
+
+// Local (not shared with peers) control block of one team.
+struct GbCtrl {
+    unsigned int grid_arrive;       // blocks that reached the current grid barrier
+    unsigned int grid_gen;          // grid barrier generation
+    unsigned int seq;               // last completed team barrier
+    unsigned int epoch;             // collectives completed (parity selects buffer halves)
+    unsigned int abort;             // a wait ran out in this or an earlier kernel
+    unsigned int pad[3];
+    unsigned long long stamps[8];   // globaltimer at the barriers of the last collective
+};
+
+struct GbTeam {
+    int rank, world;                // this rank's position in the team, team size
+    int n_islands;
+    int my_island, my_pos;          // island of this rank, position inside it
+    int island_off[GB_MAX_RANKS + 1];   // island i = order[island_off[i] .. island_off[i+1])
+    int order[GB_MAX_RANKS];        // team ranks sorted by (island, position)
+    char* ws[GB_MAX_RANKS];         // workspace base of every team rank (ws[rank] is local)
+    GbCtrl* ctrl;
+    volatile unsigned int* status;  // host-mapped: code, peer, seq, phase, ...
+    unsigned long long timeout_ns;
+};
+
+enum GbStatus { GB_OK = 0, GB_TIMEOUT_PEER = 1, GB_TIMEOUT_GRID = 2 };
+
+// ---- memory-order helpers ---------------------------------------------------------------
+__device__ __forceinline__ unsigned long long gb_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned int gb_ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void gb_st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int gb_ld_volatile(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// 16-byte load of data another GPU wrote (or that lives in a peer's memory): never from L1.
+__device__ __forceinline__ uint4 gb_ld16(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void gb_st16(void* p, uint4 v) {
+    asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ unsigned int* gb_flag_row(const GbTeam& tm, int owner) {
+    return reinterpret_cast<unsigned int*>(tm.ws[owner]);
+}
+
+__device__ __forceinline__ void gb_fail(const GbTeam& tm, unsigned code, unsigned peer,
+                                        unsigned seq, unsigned phase) {
+    if (atomicExch(&tm.ctrl->abort, 1u) == 0u) {
+        tm.status[1] = peer; tm.status[2] = seq; tm.status[3] = phase;
+        tm.status[4] = (unsigned)tm.rank;
+        __threadfence_system();
+        tm.status[0] = code;
+    }
+}
+
+// Poll `addr` until it reaches `want` (sequence numbers compare by signed difference).
+__device__ __forceinline__ bool gb_wait_flag(const GbTeam& tm, const unsigned int* addr,
+                                             unsigned want, bool sys, unsigned long long limit_ns) {
+    unsigned long long t0 = 0;
+    for (unsigned spins = 0;; ++spins) {
+        unsigned v = sys ? gb_ld_acquire_sys(addr) : gb_ld_volatile(addr);
+        if ((int)(v - want) >= 0) return true;
+        if (spins > 32) __nanosleep(spins > 4096 ? 400 : 40);
+        if ((spins & 255u) == 255u) {
+            unsigned long long now = gb_now();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_ns) return false;
+            if (gb_ld_volatile(&tm.ctrl->abort)) return false;
+        }
+        if (spins > 0x3fffffffu) return false;
+    }
+}
+
+// Grid barrier + team barrier.  Returns false when this or an earlier wait ran out; the
+// caller must then return without touching peers again.  `phase` only labels a failure.
+__device__ __forceinline__ bool gb_sync_all(const GbTeam& tm, unsigned phase, bool first) {
+    __shared__ unsigned s_gen, s_last, s_seq;
+    GbCtrl* c = tm.ctrl;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();                       // this block's stores, local and remote
+        s_gen = gb_ld_volatile(&c->grid_gen);         // read the generation before arriving
+        unsigned arrived = atomicAdd(&c->grid_arrive, 1u) + 1u;
+        s_last = (arrived == gridDim.x);
+        s_seq = gb_ld_volatile(&c->seq) + 1u;
+    }
+    __syncthreads();
+    if (s_last) {
+        // The last block to arrive meets the peers on behalf of the grid.
+        const unsigned seq = s_seq;
+        const int t = threadIdx.x;
+        if (t < tm.world && t != tm.rank) {
+            __threadfence_system();
+            gb_st_release_sys(gb_flag_row(tm, t) + tm.rank, seq);
+        }
+        if (t < tm.world && t != tm.rank) {
+            if (!gb_wait_flag(tm, gb_flag_row(tm, tm.rank) + t, seq, true, tm.timeout_ns))
+                gb_fail(tm, GB_TIMEOUT_PEER, (unsigned)t, seq, phase);
+        }
+        __syncthreads();
+        if (t == 0) {
+            c->seq = seq;
+            if (first) c->epoch += 1u;
+            if (phase < 8u) c->stamps[phase] = gb_now();
+            c->grid_arrive = 0u;
+            __threadfence();
+            atomicAdd(&c->grid_gen, 1u);              // release the grid
+        }
+    } else if (threadIdx.x == 0) {
+        if (!gb_wait_flag(tm, &c->grid_gen, s_gen + 1u, false, 2ull * tm.timeout_ns))
+            gb_fail(tm, GB_TIMEOUT_GRID, 0u, s_seq, phase);
+        __threadfence();
+    }
+    __syncthreads();
+    return gb_ld_volatile(&c->abort) == 0u;
+}
+
+// ---- element types -------------------------------------------------------------------------
+enum GbDtype { GB_F32 = 0, GB_BF16 = 1, GB_F16 = 2, GB_F64 = 3, GB_I8 = 4, GB_U8 = 5,
+               GB_I32 = 6, GB_I64 = 7 };
+enum GbOp { GB_SUM = 0, GB_MAX = 1, GB_MIN = 2 };
+
+template <typename T> struct GbAcc { typedef T type; };
+template <> struct GbAcc<__nv_bfloat16> { typedef float type; };
+template <> struct GbAcc<__half> { typedef float type; };
+
+template <typename T> __device__ __forceinline__ typename GbAcc<T>::type gb_up(T v) { return v; }
+template <> __device__ __forceinline__ float gb_up<__nv_bfloat16>(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+}
+template <> __device__ __forceinline__ float gb_up<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T gb_down(typename GbAcc<T>::type v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 gb_down<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ __half gb_down<__half>(float v) { return __float2half_rn(v); }
+
+template <int OP, typename A> __device__ __forceinline__ A gb_combine(A a, A b) {
+    if (OP == GB_SUM) return a + b;
+    if (OP == GB_MAX) return a > b ? a : b;
+    return a < b ? a : b;
+}
+// NaN propagates through MAX/MIN the way torch's maximum/minimum do.
+template <int OP> __device__ __forceinline__ float gb_combine_f(float a, float b) {
+    if (OP == GB_SUM) return __fadd_rn(a, b);
+    if (a != a) return a;
+    if (b != b) return b;
+    if (OP == GB_MAX) return a > b ? a : b;
+    return a < b ? a : b;
+}
+template <int OP> __device__ __forceinline__ double gb_combine_d(double a, double b) {
+    if (OP == GB_SUM) return a + b;
+    if (a != a) return a;
+    if (b != b) return b;
+    if (OP == GB_MAX) return a > b ? a : b;
+    return a < b ? a : b;
+}
+template <int OP, typename A> struct GbFold {
+    static __device__ __forceinline__ A run(A a, A b) { return gb_combine<OP, A>(a, b); }
+};
+template <int OP> struct GbFold<OP, float> {
+    static __device__ __forceinline__ float run(float a, float b) { return gb_combine_f<OP>(a, b); }
+};
+template <int OP> struct GbFold<OP, double> {
+    static __device__ __forceinline__ double run(double a, double b) { return gb_combine_d<OP>(a, b); }
+};
+
+// AVG: the sum divided by the team size, as one correctly rounded division.
+template <typename A> __device__ __forceinline__ A gb_divide(A v, int by) { return v / (A)by; }
+template <> __device__ __forceinline__ float gb_divide<float>(float v, int by) {
+    return __fdiv_rn(v, (float)by);
+}
+
+// ---- byte copies -----------------------------------------------------------------------------
+// Copy `nbytes` with the whole grid.  `peer_src`: the source was written by another GPU (or is
+// remote), so it is read past L1.  Falls back to narrower accesses for unaligned user tensors.
+__device__ __forceinline__ void gb_copy_bytes(void* dst, const void* src, size_t nbytes,
+                                              bool peer_src) {
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    char* d = static_cast<char*>(dst);
+    const char* s = static_cast<const char*>(src);
+    if ((((uintptr_t)d | (uintptr_t)s) & 15u) == 0) {
+        const size_t nv = nbytes >> 4;
+        size_t i = tid;
+        // four independent 16-byte transfers in flight per thread
+        for (; i + 3 * nth < nv; i += 4 * nth) {
+            uint4 a, b, c, e;
+            if (peer_src) {
+                a = gb_ld16(s + (i << 4)); b = gb_ld16(s + ((i + nth) << 4));
+                c = gb_ld16(s + ((i + 2 * nth) << 4)); e = gb_ld16(s + ((i + 3 * nth) << 4));
+            } else {
+                a = __ldg((const uint4*)(s + (i << 4))); b = __ldg((const uint4*)(s + ((i + nth) << 4)));
+                c = __ldg((const uint4*)(s + ((i + 2 * nth) << 4)));
+                e = __ldg((const uint4*)(s + ((i + 3 * nth) << 4)));
+            }
+            gb_st16(d + (i << 4), a); gb_st16(d + ((i + nth) << 4), b);
+            gb_st16(d + ((i + 2 * nth) << 4), c); gb_st16(d + ((i + 3 * nth) << 4), e);
+        }
+        for (; i < nv; i += nth) {
+            uint4 a = peer_src ? gb_ld16(s + (i << 4)) : __ldg((const uint4*)(s + (i << 4)));
+            gb_st16(d + (i << 4), a);
+        }
+        for (size_t b = (nv << 4) + tid; b < nbytes; b += nth)
+            d[b] = peer_src ? *(volatile const char*)(s + b) : s[b];
+        return;
+    }
+    if ((((uintptr_t)d | (uintptr_t)s) & 3u) == 0) {
+        const size_t nw = nbytes >> 2;
+        for (size_t i = tid; i < nw; i += nth) {
+            unsigned v = peer_src ? *(volatile const unsigned*)(s + (i << 2))
+                                  : *(const unsigned*)(s + (i << 2));
+            *(unsigned*)(d + (i << 2)) = v;
+        }
+        for (size_t b = (nw << 2) + tid; b < nbytes; b += nth)
+            d[b] = peer_src ? *(volatile const char*)(s + b) : s[b];
+        return;
+    }
+    for (size_t b = tid; b < nbytes; b += nth)
+        d[b] = peer_src ? *(volatile const char*)(s + b) : s[b];
+}

@@ -1,0 +1,92 @@
+"""Build the native library in-tree: ``gpubridge_b200/lib/libgpubridge_b200.so``.
+
+Every ``.cu`` under ``csrc/`` is compiled for sm_100a only
+(``-gencode arch=compute_100a,code=sm_100a``) and linked into one shared library that the
+Python side loads with ``ctypes``; the kernels take raw pointers and a ``cudaStream_t``,
+so neither torch's headers nor pybind11 are involved and a full rebuild takes well under a
+minute.  Objects are cached by source hash under ``gpubridge_b200/_build``.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.dirname(HERE)
+CSRC = os.path.join(PKG, "csrc")
+OBJ = os.path.join(PKG, "_build")
+LIB_DIR = os.path.join(PKG, "lib")
+LIB = os.path.join(LIB_DIR, "libgpubridge_b200.so")
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--use_fast_math=false", "-Xcompiler", "-fPIC",
+              "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr"]
+
+
+def nvcc() -> str:
+    for candidate in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if candidate and os.path.exists(candidate):
+            return candidate
+    raise RuntimeError("nvcc not found; the native library needs the CUDA 12.9 toolkit")
+
+
+def sources() -> list[str]:
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+
+
+def _digest(path: str) -> str:
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(CSRC)):
+        if name.endswith((".cuh", ".h")) or os.path.join(CSRC, name) == path:
+            with open(os.path.join(CSRC, name), "rb") as fh:
+                h.update(name.encode() + b"\0" + fh.read())
+    h.update(" ".join(ARCH + NVCC_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def _compile(path: str, verbose: bool) -> str:
+    obj = os.path.join(OBJ, f"{os.path.basename(path)}.{_digest(path)}.o")
+    if os.path.exists(obj):
+        return obj
+    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    cmd = [nvcc(), *ARCH, *flags, "-I", CSRC, "-c", path, "-o", obj + ".tmp"]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    done = subprocess.run(cmd, capture_output=True, text=True)
+    if done.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {path}:\n{done.stdout}\n{done.stderr}")
+    if verbose:
+        sys.stderr.write(done.stderr)
+    os.replace(obj + ".tmp", obj)
+    return obj
+
+
+def build(verbose: bool = False, force: bool = False) -> str:
+    """Compile what changed and link the library; returns its path."""
+    os.makedirs(OBJ, exist_ok=True)
+    os.makedirs(LIB_DIR, exist_ok=True)
+    if force:
+        for name in os.listdir(OBJ):
+            os.remove(os.path.join(OBJ, name))
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        objects = list(pool.map(lambda p: _compile(p, verbose), sources()))
+    stamp = os.path.join(OBJ, "linked.txt")
+    want = "\n".join(objects)
+    if os.path.exists(LIB) and os.path.exists(stamp) and open(stamp).read() == want:
+        return LIB
+    cmd = [nvcc(), *ARCH, "-shared", "-cudart", "shared", "-o", LIB + ".tmp", *objects]
+    done = subprocess.run(cmd, capture_output=True, text=True)
+    if done.returncode != 0:
+        raise RuntimeError(f"linking {LIB} failed:\n{done.stdout}\n{done.stderr}")
+    os.replace(LIB + ".tmp", LIB)
+    with open(stamp, "w") as fh:
+        fh.write(want)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv, force="--force" in sys.argv))

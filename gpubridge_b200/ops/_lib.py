@@ -1,0 +1,105 @@
+"""ctypes binding of the native library.
+
+The library is built in-tree by :mod:`gpubridge_b200.ops._build`.  It is loaded after
+``import torch`` so the CUDA runtime torch ships is the one both share; kernels receive
+``tensor.data_ptr()`` values and the current stream's ``cudaStream_t``.  On a machine with
+a GPU a missing library is an error (it is built on the spot if a compiler is there):
+nothing silently falls back to eager PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch  # noqa: F401 - loads libcudart before the library below
+
+from gpubridge_b200.ops import _build
+
+MAX_RANKS = 16
+STATUS_WORDS = 8
+
+DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.float64: 3,
+          torch.int8: 4, torch.uint8: 5, torch.int32: 6, torch.int64: 7}
+OPS = {"sum": 0, "max": 1, "min": 2}
+CODECS = {None: 0, ("bf16", "ref"): 1, ("bf16", "b200"): 1, ("fp8", "ref"): 2, ("fp8", "b200"): 3}
+
+
+class GbTeam(ctypes.Structure):
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("n_islands", ctypes.c_int),
+                ("my_island", ctypes.c_int), ("my_pos", ctypes.c_int),
+                ("island_off", ctypes.c_int * (MAX_RANKS + 1)),
+                ("order", ctypes.c_int * MAX_RANKS),
+                ("ws", ctypes.c_void_p * MAX_RANKS),
+                ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
+                ("timeout_ns", ctypes.c_ulonglong)]
+
+
+class GbArgs(ctypes.Structure):
+    _fields_ = [("inp", ctypes.c_void_p), ("out", ctypes.c_void_p), ("n", ctypes.c_size_t),
+                ("chunk", ctypes.c_size_t), ("stripe", ctypes.c_size_t), ("k", ctypes.c_int),
+                ("divide", ctypes.c_int), ("root", ctypes.c_int), ("pad", ctypes.c_int),
+                ("off_a", ctypes.c_size_t), ("off_b", ctypes.c_size_t), ("off_c", ctypes.c_size_t),
+                ("len_a", ctypes.c_size_t), ("len_b", ctypes.c_size_t), ("len_c", ctypes.c_size_t),
+                ("residual", ctypes.c_void_p)]
+
+
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+
+
+def available() -> bool:
+    return os.path.exists(_build.LIB)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; builds it first when it is missing and nvcc is there."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(_build.LIB):
+            _build.build()
+        loaded = ctypes.CDLL(_build.LIB)
+        _declare(loaded)
+        if loaded.gb_sizeof_team() != ctypes.sizeof(GbTeam) or \
+                loaded.gb_sizeof_args() != ctypes.sizeof(GbArgs):
+            raise RuntimeError("the native library's structures do not match ops/_lib.py; "
+                               "rebuild with python -m gpubridge_b200.ops._build --force")
+        _lib = loaded
+        return loaded
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    vp, sz, i = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    L.gb_error_string.restype = ctypes.c_char_p
+    L.gb_error_string.argtypes = [i]
+    for name in ("gb_sizeof_team", "gb_sizeof_args", "gb_sizeof_ctrl"):
+        getattr(L, name).restype = sz
+        getattr(L, name).argtypes = []
+    L.gb_payload_bytes.restype = sz
+    L.gb_payload_bytes.argtypes = [i, i, sz]
+    L.gb_symm_alloc.argtypes = [sz, ctypes.POINTER(vp)]
+    L.gb_symm_free.argtypes = [vp]
+    L.gb_symm_export.argtypes = [vp, ctypes.c_char_p]
+    L.gb_symm_import.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    L.gb_symm_unmap.argtypes = [vp]
+    L.gb_can_access_peer.argtypes = [i, i, ctypes.POINTER(i)]
+    L.gb_status_alloc.argtypes = [sz, ctypes.POINTER(vp)]
+    L.gb_status_free.argtypes = [vp]
+    L.gb_memset_async.argtypes = [vp, i, sz, vp]
+    L.gb_launch_reduce.argtypes = [i, i, i, i, ctypes.POINTER(GbTeam), ctypes.POINTER(GbArgs),
+                                   i, vp]
+    L.gb_launch_copy.argtypes = [i, ctypes.POINTER(GbTeam), ctypes.POINTER(GbArgs), i, vp]
+    L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
+    L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        text = lib().gb_error_string(code).decode()
+        raise RuntimeError(f"gpubridge native call {what} failed: {text} (CUDA error {code})")
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

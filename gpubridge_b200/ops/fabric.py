@@ -1,0 +1,435 @@
+"""The NVLink fabric of one team: symmetric workspaces and the fused collective kernels.
+
+A team is the set of ranks one group's collectives run over (the world, or a subgroup).
+Every rank allocates one workspace, exports it, and maps every peer's (CUDA IPC handles
+exchanged through the job's store).  The kernels in ``csrc/gb_collectives.cu`` then move
+data with plain loads and stores to peer memory from inside the kernel, synchronise with
+flags in the workspaces, and reduce, quantise, average and cast in the same launch.  This
+replaces the reference's island ``dist.reduce`` + host-staged bridge + island
+``dist.broadcast`` (src/gpubridge/policies.py:342-357) and the separate ``div_`` for AVG
+(src/gpubridge/collectives.py:103).
+
+All kernels of a team run on one communication stream, in program order, which must be
+the same on every rank (the usual rule for collectives).  Calls made on another stream
+are ordered with events both ways, so the caller sees current-stream semantics.
+
+Device-side waits are bounded (``GPUBRIDGE_WAIT_TIMEOUT_MS``, default 30 s).  When one
+runs out the kernel writes a status record to mapped host memory and returns;
+:meth:`Fabric.check` turns it into an exception and poisons the rank, like a failed async
+collective.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+import time
+from datetime import timedelta
+
+import torch
+
+from gpubridge_b200 import config as _config
+from gpubridge_b200 import work as _work
+from gpubridge_b200.ops import _lib
+
+MIB = 1 << 20
+FLAG_BYTES = 4096
+ONESHOT_MAX = 256 << 10          # largest tensor the one-shot kernel takes
+DEFAULT_BYTES = 384 * MIB
+THREADS = 512
+
+
+def _align_down(value: int, multiple: int) -> int:
+    return value // multiple * multiple
+
+
+def _align_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+class FabricError(RuntimeError):
+    """A device-side wait of a fused collective ran out, or the team was poisoned."""
+
+
+class Fabric:
+    """One rank's side of a team.  Build with :func:`create`."""
+
+    def __init__(self, lib, layout, rank: int, device: torch.device, ws: list[int],
+                 ws_bytes: int, ctrl: int, status: int, timeout_ms: int, store=None,
+                 key: str = "") -> None:
+        self.lib, self.layout, self.device = lib, layout, device
+        self._store, self._key = store, key
+        self.global_rank = rank
+        self.rank = layout.index(rank)
+        self.world = layout.world_size
+        self.ws, self.ws_bytes, self.ctrl, self.status = ws, ws_bytes, ctrl, status
+        self.comm_stream = torch.cuda.Stream(device, priority=-1)
+        self.max_blocks = int(os.environ.get("GPUBRIDGE_FABRIC_BLOCKS", "64"))
+        self.algo = _config.algo_setting()
+        self._status = (ctypes.c_uint * _lib.STATUS_WORDS).from_address(status)
+        self._residuals: dict[tuple, tuple[torch.Tensor, tuple]] = {}
+        self._lock = threading.Lock()
+        self._closed = False
+        self.launches = 0            # kernels launched by this team (benchmarks report it)
+
+        islands = layout.islands
+        self.n_islands = len(islands)
+        self.k = min(len(i.ranks) for i in islands)
+        self.m_max = max(len(i.ranks) for i in islands)
+        team = _lib.GbTeam()
+        team.rank, team.world, team.n_islands = self.rank, self.world, self.n_islands
+        team.my_island = layout.island_index(rank)
+        team.my_pos = islands[team.my_island].ranks.index(rank)
+        position = 0
+        for g, island in enumerate(islands):
+            team.island_off[g] = position
+            for member in island.ranks:
+                team.order[position] = layout.index(member)
+                position += 1
+        team.island_off[self.n_islands] = position
+        for r in range(self.world):
+            team.ws[r] = ws[r]
+        team.ctrl, team.status = ctrl, status
+        team.timeout_ns = timeout_ms * 1_000_000
+        self.team = team
+        self.my_pos = team.my_pos
+        self._plan_regions()
+
+    # -- workspace layout ------------------------------------------------------------------------
+    def _plan_regions(self) -> None:
+        """Carve the workspace.  Every offset and buffer length is a multiple of 4096."""
+        budget = self.ws_bytes - FLAG_BYTES
+        cursor = FLAG_BYTES
+        # one-shot: [2][world] slots
+        self.oneshot_slot = ONESHOT_MAX
+        self.off_oneshot, self.len_oneshot = cursor, self.world * self.oneshot_slot
+        cursor += 2 * self.len_oneshot
+        rest = budget - 2 * self.len_oneshot
+        if rest < 16 * MIB:
+            raise RuntimeError(f"{_config.FABRIC_BYTES_ENV}: the fabric workspace of "
+                               f"{self.ws_bytes} bytes is too small for {self.world} ranks")
+        # hierarchical all-reduce gets 45 %, reduce-scatter 30 %, all-gather 20 %, broadcast 5 %
+        unit = 4096
+        hier = rest * 45 // 100
+        per_stripe = hier // (2 * (self.m_max + self.n_islands + 1))
+        # one stripe buffer must also hold the largest coded payload (never larger than raw)
+        self.stripe_bytes = _align_down(per_stripe, 256 * 8)      # whole blocks of any dtype
+        self.off_ha, self.len_ha = cursor, self.m_max * self.stripe_bytes
+        cursor += 2 * self.len_ha
+        self.off_hb, self.len_hb = cursor, self.n_islands * self.stripe_bytes
+        cursor += 2 * self.len_hb
+        self.off_hc, self.len_hc = cursor, self.stripe_bytes
+        cursor += 2 * self.len_hc
+        rs = rest * 30 // 100
+        self.rs_chunk_bytes = _align_down(rs // (4 * self.world), unit)
+        self.off_rs, self.len_rs = cursor, self.world * self.rs_chunk_bytes
+        cursor += 4 * self.len_rs
+        ag = rest * 20 // 100
+        self.ag_chunk_bytes = _align_down(ag // 4, unit)
+        self.off_ag, self.len_ag = cursor, self.ag_chunk_bytes
+        cursor += 4 * self.len_ag
+        bc = rest * 5 // 100
+        self.bc_stripe_bytes = _align_down(bc // 4, unit)
+        self.off_bc, self.len_bc = cursor, self.bc_stripe_bytes
+        cursor += 4 * self.len_bc
+        assert cursor <= self.ws_bytes, (cursor, self.ws_bytes)
+
+    # -- stream discipline --------------------------------------------------------------------------
+    def _begin(self):
+        current = torch.cuda.current_stream(self.device)
+        if current != self.comm_stream:
+            self.comm_stream.wait_stream(current)
+        return current
+
+    def _end(self, current) -> None:
+        if current != self.comm_stream:
+            current.wait_stream(self.comm_stream)
+
+    def on_comm_stream(self, run, tensors) -> torch.cuda.Event:
+        """Run ``run()`` with the communication stream current (ordered after the caller's
+        stream); returns the event recorded after it.  The async path of the collectives."""
+        current = torch.cuda.current_stream(self.device)
+        self.comm_stream.wait_stream(current)
+        for t in tensors:
+            t.record_stream(self.comm_stream)
+        with torch.cuda.stream(self.comm_stream):
+            run()
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
+        return done
+
+    # -- health --------------------------------------------------------------------------------------
+    def check(self) -> None:
+        code = self._status[0]
+        if code == 0:
+            return
+        kinds = {1: "a peer never arrived at a barrier", 2: "a block of the local grid never "
+                 "arrived at a barrier"}
+        error = FabricError(
+            f"gpubridge fused collective failed on team rank {self._status[4]}: "
+            f"{kinds.get(code, f'status {code}')} (peer {self._status[1]}, barrier "
+            f"{self._status[2]}, step {self._status[3]}) within the device-side wait limit "
+            f"({_config.WAIT_MS_ENV})")
+        _work.poison(error)
+        raise error
+
+    def supports(self, tensors, op: str = "sum") -> bool:
+        if self._closed or op not in _lib.OPS:
+            return False
+        return all(t.device == self.device and t.dtype in _lib.DTYPES and t.is_contiguous()
+                   for t in tensors)
+
+    # -- launches --------------------------------------------------------------------------------------
+    def _grid(self, nbytes: int, cap: int | None = None) -> int:
+        blocks = -(-nbytes // (THREADS * 16 * 4))
+        return max(1, min(cap or self.max_blocks, blocks))
+
+    def _launch_reduce(self, kind: int, tensor_dtype, op: str, codec: int, args, grid: int) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        code = self.lib.gb_launch_reduce(kind, _lib.DTYPES[tensor_dtype], _lib.OPS[op], codec,
+                                         ctypes.byref(self.team), ctypes.byref(args), grid, stream)
+        _lib.check(code, "gb_launch_reduce")
+        self.launches += 1
+
+    def _launch_copy(self, kind: int, args, grid: int) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        code = self.lib.gb_launch_copy(kind, ctypes.byref(self.team), ctypes.byref(args), grid,
+                                       stream)
+        _lib.check(code, "gb_launch_copy")
+        self.launches += 1
+
+    # -- collectives -----------------------------------------------------------------------------------
+    def all_reduce(self, tensor: torch.Tensor, op: str = "sum", divide: int | None = None,
+                   mode: str = "auto", compression=None, chunk_bytes: int | None = None,
+                   out: torch.Tensor | None = None) -> None:
+        """Reduce ``tensor`` over the team into ``out`` (default: in place).
+
+        ``mode``: ``auto`` (one-shot up to 256 KiB, else hierarchical), ``striped``
+        (hierarchical always), ``chunked`` (hierarchical, ``chunk_bytes`` per pipeline step).
+        ``compression``: ``(mode, format)`` for the cross-island step, SUM of floats only.
+        """
+        n = tensor.numel()
+        if n == 0:
+            return
+        out = tensor if out is None else out
+        nbytes = tensor.nbytes
+        if compression is not None and (op != "sum" or self.n_islands < 2):
+            compression = None
+        algo = self.algo
+        oneshot = (compression is None and nbytes <= self.oneshot_slot
+                   and ((mode == "auto" and algo in ("auto", "one-shot")) or algo == "one-shot"))
+        current = self._begin()
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                args = _lib.GbArgs()
+                args.inp, args.out, args.n = tensor.data_ptr(), out.data_ptr(), n
+                args.divide = int(divide or 0)
+                if oneshot:
+                    args.off_a, args.len_a = self.off_oneshot, self.len_oneshot
+                    self._launch_reduce(0, tensor.dtype, op, 0, args, self._grid(nbytes, 16))
+                else:
+                    self._hier(tensor, args, op, compression, chunk_bytes)
+        finally:
+            self._end(current)
+
+    def _hier(self, tensor, args, op, compression, chunk_bytes) -> None:
+        esize, n, k = tensor.element_size(), tensor.numel(), self.k
+        stripe_cap = _align_down(self.stripe_bytes // esize, 256)
+        if chunk_bytes:
+            want = max(256, chunk_bytes // esize // k)
+        else:
+            # about eight pipeline steps for large tensors, never below 1 MiB per chunk
+            want = max(-(-n // (8 * k)), (MIB // esize) // k)
+        stripe = min(stripe_cap, _align_up(min(want, -(-n // k)), 256))
+        args.stripe, args.k, args.chunk = stripe, k, stripe * k
+        args.off_a, args.len_a = self.off_ha, self.len_ha
+        args.off_b, args.len_b = self.off_hb, self.len_hb
+        args.off_c, args.len_c = self.off_hc, self.len_hc
+        codec = 0
+        if compression is not None:
+            codec = _lib.CODECS[tuple(compression)]
+            nchunks = -(-n // (stripe * k))
+            args.residual = self._residual(tensor, (stripe, k, nchunks, codec)).data_ptr()
+        self._launch_reduce(1, tensor.dtype, op, codec, args, self._grid(tensor.nbytes * 2))
+
+    def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:
+        """Error feedback of this rank's stripes of ``tensor``: found by the buffer's address,
+        size and dtype (reference: compression.py:321-324); zero the first time or when the
+        chunk geometry changed."""
+        key = (tensor.data_ptr(), tensor.numel(), tensor.dtype)
+        with self._lock:
+            kept = self._residuals.get(key)
+            if kept is None or kept[1] != geometry:
+                stripe, _, nchunks, _ = geometry
+                size = stripe * nchunks if self.my_pos < self.k else 256
+                kept = (torch.zeros(size, dtype=torch.float32, device=self.device), geometry)
+                self._residuals[key] = kept
+            return kept[0]
+
+    def reset_error_feedback(self) -> None:
+        with self._lock:
+            self._residuals.clear()
+
+    def reduce_scatter(self, output: torch.Tensor, tensor: torch.Tensor, divide: int | None = None,
+                       compression=None) -> None:
+        """``output`` = slice ``rank`` of the sum of every rank's ``tensor``."""
+        n = output.numel()
+        if n == 0:
+            return
+        if compression is not None and self.n_islands > 1:
+            # compressed bridge leg: the hierarchical all-reduce into scratch, then the slice
+            scratch = torch.empty_like(tensor)
+            self.all_reduce(tensor, "sum", divide, "striped", compression, out=scratch)
+            output.view(-1).copy_(scratch.view(self.world, -1)[self.rank])
+            return
+        esize = tensor.element_size()
+        current = self._begin()
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                args = _lib.GbArgs()
+                args.inp, args.out, args.n = tensor.data_ptr(), output.data_ptr(), n
+                args.divide = int(divide or 0)
+                args.chunk = min(_align_down(self.rs_chunk_bytes // esize, 256),
+                                 _align_up(n, 256))
+                args.off_a, args.len_a = self.off_rs, self.len_rs
+                self._launch_reduce(2, tensor.dtype, "sum", 0, args, self._grid(tensor.nbytes))
+        finally:
+            self._end(current)
+
+    def all_gather(self, output: torch.Tensor, tensor: torch.Tensor) -> None:
+        nbytes = tensor.nbytes
+        if nbytes == 0:
+            return
+        current = self._begin()
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                args = _lib.GbArgs()
+                args.inp, args.out, args.n = tensor.data_ptr(), output.data_ptr(), nbytes
+                args.chunk = min(self.ag_chunk_bytes, _align_up(nbytes, 16))
+                args.off_a, args.len_a = self.off_ag, self.len_ag
+                self._launch_copy(0, args, self._grid(output.nbytes))
+        finally:
+            self._end(current)
+
+    def broadcast(self, tensor: torch.Tensor, src: int) -> None:
+        """Copy ``tensor`` from global rank ``src`` to every rank of the team."""
+        nbytes = tensor.nbytes
+        if nbytes == 0:
+            return
+        current = self._begin()
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                args = _lib.GbArgs()
+                args.out, args.n = tensor.data_ptr(), nbytes
+                args.root = self.layout.index(src)
+                stripe = min(self.bc_stripe_bytes, _align_up(-(-nbytes // self.world), 16))
+                args.stripe, args.chunk = stripe, stripe * self.world
+                args.off_a, args.len_a = self.off_bc, self.len_bc
+                self._launch_copy(1, args, self._grid(nbytes * 2))
+        finally:
+            self._end(current)
+
+    def barrier(self) -> None:
+        current = self._begin()
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                self._launch_copy(2, _lib.GbArgs(), 1)
+        finally:
+            self._end(current)
+
+    # -- teardown ------------------------------------------------------------------------------------------
+    def close(self) -> None:
+        """Unmap the peers and free the workspace.  A peer may still be loading from this
+        rank's workspace in its last kernel, so the ranks first meet on the store after each
+        has synchronised its device, unmap, and meet again before anybody frees.  If a peer
+        never shows up (it died) the memory is left to process exit rather than freed under
+        a running kernel."""
+        if self._closed:
+            return
+        self._closed = True
+        try:
+            torch.cuda.synchronize(self.device)
+        except Exception:  # noqa: BLE001 - teardown never raises
+            pass
+        short = timedelta(seconds=20)
+        try:
+            _exchange(self._store, self._key + "/closing", self.rank, self.world, "1", short)
+            for r, ptr in enumerate(self.ws):
+                if r != self.rank and ptr:
+                    self.lib.gb_symm_unmap(ptr)
+            _exchange(self._store, self._key + "/unmapped", self.rank, self.world, "1", short)
+        except Exception:  # noqa: BLE001 - a peer is gone: leak instead of freeing in use
+            return
+        self.lib.gb_symm_free(self.ws[self.rank])
+        self.lib.gb_symm_free(self.ctrl)
+        self.lib.gb_status_free(self.status)
+        self._residuals.clear()
+
+
+def _exchange(store, key: str, rank_index: int, world: int, value: str,
+              timeout: timedelta | None) -> list[str]:
+    store.set(f"{key}/{rank_index}", value)
+    keys = [f"{key}/{r}" for r in range(world)]
+    deadline = time.monotonic() + (timeout or timedelta(minutes=30)).total_seconds()
+    while True:
+        try:
+            store.wait(keys, timedelta(seconds=max(0.05, min(5.0, deadline - time.monotonic()))))
+            break
+        except Exception:  # noqa: BLE001
+            if time.monotonic() >= deadline:
+                raise RuntimeError(f"gpubridge fabric setup: peers never reported ({key})") from None
+    return [store.get(k).decode() for k in keys]
+
+
+def create(store, name: str, layout, rank: int, device: torch.device,
+           timeout: timedelta | None = None) -> Fabric | None:
+    """Map the team's workspaces.  Collective over the team's members.  Returns None - on
+    every member alike - when the team has one rank or more than 16, or some pair of its
+    GPUs cannot address each other's memory."""
+    world = layout.world_size
+    if world < 2 or world > _lib.MAX_RANKS:
+        return None
+    lib = _lib.lib()
+    me = layout.index(rank)
+    key = f"gb/{name}/fabric/{'_'.join(map(str, layout.members))}"
+    torch.cuda.set_device(device)
+    # 1. can every pair reach each other?  (device index + verdict, agreed by all)
+    indices = [int(v) for v in _exchange(store, key + "/dev", me, world, str(device.index), timeout)]
+    reachable = True
+    for other in indices:
+        if other != device.index:
+            yes = ctypes.c_int(0)
+            _lib.check(lib.gb_can_access_peer(device.index, other, ctypes.byref(yes)),
+                       "cudaDeviceCanAccessPeer")
+            reachable = reachable and bool(yes.value)
+    if len(set(indices)) != world:
+        reachable = False            # two members on one GPU: kernels that wait on each other
+    verdicts = _exchange(store, key + "/p2p", me, world, "1" if reachable else "0", timeout)
+    if "0" in verdicts:
+        return None
+    # 2. allocate, export, import
+    ws_bytes = _config.size_setting(_config.FABRIC_BYTES_ENV, DEFAULT_BYTES, multiple=4096)
+    local = ctypes.c_void_p()
+    _lib.check(lib.gb_symm_alloc(ws_bytes, ctypes.byref(local)), "cudaMalloc (fabric workspace)")
+    handle = ctypes.create_string_buffer(64)
+    _lib.check(lib.gb_symm_export(local, handle), "cudaIpcGetMemHandle")
+    handles = _exchange(store, key + "/ipc", me, world, handle.raw.hex(), timeout)
+    ws: list[int] = []
+    for r, text in enumerate(handles):
+        if r == me:
+            ws.append(local.value)
+            continue
+        mapped = ctypes.c_void_p()
+        _lib.check(lib.gb_symm_import(bytes.fromhex(text), ctypes.byref(mapped)),
+                   f"cudaIpcOpenMemHandle (team rank {r})")
+        ws.append(mapped.value)
+    ctrl = ctypes.c_void_p()
+    _lib.check(lib.gb_symm_alloc(max(256, lib.gb_sizeof_ctrl()), ctypes.byref(ctrl)),
+               "cudaMalloc (control block)")
+    status = ctypes.c_void_p()
+    _lib.check(lib.gb_status_alloc(4 * _lib.STATUS_WORDS, ctypes.byref(status)), "cudaHostAlloc")
+    fabric = Fabric(lib, layout, rank, device, ws, ws_bytes, ctrl.value, status.value,
+                    _config.wait_timeout_ms(), store, key)
+    # 3. nobody launches before everybody has mapped everything
+    _exchange(store, key + "/ready", me, world, "1", timeout)
+    return fabric

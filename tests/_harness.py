@@ -35,7 +35,9 @@ def _entry(rank, world, vendors, fn, path, env, args, mode, init, results):
         os.environ.update(env)
         if vendors[rank]:
             os.environ["GPUBRIDGE_VENDOR"] = vendors[rank]
-        os.environ.setdefault("GPUBRIDGE_SIM_HOSTNAME", "simhost")
+            os.environ.setdefault("GPUBRIDGE_SIM_HOSTNAME", "simhost")
+        else:                       # a real GPU rank: one process per GPU
+            os.environ["LOCAL_RANK"] = str(rank)
         torch.set_num_threads(1)
         import torch.distributed as dist
 
@@ -110,6 +112,11 @@ def run_ranks(vendors, fn, tmp_path, *args, env=None, mode="init", init=None, ti
 
 
 TWO_BY_TWO = ("nvidia", "nvidia", "amd", "amd")
+def gpu_ranks(world: int):
+    """``vendors`` for ``world`` real GPU ranks (the vendor comes from the torch build)."""
+    return ("",) * world
+
+
 LAYOUTS = {
     "2+2": TWO_BY_TWO,
     "interleaved": ("nvidia", "amd", "nvidia", "amd"),

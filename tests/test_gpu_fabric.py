@@ -1,0 +1,221 @@
+"""The fused NVLink collectives on real GPUs: one process per GPU, islands made by
+relabelling (``GPUBRIDGE_SPLIT_TEST`` / ``GPUBRIDGE_ISLANDS``), results checked against the
+analytic answer on integer-valued data (exact in any order) and against the PyTorch codec
+for the compressed bridge leg.  Needs at least two GPUs."""
+import os
+
+import pytest
+import torch
+
+from _harness import expected_sum, gpu_ranks, rank_tensor, run_ranks
+
+pytestmark = pytest.mark.gpu
+
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+WORLD = 8 if NGPU >= 8 else 4 if NGPU >= 4 else 2
+needs_two = pytest.mark.skipif(NGPU < 2, reason="needs at least two GPUs")
+
+SIZES = (1, 17, 4099, 65536 + 3, (1 << 20) + 5, (6 << 20) + 1)
+SPLITS = [{}, {"GPUBRIDGE_SPLIT_TEST": "half"}] + (
+    [{"GPUBRIDGE_ISLANDS": "2,2,2,2"}, {"GPUBRIDGE_ISLANDS": "3,5"}] if WORLD == 8 else
+    [{"GPUBRIDGE_ISLANDS": "1,3"}] if WORLD == 4 else [])
+
+
+def _collectives(rank, topology, policy):
+    import gpubridge_b200 as gb
+    dev = topology.device
+    world = topology.world_size
+    assert topology.fabric is not None, "the NVLink fabric must be the path under test"
+    for dtype in (torch.float32, torch.bfloat16, torch.int32, torch.float64, torch.uint8):
+        for n in SIZES:
+            if dtype is torch.uint8:
+                t = (rank_tensor(rank, n, torch.int64) + 3).to(dtype).to(dev)
+                want = sum((rank_tensor(r, n, torch.int64) + 3) for r in range(world)).to(dtype)
+            else:
+                t = rank_tensor(rank, n, dtype).to(dev)
+                want = expected_sum(world, n, dtype)
+            gb.all_reduce(t)
+            assert torch.equal(t.cpu(), want), ("all_reduce", dtype, n)
+    for n in (33, 100_003):
+        t = rank_tensor(rank, n).to(dev)
+        gb.all_reduce(t, gb.ReduceOp.AVG)
+        assert torch.equal(t.cpu(), expected_sum(world, n) / world), ("avg", n)
+        for op, fold in ((gb.ReduceOp.MAX, torch.maximum), (gb.ReduceOp.MIN, torch.minimum)):
+            t = rank_tensor(rank, n).to(dev)
+            gb.all_reduce(t, op)
+            want = rank_tensor(0, n)
+            for r in range(1, world):
+                want = fold(want, rank_tensor(r, n))
+            assert torch.equal(t.cpu(), want), (op, n)
+    # broadcast, all_gather, reduce_scatter
+    for n in (5, 70_001, (3 << 20) + 7):
+        for src in (0, world - 1):
+            t = rank_tensor(rank, n).to(dev)
+            gb.broadcast(t, src)
+            assert torch.equal(t.cpu(), rank_tensor(src, n)), ("broadcast", n, src)
+        out = torch.empty(world * n, device=dev)
+        gb.all_gather_into_tensor(out, rank_tensor(rank, n).to(dev))
+        want = torch.cat([rank_tensor(r, n) for r in range(world)])
+        assert torch.equal(out.cpu(), want), ("all_gather", n)
+        for dtype in (torch.float32, torch.bfloat16):
+            full = rank_tensor(rank, world * n, dtype).to(dev)
+            keep = full.clone()
+            out = torch.empty(n, dtype=dtype, device=dev)
+            gb.reduce_scatter_tensor(out, full)
+            want = expected_sum(world, world * n, dtype).view(world, n)[rank]
+            assert torch.equal(out.cpu(), want), ("reduce_scatter", n, dtype)
+            assert torch.equal(full, keep), "reduce_scatter must not modify its input"
+        out = torch.empty(n, device=dev)
+        gb.reduce_scatter_tensor(out, rank_tensor(rank, world * n).to(dev), gb.ReduceOp.AVG)
+        assert torch.equal(out.cpu(), expected_sum(world, world * n).view(world, n)[rank] / world)
+    # async handles and stream ordering: the tensor is produced by queued GPU work
+    big = torch.ones(1 << 22, device=dev)
+    for _ in range(20):
+        big = big * 1.0000001
+    t = (big[:4099] * 0 + rank_tensor(rank, 4099).to(dev))
+    work = gb.all_reduce(t, async_op=True)
+    assert isinstance(work, gb.Work)
+    work.wait()
+    assert torch.equal(t.cpu(), expected_sum(world, 4099))
+    works = [gb.all_reduce(rank_tensor(rank, 1000 + i).to(dev), async_op=True) for i in range(8)]
+    for i, w in enumerate(works):
+        w.wait()
+        assert torch.equal(w.get_future().value().cpu(), expected_sum(world, 1000 + i))
+    gb.barrier()
+    return topology.policy_name, topology.fabric.launches
+
+
+@needs_two
+@pytest.mark.parametrize("split", SPLITS, ids=lambda s: ",".join(s.values()) or "one-island")
+def test_collectives_default_policy(tmp_path, split):
+    out = run_ranks(gpu_ranks(WORLD), _collectives, tmp_path, "auto", env=split, timeout=240)
+    assert all(launches > 0 for _, launches in out)
+
+
+@needs_two
+@pytest.mark.parametrize("policy", ["sharded-bridge", "pipelined-reduce-bridge-broadcast"])
+def test_collectives_other_policies(tmp_path, policy):
+    env = {"GPUBRIDGE_SPLIT_TEST": "half", "GPUBRIDGE_CHUNK_BYTES": "256K"}
+    out = run_ranks(gpu_ranks(WORLD), _collectives, tmp_path, policy, env=env,
+                    init={"policy": policy}, timeout=240)
+    assert {name for name, _ in out} == {policy}
+
+
+def _compressed(rank, topology, mode, fmt):
+    """The fused compressed all-reduce against the PyTorch codec: island sums in member order,
+    one quantisation per island (with error feedback over two calls), payloads added in island
+    order, one rounding.  Blocks are aligned to the tensor, so whole-tensor quantisation is the
+    oracle."""
+    import gpubridge_b200 as gb
+    from gpubridge_b200 import compression as C
+    dev, world, layout = topology.device, topology.world_size, topology.layout
+    for dtype in (torch.float32, torch.bfloat16):
+        if dtype not in C.APPLIES_TO[mode]:
+            continue
+        for n in (300, 70_001, (2 << 20) + 13):
+            gen = [torch.Generator().manual_seed(1234 + r) for r in range(world)]
+            residuals = [torch.zeros(n) for _ in layout.islands]
+            t = torch.empty(n, dtype=dtype, device=dev)        # one buffer: error feedback
+            for step in range(2):
+                inputs = [torch.randn(n, generator=g).to(dtype) for g in gen]
+                rows = torch.empty((len(layout.islands), C.payload_nbytes(mode, n, fmt)),
+                                   dtype=torch.uint8)
+                for g, island in enumerate(layout.islands):
+                    acc = inputs[island.ranks[0]].float()
+                    for r in island.ranks[1:]:
+                        acc = acc + inputs[r].float()
+                    C.quantize_reference(mode, acc.to(dtype), residuals[g], rows[g], fmt)
+                want = torch.empty(n, dtype=dtype)
+                C.dequantize_accumulate_reference(mode, rows, want, fmt)
+                t.copy_(inputs[rank])
+                gb.all_reduce(t)
+                got = t.cpu()
+                assert torch.equal(got.view(torch.int16 if dtype is torch.bfloat16 else torch.int32),
+                                   want.view(torch.int16 if dtype is torch.bfloat16 else torch.int32)), \
+                    (mode, fmt, dtype, n, step, (got.float() - want.float()).abs().max())
+                exact = sum(x.double() for x in inputs)
+                assert (got.double() - exact).abs().max() < (0.2 if mode == "fp8" else 0.05) * world
+    return True
+
+
+@needs_two
+@pytest.mark.parametrize("mode,fmt", [("fp8", "ref"), ("fp8", "b200"), ("bf16", "ref")])
+def test_compressed_bridge_matches_codec(tmp_path, mode, fmt):
+    env = {"GPUBRIDGE_SPLIT_TEST": "half", "GPUBRIDGE_BRIDGE_COMPRESSION": mode,
+           "GPUBRIDGE_CODEC_FORMAT": fmt}
+    run_ranks(gpu_ranks(WORLD), _compressed, tmp_path, mode, fmt, env=env, timeout=240)
+
+
+def _late_peer(rank, topology):
+    """Rank 1 never launches the collective: the others' device-side wait runs out, the kernel
+    returns with a status record, and the host raises instead of hanging."""
+    import time
+
+    import gpubridge_b200 as gb
+    from gpubridge_b200.ops.fabric import FabricError
+    dev = topology.device
+    t = torch.ones(1024, device=dev)
+    if rank == 1:
+        time.sleep(3.0)
+        return "skipped"
+    gb.all_reduce(t)
+    torch.cuda.synchronize(dev)
+    try:
+        topology.fabric.check()
+    except FabricError as exc:
+        assert "never arrived" in str(exc)
+        try:
+            gb.all_reduce(t)
+        except RuntimeError as again:
+            assert "earlier async gpubridge collective failed" in str(again) or "never arrived" in str(again)
+            return "raised"
+    return "no error"
+
+
+@needs_two
+def test_a_peer_that_never_arrives_is_reported_not_hung(tmp_path):
+    env = {"GPUBRIDGE_WAIT_TIMEOUT_MS": "300", "NCCL_NVLS_ENABLE": "0"}
+    out = run_ranks(gpu_ranks(2), _late_peer, tmp_path, env=env, timeout=120)
+    assert out == ["raised", "skipped"]
+
+
+def _ddp(rank, world):
+    import torch.distributed as dist
+    from torch.nn.parallel import DistributedDataParallel as DDP
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 8)).to(dev)
+    ddp = DDP(model, device_ids=[rank])
+    opt = torch.optim.SGD(ddp.parameters(), lr=0.1)
+    torch.manual_seed(100 + rank)
+    for _ in range(3):
+        x = torch.randn(16, 32, device=dev)
+        loss = ddp(x).square().mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    gathered = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(gathered, flat)
+    assert all(torch.equal(g, gathered[0]) for g in gathered), "replicas diverged"
+    # object collectives and CPU tensors go to the group's Gloo communicator
+    objs = [None] * world
+    dist.all_gather_object(objs, {"rank": rank})
+    assert [o["rank"] for o in objs] == list(range(world))
+    if world >= 2:
+        peer = rank ^ 1
+        if peer < world:
+            send = torch.full((1000,), float(rank), device=dev)
+            recv = torch.empty(1000, device=dev)
+            import gpubridge_b200 as gb
+            ops = [dist.P2POp(dist.isend, send, peer), dist.P2POp(dist.irecv, recv, peer)]
+            for w in gb.batch_isend_irecv(ops):
+                w.wait()
+            assert torch.equal(recv.cpu(), torch.full((1000,), float(peer)))
+    return True
+
+
+@needs_two
+def test_ddp_through_the_backend(tmp_path):
+    run_ranks(gpu_ranks(WORLD), _ddp, tmp_path, mode="backend",
+              env={"GPUBRIDGE_SPLIT_TEST": "half"}, timeout=240)
