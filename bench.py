@@ -1,0 +1,388 @@
+"""Flagship benchmark: DDP training throughput (tokens/s) of the GPT-2-small shaped decoder.
+
+Config (BASELINE.json, config 2): 12 layers, d_model 768, 12 heads, MLP 3072, GELU,
+LayerNorm, vocabulary 50257, sequence 1024, micro-batch 8 per GPU, bf16 autocast, AdamW;
+weights N(0, 0.02) random init, token ids uniform from seed 0 (synthetic data: there is no
+network for datasets or checkpoints).  With N >= 2 GPUs the ranks are split into two islands
+(``GPUBRIDGE_SPLIT_TEST=half``), the way the reference forms islands on one box.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+``--impl ours`` (default) trains through ``gpubridge_b200.parallel.DataParallelTrainer``:
+flat buffers, bucketed all-reduce by the fused NVLink kernels overlapped with backward,
+fused AdamW, the step replayed from a CUDA graph.  ``--impl reference`` runs the unmodified
+reference package from ``baseline/_ref`` through its public API: ``gpubridge.init()``,
+``DistributedDataParallel`` with ``gpubridge.ddp_comm_hook``, ``torch.optim.AdamW``, on a
+plain-PyTorch model of the same architecture defined in this file.
+
+Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, barrier and
+synchronize on both sides, max over ranks) with inputs resident on the device; ``e2e`` times
+the same steps through the public API including, every step, the host-to-device copy of the
+step's tokens from pinned memory and a device-to-host read of the loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+import warnings
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+METRIC = "ddp_gpt2_small_tokens_per_s"
+BATCH, SEQ = 8, 1024
+LR = 3e-4
+
+
+# ---- clocks ------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        clocks, top, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                top = float(parts[2])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": top,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def env_world() -> tuple[int, int, int]:
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
+            int(os.environ.get("WORLD_SIZE", "1")))
+
+
+def default_rendezvous() -> None:
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("LOCAL_RANK", "0")
+
+
+def pinned_batches(vocab: int, count: int, seed: int):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(count):
+        tokens = torch.randint(vocab, (BATCH, SEQ + 1), generator=g)
+        out.append((tokens[:, :-1].contiguous().pin_memory(),
+                    tokens[:, 1:].contiguous().pin_memory()))
+    return out
+
+
+def timed(run_steps, steps: int, device, barrier) -> float:
+    """Milliseconds for ``steps`` steps on the device clock, sync + barrier on both sides."""
+    import torch
+    torch.cuda.synchronize(device)
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    run_steps(steps)
+    end.record()
+    torch.cuda.synchronize(device)
+    barrier()
+    return start.elapsed_time(end)
+
+
+# ---- our arm --------------------------------------------------------------------------------------
+def run_ours(args) -> dict:
+    import torch
+    rank, local_rank, world = env_world()
+    if world > 1:
+        os.environ.setdefault("GPUBRIDGE_SPLIT_TEST", "half")
+    sys.path.insert(0, ROOT)
+    import gpubridge_b200 as gb
+    from gpubridge_b200.models import gpt2
+    from gpubridge_b200.parallel.trainer import DataParallelTrainer
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    topology = None
+    if world > 1:
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", gb.SplitTestWarning)
+            topology = gb.init()
+    torch.manual_seed(0)
+    model = gpt2.build("gpt2-small").to(device)
+    trainer = DataParallelTrainer(model, lambda m, x, y: m.loss(x, y), topology=topology, lr=LR,
+                                  autocast=torch.bfloat16, graph=not args.no_graph)
+    data = pinned_batches(gpt2.CONFIGS["gpt2-small"].vocab, 4, seed=0 + rank)
+    resident = [(x.to(device), y.to(device)) for x, y in data]
+
+    def barrier() -> None:
+        if topology is not None:
+            topology.world_group.barrier()
+
+    def max_over_ranks(value: float) -> float:
+        if topology is None:
+            return value
+        t = torch.tensor([value], dtype=torch.float64)
+        topology.world_group.all_reduce(t, "max")
+        return float(t)
+
+    def device_steps(n: int) -> None:
+        for i in range(n):
+            trainer.step(*resident[i % len(resident)])
+
+    host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
+    losses: list[float] = []
+
+    def e2e_steps(n: int) -> None:
+        copied = None
+        for i in range(n):
+            x, y = data[i % len(data)]
+            loss = trainer.step(x, y)           # host -> device copy of the tokens inside
+            if copied is not None:              # read the previous step's loss on the host
+                copied.synchronize()
+                losses.append(float(host_loss))
+            host_loss.copy_(loss.reshape(1), non_blocking=True)
+            copied = torch.cuda.Event()
+            copied.record()
+        copied.synchronize()
+        losses.append(float(host_loss))
+
+    device_steps(args.warmup)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    before = trainer.launches
+    ms = max_over_ranks(timed(device_steps, args.steps, device, barrier))
+    launches = trainer.launches - before
+    clocks = sampler.stop()
+    e2e_steps(2)
+    e2e_ms = max_over_ranks(timed(e2e_steps, args.steps, device, barrier))
+    trainer.check()
+    tokens = BATCH * SEQ * world * args.steps
+    working_set_gb = round(torch.cuda.max_memory_allocated(device) / 1e9, 1)
+    result = {
+        "metric": METRIC, "value": round(tokens / (ms * 1e-3), 1), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "gpt2-small (12L, d768, 12H, MLP 3072, vocab 50257, tied)",
+                   "global_batch": BATCH * world, "seq_len": SEQ,
+                   "parallelism": f"dp{world}" + ("" if world == 1 else
+                                                  f" ({world // 2 + world % 2}+{world // 2} islands)"),
+                   "optimizer": "AdamW", "autocast": "bf16",
+                   "l2": f"no flush: a step touches about {working_set_gb} GB, far more than "
+                         "the 126 MB L2",
+                   "cuda_graph": not args.no_graph},
+        "clocks": clocks,
+        "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 2 * BATCH * SEQ * 8, "d2h_bytes_per_step": 4,
+                "ms_per_step": round(e2e_ms / args.steps, 3)},
+        "gpu_launches": launches,
+        "final_loss": round(losses[-1], 4) if losses else None,
+    }
+    if topology is not None:
+        gb.destroy()
+    return result if rank == 0 else {}
+
+
+# ---- the reference arm ---------------------------------------------------------------------------------
+def reference_model():
+    """The benchmark architecture in stock PyTorch modules (as the reference's own
+    train_bench.py builds it); nothing of gpubridge_b200 is imported on this path."""
+    import torch
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    width, heads, layers, vocab, context = 768, 12, 12, 50257, 1024
+
+    class Block(nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            self.ln1, self.ln2 = nn.LayerNorm(width), nn.LayerNorm(width)
+            self.qkv, self.proj = nn.Linear(width, 3 * width), nn.Linear(width, width)
+            self.fc, self.out = nn.Linear(width, 4 * width), nn.Linear(4 * width, width)
+
+        def forward(self, x):
+            b, t, w = x.shape
+            q, k, v = (z.view(b, t, heads, w // heads).transpose(1, 2)
+                       for z in self.qkv(self.ln1(x)).split(w, dim=2))
+            y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            x = x + self.proj(y.transpose(1, 2).reshape(b, t, w))
+            return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+    class GPT(nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            self.tok, self.pos = nn.Embedding(vocab, width), nn.Embedding(context, width)
+            self.blocks = nn.ModuleList(Block() for _ in range(layers))
+            self.ln = nn.LayerNorm(width)
+            self.head = nn.Linear(width, vocab, bias=False)
+            self.head.weight = self.tok.weight
+            for module in self.modules():
+                if isinstance(module, (nn.Linear, nn.Embedding)):
+                    nn.init.normal_(module.weight, mean=0.0, std=0.02)
+                    if getattr(module, "bias", None) is not None:
+                        nn.init.zeros_(module.bias)
+
+        def forward(self, idx):
+            x = self.tok(idx) + self.pos(torch.arange(idx.shape[1], device=idx.device))
+            for block in self.blocks:
+                x = block(x)
+            return self.head(self.ln(x))
+
+    return GPT(), vocab
+
+
+def run_reference(args) -> dict:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "gpubridge")):
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed "
+                "(pip install --no-index --no-deps --target baseline/_ref of the reference)"}
+    import torch
+    import torch.nn.functional as F
+    rank, local_rank, world = env_world()
+    if world > 1:
+        os.environ.setdefault("GPUBRIDGE_SPLIT_TEST", "half")
+    sys.path.insert(0, ref)
+    try:
+        import gpubridge
+    except Exception as exc:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"import gpubridge failed: {exc}"[:200]}
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        topology = gpubridge.init()
+    torch.manual_seed(0)
+    model, vocab = reference_model()
+    model = model.to(device)
+    ddp = DDP(model, device_ids=[local_rank])
+    ddp.register_comm_hook(None, gpubridge.ddp_comm_hook)
+    optimizer = torch.optim.AdamW(ddp.parameters(), lr=LR)
+    data = pinned_batches(vocab, 4, seed=0 + rank)
+    resident = [(x.to(device), y.to(device)) for x, y in data]
+
+    def one_step(x, y):
+        optimizer.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = ddp(x)
+            loss = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), y.reshape(-1))
+        loss.backward()
+        optimizer.step()
+        return loss.detach()
+
+    def barrier() -> None:
+        gpubridge.barrier()
+
+    def max_over_ranks(value: float) -> float:
+        t = torch.tensor([value], dtype=torch.float64, device=device)
+        gpubridge.all_reduce(t, gpubridge.ReduceOp.MAX)
+        return float(t)
+
+    def device_steps(n: int) -> None:
+        for i in range(n):
+            one_step(*resident[i % len(resident)])
+
+    losses: list[float] = []
+
+    def e2e_steps(n: int) -> None:
+        for i in range(n):
+            x, y = data[i % len(data)]
+            loss = one_step(x.to(device, non_blocking=True), y.to(device, non_blocking=True))
+            losses.append(loss.item())
+
+    device_steps(args.warmup)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = max_over_ranks(timed(device_steps, args.steps, device, barrier))
+    clocks = sampler.stop()
+    e2e_steps(2)
+    e2e_ms = max_over_ranks(timed(e2e_steps, args.steps, device, barrier))
+    tokens = BATCH * SEQ * world * args.steps
+    result = {
+        "metric": METRIC, "value": round(tokens / (ms * 1e-3), 1), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+        "config": {"model": "gpt2-small (12L, d768, 12H, MLP 3072, vocab 50257, tied)",
+                   "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"dp{world}",
+                   "optimizer": "AdamW", "autocast": "bf16",
+                   "policy": topology.policy_name, "run_kind": topology.run_kind},
+        "clocks": clocks,
+        "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 2 * BATCH * SEQ * 8, "d2h_bytes_per_step": 4,
+                "ms_per_step": round(e2e_ms / args.steps, 3)},
+        "gpu_launches": 0,
+        "final_loss": round(losses[-1], 4) if losses else None,
+    }
+    gpubridge.destroy()
+    return result if rank == 0 else {}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-graph", action="store_true", help="run the step eagerly")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    default_rendezvous()
+    world = int(os.environ["WORLD_SIZE"])
+    if world != args.gpus and int(os.environ["RANK"]) == 0:
+        print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with "
+              "python -m torch.distributed.run --nproc-per-node N", file=sys.stderr)
+    try:
+        result = run_ours(args) if args.impl == "ours" else run_reference(args)
+    except Exception as exc:  # noqa: BLE001
+        if args.impl == "reference":
+            result = {"impl": "reference",
+                      "unavailable": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]}
+            if int(os.environ.get("RANK", "0")) != 0:
+                result = {}
+        else:
+            raise
+    if result:
+        print(json.dumps(result), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -9,7 +9,7 @@ all_reduce, ``algbw * (n-1) / n`` for all_gather and reduce_scatter, ``algbw`` f
 Run under torchrun, one process per GPU, e.g.::
 
     GPUBRIDGE_ISLANDS=4,4 python -m torch.distributed.run --nproc-per-node 8 \
-        --master-addr 127.0.0.1 -m gpubridge_b200.bench.bench_all_reduce --max 1G
+        --master-addr 127.0.0.1 -m gpubridge_b200.bench.bench_all_reduce --largest 1G
 
 Targets: ``ours`` (the active policy), ``nccl`` (one NCCL communicator of every rank),
 ``policy:<name>`` and ``compression:<mode>[:<format>]`` (a policy instance of their own).
@@ -44,8 +44,10 @@ def sizes(lo: int, hi: int) -> list[int]:
     return out
 
 
-def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5) -> float:
-    """Median over trials of the slowest rank's device time, in milliseconds."""
+def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5, inner: int = 1) -> float:
+    """Median over trials of the slowest rank's device time per call, in milliseconds.  With
+    ``inner`` > 1 a trial is that many back-to-back calls (what a training step issues), which
+    takes the launch and host jitter of a lone call out of small-message latencies."""
     dev = topology.device
     for _ in range(warmup):
         fn()
@@ -55,10 +57,11 @@ def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5) -> fl
     for _ in range(trials):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        fn()
+        for _ in range(inner):
+            fn()
         end.record()
         end.synchronize()
-        slowest = torch.tensor([start.elapsed_time(end)], dtype=torch.float64)
+        slowest = torch.tensor([start.elapsed_time(end) / inner], dtype=torch.float64)
         topology.world_group.all_reduce(slowest, "max")
         times.append(float(slowest))
         stop = torch.tensor([1.0 if time.monotonic() - started > seconds else 0.0])
@@ -115,13 +118,14 @@ def make_target(name: str, op: str, topology, dtype, nbytes: int):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--min", default="4K")
-    ap.add_argument("--max", default="64M")
+    ap.add_argument("--smallest", default="4K", help="smallest payload")
+    ap.add_argument("--largest", default="64M", help="largest payload")
     ap.add_argument("--ops", default="all_reduce")
     ap.add_argument("--targets", default="ours,nccl")
     ap.add_argument("--dtypes", default="float32")
     ap.add_argument("--trials", type=int, default=20)
     ap.add_argument("--seconds", type=float, default=20.0)
+    ap.add_argument("--inner", type=int, default=1, help="back-to-back calls per trial")
     ap.add_argument("--json", default="")
     ap.add_argument("--write-thresholds", default="")
     args = ap.parse_args(argv)
@@ -135,7 +139,7 @@ def main(argv=None) -> int:
         for op in args.ops.split(","):
             for dtype_name in args.dtypes.split(","):
                 dtype = getattr(torch, dtype_name)
-                for nbytes in sizes(parse_size(args.min), parse_size(args.max)):
+                for nbytes in sizes(parse_size(args.smallest), parse_size(args.largest)):
                     for target in args.targets.split(","):
                         if target == "nccl" and topology.p2p_group is None:
                             continue
@@ -146,13 +150,13 @@ def main(argv=None) -> int:
                         stream = (topology.fabric.comm_stream if fused
                                   else torch.cuda.current_stream(topology.device))
                         with torch.cuda.stream(stream):
-                            ms = time_calls(fn, topology, args.trials, args.seconds)
+                            ms = time_calls(fn, topology, args.trials, args.seconds, inner=args.inner)
                         algbw = moved / (ms * 1e-3) / 1e9
                         row = {"op": op, "dtype": dtype_name, "bytes": moved, "target": target,
                                "ms": round(ms, 5), "algbw_gbs": round(algbw, 3),
                                "busbw_gbs": round(algbw * BUS[op](world), 3), "world": world,
                                "islands": [len(i.ranks) for i in topology.layout.islands],
-                               "policy": topology.policy_name}
+                               "policy": topology.policy_name, "inner": args.inner}
                         rows.append(row)
                         if rank == 0:
                             print(json.dumps(row), flush=True)

@@ -152,9 +152,13 @@ def block_scales(blocks: torch.Tensor, fmt: str) -> tuple[torch.Tensor, torch.Te
     if fmt == "ref":
         k = pow2_scale_exponent(amax)
         return _exp2(k), _exp2(-k)
+    # Both quotients must be correctly rounded divisions (what the kernels compute):
+    # ``scalar / tensor`` is evaluated by torch as ``tensor.reciprocal() * scalar``.
     one = torch.ones_like(amax)
-    scale = torch.where(amax == 0, one, amax / FP8_MAX)
-    mult = torch.where(amax == 0, one, FP8_MAX / amax)
+    top = torch.full_like(amax, FP8_MAX)
+    safe = torch.where(amax == 0, one, amax)
+    scale = torch.where(amax == 0, one, safe / top)
+    mult = torch.where(amax == 0, one, top / safe)
     return scale, mult
 
 

@@ -45,6 +45,8 @@ struct GbArgs {
     int k;                    // stripes per chunk
     int divide;               // > 0: divide the sum by it (AVG)
     int root;                 // broadcast source (team rank)
+    int role_a;               // > 0: split the grid into roles; blocks of the first role
+    int role_b;               // blocks of the second role (the rest form the last role)
     int pad;
     size_t off_a, off_b, off_c;   // regions
     size_t len_a, len_b, len_c;   // bytes of one buffer of each region
@@ -73,13 +75,12 @@ __device__ __forceinline__ size_t stripe_valid(const GbArgs& a, size_t c0, int j
 // Reduce local slots in hierarchical order into out[0 .. count).
 //   slot s lives at slots + s * slot_bytes; island g is slot_of[bounds[g] .. bounds[g+1]).
 template <typename T, int OP>
-__device__ __forceinline__ void reduce_slots(const char* slots, size_t slot_bytes,
+__device__ __forceinline__ void reduce_slots(const GbLane& L, const char* slots, size_t slot_bytes,
                                              const int* slot_of, const int* bounds, int n_groups,
                                              size_t count, T* out, int divide) {
     typedef typename GbAcc<T>::type A;
     constexpr int V = Vec<T>::N;
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = L.tid, nth = L.nth;
     const size_t nvec = count / V;
     const bool out_aligned = ((uintptr_t)out & 15u) == 0;
     for (size_t v = tid; v < nvec; v += nth) {
@@ -132,10 +133,9 @@ __device__ __forceinline__ void reduce_slots(const char* slots, size_t slot_byte
 }
 
 // Zero [lo, hi) bytes of a 16-byte aligned buffer with the whole grid.
-__device__ __forceinline__ void zero_range(char* base, size_t lo, size_t hi) {
+__device__ __forceinline__ void zero_range(const GbLane& L, char* base, size_t lo, size_t hi) {
     if (hi <= lo) return;
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = L.tid, nth = L.nth;
     size_t head = round_up(lo, 16);
     if (head > hi) head = hi;
     if (tid < head - lo) base[lo + tid] = 0;
@@ -153,12 +153,13 @@ allreduce_oneshot_kernel(GbTeam tm, GbArgs a) {
     const size_t nbytes = a.n * sizeof(T);
     const size_t base = a.off_a + parity * a.len_a;
     const size_t slot = a.len_a / (size_t)tm.world;
+    const GbLane L = gb_lane_all();
     for (int d = 0; d < tm.world; ++d) {
         const int peer = (tm.rank + d) % tm.world;
-        gb_copy_bytes(tm.ws[peer] + base + (size_t)tm.rank * slot, a.in, nbytes, false);
+        gb_copy_bytes(L, tm.ws[peer] + base + (size_t)tm.rank * slot, a.in, nbytes, false);
     }
     if (!gb_sync_all(tm, 0, true)) return;
-    reduce_slots<T, OP>(tm.ws[tm.rank] + base, slot, tm.order, tm.island_off, tm.n_islands,
+    reduce_slots<T, OP>(L, tm.ws[tm.rank] + base, slot, tm.order, tm.island_off, tm.n_islands,
                         a.n, static_cast<T*>(a.out), a.divide);
 }
 
@@ -196,15 +197,15 @@ template <> __device__ __forceinline__ float as_float_sat<double>(double v, bool
 // Step B without compression: reduce the island's slots, round to T, store into every owner
 // (or, with a single island, straight into the result buffer with AVG applied).
 template <typename T, int OP>
-__device__ __forceinline__ void island_reduce_raw(const GbTeam& tm, const GbArgs& a,
-                                                  const char* slots, size_t count, int buf) {
+__device__ __forceinline__ void island_reduce_raw(const GbLane& L, const GbTeam& tm,
+                                                  const GbArgs& a, const char* slots,
+                                                  size_t count, int buf) {
     typedef typename GbAcc<T>::type A;
     constexpr int V = Vec<T>::N;
     const int m = tm.island_off[tm.my_island + 1] - tm.island_off[tm.my_island];
     const bool bridged = tm.n_islands > 1;
     const size_t sbytes = a.stripe * sizeof(T);
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = L.tid, nth = L.nth;
     const size_t nvec = count / V;                       // count is a multiple of 256
     for (size_t v = tid; v < nvec; v += nth) {
         A part[V];
@@ -258,17 +259,17 @@ __device__ __forceinline__ void load_run(const T* src, float (&x)[EPL], bool (&f
 
 // Step B with compression: one warp per quantisation block; payload = codes, then scales.
 template <typename T, int CODEC>
-__device__ __forceinline__ void island_reduce_coded(const GbTeam& tm, const GbArgs& a,
-                                                    const char* slots, size_t count, int buf,
-                                                    float* residual) {
+__device__ __forceinline__ void island_reduce_coded(const GbLane& L, const GbTeam& tm,
+                                                    const GbArgs& a, const char* slots,
+                                                    size_t count, int buf, float* residual) {
     constexpr int BS = GbBlock<CODEC>::size;
     constexpr int EPL = BS / 32;
     const int m = tm.island_off[tm.my_island + 1] - tm.island_off[tm.my_island];
     const size_t sbytes = a.stripe * sizeof(T);
     const size_t pbytes = payload_bytes<T, CODEC>(a.stripe);
     const int lane = threadIdx.x & 31;
-    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t warp = L.tid >> 5;
+    const size_t nwarps = L.nth >> 5;
     const size_t nblk = count / BS;
     for (size_t blk = warp; blk < nblk; blk += nwarps) {
         const size_t i0 = blk * BS + (size_t)lane * EPL;
@@ -329,12 +330,11 @@ __device__ __forceinline__ void island_reduce_coded(const GbTeam& tm, const GbAr
 
 // Step C: add the island results in island order, AVG, round once, into region C.
 template <typename T, int OP, int CODEC>
-__device__ __forceinline__ void bridge_reduce(const GbTeam& tm, const GbArgs& a, size_t count,
-                                              int buf) {
+__device__ __forceinline__ void bridge_reduce(const GbLane& L, const GbTeam& tm, const GbArgs& a,
+                                              size_t count, int buf) {
     typedef typename GbAcc<T>::type A;
     constexpr int V = Vec<T>::N;
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = L.tid, nth = L.nth;
     const size_t pbytes = payload_bytes<T, CODEC>(a.stripe);
     const char* parts = tm.ws[tm.rank] + a.off_b + (size_t)buf * a.len_b;
     char* result = tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c;
@@ -412,8 +412,23 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
     const int depth = bridged ? 3 : 2;                   // iterations between A and D
     const long iters = nchunks + depth;
+    // Roles: with a split grid the blocks of role A store chunk t while those of role B
+    // reduce chunk t-1 (and t-2) and those of role D load chunk t-depth, so both directions
+    // of the links and the local memory work at the same time.  Without, every block takes
+    // every step in turn (best for a single chunk).
+    const bool split = a.role_a > 0;
+    const int b = (int)blockIdx.x;
+    const bool do_a = !split || b < a.role_a;
+    const bool do_b = !split || (b >= a.role_a && b < a.role_a + a.role_b);
+    const bool do_d = !split || b >= a.role_a + a.role_b;
+    GbLane L = gb_lane_all();
+    if (split) {
+        if (do_a) L = gb_lane_blocks(0, a.role_a);
+        else if (do_b) L = gb_lane_blocks(a.role_a, a.role_b);
+        else L = gb_lane_blocks(a.role_a + a.role_b, (int)gridDim.x - a.role_a - a.role_b);
+    }
     for (long t = 0; t < iters; ++t) {
-        if (t < nchunks) {                               // A(t)
+        if (do_a && t < nchunks) {                       // A(t)
             const size_t c0 = (size_t)t * a.chunk;
             for (int dj = 0; dj < a.k; ++dj) {
                 const int j = (tm.my_pos + dj) % a.k;
@@ -422,27 +437,27 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
                             + (size_t)tm.my_pos * sbytes;
                 const size_t valid = stripe_valid(a, c0, j);
                 if (valid)
-                    gb_copy_bytes(dst, in + c0 + (size_t)j * a.stripe, valid * sizeof(T), false);
+                    gb_copy_bytes(L, dst, in + c0 + (size_t)j * a.stripe, valid * sizeof(T), false);
                 // zeros up to the next quantisation block: padding reduces only with padding
-                zero_range(dst, valid * sizeof(T), round_up(valid, 256) * sizeof(T));
+                zero_range(L, dst, valid * sizeof(T), round_up(valid, 256) * sizeof(T));
             }
         }
-        if (owner && t >= 1 && t - 1 < nchunks) {        // B(t-1)
+        if (do_b && owner && t >= 1 && t - 1 < nchunks) {        // B(t-1)
             const long c = t - 1;
             const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
             const char* slots = tm.ws[tm.rank] + a.off_a + (size_t)(c & 1) * a.len_a;
             if (CODEC == GB_RAW)
-                island_reduce_raw<T, OP>(tm, a, slots, need, (int)(c & 1));
+                island_reduce_raw<T, OP>(L, tm, a, slots, need, (int)(c & 1));
             else
-                island_reduce_coded<T, CODEC>(tm, a, slots, need, (int)(c & 1),
+                island_reduce_coded<T, CODEC>(L, tm, a, slots, need, (int)(c & 1),
                                               a.residual + (size_t)c * a.stripe);
         }
-        if (bridged && owner && t >= 2 && t - 2 < nchunks) {   // C(t-2)
+        if (do_b && bridged && owner && t >= 2 && t - 2 < nchunks) {   // C(t-2)
             const long c = t - 2;
             const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
-            bridge_reduce<T, OP, CODEC>(tm, a, need, (int)(c & 1));
+            bridge_reduce<T, OP, CODEC>(L, tm, a, need, (int)(c & 1));
         }
-        if (t >= depth) {                                // D(t-depth)
+        if (do_d && t >= depth) {                        // D(t-depth)
             const long c = t - depth;
             const size_t c0 = (size_t)c * a.chunk;
             for (int dj = 0; dj < a.k; ++dj) {
@@ -450,7 +465,7 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
                 const int own = tm.order[tm.island_off[tm.my_island] + j];
                 const size_t valid = stripe_valid(a, c0, j);
                 if (valid)
-                    gb_copy_bytes(out + c0 + (size_t)j * a.stripe,
+                    gb_copy_bytes(L, out + c0 + (size_t)j * a.stripe,
                                   tm.ws[own] + a.off_c + (size_t)(c & 1) * a.len_c,
                                   valid * sizeof(T), true);
             }
@@ -467,11 +482,12 @@ allgather_kernel(GbTeam tm, GbArgs a) {
     const char* in = static_cast<const char*>(a.in);
     char* out = static_cast<char*>(a.out);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    const GbLane L = gb_lane_all();
     for (long t = 0; t <= nchunks; ++t) {
         if (t < nchunks) {
             const size_t c0 = (size_t)t * a.chunk;
             const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
-            gb_copy_bytes(tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
+            gb_copy_bytes(L, tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
                           in + c0, len, false);
         }
         if (t >= 1) {
@@ -480,7 +496,7 @@ allgather_kernel(GbTeam tm, GbArgs a) {
             const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
             for (int d = 0; d < tm.world; ++d) {
                 const int peer = (tm.rank + d) % tm.world;
-                gb_copy_bytes(out + (size_t)peer * a.n + c0,
+                gb_copy_bytes(L, out + (size_t)peer * a.n + c0,
                               tm.ws[peer] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
                               len, true);
             }
@@ -500,22 +516,29 @@ reduce_scatter_kernel(GbTeam tm, GbArgs a) {
     T* out = static_cast<T*>(a.out);
     const size_t slot = a.chunk * sizeof(T);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    // Roles: the blocks of role A store chunk t into its owners while the rest reduce chunk t-1.
+    const bool split = a.role_a > 0;
+    const bool do_a = !split || (int)blockIdx.x < a.role_a;
+    const bool do_b = !split || (int)blockIdx.x >= a.role_a;
+    const GbLane L = !split ? gb_lane_all()
+                   : do_a ? gb_lane_blocks(0, a.role_a)
+                          : gb_lane_blocks(a.role_a, (int)gridDim.x - a.role_a);
     for (long t = 0; t <= nchunks; ++t) {
-        if (t < nchunks) {
+        if (do_a && t < nchunks) {
             const size_t c0 = (size_t)t * a.chunk;
             const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
             for (int d = 0; d < tm.world; ++d) {
                 const int owner = (tm.rank + d) % tm.world;
-                gb_copy_bytes(tm.ws[owner] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a
+                gb_copy_bytes(L, tm.ws[owner] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a
                               + (size_t)tm.rank * slot,
                               in + (size_t)owner * a.n + c0, len * sizeof(T), false);
             }
         }
-        if (t >= 1) {
+        if (do_b && t >= 1) {
             const long c = t - 1;
             const size_t c0 = (size_t)c * a.chunk;
             const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
-            reduce_slots<T, OP>(tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
+            reduce_slots<T, OP>(L, tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
                                 slot, tm.order, tm.island_off, tm.n_islands, len, out + c0, a.divide);
         }
         if (t < nchunks && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
@@ -530,6 +553,7 @@ broadcast_kernel(GbTeam tm, GbArgs a) {
     const unsigned parity = gb_ld_volatile(&tm.ctrl->epoch) & 1u;
     char* data = static_cast<char*>(a.out);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    const GbLane L = gb_lane_all();
     for (long t = 0; t <= nchunks; ++t) {
         if (t < nchunks && tm.rank == a.root) {
             const size_t c0 = (size_t)t * a.chunk;
@@ -538,7 +562,7 @@ broadcast_kernel(GbTeam tm, GbArgs a) {
                 const size_t s0 = c0 + (size_t)j * a.stripe;
                 if (s0 >= a.n) continue;
                 const size_t len = a.n - s0 < a.stripe ? a.n - s0 : a.stripe;
-                gb_copy_bytes(tm.ws[j] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
+                gb_copy_bytes(L, tm.ws[j] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
                               data + s0, len, false);
             }
         }
@@ -550,7 +574,7 @@ broadcast_kernel(GbTeam tm, GbArgs a) {
                 const size_t s0 = c0 + (size_t)j * a.stripe;
                 if (s0 >= a.n) continue;
                 const size_t len = a.n - s0 < a.stripe ? a.n - s0 : a.stripe;
-                gb_copy_bytes(data + s0,
+                gb_copy_bytes(L, data + s0,
                               tm.ws[j] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
                               len, true);
             }

@@ -208,31 +208,46 @@ template <> __device__ __forceinline__ float gb_divide<float>(float v, int by) {
     return __fdiv_rn(v, (float)by);
 }
 
+// ---- lanes --------------------------------------------------------------------------------------
+// The threads that share one piece of work: the whole grid, or the blocks of one role when a
+// kernel splits its grid so that different pipeline steps run at the same time.
+struct GbLane {
+    size_t tid, nth;      // this thread's index among the lane's threads, and their number
+};
+__device__ __forceinline__ GbLane gb_lane_all() {
+    GbLane l;
+    l.tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    l.nth = (size_t)gridDim.x * blockDim.x;
+    return l;
+}
+__device__ __forceinline__ GbLane gb_lane_blocks(int first, int count) {
+    GbLane l;
+    l.tid = (size_t)(blockIdx.x - first) * blockDim.x + threadIdx.x;
+    l.nth = (size_t)count * blockDim.x;
+    return l;
+}
+
 // ---- byte copies -----------------------------------------------------------------------------
-// Copy `nbytes` with the whole grid.  `peer_src`: the source was written by another GPU (or is
-// remote), so it is read past L1.  Falls back to narrower accesses for unaligned user tensors.
-__device__ __forceinline__ void gb_copy_bytes(void* dst, const void* src, size_t nbytes,
-                                              bool peer_src) {
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t nth = (size_t)gridDim.x * blockDim.x;
+// Copy `nbytes` with the threads of a lane.  `peer_src`: the source was written by another GPU
+// (or is remote), so it is read past L1.  Eight independent 16-byte transfers are in flight per
+// thread, which is what hides the NVLink round trip of a remote load.  Falls back to narrower
+// accesses for unaligned user tensors.
+__device__ __forceinline__ void gb_copy_bytes(const GbLane& L, void* dst, const void* src,
+                                              size_t nbytes, bool peer_src) {
+    const size_t tid = L.tid, nth = L.nth;
     char* d = static_cast<char*>(dst);
     const char* s = static_cast<const char*>(src);
     if ((((uintptr_t)d | (uintptr_t)s) & 15u) == 0) {
         const size_t nv = nbytes >> 4;
         size_t i = tid;
-        // four independent 16-byte transfers in flight per thread
-        for (; i + 3 * nth < nv; i += 4 * nth) {
-            uint4 a, b, c, e;
-            if (peer_src) {
-                a = gb_ld16(s + (i << 4)); b = gb_ld16(s + ((i + nth) << 4));
-                c = gb_ld16(s + ((i + 2 * nth) << 4)); e = gb_ld16(s + ((i + 3 * nth) << 4));
-            } else {
-                a = __ldg((const uint4*)(s + (i << 4))); b = __ldg((const uint4*)(s + ((i + nth) << 4)));
-                c = __ldg((const uint4*)(s + ((i + 2 * nth) << 4)));
-                e = __ldg((const uint4*)(s + ((i + 3 * nth) << 4)));
-            }
-            gb_st16(d + (i << 4), a); gb_st16(d + ((i + nth) << 4), b);
-            gb_st16(d + ((i + 2 * nth) << 4), c); gb_st16(d + ((i + 3 * nth) << 4), e);
+        for (; i + 7 * nth < nv; i += 8 * nth) {
+            uint4 r[8];
+            #pragma unroll
+            for (int u = 0; u < 8; ++u)
+                r[u] = peer_src ? gb_ld16(s + ((i + u * nth) << 4))
+                                : __ldg((const uint4*)(s + ((i + u * nth) << 4)));
+            #pragma unroll
+            for (int u = 0; u < 8; ++u) gb_st16(d + ((i + u * nth) << 4), r[u]);
         }
         for (; i < nv; i += nth) {
             uint4 a = peer_src ? gb_ld16(s + (i << 4)) : __ldg((const uint4*)(s + (i << 4)));

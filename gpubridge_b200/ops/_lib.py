@@ -38,7 +38,8 @@ class GbTeam(ctypes.Structure):
 class GbArgs(ctypes.Structure):
     _fields_ = [("inp", ctypes.c_void_p), ("out", ctypes.c_void_p), ("n", ctypes.c_size_t),
                 ("chunk", ctypes.c_size_t), ("stripe", ctypes.c_size_t), ("k", ctypes.c_int),
-                ("divide", ctypes.c_int), ("root", ctypes.c_int), ("pad", ctypes.c_int),
+                ("divide", ctypes.c_int), ("root", ctypes.c_int), ("role_a", ctypes.c_int),
+                ("role_b", ctypes.c_int), ("pad", ctypes.c_int),
                 ("off_a", ctypes.c_size_t), ("off_b", ctypes.c_size_t), ("off_c", ctypes.c_size_t),
                 ("len_a", ctypes.c_size_t), ("len_b", ctypes.c_size_t), ("len_c", ctypes.c_size_t),
                 ("residual", ctypes.c_void_p)]
@@ -91,6 +92,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_launch_reduce.argtypes = [i, i, i, i, ctypes.POINTER(GbTeam), ctypes.POINTER(GbArgs),
                                    i, vp]
     L.gb_launch_copy.argtypes = [i, ctypes.POINTER(GbTeam), ctypes.POINTER(GbArgs), i, vp]
+    L.gb_adamw_step.argtypes = [vp, vp, vp, vp, sz, vp] + [ctypes.c_float] * 6 + [i, vp]
+    L.gb_xent_fwd_bwd.argtypes = [vp, i, vp, sz, sz, sz, vp, vp, vp, vp]
     L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
     L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]
 

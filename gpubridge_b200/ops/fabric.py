@@ -250,7 +250,13 @@ class Fabric:
             codec = _lib.CODECS[tuple(compression)]
             nchunks = -(-n // (stripe * k))
             args.residual = self._residual(tensor, (stripe, k, nchunks, codec)).data_ptr()
-        self._launch_reduce(1, tensor.dtype, op, codec, args, self._grid(tensor.nbytes * 2))
+        grid = self._grid(tensor.nbytes * 2)
+        nchunks = -(-n // (stripe * k))
+        if nchunks >= 4 and grid >= 12:
+            # enough chunks to keep a pipeline busy: store, reduce and load at the same time
+            args.role_b = max(2, grid // 5)
+            args.role_a = (grid - args.role_b) // 2
+        self._launch_reduce(1, tensor.dtype, op, codec, args, grid)
 
     def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:
         """Error feedback of this rank's stripes of ``tensor``: found by the buffer's address,
@@ -292,7 +298,10 @@ class Fabric:
                 args.chunk = min(_align_down(self.rs_chunk_bytes // esize, 256),
                                  _align_up(n, 256))
                 args.off_a, args.len_a = self.off_rs, self.len_rs
-                self._launch_reduce(2, tensor.dtype, "sum", 0, args, self._grid(tensor.nbytes))
+                grid = self._grid(tensor.nbytes)
+                if -(-n // args.chunk) >= 4 and grid >= 8:
+                    args.role_a = grid * 3 // 4
+                self._launch_reduce(2, tensor.dtype, "sum", 0, args, grid)
         finally:
             self._end(current)
 

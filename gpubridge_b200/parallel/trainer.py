@@ -1,0 +1,179 @@
+"""Data-parallel training step built on the fabric: flat buffers, bucketed gradient
+all-reduce overlapped with backward, fused AdamW, optionally replayed from a CUDA graph.
+
+This is the B200-first counterpart of "DistributedDataParallel + ``ddp_comm_hook`` +
+``torch.optim.AdamW``" (reference: src/gpubridge/ddp.py:41-52 and the training loop of
+scripts/gpu/train_bench.py:300-330).  The hook path still exists
+(:func:`gpubridge_b200.ddp_comm_hook`); this trainer is what a user calls when the whole
+step should be ours:
+
+* every parameter is a view into one flat float32 buffer, every gradient a view into
+  another, so the optimizer is one launch (``csrc/gb_optim.cu``) that also clears the
+  gradients;
+* gradients are cut into buckets in reverse registration order (the order backward
+  produces them); when the last gradient of a bucket has been accumulated, the bucket's
+  all-reduce (AVG fused, hierarchical, optionally compressed on the cross-island leg) is
+  launched on the fabric's communication stream while backward continues;
+* none of this needs the host between launches, and the collective kernels keep their
+  sequence numbers on the device, so the whole step - forward, backward, collectives,
+  optimizer - can be captured once and replayed as one CUDA graph on every rank.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from gpubridge_b200.ops.optim import FlatAdamW
+from gpubridge_b200.topology import Topology, get_topology, is_initialized
+
+MIB = 1 << 20
+
+
+class DataParallelTrainer:
+    """One training step per :meth:`step` call.
+
+    Args:
+        model: the module to train; its parameters are moved into the flat buffer.
+        loss_fn: ``loss_fn(model, *batch) -> scalar loss``.
+        topology: the group to average gradients over (default: the initialised world;
+            None and not initialised: a single process).
+        bucket_mb: gradient bucket size (DDP's default is 25 MB).
+        autocast: dtype of ``torch.autocast`` around forward, or None.
+        graph: capture the step in a CUDA graph after ``graph_warmup`` eager steps.
+    """
+
+    def __init__(self, model: nn.Module, loss_fn, *, topology: Topology | None = None,
+                 lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 1e-2, bucket_mb: float = 25.0,
+                 autocast: torch.dtype | None = torch.bfloat16, graph: bool = False,
+                 graph_warmup: int = 3) -> None:
+        self.model, self.loss_fn = model, loss_fn
+        if hasattr(model, "unit_grad"):
+            model.unit_grad = True          # backward always starts at the loss here
+        if topology is None and is_initialized():
+            topology = get_topology()
+        self.topology = topology
+        self.world = topology.world_size if topology is not None else 1
+        self.fabric = topology.fabric if topology is not None else None
+        self.autocast = autocast
+        params = [p for p in model.parameters() if p.requires_grad]
+        self.device = params[0].device
+        sizes = [-(-p.numel() // 64) * 64 for p in params]          # 256-byte aligned views
+        total = sum(sizes)
+        self.flat_param = torch.zeros(total, dtype=torch.float32, device=self.device)
+        self.flat_grad = torch.zeros(total, dtype=torch.float32, device=self.device)
+        # reverse registration order: the order backward fills the gradients in
+        offset, self._spans = 0, []
+        for p, size in zip(reversed(params), reversed(sizes)):
+            view = self.flat_param[offset:offset + p.numel()].view_as(p)
+            view.copy_(p.detach())
+            p.data = view
+            p.grad = self.flat_grad[offset:offset + p.numel()].view_as(p)
+            self._spans.append((p, offset, offset + size))
+            offset += size
+        self.optimizer = FlatAdamW(self.flat_param, self.flat_grad, lr, betas, eps, weight_decay)
+        self._buckets = self._make_buckets(int(bucket_mb * MIB))
+        self._pending = [0] * len(self._buckets)
+        self._sent = 0
+        self._comm_events: list[torch.cuda.Event] = []
+        if self.world > 1:
+            for index, (lo, hi, members) in enumerate(self._buckets):
+                for p in members:
+                    p.register_post_accumulate_grad_hook(self._make_hook(index))
+        self._use_graph, self._graph_warmup = graph and self.device.type == "cuda", graph_warmup
+        self._graph: torch.cuda.CUDAGraph | None = None
+        self._static_batch = None
+        self._static_loss = None
+        self._steps = 0
+        self.launches = 0
+
+    # -- buckets -------------------------------------------------------------------------------
+    def _make_buckets(self, cap_bytes: int):
+        buckets, lo, members = [], 0, []
+        for p, start, end in self._spans:
+            members.append(p)
+            if (end - lo) * 4 >= cap_bytes:
+                buckets.append((lo, end, members))
+                lo, members = end, []
+        if members:
+            buckets.append((lo, self._spans[-1][2], members))
+        return buckets
+
+    def _make_hook(self, index: int):
+        def hook(param) -> None:
+            self._pending[index] -= 1
+            if self._pending[index] == 0:
+                self._reduce_ready()
+        return hook
+
+    def _reduce_ready(self) -> None:
+        """Launch, in bucket order, every bucket whose gradients are all in."""
+        while self._sent < len(self._buckets) and self._pending[self._sent] == 0:
+            lo, hi, _ = self._buckets[self._sent]
+            self._all_reduce(self.flat_grad[lo:hi])
+            self._sent += 1
+
+    def _all_reduce(self, grads: torch.Tensor) -> None:
+        topology, fabric = self.topology, self.fabric
+        if fabric is not None:
+            # stream-ordered: fork onto the communication stream, join before the optimizer
+            comm = fabric.comm_stream
+            comm.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(comm):
+                topology.policy.select_policy(grads.nbytes).all_reduce(
+                    grads, topology, divide=self.world)
+            self.launches += 1
+        else:
+            from gpubridge_b200.collectives import all_reduce
+            from torch.distributed import ReduceOp
+            all_reduce(grads, ReduceOp.AVG, _topology=topology)
+
+    # -- the step --------------------------------------------------------------------------------
+    def _step_body(self, batch) -> torch.Tensor:
+        self._pending = [len(members) for _, _, members in self._buckets]
+        self._sent = 0
+        if self.autocast is not None and self.device.type == "cuda":
+            with torch.autocast("cuda", dtype=self.autocast):
+                loss = self.loss_fn(self.model, *batch)
+        else:
+            loss = self.loss_fn(self.model, *batch)
+        loss.backward()
+        if self.world > 1:
+            # parameters that received no gradient still belong to their bucket
+            self._pending = [0] * len(self._buckets)
+            self._reduce_ready()
+            if self.fabric is not None:
+                torch.cuda.current_stream(self.device).wait_stream(self.fabric.comm_stream)
+        self.optimizer.step(zero_grad=True)
+        self.launches += 1
+        return loss.detach()
+
+    def step(self, *batch: torch.Tensor) -> torch.Tensor:
+        """Forward, backward with overlapped gradient averaging, optimizer.  Returns the
+        loss of this rank's batch as a device tensor (no host synchronisation)."""
+        self._steps += 1
+        if not self._use_graph or (self._graph is None and self._steps <= self._graph_warmup):
+            return self._step_body([b.to(self.device, non_blocking=True) for b in batch])
+        if self._graph is None:
+            self._capture([b.to(self.device) for b in batch])
+        for static, new in zip(self._static_batch, batch):
+            static.copy_(new, non_blocking=True)
+        before = self.launches
+        self._graph.replay()
+        self.launches = before + self._launches_per_step
+        return self._static_loss
+
+    def _capture(self, batch) -> None:
+        self._static_batch = [b.clone() for b in batch]
+        torch.cuda.synchronize(self.device)
+        self._graph = torch.cuda.CUDAGraph()
+        before = self.launches
+        with torch.cuda.graph(self._graph):
+            self._static_loss = self._step_body(self._static_batch)
+        self._launches_per_step = self.launches - before
+        self.launches = before
+
+    def check(self) -> None:
+        """Raise if a device-side wait of a collective ran out."""
+        if self.fabric is not None:
+            self.fabric.check()

@@ -338,9 +338,13 @@ class GpubridgeProcessGroup(dist.ProcessGroup):
             if on_cpu:
                 self._cpu().all_gather_into(buffer, source)
             else:
-                self._run("allgather", None, [
-                    lambda b=buffer, s=source: _collectives.all_gather_into_tensor(
-                        b, s, async_op=True, _topology=topology)]).wait()
+                # a blocking call of a fused collective is ordered on the current stream, so
+                # the copies below see the gathered rows (a Work whose result holds no tensor
+                # would carry no device events to wait on)
+                try:
+                    _collectives.all_gather_into_tensor(buffer, source, _topology=topology)
+                except (ValueError, TypeError, NotImplementedError) as exc:
+                    raise type(exc)(f"{NAME} backend, allgather: {exc}") from exc
             for out, row in zip(outputs, buffer.view(self.size(), *tensor.shape).unbind(0)):
                 out.copy_(row)
         return _completed(output_lists)
@@ -405,7 +409,7 @@ class GpubridgeProcessGroup(dist.ProcessGroup):
     def _end_coalescing(self, device) -> dist.Work:
         if self._native_batch is not None:
             native, self._native_batch = self._native_batch, None
-            self._coalesced_torch.append(native._end_coalescing(device))
+            self._coalesced_torch.append(native._end_coalescing())
         works, self._coalesced = self._coalesced or [], None
         torch_works, self._coalesced_torch = self._coalesced_torch, []
         futures, members = [], list(works)
@@ -461,7 +465,7 @@ class GpubridgeProcessGroup(dist.ProcessGroup):
         if comm is not None:
             batch = self._coalesced is not None and cuda
             if batch and self._native_batch is None:
-                comm.backend._start_coalescing(tensor.device)
+                comm.backend._start_coalescing()
                 self._native_batch = comm.backend
             work = (comm.send if sending else comm.recv)(tensor, target, tag)
             if self._coalesced is not None and not batch:
