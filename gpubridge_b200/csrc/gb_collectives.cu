@@ -83,32 +83,51 @@ __device__ __forceinline__ void reduce_slots(const GbLane& L, const char* slots,
     const size_t tid = L.tid, nth = L.nth;
     const size_t nvec = count / V;
     const bool out_aligned = ((uintptr_t)out & 15u) == 0;
-    for (size_t v = tid; v < nvec; v += nth) {
-        A total[V];
+    // U vectors per thread and step, so U loads are in flight per slot (a single vector per
+    // step leaves the loop bound by memory latency)
+    constexpr int U = V >= 8 ? 4 : 8;
+    for (size_t v0 = tid; v0 < nvec; v0 += (size_t)U * nth) {
+        A total[U][V];
         for (int g = 0; g < n_groups; ++g) {
-            A part[V];
+            A part[U][V];
             for (int s = bounds[g]; s < bounds[g + 1]; ++s) {
-                Vec<T> w;
-                w.u = gb_ld16(slots + (size_t)slot_of[s] * slot_bytes + v * 16);
+                Vec<T> w[U];
+                const char* base = slots + (size_t)slot_of[s] * slot_bytes;
                 #pragma unroll
-                for (int j = 0; j < V; ++j)
-                    part[j] = (s == bounds[g]) ? gb_up<T>(w.e[j])
-                                               : GbFold<OP, A>::run(part[j], gb_up<T>(w.e[j]));
+                for (int u = 0; u < U; ++u) {
+                    const size_t v = v0 + (size_t)u * nth;
+                    if (v < nvec) w[u].u = gb_ld16(base + v * 16, L.ld);
+                }
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        part[u][j] = (s == bounds[g]) ? gb_up<T>(w[u].e[j])
+                                     : GbFold<OP, A>::run(part[u][j], gb_up<T>(w[u].e[j]));
+                }
             }
             #pragma unroll
-            for (int j = 0; j < V; ++j) {
-                A rounded = gb_up<T>(gb_down<T>(part[j]));      // the island result, in T
-                total[j] = (g == 0) ? rounded : GbFold<OP, A>::run(total[j], rounded);
+            for (int u = 0; u < U; ++u) {
+                #pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    A rounded = gb_up<T>(gb_down<T>(part[u][j]));   // the island result, in T
+                    total[u][j] = (g == 0) ? rounded : GbFold<OP, A>::run(total[u][j], rounded);
+                }
             }
         }
-        Vec<T> r;
         #pragma unroll
-        for (int j = 0; j < V; ++j)
-            r.e[j] = gb_down<T>(divide > 0 ? gb_divide<A>(total[j], divide) : total[j]);
-        if (out_aligned) gb_st16(out + v * V, r.u);
-        else {
+        for (int u = 0; u < U; ++u) {
+            const size_t v = v0 + (size_t)u * nth;
+            if (v >= nvec) continue;
+            Vec<T> r;
             #pragma unroll
-            for (int j = 0; j < V; ++j) out[v * V + j] = r.e[j];
+            for (int j = 0; j < V; ++j)
+                r.e[j] = gb_down<T>(divide > 0 ? gb_divide<A>(total[u][j], divide) : total[u][j]);
+            if (out_aligned) gb_st16(out + v * V, r.u);
+            else {
+                #pragma unroll
+                for (int j = 0; j < V; ++j) out[v * V + j] = r.e[j];
+            }
         }
     }
     // ragged tail: count is not a multiple of a 16-byte vector
@@ -153,7 +172,7 @@ allreduce_oneshot_kernel(GbTeam tm, GbArgs a) {
     const size_t nbytes = a.n * sizeof(T);
     const size_t base = a.off_a + parity * a.len_a;
     const size_t slot = a.len_a / (size_t)tm.world;
-    const GbLane L = gb_lane_all();
+    const GbLane L = gb_lane_all(tm.ld_mode);
     for (int d = 0; d < tm.world; ++d) {
         const int peer = (tm.rank + d) % tm.world;
         gb_copy_bytes(L, tm.ws[peer] + base + (size_t)tm.rank * slot, a.in, nbytes, false);
@@ -207,31 +226,45 @@ __device__ __forceinline__ void island_reduce_raw(const GbLane& L, const GbTeam&
     const size_t sbytes = a.stripe * sizeof(T);
     const size_t tid = L.tid, nth = L.nth;
     const size_t nvec = count / V;                       // count is a multiple of 256
-    for (size_t v = tid; v < nvec; v += nth) {
-        A part[V];
+    constexpr int U = V >= 8 ? 4 : 8;                    // vectors in flight per thread
+    for (size_t v0 = tid; v0 < nvec; v0 += (size_t)U * nth) {
+        A part[U][V];
         for (int p = 0; p < m; ++p) {
-            Vec<T> w;
-            w.u = gb_ld16(slots + (size_t)p * sbytes + v * 16);
+            Vec<T> w[U];
             #pragma unroll
-            for (int j = 0; j < V; ++j)
-                part[j] = (p == 0) ? gb_up<T>(w.e[j]) : GbFold<OP, A>::run(part[j], gb_up<T>(w.e[j]));
-        }
-        Vec<T> r;
-        #pragma unroll
-        for (int j = 0; j < V; ++j) r.e[j] = gb_down<T>(part[j]);
-        if (!bridged) {
-            if (a.divide > 0) {
+            for (int u = 0; u < U; ++u) {
+                const size_t v = v0 + (size_t)u * nth;
+                if (v < nvec) w[u].u = gb_ld16(slots + (size_t)p * sbytes + v * 16, L.ld);
+            }
+            #pragma unroll
+            for (int u = 0; u < U; ++u) {
                 #pragma unroll
                 for (int j = 0; j < V; ++j)
-                    r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
+                    part[u][j] = (p == 0) ? gb_up<T>(w[u].e[j])
+                                 : GbFold<OP, A>::run(part[u][j], gb_up<T>(w[u].e[j]));
             }
-            gb_st16(tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c + v * 16, r.u);
-        } else {
-            for (int d = 0; d < tm.n_islands; ++d) {
-                const int isl = (tm.my_island + d) % tm.n_islands;
-                const int owner = tm.order[tm.island_off[isl] + tm.my_pos];
-                gb_st16(tm.ws[owner] + a.off_b + (size_t)buf * a.len_b
-                        + (size_t)tm.my_island * sbytes + v * 16, r.u);
+        }
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const size_t v = v0 + (size_t)u * nth;
+            if (v >= nvec) continue;
+            Vec<T> r;
+            #pragma unroll
+            for (int j = 0; j < V; ++j) r.e[j] = gb_down<T>(part[u][j]);
+            if (!bridged) {
+                if (a.divide > 0) {
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
+                }
+                gb_st16(tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c + v * 16, r.u);
+            } else {
+                for (int d = 0; d < tm.n_islands; ++d) {
+                    const int isl = (tm.my_island + d) % tm.n_islands;
+                    const int owner = tm.order[tm.island_off[isl] + tm.my_pos];
+                    gb_st16(tm.ws[owner] + a.off_b + (size_t)buf * a.len_b
+                            + (size_t)tm.my_island * sbytes + v * 16, r.u);
+                }
             }
         }
     }
@@ -339,22 +372,42 @@ __device__ __forceinline__ void bridge_reduce(const GbLane& L, const GbTeam& tm,
     const char* parts = tm.ws[tm.rank] + a.off_b + (size_t)buf * a.len_b;
     char* result = tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c;
     const size_t nvec = count / V;
-    for (size_t v = tid; v < nvec; v += nth) {
-        Vec<T> r;
-        if (CODEC == GB_RAW) {
-            A total[V];
+    if (CODEC == GB_RAW) {
+        constexpr int U = V >= 8 ? 4 : 8;
+        for (size_t v0 = tid; v0 < nvec; v0 += (size_t)U * nth) {
+            A total[U][V];
             for (int g = 0; g < tm.n_islands; ++g) {
-                Vec<T> w;
-                w.u = gb_ld16(parts + (size_t)g * pbytes + v * 16);
+                Vec<T> w[U];
                 #pragma unroll
-                for (int j = 0; j < V; ++j)
-                    total[j] = (g == 0) ? gb_up<T>(w.e[j])
-                                        : GbFold<OP, A>::run(total[j], gb_up<T>(w.e[j]));
+                for (int u = 0; u < U; ++u) {
+                    const size_t v = v0 + (size_t)u * nth;
+                    if (v < nvec) w[u].u = gb_ld16(parts + (size_t)g * pbytes + v * 16, L.ld);
+                }
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        total[u][j] = (g == 0) ? gb_up<T>(w[u].e[j])
+                                      : GbFold<OP, A>::run(total[u][j], gb_up<T>(w[u].e[j]));
+                }
             }
             #pragma unroll
-            for (int j = 0; j < V; ++j)
-                r.e[j] = gb_down<T>(a.divide > 0 ? gb_divide<A>(total[j], a.divide) : total[j]);
-        } else {
+            for (int u = 0; u < U; ++u) {
+                const size_t v = v0 + (size_t)u * nth;
+                if (v >= nvec) continue;
+                Vec<T> r;
+                #pragma unroll
+                for (int j = 0; j < V; ++j)
+                    r.e[j] = gb_down<T>(a.divide > 0 ? gb_divide<A>(total[u][j], a.divide)
+                                                     : total[u][j]);
+                gb_st16(result + v * 16, r.u);
+            }
+        }
+        return;
+    }
+    for (size_t v = tid; v < nvec; v += nth) {
+        Vec<T> r;
+        {
             float acc[V];
             #pragma unroll
             for (int j = 0; j < V; ++j) acc[j] = 0.0f;
@@ -421,11 +474,11 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
     const bool do_a = !split || b < a.role_a;
     const bool do_b = !split || (b >= a.role_a && b < a.role_a + a.role_b);
     const bool do_d = !split || b >= a.role_a + a.role_b;
-    GbLane L = gb_lane_all();
+    GbLane L = gb_lane_all(tm.ld_mode);
     if (split) {
-        if (do_a) L = gb_lane_blocks(0, a.role_a);
-        else if (do_b) L = gb_lane_blocks(a.role_a, a.role_b);
-        else L = gb_lane_blocks(a.role_a + a.role_b, (int)gridDim.x - a.role_a - a.role_b);
+        if (do_a) L = gb_lane_blocks(0, a.role_a, tm.ld_mode);
+        else if (do_b) L = gb_lane_blocks(a.role_a, a.role_b, tm.ld_mode);
+        else L = gb_lane_blocks(a.role_a + a.role_b, (int)gridDim.x - a.role_a - a.role_b, tm.ld_mode);
     }
     for (long t = 0; t < iters; ++t) {
         if (do_a && t < nchunks) {                       // A(t)
@@ -482,7 +535,7 @@ allgather_kernel(GbTeam tm, GbArgs a) {
     const char* in = static_cast<const char*>(a.in);
     char* out = static_cast<char*>(a.out);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
-    const GbLane L = gb_lane_all();
+    const GbLane L = gb_lane_all(tm.ld_mode);
     for (long t = 0; t <= nchunks; ++t) {
         if (t < nchunks) {
             const size_t c0 = (size_t)t * a.chunk;
@@ -520,9 +573,9 @@ reduce_scatter_kernel(GbTeam tm, GbArgs a) {
     const bool split = a.role_a > 0;
     const bool do_a = !split || (int)blockIdx.x < a.role_a;
     const bool do_b = !split || (int)blockIdx.x >= a.role_a;
-    const GbLane L = !split ? gb_lane_all()
-                   : do_a ? gb_lane_blocks(0, a.role_a)
-                          : gb_lane_blocks(a.role_a, (int)gridDim.x - a.role_a);
+    const GbLane L = !split ? gb_lane_all(tm.ld_mode)
+                   : do_a ? gb_lane_blocks(0, a.role_a, tm.ld_mode)
+                          : gb_lane_blocks(a.role_a, (int)gridDim.x - a.role_a, tm.ld_mode);
     for (long t = 0; t <= nchunks; ++t) {
         if (do_a && t < nchunks) {
             const size_t c0 = (size_t)t * a.chunk;
@@ -553,7 +606,7 @@ broadcast_kernel(GbTeam tm, GbArgs a) {
     const unsigned parity = gb_ld_volatile(&tm.ctrl->epoch) & 1u;
     char* data = static_cast<char*>(a.out);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
-    const GbLane L = gb_lane_all();
+    const GbLane L = gb_lane_all(tm.ld_mode);
     for (long t = 0; t <= nchunks; ++t) {
         if (t < nchunks && tm.rank == a.root) {
             const size_t c0 = (size_t)t * a.chunk;
@@ -586,6 +639,33 @@ broadcast_kernel(GbTeam tm, GbArgs a) {
 __global__ void __launch_bounds__(THREADS)
 barrier_kernel(GbTeam tm) {
     gb_sync_all(tm, 0, true);
+}
+
+// Link probe: what one kind of traffic achieves with a given grid, and what a barrier costs.
+//   k = 0  store n bytes from the own workspace (region B) into the next rank's (region A)
+//   k = 1  load n bytes from the next rank's workspace (region B) into the own (region A)
+//   k = 2  local copy of n bytes (region B to region A)
+//   k = 3  n barriers and nothing else
+// Each pass is repeated `divide` times inside the launch; one barrier at the start and the end.
+__global__ void __launch_bounds__(THREADS)
+probe_kernel(GbTeam tm, GbArgs a) {
+    const GbLane L = gb_lane_all(tm.ld_mode);
+    const int next = (tm.rank + 1) % tm.world;
+    if (!gb_sync_all(tm, 0, true)) return;
+    if (a.k == 3) {
+        for (size_t i = 0; i < a.n; ++i)
+            if (!gb_sync_all(tm, 1, false)) return;
+        return;
+    }
+    for (int rep = 0; rep < a.divide; ++rep) {
+        if (a.k == 0)
+            gb_copy_bytes(L, tm.ws[next] + a.off_a, tm.ws[tm.rank] + a.off_b, a.n, false);
+        else if (a.k == 1)
+            gb_copy_bytes(L, tm.ws[tm.rank] + a.off_a, tm.ws[next] + a.off_b, a.n, true);
+        else
+            gb_copy_bytes(L, tm.ws[tm.rank] + a.off_a, tm.ws[tm.rank] + a.off_b, a.n, false);
+    }
+    gb_sync_all(tm, 2, false);
 }
 
 // ---- dispatch -----------------------------------------------------------------------------------------
@@ -650,12 +730,13 @@ extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const Gb
     return cudaErrorInvalidValue;
 }
 
-// kind: 0 all-gather, 1 broadcast, 2 barrier.
+// kind: 0 all-gather, 1 broadcast, 2 barrier, 3 link probe.
 extern "C" int gb_launch_copy(int kind, const GbTeam* team, const GbArgs* args, int grid,
                               cudaStream_t stream) {
     if (kind == 0) allgather_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
     else if (kind == 1) broadcast_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
     else if (kind == 2) barrier_kernel<<<1, THREADS, 0, stream>>>(*team);
+    else if (kind == 3) probe_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }

@@ -40,6 +40,8 @@ struct GbTeam {
     GbCtrl* ctrl;
     volatile unsigned int* status;  // host-mapped: code, peer, seq, phase, ...
     unsigned long long timeout_ns;
+    int ld_mode;                    // how peer-written data is loaded: 0 ld.relaxed.sys, 1 ld.global.cg
+    int pad;
 };
 
 enum GbStatus { GB_OK = 0, GB_TIMEOUT_PEER = 1, GB_TIMEOUT_GRID = 2 };
@@ -64,15 +66,20 @@ __device__ __forceinline__ unsigned int gb_ld_volatile(const unsigned int* p) {
     return v;
 }
 // 16-byte load of data another GPU wrote (or that lives in a peer's memory): never from L1.
-__device__ __forceinline__ uint4 gb_ld16(const void* p) {
-    uint4 v;
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
+// Mode 1 (the default) is a weak load that bypasses L1 (ld.global.cg): L2 is a memory-side
+// cache, so it is coherent for local memory and not involved for a peer's; the barrier that
+// precedes every such load orders it.  Mode 0 is a system-scope relaxed load.
+__device__ __forceinline__ uint4 gb_ld16(const void* p, int mode = 1) {
+    if (mode == 0) {
+        uint4 v;
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+        return v;
+    }
+    return __ldcg(reinterpret_cast<const uint4*>(p));      // ld.global.cg.v4: schedulable
 }
 __device__ __forceinline__ void gb_st16(void* p, uint4 v) {
-    asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};"
-                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    *reinterpret_cast<uint4*>(p) = v;
 }
 
 __device__ __forceinline__ unsigned int* gb_flag_row(const GbTeam& tm, int owner) {
@@ -213,15 +220,18 @@ template <> __device__ __forceinline__ float gb_divide<float>(float v, int by) {
 // kernel splits its grid so that different pipeline steps run at the same time.
 struct GbLane {
     size_t tid, nth;      // this thread's index among the lane's threads, and their number
+    int ld;               // load mode for peer-written data (GbTeam::ld_mode)
 };
-__device__ __forceinline__ GbLane gb_lane_all() {
+__device__ __forceinline__ GbLane gb_lane_all(int ld = 1) {
     GbLane l;
+    l.ld = ld;
     l.tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     l.nth = (size_t)gridDim.x * blockDim.x;
     return l;
 }
-__device__ __forceinline__ GbLane gb_lane_blocks(int first, int count) {
+__device__ __forceinline__ GbLane gb_lane_blocks(int first, int count, int ld = 1) {
     GbLane l;
+    l.ld = ld;
     l.tid = (size_t)(blockIdx.x - first) * blockDim.x + threadIdx.x;
     l.nth = (size_t)count * blockDim.x;
     return l;
@@ -244,13 +254,13 @@ __device__ __forceinline__ void gb_copy_bytes(const GbLane& L, void* dst, const 
             uint4 r[8];
             #pragma unroll
             for (int u = 0; u < 8; ++u)
-                r[u] = peer_src ? gb_ld16(s + ((i + u * nth) << 4))
+                r[u] = peer_src ? gb_ld16(s + ((i + u * nth) << 4), L.ld)
                                 : __ldg((const uint4*)(s + ((i + u * nth) << 4)));
             #pragma unroll
             for (int u = 0; u < 8; ++u) gb_st16(d + ((i + u * nth) << 4), r[u]);
         }
         for (; i < nv; i += nth) {
-            uint4 a = peer_src ? gb_ld16(s + (i << 4)) : __ldg((const uint4*)(s + (i << 4)));
+            uint4 a = peer_src ? gb_ld16(s + (i << 4), L.ld) : __ldg((const uint4*)(s + (i << 4)));
             gb_st16(d + (i << 4), a);
         }
         for (size_t b = (nv << 4) + tid; b < nbytes; b += nth)

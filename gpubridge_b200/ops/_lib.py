@@ -32,7 +32,8 @@ class GbTeam(ctypes.Structure):
                 ("order", ctypes.c_int * MAX_RANKS),
                 ("ws", ctypes.c_void_p * MAX_RANKS),
                 ("ctrl", ctypes.c_void_p), ("status", ctypes.c_void_p),
-                ("timeout_ns", ctypes.c_ulonglong)]
+                ("timeout_ns", ctypes.c_ulonglong), ("ld_mode", ctypes.c_int),
+                ("pad", ctypes.c_int)]
 
 
 class GbArgs(ctypes.Structure):

@@ -34,7 +34,11 @@ from gpubridge_b200.ops import _lib
 
 MIB = 1 << 20
 FLAG_BYTES = 4096
-ONESHOT_MAX = 256 << 10          # largest tensor the one-shot kernel takes
+ONESHOT_MAX = 1 << 20            # largest tensor the one-shot kernel takes
+# Measured with bench/bench_link.py on B200 (2 ranks): one block moves about 45 GB/s of any
+# traffic, a link direction saturates near 650-700 GB/s (16 blocks), a team barrier inside a
+# kernel costs about 10 us.  The pipeline plan below is sized from these.
+BLOCK_GBS, LINK_GBS, BARRIER_S = 45e9, 650e9, 10e-6
 DEFAULT_BYTES = 384 * MIB
 THREADS = 512
 
@@ -64,12 +68,13 @@ class Fabric:
         self.world = layout.world_size
         self.ws, self.ws_bytes, self.ctrl, self.status = ws, ws_bytes, ctrl, status
         self.comm_stream = torch.cuda.Stream(device, priority=-1)
-        self.max_blocks = int(os.environ.get("GPUBRIDGE_FABRIC_BLOCKS", "64"))
+        self.max_blocks = int(os.environ.get("GPUBRIDGE_FABRIC_BLOCKS", "96"))
         self.algo = _config.algo_setting()
         self._status = (ctypes.c_uint * _lib.STATUS_WORDS).from_address(status)
         self._residuals: dict[tuple, tuple[torch.Tensor, tuple]] = {}
         self._lock = threading.Lock()
         self._closed = False
+        self._role_cache: dict[int, tuple[int, int]] = {}
         self.launches = 0            # kernels launched by this team (benchmarks report it)
 
         islands = layout.islands
@@ -91,6 +96,7 @@ class Fabric:
             team.ws[r] = ws[r]
         team.ctrl, team.status = ctrl, status
         team.timeout_ns = timeout_ms * 1_000_000
+        team.ld_mode = int(os.environ.get("GPUBRIDGE_LD_MODE", "1"))
         self.team = team
         self.my_pos = team.my_pos
         self._plan_regions()
@@ -226,7 +232,7 @@ class Fabric:
                 args.divide = int(divide or 0)
                 if oneshot:
                     args.off_a, args.len_a = self.off_oneshot, self.len_oneshot
-                    self._launch_reduce(0, tensor.dtype, op, 0, args, self._grid(nbytes, 16))
+                    self._launch_reduce(0, tensor.dtype, op, 0, args, self._grid(nbytes, 32))
                 else:
                     self._hier(tensor, args, op, compression, chunk_bytes)
         finally:
@@ -238,8 +244,14 @@ class Fabric:
         if chunk_bytes:
             want = max(256, chunk_bytes // esize // k)
         else:
-            # about eight pipeline steps for large tensors, never below 1 MiB per chunk
-            want = max(-(-n // (8 * k)), (MIB // esize) // k)
+            # T(c) = (c + depth) * (barrier + bytes_over_the_busiest_link / c / link rate) is
+            # least at c = sqrt(depth * link time / barrier)
+            m = len(self.layout.islands[self.team.my_island].ranks)
+            share = max((m - 1) / m, (self.n_islands - 1) / k if self.n_islands > 1 else 0.0)
+            depth = 3 if self.n_islands > 1 else 2
+            link_s = tensor.nbytes * share / LINK_GBS
+            chunks = max(1, round((depth * link_s / BARRIER_S) ** 0.5))
+            want = -(-n // (chunks * k))
         stripe = min(stripe_cap, _align_up(min(want, -(-n // k)), 256))
         args.stripe, args.k, args.chunk = stripe, k, stripe * k
         args.off_a, args.len_a = self.off_ha, self.len_ha
@@ -252,11 +264,43 @@ class Fabric:
             args.residual = self._residual(tensor, (stripe, k, nchunks, codec)).data_ptr()
         grid = self._grid(tensor.nbytes * 2)
         nchunks = -(-n // (stripe * k))
-        if nchunks >= 4 and grid >= 12:
-            # enough chunks to keep a pipeline busy: store, reduce and load at the same time
-            args.role_b = max(2, grid // 5)
-            args.role_a = (grid - args.role_b) // 2
+        if nchunks >= 3 and grid >= 12:
+            # enough chunks to keep a pipeline busy: store, reduce and load at the same time,
+            # with blocks shared out by what each role moves (a local copy counts a quarter
+            # of the same bytes over a link)
+            args.role_a, args.role_b = self._roles(grid)
         self._launch_reduce(1, tensor.dtype, op, codec, args, grid)
+
+    def _roles(self, grid: int) -> tuple[int, int]:
+        """Blocks of the storing role (A) and of the reducing role (B, C); the rest load (D).
+        Chosen to minimise the slowest role of one pipeline step under the measured model:
+        every block moves BLOCK_GBS, remote traffic of a role is capped by the link."""
+        cached = self._role_cache.get(grid)
+        if cached is not None:
+            return cached
+        island = self.layout.islands[self.team.my_island]
+        m, k, islands = len(island.ranks), self.k, self.n_islands
+        owner = self.my_pos < k
+        remote = k - (1 if owner else 0)             # stripes stored to / loaded from peers
+        local = 1 if owner else 0
+
+        def seconds(blocks: int, local_stripes: float, remote_stripes: float) -> float:
+            rate = blocks * BLOCK_GBS
+            return local_stripes / rate + remote_stripes / min(rate, LINK_GBS)
+
+        reduce_local = (m + 1 + (islands + 1 if islands > 1 else 0)) / 1.5 if owner else 0.0
+        reduce_remote = float(islands - 1) if owner and islands > 1 else 0.0
+        best, choice = None, (max(1, grid // 3), max(1, grid // 3))
+        for role_b in range(1, grid - 1):
+            for role_a in range(1, grid - role_b):
+                role_d = grid - role_a - role_b
+                worst = max(seconds(role_a, local, remote),
+                            seconds(role_b, reduce_local, reduce_remote),
+                            seconds(role_d, local, remote))
+                if best is None or worst < best:
+                    best, choice = worst, (role_a, role_b)
+        self._role_cache[grid] = choice
+        return choice
 
     def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:
         """Error feedback of this rank's stripes of ``tensor``: found by the buffer's address,
@@ -343,6 +387,22 @@ class Fabric:
         try:
             with torch.cuda.stream(self.comm_stream):
                 self._launch_copy(2, _lib.GbArgs(), 1)
+        finally:
+            self._end(current)
+
+    def probe(self, kind: str, nbytes: int = 0, grid: int = 64, repeat: int = 1) -> None:
+        """Enqueue the link probe: ``store`` / ``load`` (to / from the next rank), ``copy``
+        (local), or ``barrier`` (``nbytes`` barriers).  Time it with events on the
+        communication stream."""
+        args = _lib.GbArgs()
+        args.k = {"store": 0, "load": 1, "copy": 2, "barrier": 3}[kind]
+        args.n = nbytes if kind == "barrier" else min(nbytes, self.len_ha, self.len_hb)
+        args.divide = repeat
+        args.off_a, args.off_b = self.off_ha, self.off_hb + self.len_hb
+        current = self._begin()
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                self._launch_copy(3, args, grid)
         finally:
             self._end(current)
 

@@ -34,13 +34,14 @@ class _FusedCrossEntropy(torch.autograd.Function):
             _lib.stream_ptr(logits.device))
         _lib.check(code, "gb_xent_fwd_bwd")
         launches += 1
-        ctx.save_for_backward(logits)          # now holds d(loss)/d(logits)
+        ctx.mark_dirty(logits)                 # now holds d(loss)/d(logits)
+        ctx.save_for_backward(logits)
         ctx.unit_grad = unit_grad
-        ctx.mark_dirty(logits)
-        return loss
+        ctx.mark_non_differentiable(logits)
+        return loss, logits                    # a tensor modified in place must be an output
 
     @staticmethod
-    def backward(ctx, grad_loss):
+    def backward(ctx, grad_loss, _unused=None):
         (grad_logits,) = ctx.saved_tensors
         if not ctx.unit_grad:
             grad_logits = grad_logits * grad_loss.to(grad_logits.dtype)
@@ -65,4 +66,4 @@ def fused_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, vocab: int 
               and targets.is_contiguous())
     if not usable:
         return F.cross_entropy(logits[:, :vocab].float(), targets)
-    return _FusedCrossEntropy.apply(logits, targets, vocab, unit_grad)
+    return _FusedCrossEntropy.apply(logits, targets, vocab, unit_grad)[0]
