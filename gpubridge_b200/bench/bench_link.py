@@ -26,7 +26,7 @@ def main() -> int:
     try:
         if fabric is None:
             raise SystemExit("bench_link needs a GPU team with a fabric")
-        nbytes = min(fabric.len_ha, fabric.len_hb, 64 << 20)
+        nbytes = min(fabric.len_ha, fabric.len_hb, fabric.len_hc, 64 << 20)
 
         def timed(kind: str, grid: int, n: int, repeat: int) -> float:
             with torch.cuda.stream(fabric.comm_stream):
@@ -47,9 +47,12 @@ def main() -> int:
             rows.append({"probe": "barrier", "grid": grid,
                          "us_per_barrier": round((ms - base) * 1000 / 200, 2),
                          "launch_plus_2_barriers_us": round(base * 1000, 1)})
-            for kind in ("store", "load", "copy"):
+            for kind in ("store", "load", "copy", "mixed", "mixed3"):
+                if kind.startswith("mixed") and grid < 8:
+                    continue
                 repeat = 8
                 ms = timed(kind, grid, nbytes, repeat) - base
+                # mixed: every group moves nbytes * repeat; the rate is per group
                 rows.append({"probe": kind, "grid": grid, "bytes": nbytes,
                              "gbs": round(nbytes * repeat / (ms * 1e-3) / 1e9, 1)})
         fabric.check()

@@ -646,6 +646,8 @@ barrier_kernel(GbTeam tm) {
 //   k = 1  load n bytes from the next rank's workspace (region B) into the own (region A)
 //   k = 2  local copy of n bytes (region B to region A)
 //   k = 3  n barriers and nothing else
+//   k = 4  the first half of the blocks store while the second half load (mixed traffic)
+//   k = 5  like 4 plus a third group that copies locally
 // Each pass is repeated `divide` times inside the launch; one barrier at the start and the end.
 __global__ void __launch_bounds__(THREADS)
 probe_kernel(GbTeam tm, GbArgs a) {
@@ -655,6 +657,25 @@ probe_kernel(GbTeam tm, GbArgs a) {
     if (a.k == 3) {
         for (size_t i = 0; i < a.n; ++i)
             if (!gb_sync_all(tm, 1, false)) return;
+        return;
+    }
+    if (a.k == 4 || a.k == 5) {
+        const int groups = a.k == 4 ? 2 : 3;
+        const int per = (int)gridDim.x / groups;
+        const int g = (int)blockIdx.x / per;
+        if (g < groups) {
+            const GbLane G = gb_lane_blocks(g * per, per, tm.ld_mode);
+            for (int rep = 0; rep < a.divide; ++rep) {
+                if (g == 0)
+                    gb_copy_bytes(G, tm.ws[next] + a.off_a, tm.ws[tm.rank] + a.off_b, a.n, false);
+                else if (g == 1)
+                    gb_copy_bytes(G, tm.ws[tm.rank] + a.off_c, tm.ws[next] + a.off_b, a.n, true);
+                else
+                    gb_copy_bytes(G, tm.ws[tm.rank] + a.off_a + a.len_a, tm.ws[tm.rank] + a.off_b,
+                                  a.n, false);
+            }
+        }
+        gb_sync_all(tm, 2, false);
         return;
     }
     for (int rep = 0; rep < a.divide; ++rep) {

@@ -1,0 +1,147 @@
+"""``bridge="multitcp"``: the tagged bridge over the native multi-stream TCP worker.
+
+The worker is ``csrc/gb_tcp.cpp`` inside the library (the reference ships it as a Rust crate
+with the same C ABI idea: src/gpubridge/multitcp/__init__.py, crate/src/lib.rs).  Settings:
+``GPUBRIDGE_MULTITCP_STREAMS`` (connections per peer, default 4),
+``GPUBRIDGE_MULTITCP_CHUNK_BYTES`` (default 4 MiB), ``GPUBRIDGE_MULTITCP_IFADDR`` (the
+local IPv4 address to listen on, default 127.0.0.1 for one box).
+
+``python -m gpubridge_b200.multitcp info`` prints the protocol version and the settings.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import sys
+import time
+
+from gpubridge_b200 import config as _config
+from gpubridge_b200.tagged import TaggedBridge, wait_for_keys
+from gpubridge_b200.transport import register_transport
+
+STREAMS_ENV = "GPUBRIDGE_MULTITCP_STREAMS"
+CHUNK_ENV = "GPUBRIDGE_MULTITCP_CHUNK_BYTES"
+IFADDR_ENV = "GPUBRIDGE_MULTITCP_IFADDR"
+
+
+def _library():
+    from gpubridge_b200.ops import _lib
+    L = _lib.lib()
+    if not getattr(L, "_tcp_declared", False):
+        vp, i, u64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint64
+        L.gb_tcp_create.restype = vp
+        L.gb_tcp_create.argtypes = [i, i, i, ctypes.c_char_p]
+        L.gb_tcp_address.argtypes = [vp, ctypes.c_char_p, i]
+        L.gb_tcp_connect.argtypes = [vp, ctypes.POINTER(ctypes.c_char_p), ctypes.c_double]
+        L.gb_tcp_send.restype = ctypes.c_long
+        L.gb_tcp_send.argtypes = [vp, i, vp, u64, u64]
+        L.gb_tcp_recv.restype = ctypes.c_long
+        L.gb_tcp_recv.argtypes = [vp, i, vp, u64, u64]
+        L.gb_tcp_wait.argtypes = [vp, ctypes.POINTER(ctypes.c_long), i, ctypes.c_double]
+        L.gb_tcp_abort.argtypes = [vp]
+        L.gb_tcp_close.argtypes = [vp]
+        L.gb_tcp_last_error.restype = ctypes.c_char_p
+        L.gb_tcp_last_error.argtypes = [vp]
+        L._tcp_declared = True
+    return L
+
+
+def streams_setting() -> int:
+    raw = os.environ.get(STREAMS_ENV, "").strip()
+    value = int(raw) if raw else 4
+    if not 1 <= value <= 64:
+        raise ValueError(f"{STREAMS_ENV} must be between 1 and 64")
+    return value
+
+
+class Worker:
+    """One member's native worker."""
+
+    def __init__(self, index: int, members: int, streams: int, host: str) -> None:
+        self.lib = _library()
+        self.handle = self.lib.gb_tcp_create(index, members, streams, host.encode())
+        if not self.handle:
+            raise RuntimeError(f"multitcp: {self.lib.gb_tcp_last_error(None).decode()}")
+
+    def address(self) -> str:
+        buf = ctypes.create_string_buffer(128)
+        self.lib.gb_tcp_address(self.handle, buf, 128)
+        return buf.value.decode()
+
+    def connect(self, addresses: list[str], timeout_s: float) -> None:
+        array = (ctypes.c_char_p * len(addresses))(*[a.encode() for a in addresses])
+        if self.lib.gb_tcp_connect(self.handle, array, timeout_s) != 0:
+            raise RuntimeError(f"multitcp: {self._error()}")
+
+    def _error(self) -> str:
+        return self.lib.gb_tcp_last_error(self.handle).decode()
+
+    def send(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
+        op = self.lib.gb_tcp_send(self.handle, peer, ptr, nbytes, tag)
+        if op < 0:
+            raise RuntimeError(f"multitcp: {self._error()}")
+        return op
+
+    def recv(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
+        op = self.lib.gb_tcp_recv(self.handle, peer, ptr, nbytes, tag)
+        if op < 0:
+            raise RuntimeError(f"multitcp: {self._error()}")
+        return op
+
+    def wait(self, ids: list[int], deadline: float) -> None:
+        array = (ctypes.c_long * len(ids))(*ids)
+        left = max(0.001, deadline - time.monotonic())
+        if self.lib.gb_tcp_wait(self.handle, array, len(ids), left) != 0:
+            raise RuntimeError(f"multitcp: {self._error()}")
+
+    def abort(self) -> None:
+        if self.handle:
+            self.lib.gb_tcp_abort(self.handle)
+
+    def close(self) -> None:
+        handle, self.handle = self.handle, None
+        if handle:
+            self.lib.gb_tcp_close(handle)
+
+
+@register_transport
+class MultiTcpTransport(TaggedBridge):
+    name = "multitcp"
+
+    @classmethod
+    def _connect(cls, store, key, members, rank, timeout, deadline):
+        index = members.index(rank)
+        host = os.environ.get(IFADDR_ENV, "").strip() or "127.0.0.1"
+        chunk = _config.size_setting(CHUNK_ENV, 4 << 20)
+        worker = Worker(index, len(members), streams_setting(), host)
+        try:
+            store.set(f"{key}/address/{rank}", worker.address())
+            addresses = wait_for_keys(store, [f"{key}/address/{m}" for m in members], deadline,
+                                      "every bridge member's multitcp address")
+            worker.connect(addresses, max(0.1, deadline - time.monotonic()))
+            transport = cls(worker, members, rank, timeout, chunk)
+            transport._handshake(deadline)
+            return transport
+        except BaseException:
+            worker.close()
+            raise
+
+
+def main(argv: list[str]) -> int:
+    command = argv[0] if argv else "info"
+    if command == "build":
+        from gpubridge_b200.ops import _build
+        print(_build.build())
+        return 0
+    if command == "info":
+        print(json.dumps({"protocol": _library().gb_tcp_protocol(), "streams": streams_setting(),
+                          "chunk_bytes": _config.size_setting(CHUNK_ENV, 4 << 20),
+                          "ifaddr": os.environ.get(IFADDR_ENV, "127.0.0.1")}))
+        return 0
+    print("usage: python -m gpubridge_b200.multitcp [build|info]", file=sys.stderr)
+    return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))

@@ -1,6 +1,6 @@
 """Build the native library in-tree: ``gpubridge_b200/lib/libgpubridge_b200.so``.
 
-Every ``.cu`` under ``csrc/`` is compiled for sm_100a only
+Every ``.cu`` and ``.cpp`` under ``csrc/`` is compiled for sm_100a only
 (``-gencode arch=compute_100a,code=sm_100a``) and linked into one shared library that the
 Python side loads with ``ctypes``; the kernels take raw pointers and a ``cudaStream_t``,
 so neither torch's headers nor pybind11 are involved and a full rebuild takes well under a
@@ -35,7 +35,7 @@ def nvcc() -> str:
 
 
 def sources() -> list[str]:
-    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
 
 
 def _digest(path: str) -> str:

@@ -395,10 +395,12 @@ class Fabric:
         (local), or ``barrier`` (``nbytes`` barriers).  Time it with events on the
         communication stream."""
         args = _lib.GbArgs()
-        args.k = {"store": 0, "load": 1, "copy": 2, "barrier": 3}[kind]
-        args.n = nbytes if kind == "barrier" else min(nbytes, self.len_ha, self.len_hb)
+        args.k = {"store": 0, "load": 1, "copy": 2, "barrier": 3, "mixed": 4, "mixed3": 5}[kind]
+        args.n = nbytes if kind == "barrier" else min(nbytes, self.len_ha, self.len_hb,
+                                                      self.len_hc)
         args.divide = repeat
-        args.off_a, args.off_b = self.off_ha, self.off_hb + self.len_hb
+        args.off_a, args.off_b, args.off_c = self.off_ha, self.off_hb + self.len_hb, self.off_hc
+        args.len_a = self.len_ha
         current = self._begin()
         try:
             with torch.cuda.stream(self.comm_stream):
