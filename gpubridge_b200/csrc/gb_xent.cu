@@ -178,3 +178,66 @@ extern "C" int gb_xent_fwd_bwd(void* logits, int dtype, const long long* targets
     }
     return (int)cudaErrorInvalidValue;
 }
+
+// ---- entry point that allocates nothing -------------------------------------------------------
+// See gb_xent_noalloc.h.  The scratch that gb_xent_fwd_bwd takes from its caller lives here in a
+// file-scope device array instead, so the call needs no allocation of any kind.
+#include <mutex>
+#include "gb_xent_noalloc.h"
+
+namespace {
+
+// Layout of the array: GB_XENT_NOALLOC_MAX_ROWS row losses (float), then the arrival counter.
+constexpr size_t NOALLOC_COUNTER_AT = sizeof(float) * GB_XENT_NOALLOC_MAX_ROWS;
+constexpr size_t NOALLOC_BYTES = NOALLOC_COUNTER_AT + 256;
+
+// One copy per GPU that loads the library, held until the process exits.  In host code this
+// name is only a handle for cudaGetSymbolAddress; it is not a device address.
+static __device__ __align__(256) unsigned char gb_xent_noalloc_scratch[NOALLOC_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_noalloc_mutex;
+unsigned char* g_noalloc_ptr[MAX_DEVICES] = {};
+
+// The device address of the array on the current device, looked up once per device.
+cudaError_t noalloc_scratch(unsigned char** out) {
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return err;
+    if (device < 0 || device >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> guard(g_noalloc_mutex);
+    if (g_noalloc_ptr[device] == nullptr) {
+        void* ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, gb_xent_noalloc_scratch);
+        if (err != cudaSuccess) return err;
+        g_noalloc_ptr[device] = static_cast<unsigned char*>(ptr);
+    }
+    *out = g_noalloc_ptr[device];
+    return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int gb_xent_fwd_bwd_noalloc(void* logits, int dtype, const long long* targets,
+                                       size_t rows, size_t vocab, size_t ld, float* loss_out,
+                                       cudaStream_t stream) {
+    if (rows > GB_XENT_NOALLOC_MAX_ROWS) return GB_XENT_NOALLOC_TOO_MANY_ROWS;
+    unsigned char* scratch = nullptr;
+    cudaError_t err = noalloc_scratch(&scratch);
+    if (err != cudaSuccess) return (int)err;
+    float* row_loss = reinterpret_cast<float*>(scratch);
+    unsigned int* counter = reinterpret_cast<unsigned int*>(scratch + NOALLOC_COUNTER_AT);
+    // The arrival counter must start at zero; an earlier call that was cut short may have left
+    // it otherwise.  A memset on the stream allocates nothing.
+    err = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
+    if (err != cudaSuccess) return (int)err;
+    return gb_xent_fwd_bwd(logits, dtype, targets, rows, vocab, ld, row_loss, counter, loss_out,
+                           stream);
+}
+
+extern "C" const char* gb_xent_noalloc_error(int code) {
+    if (code == GB_XENT_NOALLOC_TOO_MANY_ROWS)
+        return "gb_xent_fwd_bwd_noalloc: more rows than GB_XENT_NOALLOC_MAX_ROWS (65536); "
+               "split the batch or use gb_xent_fwd_bwd with scratch of your own";
+    return cudaGetErrorString((cudaError_t)code);
+}
