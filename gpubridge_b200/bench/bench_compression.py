@@ -1,0 +1,99 @@
+"""Codec kernel throughput against the device copy bandwidth (the reference's method:
+scripts/gpu/bench_compression.py, docs/COMPRESSION.md:228-236).
+
+For each mode, format and dtype: median of ``--trials`` timed launches (CUDA events, after
+warm-up, inputs larger than L2) of ``quantize`` (with error feedback, as a training step runs
+it) and of ``dequantize_accumulate`` over two members.  Reported as *value* bytes per second
+(``numel * element_size / t``, the reference's unit) and as a fraction of what ``b.copy_(a)``
+of the same tensor achieves, plus the algorithmic traffic fraction of the measured HBM peak in
+``MEASURED_PEAKS.json`` when that file is present.
+
+    python -m gpubridge_b200.bench.bench_compression --numel 268435456
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+from gpubridge_b200 import compression as C
+from gpubridge_b200.ops import codec
+
+
+def timed(fn, trials: int) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(trials):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        out.append(a.elapsed_time(b))
+    return statistics.median(out)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--trials", type=int, default=10)
+    ap.add_argument("--dtypes", default="float32,bfloat16")
+    ap.add_argument("--only", default="", help="mode:format:dtype:op to run a single case")
+    args = ap.parse_args(argv)
+    n = args.numel
+    peaks = {}
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    if os.path.exists(os.path.join(root, "MEASURED_PEAKS.json")):
+        peaks = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
+    rows = []
+    for dtype_name in args.dtypes.split(","):
+        dtype = getattr(torch, dtype_name)
+        x = torch.randn(n, device="cuda").to(dtype)
+        y = torch.empty_like(x)
+        copy_ms = timed(lambda: y.copy_(x), args.trials)
+        esize = x.element_size()
+        copy_gbs = 2 * n * esize / (copy_ms * 1e-3) / 1e9
+        rows.append({"op": "copy", "dtype": dtype_name, "ms": round(copy_ms, 4),
+                     "traffic_gbs": round(copy_gbs, 1)})
+        for mode in C.MODES:
+            if dtype not in C.APPLIES_TO[mode]:
+                continue
+            for fmt in (C.FORMATS if mode == "fp8" else ("ref",)):
+                if args.only and not args.only.startswith(f"{mode}:{fmt}:{dtype_name}"):
+                    continue
+                nbytes = C.payload_nbytes(mode, n, fmt)
+                payload = torch.empty((2, nbytes), dtype=torch.uint8, device="cuda")
+                residual = torch.zeros(n, device="cuda")
+                out = torch.empty_like(x)
+                cases = {
+                    "quantize": (lambda: codec.quantize(mode, x, residual, payload[0], fmt),
+                                 n * esize + 8 * n + nbytes),          # x, residual r+w, payload
+                    "dequantize": (lambda: codec.dequantize_accumulate(mode, payload, out, fmt),
+                                   2 * nbytes + n * esize),
+                }
+                codec.quantize(mode, x, None, payload[1], fmt)
+                for op, (fn, traffic) in cases.items():
+                    if args.only and not args.only.endswith(op):
+                        continue
+                    ms = timed(fn, args.trials)
+                    row = {"op": op, "mode": mode, "format": fmt, "dtype": dtype_name,
+                           "numel": n, "ms": round(ms, 4),
+                           "value_gbs": round(n * esize / (ms * 1e-3) / 1e9, 1),
+                           "of_copy_value_rate": round((n * esize / ms) / (n * esize / copy_ms), 3),
+                           "traffic_gbs": round(traffic / (ms * 1e-3) / 1e9, 1)}
+                    if peaks.get("hbm_gbs"):
+                        row["traffic_of_measured_hbm"] = round(row["traffic_gbs"] / peaks["hbm_gbs"], 3)
+                    rows.append(row)
+    for row in rows:
+        print(json.dumps(row), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -45,8 +45,8 @@ struct GbArgs {
     int k;                    // stripes per chunk
     int divide;               // > 0: divide the sum by it (AVG)
     int root;                 // broadcast source (team rank)
-    int role_a;               // > 0: split the grid into roles; blocks of the first role
-    int role_b;               // blocks of the second role (the rest form the last role)
+    int role_a;               // all-reduce: channels (0 = 1); reduce-scatter: blocks that store
+    int role_b;               // unused
     int pad;
     size_t off_a, off_b, off_c;   // regions
     size_t len_a, len_b, len_c;   // bytes of one buffer of each region
@@ -464,29 +464,30 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
     const size_t sbytes = a.stripe * sizeof(T);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
     const int depth = bridged ? 3 : 2;                   // iterations between A and D
-    const long iters = nchunks + depth;
-    // Roles: with a split grid the blocks of role A store chunk t while those of role B
-    // reduce chunk t-1 (and t-2) and those of role D load chunk t-depth, so both directions
-    // of the links and the local memory work at the same time.  Without, every block takes
-    // every step in turn (best for a single chunk).
-    const bool split = a.role_a > 0;
-    const int b = (int)blockIdx.x;
-    const bool do_a = !split || b < a.role_a;
-    const bool do_b = !split || (b >= a.role_a && b < a.role_a + a.role_b);
-    const bool do_d = !split || b >= a.role_a + a.role_b;
-    GbLane L = gb_lane_all(tm.ld_mode);
-    if (split) {
-        if (do_a) L = gb_lane_blocks(0, a.role_a, tm.ld_mode);
-        else if (do_b) L = gb_lane_blocks(a.role_a, a.role_b, tm.ld_mode);
-        else L = gb_lane_blocks(a.role_a + a.role_b, (int)gridDim.x - a.role_a - a.role_b, tm.ld_mode);
-    }
-    for (long t = 0; t < iters; ++t) {
-        if (do_a && t < nchunks) {                       // A(t)
-            const size_t c0 = (size_t)t * a.chunk;
+    // Channels: the grid is cut into `channels` equal groups of blocks.  Channel c takes the
+    // chunks c, c + channels, ... through its own pipeline, with its own barrier (control
+    // block and flag row c) and its own buffers, so while one channel sits in a barrier or
+    // reduces locally the others keep the links busy.
+    const int channels = a.role_a > 0 ? a.role_a : 1;
+    const int per = (int)gridDim.x / channels;
+    const int ch = (int)blockIdx.x / per;
+    if (ch >= channels) return;                          // grid not a multiple: idle blocks
+    const GbLane L = gb_lane_blocks(ch * per, per, tm.ld_mode);
+    const long mine = nchunks > ch ? (nchunks - ch + channels - 1) / channels : 0;
+    if (mine == 0) return;
+    const long iters = mine + depth;
+    const size_t off_a = a.off_a + (size_t)ch * 2 * a.len_a;
+    const size_t off_b = a.off_b + (size_t)ch * 2 * a.len_b;
+    const size_t off_c = a.off_c + (size_t)ch * 2 * a.len_c;
+    GbArgs b = a;                                        // this channel's regions
+    b.off_a = off_a; b.off_b = off_b; b.off_c = off_c;
+    for (long i = 0; i < iters; ++i) {
+        if (i < mine) {                                  // A(i)
+            const size_t c0 = (size_t)(ch + i * channels) * a.chunk;
             for (int dj = 0; dj < a.k; ++dj) {
                 const int j = (tm.my_pos + dj) % a.k;
                 const int own = tm.order[tm.island_off[tm.my_island] + j];
-                char* dst = tm.ws[own] + a.off_a + (size_t)(t & 1) * a.len_a
+                char* dst = tm.ws[own] + off_a + (size_t)(i & 1) * a.len_a
                             + (size_t)tm.my_pos * sbytes;
                 const size_t valid = stripe_valid(a, c0, j);
                 if (valid)
@@ -495,23 +496,23 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
                 zero_range(L, dst, valid * sizeof(T), round_up(valid, 256) * sizeof(T));
             }
         }
-        if (do_b && owner && t >= 1 && t - 1 < nchunks) {        // B(t-1)
-            const long c = t - 1;
+        if (owner && i >= 1 && i - 1 < mine) {           // B(i-1)
+            const long c = ch + (i - 1) * channels;
             const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
-            const char* slots = tm.ws[tm.rank] + a.off_a + (size_t)(c & 1) * a.len_a;
+            const char* slots = tm.ws[tm.rank] + off_a + (size_t)((i - 1) & 1) * a.len_a;
             if (CODEC == GB_RAW)
-                island_reduce_raw<T, OP>(L, tm, a, slots, need, (int)(c & 1));
+                island_reduce_raw<T, OP>(L, tm, b, slots, need, (int)((i - 1) & 1));
             else
-                island_reduce_coded<T, CODEC>(L, tm, a, slots, need, (int)(c & 1),
+                island_reduce_coded<T, CODEC>(L, tm, b, slots, need, (int)((i - 1) & 1),
                                               a.residual + (size_t)c * a.stripe);
         }
-        if (do_b && bridged && owner && t >= 2 && t - 2 < nchunks) {   // C(t-2)
-            const long c = t - 2;
+        if (bridged && owner && i >= 2 && i - 2 < mine) {        // C(i-2)
+            const long c = ch + (i - 2) * channels;
             const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
-            bridge_reduce<T, OP, CODEC>(L, tm, a, need, (int)(c & 1));
+            bridge_reduce<T, OP, CODEC>(L, tm, b, need, (int)((i - 2) & 1));
         }
-        if (do_d && t >= depth) {                        // D(t-depth)
-            const long c = t - depth;
+        if (i >= depth) {                                // D(i-depth)
+            const long c = ch + (i - depth) * channels;
             const size_t c0 = (size_t)c * a.chunk;
             for (int dj = 0; dj < a.k; ++dj) {
                 const int j = (tm.my_pos + dj) % a.k;
@@ -519,11 +520,13 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
                 const size_t valid = stripe_valid(a, c0, j);
                 if (valid)
                     gb_copy_bytes(L, out + c0 + (size_t)j * a.stripe,
-                                  tm.ws[own] + a.off_c + (size_t)(c & 1) * a.len_c,
+                                  tm.ws[own] + off_c + (size_t)((i - depth) & 1) * a.len_c,
                                   valid * sizeof(T), true);
             }
         }
-        if (t + 1 < iters && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
+        if (i + 1 < iters &&
+            !gb_sync(tm, ch, (unsigned)per, (unsigned)(i < 7 ? i : 7), i == 0 && ch == 0))
+            return;
     }
 }
 

@@ -16,6 +16,7 @@
 #include <stdint.h>
 
 #define GB_MAX_RANKS 16
+#define GB_MAX_CHANNELS 8           // independent pipelines (control blocks, flag rows)
 #define GB_FLAG_BYTES 4096          // start of every workspace: the flag rows
 #define GB_STATUS_WORDS 8
 
@@ -114,40 +115,45 @@ __device__ __forceinline__ bool gb_wait_flag(const GbTeam& tm, const unsigned in
     }
 }
 
-// Grid barrier + team barrier.  Returns false when this or an earlier wait ran out; the
-// caller must then return without touching peers again.  `phase` only labels a failure.
-__device__ __forceinline__ bool gb_sync_all(const GbTeam& tm, unsigned phase, bool first) {
+// Barrier of `nblocks` blocks of this grid and - with `with_peers` - of the same blocks on
+// every peer.  `channel` selects the control block and the flag row, so independent groups of
+// blocks (channels) can run their own pipelines and barriers inside one kernel.  Returns false
+// when this or an earlier wait ran out; the caller must then return without touching peers
+// again.  `phase` only labels a failure and selects a timestamp slot.
+__device__ __forceinline__ bool gb_sync(const GbTeam& tm, int channel, unsigned nblocks,
+                                        unsigned phase, bool first, bool with_peers = true) {
     __shared__ unsigned s_gen, s_last, s_seq;
-    GbCtrl* c = tm.ctrl;
+    GbCtrl* c = tm.ctrl + channel;
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();                       // this block's stores, local and remote
         s_gen = gb_ld_volatile(&c->grid_gen);         // read the generation before arriving
         unsigned arrived = atomicAdd(&c->grid_arrive, 1u) + 1u;
-        s_last = (arrived == gridDim.x);
+        s_last = (arrived == nblocks);
         s_seq = gb_ld_volatile(&c->seq) + 1u;
     }
     __syncthreads();
     if (s_last) {
-        // The last block to arrive meets the peers on behalf of the grid.
+        // The last block to arrive meets the peers on behalf of its channel.
         const unsigned seq = s_seq;
         const int t = threadIdx.x;
-        if (t < tm.world && t != tm.rank) {
+        const int row = channel * GB_MAX_RANKS;
+        if (with_peers && t < tm.world && t != tm.rank) {
             __threadfence_system();
-            gb_st_release_sys(gb_flag_row(tm, t) + tm.rank, seq);
+            gb_st_release_sys(gb_flag_row(tm, t) + row + tm.rank, seq);
         }
-        if (t < tm.world && t != tm.rank) {
-            if (!gb_wait_flag(tm, gb_flag_row(tm, tm.rank) + t, seq, true, tm.timeout_ns))
+        if (with_peers && t < tm.world && t != tm.rank) {
+            if (!gb_wait_flag(tm, gb_flag_row(tm, tm.rank) + row + t, seq, true, tm.timeout_ns))
                 gb_fail(tm, GB_TIMEOUT_PEER, (unsigned)t, seq, phase);
         }
         __syncthreads();
         if (t == 0) {
-            c->seq = seq;
+            if (with_peers) c->seq = seq;
             if (first) c->epoch += 1u;
             if (phase < 8u) c->stamps[phase] = gb_now();
             c->grid_arrive = 0u;
             __threadfence();
-            atomicAdd(&c->grid_gen, 1u);              // release the grid
+            atomicAdd(&c->grid_gen, 1u);              // release the channel's blocks
         }
     } else if (threadIdx.x == 0) {
         if (!gb_wait_flag(tm, &c->grid_gen, s_gen + 1u, false, 2ull * tm.timeout_ns))
@@ -155,7 +161,21 @@ __device__ __forceinline__ bool gb_sync_all(const GbTeam& tm, unsigned phase, bo
         __threadfence();
     }
     __syncthreads();
-    return gb_ld_volatile(&c->abort) == 0u;
+    return gb_ld_volatile(&tm.ctrl->abort) == 0u;
+}
+
+// The whole grid as one channel.
+__device__ __forceinline__ bool gb_sync_all(const GbTeam& tm, unsigned phase, bool first) {
+    return gb_sync(tm, 0, gridDim.x, phase, first, true);
+}
+
+__device__ __forceinline__ unsigned int gb_ld_acquire_gpu(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void gb_st_release_gpu(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
 
 // ---- element types -------------------------------------------------------------------------

@@ -95,6 +95,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_launch_copy.argtypes = [i, ctypes.POINTER(GbTeam), ctypes.POINTER(GbArgs), i, vp]
     L.gb_adamw_step.argtypes = [vp, vp, vp, vp, sz, vp] + [ctypes.c_float] * 6 + [i, vp]
     L.gb_xent_fwd_bwd.argtypes = [vp, i, vp, sz, sz, sz, vp, vp, vp, vp]
+    L.gb_allgather_gemm.argtypes = [ctypes.POINTER(GbTeam), vp, vp, vp, vp, vp, vp, ctypes.c_uint,
+                                    i, i, i, sz, i, i, vp]
     L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
     L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]
 

@@ -68,13 +68,16 @@ class Fabric:
         self.world = layout.world_size
         self.ws, self.ws_bytes, self.ctrl, self.status = ws, ws_bytes, ctrl, status
         self.comm_stream = torch.cuda.Stream(device, priority=-1)
-        self.max_blocks = int(os.environ.get("GPUBRIDGE_FABRIC_BLOCKS", "96"))
+        self.max_blocks = int(os.environ.get("GPUBRIDGE_FABRIC_BLOCKS", "128"))
         self.algo = _config.algo_setting()
         self._status = (ctypes.c_uint * _lib.STATUS_WORDS).from_address(status)
         self._residuals: dict[tuple, tuple[torch.Tensor, tuple]] = {}
         self._lock = threading.Lock()
         self._closed = False
         self._role_cache: dict[int, tuple[int, int]] = {}
+        # tuning overrides (benchmarks): fixed pipeline depth and role split
+        self.force_chunks = int(os.environ.get("GPUBRIDGE_HIER_CHUNKS", "0")) or None
+        self.force_channels = int(os.environ.get("GPUBRIDGE_HIER_CHANNELS", "0")) or None
         self.launches = 0            # kernels launched by this team (benchmarks report it)
 
         islands = layout.islands
@@ -240,67 +243,38 @@ class Fabric:
 
     def _hier(self, tensor, args, op, compression, chunk_bytes) -> None:
         esize, n, k = tensor.element_size(), tensor.numel(), self.k
-        stripe_cap = _align_down(self.stripe_bytes // esize, 256)
+        nbytes = tensor.nbytes
+        grid = self._grid(nbytes * 2)
+        # Channels: independent pipelines that hide each other's barriers and local phases.
+        # One for small tensors (a barrier costs more than the data), up to four for large.
+        channels = self.force_channels or (1 if nbytes < (4 << 20) else 2 if nbytes < (32 << 20) else 4)
+        channels = max(1, min(channels, grid // 8 or 1, 8))
+        grid = grid // channels * channels
+        stripe_cap = _align_down(self.stripe_bytes // channels // esize, 256)
         if chunk_bytes:
             want = max(256, chunk_bytes // esize // k)
         else:
-            # T(c) = (c + depth) * (barrier + bytes_over_the_busiest_link / c / link rate) is
-            # least at c = sqrt(depth * link time / barrier)
+            # per channel: T(c) = (c + depth) * (barrier + link time / c) is least at
+            # c = sqrt(depth * link time / barrier)
             m = len(self.layout.islands[self.team.my_island].ranks)
             share = max((m - 1) / m, (self.n_islands - 1) / k if self.n_islands > 1 else 0.0)
             depth = 3 if self.n_islands > 1 else 2
-            link_s = tensor.nbytes * share / LINK_GBS
-            chunks = max(1, round((depth * link_s / BARRIER_S) ** 0.5))
-            want = -(-n // (chunks * k))
-        stripe = min(stripe_cap, _align_up(min(want, -(-n // k)), 256))
+            link_s = nbytes / channels * share / LINK_GBS
+            chunks = self.force_chunks or max(1, round((depth * link_s / BARRIER_S) ** 0.5))
+            want = -(-n // (chunks * channels * k))
+        stripe = min(stripe_cap, _align_up(max(1, min(want, -(-n // k))), 256))
         args.stripe, args.k, args.chunk = stripe, k, stripe * k
-        args.off_a, args.len_a = self.off_ha, self.len_ha
-        args.off_b, args.len_b = self.off_hb, self.len_hb
-        args.off_c, args.len_c = self.off_hc, self.len_hc
+        # every channel owns two buffers of each region
+        args.off_a, args.len_a = self.off_ha, self.len_ha // channels // 4096 * 4096
+        args.off_b, args.len_b = self.off_hb, self.len_hb // channels // 4096 * 4096
+        args.off_c, args.len_c = self.off_hc, self.len_hc // channels // 4096 * 4096
+        args.role_a = channels
         codec = 0
+        nchunks = -(-n // (stripe * k))
         if compression is not None:
             codec = _lib.CODECS[tuple(compression)]
-            nchunks = -(-n // (stripe * k))
             args.residual = self._residual(tensor, (stripe, k, nchunks, codec)).data_ptr()
-        grid = self._grid(tensor.nbytes * 2)
-        nchunks = -(-n // (stripe * k))
-        if nchunks >= 3 and grid >= 12:
-            # enough chunks to keep a pipeline busy: store, reduce and load at the same time,
-            # with blocks shared out by what each role moves (a local copy counts a quarter
-            # of the same bytes over a link)
-            args.role_a, args.role_b = self._roles(grid)
         self._launch_reduce(1, tensor.dtype, op, codec, args, grid)
-
-    def _roles(self, grid: int) -> tuple[int, int]:
-        """Blocks of the storing role (A) and of the reducing role (B, C); the rest load (D).
-        Chosen to minimise the slowest role of one pipeline step under the measured model:
-        every block moves BLOCK_GBS, remote traffic of a role is capped by the link."""
-        cached = self._role_cache.get(grid)
-        if cached is not None:
-            return cached
-        island = self.layout.islands[self.team.my_island]
-        m, k, islands = len(island.ranks), self.k, self.n_islands
-        owner = self.my_pos < k
-        remote = k - (1 if owner else 0)             # stripes stored to / loaded from peers
-        local = 1 if owner else 0
-
-        def seconds(blocks: int, local_stripes: float, remote_stripes: float) -> float:
-            rate = blocks * BLOCK_GBS
-            return local_stripes / rate + remote_stripes / min(rate, LINK_GBS)
-
-        reduce_local = (m + 1 + (islands + 1 if islands > 1 else 0)) / 1.5 if owner else 0.0
-        reduce_remote = float(islands - 1) if owner and islands > 1 else 0.0
-        best, choice = None, (max(1, grid // 3), max(1, grid // 3))
-        for role_b in range(1, grid - 1):
-            for role_a in range(1, grid - role_b):
-                role_d = grid - role_a - role_b
-                worst = max(seconds(role_a, local, remote),
-                            seconds(role_b, reduce_local, reduce_remote),
-                            seconds(role_d, local, remote))
-                if best is None or worst < best:
-                    best, choice = worst, (role_a, role_b)
-        self._role_cache[grid] = choice
-        return choice
 
     def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:
         """Error feedback of this rank's stripes of ``tensor``: found by the buffer's address,
@@ -423,6 +397,11 @@ class Fabric:
         except Exception:  # noqa: BLE001 - teardown never raises
             pass
         short = timedelta(seconds=20)
+        if self.world == 1:
+            self.lib.gb_symm_free(self.ws[0])
+            self.lib.gb_symm_free(self.ctrl)
+            self.lib.gb_status_free(self.status)
+            return
         try:
             _exchange(self._store, self._key + "/closing", self.rank, self.world, "1", short)
             for r, ptr in enumerate(self.ws):
@@ -450,6 +429,22 @@ def _exchange(store, key: str, rank_index: int, world: int, value: str,
             if time.monotonic() >= deadline:
                 raise RuntimeError(f"gpubridge fabric setup: peers never reported ({key})") from None
     return [store.get(k).decode() for k in keys]
+
+
+def create_single(device: torch.device) -> Fabric:
+    """A team of one rank: no peers, no handles, the same kernels.  For single-GPU use of the
+    fused GEMM and for profiling one rank's side of the collectives."""
+    from gpubridge_b200.topology import plan_topology
+    lib = _lib.lib()
+    torch.cuda.set_device(device)
+    ws_bytes = _config.size_setting(_config.FABRIC_BYTES_ENV, DEFAULT_BYTES, multiple=4096)
+    local, ctrl, status = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+    _lib.check(lib.gb_symm_alloc(ws_bytes, ctypes.byref(local)), "cudaMalloc (fabric workspace)")
+    _lib.check(lib.gb_symm_alloc(max(4096, 8 * lib.gb_sizeof_ctrl()), ctypes.byref(ctrl)),
+               "cudaMalloc (control block)")
+    _lib.check(lib.gb_status_alloc(4 * _lib.STATUS_WORDS, ctypes.byref(status)), "cudaHostAlloc")
+    return Fabric(lib, plan_topology(["nvidia"]), 0, device, [local.value], ws_bytes, ctrl.value,
+                  status.value, _config.wait_timeout_ms(), None, "")
 
 
 def create(store, name: str, layout, rank: int, device: torch.device,
@@ -495,7 +490,7 @@ def create(store, name: str, layout, rank: int, device: torch.device,
                    f"cudaIpcOpenMemHandle (team rank {r})")
         ws.append(mapped.value)
     ctrl = ctypes.c_void_p()
-    _lib.check(lib.gb_symm_alloc(max(256, lib.gb_sizeof_ctrl()), ctypes.byref(ctrl)),
+    _lib.check(lib.gb_symm_alloc(max(4096, 8 * lib.gb_sizeof_ctrl()), ctypes.byref(ctrl)),
                "cudaMalloc (control block)")
     status = ctypes.c_void_p()
     _lib.check(lib.gb_status_alloc(4 * _lib.STATUS_WORDS, ctypes.byref(status)), "cudaHostAlloc")

@@ -1,0 +1,74 @@
+"""All-gather fused into a tcgen05 GEMM (``csrc/gb_gemm.cu``): ``y = x @ gather(w_shards).T``.
+
+The FSDP2 pattern "all-gather the sharded Linear weight, then run the Linear" as one
+persistent kernel: communication blocks bring the peers' shards over NVLink into a local
+gathered weight and raise a flag per shard; GEMM blocks (TMA -> shared memory ->
+``tcgen05.mma`` -> tensor memory -> epilogue) start on the local shard at once and take each
+remote shard as soon as its flag is up.  Replaces ``dist.all_gather_into_tensor`` +
+``F.linear`` (reference: src/gpubridge/torch_backend.py:271-285).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from gpubridge_b200.ops import _lib
+
+launches = 0
+
+
+class AllGatherLinear:
+    """State of one fused all-gather + GEMM site: the gathered weight, the shard flags and the
+    call counter.  ``fabric`` is the team's :class:`~gpubridge_b200.ops.fabric.Fabric` (one of a
+    single rank works too: then this is a plain tcgen05 GEMM)."""
+
+    def __init__(self, fabric, out_features: int, in_features: int, comm_blocks: int = 16) -> None:
+        if out_features % fabric.world:
+            raise ValueError("out_features must divide evenly over the team")
+        if in_features % 8:
+            raise ValueError("in_features must be a multiple of 8 (16-byte rows for TMA)")
+        self.fabric, self.N, self.K = fabric, out_features, in_features
+        device = fabric.device
+        self.gathered = torch.empty((out_features, in_features), dtype=torch.bfloat16, device=device)
+        self.flags = torch.zeros(fabric.world, dtype=torch.int32, device=device)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.comm_blocks = comm_blocks
+        self.gemm_blocks = max(1, sms - comm_blocks)
+        shard_bytes = out_features // fabric.world * in_features * 2
+        if fabric.world > 1 and shard_bytes > fabric.len_ag:
+            raise ValueError(f"a weight shard of {shard_bytes} bytes exceeds the fabric's staging "
+                             f"area ({fabric.len_ag}); raise GPUBRIDGE_FABRIC_BYTES")
+
+    def __call__(self, x: torch.Tensor, shard: torch.Tensor) -> torch.Tensor:
+        """``x``: [M, K] bf16; ``shard``: this rank's [N / world, K] rows.  Returns [M, N]."""
+        global launches
+        assert x.dtype == torch.bfloat16 and shard.dtype == torch.bfloat16
+        assert x.is_contiguous() and shard.is_contiguous() and x.shape[1] == self.K
+        assert shard.shape == (self.N // self.fabric.world, self.K)
+        fabric = self.fabric
+        y = torch.empty((x.shape[0], self.N), dtype=torch.bfloat16, device=x.device)
+        self.epoch += 1
+        current = fabric._begin()
+        try:
+            with torch.cuda.stream(fabric.comm_stream):
+                code = fabric.lib.gb_allgather_gemm(
+                    ctypes.byref(fabric.team), y.data_ptr(), x.data_ptr(), shard.data_ptr(),
+                    self.gathered.data_ptr(), self.flags.data_ptr(), self.error.data_ptr(),
+                    self.epoch, x.shape[0], self.N, self.K, fabric.off_ag, self.gemm_blocks,
+                    self.comm_blocks, torch.cuda.current_stream(x.device).cuda_stream)
+                if code == -3:
+                    raise RuntimeError("cuTensorMapEncodeTiled is unavailable or refused the shapes")
+                _lib.check(code, "gb_allgather_gemm")
+        finally:
+            fabric._end(current)
+        launches += 1
+        return y
+
+    def check(self) -> None:
+        """Raise if a wait inside the kernel ran out (reads one word from the device)."""
+        code = int(self.error.item())
+        if code:
+            raise RuntimeError(f"gb_allgather_gemm: a bounded wait ran out (code {code})")
