@@ -36,6 +36,10 @@ def _collectives(rank, topology, policy):
                 want = expected_sum(world, n, dtype)
             gb.all_reduce(t)
             assert torch.equal(t.cpu(), want), ("all_reduce", dtype, n)
+    n = (9 << 20) + 3                       # 36 MiB: the widest channel plan
+    t = rank_tensor(rank, n).to(dev)
+    gb.all_reduce(t)
+    assert torch.equal(t.cpu(), expected_sum(world, n)), ("all_reduce", "large", n)
     for n in (33, 100_003):
         t = rank_tensor(rank, n).to(dev)
         gb.all_reduce(t, gb.ReduceOp.AVG)
