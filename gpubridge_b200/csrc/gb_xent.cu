@@ -76,6 +76,38 @@ __device__ __forceinline__ void block_softmax_stats(float& m, float& s) {
     for (int w = 1; w < THREADS / 32; ++w) online_merge(m, s, sm[w], ss[w]);
 }
 
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+// 2^x by the special-function unit (about 2 ulp; results below 2^-126 flush to zero, which
+// is below what a sum of exponentials can resolve anyway).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Statistics are kept in the base-2 domain: t = logit * log2(e), m = running max of t,
+// s = sum of 2^(t - m).  One vector at a time: the vector's maximum decides whether the
+// running sum is rescaled (rare after the first few vectors), then each element costs one
+// fused multiply-add, one ex2 and one add.  Columns at or beyond `limit` do not count.
+template <int N>
+__device__ __forceinline__ void stats_vector(const float (&e)[N], size_t col0, size_t limit,
+                                             bool checked, float& m, float& s) {
+    float t[N];
+    float vm = -CUDART_INF_F;
+    #pragma unroll
+    for (int j = 0; j < N; ++j) {
+        t[j] = e[j] * LOG2E;
+        if (checked && col0 + j >= limit) t[j] = -CUDART_INF_F;
+        vm = fmaxf(vm, t[j]);
+    }
+    if (vm > m) { s *= fast_exp2(m - vm); m = vm; }       // m = -inf: s is 0 and 2^(-inf) is 0
+    if (m == -CUDART_INF_F) return;
+    #pragma unroll
+    for (int j = 0; j < N; ++j) s += fast_exp2(t[j] - m);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 xent_kernel(T* __restrict__ logits, const long long* __restrict__ targets, size_t rows,
@@ -83,22 +115,25 @@ xent_kernel(T* __restrict__ logits, const long long* __restrict__ targets, size_
             unsigned int* __restrict__ counter, float* __restrict__ loss_out) {
     constexpr int N = Pack<T>::N;
     const size_t nvec = ld / N;                       // ld is a multiple of N
+    const size_t nfull = vocab / N;                   // vectors that lie wholly inside the vocabulary
     for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
         T* x = logits + row * ld;
         const long long target = targets[row];
         float m = -CUDART_INF_F, s = 0.0f;
-        for (size_t v = threadIdx.x; v < nvec; v += THREADS) {
+        size_t v = threadIdx.x;
+        for (; v + THREADS < nfull; v += 2 * THREADS) {       // two vectors in flight per thread
+            float e0[N], e1[N];
+            Pack<T>::load(x + v * N, e0);
+            Pack<T>::load(x + (v + THREADS) * N, e1);
+            stats_vector<N>(e0, 0, 0, false, m, s);
+            stats_vector<N>(e1, 0, 0, false, m, s);
+        }
+        for (; v < nvec; v += THREADS) {
             float e[N];
             Pack<T>::load(x + v * N, e);
-            #pragma unroll
-            for (int j = 0; j < N; ++j) {
-                if (v * N + j < vocab) {
-                    const float val = e[j];
-                    if (val > m) { s = s * __expf(m - val) + 1.0f; m = val; }
-                    else s += __expf(val - m);
-                }
-            }
+            stats_vector<N>(e, v * N, vocab, v >= nfull, m, s);
         }
+        m *= LN2;                                     // natural units from here on
         block_softmax_stats(m, s);
         const bool counted = target >= 0 && (size_t)target < vocab;   // ignore_index style
         if (threadIdx.x == 0) {
@@ -106,20 +141,23 @@ xent_kernel(T* __restrict__ logits, const long long* __restrict__ targets, size_
             row_loss[row] = counted ? (__logf(s) + m - picked) : 0.0f;
         }
         __syncthreads();                              // x[target] is read before it is rewritten
-        const float inv = 1.0f / s;
-        for (size_t v = threadIdx.x; v < nvec; v += THREADS) {
+        const float coef = counted ? grad_scale / s : 0.0f;
+        const float m2 = m * LOG2E;
+        const size_t tvec = counted ? (size_t)target / N : (size_t)-1;
+        const int tlane = counted ? (int)((size_t)target % N) : 0;
+        for (v = threadIdx.x; v < nvec; v += THREADS) {
             float e[N];
             Pack<T>::load(x + v * N, e);
+            const bool tail = v >= nfull;
             #pragma unroll
             for (int j = 0; j < N; ++j) {
-                const size_t col = v * N + j;
-                float g = 0.0f;
-                if (col < vocab && counted) {
-                    g = __expf(e[j] - m) * inv;
-                    if ((long long)col == target) g -= 1.0f;
-                    g *= grad_scale;
-                }
+                float g = fast_exp2(fmaf(e[j], LOG2E, -m2)) * coef;
+                if (tail && v * N + j >= vocab) g = 0.0f;
                 e[j] = g;
+            }
+            if (v == tvec) {
+                #pragma unroll
+                for (int j = 0; j < N; ++j) if (j == tlane) e[j] -= grad_scale;
             }
             Pack<T>::store(x + v * N, e);
         }

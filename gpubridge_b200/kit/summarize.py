@@ -1,0 +1,108 @@
+"""Merge the per-rank journals of a kit run into ``summary.json`` and ``summary.md``.
+
+    python -m gpubridge_b200.kit.summarize [--partial] DIR [DIR ...]
+
+A directory of ``rank<N>.json`` journals gets a stage-by-rank table; exit code 1 if a rank is
+missing, a stage failed or a rank was left inside a stage.  Relabelled (split-test) runs are
+flagged at the top.  ``--partial``: this machine holds only some ranks of a multi-machine
+job; absent ranks are listed, not failed.  Same role as the reference's
+``scripts/gpu/summarize.py``.
+"""
+from __future__ import annotations
+
+import json
+import re
+import sys
+from pathlib import Path
+from typing import Any
+
+from gpubridge_b200.kit import write_json
+
+BANNER = ("> **SPLIT TEST - not a mixed-vendor result.** The islands are relabelled ranks of "
+          "a single-vendor job.")
+_MARK = {True: "ok", False: "FAIL", None: "-"}
+
+
+def load(directory: Path) -> dict[int, dict[str, Any]]:
+    journals = {}
+    for path in directory.glob("rank*.json"):
+        m = re.fullmatch(r"rank(\d+)\.json", path.name)
+        if m:
+            journals[int(m.group(1))] = json.loads(path.read_text())
+    return journals
+
+
+def summarize(directory: Path, partial: bool = False) -> tuple[dict[str, Any], str]:
+    journals = load(directory)
+    runs = [j["run"] for j in journals.values() if j.get("run")]
+    world = runs[0]["world_size"] if runs else None
+    missing = sorted(set(range(world)) - set(journals)) if world else []
+    split = next((r["split_test"] for r in runs if r.get("split_test")), None)
+    stage_names: list[str] = []
+    for j in journals.values():
+        for s in j["stages"]:
+            if s["name"] not in stage_names:
+                stage_names.append(s["name"])
+    problems: dict[str, str] = {}
+    for rank, j in sorted(journals.items()):
+        for s in j["stages"]:
+            where = f"rank {rank} / {s['name']}"
+            if s["ok"] is False:
+                problems[where] = s.get("error") or json.dumps(
+                    {k: v for k, v in s.items() if k not in ("name", "ok")}, default=str)
+            elif s["ok"] is None:
+                problems[where] = "the rank was left inside this stage"
+    table = {name: {rank: next((s["ok"] for s in j["stages"] if s["name"] == name), None)
+                    for rank, j in sorted(journals.items())} for name in stage_names}
+    ok = (bool(journals) and (partial or not missing) and not problems
+          and all(j.get("ok") for j in journals.values()))
+    first = journals[min(journals)] if journals else {}
+    summary = {
+        "directory": str(directory), "ok": ok, "run_kind": runs[0]["kind"] if runs else "unknown",
+        "policy": runs[0].get("policy") if runs else None, "split_test": split,
+        "fused": runs[0].get("fused") if runs else None,
+        "ranks_reported": sorted(journals), "ranks_missing": missing, "partial": partial,
+        "islands": runs[0]["islands"] if runs else None,
+        "environment": {k: first.get("environment", {}).get(k)
+                        for k in ("torch", "torch_cuda", "nccl", "gpubridge_b200")},
+        "stages": table, "errors": problems,
+    }
+    lines = [f"# {directory.name}: {'PASS' if ok else 'FAIL'}", ""]
+    if split:
+        lines += [BANNER, ""]
+    lines += [f"Run kind `{summary['run_kind']}`, policy `{summary['policy']}`, fused kernels "
+              f"`{summary['fused']}`, split test `{split or 'off'}`, "
+              f"{len(journals)}{f' of {world}' if world else ''} ranks reported.", ""]
+    if missing:
+        lines += [(f"Ranks {missing} ran on another machine (partial summary)." if partial else
+                   f"**Missing ranks:** {missing} (died before writing a journal?)"), ""]
+    lines += ["| stage | " + " | ".join(f"rank {r}" for r in sorted(journals)) + " |",
+              "|" + " --- |" * (len(journals) + 1)]
+    for name, row in table.items():
+        lines.append(f"| {name} | " + " | ".join(_MARK[v] for v in row.values()) + " |")
+    if problems:
+        lines += ["", "## Problems", ""]
+        for where, what in problems.items():
+            lines += [f"* **{where}**", "", "```", what.strip()[-2000:], "```", ""]
+    return summary, "\n".join(lines) + "\n"
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    partial = "--partial" in argv
+    dirs = [Path(a) for a in argv if a != "--partial"]
+    if not dirs:
+        print(__doc__, file=sys.stderr)
+        return 2
+    failed = False
+    for d in dirs:
+        summary, text = summarize(d, partial)
+        write_json(d / "summary.json", summary)
+        (d / "summary.md").write_text(text)
+        print(text)
+        failed = failed or not summary["ok"]
+    return 1 if failed else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,78 @@
+"""The validation kit on CPU ranks: the thirteen-stage check and its summary, the negative
+init test, the point-to-point checks through the torch backend, and redaction."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _torchrun(nproc, port, module, *args, env=None, timeout=300):
+    full = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1", **(env or {}))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+           f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1", "--master-port", str(port),
+           "-m", module, *args]
+    return subprocess.run(cmd, env=full, cwd=ROOT, capture_output=True, text=True,
+                          timeout=timeout)
+
+
+SIM = {"GPUBRIDGE_VENDOR": "nvidia", "GPUBRIDGE_SPLIT_TEST": "half"}
+
+
+def test_check_and_summary(tmp_path):
+    out = tmp_path / "check"
+    done = _torchrun(2, 29721, "gpubridge_b200.kit.check", "--out", str(out),
+                     "--in-flight-settle", "0.2", "--timeout", "120", env=SIM)
+    assert done.returncode == 0, done.stderr[-3000:]
+    from gpubridge_b200.kit import summarize
+    assert summarize.main([str(out)]) == 0
+    summary = json.loads((out / "summary.json").read_text())
+    assert summary["ok"] and summary["split_test"] == "half"
+    assert list(summary["stages"]) == [
+        "init", "device", "dtypes", "busy_gpu", "broadcast", "reductions", "all_gather",
+        "reduce_scatter", "async", "reduction_agreement", "in_flight", "barrier", "destroy"]
+    assert "SPLIT TEST" in (out / "summary.md").read_text()
+    # a missing rank fails the summary unless it is declared partial
+    (out / "rank1.json").unlink()
+    assert summarize.main([str(out)]) == 1
+    assert summarize.main(["--partial", str(out)]) == 0
+
+
+def test_expected_init_error(tmp_path):
+    out = tmp_path / "neg"
+    done = _torchrun(2, 29722, "gpubridge_b200.kit.check", "--out", str(out),
+                     "--expect-init-error", "No GPU is visible", "--timeout", "60",
+                     env={"GPUBRIDGE_VENDOR": ""})
+    assert done.returncode == 0, done.stderr[-3000:]
+    record = json.loads((out / "rank0.json").read_text())
+    assert record["ok"] and record["stages"][0]["name"] == "expected_init_error"
+    # the wrong pattern fails the run
+    done = _torchrun(2, 29723, "gpubridge_b200.kit.check", "--out", str(tmp_path / "neg2"),
+                     "--expect-init-error", "LOCAL_RANK", "--timeout", "60",
+                     env={"GPUBRIDGE_VENDOR": ""})
+    assert done.returncode != 0
+
+
+def test_p2p_only(tmp_path):
+    out = tmp_path / "p2p"
+    done = _torchrun(2, 29724, "gpubridge_b200.kit.check", "--out", str(out), "--p2p-only",
+                     "--timeout", "120", env=SIM)
+    assert done.returncode == 0, done.stderr[-3000:]
+    record = json.loads((out / "rank1.json").read_text())
+    cases = record["stages"][1]["cases"]
+    assert len(cases) == 30 and all(c["ok"] for c in cases)
+
+
+def test_redaction(monkeypatch, tmp_path):
+    from gpubridge_b200 import kit
+    monkeypatch.setenv("HOME", "/home/somebody")
+    text = kit.redact("see /home/somebody/run and https://me:secret@host/x")
+    assert "somebody" not in text and "secret" not in text and "~/run" in text
+    env = kit.recorded_env({"GPUBRIDGE_POLICY": "auto", "GPUBRIDGE_API_TOKEN": "x",
+                            "HOME": "/h", "NCCL_DEBUG": "INFO"})
+    assert env == {"GPUBRIDGE_POLICY": "auto", "NCCL_DEBUG": "INFO"}
+    kit.write_json(tmp_path / "a" / "b.json", {"p": "/home/somebody/x", "n": [1, {"q": (2,)}]})
+    assert json.loads((tmp_path / "a" / "b.json").read_text()) == {"p": "~/x", "n": [1, {"q": [2]}]}
