@@ -4,7 +4,10 @@ pipelined collectives and the device-side timeouts (the reference has a TCP band
 probe for its host bridge: scripts/gpu/preflight.py).
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
-        -m gpubridge_b200.bench.bench_link
+        -m gpubridge_b200.bench.bench_link [grids, e.g. 1,8,32,128]
+
+``ring-`` rows move the same bytes through the bulk-copy ring (TMA loads into shared memory,
+ordinary stores out of it) instead of loads into registers.
 """
 from __future__ import annotations
 
@@ -41,13 +44,15 @@ def main() -> int:
             topology.world_group.all_reduce(t, "max")
             return float(t)
 
-        for grid in (1, 8, 32, 64, 120):
+        grids = [int(g) for g in (sys.argv[1] if len(sys.argv) > 1 else "1,4,8,16,32,64,128").split(",")]
+        for grid in grids:
             base = timed("barrier", grid, 0, 1)                    # launch + two barriers
             ms = timed("barrier", grid, 200, 1)
             rows.append({"probe": "barrier", "grid": grid,
                          "us_per_barrier": round((ms - base) * 1000 / 200, 2),
                          "launch_plus_2_barriers_us": round(base * 1000, 1)})
-            for kind in ("store", "load", "copy", "mixed", "mixed3"):
+            for kind in ("store", "ring-store", "load", "ring-load", "copy", "ring-copy", "mixed",
+                         "mixed3"):
                 if kind.startswith("mixed") and grid < 8:
                     continue
                 repeat = 8

@@ -34,6 +34,7 @@
 // kernel, when every peer has left the previous collective.  Inside a pipelined kernel the
 // two buffers of a region alternate with the chunk index.
 #include "gb_codec.cuh"
+#include "gb_bulk.cuh"
 
 // Byte offsets are into a workspace; every offset and length is a multiple of 16.
 struct GbArgs {
@@ -530,6 +531,159 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
     }
 }
 
+// ---- hierarchical all-reduce through the bulk-copy ring -----------------------------------------
+// The same steps, buffers and summation order as allreduce_hier_kernel without compression;
+// every read (input stripes, island slots, island results, the owner's result) is a bulk copy
+// into shared memory issued ahead of its use, every write an ordinary store from there.
+
+// Step B: fold the island's slots in member order, round to T, store.
+template <typename T, int OP>
+__device__ __forceinline__ bool island_reduce_ring(GbRing& R, const GbTeam& tm, const GbArgs& a,
+                                                   int bi, int nb, const char* slots, size_t count,
+                                                   int buf) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = Vec<T>::N;
+    const int m = tm.island_off[tm.my_island + 1] - tm.island_off[tm.my_island];
+    const bool bridged = tm.n_islands > 1;
+    const size_t sbytes = a.stripe * sizeof(T);
+    return gb_ring_run(R, tm, bi, nb, slots, sbytes, m, count * sizeof(T), true,
+        [&](const unsigned char* stage, unsigned pitch, size_t off, unsigned len) {
+            const unsigned nv = len >> 4;
+            for (unsigned v = threadIdx.x; v < nv; v += THREADS) {
+                A part[V];
+                for (int p = 0; p < m; ++p) {
+                    Vec<T> w;
+                    w.u = *reinterpret_cast<const uint4*>(stage + (size_t)p * pitch + ((size_t)v << 4));
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        part[j] = (p == 0) ? gb_up<T>(w.e[j])
+                                           : GbFold<OP, A>::run(part[j], gb_up<T>(w.e[j]));
+                }
+                Vec<T> r;
+                #pragma unroll
+                for (int j = 0; j < V; ++j) r.e[j] = gb_down<T>(part[j]);
+                const size_t at = off + ((size_t)v << 4);
+                if (!bridged) {
+                    if (a.divide > 0) {
+                        #pragma unroll
+                        for (int j = 0; j < V; ++j)
+                            r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
+                    }
+                    gb_st16(tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c + at, r.u);
+                } else {
+                    for (int d = 0; d < tm.n_islands; ++d) {
+                        const int isl = (tm.my_island + d) % tm.n_islands;
+                        const int owner = tm.order[tm.island_off[isl] + tm.my_pos];
+                        gb_st16(tm.ws[owner] + a.off_b + (size_t)buf * a.len_b
+                                + (size_t)tm.my_island * sbytes + at, r.u);
+                    }
+                }
+            }
+        });
+}
+
+// Step C: add the island results in island order, AVG, one rounding, into region C.
+template <typename T, int OP>
+__device__ __forceinline__ bool bridge_reduce_ring(GbRing& R, const GbTeam& tm, const GbArgs& a,
+                                                   int bi, int nb, size_t count, int buf) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = Vec<T>::N;
+    const size_t sbytes = a.stripe * sizeof(T);
+    const char* parts = tm.ws[tm.rank] + a.off_b + (size_t)buf * a.len_b;
+    char* result = tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c;
+    const int groups = tm.n_islands;
+    return gb_ring_run(R, tm, bi, nb, parts, sbytes, groups, count * sizeof(T), true,
+        [&](const unsigned char* stage, unsigned pitch, size_t off, unsigned len) {
+            const unsigned nv = len >> 4;
+            for (unsigned v = threadIdx.x; v < nv; v += THREADS) {
+                A total[V];
+                for (int g = 0; g < groups; ++g) {
+                    Vec<T> w;
+                    w.u = *reinterpret_cast<const uint4*>(stage + (size_t)g * pitch + ((size_t)v << 4));
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        total[j] = (g == 0) ? gb_up<T>(w.e[j])
+                                            : GbFold<OP, A>::run(total[j], gb_up<T>(w.e[j]));
+                }
+                Vec<T> r;
+                #pragma unroll
+                for (int j = 0; j < V; ++j)
+                    r.e[j] = gb_down<T>(a.divide > 0 ? gb_divide<A>(total[j], a.divide) : total[j]);
+                gb_st16(result + off + ((size_t)v << 4), r.u);
+            }
+        });
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(THREADS)
+allreduce_ring_kernel(GbTeam tm, GbArgs a) {
+    GbRing R = gb_ring_init();
+    const T* in = static_cast<const T*>(a.in);
+    T* out = static_cast<T*>(a.out);
+    const bool owner = tm.my_pos < a.k;
+    const bool bridged = tm.n_islands > 1;
+    const size_t sbytes = a.stripe * sizeof(T);
+    const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    const int depth = bridged ? 3 : 2;
+    const int channels = a.role_a > 0 ? a.role_a : 1;
+    const int per = (int)gridDim.x / channels;
+    const int ch = (int)blockIdx.x / per;
+    if (ch >= channels) return;
+    const int bi = (int)blockIdx.x - ch * per;
+    const GbLane L = gb_lane_blocks(ch * per, per, tm.ld_mode);
+    const long mine = nchunks > ch ? (nchunks - ch + channels - 1) / channels : 0;
+    if (mine == 0) return;
+    const long iters = mine + depth;
+    GbArgs b = a;                                        // this channel's regions
+    b.off_a = a.off_a + (size_t)ch * 2 * a.len_a;
+    b.off_b = a.off_b + (size_t)ch * 2 * a.len_b;
+    b.off_c = a.off_c + (size_t)ch * 2 * a.len_c;
+    for (long i = 0; i < iters; ++i) {
+        if (i < mine) {                                  // A(i)
+            const size_t c0 = (size_t)(ch + i * channels) * a.chunk;
+            for (int dj = 0; dj < a.k; ++dj) {
+                const int j = (tm.my_pos + dj) % a.k;
+                const int own = tm.order[tm.island_off[tm.my_island] + j];
+                char* dst = tm.ws[own] + b.off_a + (size_t)(i & 1) * a.len_a
+                            + (size_t)tm.my_pos * sbytes;
+                const size_t valid = stripe_valid(a, c0, j);
+                if (valid && !gb_ring_copy(R, tm, L, bi, per, dst, in + c0 + (size_t)j * a.stripe,
+                                           valid * sizeof(T), false))
+                    return;
+                zero_range(L, dst, valid * sizeof(T), round_up(valid, 256) * sizeof(T));
+            }
+        }
+        if (owner && i >= 1 && i - 1 < mine) {           // B(i-1)
+            const long c = ch + (i - 1) * channels;
+            const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
+            const char* slots = tm.ws[tm.rank] + b.off_a + (size_t)((i - 1) & 1) * a.len_a;
+            if (!island_reduce_ring<T, OP>(R, tm, b, bi, per, slots, need, (int)((i - 1) & 1)))
+                return;
+        }
+        if (bridged && owner && i >= 2 && i - 2 < mine) {        // C(i-2)
+            const long c = ch + (i - 2) * channels;
+            const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
+            if (!bridge_reduce_ring<T, OP>(R, tm, b, bi, per, need, (int)((i - 2) & 1))) return;
+        }
+        if (i >= depth) {                                // D(i-depth)
+            const long c = ch + (i - depth) * channels;
+            const size_t c0 = (size_t)c * a.chunk;
+            for (int dj = 0; dj < a.k; ++dj) {
+                const int j = (tm.my_pos + dj) % a.k;
+                const int own = tm.order[tm.island_off[tm.my_island] + j];
+                const size_t valid = stripe_valid(a, c0, j);
+                if (valid && !gb_ring_copy(R, tm, L, bi, per, out + c0 + (size_t)j * a.stripe,
+                                           tm.ws[own] + b.off_c + (size_t)((i - depth) & 1) * a.len_c,
+                                           valid * sizeof(T), true))
+                    return;
+            }
+        }
+        if (i + 1 < iters &&
+            !gb_sync(tm, ch, (unsigned)per, (unsigned)(i < 7 ? i : 7), i == 0 && ch == 0))
+            return;
+    }
+}
+
 // ---- all-gather ---------------------------------------------------------------------------------
 // Region A: [2 parities][2 chunk buffers] of len_a bytes.  n and chunk are bytes.
 __global__ void __launch_bounds__(THREADS)
@@ -651,6 +805,7 @@ barrier_kernel(GbTeam tm) {
 //   k = 3  n barriers and nothing else
 //   k = 4  the first half of the blocks store while the second half load (mixed traffic)
 //   k = 5  like 4 plus a third group that copies locally
+//   k = 6, 7, 8  like 0, 1, 2 but through the bulk-copy ring
 // Each pass is repeated `divide` times inside the launch; one barrier at the start and the end.
 __global__ void __launch_bounds__(THREADS)
 probe_kernel(GbTeam tm, GbArgs a) {
@@ -681,6 +836,24 @@ probe_kernel(GbTeam tm, GbArgs a) {
         gb_sync_all(tm, 2, false);
         return;
     }
+    if (a.k >= 6) {
+        GbRing R = gb_ring_init();
+        for (int rep = 0; rep < a.divide; ++rep) {
+            bool ok;
+            if (a.k == 6)
+                ok = gb_ring_copy(R, tm, L, (int)blockIdx.x, (int)gridDim.x, tm.ws[next] + a.off_a,
+                                  tm.ws[tm.rank] + a.off_b, a.n, false);
+            else if (a.k == 7)
+                ok = gb_ring_copy(R, tm, L, (int)blockIdx.x, (int)gridDim.x, tm.ws[tm.rank] + a.off_a,
+                                  tm.ws[next] + a.off_b, a.n, true);
+            else
+                ok = gb_ring_copy(R, tm, L, (int)blockIdx.x, (int)gridDim.x, tm.ws[tm.rank] + a.off_a,
+                                  tm.ws[tm.rank] + a.off_b, a.n, false);
+            if (!ok) return;
+        }
+        gb_sync_all(tm, 2, false);
+        return;
+    }
     for (int rep = 0; rep < a.divide; ++rep) {
         if (a.k == 0)
             gb_copy_bytes(L, tm.ws[next] + a.off_a, tm.ws[tm.rank] + a.off_b, a.n, false);
@@ -698,6 +871,13 @@ cudaError_t launch_plain(int kind, const GbTeam& tm, const GbArgs& a, int grid, 
     if (kind == 0) allreduce_oneshot_kernel<T, OP><<<grid, THREADS, 0, s>>>(tm, a);
     else if (kind == 1) allreduce_hier_kernel<T, OP, GB_RAW><<<grid, THREADS, 0, s>>>(tm, a);
     else if (kind == 2) reduce_scatter_kernel<T, OP><<<grid, THREADS, 0, s>>>(tm, a);
+    else if (kind == 3) {
+        // the ring needs more dynamic shared memory than the default limit: opt in once
+        static cudaError_t opted = cudaFuncSetAttribute(
+            allreduce_ring_kernel<T, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, GB_RING_SMEM);
+        if (opted != cudaSuccess) return opted;
+        allreduce_ring_kernel<T, OP><<<grid, THREADS, GB_RING_SMEM, s>>>(tm, a);
+    }
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }
@@ -725,7 +905,8 @@ cudaError_t launch_coded(int codec, const GbTeam& tm, const GbArgs& a, int grid,
 
 }  // namespace
 
-// kind: 0 one-shot all-reduce, 1 hierarchical all-reduce, 2 reduce-scatter.
+// kind: 0 one-shot all-reduce, 1 hierarchical all-reduce, 2 reduce-scatter,
+//       3 hierarchical all-reduce through the bulk-copy ring (no codec).
 // codec (kind 1, SUM, floating point only): GbCodec.  Returns a cudaError_t.
 extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const GbTeam* team,
                                 const GbArgs* args, int grid, cudaStream_t stream) {
@@ -760,7 +941,12 @@ extern "C" int gb_launch_copy(int kind, const GbTeam* team, const GbArgs* args, 
     if (kind == 0) allgather_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
     else if (kind == 1) broadcast_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
     else if (kind == 2) barrier_kernel<<<1, THREADS, 0, stream>>>(*team);
-    else if (kind == 3) probe_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
+    else if (kind == 3) {
+        static cudaError_t opted = cudaFuncSetAttribute(
+            probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GB_RING_SMEM);
+        if (opted != cudaSuccess) return opted;
+        probe_kernel<<<grid, THREADS, args->k >= 6 ? GB_RING_SMEM : 0, stream>>>(*team, *args);
+    }
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }

@@ -8,8 +8,6 @@ hierarchical reduction, the optional compressed bridge leg and the division by t
 size happen in the same launch, and the returned future is stream-ordered, so the host
 thread driving backward never blocks.
 """
-from __future__ import annotations
-
 import torch
 import torch.distributed as dist
 from torch.distributed import ReduceOp
@@ -17,7 +15,8 @@ from torch.distributed import ReduceOp
 from gpubridge_b200.collectives import all_reduce
 
 
-def ddp_comm_hook(state: object, bucket: "dist.GradBucket") -> "torch.futures.Future[torch.Tensor]":
+# The annotations are real objects, not strings: DDP checks them when the hook is registered.
+def ddp_comm_hook(state: object, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """Average one gradient bucket over every rank; ``state`` may be a Topology (a
     subgroup's) or None for the initialised world."""
     from gpubridge_b200.topology import Topology

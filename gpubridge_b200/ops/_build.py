@@ -88,5 +88,11 @@ def build(verbose: bool = False, force: bool = False) -> str:
     return LIB
 
 
-if __name__ == "__main__":
+def main() -> int:
+    """``python -m gpubridge_b200.ops._build [-v] [--force]``: build and print the path."""
     print(build(verbose="-v" in sys.argv, force="--force" in sys.argv))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -78,6 +78,8 @@ class Fabric:
         # tuning overrides (benchmarks): fixed pipeline depth and role split
         self.force_chunks = int(os.environ.get("GPUBRIDGE_HIER_CHUNKS", "0")) or None
         self.force_channels = int(os.environ.get("GPUBRIDGE_HIER_CHANNELS", "0")) or None
+        # reads through the bulk-copy ring (TMA into shared memory) instead of register loads
+        self.ring = os.environ.get("GPUBRIDGE_RING", "1") != "0"
         self.launches = 0            # kernels launched by this team (benchmarks report it)
 
         islands = layout.islands
@@ -250,13 +252,19 @@ class Fabric:
         channels = self.force_channels or (1 if nbytes < (4 << 20) else 2 if nbytes < (32 << 20) else 4)
         channels = max(1, min(channels, grid // 8 or 1, 8))
         grid = grid // channels * channels
-        stripe_cap = _align_down(self.stripe_bytes // channels // esize, 256)
+        # every channel owns two buffers of each region; a stripe must fit the smallest slot
+        len_a = self.len_ha // channels // 4096 * 4096
+        len_b = self.len_hb // channels // 4096 * 4096
+        len_c = self.len_hc // channels // 4096 * 4096
+        slot = min(len_a // self.m_max, len_b // self.n_islands, len_c)
+        stripe_cap = _align_down(slot // esize, 256)
         if chunk_bytes:
             want = max(256, chunk_bytes // esize // k)
         else:
             # per channel: T(c) = (c + depth) * (barrier + link time / c) is least at
             # c = sqrt(depth * link time / barrier)
-            m = len(self.layout.islands[self.team.my_island].ranks)
+            # (the plan must come out the same on every rank: use the largest island)
+            m = self.m_max
             share = max((m - 1) / m, (self.n_islands - 1) / k if self.n_islands > 1 else 0.0)
             depth = 3 if self.n_islands > 1 else 2
             link_s = nbytes / channels * share / LINK_GBS
@@ -264,17 +272,18 @@ class Fabric:
             want = -(-n // (chunks * channels * k))
         stripe = min(stripe_cap, _align_up(max(1, min(want, -(-n // k))), 256))
         args.stripe, args.k, args.chunk = stripe, k, stripe * k
-        # every channel owns two buffers of each region
-        args.off_a, args.len_a = self.off_ha, self.len_ha // channels // 4096 * 4096
-        args.off_b, args.len_b = self.off_hb, self.len_hb // channels // 4096 * 4096
-        args.off_c, args.len_c = self.off_hc, self.len_hc // channels // 4096 * 4096
+        args.off_a, args.len_a = self.off_ha, len_a
+        args.off_b, args.len_b = self.off_hb, len_b
+        args.off_c, args.len_c = self.off_hc, len_c
         args.role_a = channels
         codec = 0
         nchunks = -(-n // (stripe * k))
         if compression is not None:
             codec = _lib.CODECS[tuple(compression)]
             args.residual = self._residual(tensor, (stripe, k, nchunks, codec)).data_ptr()
-        self._launch_reduce(1, tensor.dtype, op, codec, args, grid)
+        aligned = (args.inp | args.out) % 16 == 0
+        kind = 3 if (self.ring and codec == 0 and aligned) else 1
+        self._launch_reduce(kind, tensor.dtype, op, codec, args, grid)
 
     def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:
         """Error feedback of this rank's stripes of ``tensor``: found by the buffer's address,
@@ -366,10 +375,12 @@ class Fabric:
 
     def probe(self, kind: str, nbytes: int = 0, grid: int = 64, repeat: int = 1) -> None:
         """Enqueue the link probe: ``store`` / ``load`` (to / from the next rank), ``copy``
-        (local), or ``barrier`` (``nbytes`` barriers).  Time it with events on the
+        (local), their ``ring-`` forms (through the bulk-copy ring), or ``barrier`` (``nbytes``
+        barriers).  Time it with events on the
         communication stream."""
         args = _lib.GbArgs()
-        args.k = {"store": 0, "load": 1, "copy": 2, "barrier": 3, "mixed": 4, "mixed3": 5}[kind]
+        args.k = {"store": 0, "load": 1, "copy": 2, "barrier": 3, "mixed": 4, "mixed3": 5,
+                  "ring-store": 6, "ring-load": 7, "ring-copy": 8}[kind]
         args.n = nbytes if kind == "barrier" else min(nbytes, self.len_ha, self.len_hb,
                                                       self.len_hc)
         args.divide = repeat

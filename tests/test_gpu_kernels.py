@@ -69,3 +69,37 @@ def test_trainer_step_eager_and_graph_agree():
 def test_smoke_entry_point():
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+@pytest.mark.parametrize("ring", [True, False], ids=["ring", "registers"])
+def test_single_rank_all_reduce_paths(ring):
+    """A team of one runs every step of the hierarchical all-reduce against local memory:
+    the result must be the input (SUM), the input / 3 (a stand-in divisor) and must not depend
+    on whether reads go through the bulk-copy ring or through registers."""
+    from gpubridge_b200.ops import fabric as F
+    device = torch.device("cuda", 0)
+    team = F.create_single(device)
+    team.ring = ring
+    try:
+        for dtype in (torch.float32, torch.bfloat16, torch.float64, torch.int32, torch.uint8):
+            for n in (1, 17, 4099, 65536 + 3, (1 << 20) + 5, (9 << 20) + 3):
+                x = (torch.arange(n, device=device) % 13).to(dtype)
+                y = x.clone()
+                team.all_reduce(y, "sum", None, "striped")
+                torch.cuda.synchronize()
+                assert torch.equal(y, x), (dtype, n)
+        x = (torch.arange((3 << 20) + 7, device=device) % 97).float()
+        y = x.clone()
+        team.all_reduce(y, "sum", 3, "striped")
+        assert torch.equal(y, x / 3)
+        # a view that is not 16-byte aligned falls back to register copies
+        z = x[1:4099 + 1].clone()
+        base = torch.zeros(4099 + 8, device=device)
+        view = base[1:1 + 4099]
+        view.copy_(z)
+        team.all_reduce(view, "sum", None, "striped")
+        assert torch.equal(view, z)
+        torch.cuda.synchronize()
+        team.check()
+    finally:
+        team.close()

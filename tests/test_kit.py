@@ -76,3 +76,23 @@ def test_redaction(monkeypatch, tmp_path):
     assert env == {"GPUBRIDGE_POLICY": "auto", "NCCL_DEBUG": "INFO"}
     kit.write_json(tmp_path / "a" / "b.json", {"p": "/home/somebody/x", "n": [1, {"q": (2,)}]})
     assert json.loads((tmp_path / "a" / "b.json").read_text()) == {"p": "~/x", "n": [1, {"q": [2]}]}
+
+
+def test_numerical_gate_software_only(tmp_path):
+    """The bridged arm passes its positive runs and every negative control fails."""
+    out = tmp_path / "gate"
+    done = _torchrun(4, 29725, "gpubridge_b200.kit.numerical_gate", "--software-only",
+                     "--out", str(out), "--timeout", "120")
+    assert done.returncode == 0, done.stderr[-3000:]
+    result = json.loads((out / "gate.json").read_text())
+    assert result["passed"] and "bridged/sgd/sum" in result["runs"]
+    from gpubridge_b200.kit import numerical_gate as gate
+    records = []
+    for r in range(4):
+        records += json.loads((out / f"gate-bridged-rank{r}.json").read_text())
+    # a control that passes, or a positive run that fails, flips the verdict
+    broken = [dict(r, passed=True) if r["control"] == "scale" else r for r in records]
+    assert not gate.verdict(broken)["passed"]
+    broken = [dict(r, passed=False) if r["control"] == "none" and r["rank"] == 2 else r
+              for r in records]
+    assert not gate.verdict(broken)["passed"]
