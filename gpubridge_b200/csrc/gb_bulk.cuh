@@ -190,3 +190,108 @@ __device__ __forceinline__ bool gb_ring_copy(GbRing& R, const GbTeam& tm, const 
     if (body < nbytes) gb_copy_bytes(L, d + body, s + body, nbytes - body, after_peer_writes);
     return true;
 }
+
+// ---- several transfers through one pipeline -----------------------------------------------------
+// The steps a pipelined collective runs between two barriers are independent of each other, so
+// their tiles are queued back to back: the ring stays full across step boundaries instead of
+// draining and refilling (a refill costs one memory latency per step and block).
+struct GbJob {
+    const char* src;        // source p of the job starts at src + p * src_stride
+    size_t src_stride;
+    size_t bytes;           // per source; a multiple of 16
+    char* dst;              // kind-specific (copy: destination of byte 0)
+    int m;                  // sources
+    int kind;               // meaning is the caller's
+    int arg;                // kind-specific
+    unsigned tile;          // derived by gb_jobs_plan
+    unsigned first;         // block that takes tile 0
+    size_t ntiles;
+};
+
+#define GB_MAX_JOBS (2 * GB_MAX_RANKS + 2)
+
+// Tile sizes and a round-robin assignment that continues from job to job.
+__device__ __forceinline__ void gb_jobs_plan(GbJob* jobs, int njobs, int nb) {
+    size_t total = 0;
+    for (int j = 0; j < njobs; ++j) total += jobs[j].bytes * (size_t)jobs[j].m;
+    size_t seen = 0;
+    for (int j = 0; j < njobs; ++j) {
+        GbJob& job = jobs[j];
+        // size tiles as if the whole queue were one transfer, so small jobs do not get
+        // needlessly small tiles and large queues use whole stages
+        unsigned cap = (GB_RING_STAGE_BYTES / (unsigned)job.m) & ~1023u;
+        size_t even = (total / (size_t)job.m / (size_t)nb + 1023u) & ~(size_t)1023u;
+        if (even < 4096u) even = 4096u;
+        job.tile = even < cap ? (unsigned)even : cap;
+        job.ntiles = (job.bytes + job.tile - 1) / job.tile;
+        job.first = (unsigned)(seen % (size_t)nb);
+        seen += job.ntiles;
+    }
+}
+
+struct GbCursor { int j; size_t t; };
+
+__device__ __forceinline__ void gb_cursor_settle(GbCursor& c, const GbJob* jobs, int njobs, int bi,
+                                                 int nb) {
+    while (c.j < njobs && c.t >= jobs[c.j].ntiles) {
+        ++c.j;
+        if (c.j < njobs) c.t = (size_t)((bi - (int)jobs[c.j].first + nb) % nb);
+    }
+}
+
+// Run the queue.  `jobs` lives in shared memory and was planned by gb_jobs_plan.  For every
+// tile all threads call consume(job, stage_base, pitch, offset, len).
+template <typename F>
+__device__ __forceinline__ bool gb_ring_run_jobs(GbRing& R, const GbTeam& tm, int bi, int nb,
+                                                 const GbJob* jobs, int njobs, F&& consume) {
+    if (njobs == 0) return true;
+    const bool issuer = threadIdx.x == 0;
+    GbCursor cc;
+    cc.j = 0;
+    cc.t = (size_t)((bi - (int)jobs[0].first + nb) % nb);
+    gb_cursor_settle(cc, jobs, njobs, bi, nb);
+    GbCursor ic = cc;
+    unsigned issued = R.uses, use = R.uses;
+    auto issue_one = [&]() {
+        const GbJob& job = jobs[ic.j];
+        const size_t off = ic.t * job.tile;
+        const unsigned len = (unsigned)(job.bytes - off < job.tile ? job.bytes - off : job.tile);
+        gb_ring_issue(R, issued, job.src, job.src_stride, job.m, off, len, job.tile);
+        ++issued;
+        ic.t += (size_t)nb;
+        gb_cursor_settle(ic, jobs, njobs, bi, nb);
+    };
+    if (issuer) {
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        for (int a = 0; a < GB_RING_STAGES - 1 && ic.j < njobs; ++a) issue_one();
+    }
+    bool failed = false;
+    while (cc.j < njobs) {
+        if (issuer && ic.j < njobs) issue_one();
+        const GbJob& job = jobs[cc.j];
+        const size_t off = cc.t * job.tile;
+        const unsigned len = (unsigned)(job.bytes - off < job.tile ? job.bytes - off : job.tile);
+        const unsigned stage = use % GB_RING_STAGES;
+        if (!gb_mbar_wait(&R.full[stage], (use / GB_RING_STAGES) & 1u, tm.timeout_ns))
+            *R.fail = 1u;
+        else
+            consume(job, R.buf + (size_t)stage * GB_RING_STAGE_BYTES, job.tile, off, len);
+        __syncthreads();
+        if (*R.fail) { failed = true; break; }
+        ++use;
+        cc.t += (size_t)nb;
+        gb_cursor_settle(cc, jobs, njobs, bi, nb);
+    }
+    if (failed) {
+        if (issuer) {
+            gb_fail(tm, GB_TIMEOUT_COPY, (unsigned)tm.rank, use, 1u);
+            for (unsigned u = use; u != issued; ++u)      // copies still in flight
+                gb_mbar_wait(&R.full[u % GB_RING_STAGES], (u / GB_RING_STAGES) & 1u,
+                             tm.timeout_ns / 4u + 1u);
+        }
+        __syncthreads();
+        return false;
+    }
+    R.uses = use;
+    return true;
+}

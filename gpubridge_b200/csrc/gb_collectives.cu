@@ -536,6 +536,213 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
 // every read (input stripes, island slots, island results, the owner's result) is a bulk copy
 // into shared memory issued ahead of its use, every write an ordinary store from there.
 
+// One tile of step B: fold the island's slots in member order, round to T, store.
+template <typename T, int OP>
+__device__ __forceinline__ void island_reduce_tile(const GbTeam& tm, const GbArgs& a, int buf,
+                                                   const unsigned char* stage, unsigned pitch,
+                                                   size_t off, unsigned len) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = Vec<T>::N;
+    const int m = tm.island_off[tm.my_island + 1] - tm.island_off[tm.my_island];
+    const bool bridged = tm.n_islands > 1;
+    const size_t sbytes = a.stripe * sizeof(T);
+    const unsigned nv = len >> 4;
+    for (unsigned v = threadIdx.x; v < nv; v += THREADS) {
+        A part[V];
+        for (int p = 0; p < m; ++p) {
+            Vec<T> w;
+            w.u = *reinterpret_cast<const uint4*>(stage + (size_t)p * pitch + ((size_t)v << 4));
+            #pragma unroll
+            for (int j = 0; j < V; ++j)
+                part[j] = (p == 0) ? gb_up<T>(w.e[j]) : GbFold<OP, A>::run(part[j], gb_up<T>(w.e[j]));
+        }
+        Vec<T> r;
+        #pragma unroll
+        for (int j = 0; j < V; ++j) r.e[j] = gb_down<T>(part[j]);
+        const size_t at = off + ((size_t)v << 4);
+        if (!bridged) {
+            if (a.divide > 0) {
+                #pragma unroll
+                for (int j = 0; j < V; ++j)
+                    r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
+            }
+            gb_st16(tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c + at, r.u);
+        } else {
+            for (int d = 0; d < tm.n_islands; ++d) {
+                const int isl = (tm.my_island + d) % tm.n_islands;
+                const int owner = tm.order[tm.island_off[isl] + tm.my_pos];
+                gb_st16(tm.ws[owner] + a.off_b + (size_t)buf * a.len_b
+                        + (size_t)tm.my_island * sbytes + at, r.u);
+            }
+        }
+    }
+}
+
+// One tile of step C: add the island results in island order, AVG, one rounding, into region C.
+template <typename T, int OP>
+__device__ __forceinline__ void bridge_reduce_tile(const GbTeam& tm, const GbArgs& a, int buf,
+                                                   const unsigned char* stage, unsigned pitch,
+                                                   size_t off, unsigned len) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = Vec<T>::N;
+    char* result = tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c;
+    const int groups = tm.n_islands;
+    const unsigned nv = len >> 4;
+    for (unsigned v = threadIdx.x; v < nv; v += THREADS) {
+        A total[V];
+        for (int g = 0; g < groups; ++g) {
+            Vec<T> w;
+            w.u = *reinterpret_cast<const uint4*>(stage + (size_t)g * pitch + ((size_t)v << 4));
+            #pragma unroll
+            for (int j = 0; j < V; ++j)
+                total[j] = (g == 0) ? gb_up<T>(w.e[j]) : GbFold<OP, A>::run(total[j], gb_up<T>(w.e[j]));
+        }
+        Vec<T> r;
+        #pragma unroll
+        for (int j = 0; j < V; ++j)
+            r.e[j] = gb_down<T>(a.divide > 0 ? gb_divide<A>(total[j], a.divide) : total[j]);
+        gb_st16(result + off + ((size_t)v << 4), r.u);
+    }
+}
+
+__device__ __forceinline__ void copy_tile(char* dst, const unsigned char* stage, size_t off,
+                                          unsigned len) {
+    const unsigned nv = len >> 4;
+    char* out = dst + off;
+    for (unsigned v = threadIdx.x; v < nv; v += THREADS)
+        gb_st16(out + ((size_t)v << 4), *reinterpret_cast<const uint4*>(stage + ((size_t)v << 4)));
+}
+
+enum { JOB_COPY = 0, JOB_ISLAND = 1, JOB_BRIDGE = 2 };
+
+__device__ __forceinline__ void job_set(GbJob& job, int kind, const char* src, size_t stride, int m,
+                                        size_t bytes, char* dst, int arg) {
+    job.kind = kind; job.src = src; job.src_stride = stride; job.m = m; job.bytes = bytes;
+    job.dst = dst; job.arg = arg;
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(THREADS)
+allreduce_ring_kernel(GbTeam tm, GbArgs a) {
+    __shared__ GbJob jobs[GB_MAX_JOBS];
+    __shared__ int njobs;
+    GbRing R = gb_ring_init();
+    const T* in = static_cast<const T*>(a.in);
+    T* out = static_cast<T*>(a.out);
+    const bool owner = tm.my_pos < a.k;
+    const bool bridged = tm.n_islands > 1;
+    const size_t sbytes = a.stripe * sizeof(T);
+    const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
+    const int depth = bridged ? 3 : 2;
+    const int channels = a.role_a > 0 ? a.role_a : 1;
+    const int per = (int)gridDim.x / channels;
+    const int ch = (int)blockIdx.x / per;
+    if (ch >= channels) return;
+    const int bi = (int)blockIdx.x - ch * per;
+    const GbLane L = gb_lane_blocks(ch * per, per, tm.ld_mode);
+    const long mine = nchunks > ch ? (nchunks - ch + channels - 1) / channels : 0;
+    if (mine == 0) return;
+    const long iters = mine + depth;
+    const int members = tm.island_off[tm.my_island + 1] - tm.island_off[tm.my_island];
+    GbArgs b = a;                                        // this channel's regions
+    b.off_a = a.off_a + (size_t)ch * 2 * a.len_a;
+    b.off_b = a.off_b + (size_t)ch * 2 * a.len_b;
+    b.off_c = a.off_c + (size_t)ch * 2 * a.len_c;
+    for (long i = 0; i < iters; ++i) {
+        const bool do_a = i < mine;
+        const bool do_b = owner && i >= 1 && i - 1 < mine;
+        const bool do_c = bridged && owner && i >= 2 && i - 2 < mine;
+        const bool do_d = i >= depth;
+        const size_t a0 = (size_t)(ch + i * channels) * a.chunk;          // chunk of step A
+        const size_t d0 = (size_t)(ch + (i - depth) * channels) * a.chunk; // chunk of step D
+        __syncthreads();                                 // the last queue is no longer read
+        if (threadIdx.x == 0) {
+            int n = 0;
+            if (do_d) {
+                for (int dj = 0; dj < a.k; ++dj) {
+                    const int j = (tm.my_pos + dj) % a.k;
+                    const int own = tm.order[tm.island_off[tm.my_island] + j];
+                    const size_t body = (stripe_valid(a, d0, j) * sizeof(T)) & ~(size_t)15;
+                    if (body)
+                        job_set(jobs[n++], JOB_COPY,
+                                tm.ws[own] + b.off_c + (size_t)((i - depth) & 1) * a.len_c, 0, 1, body,
+                                reinterpret_cast<char*>(out + d0 + (size_t)j * a.stripe), 0);
+                }
+            }
+            if (do_c) {
+                const long c = ch + (i - 2) * channels;
+                const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
+                if (need)
+                    job_set(jobs[n++], JOB_BRIDGE,
+                            tm.ws[tm.rank] + b.off_b + (size_t)((i - 2) & 1) * a.len_b, sbytes,
+                            tm.n_islands, need * sizeof(T), nullptr, (int)((i - 2) & 1));
+            }
+            if (do_b) {
+                const long c = ch + (i - 1) * channels;
+                const size_t need = round_up(stripe_valid(a, (size_t)c * a.chunk, tm.my_pos), 256);
+                if (need)
+                    job_set(jobs[n++], JOB_ISLAND,
+                            tm.ws[tm.rank] + b.off_a + (size_t)((i - 1) & 1) * a.len_a, sbytes,
+                            members, need * sizeof(T), nullptr, (int)((i - 1) & 1));
+            }
+            if (do_a) {
+                for (int dj = 0; dj < a.k; ++dj) {
+                    const int j = (tm.my_pos + dj) % a.k;
+                    const int own = tm.order[tm.island_off[tm.my_island] + j];
+                    const size_t body = (stripe_valid(a, a0, j) * sizeof(T)) & ~(size_t)15;
+                    if (body)
+                        job_set(jobs[n++], JOB_COPY,
+                                reinterpret_cast<const char*>(in + a0 + (size_t)j * a.stripe), 0, 1,
+                                body, tm.ws[own] + b.off_a + (size_t)(i & 1) * a.len_a
+                                      + (size_t)tm.my_pos * sbytes, 0);
+                }
+            }
+            gb_jobs_plan(jobs, n, per);
+            njobs = n;
+        }
+        __syncthreads();
+        // what the copy engine cannot take: ends shorter than 16 bytes, and the zero padding
+        // up to the next quantisation block (padding reduces only with padding)
+        if (do_a) {
+            for (int j = 0; j < a.k; ++j) {
+                const int own = tm.order[tm.island_off[tm.my_island] + j];
+                char* dst = tm.ws[own] + b.off_a + (size_t)(i & 1) * a.len_a
+                            + (size_t)tm.my_pos * sbytes;
+                const size_t vb = stripe_valid(a, a0, j) * sizeof(T);
+                const size_t body = vb & ~(size_t)15;
+                if (vb > body)
+                    gb_copy_bytes(L, dst + body,
+                                  reinterpret_cast<const char*>(in + a0 + (size_t)j * a.stripe) + body,
+                                  vb - body, false);
+                zero_range(L, dst, vb, round_up(vb / sizeof(T), 256) * sizeof(T));
+            }
+        }
+        if (do_d) {
+            for (int j = 0; j < a.k; ++j) {
+                const int own = tm.order[tm.island_off[tm.my_island] + j];
+                const size_t vb = stripe_valid(a, d0, j) * sizeof(T);
+                const size_t body = vb & ~(size_t)15;
+                if (vb > body)
+                    gb_copy_bytes(L, reinterpret_cast<char*>(out + d0 + (size_t)j * a.stripe) + body,
+                                  tm.ws[own] + b.off_c + (size_t)((i - depth) & 1) * a.len_c + body,
+                                  vb - body, true);
+            }
+        }
+        const bool ok = gb_ring_run_jobs(R, tm, bi, per, jobs, njobs,
+            [&](const GbJob& job, const unsigned char* stage, unsigned pitch, size_t off, unsigned len) {
+                if (job.kind == JOB_COPY) copy_tile(job.dst, stage, off, len);
+                else if (job.kind == JOB_ISLAND)
+                    island_reduce_tile<T, OP>(tm, b, job.arg, stage, pitch, off, len);
+                else bridge_reduce_tile<T, OP>(tm, b, job.arg, stage, pitch, off, len);
+            });
+        if (!ok) return;
+        if (i + 1 < iters &&
+            !gb_sync(tm, ch, (unsigned)per, (unsigned)(i < 7 ? i : 7), i == 0 && ch == 0))
+            return;
+    }
+}
+
+// ---- the same kernel with one ring run per step (kept for A/B measurements) ---------------------
 // Step B: fold the island's slots in member order, round to T, store.
 template <typename T, int OP>
 __device__ __forceinline__ bool island_reduce_ring(GbRing& R, const GbTeam& tm, const GbArgs& a,
@@ -616,7 +823,7 @@ __device__ __forceinline__ bool bridge_reduce_ring(GbRing& R, const GbTeam& tm, 
 
 template <typename T, int OP>
 __global__ void __launch_bounds__(THREADS)
-allreduce_ring_kernel(GbTeam tm, GbArgs a) {
+allreduce_ring_phased_kernel(GbTeam tm, GbArgs a) {
     GbRing R = gb_ring_init();
     const T* in = static_cast<const T*>(a.in);
     T* out = static_cast<T*>(a.out);
@@ -688,17 +895,21 @@ allreduce_ring_kernel(GbTeam tm, GbArgs a) {
 // Region A: [2 parities][2 chunk buffers] of len_a bytes.  n and chunk are bytes.
 __global__ void __launch_bounds__(THREADS)
 allgather_kernel(GbTeam tm, GbArgs a) {
+    GbRing R = gb_ring_init();
     const unsigned parity = gb_ld_volatile(&tm.ctrl->epoch) & 1u;
     const char* in = static_cast<const char*>(a.in);
     char* out = static_cast<char*>(a.out);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
     const GbLane L = gb_lane_all(tm.ld_mode);
+    const int bi = (int)blockIdx.x, nb = (int)gridDim.x;
     for (long t = 0; t <= nchunks; ++t) {
         if (t < nchunks) {
             const size_t c0 = (size_t)t * a.chunk;
             const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
-            gb_copy_bytes(L, tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
-                          in + c0, len, false);
+            if (!gb_ring_copy(R, tm, L, bi, nb,
+                              tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
+                              in + c0, len, false))
+                return;
         }
         if (t >= 1) {
             const long c = t - 1;
@@ -706,9 +917,10 @@ allgather_kernel(GbTeam tm, GbArgs a) {
             const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
             for (int d = 0; d < tm.world; ++d) {
                 const int peer = (tm.rank + d) % tm.world;
-                gb_copy_bytes(L, out + (size_t)peer * a.n + c0,
-                              tm.ws[peer] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
-                              len, true);
+                if (!gb_ring_copy(R, tm, L, bi, nb, out + (size_t)peer * a.n + c0,
+                                  tm.ws[peer] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
+                                  len, true))
+                    return;
             }
         }
         if (t < nchunks && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
@@ -733,15 +945,20 @@ reduce_scatter_kernel(GbTeam tm, GbArgs a) {
     const GbLane L = !split ? gb_lane_all(tm.ld_mode)
                    : do_a ? gb_lane_blocks(0, a.role_a, tm.ld_mode)
                           : gb_lane_blocks(a.role_a, (int)gridDim.x - a.role_a, tm.ld_mode);
+    GbRing R = gb_ring_init();
+    const int ring_bi = !split || do_a ? (int)blockIdx.x : (int)blockIdx.x - a.role_a;
+    const int ring_nb = !split ? (int)gridDim.x : do_a ? a.role_a : (int)gridDim.x - a.role_a;
     for (long t = 0; t <= nchunks; ++t) {
         if (do_a && t < nchunks) {
             const size_t c0 = (size_t)t * a.chunk;
             const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
             for (int d = 0; d < tm.world; ++d) {
                 const int owner = (tm.rank + d) % tm.world;
-                gb_copy_bytes(L, tm.ws[owner] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a
-                              + (size_t)tm.rank * slot,
-                              in + (size_t)owner * a.n + c0, len * sizeof(T), false);
+                if (!gb_ring_copy(R, tm, L, ring_bi, ring_nb,
+                                  tm.ws[owner] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a
+                                  + (size_t)tm.rank * slot,
+                                  in + (size_t)owner * a.n + c0, len * sizeof(T), false))
+                    return;
             }
         }
         if (do_b && t >= 1) {
@@ -764,6 +981,8 @@ broadcast_kernel(GbTeam tm, GbArgs a) {
     char* data = static_cast<char*>(a.out);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
     const GbLane L = gb_lane_all(tm.ld_mode);
+    GbRing R = gb_ring_init();
+    const int bi = (int)blockIdx.x, nb = (int)gridDim.x;
     for (long t = 0; t <= nchunks; ++t) {
         if (t < nchunks && tm.rank == a.root) {
             const size_t c0 = (size_t)t * a.chunk;
@@ -772,8 +991,10 @@ broadcast_kernel(GbTeam tm, GbArgs a) {
                 const size_t s0 = c0 + (size_t)j * a.stripe;
                 if (s0 >= a.n) continue;
                 const size_t len = a.n - s0 < a.stripe ? a.n - s0 : a.stripe;
-                gb_copy_bytes(L, tm.ws[j] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
-                              data + s0, len, false);
+                if (!gb_ring_copy(R, tm, L, bi, nb,
+                                  tm.ws[j] + a.off_a + (size_t)(parity * 2 + (t & 1)) * a.len_a,
+                                  data + s0, len, false))
+                    return;
             }
         }
         if (t >= 1 && tm.rank != a.root) {
@@ -784,9 +1005,10 @@ broadcast_kernel(GbTeam tm, GbArgs a) {
                 const size_t s0 = c0 + (size_t)j * a.stripe;
                 if (s0 >= a.n) continue;
                 const size_t len = a.n - s0 < a.stripe ? a.n - s0 : a.stripe;
-                gb_copy_bytes(L, data + s0,
-                              tm.ws[j] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
-                              len, true);
+                if (!gb_ring_copy(R, tm, L, bi, nb, data + s0,
+                                  tm.ws[j] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
+                                  len, true))
+                    return;
             }
         }
         if (t < nchunks && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
@@ -870,13 +1092,25 @@ template <typename T, int OP>
 cudaError_t launch_plain(int kind, const GbTeam& tm, const GbArgs& a, int grid, cudaStream_t s) {
     if (kind == 0) allreduce_oneshot_kernel<T, OP><<<grid, THREADS, 0, s>>>(tm, a);
     else if (kind == 1) allreduce_hier_kernel<T, OP, GB_RAW><<<grid, THREADS, 0, s>>>(tm, a);
-    else if (kind == 2) reduce_scatter_kernel<T, OP><<<grid, THREADS, 0, s>>>(tm, a);
+    else if (kind == 2) {
+        static cudaError_t opted = cudaFuncSetAttribute(
+            reduce_scatter_kernel<T, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, GB_RING_SMEM);
+        if (opted != cudaSuccess) return opted;
+        reduce_scatter_kernel<T, OP><<<grid, THREADS, GB_RING_SMEM, s>>>(tm, a);
+    }
     else if (kind == 3) {
         // the ring needs more dynamic shared memory than the default limit: opt in once
         static cudaError_t opted = cudaFuncSetAttribute(
             allreduce_ring_kernel<T, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, GB_RING_SMEM);
         if (opted != cudaSuccess) return opted;
         allreduce_ring_kernel<T, OP><<<grid, THREADS, GB_RING_SMEM, s>>>(tm, a);
+    }
+    else if (kind == 4) {
+        static cudaError_t opted = cudaFuncSetAttribute(
+            allreduce_ring_phased_kernel<T, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            GB_RING_SMEM);
+        if (opted != cudaSuccess) return opted;
+        allreduce_ring_phased_kernel<T, OP><<<grid, THREADS, GB_RING_SMEM, s>>>(tm, a);
     }
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
@@ -938,8 +1172,18 @@ extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const Gb
 // kind: 0 all-gather, 1 broadcast, 2 barrier, 3 link probe.
 extern "C" int gb_launch_copy(int kind, const GbTeam* team, const GbArgs* args, int grid,
                               cudaStream_t stream) {
-    if (kind == 0) allgather_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
-    else if (kind == 1) broadcast_kernel<<<grid, THREADS, 0, stream>>>(*team, *args);
+    if (kind == 0) {
+        static cudaError_t opted = cudaFuncSetAttribute(
+            allgather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GB_RING_SMEM);
+        if (opted != cudaSuccess) return opted;
+        allgather_kernel<<<grid, THREADS, GB_RING_SMEM, stream>>>(*team, *args);
+    }
+    else if (kind == 1) {
+        static cudaError_t opted = cudaFuncSetAttribute(
+            broadcast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GB_RING_SMEM);
+        if (opted != cudaSuccess) return opted;
+        broadcast_kernel<<<grid, THREADS, GB_RING_SMEM, stream>>>(*team, *args);
+    }
     else if (kind == 2) barrier_kernel<<<1, THREADS, 0, stream>>>(*team);
     else if (kind == 3) {
         static cudaError_t opted = cudaFuncSetAttribute(

@@ -79,7 +79,9 @@ class Fabric:
         self.force_chunks = int(os.environ.get("GPUBRIDGE_HIER_CHUNKS", "0")) or None
         self.force_channels = int(os.environ.get("GPUBRIDGE_HIER_CHANNELS", "0")) or None
         # reads through the bulk-copy ring (TMA into shared memory) instead of register loads
-        self.ring = os.environ.get("GPUBRIDGE_RING", "1") != "0"
+        # ("phased": one ring run per step instead of one queue per iteration)
+        ring = os.environ.get("GPUBRIDGE_RING", "1")
+        self.ring = False if ring == "0" else "phased" if ring == "phased" else True
         self.launches = 0            # kernels launched by this team (benchmarks report it)
 
         islands = layout.islands
@@ -282,7 +284,7 @@ class Fabric:
             codec = _lib.CODECS[tuple(compression)]
             args.residual = self._residual(tensor, (stripe, k, nchunks, codec)).data_ptr()
         aligned = (args.inp | args.out) % 16 == 0
-        kind = 3 if (self.ring and codec == 0 and aligned) else 1
+        kind = (4 if self.ring == "phased" else 3) if (self.ring and codec == 0 and aligned) else 1
         self._launch_reduce(kind, tensor.dtype, op, codec, args, grid)
 
     def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:

@@ -91,7 +91,7 @@ def test_single_rank_all_reduce_paths(ring):
         x = (torch.arange((3 << 20) + 7, device=device) % 97).float()
         y = x.clone()
         team.all_reduce(y, "sum", 3, "striped")
-        assert torch.equal(y, x / 3)
+        assert torch.equal(y, x / torch.full_like(x, 3))      # tensor / tensor: IEEE division
         # a view that is not 16-byte aligned falls back to register copies
         z = x[1:4099 + 1].clone()
         base = torch.zeros(4099 + 8, device=device)
