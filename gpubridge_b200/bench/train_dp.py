@@ -37,6 +37,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--backend", default="gpubridge", help="gpubridge or nccl (the baseline)")
+    ap.add_argument("--rng", default="device", choices=("cpu", "device"),
+                    help="where the random initial weights are drawn (same seed on every rank)")
     args = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -50,7 +52,7 @@ def main(argv=None) -> int:
         warnings.simplefilter("ignore", gb.SplitTestWarning)
         dist.init_process_group(args.backend if on_gpu or args.backend == "gpubridge" else "gloo")
     dtype = torch.bfloat16 if on_gpu else torch.float32
-    model = llama.build(args.model, seed=0, device=device, dtype=torch.float32)
+    model = llama.build(args.model, seed=0, device=device, dtype=torch.float32, rng=args.rng)
     config = model.config
     if args.mode == "ddp":
         from torch.nn.parallel import DistributedDataParallel as DDP

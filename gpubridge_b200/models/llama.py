@@ -114,19 +114,26 @@ class Llama(nn.Module):
                                    self.config.vocab, unit_grad=self.unit_grad)
 
 
-def build(name: str, seed: int = 0, device="cpu", dtype=torch.float32) -> Llama:
+def build(name: str, seed: int = 0, device="cpu", dtype=torch.float32, rng: str = "cpu") -> Llama:
     """The named model with deterministic N(0, 0.02) weights (norm weights stay 1).  Built on
     the meta device and materialised on ``device`` so an 8 B model never sits in host memory
-    twice."""
+    twice.  ``rng="cpu"`` draws the weights from a CPU generator (the same values on any
+    machine, as the reference's models do); ``rng="device"`` draws them on ``device`` (seconds
+    instead of minutes for billions of parameters; the same values on the same kind of GPU)."""
     config = CONFIGS[name]
     with torch.device("meta"):
         model = Llama(config)
     model.to_empty(device=device)
     generator = torch.Generator(device="cpu").manual_seed(seed)
+    on_device = rng == "device" and torch.device(device).type == "cuda"
+    if on_device:
+        generator = torch.Generator(device=device).manual_seed(seed)
     with torch.no_grad():
         for parameter in model.parameters():
             if parameter.dim() == 1:
                 parameter.fill_(1.0)
+            elif on_device:
+                parameter.normal_(0.0, 0.02, generator=generator)
             else:
                 values = torch.empty(parameter.shape, dtype=torch.float32)
                 values.normal_(0.0, 0.02, generator=generator)

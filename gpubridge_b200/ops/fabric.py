@@ -78,6 +78,12 @@ class Fabric:
         # tuning overrides (benchmarks): fixed pipeline depth and role split
         self.force_chunks = int(os.environ.get("GPUBRIDGE_HIER_CHUNKS", "0")) or None
         self.force_channels = int(os.environ.get("GPUBRIDGE_HIER_CHANNELS", "0")) or None
+        # Grids of the copy-shaped collectives.  With the bulk-copy ring 16 CTAs already run a
+        # link at 640-680 GB/s (measured), so all-gather and broadcast take few SMs and leave
+        # the rest to the compute they overlap with; reduce-scatter also reduces locally.
+        self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "32"))
+        self.overlap_blocks = int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
+        self.scatter_blocks = int(os.environ.get("GPUBRIDGE_SCATTER_BLOCKS", "64"))
         # reads through the bulk-copy ring (TMA into shared memory) instead of register loads
         # ("phased": one ring run per step instead of one queue per iteration)
         ring = os.environ.get("GPUBRIDGE_RING", "1")
@@ -165,10 +171,16 @@ class Fabric:
         self.comm_stream.wait_stream(current)
         for t in tensors:
             t.record_stream(self.comm_stream)
-        with torch.cuda.stream(self.comm_stream):
-            run()
-            done = torch.cuda.Event()
-            done.record(self.comm_stream)
+        # an asynchronous collective runs beside the caller's compute: it takes few SMs
+        full = self.max_blocks
+        self.max_blocks = min(full, self.overlap_blocks)
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                run()
+                done = torch.cuda.Event()
+                done.record(self.comm_stream)
+        finally:
+            self.max_blocks = full
         return done
 
     # -- health --------------------------------------------------------------------------------------
@@ -327,7 +339,7 @@ class Fabric:
                 args.chunk = min(_align_down(self.rs_chunk_bytes // esize, 256),
                                  _align_up(n, 256))
                 args.off_a, args.len_a = self.off_rs, self.len_rs
-                grid = self._grid(tensor.nbytes)
+                grid = self._grid(tensor.nbytes, min(self.scatter_blocks, self.max_blocks))
                 if -(-n // args.chunk) >= 4 and grid >= 8:
                     args.role_a = grid * 3 // 4
                 self._launch_reduce(2, tensor.dtype, "sum", 0, args, grid)
@@ -345,7 +357,7 @@ class Fabric:
                 args.inp, args.out, args.n = tensor.data_ptr(), output.data_ptr(), nbytes
                 args.chunk = min(self.ag_chunk_bytes, _align_up(nbytes, 16))
                 args.off_a, args.len_a = self.off_ag, self.len_ag
-                self._launch_copy(0, args, self._grid(output.nbytes))
+                self._launch_copy(0, args, self._grid(output.nbytes, min(self.copy_blocks, self.max_blocks)))
         finally:
             self._end(current)
 
@@ -363,7 +375,7 @@ class Fabric:
                 stripe = min(self.bc_stripe_bytes, _align_up(-(-nbytes // self.world), 16))
                 args.stripe, args.chunk = stripe, stripe * self.world
                 args.off_a, args.len_a = self.off_bc, self.len_bc
-                self._launch_copy(1, args, self._grid(nbytes * 2))
+                self._launch_copy(1, args, self._grid(nbytes * 2, min(self.copy_blocks, self.max_blocks)))
         finally:
             self._end(current)
 

@@ -40,14 +40,18 @@ class DataParallelTrainer:
         bucket_mb: gradient bucket size (DDP's default is 25 MB).
         autocast: dtype of ``torch.autocast`` around forward, or None.
         graph: capture the step in a CUDA graph after ``graph_warmup`` eager steps.
+        overlap_blocks: CTAs of a bucket all-reduce that runs beside backward
+            (``GPUBRIDGE_OVERLAP_BLOCKS``, default 32); the last bucket uses the full grid.
     """
 
     def __init__(self, model: nn.Module, loss_fn, *, topology: Topology | None = None,
                  lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 1e-2, bucket_mb: float = 25.0,
                  autocast: torch.dtype | None = torch.bfloat16, graph: bool = False,
-                 graph_warmup: int = 3) -> None:
+                 graph_warmup: int = 3, overlap_blocks: int | None = None) -> None:
         self.model, self.loss_fn = model, loss_fn
+        import os
+        self.overlap_blocks = overlap_blocks or int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
         if hasattr(model, "unit_grad"):
             model.unit_grad = True          # backward always starts at the loss here
         if topology is None and is_initialized():
@@ -110,18 +114,26 @@ class DataParallelTrainer:
         """Launch, in bucket order, every bucket whose gradients are all in."""
         while self._sent < len(self._buckets) and self._pending[self._sent] == 0:
             lo, hi, _ = self._buckets[self._sent]
-            self._all_reduce(self.flat_grad[lo:hi])
+            self._all_reduce(self.flat_grad[lo:hi], tail=self._sent == len(self._buckets) - 1)
             self._sent += 1
 
-    def _all_reduce(self, grads: torch.Tensor) -> None:
+    def _all_reduce(self, grads: torch.Tensor, tail: bool = False) -> None:
         topology, fabric = self.topology, self.fabric
         if fabric is not None:
-            # stream-ordered: fork onto the communication stream, join before the optimizer
+            # stream-ordered: fork onto the communication stream, join before the optimizer.
+            # A bucket that runs beside backward takes few SMs (a CTA of the collective owns
+            # its SM, so a full grid would serialise with the GEMMs instead of overlapping);
+            # the last bucket has nothing left to overlap with and takes the full grid.
             comm = fabric.comm_stream
             comm.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(comm):
-                topology.policy.select_policy(grads.nbytes).all_reduce(
-                    grads, topology, divide=self.world)
+            full = fabric.max_blocks
+            fabric.max_blocks = full if tail else min(full, self.overlap_blocks)
+            try:
+                with torch.cuda.stream(comm):
+                    topology.policy.select_policy(grads.nbytes).all_reduce(
+                        grads, topology, divide=self.world)
+            finally:
+                fabric.max_blocks = full
             self.launches += 1
         else:
             from gpubridge_b200.collectives import all_reduce
