@@ -28,6 +28,8 @@ from datetime import timedelta
 
 import torch
 
+from gpubridge_b200._mutation import mutated
+
 from gpubridge_b200 import config as _config
 from gpubridge_b200 import work as _work
 from gpubridge_b200.ops import _lib
@@ -156,19 +158,20 @@ class Fabric:
     # -- stream discipline --------------------------------------------------------------------------
     def _begin(self):
         current = torch.cuda.current_stream(self.device)
-        if current != self.comm_stream:
+        if current != self.comm_stream and not mutated("comm-ignores-caller"):
             self.comm_stream.wait_stream(current)
         return current
 
     def _end(self, current) -> None:
-        if current != self.comm_stream:
+        if current != self.comm_stream and not mutated("caller-ignores-comm"):
             current.wait_stream(self.comm_stream)
 
     def on_comm_stream(self, run, tensors) -> torch.cuda.Event:
         """Run ``run()`` with the communication stream current (ordered after the caller's
         stream); returns the event recorded after it.  The async path of the collectives."""
         current = torch.cuda.current_stream(self.device)
-        self.comm_stream.wait_stream(current)
+        if not mutated("async-ignores-caller"):
+            self.comm_stream.wait_stream(current)
         for t in tensors:
             t.record_stream(self.comm_stream)
         # an asynchronous collective runs beside the caller's compute: it takes few SMs

@@ -17,6 +17,8 @@ from __future__ import annotations
 
 import torch
 
+from gpubridge_b200._mutation import mutated
+
 
 class HostStaging:
     """On CPU a tensor already is host memory: slots are the chunks, copies are no-ops."""
@@ -62,7 +64,8 @@ class ChunkStaging(HostStaging):
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
         for stream in (self.out_stream, self.back_stream):
-            stream.wait_event(ready)
+            if not mutated("staging-ignores-caller"):
+                stream.wait_event(ready)
             tensor.record_stream(stream)
 
     def _copy(self, stream, dst, src, after):

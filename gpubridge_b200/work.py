@@ -24,6 +24,8 @@ from typing import Any
 
 import torch
 
+from gpubridge_b200._mutation import mutated
+
 QUEUE_ENV = "GPUBRIDGE_ASYNC_QUEUE"
 DEFAULT_QUEUE = 1024
 
@@ -65,7 +67,7 @@ class Work:
             raise TimeoutError(f"gpubridge async {self.op} did not finish within {seconds} s")
         if self._error is not None:
             raise RuntimeError(f"gpubridge async {self.op} failed: {self._error}") from self._error
-        if self._event is not None:
+        if self._event is not None and not mutated("wait-skips-stream"):
             torch.cuda.current_stream(self._device).wait_event(self._event)
         if self._check is not None and self._event is not None and self._event.query():
             self._check()
