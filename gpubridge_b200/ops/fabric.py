@@ -88,7 +88,7 @@ class Fabric:
         self.scatter_blocks = int(os.environ.get("GPUBRIDGE_SCATTER_BLOCKS", "64"))
         # reads through the bulk-copy ring (TMA into shared memory) instead of register loads
         # ("phased": one ring run per step instead of one queue per iteration)
-        ring = os.environ.get("GPUBRIDGE_RING", "1")
+        ring = os.environ.get("GPUBRIDGE_RING", "phased")
         self.ring = False if ring == "0" else "phased" if ring == "phased" else True
         self.launches = 0            # kernels launched by this team (benchmarks report it)
 
