@@ -39,6 +39,8 @@ def _library():
         L.gb_tcp_recv.restype = ctypes.c_long
         L.gb_tcp_recv.argtypes = [vp, i, vp, u64, u64]
         L.gb_tcp_wait.argtypes = [vp, ctypes.POINTER(ctypes.c_long), i, ctypes.c_double]
+        L.gb_tcp_all_reduce.argtypes = [vp, vp, u64, i, i, u64, u64, ctypes.c_double]
+        L.gb_tcp_broadcast.argtypes = [vp, vp, u64, i, u64, u64, ctypes.c_double]
         L.gb_tcp_abort.argtypes = [vp]
         L.gb_tcp_close.argtypes = [vp]
         L.gb_tcp_last_error.restype = ctypes.c_char_p
@@ -93,6 +95,20 @@ class Worker:
         array = (ctypes.c_long * len(ids))(*ids)
         left = max(0.001, deadline - time.monotonic())
         if self.lib.gb_tcp_wait(self.handle, array, len(ids), left) != 0:
+            raise RuntimeError(f"multitcp: {self._error()}")
+
+    # The collectives themselves, run inside the library (csrc/gb_tcp.cpp): same tags and
+    # algorithms as tagged.py, without a Python round trip per chunk.
+    def all_reduce(self, ptr: int, count: int, dtype: int, op: int, chunk_elems: int, seq: int,
+                   deadline: float) -> None:
+        left = max(0.001, deadline - time.monotonic())
+        if self.lib.gb_tcp_all_reduce(self.handle, ptr, count, dtype, op, chunk_elems, seq, left) != 0:
+            raise RuntimeError(f"multitcp: {self._error()}")
+
+    def broadcast(self, ptr: int, nbytes: int, root: int, chunk_bytes: int, seq: int,
+                  deadline: float) -> None:
+        left = max(0.001, deadline - time.monotonic())
+        if self.lib.gb_tcp_broadcast(self.handle, ptr, nbytes, root, chunk_bytes, seq, left) != 0:
             raise RuntimeError(f"multitcp: {self._error()}")
 
     def abort(self) -> None:

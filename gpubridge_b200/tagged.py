@@ -18,7 +18,7 @@ Tag layout (64 bits): sequence (24) | step (12) | sender (8) | chunk (20).
 """
 from __future__ import annotations
 
-import itertools
+import os
 import time
 from collections.abc import Sequence
 from datetime import timedelta
@@ -30,6 +30,17 @@ from gpubridge_b200.transport import BridgeTransport, LinkContext
 
 DEFAULT_TIMEOUT = timedelta(minutes=30)
 HANDSHAKE_STEP = 0xFFF
+
+#: dtype and op codes of the native collectives (csrc/gb_tcp.cpp)
+_NATIVE_DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.float64: 3,
+                  torch.int8: 4, torch.uint8: 5, torch.int32: 6, torch.int64: 7}
+_NATIVE_OPS = {"sum": 0, "max": 1, "min": 2}
+
+
+def native_collectives() -> bool:
+    """``GPUBRIDGE_TAGGED_NATIVE=0`` keeps the collectives in Python (the oracle of the tests)."""
+    return os.environ.get("GPUBRIDGE_TAGGED_NATIVE", "1") != "0"
+
 
 _REDUCE = {"sum": torch.Tensor.add_, "max": lambda a, b: torch.maximum(a, b, out=a),
            "min": lambda a, b: torch.minimum(a, b, out=a)}
@@ -168,6 +179,11 @@ class TaggedBridge(BridgeTransport):
         size, fold = len(self.members), _REDUCE[op]
         flat = tensor.view(-1)
         worker = self.worker
+        if (hasattr(worker, "all_reduce") and tensor.dtype in _NATIVE_DTYPES
+                and native_collectives()):
+            worker.all_reduce(flat.data_ptr(), flat.numel(), _NATIVE_DTYPES[tensor.dtype],
+                              _NATIVE_OPS[op], chunk, seq, deadline)
+            return
         if size == 2:
             (peer,) = self._peers()
             scratch = torch.empty_like(flat)
@@ -209,6 +225,10 @@ class TaggedBridge(BridgeTransport):
         seq, deadline, chunk = self._begin(tensor)
         root = self.members.index(src)
         flat = tensor.view(-1)
+        if hasattr(self.worker, "broadcast") and native_collectives():
+            self.worker.broadcast(flat.data_ptr(), flat.numel() * flat.element_size(), root,
+                                  chunk * flat.element_size(), seq, deadline)
+            return
         if self.index == root:
             ids = [i for peer in self._peers()
                    for i in self._post(self.worker.send, peer, flat, seq, 0, root, chunk)]

@@ -62,3 +62,86 @@ def test_worker_reports_a_vanished_peer():
     with pytest.raises(RuntimeError):
         a.send(1, src.data_ptr(), 32, 9)            # the worker stays broken
     a.close()
+
+
+def _native_equals_python(members: int):
+    """The collectives inside the library against the same algorithms in Python, thread per
+    member, every dtype and op, sizes around the chunk boundaries: bit for bit."""
+    import threading
+    import time
+    from datetime import timedelta
+    from gpubridge_b200 import tagged
+    from gpubridge_b200.multitcp import MultiTcpTransport, Worker
+
+    def link():
+        workers = [Worker(i, members, 2, "127.0.0.1") for i in range(members)]
+        addresses = [w.address() for w in workers]
+        threads = [threading.Thread(target=w.connect, args=(addresses, 20.0)) for w in workers]
+        [t.start() for t in threads]
+        [t.join() for t in threads]
+        return [MultiTcpTransport(w, list(range(members)), i, timedelta(seconds=30), 4096)
+                for i, w in enumerate(workers)]
+
+    def values(rank, n, dtype):
+        g = torch.Generator().manual_seed(100 * rank + n)
+        if dtype.is_floating_point:
+            t = (torch.randn(n, generator=g) * 3).to(dtype)
+            if n > 4:
+                t[3] = float("nan") if rank == 0 else 1.0
+            return t
+        return torch.randint(-100, 100, (n,), generator=g).to(dtype)
+
+    def run(transports, fn):
+        errors = []
+
+        def one(tr, rank):
+            try:
+                fn(tr, rank)
+            except BaseException as exc:  # noqa: BLE001
+                errors.append(exc)
+        threads = [threading.Thread(target=one, args=(tr, r)) for r, tr in enumerate(transports)]
+        [t.start() for t in threads]
+        [t.join() for t in threads]
+        assert not errors, errors
+
+    import os
+    results = {}
+    for native in ("1", "0"):
+        os.environ["GPUBRIDGE_TAGGED_NATIVE"] = native
+        transports = link()
+        got = {}
+
+        def work(tr, rank, got=got):
+            for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.float64,
+                          torch.int8, torch.uint8, torch.int32, torch.int64):
+                for n in (1, 2, 1023, 1024, 1025, 5000):
+                    for op in ("sum", "max", "min"):
+                        t = values(rank, n, dtype)
+                        tr.all_reduce(t, op)
+                        got[(rank, str(dtype), n, op)] = t.clone()
+            t = values(rank, 3000, torch.float32)
+            tr.broadcast(t, members - 1)
+            got[(rank, "bcast")] = t.clone()
+        try:
+            run(transports, work)
+        finally:
+            for tr in transports:
+                tr.close()
+        results[native] = got
+    os.environ.pop("GPUBRIDGE_TAGGED_NATIVE", None)
+    assert results["1"].keys() == results["0"].keys()
+    for key, want in results["0"].items():
+        have = results["1"][key]
+        same = torch.equal(have.view(torch.uint8), want.view(torch.uint8)) if have.dtype != torch.bool else True
+        if not same:                      # NaN payload bits may differ; values must not
+            assert torch.equal(have.isnan(), want.isnan()), key
+            assert torch.equal(have.nan_to_num(), want.nan_to_num()), key
+    assert torch.equal(results["1"][(0, "bcast")], values(members - 1, 3000, torch.float32))
+
+
+def test_native_collectives_equal_python_two_members():
+    _native_equals_python(2)
+
+
+def test_native_collectives_equal_python_ring():
+    _native_equals_python(3)
