@@ -55,7 +55,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                 "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
                 stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -188,9 +188,9 @@ def run_ours(args) -> dict:
     before = trainer.launches
     ms = max_over_ranks(timed(device_steps, args.steps, device, barrier))
     launches = trainer.launches - before
-    clocks = sampler.stop()
     e2e_steps(2)
     e2e_ms = max_over_ranks(timed(e2e_steps, args.steps, device, barrier))
+    clocks = sampler.stop()                     # sampled through both timed regions
     trainer.check()
     tokens = BATCH * SEQ * world * args.steps
     working_set_gb = round(torch.cuda.max_memory_allocated(device) / 1e9, 1)
@@ -331,9 +331,9 @@ def run_reference(args) -> dict:
     sampler = ClockSampler(local_rank)
     sampler.start()
     ms = max_over_ranks(timed(device_steps, args.steps, device, barrier))
-    clocks = sampler.stop()
     e2e_steps(2)
     e2e_ms = max_over_ranks(timed(e2e_steps, args.steps, device, barrier))
+    clocks = sampler.stop()                     # sampled through both timed regions
     tokens = BATCH * SEQ * world * args.steps
     result = {
         "metric": METRIC, "value": round(tokens / (ms * 1e-3), 1), "unit": "tokens/s",
@@ -358,12 +358,15 @@ def run_reference(args) -> dict:
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries one JSON line
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     default_rendezvous()
     world = int(os.environ["WORLD_SIZE"])
     if world != args.gpus and int(os.environ["RANK"]) == 0:

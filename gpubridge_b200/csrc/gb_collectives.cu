@@ -52,6 +52,8 @@ struct GbArgs {
     size_t off_a, off_b, off_c;   // regions
     size_t len_a, len_b, len_c;   // bytes of one buffer of each region
     float* residual;          // error feedback of this rank's stripes (compressed all-reduce)
+    char* sym;                // NVLS all-reduce: this rank's multicast-bound buffer ...
+    char* mc;                 // ... and the multicast address of the same buffer on every rank
 };
 
 namespace {
@@ -891,6 +893,86 @@ allreduce_ring_phased_kernel(GbTeam tm, GbArgs a) {
     }
 }
 
+// ---- all-reduce through the switch (NVLS) --------------------------------------------------------
+// One island, SUM / AVG of f32, bf16 or f16.  Every rank owns a buffer bound to one NVLink
+// multicast object: a multimem.ld_reduce on the multicast address returns the sum of that
+// address over all ranks, computed inside the NVSwitch, and a multimem.st writes all ranks'
+// copies at once.  Per chunk: copy the input into the own buffer; barrier; reduce the own
+// 1/world slice through the switch and write it back to everybody; barrier; copy the buffer
+// to the output.  A GPU then receives and sends one chunk's worth of data per chunk instead of
+// 2 (world - 1) / world: half the traffic of the two-shot exchange over peer memory.  Every
+// element is reduced by exactly one rank, so all ranks end with identical bits; the order of
+// the addends is the switch's.  Region: `sym` / `mc` + off_a, two halves of len_a bytes that
+// alternate with the chunk index (a peer may still be reading the half of chunk c while chunk
+// c + 1 is written).
+template <typename T> struct Multimem;
+template <> struct Multimem<float> {
+    static __device__ __forceinline__ uint4 load_sum(const char* mc) {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+template <> struct Multimem<__nv_bfloat16> {
+    static __device__ __forceinline__ uint4 load_sum(const char* mc) {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+template <> struct Multimem<__half> {
+    static __device__ __forceinline__ uint4 load_sum(const char* mc) {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+__device__ __forceinline__ void multimem_store(char* mc, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+allreduce_nvls_kernel(GbTeam tm, GbArgs a) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = Vec<T>::N;
+    const char* in = static_cast<const char*>(a.in);
+    char* out = static_cast<char*>(a.out);
+    const GbLane L = gb_lane_all(tm.ld_mode);
+    const size_t total = a.n * sizeof(T);
+    const size_t chunk = a.chunk * sizeof(T);              // a multiple of 16 * world
+    const long nchunks = (long)((total + chunk - 1) / chunk);
+    for (long c = 0; c < nchunks; ++c) {
+        const size_t c0 = (size_t)c * chunk;
+        const size_t len = total - c0 < chunk ? total - c0 : chunk;
+        const size_t padded = round_up(len, 16 * (size_t)tm.world);
+        char* mine = a.sym + a.off_a + (size_t)(c & 1) * a.len_a;
+        char* everyone = a.mc + a.off_a + (size_t)(c & 1) * a.len_a;
+        gb_copy_bytes(L, mine, in + c0, len, false);
+        zero_range(L, mine, len, padded);
+        if (!gb_sync_all(tm, (unsigned)(c < 3 ? 2 * c : 6), c == 0)) return;
+        const size_t slice = padded / (size_t)tm.world;    // a multiple of 16
+        const size_t s0 = (size_t)tm.rank * slice;
+        const size_t nvec = slice >> 4;
+        for (size_t v = L.tid; v < nvec; v += L.nth) {
+            Vec<T> r;
+            r.u = Multimem<T>::load_sum(everyone + s0 + (v << 4));
+            if (a.divide > 0) {
+                #pragma unroll
+                for (int j = 0; j < V; ++j)
+                    r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
+            }
+            multimem_store(everyone + s0 + (v << 4), r.u);
+        }
+        if (!gb_sync_all(tm, (unsigned)(c < 3 ? 2 * c + 1 : 7), false)) return;
+        gb_copy_bytes(L, out + c0, mine, len, true);
+    }
+}
+
 // ---- all-gather ---------------------------------------------------------------------------------
 // Region A: [2 parities][2 chunk buffers] of len_a bytes.  n and chunk are bytes.
 __global__ void __launch_bounds__(THREADS)
@@ -1117,6 +1199,12 @@ cudaError_t launch_plain(int kind, const GbTeam& tm, const GbArgs& a, int grid, 
 }
 
 template <typename T>
+cudaError_t launch_nvls(const GbTeam& tm, const GbArgs& a, int grid, cudaStream_t s) {
+    allreduce_nvls_kernel<T><<<grid, THREADS, 0, s>>>(tm, a);
+    return cudaGetLastError();
+}
+
+template <typename T>
 cudaError_t launch_op(int kind, int op, const GbTeam& tm, const GbArgs& a, int grid, cudaStream_t s) {
     if (op == GB_SUM) return launch_plain<T, GB_SUM>(kind, tm, a, grid, s);
     if (kind == 2) return cudaErrorInvalidValue;            // reduce-scatter: SUM only
@@ -1140,7 +1228,8 @@ cudaError_t launch_coded(int codec, const GbTeam& tm, const GbArgs& a, int grid,
 }  // namespace
 
 // kind: 0 one-shot all-reduce, 1 hierarchical all-reduce, 2 reduce-scatter,
-//       3 hierarchical all-reduce through the bulk-copy ring (no codec).
+//       3 / 4 hierarchical all-reduce through the bulk-copy ring (queue / phased; no codec),
+//       5 all-reduce through the switch (NVLS multimem).
 // codec (kind 1, SUM, floating point only): GbCodec.  Returns a cudaError_t.
 extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const GbTeam* team,
                                 const GbArgs* args, int grid, cudaStream_t stream) {
@@ -1153,6 +1242,15 @@ extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const Gb
             case GB_F64: return launch_coded<double>(codec, tm, a, grid, stream);
             case GB_BF16: return launch_coded<__nv_bfloat16>(codec, tm, a, grid, stream);
             case GB_F16: return launch_coded<__half>(codec, tm, a, grid, stream);
+        }
+        return cudaErrorInvalidValue;
+    }
+    if (kind == 5) {                        // through the switch: SUM of f32, bf16, f16 only
+        if (op != GB_SUM || a.mc == nullptr || a.sym == nullptr) return cudaErrorInvalidValue;
+        switch (dtype) {
+            case GB_F32: return launch_nvls<float>(tm, a, grid, stream);
+            case GB_BF16: return launch_nvls<__nv_bfloat16>(tm, a, grid, stream);
+            case GB_F16: return launch_nvls<__half>(tm, a, grid, stream);
         }
         return cudaErrorInvalidValue;
     }
