@@ -36,7 +36,8 @@ from gpubridge_b200.ops import _lib
 
 MIB = 1 << 20
 FLAG_BYTES = 4096
-ONESHOT_MAX = 1 << 20            # largest tensor the one-shot kernel takes
+ONESHOT_MAX = 1 << 20
+NVLS_DTYPES = (torch.float32, torch.bfloat16, torch.float16)            # largest tensor the one-shot kernel takes
 # Measured with bench/bench_link.py on B200 (2 ranks): one block moves about 45 GB/s of any
 # traffic, a link direction saturates near 650-700 GB/s (16 blocks), a team barrier inside a
 # kernel costs about 10 us.  The pipeline plan below is sized from these.
@@ -83,6 +84,7 @@ class Fabric:
         # Grids of the copy-shaped collectives.  With the bulk-copy ring 16 CTAs already run a
         # link at 640-680 GB/s (measured), so all-gather and broadcast take few SMs and leave
         # the rest to the compute they overlap with; reduce-scatter also reduces locally.
+        self.nvls = None        # (tensor, handle, local pointer, multicast pointer, bytes per half)
         self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "32"))
         self.overlap_blocks = int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
         self.scatter_blocks = int(os.environ.get("GPUBRIDGE_SCATTER_BLOCKS", "64"))
@@ -186,6 +188,30 @@ class Fabric:
             self.max_blocks = full
         return done
 
+    # -- in-switch reduction ------------------------------------------------------------------------
+    def enable_nvls(self, group, nbytes: int | None = None) -> bool:
+        """Bind a buffer of this rank to an NVLink multicast object shared with every member of
+        ``group`` (a torch process group with exactly this team's ranks), so that large SUM
+        all-reduces of one island run through the switch.  Collective over the group.  The
+        allocation and the multicast binding are torch's symmetric memory; the kernel is
+        ``allreduce_nvls_kernel``.  Returns False - on every rank alike - when the fabric or
+        the torch build cannot do it."""
+        if self.n_islands != 1 or self.world < 2:
+            return False
+        try:
+            import torch.distributed._symmetric_memory as symm
+            nbytes = nbytes or _config.size_setting("GPUBRIDGE_NVLS_BYTES", 128 * MIB, multiple=4096)
+            buffer = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+            handle = symm.rendezvous(buffer, group)
+            multicast = int(getattr(handle, "multicast_ptr", 0) or 0)
+        except Exception:  # noqa: BLE001 - an optional path: any refusal means "not available"
+            return False
+        if multicast == 0:
+            return False
+        half = _align_down(nbytes // 2, 16 * self.world * 256)
+        self.nvls = (buffer, handle, buffer.data_ptr(), multicast, half)
+        return True
+
     # -- health --------------------------------------------------------------------------------------
     def check(self) -> None:
         code = self._status[0]
@@ -255,6 +281,14 @@ class Fabric:
                 if oneshot:
                     args.off_a, args.len_a = self.off_oneshot, self.len_oneshot
                     self._launch_reduce(0, tensor.dtype, op, 0, args, self._grid(nbytes, 32))
+                elif (self.nvls is not None and op == "sum" and compression is None
+                      and tensor.dtype in NVLS_DTYPES and mode != "chunked"):
+                    _, _, local, multicast, half = self.nvls
+                    esize = tensor.element_size()
+                    args.sym, args.mc = local, multicast
+                    args.off_a, args.len_a = 0, half
+                    args.chunk = _align_down(half, 16 * self.world) // esize
+                    self._launch_reduce(5, tensor.dtype, op, 0, args, self._grid(nbytes))
                 else:
                     self._hier(tensor, args, op, compression, chunk_bytes)
         finally:
@@ -424,6 +458,7 @@ class Fabric:
             torch.cuda.synchronize(self.device)
         except Exception:  # noqa: BLE001 - teardown never raises
             pass
+        self.nvls = None
         short = timedelta(seconds=20)
         if self.world == 1:
             self.lib.gb_symm_free(self.ws[0])

@@ -493,7 +493,22 @@ def _assemble(store, name: str, layout: Layout, rank: int, peers, cfg: Config,
                         cpu_group=cpu_group, fabric=fabric, context=context,
                         p2p_group=p2p_group)
     topology.policy.setup(topology)
+    _maybe_nvls(topology)
     return topology
+
+
+def _maybe_nvls(topology: "Topology") -> None:
+    """``GPUBRIDGE_NVLS=1``: reduce large single-island sums inside the NVSwitch.  Needs the
+    team to be the whole job (the multicast binding goes through the default process group).
+    Off by default; tests that let a rank die run with it off."""
+    import os
+    fabric = topology.fabric
+    if fabric is None or os.environ.get("GPUBRIDGE_NVLS", "0") != "1":
+        return
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size() != topology.world_size:
+        return
+    fabric.enable_nvls(dist.group.WORLD)
 
 
 def close_topology(topology: Topology) -> None:

@@ -105,6 +105,57 @@ def test_collectives_other_policies(tmp_path, policy):
     assert {name for name, _ in out} == {policy}
 
 
+def _through_the_switch(rank, topology):
+    """Sums of one island reduced inside the NVSwitch (multimem): exact on integer-valued
+    data, identical on every rank, AVG divided once; the time of a 64 MiB call beside the
+    peer-memory kernel's."""
+    import time
+    import gpubridge_b200 as gb
+    fabric = topology.fabric
+    if fabric is None or fabric.nvls is None:
+        return "unavailable"
+    dev, world = topology.device, topology.world_size
+    before = fabric.launches
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for n in ((1 << 20) + 5, (9 << 20) + 3, (40 << 20) + 1):
+            if dtype is not torch.float32 and n > (10 << 20):
+                continue
+            t = rank_tensor(rank, n, dtype).to(dev)
+            gb.all_reduce(t)
+            assert torch.equal(t.cpu(), expected_sum(world, n, dtype)), ("sum", dtype, n)
+    t = rank_tensor(rank, (3 << 20) + 7).to(dev)
+    gb.all_reduce(t, gb.ReduceOp.AVG)
+    assert torch.equal(t.cpu(), expected_sum(world, (3 << 20) + 7) / world)
+    assert fabric.launches > before
+    timings = {}
+    big = torch.ones(16 << 20, device=dev)
+    for label in ("switch", "peer-memory"):
+        saved = fabric.nvls
+        if label == "peer-memory":
+            fabric.nvls = None
+        for _ in range(3):
+            gb.all_reduce(big)
+        torch.cuda.synchronize()
+        gb.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(10):
+            gb.all_reduce(big)
+        torch.cuda.synchronize()
+        timings[label] = round((time.perf_counter() - t0) / 10 * 1e6, 1)
+        fabric.nvls = saved
+    return timings
+
+
+@needs_two
+def test_all_reduce_through_the_switch(tmp_path):
+    out = run_ranks(gpu_ranks(WORLD), _through_the_switch, tmp_path, env={"GPUBRIDGE_NVLS": "1"},
+                    timeout=240)
+    if any(o == "unavailable" for o in out):
+        pytest.skip("no NVLink multicast binding on this machine")
+    print("64 MiB all-reduce, us per call:", out[0])
+
+
 def _compressed(rank, topology, mode, fmt):
     """The fused compressed all-reduce against the PyTorch codec: island sums in member order,
     one quantisation per island (with error feedback over two calls), payloads added in island
