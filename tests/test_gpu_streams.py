@@ -56,23 +56,30 @@ def _wrong(t, value):
     return f"{bad} elements wrong" if bad else ""
 
 
+# Every scenario runs twice and only the second pass is judged: the first use of a kernel in a
+# process loads its module, which synchronises the device and would hide a missing wait.
+
 def test_sync_collective_waits_for_caller(team):
-    out = torch.zeros(N, device=team.device)
-    x = _late_input(team.device, 3.0)
-    team.all_reduce(x, "sum", None, "striped", out=out)
-    torch.cuda.synchronize()
-    assert not _wrong(out, 3.0), _wrong(out, 3.0)
+    for _ in range(2):
+        out = torch.zeros(N, device=team.device)
+        x = _late_input(team.device, 3.0)
+        team.all_reduce(x, "sum", None, "striped", out=out)
+        torch.cuda.synchronize()
+        verdict = _wrong(out, 3.0)
+    assert not verdict, verdict
 
 
 def test_caller_waits_for_sync_collective(team):
     big = 1 << 26                                   # 256 MiB: the kernel runs for a while
     x = torch.full((big,), 5.0, device=team.device)
-    out = torch.full((big,), POISON, device=team.device)
-    torch.cuda.synchronize()
-    team.all_reduce(x, "sum", None, "striped", out=out)
-    seen = out[-4096:].clone()                      # queued on the caller's stream at once
-    torch.cuda.synchronize()
-    assert not _wrong(seen, 5.0), _wrong(seen, 5.0)
+    for _ in range(2):
+        out = torch.full((big,), POISON, device=team.device)
+        torch.cuda.synchronize()
+        team.all_reduce(x, "sum", None, "striped", out=out)
+        seen = out[-4096:].clone()                  # queued on the caller's stream at once
+        torch.cuda.synchronize()
+        verdict = _wrong(seen, 5.0)
+    assert not verdict, verdict
 
 
 def _launch_async(team, x, out):
@@ -84,24 +91,28 @@ def _launch_async(team, x, out):
 
 
 def test_async_collective_waits_for_caller(team):
-    out = torch.zeros(N, device=team.device)
-    x = _late_input(team.device, 7.0)
-    work = _launch_async(team, x, out)
-    work.wait()
-    torch.cuda.synchronize()
-    assert not _wrong(out, 7.0), _wrong(out, 7.0)
+    for _ in range(2):
+        out = torch.zeros(N, device=team.device)
+        x = _late_input(team.device, 7.0)
+        work = _launch_async(team, x, out)
+        work.wait()
+        torch.cuda.synchronize()
+        verdict = _wrong(out, 7.0)
+    assert not verdict, verdict
 
 
 def test_wait_orders_the_callers_stream(team):
     big = 1 << 26
     x = torch.full((big,), 9.0, device=team.device)
-    out = torch.full((big,), POISON, device=team.device)
-    torch.cuda.synchronize()
-    work = _launch_async(team, x, out)
-    work.wait()                                     # orders this stream; the host does not block
-    seen = out[-4096:].clone()
-    torch.cuda.synchronize()
-    assert not _wrong(seen, 9.0), _wrong(seen, 9.0)
+    for _ in range(2):
+        out = torch.full((big,), POISON, device=team.device)
+        torch.cuda.synchronize()
+        work = _launch_async(team, x, out)
+        work.wait()                                 # orders this stream; the host does not block
+        seen = out[-4096:].clone()
+        torch.cuda.synchronize()
+        verdict = _wrong(seen, 9.0)
+    assert not verdict, verdict
 
 
 def test_staging_waits_for_caller():
@@ -109,12 +120,14 @@ def test_staging_waits_for_caller():
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     staging = ChunkStaging(device, N * 4, 2)
-    x = _late_input(device, 11.0)
-    staging.begin(x)
-    slot = staging.slot(0, x)
-    done = staging.to_host(slot, x)
-    staging.wait_host(done)
-    host = slot.clone()
-    torch.cuda.synchronize()
+    for _ in range(2):
+        x = _late_input(device, 11.0)
+        staging.begin(x)
+        slot = staging.slot(0, x)
+        done = staging.to_host(slot, x)
+        staging.wait_host(done)
+        host = slot.clone()
+        torch.cuda.synchronize()
+        verdict = _wrong(host, 11.0)
     staging.close()
-    assert not _wrong(host, 11.0), _wrong(host, 11.0)
+    assert not verdict, verdict
