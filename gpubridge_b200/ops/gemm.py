@@ -23,7 +23,8 @@ class AllGatherLinear:
     call counter.  ``fabric`` is the team's :class:`~gpubridge_b200.ops.fabric.Fabric` (one of a
     single rank works too: then this is a plain tcgen05 GEMM)."""
 
-    def __init__(self, fabric, out_features: int, in_features: int, comm_blocks: int = 16) -> None:
+    def __init__(self, fabric, out_features: int, in_features: int, comm_blocks: int = 16,
+                 pair: bool | None = None) -> None:
         if out_features % fabric.world:
             raise ValueError("out_features must divide evenly over the team")
         if in_features % 8:
@@ -35,8 +36,14 @@ class AllGatherLinear:
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
         self.epoch = 0
         sms = torch.cuda.get_device_properties(device).multi_processor_count
-        self.comm_blocks = comm_blocks
-        self.gemm_blocks = max(1, sms - comm_blocks)
+        # pair: CTA pairs (tcgen05 cta_group::2) share the weight operand; GPUBRIDGE_GEMM_PAIR=0
+        # selects the single-CTA kernel
+        import os
+        self.pair = (os.environ.get("GPUBRIDGE_GEMM_PAIR", "1") != "0") if pair is None else pair
+        self.comm_blocks = comm_blocks + (comm_blocks & 1 if self.pair else 0)
+        self.gemm_blocks = max(2, sms - self.comm_blocks)
+        if self.pair:
+            self.gemm_blocks -= self.gemm_blocks & 1
         shard_bytes = out_features // fabric.world * in_features * 2
         if fabric.world > 1 and shard_bytes > fabric.len_ag:
             raise ValueError(f"a weight shard of {shard_bytes} bytes exceeds the fabric's staging "
@@ -54,7 +61,8 @@ class AllGatherLinear:
         current = fabric._begin()
         try:
             with torch.cuda.stream(fabric.comm_stream):
-                code = fabric.lib.gb_allgather_gemm(
+                entry = fabric.lib.gb_allgather_gemm_pair if self.pair else fabric.lib.gb_allgather_gemm
+                code = entry(
                     ctypes.byref(fabric.team), y.data_ptr(), x.data_ptr(), shard.data_ptr(),
                     self.gathered.data_ptr(), self.flags.data_ptr(), self.error.data_ptr(),
                     self.epoch, x.shape[0], self.N, self.K, fabric.off_ag, self.gemm_blocks,

@@ -7,9 +7,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("pair", [False, True], ids=["one-cta", "cta-pair"])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1000, 1280, 200),
                                    (2048, 2048, 2048)])
-def test_allgather_gemm_single_rank(M, N, K):
+def test_allgather_gemm_single_rank(M, N, K, pair):
     from gpubridge_b200.ops import fabric as F
     from gpubridge_b200.ops.gemm import AllGatherLinear
     device = torch.device("cuda", 0)
@@ -18,7 +19,7 @@ def test_allgather_gemm_single_rank(M, N, K):
         torch.manual_seed(M + N + K)
         x = (torch.randn(M, K, device=device) * 0.5).to(torch.bfloat16)
         w = (torch.randn(N, K, device=device) * 0.5).to(torch.bfloat16)
-        op = AllGatherLinear(team, N, K)
+        op = AllGatherLinear(team, N, K, pair=pair)
         for _ in range(2):                               # the second call reuses flags and buffers
             y = op(x, w)
         torch.cuda.synchronize(device)
