@@ -902,9 +902,8 @@ allreduce_ring_phased_kernel(GbTeam tm, GbArgs a) {
 // to the output.  A GPU then receives and sends one chunk's worth of data per chunk instead of
 // 2 (world - 1) / world: half the traffic of the two-shot exchange over peer memory.  Every
 // element is reduced by exactly one rank, so all ranks end with identical bits; the order of
-// the addends is the switch's.  Region: `sym` / `mc` + off_a, two halves of len_a bytes that
-// alternate with the chunk index (a peer may still be reading the half of chunk c while chunk
-// c + 1 is written).
+// the addends is the switch's.  Region: `sym` / `mc` + off_a, three buffers of len_a bytes used in
+// turn by the chunks.
 template <typename T> struct Multimem;
 template <> struct Multimem<float> {
     static __device__ __forceinline__ uint4 load_sum(const char* mc) {
@@ -942,34 +941,55 @@ allreduce_nvls_kernel(GbTeam tm, GbArgs a) {
     constexpr int V = Vec<T>::N;
     const char* in = static_cast<const char*>(a.in);
     char* out = static_cast<char*>(a.out);
-    const GbLane L = gb_lane_all(tm.ld_mode);
     const size_t total = a.n * sizeof(T);
     const size_t chunk = a.chunk * sizeof(T);              // a multiple of 16 * world
     const long nchunks = (long)((total + chunk - 1) / chunk);
-    for (long c = 0; c < nchunks; ++c) {
+    // Software pipeline over three buffers, one barrier per iteration: iteration i copies
+    // chunk i into the own buffer, reduces chunk i - 1 through the switch and copies chunk
+    // i - 2 out.  The first `a.k` blocks do the switch step (link-bound: few SMs saturate it),
+    // the others the two local copies, so the steps of an iteration run side by side.
+    const int reducers = a.k > 0 && a.k < (int)gridDim.x ? a.k : (int)gridDim.x;
+    const bool split = reducers < (int)gridDim.x;
+    const bool do_reduce = !split || (int)blockIdx.x < reducers;
+    const bool do_copy = !split || (int)blockIdx.x >= reducers;
+    const GbLane L = !split ? gb_lane_all(tm.ld_mode)
+                   : do_reduce ? gb_lane_blocks(0, reducers, tm.ld_mode)
+                               : gb_lane_blocks(reducers, (int)gridDim.x - reducers, tm.ld_mode);
+    auto len_of = [&](long c) {
         const size_t c0 = (size_t)c * chunk;
-        const size_t len = total - c0 < chunk ? total - c0 : chunk;
-        const size_t padded = round_up(len, 16 * (size_t)tm.world);
-        char* mine = a.sym + a.off_a + (size_t)(c & 1) * a.len_a;
-        char* everyone = a.mc + a.off_a + (size_t)(c & 1) * a.len_a;
-        gb_copy_bytes(L, mine, in + c0, len, false);
-        zero_range(L, mine, len, padded);
-        if (!gb_sync_all(tm, (unsigned)(c < 3 ? 2 * c : 6), c == 0)) return;
-        const size_t slice = padded / (size_t)tm.world;    // a multiple of 16
-        const size_t s0 = (size_t)tm.rank * slice;
-        const size_t nvec = slice >> 4;
-        for (size_t v = L.tid; v < nvec; v += L.nth) {
-            Vec<T> r;
-            r.u = Multimem<T>::load_sum(everyone + s0 + (v << 4));
-            if (a.divide > 0) {
-                #pragma unroll
-                for (int j = 0; j < V; ++j)
-                    r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
-            }
-            multimem_store(everyone + s0 + (v << 4), r.u);
+        return total - c0 < chunk ? total - c0 : chunk;
+    };
+    for (long i = 0; i < nchunks + 2; ++i) {
+        if (do_copy && i < nchunks) {                       // copy chunk i in
+            const size_t len = len_of(i);
+            char* mine = a.sym + a.off_a + (size_t)(i % 3) * a.len_a;
+            gb_copy_bytes(L, mine, in + (size_t)i * chunk, len, false);
+            zero_range(L, mine, len, round_up(len, 16 * (size_t)tm.world));
         }
-        if (!gb_sync_all(tm, (unsigned)(c < 3 ? 2 * c + 1 : 7), false)) return;
-        gb_copy_bytes(L, out + c0, mine, len, true);
+        if (do_reduce && i >= 1 && i - 1 < nchunks) {       // reduce chunk i - 1 in the switch
+            const long c = i - 1;
+            const size_t padded = round_up(len_of(c), 16 * (size_t)tm.world);
+            char* everyone = a.mc + a.off_a + (size_t)(c % 3) * a.len_a;
+            const size_t slice = padded / (size_t)tm.world;    // a multiple of 16
+            const size_t s0 = (size_t)tm.rank * slice;
+            const size_t nvec = slice >> 4;
+            for (size_t v = L.tid; v < nvec; v += L.nth) {
+                Vec<T> r;
+                r.u = Multimem<T>::load_sum(everyone + s0 + (v << 4));
+                if (a.divide > 0) {
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
+                }
+                multimem_store(everyone + s0 + (v << 4), r.u);
+            }
+        }
+        if (do_copy && i >= 2) {                            // copy chunk i - 2 out
+            const long c = i - 2;
+            gb_copy_bytes(L, out + (size_t)c * chunk,
+                          a.sym + a.off_a + (size_t)(c % 3) * a.len_a, len_of(c), true);
+        }
+        if (i + 1 < nchunks + 2 && !gb_sync_all(tm, (unsigned)(i < 7 ? i : 7), i == 0)) return;
     }
 }
 

@@ -84,7 +84,8 @@ class Fabric:
         # Grids of the copy-shaped collectives.  With the bulk-copy ring 16 CTAs already run a
         # link at 640-680 GB/s (measured), so all-gather and broadcast take few SMs and leave
         # the rest to the compute they overlap with; reduce-scatter also reduces locally.
-        self.nvls = None        # (tensor, handle, local pointer, multicast pointer, bytes per half)
+        self.nvls = None        # (tensor, handle, local pointer, multicast pointer, bytes per buffer)
+        self.nvls_reducers = int(os.environ.get("GPUBRIDGE_NVLS_REDUCERS", "48"))
         self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "32"))
         self.overlap_blocks = int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
         self.scatter_blocks = int(os.environ.get("GPUBRIDGE_SCATTER_BLOCKS", "64"))
@@ -200,7 +201,7 @@ class Fabric:
             return False
         try:
             import torch.distributed._symmetric_memory as symm
-            nbytes = nbytes or _config.size_setting("GPUBRIDGE_NVLS_BYTES", 128 * MIB, multiple=4096)
+            nbytes = nbytes or _config.size_setting("GPUBRIDGE_NVLS_BYTES", 192 * MIB, multiple=4096)
             buffer = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
             handle = symm.rendezvous(buffer, group)
             multicast = int(getattr(handle, "multicast_ptr", 0) or 0)
@@ -208,8 +209,8 @@ class Fabric:
             return False
         if multicast == 0:
             return False
-        half = _align_down(nbytes // 2, 16 * self.world * 256)
-        self.nvls = (buffer, handle, buffer.data_ptr(), multicast, half)
+        third = _align_down(nbytes // 3, 16 * self.world * 256)
+        self.nvls = (buffer, handle, buffer.data_ptr(), multicast, third)
         return True
 
     # -- health --------------------------------------------------------------------------------------
@@ -283,12 +284,18 @@ class Fabric:
                     self._launch_reduce(0, tensor.dtype, op, 0, args, self._grid(nbytes, 32))
                 elif (self.nvls is not None and op == "sum" and compression is None
                       and tensor.dtype in NVLS_DTYPES and mode != "chunked"):
-                    _, _, local, multicast, half = self.nvls
+                    _, _, local, multicast, third = self.nvls
                     esize = tensor.element_size()
                     args.sym, args.mc = local, multicast
-                    args.off_a, args.len_a = 0, half
-                    args.chunk = _align_down(half, 16 * self.world) // esize
-                    self._launch_reduce(5, tensor.dtype, op, 0, args, self._grid(nbytes))
+                    args.off_a, args.len_a = 0, third
+                    # chunks small enough that the three-stage pipeline fills: at least four
+                    chunk = min(third, max(1 << 20, -(-nbytes // 4)))
+                    args.chunk = _align_up(chunk, 16 * self.world * 16) // esize
+                    if args.chunk * esize > third:
+                        args.chunk = _align_down(third, 16 * self.world * 16) // esize
+                    grid = self._grid(nbytes)
+                    args.k = self.nvls_reducers if grid >= 2 * self.nvls_reducers else 0
+                    self._launch_reduce(5, tensor.dtype, op, 0, args, grid)
                 else:
                     self._hier(tensor, args, op, compression, chunk_bytes)
         finally:
