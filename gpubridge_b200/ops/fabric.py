@@ -125,7 +125,10 @@ class Fabric:
         budget = self.ws_bytes - FLAG_BYTES
         cursor = FLAG_BYTES
         # one-shot: [2][world] slots
-        self.oneshot_slot = ONESHOT_MAX
+        # One-shot moves (world - 1) bytes per byte against the pipelined kernel's
+        # 2 (world - 1) / world, but needs one barrier instead of three or more: it wins up to
+        # about 16 MiB / world (measured crossovers: 4-8 MiB at 2 GPUs, 1-2 MiB at 8).
+        self.oneshot_slot = max(ONESHOT_MAX, min(8 * ONESHOT_MAX, 16 * ONESHOT_MAX // max(1, self.world)))
         self.off_oneshot, self.len_oneshot = cursor, self.world * self.oneshot_slot
         cursor += 2 * self.len_oneshot
         rest = budget - 2 * self.len_oneshot
