@@ -96,3 +96,22 @@ def test_numerical_gate_software_only(tmp_path):
     broken = [dict(r, passed=False) if r["control"] == "none" and r["rank"] == 2 else r
               for r in records]
     assert not gate.verdict(broken)["passed"]
+
+
+def test_preflight_two_sides_on_one_machine(tmp_path):
+    """Master and worker on this machine: interfaces listed, a pair chosen both ways, the Gloo
+    check passes, both records written."""
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    base = [sys.executable, "-m", "gpubridge_b200.kit.preflight", "--master-addr", "127.0.0.1",
+            "--port", "29726", "--bandwidth-seconds", "0.2", "--out", str(tmp_path)]
+    master = subprocess.Popen(base + ["--role", "master"], env=env, cwd=ROOT,
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    worker = subprocess.run(base + ["--role", "worker"], env=env, cwd=ROOT, capture_output=True,
+                            text=True, timeout=120)
+    out, err = master.communicate(timeout=120)
+    assert worker.returncode == 0, worker.stderr[-2000:]
+    assert master.returncode == 0, err[-2000:]
+    for role in ("master", "worker"):
+        record = json.loads((tmp_path / f"preflight-{role}.json").read_text())
+        assert record["ok"] and record["checks"]["gloo"] == "ok"
+        assert record["chosen_ifname"] and record["bandwidth"]["out_MBps"] > 0
