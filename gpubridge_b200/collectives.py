@@ -32,9 +32,21 @@ _OP_NAMES = ((ReduceOp.SUM, "sum"), (ReduceOp.AVG, "avg"), (ReduceOp.MAX, "max")
 REDUCE_OPS = dict(_OP_NAMES)
 
 
+_OP_FAST: dict = {"sum": "sum", "avg": "avg", "max": "max", "min": "min"}
+for _known, _name in _OP_NAMES:
+    try:
+        _OP_FAST[_known] = _name          # the enum members hash; a ReduceOp(...) instance may not
+    except TypeError:
+        pass
+
+
 def _op_name(op, fn: str) -> str:
-    if isinstance(op, str) and op in ("sum", "avg", "max", "min"):
-        return op
+    try:
+        fast = _OP_FAST.get(op)
+    except TypeError:
+        fast = None
+    if fast is not None:
+        return fast
     for known, name in _OP_NAMES:
         try:
             if op == known:
