@@ -1,0 +1,77 @@
+"""Single-process environment probe: what this machine offers before any job starts.
+
+    python -m gpubridge_b200.kit.probe --out results/probe [--allow-no-gpu]
+
+Stages, each recorded in ``probe.json``: GPUs visible to PyTorch; every GPU is a Blackwell
+part the native library is built for (compute capability 10.x); the native library exists
+(or builds) and loads; its struct layouts match the bindings; the import resolves to this
+checkout; every pair of GPUs can address each other's memory (what the fused kernels need).
+A failed stage prints one line on stderr and the exit code is 1.  Same role as the
+reference's ``scripts/gpu/probe.py``.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+from pathlib import Path
+
+from gpubridge_b200.kit import Journal
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--out", type=Path, required=True)
+    ap.add_argument("--allow-no-gpu", action="store_true")
+    args = ap.parse_args(argv)
+    journal = Journal(args.out / "probe.json", "gpubridge_b200.kit.probe", hang_dump_seconds=0)
+    env = journal.data["environment"]
+    count = env["device_count"]
+
+    def fail(entry, message):
+        entry["ok"] = False
+        entry["error"] = message
+        print(f"probe: {entry['name']}: {message}", file=sys.stderr)
+
+    with journal.stage("gpus_visible") as e:
+        e["device_count"] = count
+        if count == 0 and not args.allow_no_gpu:
+            fail(e, "no GPU visible to PyTorch (check the GPU request and the driver)")
+    with journal.stage("blackwell") as e:
+        other = [d for d in env["devices"] if d and not d["capability"].startswith("10.")]
+        e["devices"] = [d["name"] for d in env["devices"] if d]
+        if other:
+            fail(e, f"the native library targets sm_100a; found {[d['name'] for d in other]}")
+    with journal.stage("native_library") as e:
+        try:
+            from gpubridge_b200.ops import _build, _lib
+            e["path"] = _build.LIB
+            e["prebuilt"] = _lib.available()
+            if count or _lib.available():
+                handle = _lib.lib()
+                e["sizeof"] = {"team": handle.gb_sizeof_team(), "args": handle.gb_sizeof_args(),
+                               "ctrl": handle.gb_sizeof_ctrl()}
+            else:
+                e["skipped"] = "no GPU and no built library"
+        except Exception as exc:  # noqa: BLE001
+            fail(e, f"{type(exc).__name__}: {exc}")
+    with journal.stage("import") as e:
+        import gpubridge_b200
+        here = Path(__file__).resolve().parents[1]
+        e["imported_from"] = str(Path(gpubridge_b200.__file__).resolve().parent)
+        if Path(gpubridge_b200.__file__).resolve().parent != here:
+            fail(e, f"import gpubridge_b200 resolved outside this checkout ({here})")
+    with journal.stage("peer_access") as e:
+        if count >= 2:
+            import torch
+            blocked = [(a, b) for a in range(count) for b in range(count)
+                       if a != b and not torch.cuda.can_device_access_peer(a, b)]
+            e["pairs_checked"] = count * (count - 1)
+            if blocked:
+                fail(e, f"GPU pairs without peer access: {blocked[:8]} - the fused kernels need it")
+        else:
+            e["skipped"] = "fewer than two GPUs"
+    return journal.close()
+
+
+if __name__ == "__main__":
+    sys.exit(main())

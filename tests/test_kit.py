@@ -115,3 +115,14 @@ def test_preflight_two_sides_on_one_machine(tmp_path):
         record = json.loads((tmp_path / f"preflight-{role}.json").read_text())
         assert record["ok"] and record["checks"]["gloo"] == "ok"
         assert record["chosen_ifname"] and record["bandwidth"]["out_MBps"] > 0
+
+
+def test_probe_without_gpu(tmp_path):
+    from gpubridge_b200.kit import probe
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("the CPU form of the probe")
+    assert probe.main(["--out", str(tmp_path), "--allow-no-gpu"]) == 0
+    assert probe.main(["--out", str(tmp_path / "strict")]) == 1       # no GPU is a failure by default
+    record = json.loads((tmp_path / "strict" / "probe.json").read_text())
+    assert record["stages"][0]["name"] == "gpus_visible" and record["stages"][0]["ok"] is False
