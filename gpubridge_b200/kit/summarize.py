@@ -87,6 +87,36 @@ def summarize(directory: Path, partial: bool = False) -> tuple[dict[str, Any], s
     return summary, "\n".join(lines) + "\n"
 
 
+def summarize_scaling(directory: Path) -> tuple[dict[str, Any], str]:
+    """Weak-scaling table from ``train-n<N>.json`` records (examples/train_synthetic.py)."""
+    runs = {}
+    for path in directory.glob("train-n*.json"):
+        record = json.loads(path.read_text())
+        runs[record["world_size"]] = record
+    base = runs.get(1, {}).get("samples_per_sec")
+    rows = []
+    for n, record in sorted(runs.items()):
+        rate = record.get("samples_per_sec")
+        rows.append({"gpus": n, "samples_per_sec": rate,
+                     "efficiency": rate / (n * base) if base and rate else None,
+                     "step_ms_median": record.get("step_ms_median"),
+                     "params_in_sync": record.get("params_in_sync"),
+                     "split_test": (record.get("run") or {}).get("split_test")})
+    split = next((r["split_test"] for r in rows if r["split_test"]), None)
+    ok = bool(rows) and all(r["params_in_sync"] for r in rows)
+    lines = [f"# {directory.name}: scaling", ""]
+    if split:
+        lines += [BANNER, ""]
+    lines += ["Weak scaling: fixed batch per GPU; efficiency = samples/s on N GPUs / (N x samples/s "
+              "on 1 GPU).", "", "| GPUs | samples/s | efficiency | median step (ms) | parameters in sync |",
+              "| --- | --- | --- | --- | --- |"]
+    for r in rows:
+        eff = f"{r['efficiency']:.2f}" if r["efficiency"] is not None else "-"
+        lines.append(f"| {r['gpus']} | {r['samples_per_sec']} | {eff} | {r['step_ms_median']} | "
+                     f"{r['params_in_sync']} |")
+    return {"directory": str(directory), "ok": ok, "split_test": split, "rows": rows}, "\n".join(lines) + "\n"
+
+
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     partial = "--partial" in argv
@@ -96,7 +126,10 @@ def main(argv=None) -> int:
         return 2
     failed = False
     for d in dirs:
-        summary, text = summarize(d, partial)
+        if any(d.glob("train-n*.json")):
+            summary, text = summarize_scaling(d)
+        else:
+            summary, text = summarize(d, partial)
         write_json(d / "summary.json", summary)
         (d / "summary.md").write_text(text)
         print(text)
