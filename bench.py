@@ -1,6 +1,6 @@
 """Flagship benchmark: DDP training throughput (tokens/s) of the GPT-2-small shaped decoder.
 
-Config (BASELINE.json, config 2): 12 layers, d_model 768, 12 heads, MLP 3072, GELU,
+Model: GPT-2 small, 12 layers, d_model 768, 12 heads, MLP 3072, GELU,
 LayerNorm, vocabulary 50257, sequence 1024, micro-batch 8 per GPU, bf16 autocast, AdamW;
 weights N(0, 0.02) random init, token ids uniform from seed 0 (synthetic data: there is no
 network for datasets or checkpoints).  With N >= 2 GPUs the ranks are split into two islands

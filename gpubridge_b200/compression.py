@@ -13,7 +13,7 @@ Two payload formats:
 ``ref``   the reference's, bit for bit: 256 values per block, power-of-two scale
           (smallest 2^k with amax/2^k <= 448, k <= 119, 0 for an all-zero block);
           payload = fp32 scales, then one code byte per value, padded to 4 bytes.
-``b200``  128 values per block, fp32 scale ``amax/448`` (the BASELINE configuration);
+``b200``  128 values per block, fp32 scale ``amax/448`` (the format of the HSDP benchmark);
           same layout with 128-value blocks.  Encoding multiplies by ``448/amax``.
 
 Per-quantisation error bounds (the numerical gate): bf16 ``2^-8 |v|``; fp8

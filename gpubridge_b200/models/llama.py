@@ -1,7 +1,7 @@
 """Llama-style decoder: RMSNorm, rotary positions, grouped-query attention, SwiGLU.
 
 The FSDP2 / HSDP benchmark models.  Named shapes: the reference's ``llama-tiny/125m/350m/1b``
-(scripts/gpu/llama.py:49-58) plus the two BASELINE configurations - ``llama-1.3b`` (24 layers,
+(scripts/gpu/llama.py:49-58) plus the two large benchmark shapes - ``llama-1.3b`` (24 layers,
 d_model 2048, 16 heads, FFN 5632, vocabulary 32000) and ``llama3-8b`` (32 layers, d_model 4096,
 32 query / 8 KV heads, FFN 14336, vocabulary 128256).  Weights are N(0, 0.02) from a CPU
 generator with a fixed seed, so every rank (and a single-process oracle) builds the same model.
