@@ -21,6 +21,7 @@ collective.
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 import os
 import threading
 import time
@@ -52,6 +53,54 @@ def _align_down(value: int, multiple: int) -> int:
 
 def _align_up(value: int, multiple: int) -> int:
     return -(-value // multiple) * multiple
+
+
+@dataclasses.dataclass(frozen=True)
+class HierPlan:
+    channels: int
+    grid: int
+    stripe: int          # elements per stripe of a chunk (a multiple of 256)
+    nchunks: int
+    len_a: int           # bytes of one buffer of each region, per channel
+    len_b: int
+    len_c: int
+
+
+def plan_hier(n: int, esize: int, *, k: int, m_max: int, n_islands: int, len_ha: int, len_hb: int,
+              len_hc: int, grid: int, chunk_bytes: int | None = None,
+              force_channels: int | None = None, force_chunks: int | None = None) -> HierPlan:
+    """Channels, chunking and buffer sizes of one hierarchical all-reduce.
+
+    Pure arithmetic on values every rank of the team shares (never this rank's own island
+    size or position): all ranks must come out with the same plan, or their stripes do not
+    line up.  Every channel owns two buffers of each region; a stripe fits the smallest slot
+    (``m_max`` slots in region A, ``n_islands`` in region B, one in region C)."""
+    nbytes = n * esize
+    # Channels: independent pipelines that hide each other's barriers and local phases.
+    # One for small tensors (a barrier costs more than the data), up to four for large.
+    channels = force_channels or (1 if nbytes < (4 << 20) else 2 if nbytes < (32 << 20) else 4)
+    channels = max(1, min(channels, grid // 8 or 1, 8))
+    grid = max(channels, grid // channels * channels)
+    len_a = len_ha // channels // 4096 * 4096
+    len_b = len_hb // channels // 4096 * 4096
+    len_c = len_hc // channels // 4096 * 4096
+    slot = min(len_a // m_max, len_b // n_islands, len_c)
+    stripe_cap = _align_down(slot // esize, 256)
+    if stripe_cap < 256:
+        raise RuntimeError("the fabric workspace is too small for this team; raise "
+                           f"{_config.FABRIC_BYTES_ENV}")
+    if chunk_bytes:
+        want = max(256, chunk_bytes // esize // k)
+    else:
+        # per channel: T(c) = (c + depth) * (barrier + link time / c) is least at
+        # c = sqrt(depth * link time / barrier)
+        share = max((m_max - 1) / m_max, (n_islands - 1) / k if n_islands > 1 else 0.0)
+        depth = 3 if n_islands > 1 else 2
+        link_s = nbytes / channels * share / LINK_GBS
+        chunks = force_chunks or max(1, round((depth * link_s / BARRIER_S) ** 0.5))
+        want = -(-n // (chunks * channels * k))
+    stripe = min(stripe_cap, _align_up(max(1, min(want, -(-n // k))), 256))
+    return HierPlan(channels, grid, stripe, -(-n // (stripe * k)), len_a, len_b, len_c)
 
 
 class FabricError(RuntimeError):
@@ -305,46 +354,23 @@ class Fabric:
             self._end(current)
 
     def _hier(self, tensor, args, op, compression, chunk_bytes) -> None:
-        esize, n, k = tensor.element_size(), tensor.numel(), self.k
-        nbytes = tensor.nbytes
-        grid = self._grid(nbytes * 2)
-        # Channels: independent pipelines that hide each other's barriers and local phases.
-        # One for small tensors (a barrier costs more than the data), up to four for large.
-        channels = self.force_channels or (1 if nbytes < (4 << 20) else 2 if nbytes < (32 << 20) else 4)
-        channels = max(1, min(channels, grid // 8 or 1, 8))
-        grid = grid // channels * channels
-        # every channel owns two buffers of each region; a stripe must fit the smallest slot
-        len_a = self.len_ha // channels // 4096 * 4096
-        len_b = self.len_hb // channels // 4096 * 4096
-        len_c = self.len_hc // channels // 4096 * 4096
-        slot = min(len_a // self.m_max, len_b // self.n_islands, len_c)
-        stripe_cap = _align_down(slot // esize, 256)
-        if chunk_bytes:
-            want = max(256, chunk_bytes // esize // k)
-        else:
-            # per channel: T(c) = (c + depth) * (barrier + link time / c) is least at
-            # c = sqrt(depth * link time / barrier)
-            # (the plan must come out the same on every rank: use the largest island)
-            m = self.m_max
-            share = max((m - 1) / m, (self.n_islands - 1) / k if self.n_islands > 1 else 0.0)
-            depth = 3 if self.n_islands > 1 else 2
-            link_s = nbytes / channels * share / LINK_GBS
-            chunks = self.force_chunks or max(1, round((depth * link_s / BARRIER_S) ** 0.5))
-            want = -(-n // (chunks * channels * k))
-        stripe = min(stripe_cap, _align_up(max(1, min(want, -(-n // k))), 256))
-        args.stripe, args.k, args.chunk = stripe, k, stripe * k
-        args.off_a, args.len_a = self.off_ha, len_a
-        args.off_b, args.len_b = self.off_hb, len_b
-        args.off_c, args.len_c = self.off_hc, len_c
-        args.role_a = channels
+        plan = plan_hier(tensor.numel(), tensor.element_size(), k=self.k, m_max=self.m_max,
+                         n_islands=self.n_islands, len_ha=self.len_ha, len_hb=self.len_hb,
+                         len_hc=self.len_hc, grid=self._grid(tensor.nbytes * 2),
+                         chunk_bytes=chunk_bytes, force_channels=self.force_channels,
+                         force_chunks=self.force_chunks)
+        args.stripe, args.k, args.chunk = plan.stripe, self.k, plan.stripe * self.k
+        args.off_a, args.len_a = self.off_ha, plan.len_a
+        args.off_b, args.len_b = self.off_hb, plan.len_b
+        args.off_c, args.len_c = self.off_hc, plan.len_c
+        args.role_a = plan.channels
         codec = 0
-        nchunks = -(-n // (stripe * k))
         if compression is not None:
             codec = _lib.CODECS[tuple(compression)]
-            args.residual = self._residual(tensor, (stripe, k, nchunks, codec)).data_ptr()
+            args.residual = self._residual(tensor, (plan.stripe, self.k, plan.nchunks, codec)).data_ptr()
         aligned = (args.inp | args.out) % 16 == 0
         kind = (4 if self.ring == "phased" else 3) if (self.ring and codec == 0 and aligned) else 1
-        self._launch_reduce(kind, tensor.dtype, op, codec, args, grid)
+        self._launch_reduce(kind, tensor.dtype, op, codec, args, plan.grid)
 
     def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:
         """Error feedback of this rank's stripes of ``tensor``: found by the buffer's address,
