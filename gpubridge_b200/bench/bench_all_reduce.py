@@ -49,19 +49,28 @@ def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5, inner
     ``inner`` > 1 a trial is that many back-to-back calls (what a training step issues), which
     takes the launch and host jitter of a lone call out of small-message latencies."""
     dev = topology.device
+    on_gpu = dev.type == "cuda"
     for _ in range(warmup):
         fn()
-    torch.cuda.synchronize(dev)
+    if on_gpu:
+        torch.cuda.synchronize(dev)
     topology.world_group.barrier()
     times, started = [], time.monotonic()
     for _ in range(trials):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(inner):
-            fn()
-        end.record()
-        end.synchronize()
-        slowest = torch.tensor([start.elapsed_time(end) / inner], dtype=torch.float64)
+        if on_gpu:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(inner):
+                fn()
+            end.record()
+            end.synchronize()
+            took = start.elapsed_time(end)
+        else:                                   # CPU simulation: the host clock
+            t0 = time.perf_counter()
+            for _ in range(inner):
+                fn()
+            took = (time.perf_counter() - t0) * 1e3
+        slowest = torch.tensor([took / inner], dtype=torch.float64)
         topology.world_group.all_reduce(slowest, "max")
         times.append(float(slowest))
         stop = torch.tensor([1.0 if time.monotonic() - started > seconds else 0.0])
@@ -147,9 +156,13 @@ def main(argv=None) -> int:
                         # the fused kernels are timed on the stream they run on, as the async
                         # (DDP / FSDP) path uses them; NCCL is timed on the current stream
                         fused = target != "nccl" and topology.fabric is not None
-                        stream = (topology.fabric.comm_stream if fused
-                                  else torch.cuda.current_stream(topology.device))
-                        with torch.cuda.stream(stream):
+                        if topology.device.type == "cuda":
+                            stream = (topology.fabric.comm_stream if fused
+                                      else torch.cuda.current_stream(topology.device))
+                            with torch.cuda.stream(stream):
+                                ms = time_calls(fn, topology, args.trials, args.seconds,
+                                                inner=args.inner)
+                        else:
                             ms = time_calls(fn, topology, args.trials, args.seconds, inner=args.inner)
                         algbw = moved / (ms * 1e-3) / 1e9
                         row = {"op": op, "dtype": dtype_name, "bytes": moved, "target": target,
@@ -157,6 +170,8 @@ def main(argv=None) -> int:
                                "busbw_gbs": round(algbw * BUS[op](world), 3), "world": world,
                                "islands": [len(i.ranks) for i in topology.layout.islands],
                                "policy": topology.policy_name, "inner": args.inner}
+                        if target.startswith("compression:") and op == "all_reduce":
+                            row.update(compression_check(target, topology, dtype, nbytes))
                         rows.append(row)
                         if rank == 0:
                             print(json.dumps(row), flush=True)
@@ -170,6 +185,36 @@ def main(argv=None) -> int:
     if rank == 0 and args.write_thresholds:
         write_thresholds(rows, args.write_thresholds)
     return 0
+
+
+def compression_check(target: str, topology, dtype, nbytes: int) -> dict:
+    """One compressed all-reduce of fresh data against the fp64 sum: the largest error relative
+    to the largest magnitude of the result, and whether every rank holds identical bits (the
+    reference's ``--compression`` check, scripts/gpu/bench_all_reduce.py:331-379)."""
+    fn_policy = make_target(target, "all_reduce", topology, dtype, nbytes)
+    del fn_policy
+    dev, world = topology.device, topology.world_size
+    n = max(1, nbytes // torch.empty(0, dtype=dtype).element_size())
+    inputs = [torch.randn(n, generator=torch.Generator().manual_seed(99 + r)).to(dtype)
+              for r in range(world)]
+    exact = torch.stack([t.double() for t in inputs]).sum(0)
+    mine = inputs[topology.rank].to(dev)
+    parts = target.split(":")
+    policy = type(topology.policy)(compression=parts[1]) if hasattr(
+        topology.policy, "compression") else topology.policy
+    policy.setup(topology)
+    if len(parts) > 2:
+        policy._fmt = parts[2]
+    policy.all_reduce(mine, topology)
+    if dev.type == "cuda":
+        torch.cuda.synchronize(dev)
+    got = mine.cpu()
+    error = float((got.double() - exact).abs().max() / exact.abs().max().clamp_min(1e-30))
+    bits = got.view(torch.uint8).to(torch.int32)
+    hi, lo = bits.clone(), bits.clone()
+    topology.world_group.all_reduce(hi, "max")
+    topology.world_group.all_reduce(lo, "min")
+    return {"max_rel_error": round(error, 6), "identical_bits": bool(torch.equal(hi, lo))}
 
 
 def write_thresholds(rows: list[dict], path: str) -> None:
