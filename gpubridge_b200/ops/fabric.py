@@ -20,6 +20,7 @@ collective.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import dataclasses
 import os
@@ -121,6 +122,7 @@ class Fabric:
         self.ws, self.ws_bytes, self.ctrl, self.status = ws, ws_bytes, ctrl, status
         self.comm_stream = torch.cuda.Stream(device, priority=-1)
         self.max_blocks = int(os.environ.get("GPUBRIDGE_FABRIC_BLOCKS", "128"))
+        self._caps = threading.local()          # per-thread grid cap, see grid_cap()
         self.algo = _config.algo_setting()
         self._status = (ctypes.c_uint * _lib.STATUS_WORDS).from_address(status)
         self._residuals: dict[tuple, tuple[torch.Tensor, tuple]] = {}
@@ -230,15 +232,10 @@ class Fabric:
         for t in tensors:
             t.record_stream(self.comm_stream)
         # an asynchronous collective runs beside the caller's compute: it takes few SMs
-        full = self.max_blocks
-        self.max_blocks = min(full, self.overlap_blocks)
-        try:
-            with torch.cuda.stream(self.comm_stream):
-                run()
-                done = torch.cuda.Event()
-                done.record(self.comm_stream)
-        finally:
-            self.max_blocks = full
+        with self.grid_cap(self.overlap_blocks), torch.cuda.stream(self.comm_stream):
+            run()
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
         return done
 
     # -- in-switch reduction ------------------------------------------------------------------------
@@ -289,7 +286,19 @@ class Fabric:
     # -- launches --------------------------------------------------------------------------------------
     def _grid(self, nbytes: int, cap: int | None = None) -> int:
         blocks = -(-nbytes // (THREADS * 16 * 4))
-        return max(1, min(cap or self.max_blocks, blocks))
+        limit = min(cap or self.max_blocks, self.max_blocks, getattr(self._caps, "value", 1 << 30))
+        return max(1, min(limit, blocks))
+
+    @contextlib.contextmanager
+    def grid_cap(self, blocks: int | None):
+        """Launches of the calling thread inside the block use at most ``blocks`` CTAs (a
+        collective that runs beside compute should leave it the SMs)."""
+        before = getattr(self._caps, "value", 1 << 30)
+        self._caps.value = min(before, blocks) if blocks else before
+        try:
+            yield
+        finally:
+            self._caps.value = before
 
     def _launch_reduce(self, kind: int, tensor_dtype, op: str, codec: int, args, grid: int) -> None:
         stream = torch.cuda.current_stream(self.device).cuda_stream

@@ -126,14 +126,9 @@ class DataParallelTrainer:
             # the last bucket has nothing left to overlap with and takes the full grid.
             comm = fabric.comm_stream
             comm.wait_stream(torch.cuda.current_stream(self.device))
-            full = fabric.max_blocks
-            fabric.max_blocks = full if tail else min(full, self.overlap_blocks)
-            try:
-                with torch.cuda.stream(comm):
-                    topology.policy.select_policy(grads.nbytes).all_reduce(
-                        grads, topology, divide=self.world)
-            finally:
-                fabric.max_blocks = full
+            with fabric.grid_cap(None if tail else self.overlap_blocks), torch.cuda.stream(comm):
+                topology.policy.select_policy(grads.nbytes).all_reduce(
+                    grads, topology, divide=self.world)
             self.launches += 1
         else:
             from gpubridge_b200.collectives import all_reduce
