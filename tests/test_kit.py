@@ -126,3 +126,23 @@ def test_probe_without_gpu(tmp_path):
     assert probe.main(["--out", str(tmp_path / "strict")]) == 1       # no GPU is a failure by default
     record = json.loads((tmp_path / "strict" / "probe.json").read_text())
     assert record["stages"][0]["name"] == "gpus_visible" and record["stages"][0]["ok"] is False
+
+
+def test_runbook_plan_and_one_step(tmp_path):
+    from gpubridge_b200.kit import runbook
+    steps = runbook.plan(tmp_path, 8, cpu=False)
+    names = [s["name"] for s in steps]
+    assert names[0] == "probe" and "check-3+5" in names and "streams" in names
+    assert "gate-bridged" in names and "scaling-8" in names and names[-1] == "scaling-summary"
+    assert runbook.main(["--out", str(tmp_path), "--gpus", "2", "--cpu", "--dry-run"]) == 0
+    # one real step, and a failing one is recorded without stopping the run
+    os.environ["GPUBRIDGE_VENDOR"] = "nvidia"
+    try:
+        assert runbook.main(["--out", str(tmp_path / "run"), "--gpus", "2", "--cpu", "--only", "probe"]) == 0
+    finally:
+        os.environ.pop("GPUBRIDGE_VENDOR", None)
+    rows = [json.loads(l) for l in (tmp_path / "run" / "steps.jsonl").read_text().splitlines()]
+    assert rows == [dict(rows[0], step="probe", ok=True)]
+    bad = runbook.run_step({"name": "boom", "cmd": [sys.executable, "-c", "raise SystemExit(3)"],
+                            "env": {}, "expect": None, "timeout": None}, tmp_path / "run", 30)
+    assert bad["ok"] is False and bad["exit_code"] == 3
