@@ -380,6 +380,17 @@ class GpubridgeProcessGroup(dist.ProcessGroup):
             joined.append(torch.cat([s.reshape(-1) for s in slices]))
         return self.reduce_scatter_tensor_coalesced(list(outputs), joined, opts)
 
+    # the names later torch releases give the same entry points (reference:
+    # docs/TORCH_BACKEND.md:169-179)
+    def all_gather_single(self, output, input, opts=None):  # noqa: A002, D102
+        return self._allgather_base(output, input, opts)
+
+    def all_gather_single_coalesced(self, outputs, inputs, opts=None):  # noqa: D102
+        return self.allgather_into_tensor_coalesced(outputs, inputs, opts)
+
+    def reduce_scatter_single(self, output, input, opts=None):  # noqa: A002, D102
+        return self._reduce_scatter_base(output, input, opts)
+
     def barrier(self, opts=None):  # noqa: D102
         topology = self._topology()
         return self._run("barrier", [], [
