@@ -31,7 +31,6 @@ import statistics
 import subprocess
 import sys
 import threading
-import time
 import warnings
 
 ROOT = os.path.dirname(os.path.abspath(__file__))

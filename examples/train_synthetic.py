@@ -15,8 +15,6 @@ differed.  ``python -m gpubridge_b200.kit.summarize DIR`` turns a directory of
 from __future__ import annotations
 
 import argparse
-import json
-import os
 import statistics
 import sys
 import time

@@ -19,14 +19,12 @@ from __future__ import annotations
 
 import argparse
 import json
-import os
 import statistics
 import sys
 import time
 import warnings
 
 import torch
-import torch.distributed as dist
 
 import gpubridge_b200 as gb
 from gpubridge_b200 import policies as _policies

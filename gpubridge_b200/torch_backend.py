@@ -46,7 +46,6 @@ from gpubridge_b200 import p2p as _p2p
 from gpubridge_b200 import topology as _topology
 from gpubridge_b200 import work as _work
 from gpubridge_b200.config import BRIDGE_ENV, POLICY_ENV, is_simulated
-from gpubridge_b200.groups import make_comm
 from gpubridge_b200.policies import DEFAULT_POLICY, resolve_policy
 from gpubridge_b200.transport import (DEFAULT_TRANSPORT, GlooTransport, NvlinkTransport,
                                       resolve_transport)

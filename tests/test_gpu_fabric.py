@@ -2,8 +2,6 @@
 relabelling (``GPUBRIDGE_SPLIT_TEST`` / ``GPUBRIDGE_ISLANDS``), results checked against the
 analytic answer on integer-valued data (exact in any order) and against the PyTorch codec
 for the compressed bridge leg.  Needs at least two GPUs."""
-import os
-
 import pytest
 import torch
 

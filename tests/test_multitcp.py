@@ -70,7 +70,6 @@ def _native_equals_python(members: int):
     import threading
     import time
     from datetime import timedelta
-    from gpubridge_b200 import tagged
     from gpubridge_b200.multitcp import MultiTcpTransport, Worker
 
     def link():
