@@ -232,8 +232,30 @@ def error_bound(mode: str, v: torch.Tensor, fmt: str = "ref") -> torch.Tensor:
 
 # ---- dispatch ------------------------------------------------------------------------------
 
+KERNELS_ENV = "GPUBRIDGE_COMPRESSION_KERNELS"
+
+
+def kernels_setting() -> str:
+    """``auto`` (default): the sm_100a kernels on GPU tensors, PyTorch otherwise; ``native``:
+    the kernels or an error; ``torch``: the PyTorch codec everywhere (the reference's values
+    are auto | triton | torch, compression.py:89 there; ``triton`` is read as ``native``)."""
+    import os
+    value = os.environ.get(KERNELS_ENV, "auto").strip().lower() or "auto"
+    if value == "triton":
+        value = "native"
+    if value not in ("auto", "native", "torch"):
+        raise ValueError(f"{KERNELS_ENV} must be auto, native or torch, got {value!r}")
+    return value
+
+
 def _device_codec(tensor: torch.Tensor):
+    choice = kernels_setting()
+    if choice == "torch":
+        return None
     if tensor.device.type != "cuda":
+        if choice == "native":
+            raise RuntimeError(f"{KERNELS_ENV}=native: the codec kernels need a CUDA tensor, "
+                               f"got one on {tensor.device}")
         return None
     from gpubridge_b200.ops import codec
     return codec

@@ -4,7 +4,8 @@ The worker is ``csrc/gb_tcp.cpp`` inside the library (the reference ships it as 
 with the same C ABI idea: src/gpubridge/multitcp/__init__.py, crate/src/lib.rs).  Settings:
 ``GPUBRIDGE_MULTITCP_STREAMS`` (connections per peer, default 4),
 ``GPUBRIDGE_MULTITCP_CHUNK_BYTES`` (default 4 MiB), ``GPUBRIDGE_MULTITCP_IFADDR`` (the
-local IPv4 address to listen on, default 127.0.0.1 for one box).
+local IPv4 address to listen on) or ``GPUBRIDGE_MULTITCP_IFNAME`` (an interface name, as in
+the reference); default 127.0.0.1 for one box.
 
 ``python -m gpubridge_b200.multitcp info`` prints the protocol version and the settings.
 """
@@ -23,6 +24,25 @@ from gpubridge_b200.transport import register_transport
 STREAMS_ENV = "GPUBRIDGE_MULTITCP_STREAMS"
 CHUNK_ENV = "GPUBRIDGE_MULTITCP_CHUNK_BYTES"
 IFADDR_ENV = "GPUBRIDGE_MULTITCP_IFADDR"
+IFNAME_ENV = "GPUBRIDGE_MULTITCP_IFNAME"          # the reference's way to name the interface
+
+
+def listen_address() -> str:
+    """The local IPv4 address the worker listens on: ``GPUBRIDGE_MULTITCP_IFADDR``, else the
+    first IPv4 address of the interface named by ``GPUBRIDGE_MULTITCP_IFNAME``, else loopback."""
+    address = os.environ.get(IFADDR_ENV, "").strip()
+    if address:
+        return address
+    name = os.environ.get(IFNAME_ENV, "").strip()
+    if name:
+        import socket
+
+        import psutil
+        for entry in psutil.net_if_addrs().get(name, []):
+            if entry.family == socket.AF_INET:
+                return entry.address
+        raise ValueError(f"{IFNAME_ENV}={name}: no such interface with an IPv4 address here")
+    return "127.0.0.1"
 
 
 def _library():
@@ -128,7 +148,7 @@ class MultiTcpTransport(TaggedBridge):
     @classmethod
     def _connect(cls, store, key, members, rank, timeout, deadline):
         index = members.index(rank)
-        host = os.environ.get(IFADDR_ENV, "").strip() or "127.0.0.1"
+        host = listen_address()
         chunk = _config.size_setting(CHUNK_ENV, 4 << 20)
         worker = Worker(index, len(members), streams_setting(), host)
         try:
@@ -153,7 +173,7 @@ def main(argv: list[str]) -> int:
     if command == "info":
         print(json.dumps({"protocol": _library().gb_tcp_protocol(), "streams": streams_setting(),
                           "chunk_bytes": _config.size_setting(CHUNK_ENV, 4 << 20),
-                          "ifaddr": os.environ.get(IFADDR_ENV, "127.0.0.1")}))
+                          "ifaddr": listen_address()}))
         return 0
     print("usage: python -m gpubridge_b200.multitcp [build|info]", file=sys.stderr)
     return 2

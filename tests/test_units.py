@@ -223,3 +223,28 @@ def test_transport_registry():
         transport.resolve_transport("ucx")
     with pytest.raises(TypeError):
         transport.register_transport(int)
+
+
+def test_compression_kernel_setting_and_multitcp_interface(monkeypatch):
+    from gpubridge_b200 import compression as C
+    from gpubridge_b200 import multitcp
+    import torch
+    monkeypatch.setenv("GPUBRIDGE_COMPRESSION_KERNELS", "torch")
+    assert C.kernels_setting() == "torch" and C._device_codec(torch.zeros(1)) is None
+    monkeypatch.setenv("GPUBRIDGE_COMPRESSION_KERNELS", "triton")
+    assert C.kernels_setting() == "native"
+    import pytest
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        C._device_codec(torch.zeros(1))
+    monkeypatch.setenv("GPUBRIDGE_COMPRESSION_KERNELS", "sometimes")
+    with pytest.raises(ValueError):
+        C.kernels_setting()
+    monkeypatch.delenv("GPUBRIDGE_COMPRESSION_KERNELS")
+    monkeypatch.delenv("GPUBRIDGE_MULTITCP_IFADDR", raising=False)
+    monkeypatch.setenv("GPUBRIDGE_MULTITCP_IFNAME", "lo")
+    assert multitcp.listen_address().startswith("127.")
+    monkeypatch.setenv("GPUBRIDGE_MULTITCP_IFNAME", "no-such-interface0")
+    with pytest.raises(ValueError, match="no such interface"):
+        multitcp.listen_address()
+    monkeypatch.setenv("GPUBRIDGE_MULTITCP_IFADDR", "10.1.2.3")
+    assert multitcp.listen_address() == "10.1.2.3"
