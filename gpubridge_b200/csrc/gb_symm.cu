@@ -65,4 +65,10 @@ int gb_memset_async(void* ptr, int value, size_t bytes, cudaStream_t stream) {
     return (int)cudaMemsetAsync(ptr, value, bytes, stream);
 }
 
+// Copy `bytes` of device memory into pinned host memory on `stream` (the barrier timestamps of
+// the last collective, for observers).
+int gb_copy_to_host(void* host, const void* device, size_t bytes, cudaStream_t stream) {
+    return (int)cudaMemcpyAsync(host, device, bytes, cudaMemcpyDeviceToHost, stream);
+}
+
 }  // extern "C"

@@ -34,15 +34,27 @@ class Mark:
     event: "torch.cuda.Event | None" = None
     device_ns: int | None = None
     """A ``globaltimer`` reading taken inside a kernel; set for phases of fused kernels."""
+    source: "tuple[torch.Tensor, int] | None" = None
+    """Where a ``globaltimer`` reading will be once ``event`` has completed: element ``i`` of
+    a pinned host tensor that an asynchronous copy fills (no host wait when the mark is made)."""
 
     def ready(self) -> bool:
         return self.event is None or self.event.query()
 
+    def ns(self) -> int | None:
+        """The device timestamp, if this mark has one (read it only when :meth:`ready`)."""
+        if self.device_ns is not None:
+            return self.device_ns
+        if self.source is not None:
+            return int(self.source[0][self.source[1]])
+        return None
+
 
 def elapsed_ms(start: Mark, end: Mark) -> float:
     """Milliseconds between two ready marks, on the device clock when both have one."""
-    if start.device_ns is not None and end.device_ns is not None:
-        return (end.device_ns - start.device_ns) / 1e6
+    a, b = start.ns(), end.ns()
+    if a is not None and b is not None:
+        return (b - a) / 1e6
     if start.event is not None and end.event is not None:
         return start.event.elapsed_time(end.event)
     return (end.host_ns - start.host_ns) / 1e6
@@ -277,6 +289,22 @@ def device_phases(names: list[str], stamps_ns: list[int]) -> None:
     for i, name in enumerate(names):
         flight.phases.append(Phase(name, Mark(host, None, stamps_ns[i]),
                                    Mark(host, None, stamps_ns[i + 1])))
+
+
+def device_phases_later(names: list[str], stamps: torch.Tensor, event) -> None:
+    """Like :func:`device_phases` for timestamps that an asynchronous copy is still bringing to
+    ``stamps`` (pinned host memory, ``len(names) + 1`` values); ``event`` completes after the
+    copy.  The phases are ready when the event is."""
+    flight = _local.flight
+    if flight is None:
+        return
+    flight.done = (*flight.done, *names)
+    if not flight.watched:
+        return
+    host = time.perf_counter_ns()
+    for i, name in enumerate(names):
+        flight.phases.append(Phase(name, Mark(host, event, None, (stamps, i)),
+                                   Mark(host, event, None, (stamps, i + 1))))
 
 
 def _deliver(record: CollectiveRecord) -> None:

@@ -98,6 +98,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_allgather_gemm.argtypes = [ctypes.POINTER(GbTeam), vp, vp, vp, vp, vp, vp, ctypes.c_uint,
                                     i, i, i, sz, i, i, vp]
     L.gb_allgather_gemm_pair.argtypes = L.gb_allgather_gemm.argtypes
+    L.gb_copy_to_host.argtypes = [vp, vp, sz, vp]
     L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
     L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]
 

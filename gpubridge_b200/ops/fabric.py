@@ -33,6 +33,7 @@ import torch
 from gpubridge_b200._mutation import mutated
 
 from gpubridge_b200 import config as _config
+from gpubridge_b200 import observe as _observe
 from gpubridge_b200 import work as _work
 from gpubridge_b200.ops import _lib
 
@@ -380,6 +381,29 @@ class Fabric:
         aligned = (args.inp | args.out) % 16 == 0
         kind = (4 if self.ring == "phased" else 3) if (self.ring and codec == 0 and aligned) else 1
         self._launch_reduce(kind, tensor.dtype, op, codec, args, plan.grid)
+        if _observe.watching() and not torch.cuda.is_current_stream_capturing():
+            self._report_phases(plan)
+
+    def _report_phases(self, plan: "HierPlan") -> None:
+        """Hand observers the kernel's own timestamps: the barriers between the steps of the
+        first channel (``globaltimer`` values the kernel leaves in its control block), copied
+        to pinned memory behind the kernel - the host does not wait."""
+        bridged = self.n_islands > 1
+        per_channel = -(-plan.nchunks // plan.channels)
+        barriers = min(8, per_channel + (3 if bridged else 2) - 1)
+        if barriers < 2:
+            return
+        if per_channel == 1:
+            names = ["island-reduce", "bridge-reduce"][:barriers - 1]
+        else:
+            names = [f"pipeline-step-{i + 1}" for i in range(barriers - 1)]
+        stamps = torch.zeros(8, dtype=torch.int64).pin_memory()
+        stream = torch.cuda.current_stream(self.device)
+        _lib.check(self.lib.gb_copy_to_host(stamps.data_ptr(), self.ctrl + 32, 64, stream.cuda_stream),
+                   "cudaMemcpyAsync (barrier timestamps)")
+        done = torch.cuda.Event(enable_timing=True)
+        done.record(stream)
+        _observe.device_phases_later(names, stamps, done)
 
     def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:
         """Error feedback of this rank's stripes of ``tensor``: found by the buffer's address,

@@ -154,6 +154,38 @@ def test_all_reduce_through_the_switch(tmp_path):
     print("64 MiB all-reduce, us per call:", out[0])
 
 
+def _observed(rank, topology):
+    """An observer sees the steps inside the fused kernel, timed by the kernel itself."""
+    import gpubridge_b200 as gb
+    records = []
+
+    class Keep(gb.CollectiveObserver):
+        def on_collective(self, record):
+            records.append(record)
+
+    watcher = Keep()
+    gb.add_observer(watcher)
+    try:
+        t = torch.ones(8 << 20, device=topology.device)            # 32 MiB: the pipelined kernel
+        gb.all_reduce(t)
+        torch.cuda.synchronize()
+    finally:
+        gb.remove_observer(watcher)
+    record = records[-1]
+    names = [p.name for p in record.phases]
+    assert names and all(n.startswith(("pipeline-step", "island-reduce", "bridge-reduce")) for n in names)
+    spans = [p.elapsed_ms() for p in record.phases]
+    assert all(p.start.ready() and p.end.ready() for p in record.phases)
+    assert all(0 <= ms < 100 for ms in spans) and sum(spans) > 0, spans
+    return names, spans
+
+
+@needs_two
+def test_observer_sees_the_kernels_steps(tmp_path):
+    out = run_ranks(gpu_ranks(2), _observed, tmp_path, env={"GPUBRIDGE_SPLIT_TEST": "half"}, timeout=120)
+    print("phases inside the fused all-reduce:", out[0])
+
+
 def _compressed(rank, topology, mode, fmt):
     """The fused compressed all-reduce against the PyTorch codec: island sums in member order,
     one quantisation per island (with error feedback over two calls), payloads added in island

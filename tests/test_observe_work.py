@@ -160,3 +160,32 @@ def _reinit(rank, world, path):
 
 def test_destroy_and_init_again(tmp_path):
     run_ranks(TWO_BY_TWO, _reinit, tmp_path, mode="raw")
+
+
+def test_marks_that_arrive_later():
+    """Device timestamps of a fused kernel reach the host by an asynchronous copy: the phases
+    exist at once, are ready when the copy's event is, and read the pinned buffer lazily."""
+    import torch
+    from gpubridge_b200 import observe
+
+    class Event:
+        def __init__(self): self.done = False
+        def query(self): return self.done
+
+    stamps = torch.zeros(3, dtype=torch.int64)
+    event = Event()
+    flight = observe._Flight(1, "all_reduce", "p")
+    flight.watched = True
+    observe._local.flight = flight
+    try:
+        observe.device_phases_later(["island-reduce", "bridge-reduce"], stamps, event)
+    finally:
+        observe._local.flight = None
+    assert [p.name for p in flight.phases] == ["island-reduce", "bridge-reduce"]
+    assert flight.done == ("island-reduce", "bridge-reduce")
+    assert not flight.phases[0].start.ready()
+    stamps.copy_(torch.tensor([1_000_000, 3_500_000, 4_000_000]))      # the copy lands
+    event.done = True
+    assert flight.phases[0].end.ready()
+    assert flight.phases[0].elapsed_ms() == 2.5 and flight.phases[1].elapsed_ms() == 0.5
+    assert observe.Mark(0, None, 7).ns() == 7 and observe.Mark(0).ns() is None
