@@ -248,3 +248,20 @@ def test_compression_kernel_setting_and_multitcp_interface(monkeypatch):
         multitcp.listen_address()
     monkeypatch.setenv("GPUBRIDGE_MULTITCP_IFADDR", "10.1.2.3")
     assert multitcp.listen_address() == "10.1.2.3"
+
+
+def test_utils_clock_summary_and_timing():
+    import torch
+    from gpubridge_b200.utils import clocks, device_time, human_bytes, max_over_ranks
+    lines = ["0, 1920, 1965, 650.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+             "0, 1350, 1965, 990.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+             "garbage", "0, 1400, 1965, 991.0, 0x0, Not Active, Active, Not Active, Not Active"]
+    s = clocks.summarise(lines)
+    assert s["sm_mhz"] == 1400 and s["sm_max_mhz"] == 1965 and s["samples"] == 3
+    assert s["reasons"] == ["hw_thermal_slowdown", "sw_power_cap"] and not clocks.acceptable(s)
+    assert clocks.acceptable(clocks.summarise(lines[:2]))                    # a power cap is kept
+    assert not clocks.acceptable({"sm_mhz": 600.0, "sm_max_mhz": 1965.0, "reasons": []})
+    calls = []
+    ms = device_time(lambda n: calls.append(n), 7, torch.device("cpu"), barrier=lambda: calls.append("b"))
+    assert calls == ["b", 7, "b"] and ms >= 0
+    assert max_over_ranks(3.5) == 3.5 and human_bytes(4 << 20) == "4M" and human_bytes(1000) == "1000"
