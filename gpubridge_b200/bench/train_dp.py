@@ -96,7 +96,11 @@ def main(argv=None) -> int:
     if on_gpu:
         torch.cuda.synchronize(device)
     dist.barrier()
+    sampler = None
     if on_gpu:
+        from gpubridge_b200.utils import ClockSampler
+        sampler = ClockSampler(local)
+        sampler.start()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
     t0 = time.perf_counter()
@@ -108,6 +112,7 @@ def main(argv=None) -> int:
         ms = start.elapsed_time(end)
     else:
         ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop() if sampler is not None else None
     dist.barrier()
     slowest = torch.tensor([ms], dtype=torch.float64, device=device)
     dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
@@ -123,6 +128,7 @@ def main(argv=None) -> int:
             "loss": round(float(loss), 4),
             "compression": os.environ.get("GPUBRIDGE_BRIDGE_COMPRESSION", ""),
             "parameters": sum(p.numel() for p in core.parameters()),
+            "clocks": clocks,
         }), flush=True)
     dist.destroy_process_group()
     return 0
