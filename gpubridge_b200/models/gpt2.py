@@ -14,6 +14,9 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from gpubridge_b200.models.attention import causal_attention
+from gpubridge_b200.ops.layernorm import FusedLayerNorm
+
 
 @dataclass(frozen=True)
 class GPTConfig:
@@ -35,7 +38,7 @@ class Block(nn.Module):
     def __init__(self, c: GPTConfig) -> None:
         super().__init__()
         self.heads = c.heads
-        self.ln1, self.ln2 = nn.LayerNorm(c.width), nn.LayerNorm(c.width)
+        self.ln1, self.ln2 = FusedLayerNorm(c.width), FusedLayerNorm(c.width)
         self.qkv, self.proj = nn.Linear(c.width, 3 * c.width), nn.Linear(c.width, c.width)
         self.fc, self.out = nn.Linear(c.width, c.mlp), nn.Linear(c.mlp, c.width)
 
@@ -43,7 +46,7 @@ class Block(nn.Module):
         b, t, w = x.shape
         qkv = self.qkv(self.ln1(x)).view(b, t, 3, self.heads, w // self.heads)
         q, k, v = (z.transpose(1, 2) for z in qkv.unbind(2))
-        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        y = causal_attention(q, k, v)
         x = x + self.proj(y.transpose(1, 2).reshape(b, t, w))
         return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
 
@@ -56,7 +59,7 @@ class GPT(nn.Module):
         self.tok = nn.Embedding(self.padded_vocab, c.width)
         self.pos = nn.Embedding(c.context, c.width)
         self.blocks = nn.ModuleList(Block(c) for _ in range(c.layers))
-        self.ln = nn.LayerNorm(c.width)
+        self.ln = FusedLayerNorm(c.width)
         self.head = nn.Linear(c.width, self.padded_vocab, bias=False)
         self.head.weight = self.tok.weight          # tied, as in GPT-2
         self.apply(self._init)

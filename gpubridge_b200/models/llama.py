@@ -14,6 +14,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from gpubridge_b200.models.attention import causal_attention
+
 
 @dataclass(frozen=True)
 class LlamaConfig:
@@ -82,8 +84,7 @@ class Block(nn.Module):
         k = self.wk(h).view(b, t, self.kv_heads, self.head_dim).transpose(1, 2)
         v = self.wv(h).view(b, t, self.kv_heads, self.head_dim).transpose(1, 2)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-        y = F.scaled_dot_product_attention(q, k, v, is_causal=True,
-                                           enable_gqa=self.kv_heads != self.heads)
+        y = causal_attention(q, k, v, enable_gqa=self.kv_heads != self.heads)
         x = x + self.wo(y.transpose(1, 2).reshape(b, t, -1))
         h = self.ffn_norm(x)
         return x + self.down(F.silu(self.gate(h)) * self.up(h))

@@ -103,3 +103,42 @@ def test_single_rank_all_reduce_paths(ring):
         team.check()
     finally:
         team.close()
+
+
+@pytest.mark.parametrize("rows,d", [(33, 128), (1000, 768), (4096, 1024), (7, 2048)])
+@pytest.mark.parametrize("case", ["fp32", "autocast", "bf16"])
+def test_fused_layer_norm(rows, d, case):
+    """Forward, dx, dgamma and dbeta against F.layer_norm computed in fp32 from the same inputs."""
+    from gpubridge_b200.ops.layernorm import fused_layer_norm
+    device = torch.device("cuda", 0)
+    torch.manual_seed(rows + d)
+    x = torch.randn(rows, d, device=device) * 2 + 0.5
+    w = torch.randn(d, device=device) * 0.5 + 1
+    b = torch.randn(d, device=device) * 0.1
+    go = torch.randn(rows, d, device=device)
+    if case == "bf16":
+        x = x.to(torch.bfloat16)
+    xr = x.float().clone().requires_grad_(True)
+    wr, br = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    want = torch.nn.functional.layer_norm(xr, (d,), wr, br, 1e-5)
+    xf = x.clone().requires_grad_(True)
+    wf, bf = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    if case == "autocast":
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            got = fused_layer_norm(xf, wf, bf, 1e-5)
+        assert got.dtype == torch.bfloat16
+    else:
+        got = fused_layer_norm(xf, wf, bf, 1e-5)
+        assert got.dtype == x.dtype
+    low = got.dtype == torch.bfloat16
+    grad = go.to(got.dtype)
+    want.backward(grad.float())
+    got.backward(grad)
+    torch.cuda.synchronize()
+    tol = dict(atol=3e-2, rtol=2e-2) if low else dict(atol=2e-5, rtol=2e-5)
+    assert torch.allclose(got.float(), want.detach(), **tol)
+    gtol = dict(atol=5e-2, rtol=3e-2) if case == "bf16" else dict(atol=1e-4, rtol=1e-4)
+    assert torch.allclose(xf.grad.float(), xr.grad, **gtol)
+    scale = max(1.0, rows ** 0.5)
+    assert torch.allclose(wf.grad, wr.grad, atol=2e-4 * scale, rtol=2e-4)
+    assert torch.allclose(bf.grad, br.grad, atol=2e-4 * scale, rtol=2e-4)
