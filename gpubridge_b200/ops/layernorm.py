@@ -3,7 +3,7 @@ dtype the consumer wants, dx and the gamma / beta partial sums in one backward p
 
 ``FusedLayerNorm`` is an ``nn.LayerNorm`` (same parameters, same state dict) whose forward uses
 the kernels for CUDA inputs of width 128 k (k = 1..8, 10, 12, 16) and ``F.layer_norm`` otherwise;
-``GPUBRIDGE_FUSED_NORM=1`` switches the kernels on (off by default).  Under ``torch.autocast`` the output is the
+``GPUBRIDGE_FUSED_NORM=0`` switches the kernels off.  Under ``torch.autocast`` the output is the
 autocast dtype: ``F.layer_norm`` would produce fp32 and the next Linear would cast it, which is
 the same rounding done by one more kernel.
 """
@@ -23,7 +23,7 @@ _CODES = {torch.float32: 0, torch.bfloat16: 1}
 
 
 def enabled() -> bool:
-    return os.environ.get("GPUBRIDGE_FUSED_NORM", "0") == "1"
+    return os.environ.get("GPUBRIDGE_FUSED_NORM", "1") != "0"
 
 
 def usable(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | None) -> bool:
