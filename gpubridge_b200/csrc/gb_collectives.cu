@@ -744,7 +744,12 @@ allreduce_ring_kernel(GbTeam tm, GbArgs a) {
     }
 }
 
-// ---- the same kernel with one ring run per step (kept for A/B measurements) ---------------------
+// ---- the same kernel with one ring run per step ---------------------------------------------------
+// With more than two islands the bridge can run "two-shot" (a.role_b != 0): owner j of island g
+// sends sub-stripe h of its island result only to owner j of island h, which adds the islands'
+// sub-stripes in leader order and sends the finished sub-stripe to owner j of every island.
+// That moves 2 (I - 1) / I stripes per owner instead of I - 1, with the same number of steps
+// and barriers and the same order of additions.
 // Step B: fold the island's slots in member order, round to T, store.
 template <typename T, int OP>
 __device__ __forceinline__ bool island_reduce_ring(GbRing& R, const GbTeam& tm, const GbArgs& a,
@@ -779,6 +784,12 @@ __device__ __forceinline__ bool island_reduce_ring(GbRing& R, const GbTeam& tm, 
                             r.e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(r.e[j]), a.divide));
                     }
                     gb_st16(tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c + at, r.u);
+                } else if (a.role_b != 0) {
+                    const size_t subbytes = sbytes / (size_t)tm.n_islands;
+                    const size_t h = at / subbytes;
+                    const int owner = tm.order[tm.island_off[h] + tm.my_pos];
+                    gb_st16(tm.ws[owner] + a.off_b + (size_t)buf * a.len_b
+                            + (size_t)tm.my_island * subbytes + (at - h * subbytes), r.u);
                 } else {
                     for (int d = 0; d < tm.n_islands; ++d) {
                         const int isl = (tm.my_island + d) % tm.n_islands;
@@ -801,6 +812,38 @@ __device__ __forceinline__ bool bridge_reduce_ring(GbRing& R, const GbTeam& tm, 
     const char* parts = tm.ws[tm.rank] + a.off_b + (size_t)buf * a.len_b;
     char* result = tm.ws[tm.rank] + a.off_c + (size_t)buf * a.len_c;
     const int groups = tm.n_islands;
+    if (a.role_b != 0) {
+        // two-shot: this owner finishes sub-stripe `my_island` and sends it to every island
+        const size_t sub = a.stripe / (size_t)groups, subbytes = sub * sizeof(T);
+        const size_t lo = (size_t)tm.my_island * sub;
+        const size_t mine = count > lo ? (count - lo < sub ? count - lo : sub) : 0;
+        if (mine == 0) return true;
+        return gb_ring_run(R, tm, bi, nb, parts, subbytes, groups, mine * sizeof(T), true,
+            [&](const unsigned char* stage, unsigned pitch, size_t off, unsigned len) {
+                const unsigned nv = len >> 4;
+                for (unsigned v = threadIdx.x; v < nv; v += THREADS) {
+                    A total[V];
+                    for (int g = 0; g < groups; ++g) {
+                        Vec<T> w;
+                        w.u = *reinterpret_cast<const uint4*>(stage + (size_t)g * pitch + ((size_t)v << 4));
+                        #pragma unroll
+                        for (int j = 0; j < V; ++j)
+                            total[j] = (g == 0) ? gb_up<T>(w.e[j])
+                                                : GbFold<OP, A>::run(total[j], gb_up<T>(w.e[j]));
+                    }
+                    Vec<T> r;
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        r.e[j] = gb_down<T>(a.divide > 0 ? gb_divide<A>(total[j], a.divide) : total[j]);
+                    const size_t at = (size_t)tm.my_island * subbytes + off + ((size_t)v << 4);
+                    for (int d = 0; d < groups; ++d) {
+                        const int isl = (tm.my_island + d) % groups;
+                        const int owner = tm.order[tm.island_off[isl] + tm.my_pos];
+                        gb_st16(tm.ws[owner] + a.off_c + (size_t)buf * a.len_c + at, r.u);
+                    }
+                }
+            });
+    }
     return gb_ring_run(R, tm, bi, nb, parts, sbytes, groups, count * sizeof(T), true,
         [&](const unsigned char* stage, unsigned pitch, size_t off, unsigned len) {
             const unsigned nv = len >> 4;

@@ -70,13 +70,16 @@ class HierPlan:
 
 def plan_hier(n: int, esize: int, *, k: int, m_max: int, n_islands: int, len_ha: int, len_hb: int,
               len_hc: int, grid: int, chunk_bytes: int | None = None,
-              force_channels: int | None = None, force_chunks: int | None = None) -> HierPlan:
+              force_channels: int | None = None, force_chunks: int | None = None,
+              stripe_multiple: int = 256) -> HierPlan:
     """Channels, chunking and buffer sizes of one hierarchical all-reduce.
 
     Pure arithmetic on values every rank of the team shares (never this rank's own island
     size or position): all ranks must come out with the same plan, or their stripes do not
     line up.  Every channel owns two buffers of each region; a stripe fits the smallest slot
-    (``m_max`` slots in region A, ``n_islands`` in region B, one in region C)."""
+    (``m_max`` slots in region A, ``n_islands`` in region B, one in region C).  ``stripe_multiple``:
+    the stripe length is a multiple of it (256 values; 256 * islands for the two-shot bridge,
+    whose sub-stripes must be whole quantisation-block multiples too)."""
     nbytes = n * esize
     # Channels: independent pipelines that hide each other's barriers and local phases.
     # One for small tensors (a barrier costs more than the data), up to four for large.
@@ -87,8 +90,8 @@ def plan_hier(n: int, esize: int, *, k: int, m_max: int, n_islands: int, len_ha:
     len_b = len_hb // channels // 4096 * 4096
     len_c = len_hc // channels // 4096 * 4096
     slot = min(len_a // m_max, len_b // n_islands, len_c)
-    stripe_cap = _align_down(slot // esize, 256)
-    if stripe_cap < 256:
+    stripe_cap = _align_down(slot // esize, stripe_multiple)
+    if stripe_cap < stripe_multiple:
         raise RuntimeError("the fabric workspace is too small for this team; raise "
                            f"{_config.FABRIC_BYTES_ENV}")
     if chunk_bytes:
@@ -101,7 +104,7 @@ def plan_hier(n: int, esize: int, *, k: int, m_max: int, n_islands: int, len_ha:
         link_s = nbytes / channels * share / LINK_GBS
         chunks = force_chunks or max(1, round((depth * link_s / BARRIER_S) ** 0.5))
         want = -(-n // (chunks * channels * k))
-    stripe = min(stripe_cap, _align_up(max(1, min(want, -(-n // k))), 256))
+    stripe = min(stripe_cap, _align_up(max(1, min(want, -(-n // k))), stripe_multiple))
     return HierPlan(channels, grid, stripe, -(-n // (stripe * k)), len_a, len_b, len_c)
 
 
@@ -136,6 +139,7 @@ class Fabric:
         # Grids of the copy-shaped collectives.  With the bulk-copy ring 16 CTAs already run a
         # link at 640-680 GB/s (measured), so all-gather and broadcast take few SMs and leave
         # the rest to the compute they overlap with; reduce-scatter also reduces locally.
+        self.two_shot = os.environ.get("GPUBRIDGE_BRIDGE_TWO_SHOT", "0") == "1"
         self.nvls = None        # (tensor, handle, local pointer, multicast pointer, bytes per buffer)
         self.nvls_reducers = int(os.environ.get("GPUBRIDGE_NVLS_REDUCERS", "48"))
         self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "32"))
@@ -364,11 +368,18 @@ class Fabric:
             self._end(current)
 
     def _hier(self, tensor, args, op, compression, chunk_bytes) -> None:
+        aligned = (args.inp | args.out) % 16 == 0
+        ring = bool(self.ring) and compression is None and aligned
+        # more than two islands: the bridge can move 2 (I - 1) / I stripes per owner instead of
+        # I - 1 (GPUBRIDGE_BRIDGE_TWO_SHOT=1; the phased ring kernel only)
+        two_shot = (ring and self.ring == "phased" and self.n_islands >= 3 and self.two_shot)
         plan = plan_hier(tensor.numel(), tensor.element_size(), k=self.k, m_max=self.m_max,
                          n_islands=self.n_islands, len_ha=self.len_ha, len_hb=self.len_hb,
                          len_hc=self.len_hc, grid=self._grid(tensor.nbytes * 2),
                          chunk_bytes=chunk_bytes, force_channels=self.force_channels,
-                         force_chunks=self.force_chunks)
+                         force_chunks=self.force_chunks,
+                         stripe_multiple=256 * self.n_islands if two_shot else 256)
+        args.role_b = 1 if two_shot else 0
         args.stripe, args.k, args.chunk = plan.stripe, self.k, plan.stripe * self.k
         args.off_a, args.len_a = self.off_ha, plan.len_a
         args.off_b, args.len_b = self.off_hb, plan.len_b
@@ -378,8 +389,7 @@ class Fabric:
         if compression is not None:
             codec = _lib.CODECS[tuple(compression)]
             args.residual = self._residual(tensor, (plan.stripe, self.k, plan.nchunks, codec)).data_ptr()
-        aligned = (args.inp | args.out) % 16 == 0
-        kind = (4 if self.ring == "phased" else 3) if (self.ring and codec == 0 and aligned) else 1
+        kind = (4 if self.ring == "phased" else 3) if ring else 1
         self._launch_reduce(kind, tensor.dtype, op, codec, args, plan.grid)
         if _observe.watching() and not torch.cuda.is_current_stream_capturing():
             self._report_phases(plan)

@@ -65,3 +65,15 @@ def test_small_workspace_is_refused():
     with pytest.raises(RuntimeError, match="too small"):
         plan_hier(1 << 20, 4, k=1, m_max=8, n_islands=1, len_ha=8192, len_hb=8192, len_hc=1024,
                   grid=128)
+
+
+def test_two_shot_stripes_split_evenly_over_the_islands():
+    for world, islands in ((8, [2, 2, 2, 2]), (8, [1, 2, 5]), (4, [1, 1, 2])):
+        m_max, k, n_islands = max(islands), min(islands), len(islands)
+        len_ha, len_hb, len_hc = _regions(world, m_max, n_islands)
+        for nbytes in (3 * MIB + 12, 36 * MIB + 12, 1 << 30):
+            plan = plan_hier(nbytes // 4, 4, k=k, m_max=m_max, n_islands=n_islands, len_ha=len_ha,
+                             len_hb=len_hb, len_hc=len_hc, grid=128,
+                             stripe_multiple=256 * n_islands)
+            assert plan.stripe % (256 * n_islands) == 0
+            assert m_max * plan.stripe * 4 <= plan.len_a and plan.stripe * 4 <= plan.len_c

@@ -15,8 +15,11 @@ needs_two = pytest.mark.skipif(NGPU < 2, reason="needs at least two GPUs")
 
 SIZES = (1, 17, 4099, 65536 + 3, (1 << 20) + 5, (6 << 20) + 1)
 SPLITS = [{}, {"GPUBRIDGE_SPLIT_TEST": "half"}] + (
-    [{"GPUBRIDGE_ISLANDS": "2,2,2,2"}, {"GPUBRIDGE_ISLANDS": "3,5"}] if WORLD == 8 else
-    [{"GPUBRIDGE_ISLANDS": "1,3"}] if WORLD == 4 else [])
+    [{"GPUBRIDGE_ISLANDS": "2,2,2,2"}, {"GPUBRIDGE_ISLANDS": "3,5"},
+     {"GPUBRIDGE_ISLANDS": "2,2,2,2", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"},
+     {"GPUBRIDGE_ISLANDS": "1,2,5", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"}] if WORLD == 8 else
+    [{"GPUBRIDGE_ISLANDS": "1,3"},
+     {"GPUBRIDGE_ISLANDS": "1,1,2", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"}] if WORLD == 4 else [])
 
 
 def _collectives(rank, topology, policy):
