@@ -2,6 +2,8 @@
 relabelling (``GPUBRIDGE_SPLIT_TEST`` / ``GPUBRIDGE_ISLANDS``), results checked against the
 analytic answer on integer-valued data (exact in any order) and against the PyTorch codec
 for the compressed bridge leg.  Needs at least two GPUs."""
+import os
+
 import pytest
 import torch
 
@@ -15,11 +17,14 @@ needs_two = pytest.mark.skipif(NGPU < 2, reason="needs at least two GPUs")
 
 SIZES = (1, 17, 4099, 65536 + 3, (1 << 20) + 5, (6 << 20) + 1)
 SPLITS = [{}, {"GPUBRIDGE_SPLIT_TEST": "half"}] + (
-    [{"GPUBRIDGE_ISLANDS": "2,2,2,2"}, {"GPUBRIDGE_ISLANDS": "3,5"},
-     {"GPUBRIDGE_ISLANDS": "2,2,2,2", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"},
-     {"GPUBRIDGE_ISLANDS": "1,2,5", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"}] if WORLD == 8 else
-    [{"GPUBRIDGE_ISLANDS": "1,3"},
-     {"GPUBRIDGE_ISLANDS": "1,1,2", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"}] if WORLD == 4 else [])
+    [{"GPUBRIDGE_ISLANDS": "2,2,2,2"}, {"GPUBRIDGE_ISLANDS": "3,5"}] if WORLD == 8 else
+    [{"GPUBRIDGE_ISLANDS": "1,3"}] if WORLD == 4 else [])
+# The two-shot bridge (three or more islands) has not run on hardware yet: its cases join the
+# suite when GPUBRIDGE_TEST_TWO_SHOT=1 says so, and move into SPLITS once they have passed.
+if os.environ.get("GPUBRIDGE_TEST_TWO_SHOT") == "1":
+    SPLITS += ([{"GPUBRIDGE_ISLANDS": "2,2,2,2", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"},
+                {"GPUBRIDGE_ISLANDS": "1,2,5", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"}] if WORLD == 8 else
+               [{"GPUBRIDGE_ISLANDS": "1,1,2", "GPUBRIDGE_BRIDGE_TWO_SHOT": "1"}] if WORLD == 4 else [])
 
 
 def _collectives(rank, topology, policy):
