@@ -93,7 +93,13 @@ class _Worker:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self.limit = queue_limit()
-        self.queue: queue.Queue = queue.Queue(self.limit)
+        # a SimpleQueue (one C-level lock) plus a count of accepted items: cheaper per call
+        # than queue.Queue's two condition variables, with the same bound and join()
+        self.queue: queue.SimpleQueue = queue.SimpleQueue()
+        self._accepted = 0
+        self._count_lock = threading.Lock()
+        self._idle = threading.Event()
+        self._idle.set()
         self.failed: BaseException | None = None
         self.stream: torch.cuda.Stream | None = None
         self.thread = threading.Thread(target=self._loop, name="gpubridge-async", daemon=True)
@@ -105,14 +111,26 @@ class _Worker:
         if self.device.type == "cuda":
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(self.device))
-        try:
-            self.queue.put_nowait((work, fn, ready, tuple(tensors)))
-        except queue.Full:
-            raise RuntimeError(
-                f"gpubridge async queue is full ({self.limit} queued collectives); wait for "
-                "accepted work before retrying this collective, preserving the same collective "
-                f"order on every rank ({QUEUE_ENV})") from None
+        with self._count_lock:
+            if self._accepted >= self.limit:
+                raise RuntimeError(
+                    f"gpubridge async queue is full ({self.limit} queued collectives); wait for "
+                    "accepted work before retrying this collective, preserving the same "
+                    f"collective order on every rank ({QUEUE_ENV})")
+            self._accepted += 1
+            self._idle.clear()
+        self.queue.put((work, fn, ready, tuple(tensors)))
         return work
+
+    def _retire(self) -> None:
+        with self._count_lock:
+            self._accepted -= 1
+            if self._accepted == 0:
+                self._idle.set()
+
+    def join(self) -> None:
+        """Until everything accepted so far has run."""
+        self._idle.wait()
 
     def _loop(self) -> None:
         if self.device.type == "cuda":
@@ -134,7 +152,8 @@ class _Worker:
                     self.failed = error
                     work._finish(error)
             finally:
-                self.queue.task_done()
+                if item is not None:
+                    self._retire()
 
     def _one(self, work, fn, ready, tensors) -> None:
         if self.stream is None:
@@ -163,7 +182,7 @@ class _Worker:
             if item is not None:
                 item[0]._finish(RuntimeError(f"gpubridge async {item[0].op} not run: its "
                                              "process groups were destroyed"))
-            self.queue.task_done()
+                self._retire()
         self.queue.put(None)
         self.thread.join(timeout)
 
@@ -206,7 +225,7 @@ def launch(device: torch.device, op: str, fn: Callable[[], "torch.cuda.Event | N
     device work on ``stream`` and returns the event recorded after it."""
     check_healthy()
     if _worker is not None:
-        _worker.queue.join()      # keep program order with queued collectives
+        _worker.join()            # keep program order with queued collectives
         check_healthy()
     work = Work(op, device, result)
     try:
@@ -226,7 +245,7 @@ def launch(device: torch.device, op: str, fn: Callable[[], "torch.cuda.Event | N
 
 def drain() -> None:
     if _worker is not None:
-        _worker.queue.join()
+        _worker.join()
     check_healthy()
 
 
