@@ -146,3 +146,52 @@ def test_runbook_plan_and_one_step(tmp_path):
     bad = runbook.run_step({"name": "boom", "cmd": [sys.executable, "-c", "raise SystemExit(3)"],
                             "env": {}, "expect": None, "timeout": None}, tmp_path / "run", 30)
     assert bad["ok"] is False and bad["exit_code"] == 3
+
+
+def test_triage_puts_problems_first(tmp_path, capsys):
+    """A fabricated runbook directory: a failed step, a step past its limit, a log without a
+    verdict and a failed check summary all appear above the detail; addresses are redacted."""
+    import tarfile
+    from gpubridge_b200.kit import triage
+
+    run = tmp_path / "rb"
+    (run / "check-half").mkdir(parents=True)
+    (run / "probe").mkdir()
+    rows = [{"step": "probe", "ok": True, "exit_code": 0, "seconds": 1.0, "log": "probe.log"},
+            {"step": "sweep", "ok": False, "exit_code": 1, "seconds": 3.0, "log": "sweep.log"},
+            {"step": "sweep", "ok": False, "exit_code": 2, "seconds": 4.0, "log": "sweep.log"},
+            {"step": "gate-bridged", "ok": False, "exit_code": None, "seconds": 9.0, "log": "gate-bridged.log"}]
+    (run / "steps.jsonl").write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    (run / "probe.log").write_text("fine\n")
+    (run / "sweep.log").write_text("starting\nRuntimeError: connect to 10.1.2.3 refused by node-17\nbye\n")
+    (run / "gate-bridged.log").write_text("the step ran past its limit\n")
+    (run / "p2p.log").write_text("half a line")
+    (run / "check-half" / "summary.json").write_text(json.dumps(
+        {"ok": False, "stages": {"init": {"0": True, "1": True}, "all_reduce": {"0": True, "1": False}},
+         "ranks_missing": []}))
+    (run / "probe" / "probe.json").write_text(json.dumps(
+        {"environment": {"hostname": "node-17", "device_count": 2, "devices": [{"name": "B200"}, {"name": "B200"}],
+                         "torch": "2.11", "torch_cuda": "12.8", "nccl": "2.28.9", "gpubridge_b200": "0.1.0"}}))
+    (run / "sweep.json").write_text(json.dumps(
+        [{"bytes": 1 << 20, "target": "ours", "ms": 0.02, "busbw_gbs": 90.0},
+         {"bytes": 1 << 20, "target": "nccl", "ms": 0.03, "busbw_gbs": 60.0}]))
+
+    assert triage.main([str(run)]) == 1
+    text = capsys.readouterr().out
+    assert text.index("PROBLEMS") < text.index("ran on host 1")
+    assert "step sweep: FAILED (exit code 2" in text and "exit code 1" not in text
+    assert "step gate-bridged: FAILED (ran past its limit" in text
+    assert "step p2p: left unfinished" in text
+    assert "check-half: all_reduce: r1" in text
+    assert "10.1.2.3" not in text and "node-17" not in text and "<ip>" in text
+    assert "ours = 1.50x nccl's speed" in text
+    assert "verdict: 0 of 1 run(s) clean" in text
+
+    ball = tmp_path / "rb.tgz"
+    with tarfile.open(ball, "w:gz") as tar:
+        tar.add(run, arcname="results/rb")
+    assert triage.main([str(ball), "--max-lines", "6"]) == 1
+    short = capsys.readouterr().out.splitlines()
+    assert len(short) == 6 and short[-1].startswith("verdict") and "more lines" in short[-2]
+    (tmp_path / "empty").mkdir()
+    assert triage.main([str(tmp_path / "empty")]) == 2
