@@ -42,19 +42,27 @@ class DataParallelTrainer:
         graph: capture the step in a CUDA graph after ``graph_warmup`` eager steps.
         overlap_blocks: CTAs of a bucket all-reduce that runs beside backward
             (``GPUBRIDGE_OVERLAP_BLOCKS``, default 32); the last bucket uses the full grid.
+        unit_grad: tell a model that has a ``unit_grad`` switch that backward starts at its
+            loss with gradient 1 (its fused loss then skips the multiply); pass False when
+            ``loss_fn`` scales the model's loss.
+        exchange: False trains this rank alone even inside an initialised job (the
+            compute-only phase of a benchmark).
     """
 
     def __init__(self, model: nn.Module, loss_fn, *, topology: Topology | None = None,
                  lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 1e-2, bucket_mb: float = 25.0,
                  autocast: torch.dtype | None = torch.bfloat16, graph: bool = False,
-                 graph_warmup: int = 3, overlap_blocks: int | None = None) -> None:
+                 graph_warmup: int = 3, overlap_blocks: int | None = None,
+                 unit_grad: bool = True, exchange: bool = True) -> None:
         self.model, self.loss_fn = model, loss_fn
         import os
         self.overlap_blocks = overlap_blocks or int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
         if hasattr(model, "unit_grad"):
-            model.unit_grad = True          # backward always starts at the loss here
-        if topology is None and is_initialized():
+            model.unit_grad = unit_grad     # backward always starts at the loss here
+        if not exchange:
+            topology = None
+        elif topology is None and is_initialized():
             topology = get_topology()
         self.topology = topology
         self.world = topology.world_size if topology is not None else 1
@@ -79,6 +87,7 @@ class DataParallelTrainer:
         self._buckets = self._make_buckets(int(bucket_mb * MIB))
         self._pending = [0] * len(self._buckets)
         self._sent = 0
+        self._syncing = True
         self._comm_events: list[torch.cuda.Event] = []
         if self.world > 1:
             for index, (lo, hi, members) in enumerate(self._buckets):
@@ -105,6 +114,8 @@ class DataParallelTrainer:
 
     def _make_hook(self, index: int):
         def hook(param) -> None:
+            if not self._syncing:           # an earlier micro-batch: gradients only accumulate
+                return
             self._pending[index] -= 1
             if self._pending[index] == 0:
                 self._reduce_ready()
@@ -143,16 +154,21 @@ class DataParallelTrainer:
             total += self.fabric.launches
         return total
 
-    def _step_body(self, batch) -> torch.Tensor:
+    def _step_body(self, batch, earlier=()) -> torch.Tensor:
         own_before = self._own_kernels()
         self._pending = [len(members) for _, _, members in self._buckets]
         self._sent = 0
-        if self.autocast is not None and self.device.type == "cuda":
-            with torch.autocast("cuda", dtype=self.autocast):
-                loss = self.loss_fn(self.model, *batch)
-        else:
-            loss = self.loss_fn(self.model, *batch)
-        loss.backward()
+        total = None
+        for micro in (*earlier, batch):
+            self._syncing = micro is batch
+            if self.autocast is not None and self.device.type == "cuda":
+                with torch.autocast("cuda", dtype=self.autocast):
+                    loss = self.loss_fn(self.model, *micro)
+            else:
+                loss = self.loss_fn(self.model, *micro)
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        loss = total
         if self.world > 1:
             # parameters that received no gradient still belong to their bucket
             self._pending = [0] * len(self._buckets)
@@ -161,7 +177,18 @@ class DataParallelTrainer:
                 torch.cuda.current_stream(self.device).wait_stream(self.fabric.comm_stream)
         self.optimizer.step(zero_grad=True)
         self.launches += self._own_kernels() - own_before
-        return loss.detach()
+        return loss
+
+    def step_accumulated(self, micro_batches) -> torch.Tensor:
+        """One optimizer step over several micro-batches: forward and backward on each in
+        turn, gradients summed in the flat buffer, buckets averaged once, during the last
+        backward (what ``DistributedDataParallel.no_sync()`` does for the reference's
+        ``--accumulate``, scripts/gpu/train_bench.py:57-68).  Runs eagerly.  Returns the sum
+        of the micro-batch losses; weight them inside ``loss_fn`` so the sum is the loss
+        wanted."""
+        self._steps += 1
+        moved = [[b.to(self.device, non_blocking=True) for b in micro] for micro in micro_batches]
+        return self._step_body(moved[-1], earlier=moved[:-1])
 
     def step(self, *batch: torch.Tensor) -> torch.Tensor:
         """Forward, backward with overlapped gradient averaging, optimizer.  Returns the

@@ -45,3 +45,68 @@ def test_per_call_table(tmp_path):
     assert done.returncode == 0, done.stderr[-3000:]
     record = json.loads(out.read_text())
     assert record["stub_comm"] and "reduce-bridge-broadcast/sync/plain" in record["us_per_call"]
+
+
+def test_train_bench_shares():
+    from gpubridge_b200.bench.train_bench import even_shares, speed_shares
+    import pytest
+    assert even_shares(7, 3) == [3, 2, 2]
+    with pytest.raises(ValueError):
+        even_shares(2, 3)
+    assert speed_shares(12, [1.0, 2.0]) == [8, 4]          # twice as fast: twice the samples
+    assert speed_shares(5, [1.0, 1.0]) == [3, 2]           # ties go to the lower rank
+    assert speed_shares(6, [1.0, 100.0], floor=2) == [4, 2]
+    shares = speed_shares(64, [0.8, 1.0, 1.3, 2.1])
+    assert sum(shares) == 64 and shares == sorted(shares, reverse=True)
+    worst = max(s * t for s, t in zip(shares, [0.8, 1.0, 1.3, 2.1]))
+    assert all(worst <= (s + 1) * t + 1e-9 for s, t in zip(shares, [0.8, 1.0, 1.3, 2.1]))
+    with pytest.raises(ValueError):
+        speed_shares(3, [1.0, 0.0])
+
+
+def test_accumulated_step_equals_one_step():
+    """Micro-batches weighted by their share give the update of one backward over the whole batch."""
+    import torch
+    from gpubridge_b200.parallel.trainer import DataParallelTrainer
+
+    def make():
+        torch.manual_seed(3)
+        return torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 1))
+
+    x, y = torch.randn(8, 6), torch.randn(8, 1)
+    mean = lambda m, a, b: torch.nn.functional.mse_loss(m(a), b)                      # noqa: E731
+    share = lambda m, a, b: torch.nn.functional.mse_loss(m(a), b) * (a.shape[0] / 8)  # noqa: E731
+    whole = DataParallelTrainer(make(), mean, autocast=None, exchange=False)
+    parts = DataParallelTrainer(make(), share, autocast=None, exchange=False)
+    for _ in range(3):
+        a = whole.step(x, y)
+        b = parts.step_accumulated([(x[:3], y[:3]), (x[3:4], y[3:4]), (x[4:], y[4:])])
+        assert torch.allclose(a, b, atol=1e-6)
+    assert torch.allclose(whole.flat_param, parts.flat_param, atol=1e-6)
+
+
+def test_train_bench_two_ranks(tmp_path):
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1", GPUBRIDGE_VENDOR="nvidia",
+               GPUBRIDGE_SPLIT_TEST="half")
+    for port, extra in ((29741, ["--model", "tiny-gpt", "--engine", "trainer", "--batch-sizes", "3,5",
+                                 "--accumulate", "2"]),
+                        (29742, ["--model", "tiny-resnet", "--global-batch", "7", "--controlled"]),
+                        (29743, ["--model", "tiny-gpt", "--grad-sync", "native"])):
+        out = tmp_path / f"tb{port}.json"
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), "-m",
+               "gpubridge_b200.bench.train_bench", *extra, "--steps", "3", "--warmup-steps", "1",
+               "--comm-trials", "2", "--json", str(out)]
+        done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=300)
+        assert done.returncode == 0, done.stderr[-3000:]
+        r = json.loads(out.read_text())
+        assert r["params_identical"] and r["params_finite"] and r["params_sum_spread"] == 0.0
+        assert r["exchanges_per_step"] == len(r["bucket_bytes"]) >= 1
+        assert r["samples_per_s"] > 0 and len(r["ranks"]) == 2
+        assert abs(r["ddp_step_ms"] - r["slowest_compute_ms"] - r["exposed_comm_ms"]) < 2e-3
+        if "--batch-sizes" in extra:
+            assert [x["batch"] for x in r["ranks"]] == [3, 5] and r["ranks"][1]["micro_batches"] == [3, 2]
+        if "--controlled" in extra:
+            assert r["controlled"]["initial_parameters"] and r["dtype"] == "fp32" and r["split"] == "even"
+        if "native" in extra:
+            assert "stand-in" in r["note"]
