@@ -46,6 +46,29 @@ class GbArgs(ctypes.Structure):
                 ("residual", ctypes.c_void_p), ("sym", ctypes.c_void_p), ("mc", ctypes.c_void_p)]
 
 
+class GbEngineConfig(ctypes.Structure):
+    """What the native engine needs of a team: grids, switches and the workspace regions."""
+    _fields_ = ([("ws_bytes", ctypes.c_size_t)]
+                + [(name, ctypes.c_int) for name in (
+                    "k", "m_max", "max_blocks", "copy_blocks", "scatter_blocks", "overlap_blocks",
+                    "ring", "two_shot", "force_chunks", "force_channels", "algo")]
+                + [(name, ctypes.c_size_t) for name in (
+                    "oneshot_slot", "off_oneshot", "len_oneshot", "off_ha", "len_ha", "off_hb",
+                    "len_hb", "off_hc", "len_hc", "off_rs", "len_rs", "rs_chunk_bytes", "off_ag",
+                    "len_ag", "ag_chunk_bytes", "off_bc", "len_bc", "bc_stripe_bytes")])
+
+
+class GbLaunch(ctypes.Structure):
+    _fields_ = [("family", ctypes.c_int), ("kind", ctypes.c_int), ("grid", ctypes.c_int),
+                ("args", GbArgs)]
+
+
+class GbHierPlanOut(ctypes.Structure):
+    _fields_ = [("channels", ctypes.c_int), ("grid", ctypes.c_int), ("stripe", ctypes.c_size_t),
+                ("nchunks", ctypes.c_size_t), ("len_a", ctypes.c_size_t),
+                ("len_b", ctypes.c_size_t), ("len_c", ctypes.c_size_t)]
+
+
 _lock = threading.Lock()
 _lib: ctypes.CDLL | None = None
 
@@ -65,7 +88,9 @@ def lib() -> ctypes.CDLL:
         loaded = ctypes.CDLL(_build.LIB)
         _declare(loaded)
         if loaded.gb_sizeof_team() != ctypes.sizeof(GbTeam) or \
-                loaded.gb_sizeof_args() != ctypes.sizeof(GbArgs):
+                loaded.gb_sizeof_args() != ctypes.sizeof(GbArgs) or \
+                loaded.gb_sizeof_engine_config() != ctypes.sizeof(GbEngineConfig) or \
+                loaded.gb_sizeof_launch() != ctypes.sizeof(GbLaunch):
             raise RuntimeError("the native library's structures do not match ops/_lib.py; "
                                "rebuild with python -m gpubridge_b200.ops._build --force")
         _lib = loaded
@@ -76,7 +101,8 @@ def _declare(L: ctypes.CDLL) -> None:
     vp, sz, i = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
     L.gb_error_string.restype = ctypes.c_char_p
     L.gb_error_string.argtypes = [i]
-    for name in ("gb_sizeof_team", "gb_sizeof_args", "gb_sizeof_ctrl"):
+    for name in ("gb_sizeof_team", "gb_sizeof_args", "gb_sizeof_ctrl", "gb_sizeof_engine_config",
+                 "gb_sizeof_launch"):
         getattr(L, name).restype = sz
         getattr(L, name).argtypes = []
     L.gb_payload_bytes.restype = sz
@@ -99,6 +125,25 @@ def _declare(L: ctypes.CDLL) -> None:
                                     i, i, i, sz, i, i, vp]
     L.gb_allgather_gemm_pair.argtypes = L.gb_allgather_gemm.argtypes
     L.gb_copy_to_host.argtypes = [vp, vp, sz, vp]
+    L.gb_plan_hier.argtypes = [sz, i, i, i, i, sz, sz, sz, i, sz, i, i, i, ctypes.POINTER(GbHierPlanOut)]
+    L.gb_engine_create.restype = vp
+    L.gb_engine_create.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbEngineConfig)]
+    L.gb_engine_destroy.restype = None
+    L.gb_engine_destroy.argtypes = [vp]
+    L.gb_engine_launches.restype = ctypes.c_ulonglong
+    L.gb_engine_launches.argtypes = [vp]
+    L.gb_engine_status.restype = ctypes.c_uint
+    L.gb_engine_status.argtypes = [vp]
+    launch = ctypes.POINTER(GbLaunch)
+    L.gb_engine_prepare_all_reduce.argtypes = [vp, vp, vp, sz, i, i, i, i, launch]
+    L.gb_engine_prepare_reduce_scatter.argtypes = [vp, vp, vp, sz, i, i, i, launch]
+    L.gb_engine_prepare_all_gather.argtypes = [vp, vp, vp, sz, i, launch]
+    L.gb_engine_prepare_broadcast.argtypes = [vp, vp, sz, i, i, launch]
+    L.gb_engine_all_reduce.argtypes = [vp, vp, vp, sz, i, i, i, i, vp]
+    L.gb_engine_reduce_scatter.argtypes = [vp, vp, vp, sz, i, i, i, vp]
+    L.gb_engine_all_gather.argtypes = [vp, vp, vp, sz, i, vp]
+    L.gb_engine_broadcast.argtypes = [vp, vp, sz, i, i, vp]
+    L.gb_engine_barrier.argtypes = [vp, vp]
     L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
     L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]
 

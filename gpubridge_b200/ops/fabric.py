@@ -150,6 +150,7 @@ class Fabric:
         ring = os.environ.get("GPUBRIDGE_RING", "phased")
         self.ring = False if ring == "0" else "phased" if ring == "phased" else True
         self.launches = 0            # kernels launched by this team (benchmarks report it)
+        self._engine = None
 
         islands = layout.islands
         self.n_islands = len(islands)
@@ -266,6 +267,33 @@ class Fabric:
         third = _align_down(nbytes // 3, 16 * self.world * 256)
         self.nvls = (buffer, handle, buffer.data_ptr(), multicast, third)
         return True
+
+    # -- the native engine -----------------------------------------------------------------------------
+    def engine_config(self) -> "_lib.GbEngineConfig":
+        c = _lib.GbEngineConfig()
+        c.ws_bytes, c.k, c.m_max = self.ws_bytes, self.k, self.m_max
+        c.max_blocks, c.copy_blocks = self.max_blocks, self.copy_blocks
+        c.scatter_blocks, c.overlap_blocks = self.scatter_blocks, self.overlap_blocks
+        c.ring = 0 if not self.ring else 2 if self.ring == "phased" else 1
+        c.two_shot = int(self.two_shot)
+        c.force_chunks, c.force_channels = self.force_chunks or 0, self.force_channels or 0
+        c.algo = {"auto": 0, "one-shot": 1}.get(self.algo, 2)
+        for name in ("oneshot_slot", "off_oneshot", "len_oneshot", "off_ha", "len_ha", "off_hb",
+                     "len_hb", "off_hc", "len_hc", "off_rs", "len_rs", "rs_chunk_bytes", "off_ag",
+                     "len_ag", "ag_chunk_bytes", "off_bc", "len_bc", "bc_stripe_bytes"):
+            setattr(c, name, getattr(self, name))
+        return c
+
+    def engine(self) -> int:
+        """Handle of this team's native engine (planner and launches in C++, for the C++
+        front end), created on first use.  0 when a feature only the Python path has is on
+        (in-switch reduction)."""
+        if self.nvls is not None or self._closed:
+            return 0
+        if self._engine is None:
+            self._engine = self.lib.gb_engine_create(ctypes.byref(self.team),
+                                                     ctypes.byref(self.engine_config()))
+        return self._engine or 0
 
     # -- health --------------------------------------------------------------------------------------
     def check(self) -> None:
@@ -533,6 +561,9 @@ class Fabric:
         if self._closed:
             return
         self._closed = True
+        if self._engine:
+            self.lib.gb_engine_destroy(self._engine)
+            self._engine = None
         try:
             torch.cuda.synchronize(self.device)
         except Exception:  # noqa: BLE001 - teardown never raises

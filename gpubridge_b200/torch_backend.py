@@ -54,6 +54,10 @@ NAME = "gpubridge"
 
 _lock = threading.RLock()
 _owner: "GpubridgeProcessGroup | None" = None     # the group that owns the world topology
+# Jobs of this process so far.  A launcher's store outlives destroy_process_group(), so the
+# keys of a second job must not meet the first job's: every name carries the count, which
+# all ranks share because every rank creates its world group once per job.
+_generation = 0
 _subgroups: "list[GpubridgeProcessGroup]" = []
 
 
@@ -149,7 +153,13 @@ class GpubridgeProcessGroup(dist.ProcessGroup):
         self._native_batch = None
         self._engine: _p2p.Engine | None = None
         self._engine_lock = threading.Lock()
-        self._p2p_store = dist.PrefixStore("gpubridge-p2p", store) if store is not None else None
+        global _generation
+        if not self._members:
+            _generation += 1
+        self._generation = _generation
+        self._p2p_store = (dist.PrefixStore(f"gpubridge-p2p{self._generation}", store)
+                           if store is not None else None)
+        self._on_shutdown: Callable[[], None] | None = None     # set by the C++ front end's glue
 
     # -- identity ----------------------------------------------------------------------------
     @property
@@ -204,7 +214,7 @@ class GpubridgeProcessGroup(dist.ProcessGroup):
                                               "problems": (*local.problems, *problems)})
             topology = _topology.build_topology(
                 self._store, self.rank(), self.size(), local, cfg, transport=transport,
-                policy=chosen, timeout=self._timeout, name="pg")
+                policy=chosen, timeout=self._timeout, name=f"pg{self._generation}")
             _work.shutdown()
             _observe._reset()
             _topology._set_topology(topology)
@@ -225,7 +235,7 @@ class GpubridgeProcessGroup(dist.ProcessGroup):
                 self._building = True
                 try:
                     self._built = _topology.build_subtopology(world, self._store, self._members,
-                                                              "sub", self._timeout)
+                                                              f"sub{self._generation}", self._timeout)
                 finally:
                     self._building = False
                 with _lock:
@@ -235,11 +245,38 @@ class GpubridgeProcessGroup(dist.ProcessGroup):
     def _cpu(self):
         return self._topology().cpu_group
 
+    # -- the C++ front end (native_backend.py) asks these ------------------------------------------
+    def _native_team(self):
+        """``(engine, stream, device index, grid cap, team rank of each group rank)`` when this
+        group's collectives on CUDA tensors can be planned and launched by the native engine,
+        else None: no NVLink fabric, a compressed bridge, or a policy that shapes the fused
+        kernel differently (pipelined, sharded, auto-tuned)."""
+        from gpubridge_b200 import policies as _policies
+        topology = self._topology()
+        fabric, policy = topology.fabric, topology.policy
+        if fabric is None or type(policy) not in (_policies.ReduceBridgeBroadcast, _policies.NativeOnly):
+            return None
+        if getattr(policy, "_mode", ""):
+            return None
+        engine = fabric.engine()
+        if not engine:
+            return None
+        team_rank = [fabric.layout.index(self._global(r)) for r in range(self.size())]
+        return (engine, fabric.comm_stream.cuda_stream, fabric.device.index, fabric.overlap_blocks,
+                team_rank)
+
+    def _native_failed(self) -> None:
+        """A device-side wait of this team ran out: raise what the kernel recorded."""
+        self._topology().fabric.check()
+
     def shutdown(self) -> None:
         """Called by ``destroy_process_group()``; releases state without running what is
         queued and never raises."""
         if self._engine is not None:
             self._engine.close()
+        released, self._on_shutdown = self._on_shutdown, None
+        if released is not None:
+            released()
         if self._members:
             _close_subgroup(self)
         else:

@@ -52,8 +52,11 @@ def _entry(rank, world, vendors, fn, path, env, args, mode, init, results):
                     out = fn(rank, topology, *args)
                 finally:
                     gb.destroy()
-            elif mode == "backend":
-                dist.init_process_group("gpubridge", init_method=f"file://{path}", rank=rank,
+            elif mode in ("backend", "native-backend"):
+                if mode == "native-backend":
+                    import gpubridge_b200.native_backend  # noqa: F401 - registers the name
+                dist.init_process_group("gpubridge" if mode == "backend" else "gpubridge_native",
+                                        init_method=f"file://{path}", rank=rank,
                                         world_size=world, timeout=timeout)
                 try:
                     out = fn(rank, world, *args)
