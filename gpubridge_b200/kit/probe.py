@@ -5,9 +5,11 @@
 Stages, each recorded in ``probe.json``: GPUs visible to PyTorch; every GPU is a Blackwell
 part the native library is built for (compute capability 10.x); the native library exists
 (or builds) and loads; its struct layouts match the bindings; the import resolves to this
-checkout; every pair of GPUs can address each other's memory (what the fused kernels need).
+checkout; every pair of GPUs can address each other's memory (what the fused kernels need);
+``CUDA_VISIBLE_DEVICES`` selects the GPU it names (a child that sees only the last GPU must
+find that GPU's PCI address at ``cuda:0`` - one process per GPU depends on it).
 A failed stage prints one line on stderr and the exit code is 1.  Same role as the
-reference's ``scripts/gpu/probe.py``.
+reference's ``scripts/gpu/probe.py``, ``import_check.py`` and ``device_map.py``.
 """
 from __future__ import annotations
 
@@ -16,6 +18,22 @@ import sys
 from pathlib import Path
 
 from gpubridge_b200.kit import Journal
+
+CHILD = ("import torch; p = torch.cuda.get_device_properties(0) if torch.cuda.device_count() else None; "
+         "print('pci=' + (f'{p.pci_bus_id:02x}:{p.pci_device_id:02x}' if p else 'none'))")
+
+
+def child_pci(visible: str, run=None) -> str:
+    """PCI address of ``cuda:0`` in a fresh process that sees only ``visible``."""
+    import os
+    import subprocess
+    run = run or subprocess.run
+    done = run([sys.executable, "-c", CHILD], env=dict(os.environ, CUDA_VISIBLE_DEVICES=visible),
+               capture_output=True, text=True, timeout=300)
+    for line in done.stdout.splitlines():
+        if line.startswith("pci="):
+            return line[4:]
+    raise RuntimeError(f"the child printed no address (exit code {done.returncode}): {done.stderr[-300:]}")
 
 
 def main(argv=None) -> int:
@@ -68,6 +86,22 @@ def main(argv=None) -> int:
             e["pairs_checked"] = count * (count - 1)
             if blocked:
                 fail(e, f"GPU pairs without peer access: {blocked[:8]} - the fused kernels need it")
+        else:
+            e["skipped"] = "fewer than two GPUs"
+    with journal.stage("device_map") as e:
+        if count >= 2:
+            import os
+            names = os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")
+            last = names[count - 1] if len(names) == count and names[0] else str(count - 1)
+            want = env["devices"][count - 1]["pci_bus_id"]
+            e["selected"], e["expected_pci"] = last, want
+            try:
+                e["child_pci"] = child_pci(last)
+                if e["child_pci"] != want:
+                    fail(e, f"CUDA_VISIBLE_DEVICES={last} gave the child the GPU at {e['child_pci']}, "
+                            f"not the one at {want}: ranks would not sit on the GPUs they are given")
+            except Exception as exc:  # noqa: BLE001
+                fail(e, f"{type(exc).__name__}: {exc}")
         else:
             e["skipped"] = "fewer than two GPUs"
     return journal.close()

@@ -146,3 +146,20 @@ def synthetic_tokens(config: LlamaConfig, batch: int, seq: int, seed: int = 0):
     g = torch.Generator().manual_seed(seed)
     tokens = torch.randint(config.vocab, (batch, seq + 1), generator=g)
     return tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()
+
+
+def rule_batch(config: LlamaConfig, step: int, rows: int, seq: int, seed: int = 0):
+    """The whole batch of training step ``step``: ``rows`` (input, target) sequences that are
+    the same whatever the world size, so runs at different scales see the same data and
+    their loss curves can be laid over each other.  The tokens follow a rule a model can
+    learn - each token is an affine function of the one before it plus one of four small
+    offsets - so the loss falls instead of sitting at log(vocab) as it does on uniform
+    noise.  Same purpose as the reference's ``global_batch`` (scripts/gpu/llama.py:170-184)."""
+    g = torch.Generator().manual_seed(seed * 1_000_003 + step)
+    first = torch.randint(config.vocab, (rows, 1), generator=g)
+    jitter = torch.randint(4, (rows, seq), generator=g)
+    columns = [first[:, 0]]
+    for i in range(seq):
+        columns.append((columns[-1] * 7 + 13 + jitter[:, i]) % config.vocab)
+    tokens = torch.stack(columns, dim=1)
+    return tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()

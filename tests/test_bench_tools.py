@@ -110,3 +110,57 @@ def test_train_bench_two_ranks(tmp_path):
             assert r["controlled"]["initial_parameters"] and r["dtype"] == "fp32" and r["split"] == "even"
         if "native" in extra:
             assert "stand-in" in r["note"]
+
+
+def test_recorded_train_dp_and_report(tmp_path):
+    """Same data at any scale: a single process, DDP with unequal shares and HSDP land on the
+    same loss curve, and the report lays them side by side."""
+    from gpubridge_b200.bench.train_dp import shares_for
+    from gpubridge_b200.kit import report
+    assert shares_for([1, 1, 1], 8) == [3, 3, 2] and shares_for([3.0, 1.0], 8) == [6, 2]
+    assert sum(shares_for([0.7, 1.9, 1.1], 17)) == 17 and min(shares_for([100.0, 1.0], 5)) == 1
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1", GPUBRIDGE_VENDOR="nvidia",
+               GPUBRIDGE_SPLIT_TEST="half")
+    runs = tmp_path / "runs"
+    runs.mkdir()
+    for port, ranks, mode, extra in ((29751, 1, "single", ["--micro", "3"]),
+                                     (29752, 2, "ddp", ["--shares", "5,3"]),
+                                     (29754, 4, "hsdp", [])):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "gpubridge_b200.bench.train_dp",
+               "--model", "llama-tiny", "--mode", mode, "--seq", "16", "--steps", "6", "--warmup", "1",
+               "--global-batch", "8", "--check-every", "3", "--lr", "3e-3", *extra,
+               "--json", str(runs / f"dp_{mode}.json")]
+        done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=400)
+        assert done.returncode == 0, done.stderr[-3000:]
+    got = {m: json.loads((runs / f"dp_{m}.json").read_text()) for m in ("single", "ddp", "hsdp")}
+    assert got["ddp"]["shares"] == [5, 3] and got["ddp"]["parameters_identical"] is True
+    assert got["hsdp"]["parameters_identical"] is True and len(got["hsdp"]["parameter_checks"]) == 2
+    for mode in ("ddp", "hsdp"):
+        gaps = [abs(a - b) for a, b in zip(got[mode]["losses"], got["single"]["losses"])]
+        assert max(gaps) < 1e-4, (mode, gaps)
+    assert got["single"]["losses"][-1] < got["single"]["losses"][0]
+    assert report.main(["dp", str(runs), "--out", str(tmp_path / "rep"), "--tail", "3"]) == 0
+    text = (tmp_path / "rep" / "dp_report.md").read_text()
+    assert "(baseline)" in text and "[5, 3]" in text and "| yes |" in text
+    assert (tmp_path / "rep" / "loss_curves.csv").read_text().count("\n") == 8
+    assert (tmp_path / "rep" / "loss_curves.svg").read_text().count("<polyline") == 3
+
+
+def test_ddp_divergence_report(tmp_path, capsys):
+    from gpubridge_b200.kit import report
+    base = {"world_size": 2, "engine": "ddp", "samples_per_sec": 10.0, "params_in_sync": True,
+            "first_gradient_difference": None, "first_parameter_difference": None}
+    rows = {"a": base, "b": {**base, "params_in_sync": False, "first_gradient_difference": 3,
+                             "first_parameter_difference": 3},
+            "c": {**base, "params_in_sync": False, "first_parameter_difference": 7},
+            "old": {"world_size": 2, "samples_per_sec": 1.0, "params_in_sync": True}}
+    for name, row in rows.items():
+        (tmp_path / f"{name}.json").write_text(json.dumps(row))
+    assert report.main(["ddp", str(tmp_path), "--out", str(tmp_path / "o")]) == 1
+    text = capsys.readouterr().out
+    assert "| a | 2 | ddp | - | 10.0 | - | - | in sync |" in text
+    assert "step 3 | step 3 | gradients differ after all_reduce" in text
+    assert "| - | step 7 | parameters differ, gradients equal" in text
+    assert "no per-step check" in text and "2 of 4 runs in sync" in text
+    assert (tmp_path / "o" / "train_ddp_report.md").exists()
