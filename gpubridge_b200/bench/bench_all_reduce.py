@@ -18,6 +18,7 @@ Targets: ``ours`` (the active policy), ``nccl`` (one NCCL communicator of every 
 from __future__ import annotations
 
 import argparse
+import os
 import json
 import statistics
 import sys
@@ -134,12 +135,14 @@ def main(argv=None) -> int:
     ap.add_argument("--seconds", type=float, default=20.0)
     ap.add_argument("--inner", type=int, default=1, help="back-to-back calls per trial")
     ap.add_argument("--json", default="")
+    ap.add_argument("--bridge", default=os.environ.get("GPUBRIDGE_BRIDGE", "").strip() or None,
+                    help="bridge transport between islands (default: GPUBRIDGE_BRIDGE, else init()'s choice)")
     ap.add_argument("--write-thresholds", default="")
     args = ap.parse_args(argv)
 
     with warnings.catch_warnings():
         warnings.simplefilter("ignore", gb.SplitTestWarning)
-        topology = gb.init()
+        topology = gb.init(**({"bridge": args.bridge} if args.bridge else {}))
     rank, world = topology.rank, topology.world_size
     rows = []
     try:

@@ -74,7 +74,8 @@ def main(argv=None) -> int:
     ap.add_argument("--timeout", type=float, default=default_timeout(600))
     ap.add_argument("--dtypes", default=",".join(DTYPES))
     ap.add_argument("--policy", default="auto")
-    ap.add_argument("--bridge", default=None, help="bridge transport (default: init()'s choice)")
+    ap.add_argument("--bridge", default=os.environ.get("GPUBRIDGE_BRIDGE", "").strip() or None,
+                    help="bridge transport (default: GPUBRIDGE_BRIDGE, else init()'s choice)")
     ap.add_argument("--p2p-only", action="store_true")
     ap.add_argument("--large-numel", type=int, default=None)
     ap.add_argument("--busy-seconds", type=float, default=0.05)

@@ -1,4 +1,6 @@
-"""pytest configuration: the ``gpu`` marker, and a clean environment for every test."""
+"""pytest configuration: the ``gpu`` marker, a clean environment for every test, and shards
+(``GPUBRIDGE_TEST_SHARD=K/N`` keeps every N-th test file, starting with the K-th, so that a
+CI matrix of N jobs runs the suite once between them)."""
 import os
 import sys
 
@@ -20,7 +22,22 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA GPU (run with pytest -m gpu on a B200)")
 
 
+def shard_of(files: list[str], spec: str) -> set[str]:
+    """The files of shard ``K/N`` (K from 1): round-robin over the sorted names, so shards
+    stay balanced as files are added."""
+    k, n = (int(v) for v in spec.split("/"))
+    if not 1 <= k <= n:
+        raise ValueError(f"GPUBRIDGE_TEST_SHARD={spec}: want K/N with 1 <= K <= N")
+    return {f for i, f in enumerate(sorted(set(files))) if i % n == k - 1}
+
+
 def pytest_collection_modifyitems(config, items):
+    spec = os.environ.get("GPUBRIDGE_TEST_SHARD", "").strip()
+    if spec:
+        keep = shard_of([str(item.fspath) for item in items], spec)
+        dropped = [item for item in items if str(item.fspath) not in keep]
+        items[:] = [item for item in items if str(item.fspath) in keep]
+        config.hook.pytest_deselected(items=dropped)
     import torch
     if torch.cuda.is_available():
         return

@@ -265,3 +265,14 @@ def test_utils_clock_summary_and_timing():
     ms = device_time(lambda n: calls.append(n), 7, torch.device("cpu"), barrier=lambda: calls.append("b"))
     assert calls == ["b", 7, "b"] and ms >= 0
     assert max_over_ranks(3.5) == 3.5 and human_bytes(4 << 20) == "4M" and human_bytes(1000) == "1000"
+
+
+def test_shards_cover_every_file_once():
+    from conftest import shard_of
+    files = [f"tests/test_{i}.py" for i in range(11)]
+    shards = [shard_of(files, f"{k}/4") for k in range(1, 5)]
+    assert set().union(*shards) == set(files) and sum(len(s) for s in shards) == len(files)
+    assert max(len(s) for s in shards) - min(len(s) for s in shards) <= 1
+    import pytest
+    with pytest.raises(ValueError):
+        shard_of(files, "5/4")
