@@ -195,3 +195,39 @@ def test_triage_puts_problems_first(tmp_path, capsys):
     assert len(short) == 6 and short[-1].startswith("verdict") and "more lines" in short[-2]
     (tmp_path / "empty").mkdir()
     assert triage.main([str(tmp_path / "empty")]) == 2
+
+
+def test_validation_tables_never_count_simulation(tmp_path, capsys):
+    """Two fabricated jobs: a CPU-simulation job that passed everything and a GPU job with one
+    failed stage.  Items the simulation alone covers read "simulation only"; the GPU job's
+    failure makes its item FAILED; hosts are numbered."""
+    from gpubridge_b200.kit import validation_tables
+
+    def job(name, cuda, bad_stage=None, extra_steps=()):
+        d = tmp_path / "results" / name
+        (d / "check-half").mkdir(parents=True)
+        (d / "probe").mkdir()
+        env = {"hostname": f"secret-{name}", "cuda_available": cuda, "device_count": 8 if cuda else 0,
+               "devices": [{"name": "NVIDIA B200"}] * (8 if cuda else 0), "torch": "2.11", "torch_cuda": "12.8",
+               "nccl": "2.28.9", "gpubridge_b200": "0.1.0", "env": {} if cuda else {"GPUBRIDGE_VENDOR": "nvidia"}}
+        rows = [{"step": s, "ok": True, "exit_code": 0, "seconds": 1, "log": f"{s}.log"}
+                for s in ("probe", "check-half", "summary-half", "sweep", *extra_steps)]
+        (d / "steps.jsonl").write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+        stages = {s: {"0": True, "1": s != bad_stage} for s in ("init", "device", "dtypes", "broadcast", "barrier", "destroy")}
+        (d / "check-half" / "summary.json").write_text(json.dumps({"ok": bad_stage is None, "stages": stages, "ranks_missing": []}))
+        (d / "check-half" / "rank0.json").write_text(json.dumps({"environment": env}))
+        (d / "probe" / "probe.json").write_text(json.dumps({"environment": env}))
+        (d / "sweep.json").write_text(json.dumps([{"bytes": 1 << 20, "target": "ours", "ms": 0.02, "busbw_gbs": 90.0},
+                                                  {"bytes": 1 << 20, "target": "nccl", "ms": 0.03, "busbw_gbs": 60.0}]))
+
+    job("sim", cuda=False, extra_steps=("p2p",))
+    job("gpu", cuda=True, bad_stage="dtypes")
+    assert validation_tables.main([str(tmp_path / "results")]) == 1
+    text = capsys.readouterr().out
+    assert "secret" not in text and "host 1" in text and "host 2" in text
+    assert "| sim | CPU simulation | 5 |" in text and "| gpu | GPU | 4 |" in text and "8 x NVIDIA B200" in text
+    data = json.loads((tmp_path / "results" / "validation_tables.json").read_text())
+    verdicts = {i["item"]: i["verdict"] for i in data["items"]}
+    assert verdicts["dtypes"] == "FAILED" and verdicts["discovery"] == "passed"
+    assert verdicts["p2p"] == "simulation only" and verdicts["numerics"] == "not run"
+    assert {(b["job"], b["speed_vs_nccl"]) for b in data["benchmarks"]} == {("sim", 1.5), ("gpu", 1.5)}
