@@ -278,6 +278,19 @@ class GbBackend : public c10d::Backend {
         py::gil_scoped_acquire gil;
         return hold(fallback_.attr("barrier")(opts));
     }
+    // Coalescing (batch_isend_irecv, coalesced collectives) is the Python group's: while a
+    // batch is open every call goes there, so that it sees the whole batch.
+    bool supportsCoalescing() const override { return true; }
+    void startCoalescing() override {
+        coalescing_.store(true);
+        py::gil_scoped_acquire gil;
+        fallback_.attr("_start_coalescing")(py::none());
+    }
+    c10::intrusive_ptr<c10d::Work> endCoalescing() override {
+        coalescing_.store(false);
+        py::gil_scoped_acquire gil;
+        return hold(fallback_.attr("_end_coalescing")(py::none()));
+    }
     void shutdown() override {
         forget();
         py::gil_scoped_acquire gil;
@@ -305,7 +318,7 @@ class GbBackend : public c10d::Backend {
 
     // The team when every tensor can go down the native path, else null.
     const NativeTeam* native_for(const std::vector<at::Tensor>& tensors) {
-        if (tensors.empty()) return nullptr;
+        if (tensors.empty() || coalescing_.load()) return nullptr;
         for (const auto& t : tensors)
             if (!t.is_cuda() || !t.is_contiguous() || dtype_code(t.scalar_type()) < 0) return nullptr;
         {
@@ -373,6 +386,7 @@ class GbBackend : public c10d::Backend {
     bool asked_ = false;
     NativeTeam team_;
     std::atomic<uint64_t> native_calls_{0}, fallback_calls_{0};
+    std::atomic<bool> coalescing_{false};
 };
 
 }  // namespace

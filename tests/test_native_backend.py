@@ -49,6 +49,12 @@ RANKS = textwrap.dedent('''
             dist.send(torch.tensor([7.]), 1)
         elif r == 1:
             x = torch.zeros(1); dist.recv(x, 0); assert x.item() == 7
+        peer = r ^ 1
+        got = torch.zeros(3)
+        ops = [dist.P2POp(dist.isend, torch.full((3,), float(r)), peer), dist.P2POp(dist.irecv, got, peer)]
+        for w_ in dist.batch_isend_irecv(ops):        # torch's own helper: the backend coalesces
+            w_.wait()
+        assert got.tolist() == [float(peer)] * 3
         sub = dist.new_group([0, 1])
         if r < 2:
             s = torch.ones(2) * (r + 1); dist.all_reduce(s, group=sub); assert s[0] == 3
