@@ -32,6 +32,7 @@ class LlamaConfig:
 
 CONFIGS = {
     "llama-tiny": LlamaConfig(2, 64, 4, 2, 176, 256, 64),
+    "llama-mini": LlamaConfig(4, 64, 4, 2, 176, 256, 64),          # four blocks: pipelines of up to four stages on CPU
     "llama-125m": LlamaConfig(12, 768, 12, 12, 2048, 32000, 2048),
     "llama-350m": LlamaConfig(24, 1024, 16, 16, 2816, 32000, 2048),
     "llama-1b": LlamaConfig(16, 2048, 32, 8, 8192, 32000, 2048),

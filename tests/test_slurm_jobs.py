@@ -75,3 +75,25 @@ def test_a_failing_step_is_recorded_and_the_job_goes_on(cluster, tmp_path):
     assert [journal[s]["ok"] for s in ("good", "bad", "slow", "after")] == [True, False, False, True]
     assert journal["bad"]["exit_code"] == 3 and journal["slow"]["exit_code"] is None
     assert "step bad: FAILED (exit code 3" in done.stdout and "step slow: FAILED (ran past its limit" in done.stdout
+
+
+def test_two_machines_without_a_scheduler(cluster, tmp_path):
+    """node.sh on "both machines" at once (this one, twice): each side's host name is made up,
+    so the two sides form two islands joined by the host bridge."""
+    out = tmp_path / "pair"
+    sides = []
+    for node in (0, 1):
+        env = dict(cluster, NODE_RANK=str(node), MASTER_ADDR="127.0.0.1", OUT=str(out), GPUS="2",
+                   MASTER_PORT="29640", PREFLIGHT_SECONDS="0.3", SWEEP_LARGEST="256K",
+                   GPUBRIDGE_SIM_HOSTNAME=f"machine-{node}")
+        sides.append(subprocess.Popen([os.path.join(SLURM, "node.sh")], env=env, cwd=tmp_path,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    texts = [side.communicate(timeout=1200)[0] for side in sides]
+    assert [side.returncode for side in sides] == [0, 0], texts
+    for node in (0, 1):
+        journal = steps(out / f"node{node}")
+        assert list(journal) == ["preflight", "check-gloo", "check-multitcp", "sweep"]
+        assert all(row["ok"] for row in journal.values()), texts[node]
+    record = json.loads((out / "check-multitcp" / "rank3.json").read_text())
+    assert record["run"]["bridge"] == "multitcp"
+    assert [i["ranks"] for i in record["run"]["islands"]] == [[0, 1], [2, 3]]
