@@ -11,7 +11,9 @@ and async calls, without an observer and with one that does nothing, every rank 
 drift spreads evenly; rank 0's medians are reported next to one plain all-reduce on the
 world's host communicator.  ``--stub-comm`` makes every communicator call return at once
 after start-up, leaving checks, policy dispatch, phases and (async) the worker thread.
-Counterpart of the reference's ``scripts/bench_per_call.py``.
+``--profile N`` adds, for rank 0, the N functions with the most own time over one more round of
+synchronous calls (cProfile; the profiler itself makes every call slower, so read shares, not
+absolutes).  Counterpart of the reference's ``scripts/bench_per_call.py``.
 """
 from __future__ import annotations
 
@@ -38,7 +40,22 @@ def _stub() -> None:
         setattr(groups.Comm, name, lambda self, *a, **k: None)
 
 
-def _rank(rank: int, vendors, policies, calls, rounds, stub, rendezvous, out) -> None:
+def _hot_functions(fn, calls: int, top: int) -> list[dict]:
+    import cProfile
+    import pstats
+    profiler = cProfile.Profile()
+    profiler.enable()
+    for _ in range(calls):
+        fn()
+    profiler.disable()
+    stats = pstats.Stats(profiler)
+    rows = sorted(stats.stats.items(), key=lambda kv: -kv[1][2])[:top]          # by own time
+    return [{"function": f"{os.path.basename(file)}:{line}({name})", "calls_per_call": round(nc / calls, 2),
+             "own_us_per_call": round(tt / calls * 1e6, 2), "cumulative_us_per_call": round(ct / calls * 1e6, 2)}
+            for (file, line, name), (cc, nc, tt, ct, _) in rows]
+
+
+def _rank(rank: int, vendors, policies, calls, rounds, stub, rendezvous, out, profile=0) -> None:
     os.environ["GPUBRIDGE_VENDOR"] = vendors[rank]
     import gpubridge_b200 as gb
 
@@ -75,13 +92,19 @@ def _rank(rank: int, vendors, policies, calls, rounds, stub, rendezvous, out) ->
                     topo.cpu_group.all_reduce(t, "sum")
                 results.setdefault(f"{policy}/bare-world-call", []).append(
                     (time.perf_counter() - start) / calls)
+        if profile:
+            # every rank makes the calls (they are collectives); rank 0 keeps the profile
+            hot = _hot_functions(lambda: gb.all_reduce(t), calls, profile)
+            if rank == 0:
+                results[f"{policy}/profile"] = hot
         gb.destroy()
         if stub:
             import importlib
             from gpubridge_b200 import groups
             importlib.reload(groups)
     if rank == 0:
-        Path(out).write_text(json.dumps({k: statistics.median(v) * 1e6 for k, v in results.items()}))
+        Path(out).write_text(json.dumps({k: v if k.endswith("/profile") else statistics.median(v) * 1e6
+                                         for k, v in results.items()}))
 
 
 def main(argv=None) -> int:
@@ -91,6 +114,8 @@ def main(argv=None) -> int:
     ap.add_argument("--calls", type=int, default=200)
     ap.add_argument("--rounds", type=int, default=5)
     ap.add_argument("--stub-comm", action="store_true")
+    ap.add_argument("--profile", type=int, default=0, metavar="N",
+                    help="rank 0: the N functions with the most own time per synchronous call")
     ap.add_argument("--out", type=Path)
     args = ap.parse_args(argv)
     set_now = [name for name in SETTINGS if os.environ.get(name)]
@@ -105,14 +130,19 @@ def main(argv=None) -> int:
     with tempfile.TemporaryDirectory() as tmp:
         result = os.path.join(tmp, "result.json")
         mp.spawn(_rank, args=(vendors, policies, args.calls, args.rounds, args.stub_comm,
-                              os.path.join(tmp, "rdv"), result), nprocs=len(vendors))
+                              os.path.join(tmp, "rdv"), result, args.profile), nprocs=len(vendors))
         medians = json.loads(Path(result).read_text())
+    profiles = {k: medians.pop(k) for k in [k for k in medians if k.endswith("/profile")]}
     record = {"vendors": vendors, "calls": args.calls, "rounds": args.rounds,
               "stub_comm": args.stub_comm, "torch": torch.__version__,
-              "cpus": os.cpu_count(), "us_per_call": medians}
+              "cpus": os.cpu_count(), "us_per_call": medians, "profiles": profiles}
     print(f"{'case':<48} us per call")
     for key, value in medians.items():
         print(f"{key:<48} {value:9.1f}")
+    for key, rows in profiles.items():
+        print(f"\n{key}: own time per call")
+        for row in rows:
+            print(f"  {row['own_us_per_call']:8.2f} us  x{row['calls_per_call']:<5} {row['function']}")
     if args.out:
         args.out.parent.mkdir(parents=True, exist_ok=True)
         args.out.write_text(json.dumps(record, indent=1))

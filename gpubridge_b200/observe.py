@@ -14,6 +14,7 @@ observer sees "island-reduce / bridge / island-broadcast" although one launch ra
 from __future__ import annotations
 
 import abc
+import os
 import threading
 import time
 import warnings
@@ -206,6 +207,31 @@ def _mark(device: torch.device | None) -> Mark:
     return Mark(time.perf_counter_ns(), event)
 
 
+def _nvtx_setting():
+    """``torch.cuda.nvtx`` when ``GPUBRIDGE_NVTX=1`` and the build has it, else None.  Ranges
+    named ``gpubridge.<op> <bytes>`` (and ``gpubridge.<phase>`` inside them) then show every
+    collective on the host timeline of a profiler that reads NVTX."""
+    if os.environ.get("GPUBRIDGE_NVTX", "0") != "1":
+        return None
+    try:
+        from torch.cuda import nvtx
+        nvtx.range_push("gpubridge.nvtx-check")
+        nvtx.range_pop()
+        return nvtx
+    except Exception:  # noqa: BLE001 - a build without NVTX: ranges are an extra, never an error
+        return None
+
+
+_nvtx = _nvtx_setting()
+
+
+def reload_nvtx() -> bool:
+    """Read ``GPUBRIDGE_NVTX`` again (it is read once, at import); True when ranges are on."""
+    global _nvtx
+    _nvtx = _nvtx_setting()
+    return _nvtx is not None
+
+
 class collective:  # noqa: N801 - used as ``with collective(...)``
     """Count one validated collective, list it as in flight, record it if watched."""
 
@@ -227,6 +253,8 @@ class collective:  # noqa: N801 - used as ``with collective(...)``
         f.ident, f.since = threading.get_ident(), time.monotonic()
         _table[f.ident] = f
         _local.flight = f
+        if _nvtx is not None:
+            _nvtx.range_push(f"gpubridge.{f.op} {0 if self.tensor is None else self.tensor.nbytes}")
         if f.watched:
             self.start = _mark(f.device)
 
@@ -234,6 +262,8 @@ class collective:  # noqa: N801 - used as ``with collective(...)``
         f = self.flight
         _table.pop(f.ident, None)
         _local.flight = None
+        if _nvtx is not None:
+            _nvtx.range_pop()
         if exc_type is not None or not f.watched:
             return
         t = self.tensor
@@ -259,12 +289,16 @@ class _PhaseScope:
     def __enter__(self) -> None:
         f = self.flight
         self.outer, f.phase = f.phase, self.name
+        if _nvtx is not None:
+            _nvtx.range_push(f"gpubridge.{self.name}")
         if f.watched:
             self.start = _mark(f.device)
 
     def __exit__(self, exc_type, *exc) -> None:
         f = self.flight
         f.phase = self.outer
+        if _nvtx is not None:
+            _nvtx.range_pop()
         f.done = (*f.done, self.name)
         if exc_type is None and f.watched:
             f.phases.append(Phase(self.name, self.start, _mark(f.device)))

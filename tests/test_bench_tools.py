@@ -40,11 +40,23 @@ def test_per_call_table(tmp_path):
     out = tmp_path / "per_call.json"
     done = subprocess.run([sys.executable, "-m", "gpubridge_b200.bench.bench_per_call", "--calls", "20",
                            "--rounds", "1", "--stub-comm", "--policies", "reduce-bridge-broadcast",
-                           "--out", str(out)], env=env, cwd=ROOT, capture_output=True, text=True,
+                           "--profile", "4", "--out", str(out)], env=env, cwd=ROOT, capture_output=True, text=True,
                           timeout=300)
     assert done.returncode == 0, done.stderr[-3000:]
     record = json.loads(out.read_text())
     assert record["stub_comm"] and "reduce-bridge-broadcast/sync/plain" in record["us_per_call"]
+    hot = record["profiles"]["reduce-bridge-broadcast/profile"]
+    assert len(hot) == 4 and all(row["own_us_per_call"] > 0 for row in hot)
+    assert any("all_reduce" in row["function"] for row in hot)
+
+
+def test_import_time_bench(tmp_path):
+    from gpubridge_b200.bench import bench_import
+    out = tmp_path / "import.json"
+    assert bench_import.main(["--runs", "1", "--out", str(out)]) == 0
+    record = json.loads(out.read_text())
+    assert record["with_package_s"] > 0 and record["slowest_modules"]
+    assert all(row["module"].startswith("gpubridge_b200") for row in record["slowest_modules"])
 
 
 def test_train_bench_shares():

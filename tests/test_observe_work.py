@@ -189,3 +189,37 @@ def test_marks_that_arrive_later():
     assert flight.phases[0].end.ready()
     assert flight.phases[0].elapsed_ms() == 2.5 and flight.phases[1].elapsed_ms() == 0.5
     assert observe.Mark(0, None, 7).ns() == 7 and observe.Mark(0).ns() is None
+
+
+def _nvtx_ranges(rank, topology):
+    import gpubridge_b200 as gb
+    from gpubridge_b200 import observe
+
+    class Recorder:
+        def __init__(self):
+            self.events, self.depth = [], 0
+
+        def range_push(self, name):
+            self.depth += 1
+            self.events.append(("push", name, self.depth))
+
+        def range_pop(self):
+            self.events.append(("pop", None, self.depth))
+            self.depth -= 1
+
+    recorder = observe._nvtx = Recorder()
+    try:
+        gb.all_reduce(torch.ones(10))
+        gb.broadcast(torch.ones(4), 0)
+    finally:
+        observe._nvtx = None
+    return recorder.events, recorder.depth
+
+
+def test_nvtx_ranges_bracket_collectives_and_phases(tmp_path):
+    events, depth = run_ranks(("nvidia", "amd"), _nvtx_ranges, tmp_path)[0]
+    assert depth == 0 and len([e for e in events if e[0] == "push"]) == len([e for e in events if e[0] == "pop"])
+    names = [name for kind, name, _ in events if kind == "push"]
+    assert names[0] == "gpubridge.all_reduce 40" and "gpubridge.broadcast 16" in names
+    inner = [name for kind, name, level in events if kind == "push" and level == 2]
+    assert "gpubridge.bridge" in inner           # phases nest inside their collective
