@@ -24,14 +24,17 @@ class AllGatherLinear:
     single rank works too: then this is a plain tcgen05 GEMM)."""
 
     def __init__(self, fabric, out_features: int, in_features: int, comm_blocks: int = 16,
-                 pair: bool | None = None) -> None:
+                 pair: bool | None = None, gathered: torch.Tensor | None = None) -> None:
         if out_features % fabric.world:
             raise ValueError("out_features must divide evenly over the team")
         if in_features % 8:
             raise ValueError("in_features must be a multiple of 8 (16-byte rows for TMA)")
         self.fabric, self.N, self.K = fabric, out_features, in_features
         device = fabric.device
-        self.gathered = torch.empty((out_features, in_features), dtype=torch.bfloat16, device=device)
+        # ``gathered``: a caller-owned [out, in] bf16 buffer (layers of one shape can share it)
+        self.gathered = (torch.empty((out_features, in_features), dtype=torch.bfloat16, device=device)
+                         if gathered is None else gathered)
+        assert self.gathered.shape == (out_features, in_features) and self.gathered.is_contiguous()
         self.flags = torch.zeros(fabric.world, dtype=torch.int32, device=device)
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
         self.epoch = 0

@@ -5,10 +5,18 @@ Stock FSDP2 runs ``all_gather_into_tensor(weight shards)`` and then ``F.linear``
 src/gpubridge/torch_backend.py:271-285 carries the all-gather).  Here, on GPUs that share a
 fabric, forward is one kernel (``csrc/gb_gemm*.cu``): communication CTAs bring the peers'
 shards over NVLink while tcgen05 GEMM CTAs already multiply the local shard, and take each
-remote shard as soon as its flag is up.  Backward reuses the gathered weight that forward
-left in local memory for ``dX = dY @ W`` and reduce-scatters ``dW = dY^T @ X`` so that every
-rank ends with the averaged gradient of its own rows.  Without a fabric (CPU simulation,
-several hosts) the same module all-gathers through the collectives and calls ``F.linear``.
+remote shard as soon as its flag is up.  Backward needs the whole weight once more for
+``dX = dY @ W`` and reduce-scatters ``dW = dY^T @ X`` so that every rank ends with the
+averaged gradient of its own rows.  Without a fabric (CPU simulation, several hosts) the same
+module all-gathers through the collectives and calls ``F.linear``.
+
+Memory is what makes sharding worth it, so the gathered weight is not the layer's: layers of
+one shape (and dtype) on one topology share one *slot*, the way FSDP2 reshards after forward.
+Forward gathers into the slot and marks it as this call's; backward uses it as it is when
+nothing else has gathered into it since (the last layer of a stack, a layer on its own) and
+gathers again otherwise (one fused copy kernel over NVLink).  A stack of L equal layers holds
+one whole weight, not L.  ``reshard_after_forward=False`` gives a layer a slot of its own:
+no second gather, a whole weight resident per layer.
 
     layer = ShardedLinear(4096, 14336)          # every rank holds 14336 / world rows
     y = layer(x)                                # x: [tokens, 4096], y: [tokens, 14336]
@@ -16,6 +24,7 @@ several hosts) the same module all-gathers through the collectives and calls ``F
 from __future__ import annotations
 
 import math
+import weakref
 
 import torch
 from torch import nn
@@ -25,21 +34,52 @@ from gpubridge_b200 import collectives
 from gpubridge_b200.topology import Topology, get_topology, is_initialized
 
 
+class GatherSlot:
+    """One whole weight's worth of memory and the record of whose gather it holds."""
+
+    def __init__(self, topology) -> None:
+        self.topology = weakref.ref(topology) if topology is not None else None
+        self.buffer: torch.Tensor | None = None
+        self.op = None                      # the fused all-gather GEMM site bound to ``buffer``
+        self.holder: object | None = None   # token of the forward call whose weight is in it
+        self.gathers = 0                    # gathers into this slot, forward and backward (tests)
+
+
+_slots: dict[tuple, GatherSlot] = {}
+
+
+def _slot_for(topology, key: tuple) -> GatherSlot:
+    """The shared slot of ``key`` on ``topology``.  The table is keyed by the topology's id;
+    the weak reference tells a live topology from a new one that got a dead one's id."""
+    full_key = (id(topology), *key)
+    slot = _slots.get(full_key)
+    if slot is None or (slot.topology is not None and slot.topology() is not topology):
+        slot = _slots[full_key] = GatherSlot(topology)
+    return slot
+
+
+def release_slots(topology=None) -> None:
+    """Drop the shared slots of ``topology`` (all of them by default): frees their memory."""
+    for key in [k for k in _slots if topology is None or k[0] == id(topology)]:
+        del _slots[key]
+
+
 class _FusedForward(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, shard, layer):
         x2 = x.reshape(-1, x.shape[-1])
-        y = layer._gemm(x2.contiguous(), shard.contiguous())
+        ctx.token = object()
+        y = layer._gemm(x2.contiguous(), shard.contiguous(), ctx.token)
         ctx.layer = layer
-        ctx.save_for_backward(x2)
+        ctx.save_for_backward(x2, shard)
         return y.view(*x.shape[:-1], y.shape[-1])
 
     @staticmethod
     def backward(ctx, dy):
         layer = ctx.layer
-        (x2,) = ctx.saved_tensors
+        x2, shard = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
-        weight = layer._gathered()                       # left in local memory by forward
+        weight = layer._gathered(shard, ctx.token)       # still in the slot, or gathered again
         dx = (dy2 @ weight).view(*dy.shape[:-1], weight.shape[1]) if ctx.needs_input_grad[0] else None
         dshard = None
         if ctx.needs_input_grad[1]:
@@ -54,7 +94,8 @@ class ShardedLinear(nn.Module):
     owns (what FSDP2's reduce-scatter leaves)."""
 
     def __init__(self, in_features: int, out_features: int, *, topology: Topology | None = None,
-                 device=None, dtype=torch.bfloat16, seed: int = 0) -> None:
+                 device=None, dtype=torch.bfloat16, seed: int = 0,
+                 reshard_after_forward: bool = True) -> None:
         super().__init__()
         if topology is None and is_initialized():
             topology = get_topology()
@@ -71,8 +112,8 @@ class ShardedLinear(nn.Module):
         g = torch.Generator().manual_seed(seed)
         full = torch.empty(out_features, in_features).uniform_(-1, 1, generator=g) / math.sqrt(in_features)
         self.weight = nn.Parameter(full[self.rank * rows:(self.rank + 1) * rows].to(device=device, dtype=dtype))
-        self._op = None
-        self._full = None
+        self.reshard_after_forward = reshard_after_forward
+        self._own_slot = None if reshard_after_forward else GatherSlot(topology)
 
     # -- the three pieces ---------------------------------------------------------------------
     def _fused(self) -> bool:
@@ -80,22 +121,44 @@ class ShardedLinear(nn.Module):
         return (fabric is not None and self.weight.is_cuda and self.weight.dtype == torch.bfloat16
                 and self.in_features % 8 == 0)
 
-    def _gemm(self, x2: torch.Tensor, shard: torch.Tensor) -> torch.Tensor:
-        if self._fused():
-            if self._op is None:
-                from gpubridge_b200.ops.gemm import AllGatherLinear
-                self._op = AllGatherLinear(self.topology.fabric, self.out_features, self.in_features)
-            return self._op(x2.to(torch.bfloat16), shard)
-        if self.world == 1:
-            self._full = shard
-        else:
-            self._full = torch.empty((self.out_features, self.in_features), dtype=shard.dtype,
-                                     device=shard.device)
-            collectives.all_gather_into_tensor(self._full, shard, _topology=self.topology)
-        return torch.nn.functional.linear(x2, self._full)
+    def _slot(self) -> GatherSlot:
+        if self._own_slot is not None:
+            return self._own_slot
+        return _slot_for(self.topology, (self.out_features, self.in_features, self.weight.dtype,
+                                         str(self.weight.device), self._fused()))
 
-    def _gathered(self) -> torch.Tensor:
-        return self._op.gathered if self._op is not None else self._full
+    def _buffer(self, slot: GatherSlot) -> torch.Tensor:
+        if slot.buffer is None:
+            slot.buffer = torch.empty((self.out_features, self.in_features), dtype=self.weight.dtype,
+                                      device=self.weight.device)
+        return slot.buffer
+
+    def _gemm(self, x2: torch.Tensor, shard: torch.Tensor, token: object) -> torch.Tensor:
+        if self.world == 1 and not self._fused():
+            return torch.nn.functional.linear(x2, shard)
+        slot = self._slot()
+        full = self._buffer(slot)
+        slot.holder, slot.gathers = token, slot.gathers + 1
+        if self._fused():
+            if slot.op is None:
+                from gpubridge_b200.ops.gemm import AllGatherLinear
+                slot.op = AllGatherLinear(self.topology.fabric, self.out_features, self.in_features,
+                                          gathered=full)
+            return slot.op(x2.to(torch.bfloat16), shard)
+        collectives.all_gather_into_tensor(full, shard, _topology=self.topology)
+        return torch.nn.functional.linear(x2, full)
+
+    def _gathered(self, shard: torch.Tensor, token: object) -> torch.Tensor:
+        """The whole weight for backward: what forward left in the slot if it is still this
+        call's, else gathered again."""
+        if self.world == 1 and not self._fused():
+            return shard
+        slot = self._slot()
+        full = self._buffer(slot)
+        if slot.holder is not token:
+            collectives.all_gather_into_tensor(full, shard.contiguous(), _topology=self.topology)
+            slot.holder, slot.gathers = token, slot.gathers + 1
+        return full
 
     def _scatter_gradient(self, dw: torch.Tensor) -> torch.Tensor:
         if self.world == 1:

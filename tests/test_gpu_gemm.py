@@ -89,8 +89,10 @@ def _fused_on_a_team(rank, topology):
     y = layer(x)
     y.float().square().sum().backward()
     torch.cuda.synchronize(dev)
-    assert layer._op is not None, "the fused kernel must be the path under test"
-    whole = layer._gathered().float().cpu()
+    slot = layer._slot()
+    assert slot.op is not None, "the fused kernel must be the path under test"
+    assert slot.gathers == 1, "a layer on its own reuses what forward left in the slot"
+    whole = slot.buffer.float().cpu()
     xs = x.detach().float().cpu()
     assert torch.allclose(y.float().cpu(), xs @ whole.t(), atol=5e-2, rtol=2e-2)
     dy = (2 * y.detach().float()).to(torch.bfloat16).float().cpu()
