@@ -1,7 +1,9 @@
 """Data-parallel training throughput of the Llama-style models through backend="gpubridge":
-``ddp``, ``fsdp2`` (``fully_shard`` on a 1-D mesh) and ``hsdp`` (shard inside an island,
+``ddp``, ``fsdp2`` (``fully_shard`` on a 1-D mesh), ``hsdp`` (shard inside an island,
 replicate across islands; the cross-island gradient all-reduce is the compressed one when
-``GPUBRIDGE_BRIDGE_COMPRESSION`` is set).  Counterpart of the reference's
+``GPUBRIDGE_BRIDGE_COMPRESSION`` is set) and ``fused`` (recorded runs: this library's own
+sharding - every block's Linear layers become ``ShardedLinear``, whose all-gather is fused
+into the tcgen05 GEMM; the rest stays replicated and is averaged with one all-reduce).  Counterpart of the reference's
 scripts/gpu/train_dp.py.
 
     GPUBRIDGE_ISLANDS=4,4 GPUBRIDGE_BRIDGE_COMPRESSION=fp8 GPUBRIDGE_CODEC_FORMAT=b200 \
@@ -97,6 +99,16 @@ def recorded(args) -> int:
         from torch.nn.parallel import DistributedDataParallel as DDP
         model = DDP(model, device_ids=[local] if on_gpu else None)
         replicas = dist.group.WORLD
+    elif args.mode == "fused":
+        from gpubridge_b200.parallel.sharded_model import ReplicatedSync, shard_linears
+        if args.backend != "gpubridge":
+            raise SystemExit("--mode fused runs on the gpubridge backend")
+        if on_gpu:
+            model.to(dtype)                      # the fused GEMM takes bf16 operands
+        topology = gb.get_topology()
+        sharded = shard_linears(model.blocks, topology)
+        replicated = ReplicatedSync(model, topology)
+        replicas = dist.group.WORLD             # the parameters that stayed whole must stay identical
     elif args.mode in ("fsdp2", "hsdp"):
         from torch.distributed.device_mesh import init_device_mesh
         from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
@@ -178,13 +190,15 @@ def recorded(args) -> int:
             loss = forward_loss(x[part], y[part]) * (weight * rows / mine)
             loss.backward()
             local_loss += float(loss.detach()) if not on_gpu else loss.detach()
+        if args.mode == "fused":
+            replicated.average_gradients()
         optimizer.step()
         wait()
         times.append(max(everyone(time.perf_counter() - t0)))
         # the weighted losses average to the whole batch's mean loss
         losses.append(sum(float(v) for v in everyone(float(local_loss))) / world)
         if replicas is not None and args.check_every and (step + 1) % args.check_every == 0:
-            got = everyone(_digest(core.parameters()))
+            got = everyone(_digest(replicated.params if args.mode == "fused" else core.parameters()))
             members = dist.get_process_group_ranks(replicas)
             mates = everyone(members)
             groups = {tuple(m) for m in mates}
@@ -203,6 +217,9 @@ def recorded(args) -> int:
               "parameter_checks": checks,
               "parameters_identical": all(c["identical"] for c in checks) if checks else None,
               "parameters": sum(p.numel() for p in core.parameters()), "environment": environment()}
+    if args.mode == "fused":
+        record["sharded_layers"] = len(sharded)
+        record["parameter_bytes"] = replicated.memory(model)
     if rank == 0:
         print(json.dumps({k: v for k, v in record.items() if k not in ("losses", "step_ms", "environment",
                                                                          "parameter_checks")}), flush=True)
@@ -215,7 +232,7 @@ def recorded(args) -> int:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--model", default="llama-125m", choices=sorted(llama.CONFIGS))
-    ap.add_argument("--mode", default="fsdp2", choices=("single", "ddp", "fsdp2", "hsdp"))
+    ap.add_argument("--mode", default="fsdp2", choices=("single", "ddp", "fsdp2", "hsdp", "fused"))
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=10)
@@ -250,6 +267,14 @@ def main(argv=None) -> int:
     if args.mode == "ddp":
         from torch.nn.parallel import DistributedDataParallel as DDP
         model = DDP(model, device_ids=[local] if on_gpu else None)
+    elif args.mode == "fused":
+        from gpubridge_b200.parallel.sharded_model import ReplicatedSync, shard_linears
+        if args.backend != "gpubridge":
+            raise SystemExit("--mode fused runs on the gpubridge backend")
+        if on_gpu:
+            model.to(dtype)                      # the fused GEMM takes bf16 operands
+        shard_linears(model.blocks, gb.get_topology())
+        replicated = ReplicatedSync(model, gb.get_topology())
     elif args.mode in ("fsdp2", "hsdp"):
         from torch.distributed.device_mesh import init_device_mesh
         from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
@@ -281,6 +306,8 @@ def main(argv=None) -> int:
         loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]).float(),
                                                  y.reshape(-1))
         loss.backward()
+        if args.mode == "fused":
+            replicated.average_gradients()
         optimizer.step()
         return loss.detach()
 

@@ -115,6 +115,29 @@ class ShardedLinear(nn.Module):
         self.reshard_after_forward = reshard_after_forward
         self._own_slot = None if reshard_after_forward else GatherSlot(topology)
 
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, topology: Topology | None = None,
+                    reshard_after_forward: bool = True) -> "ShardedLinear":
+        """A sharded layer holding this rank's rows of ``linear.weight`` (every rank passes the
+        same whole weight, e.g. a model built from one seed).  ``linear`` must have no bias."""
+        if linear.bias is not None:
+            raise ValueError("ShardedLinear has no bias")
+        layer = cls.__new__(cls)
+        nn.Module.__init__(layer)
+        if topology is None and is_initialized():
+            topology = get_topology()
+        layer.topology = topology
+        layer.world = topology.world_size if topology is not None else 1
+        layer.rank = topology.rank if topology is not None else 0
+        layer.out_features, layer.in_features = linear.weight.shape
+        if layer.out_features % layer.world:
+            raise ValueError(f"out_features ({layer.out_features}) must divide over {layer.world} ranks")
+        rows = layer.out_features // layer.world
+        layer.weight = nn.Parameter(linear.weight.detach()[layer.rank * rows:(layer.rank + 1) * rows].clone())
+        layer.reshard_after_forward = reshard_after_forward
+        layer._own_slot = None if reshard_after_forward else GatherSlot(topology)
+        return layer
+
     # -- the three pieces ---------------------------------------------------------------------
     def _fused(self) -> bool:
         fabric = self.topology.fabric if self.topology is not None else None

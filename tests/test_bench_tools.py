@@ -137,7 +137,8 @@ def test_recorded_train_dp_and_report(tmp_path):
     runs.mkdir()
     for port, ranks, mode, extra in ((29751, 1, "single", ["--micro", "3"]),
                                      (29752, 2, "ddp", ["--shares", "5,3"]),
-                                     (29754, 4, "hsdp", [])):
+                                     (29754, 4, "hsdp", []),
+                                     (29755, 2, "fused", [])):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}",
                "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "gpubridge_b200.bench.train_dp",
                "--model", "llama-tiny", "--mode", mode, "--seq", "16", "--steps", "6", "--warmup", "1",
@@ -145,10 +146,11 @@ def test_recorded_train_dp_and_report(tmp_path):
                "--json", str(runs / f"dp_{mode}.json")]
         done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=400)
         assert done.returncode == 0, done.stderr[-3000:]
-    got = {m: json.loads((runs / f"dp_{m}.json").read_text()) for m in ("single", "ddp", "hsdp")}
+    got = {m: json.loads((runs / f"dp_{m}.json").read_text()) for m in ("single", "ddp", "hsdp", "fused")}
+    assert got["fused"]["sharded_layers"] == 14 and got["fused"]["parameters_identical"] is True
     assert got["ddp"]["shares"] == [5, 3] and got["ddp"]["parameters_identical"] is True
     assert got["hsdp"]["parameters_identical"] is True and len(got["hsdp"]["parameter_checks"]) == 2
-    for mode in ("ddp", "hsdp"):
+    for mode in ("ddp", "hsdp", "fused"):
         gaps = [abs(a - b) for a, b in zip(got[mode]["losses"], got["single"]["losses"])]
         assert max(gaps) < 1e-4, (mode, gaps)
     assert got["single"]["losses"][-1] < got["single"]["losses"][0]
@@ -156,7 +158,7 @@ def test_recorded_train_dp_and_report(tmp_path):
     text = (tmp_path / "rep" / "dp_report.md").read_text()
     assert "(baseline)" in text and "[5, 3]" in text and "| yes |" in text
     assert (tmp_path / "rep" / "loss_curves.csv").read_text().count("\n") == 8
-    assert (tmp_path / "rep" / "loss_curves.svg").read_text().count("<polyline") == 3
+    assert (tmp_path / "rep" / "loss_curves.svg").read_text().count("<polyline") == 4
 
 
 def test_ddp_divergence_report(tmp_path, capsys):
