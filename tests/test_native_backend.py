@@ -94,3 +94,18 @@ def test_cpp_backend_hands_the_whole_surface_over(tmp_path):
     done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, (done.stdout + done.stderr)[-4000:]
     assert done.stdout.count("ok") == 4
+
+
+@pytest.mark.parametrize("extra", [[], ["--hsdp", "2"]])
+def test_fsdp2_and_hsdp_bit_for_bit_through_the_cpp_front_end(extra):
+    """The FSDP2 / HSDP example's --verify (parameters equal a single-process replay, bit for
+    bit) with the C++ backend under torch's own ProcessGroup: device-mesh subgroups included."""
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1", GPUBRIDGE_VENDOR="nvidia",
+               GPUBRIDGE_SPLIT_TEST="half")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+           "--master-addr", "127.0.0.1", "--master-port", "29773" if extra else "29772",
+           os.path.join(ROOT, "examples", "fsdp2_torch_backend.py"), "--verify", "--backend",
+           "gpubridge_native", *extra]
+    done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, (done.stdout + done.stderr)[-4000:]
+    assert "bit for bit" in done.stdout
