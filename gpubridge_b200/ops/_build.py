@@ -74,6 +74,10 @@ def build(verbose: bool = False, force: bool = False) -> str:
             os.remove(os.path.join(OBJ, name))
     with ThreadPoolExecutor(max_workers=4) as pool:
         objects = list(pool.map(lambda p: _compile(p, verbose), sources()))
+    for name in os.listdir(OBJ):               # objects of sources as they were before: dead weight
+        path = os.path.join(OBJ, name)
+        if name.endswith((".o", ".tmp")) and path not in objects:
+            os.remove(path)
     stamp = os.path.join(OBJ, "linked.txt")
     want = "\n".join(objects)
     if os.path.exists(LIB) and os.path.exists(stamp) and open(stamp).read() == want:
