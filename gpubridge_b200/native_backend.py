@@ -3,6 +3,8 @@
     import gpubridge_b200.native_backend        # registers the name
     dist.init_process_group(backend="gpubridge_native")
 
+or, for a program that already says ``backend="gpubridge"``: ``GPUBRIDGE_FRONT_END=native``.
+
 torch wraps what :func:`create` returns - a ``c10d::Backend`` written in C++
 (``csrc_torch/gb_c10d.cpp``) - in its own C++ ProcessGroup, so a collective on a CUDA tensor
 goes dispatcher -> backend -> native engine -> kernel launch without running a line of Python:
@@ -42,7 +44,7 @@ def create(options, backend_options=None):
     with _lock:
         backend = _made.get(options.group_id)
         if backend is None:
-            fallback = _python_backend.create(options, backend_options)
+            fallback = _python_backend.create_python(options, backend_options)
             backend = _build_c10d.load().GbBackend(options.group_rank, options.group_size, fallback)
             _made[options.group_id] = backend
             _python_groups[options.group_id] = fallback

@@ -641,9 +641,20 @@ def _teardown(group: GpubridgeProcessGroup) -> None:
         _close_subgroup(sub)
 
 
-def create(options, backend_options=None) -> GpubridgeProcessGroup:
-    """The creator torch calls (``extended_api=True``) on a group's members.  The world's
-    topology is built here, inside ``init_process_group``, which every rank calls."""
+def create(options, backend_options=None):
+    """The creator torch calls (``extended_api=True``) on a group's members.  With
+    ``GPUBRIDGE_FRONT_END=native`` the group is fronted by the C++ backend of
+    :mod:`gpubridge_b200.native_backend` (the same as asking for ``backend="gpubridge_native"``);
+    otherwise it is the Python process group."""
+    if os.environ.get("GPUBRIDGE_FRONT_END", "python").strip().lower() == "native":
+        from gpubridge_b200 import native_backend
+        return native_backend.create(options, backend_options)
+    return create_python(options, backend_options)
+
+
+def create_python(options, backend_options=None) -> GpubridgeProcessGroup:
+    """The Python process group of a new group.  The world's topology is built here, inside
+    ``init_process_group``, which every rank calls."""
     ranks = list(options.global_ranks_in_group)
     if ranks != sorted(ranks):
         raise RuntimeError(f"the {NAME} torch.distributed backend takes a subgroup's ranks in "

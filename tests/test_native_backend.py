@@ -96,6 +96,28 @@ def test_cpp_backend_hands_the_whole_surface_over(tmp_path):
     assert done.stdout.count("ok") == 4
 
 
+def test_front_end_switch_for_programs_that_name_the_python_backend(tmp_path):
+    script = tmp_path / "ranks.py"
+    script.write_text(textwrap.dedent('''
+        import torch, torch.distributed as dist
+        import gpubridge_b200, gpubridge_b200.native_backend as nb
+        dist.init_process_group(backend="gpubridge")
+        t = torch.ones(4) * (dist.get_rank() + 1)
+        dist.all_reduce(t)
+        assert t[0].item() == 3
+        assert nb.backend_of() is not None and nb.backend_of().fallback_calls >= 1
+        dist.destroy_process_group()
+        print("ok")
+    '''))
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1", GPUBRIDGE_VENDOR="nvidia",
+               GPUBRIDGE_SPLIT_TEST="half", GPUBRIDGE_FRONT_END="native")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29774", str(script)]
+    done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, (done.stdout + done.stderr)[-3000:]
+    assert done.stdout.count("ok") == 2
+
+
 @pytest.mark.parametrize("extra", [[], ["--hsdp", "2"]])
 def test_fsdp2_and_hsdp_bit_for_bit_through_the_cpp_front_end(extra):
     """The FSDP2 / HSDP example's --verify (parameters equal a single-process replay, bit for
