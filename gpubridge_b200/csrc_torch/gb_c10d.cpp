@@ -274,6 +274,23 @@ class GbBackend : public c10d::Backend {
         py::gil_scoped_acquire gil;
         return hold(fallback_.attr("recv")(tensors, src, tag));
     }
+    // Refused by the library (with the reason, on every rank): let the Python group say so.
+    c10::intrusive_ptr<c10d::Work> alltoall_base(at::Tensor& output, at::Tensor& input,
+                                                 std::vector<int64_t>& output_splits,
+                                                 std::vector<int64_t>& input_splits,
+                                                 const c10d::AllToAllOptions& opts) override {
+        py::gil_scoped_acquire gil;
+        return hold(fallback_.attr("alltoall_base")(output, input, output_splits, input_splits, opts));
+    }
+    c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
+                                            const c10d::AllToAllOptions& opts) override {
+        py::gil_scoped_acquire gil;
+        return hold(fallback_.attr("alltoall")(outputs, inputs, opts));
+    }
+    c10::intrusive_ptr<c10d::Work> recvAnysource(std::vector<at::Tensor>& tensors, int tag) override {
+        py::gil_scoped_acquire gil;
+        return hold(fallback_.attr("recv_anysource")(tensors, tag));
+    }
     c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& opts) override {
         py::gil_scoped_acquire gil;
         return hold(fallback_.attr("barrier")(opts));

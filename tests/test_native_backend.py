@@ -131,3 +131,13 @@ def test_fsdp2_and_hsdp_bit_for_bit_through_the_cpp_front_end(extra):
     done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, (done.stdout + done.stderr)[-4000:]
     assert "bit for bit" in done.stdout
+
+
+def test_the_backend_suite_passes_through_the_cpp_front_end():
+    """Every test of the Python backend's suite (DDP, every collective, refusals with their
+    reasons, FSDP2, HSDP, subgroups, re-init) once more with GPUBRIDGE_FRONT_END=native."""
+    env = dict(os.environ, PYTHONPATH=ROOT, GPUBRIDGE_FRONT_END="native")
+    done = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_backend.py"),
+                           "-q", "-x", "-p", "no:cacheprovider"], env=env, cwd=ROOT, capture_output=True,
+                          text=True, timeout=1200)
+    assert done.returncode == 0, done.stdout[-4000:]
