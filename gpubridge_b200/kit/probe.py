@@ -6,6 +6,7 @@ Stages, each recorded in ``probe.json``: GPUs visible to PyTorch; every GPU is a
 part the native library is built for (compute capability 10.x); the native library exists
 (or builds) and loads; its struct layouts match the bindings; the import resolves to this
 checkout; every pair of GPUs can address each other's memory (what the fused kernels need);
+what NVML reports of the NVLink side (links per GPU, whether they end at an NVSwitch);
 ``CUDA_VISIBLE_DEVICES`` selects the GPU it names (a child that sees only the last GPU must
 find that GPU's PCI address at ``cuda:0`` - one process per GPU depends on it).
 A failed stage prints one line on stderr and the exit code is 1.  Same role as the
@@ -88,6 +89,20 @@ def main(argv=None) -> int:
                 fail(e, f"GPU pairs without peer access: {blocked[:8]} - the fused kernels need it")
         else:
             e["skipped"] = "fewer than two GPUs"
+    with journal.stage("nvlink") as e:
+        from gpubridge_b200.utils.links import link_layout
+        layout = link_layout() if count else None
+        if layout is None:
+            e["skipped"] = "no GPU or no NVML"
+        else:
+            e.update(layout)
+            # reported, never a failure: peer access (above) is what decides whether the fused
+            # kernels can run; this says what kind of box the numbers come from
+            if count >= 2 and layout["fabric"] == "none":
+                e["warning"] = "NVML reports no active NVLink: peer traffic would cross PCIe"
+            elif layout["links_uneven"]:
+                e["warning"] = ("GPUs report different numbers of active NVLink links: "
+                                f"{[g['links_active'] for g in layout['gpus']]}")
     with journal.stage("device_map") as e:
         if count >= 2:
             import os

@@ -276,3 +276,43 @@ def test_shards_cover_every_file_once():
     import pytest
     with pytest.raises(ValueError):
         shard_of(files, "5/4")
+
+
+def test_link_layout_from_a_fake_nvml():
+    from gpubridge_b200.utils.links import link_layout
+
+    class FakeNvml:
+        NVML_NVLINK_MAX_LINKS = 18
+
+        def __init__(self, links, remote, broken=()):
+            self.links, self.remote, self.broken, self.calls = links, remote, broken, []
+
+        def nvmlInit(self): self.calls.append("init")
+        def nvmlShutdown(self): self.calls.append("shutdown")
+        def nvmlDeviceGetCount(self): return len(self.links)
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetName(self, h): return b"NVIDIA B200"
+
+        def nvmlDeviceGetNvLinkState(self, h, link):
+            if link >= 18 - len(self.broken) and h in self.broken:
+                raise RuntimeError("not supported")
+            return 1 if link < self.links[h] else 0
+
+        def nvmlDeviceGetNvLinkVersion(self, h, link): return 5
+        def nvmlDeviceGetNvLinkRemoteDeviceType(self, h, link): return self.remote
+
+    box = FakeNvml([18] * 8, remote=2)
+    layout = link_layout(box)
+    assert layout["fabric"] == "nvswitch" and not layout["links_uneven"]
+    assert layout["gpus"][3] == {"index": 3, "name": "NVIDIA B200", "links_active": 18, "link_version": 5,
+                                 "to_switch": 18, "to_gpu": 0, "to_other": 0}
+    assert box.calls == ["init", "shutdown"]                 # only getters in between
+    assert link_layout(FakeNvml([4, 4], remote=0))["fabric"] == "direct"
+    lost = link_layout(FakeNvml([18, 16], remote=2))
+    assert lost["links_uneven"] and lost["fabric"] == "nvswitch"
+    assert link_layout(FakeNvml([0, 0], remote=2))["fabric"] == "none"
+
+    class NoNvml:
+        def nvmlInit(self): raise OSError("libnvidia-ml.so not found")
+
+    assert link_layout(NoNvml()) is None
