@@ -104,10 +104,18 @@ def environment() -> dict[str, Any]:
         "nccl": _try(lambda: ".".join(map(str, torch.cuda.nccl.version()))),
         "cuda_available": has_gpu, "device_count": count,
         "devices": [_try(lambda i=i: device_info(i)) for i in range(count)],
+        "nvlink_fabric": _try(_nvlink_fabric) if has_gpu else None,
         "probe": _try(lambda: asdict(gb.probe())),
         "native_library": _try(_native_library),
         "env": recorded_env(),
     })
+
+
+def _nvlink_fabric() -> str | None:
+    """``nvswitch`` / ``direct`` / ``mixed`` / ``none`` as NVML reports it (read-only)."""
+    from gpubridge_b200.utils.links import link_layout
+    layout = link_layout()
+    return None if layout is None else layout["fabric"]
 
 
 def _native_library() -> dict[str, Any]:
