@@ -158,6 +158,8 @@ class GbBackend : public c10d::Backend {
         if (team != nullptr && floats_only)
             for (const auto& t : tensors) if (!is_float(t.scalar_type())) team = nullptr;
         if (team == nullptr) return via_python("allreduce", tensors, opts);
+        // launches go to the team's GPU whatever device the caller has current
+        c10::cuda::CUDAGuard on_device(c10::DeviceIndex(team->device));
         auto comm = enter(*team, tensors);
         for (auto& t : tensors) {
             if (t.numel() == 0) continue;
@@ -178,6 +180,8 @@ class GbBackend : public c10d::Backend {
         const NativeTeam* team = native_for(tensors);
         if (team == nullptr || opts.rootRank < 0 || size_t(opts.rootRank) >= team->team_rank.size())
             return via_python("broadcast", tensors, opts);
+        // launches go to the team's GPU whatever device the caller has current
+        c10::cuda::CUDAGuard on_device(c10::DeviceIndex(team->device));
         auto comm = enter(*team, tensors);
         for (auto& t : tensors) {
             if (t.numel() == 0) continue;
@@ -197,6 +201,8 @@ class GbBackend : public c10d::Backend {
             py::gil_scoped_acquire gil;
             return hold(fallback_.attr("_allgather_base")(output, input, opts));
         }
+        // launches go to the team's GPU whatever device the caller has current
+        c10::cuda::CUDAGuard on_device(c10::DeviceIndex(team->device));
         auto comm = enter(*team, both);
         if (input.numel() != 0)
             check(gb_engine_all_gather(team->engine, input.data_ptr(), output.data_ptr(), size_t(input.nbytes()),
@@ -217,6 +223,8 @@ class GbBackend : public c10d::Backend {
             py::gil_scoped_acquire gil;
             return hold(fallback_.attr("_reduce_scatter_base")(output, input, opts));
         }
+        // launches go to the team's GPU whatever device the caller has current
+        c10::cuda::CUDAGuard on_device(c10::DeviceIndex(team->device));
         auto comm = enter(*team, both);
         if (output.numel() != 0)
             check(gb_engine_reduce_scatter(team->engine, input.data_ptr(), output.data_ptr(), size_t(output.numel()),
