@@ -24,6 +24,7 @@ no second gather, a whole weight resident per layer.
 from __future__ import annotations
 
 import math
+import os
 import weakref
 
 import torch
@@ -83,8 +84,7 @@ class _FusedForward(torch.autograd.Function):
         dx = (dy2 @ weight).view(*dy.shape[:-1], weight.shape[1]) if ctx.needs_input_grad[0] else None
         dshard = None
         if ctx.needs_input_grad[1]:
-            dw = (dy2.t() @ x2).contiguous()             # [N, K], this rank's contribution
-            dshard = layer._scatter_gradient(dw)
+            dshard = layer._weight_gradient(dy2, x2)
         return dx, dshard, None
 
 
@@ -114,6 +114,7 @@ class ShardedLinear(nn.Module):
         self.weight = nn.Parameter(full[self.rank * rows:(self.rank + 1) * rows].to(device=device, dtype=dtype))
         self.reshard_after_forward = reshard_after_forward
         self._own_slot = None if reshard_after_forward else GatherSlot(topology)
+        self.grad_chunks = int(os.environ.get("GPUBRIDGE_SHARDED_GRAD_CHUNKS", "1"))
 
     @classmethod
     def from_linear(cls, linear: nn.Linear, topology: Topology | None = None,
@@ -136,6 +137,7 @@ class ShardedLinear(nn.Module):
         layer.weight = nn.Parameter(linear.weight.detach()[layer.rank * rows:(layer.rank + 1) * rows].clone())
         layer.reshard_after_forward = reshard_after_forward
         layer._own_slot = None if reshard_after_forward else GatherSlot(topology)
+        layer.grad_chunks = int(os.environ.get("GPUBRIDGE_SHARDED_GRAD_CHUNKS", "1"))
         return layer
 
     # -- the three pieces ---------------------------------------------------------------------
@@ -183,11 +185,33 @@ class ShardedLinear(nn.Module):
             slot.holder, slot.gathers = token, slot.gathers + 1
         return full
 
-    def _scatter_gradient(self, dw: torch.Tensor) -> torch.Tensor:
+    def _weight_gradient(self, dy2: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
+        """This rank's rows of the averaged ``dW = dY^T @ X``.
+
+        ``GPUBRIDGE_SHARDED_GRAD_CHUNKS`` (default 1) cuts every owner's rows into that many
+        pieces: piece s of all owners is one batched GEMM into a contiguous [world, rows / S, K]
+        buffer and one asynchronous reduce-scatter, so the exchange of piece s runs on the
+        communication stream (on few CTAs) while the GEMM of piece s + 1 runs - the overlap a
+        single GEMM -> reduce-scatter kernel would give tile by tile, from two kernels."""
         if self.world == 1:
-            return dw
+            return (dy2.t() @ x2).contiguous()
         out = torch.empty_like(self.weight)
-        collectives.reduce_scatter_tensor(out, dw, ReduceOp.AVG, _topology=self.topology)
+        rows = self.out_features // self.world
+        pieces = max(1, min(self.grad_chunks, rows))
+        if pieces == 1 or rows % pieces:
+            dw = (dy2.t() @ x2).contiguous()             # [N, K], this rank's contribution
+            collectives.reduce_scatter_tensor(out, dw, ReduceOp.AVG, _topology=self.topology)
+            return out
+        per = rows // pieces
+        dyt = dy2.t().reshape(self.world, rows, dy2.shape[0])            # [owner, row, token]
+        works = []
+        for s in range(pieces):
+            part = torch.matmul(dyt[:, s * per:(s + 1) * per, :], x2)    # [owner, per, K]
+            works.append(collectives.reduce_scatter_tensor(
+                out[s * per:(s + 1) * per], part.contiguous(), ReduceOp.AVG, async_op=True,
+                _topology=self.topology))
+        for work in works:
+            work.wait()
         return out
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -39,6 +39,12 @@ def _layer(rank, topology):
     want = torch.stack(grads).mean(0)[rank * rows:(rank + 1) * rows]
     assert torch.allclose(layer.weight.grad, want, atol=1e-10)
     assert torch.allclose(x.grad, dx, atol=1e-10)
+    # the weight gradient in pieces (a batched GEMM and an asynchronous reduce-scatter per piece)
+    pieced = ShardedLinear(16, 24, topology=topology, dtype=torch.float64)
+    pieced.grad_chunks = 3 if rows % 3 == 0 else 2
+    x2 = xs[rank].clone().requires_grad_(True)
+    pieced(x2).square().sum().backward()
+    assert torch.allclose(pieced.weight.grad, want, atol=1e-10)
     return True
 
 
