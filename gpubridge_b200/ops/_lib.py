@@ -124,6 +124,10 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_allgather_gemm.argtypes = [ctypes.POINTER(GbTeam), vp, vp, vp, vp, vp, vp, ctypes.c_uint,
                                     i, i, i, sz, i, i, vp]
     L.gb_allgather_gemm_pair.argtypes = L.gb_allgather_gemm.argtypes
+    L.gb_gemm_reduce_scatter_bytes.restype = sz
+    L.gb_gemm_reduce_scatter_bytes.argtypes = [i, i, i]
+    L.gb_gemm_reduce_scatter.argtypes = [ctypes.POINTER(GbTeam), vp, vp, vp, vp, i, i, i, sz, sz,
+                                         i, i, i, vp]
     L.gb_copy_to_host.argtypes = [vp, vp, sz, vp]
     L.gb_plan_hier.argtypes = [sz, i, i, i, i, sz, sz, sz, i, sz, i, i, i, ctypes.POINTER(GbHierPlanOut)]
     L.gb_engine_create.restype = vp

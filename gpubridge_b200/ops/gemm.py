@@ -83,3 +83,68 @@ class AllGatherLinear:
         code = int(self.error.item())
         if code:
             raise RuntimeError(f"gb_allgather_gemm: a bounded wait ran out (code {code})")
+
+
+class GemmReduceScatter:
+    """``out = mean over ranks of (a @ b.T)[rows of this rank]`` in one kernel
+    (``csrc/gb_gemm_rs.cu``): a tcgen05 GEMM whose epilogue stores every row of the product
+    into its owner's workspace over NVLink (bf16 partials, the slot of the sending rank), then
+    a team barrier and the fp32 sum of the slots of the own rows.  ``a``: [P, R], ``b``: [Q, R],
+    both bf16 and contiguous; P divides over the team, Q and R are multiples of 8.  The weight
+    gradient of a row-sharded Linear is ``GemmReduceScatter(fabric)(dy.T, x.T)``.
+
+    Stages through the fabric's reduce-scatter region; :meth:`fits` says whether the shapes do.
+    """
+
+    def __init__(self, fabric) -> None:
+        self.fabric = fabric
+        self.error = torch.zeros(1, dtype=torch.int32, device=fabric.device)
+        self.region = (fabric.off_rs, 4 * fabric.len_rs)
+
+    def fits(self, P: int, Q: int, R: int) -> bool:
+        world = self.fabric.world
+        if P % world or Q % 8 or R % 8 or min(P, Q, R) <= 0:
+            return False
+        need = self.fabric.lib.gb_gemm_reduce_scatter_bytes(world, P, Q)
+        return 0 < need // 2 <= self.region[1] // 2
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, divide: int | None = None,
+                 out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        global launches
+        assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+        assert a.is_contiguous() and b.is_contiguous() and a.shape[1] == b.shape[1]
+        assert out_dtype in (torch.bfloat16, torch.float32)
+        fabric = self.fabric
+        P, R = a.shape
+        Q = b.shape[0]
+        if not self.fits(P, Q, R):
+            raise ValueError(f"shapes [{P}, {R}] x [{Q}, {R}] do not fit the fused GEMM + reduce-scatter "
+                             f"(rows over {fabric.world} ranks, multiples of 8, staging "
+                             f"{self.region[1] // 2} bytes per collective)")
+        out = torch.empty((P // fabric.world, Q), dtype=out_dtype, device=a.device)
+        current = fabric._begin()
+        try:
+            with torch.cuda.stream(fabric.comm_stream):
+                code = fabric.lib.gb_gemm_reduce_scatter(
+                    ctypes.byref(fabric.team), out.data_ptr(), a.data_ptr(), b.data_ptr(),
+                    self.error.data_ptr(), P, Q, R, self.region[0], self.region[1],
+                    int(divide or 0), int(out_dtype == torch.float32), 0,
+                    torch.cuda.current_stream(a.device).cuda_stream)
+                if code == -3:
+                    raise RuntimeError("cuTensorMapEncodeTiled is unavailable or refused the shapes")
+                if code == -4:
+                    raise RuntimeError("the fabric's reduce-scatter region is too small for these shapes")
+                _lib.check(code, "gb_gemm_reduce_scatter")
+                for t in (a, b, out):
+                    t.record_stream(fabric.comm_stream)
+        finally:
+            fabric._end(current)
+        launches += 1
+        return out
+
+    def check(self) -> None:
+        """Raise if a wait inside the kernel ran out (reads one word from the device)."""
+        code = int(self.error.item())
+        if code:
+            raise RuntimeError(f"the fused GEMM + reduce-scatter gave up on a wait (code {code})")
+        self.fabric.check()

@@ -42,6 +42,7 @@ class GatherSlot:
         self.topology = weakref.ref(topology) if topology is not None else None
         self.buffer: torch.Tensor | None = None
         self.op = None                      # the fused all-gather GEMM site bound to ``buffer``
+        self.scatter = None                 # the fused GEMM + reduce-scatter of the weight gradient
         self.holder: object | None = None   # token of the forward call whose weight is in it
         self.gathers = 0                    # gathers into this slot, forward and backward (tests)
 
@@ -115,6 +116,7 @@ class ShardedLinear(nn.Module):
         self.reshard_after_forward = reshard_after_forward
         self._own_slot = None if reshard_after_forward else GatherSlot(topology)
         self.grad_chunks = int(os.environ.get("GPUBRIDGE_SHARDED_GRAD_CHUNKS", "1"))
+        self.fused_gradient = os.environ.get("GPUBRIDGE_GEMM_RS", "0") == "1"
 
     @classmethod
     def from_linear(cls, linear: nn.Linear, topology: Topology | None = None,
@@ -138,6 +140,7 @@ class ShardedLinear(nn.Module):
         layer.reshard_after_forward = reshard_after_forward
         layer._own_slot = None if reshard_after_forward else GatherSlot(topology)
         layer.grad_chunks = int(os.environ.get("GPUBRIDGE_SHARDED_GRAD_CHUNKS", "1"))
+        layer.fused_gradient = os.environ.get("GPUBRIDGE_GEMM_RS", "0") == "1"
         return layer
 
     # -- the three pieces ---------------------------------------------------------------------
@@ -188,6 +191,8 @@ class ShardedLinear(nn.Module):
     def _weight_gradient(self, dy2: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
         """This rank's rows of the averaged ``dW = dY^T @ X``.
 
+        ``GPUBRIDGE_GEMM_RS=1``: on the fused path, one kernel (``csrc/gb_gemm_rs.cu``) whose
+        epilogue sends every row of the product to its owner.  Otherwise
         ``GPUBRIDGE_SHARDED_GRAD_CHUNKS`` (default 1) cuts every owner's rows into that many
         pieces: piece s of all owners is one batched GEMM into a contiguous [world, rows / S, K]
         buffer and one asynchronous reduce-scatter, so the exchange of piece s runs on the
@@ -195,6 +200,15 @@ class ShardedLinear(nn.Module):
         single GEMM -> reduce-scatter kernel would give tile by tile, from two kernels."""
         if self.world == 1:
             return (dy2.t() @ x2).contiguous()
+        if self.fused_gradient and self._fused() and dy2.dtype == torch.bfloat16 == x2.dtype:
+            # one kernel: the GEMM's epilogue sends every row to its owner, a reducing tail follows
+            slot = self._slot()
+            if slot.scatter is None:
+                from gpubridge_b200.ops.gemm import GemmReduceScatter
+                slot.scatter = GemmReduceScatter(self.topology.fabric)
+            if slot.scatter.fits(self.out_features, self.in_features, dy2.shape[0]):
+                return slot.scatter(dy2.t().contiguous(), x2.t().contiguous(), divide=self.world,
+                                    out_dtype=self.weight.dtype)
         out = torch.empty_like(self.weight)
         rows = self.out_features // self.world
         pieces = max(1, min(self.grad_chunks, rows))
