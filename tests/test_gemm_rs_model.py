@@ -33,14 +33,18 @@ def test_schedule_and_addressing(world, P, Q):
                 assert (p0, q0) not in seen
                 seen.add((p0, q0))
                 order.append(p0)
-                for row in range(p0, min(p0 + BM, P)):
+                row = p0
+                while row < min(p0 + BM, P):                      # the tile's rows, owner by owner
                     owner, at = divmod(row, rows)
-                    base = parity * half + rank * slot + at * Q
+                    count = min(rows - at, min(p0 + BM, P) - row)
+                    base = parity * half + rank * slot             # the kernel: + at * Q + col per row
                     cols = slice(q0, min(q0 + BN, Q))
-                    where = slice(base + cols.start, base + cols.stop)
-                    assert not written[owner][where].any(), "two writers on one staging element"
-                    written[owner][where] = True
-                    staging[owner][where] = products[rank][row, cols]
+                    mark = written[owner][base:base + slot].reshape(rows, Q)
+                    data = staging[owner][base:base + slot].reshape(rows, Q)
+                    assert not mark[at:at + count, cols].any(), "two writers on one staging element"
+                    mark[at:at + count, cols] = True
+                    data[at:at + count, cols] = products[rank][row:row + count, cols]
+                    row += count
             assert len(seen) == -(-P // BM) * -(-Q // BN)
             if world > 1 and rows % BM == 0:
                 own = [p0 for p0 in order if rank * rows <= p0 < (rank + 1) * rows]
