@@ -6,7 +6,6 @@ to torch (scripts/gpu/llama.py:109, train_bench.py:172); this keeps that default
 choice measurable."""
 from __future__ import annotations
 
-import contextlib
 import functools
 import os
 
