@@ -138,7 +138,16 @@ def main(argv=None) -> int:
     ap.add_argument("--bridge", default=os.environ.get("GPUBRIDGE_BRIDGE", "").strip() or None,
                     help="bridge transport between islands (default: GPUBRIDGE_BRIDGE, else init()'s choice)")
     ap.add_argument("--write-thresholds", default="")
+    ap.add_argument("--candidates", default="", help="policies to race at every size (adds a "
+                    "policy:NAME target for each; with --write-thresholds the winners become the rules)")
+    ap.add_argument("--phases", action="store_true", help="for the target `ours`: the phases of the "
+                    "all-reduce through the public API with an observer attached - the slowest rank's "
+                    "median per phase (device timestamps inside the fused kernel, stream events around "
+                    "the steps of the composed path)")
     args = ap.parse_args(argv)
+    if args.candidates:
+        args.targets = ",".join([*filter(None, args.targets.split(",")),
+                                 *(f"policy:{name}" for name in args.candidates.split(","))])
 
     with warnings.catch_warnings():
         warnings.simplefilter("ignore", gb.SplitTestWarning)
@@ -173,6 +182,8 @@ def main(argv=None) -> int:
                                "policy": topology.policy_name, "inner": args.inner}
                         if target.startswith("compression:") and op == "all_reduce":
                             row.update(compression_check(target, topology, dtype, nbytes))
+                        if args.phases and target == "ours" and op == "all_reduce":
+                            row["phases_ms"] = phase_times(topology, dtype, nbytes, min(args.trials, 10))
                         rows.append(row)
                         if rank == 0:
                             print(json.dumps(row), flush=True)
@@ -186,6 +197,44 @@ def main(argv=None) -> int:
     if rank == 0 and args.write_thresholds:
         write_thresholds(rows, args.write_thresholds)
     return 0
+
+
+class _Records(gb.CollectiveObserver):
+    def __init__(self) -> None:
+        self.records = []
+
+    def on_collective(self, record) -> None:
+        self.records.append(record)
+
+
+def phase_times(topology, dtype, nbytes: int, trials: int) -> dict[str, float]:
+    """``{phase: ms}``: all-reduces through the public API with an observer attached; per
+    phase the median over the trials, then the slowest rank's (ranks that do not take part in
+    a phase - members during the bridge step - do not report it)."""
+    import torch.distributed as dist
+    dev = topology.device
+    n = max(1, nbytes // torch.empty(0, dtype=dtype).element_size())
+    t = torch.ones(n, dtype=dtype, device=dev)
+    watcher = _Records()
+    gb.all_reduce(t)                                          # warm
+    gb.add_observer(watcher)
+    try:
+        for _ in range(trials):
+            gb.all_reduce(t)
+        if dev.type == "cuda":
+            torch.cuda.synchronize(dev)
+    finally:
+        gb.remove_observer(watcher)
+    seen: dict[str, list[float]] = {}
+    for record in watcher.records:
+        seen.setdefault("total", []).append(gb.elapsed_ms(record.start, record.end))
+        for phase in record.phases:
+            seen.setdefault(phase.name, []).append(phase.elapsed_ms())
+    mine = {name: statistics.median(values) for name, values in seen.items()}
+    everyone = [None] * topology.world_size
+    dist.all_gather_object(everyone, mine)
+    names = sorted({name for m in everyone for name in m})
+    return {name: round(max(m[name] for m in everyone if name in m), 5) for name in names}
 
 
 def compression_check(target: str, topology, dtype, nbytes: int) -> dict:

@@ -16,11 +16,15 @@ def test_sweep_matrix_and_thresholds(tmp_path):
            "--master-addr", "127.0.0.1", "--master-port", "29727", "-m",
            "gpubridge_b200.bench.bench_all_reduce", "--smallest", "4K", "--largest", "64K",
            "--targets", "ours,compression:fp8,policy:flat-gloo,policy:reduce-bridge-broadcast",
-           "--trials", "2", "--seconds", "1", "--json", str(out), "--write-thresholds", str(rules)]
+           "--trials", "2", "--seconds", "1", "--phases", "--candidates", "sharded-bridge",
+           "--json", str(out), "--write-thresholds", str(rules)]
     done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0, done.stderr[-3000:]
     rows = json.loads(out.read_text())
     assert {r["target"] for r in rows} >= {"ours", "compression:fp8", "policy:flat-gloo"}
+    assert "policy:sharded-bridge" in {r["target"] for r in rows}            # from --candidates
+    ours = [r for r in rows if r["target"] == "ours"]
+    assert all({"island-reduce", "bridge", "island-broadcast", "total"} <= set(r["phases_ms"]) for r in ours)
     coded = [r for r in rows if r["target"] == "compression:fp8"]
     assert all(r["identical_bits"] and 0 < r["max_rel_error"] < 0.2 for r in coded)
     saved = json.loads(rules.read_text())
