@@ -79,6 +79,38 @@ def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5, inner
     return statistics.median(times)
 
 
+_made: dict[str, object] = {}           # target name -> its policy, set up once per job
+
+
+def target_policy(name: str, topology):
+    """The policy behind a target: the job's own, or one set up for ``policy:NAME`` /
+    ``compression:MODE[:FORMAT]`` - once, whatever the number of sizes (setting a policy up is
+    collective and may build communicators)."""
+    if not (name.startswith("policy:") or name.startswith("compression:")):
+        return topology.policy
+    if name not in _made:
+        if name.startswith("policy:"):
+            cls = _policies.choose_policy(_policies.resolve_policy(name.split(":", 1)[1]), topology.layout)
+            policy = cls()
+            policy.setup(topology)
+        else:
+            parts = name.split(":")
+            policy = type(topology.policy)(compression=parts[1]) if hasattr(
+                topology.policy, "compression") else topology.policy
+            policy.setup(topology)
+            if len(parts) > 2:
+                policy._fmt = parts[2]
+        _made[name] = policy
+    return _made[name]
+
+
+def close_targets(topology) -> None:
+    for policy in _made.values():
+        if policy is not topology.policy:
+            policy.close()
+    _made.clear()
+
+
 def make_target(name: str, op: str, topology, dtype, nbytes: int):
     """A zero-argument callable running ``op`` once on ``nbytes`` of ``dtype``."""
     dev, world = topology.device, topology.world_size
@@ -98,19 +130,7 @@ def make_target(name: str, op: str, topology, dtype, nbytes: int):
         out = torch.empty(n // world, dtype=dtype, device=dev)
         src = full[: out.numel() * world]
         return lambda: comm.reduce_scatter_into(out, src), src.nbytes
-    policy = topology.policy
-    if name.startswith("policy:"):
-        cls = _policies.choose_policy(_policies.resolve_policy(name.split(":", 1)[1]),
-                                      topology.layout)
-        policy = cls()
-        policy.setup(topology)
-    elif name.startswith("compression:"):
-        parts = name.split(":")
-        policy = type(topology.policy)(compression=parts[1]) if hasattr(
-            topology.policy, "compression") else topology.policy
-        policy.setup(topology)
-        if len(parts) > 2:
-            policy._fmt = parts[2]
+    policy = target_policy(name, topology)
     if op == "all_reduce":
         return lambda: policy.all_reduce(full, topology), nbytes
     if op == "broadcast":
@@ -190,6 +210,7 @@ def main(argv=None) -> int:
         if topology.fabric is not None:
             topology.fabric.check()
     finally:
+        close_targets(topology)
         gb.destroy()
     if rank == 0 and args.json:
         with open(args.json, "w") as fh:
@@ -241,20 +262,13 @@ def compression_check(target: str, topology, dtype, nbytes: int) -> dict:
     """One compressed all-reduce of fresh data against the fp64 sum: the largest error relative
     to the largest magnitude of the result, and whether every rank holds identical bits (the
     reference's ``--compression`` check, scripts/gpu/bench_all_reduce.py:331-379)."""
-    fn_policy = make_target(target, "all_reduce", topology, dtype, nbytes)
-    del fn_policy
     dev, world = topology.device, topology.world_size
     n = max(1, nbytes // torch.empty(0, dtype=dtype).element_size())
     inputs = [torch.randn(n, generator=torch.Generator().manual_seed(99 + r)).to(dtype)
               for r in range(world)]
     exact = torch.stack([t.double() for t in inputs]).sum(0)
     mine = inputs[topology.rank].to(dev)
-    parts = target.split(":")
-    policy = type(topology.policy)(compression=parts[1]) if hasattr(
-        topology.policy, "compression") else topology.policy
-    policy.setup(topology)
-    if len(parts) > 2:
-        policy._fmt = parts[2]
+    policy = target_policy(target, topology)
     policy.all_reduce(mine, topology)
     if dev.type == "cuda":
         torch.cuda.synchronize(dev)

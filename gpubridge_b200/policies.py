@@ -25,6 +25,7 @@ exact results on integer-valued data.
 from __future__ import annotations
 
 import abc
+import dataclasses
 import json
 import os
 from typing import TYPE_CHECKING, Any, ClassVar
@@ -540,6 +541,9 @@ class PipelinedReduceBridgeBroadcast(ReduceBridgeBroadcast):
         recv.end(last_back)
 
 
+_link_setups: dict[str, int] = {}      # topology context name -> sharded-bridge set-ups so far
+
+
 class ShardedBridge(ReduceBridgeBroadcast):
     """k ranks per island share the bridge step, one stripe each (k = smallest island).
 
@@ -573,8 +577,16 @@ class ShardedBridge(ReduceBridgeBroadcast):
         groups = [sorted(i.ranks[j] for i in islands) for j in range(1, self.k)]
         links: list = []
         if groups:
+            # A second instance of this policy on the same topology (a benchmark racing
+            # policies, an auto-tuned policy's candidates) must not meet the first one's store
+            # keys: the count of set-ups - the same on every rank, set-up being collective -
+            # is part of the links' names.
+            context = topology.context
+            count = _link_setups[context.name] = _link_setups.get(context.name, 0) + 1
+            if count > 1:
+                context = dataclasses.replace(context, name=f"{context.name}.setup{count}")
             links = topology.transport.create_groups(groups, timeout=topology.timeout,
-                                                     context=topology.context)
+                                                     context=context)
             for ranks, link in zip(groups, links):
                 if (link is not None) != (topology.rank in ranks):
                     raise RuntimeError(

@@ -114,3 +114,26 @@ def _config_one(rank, topology):
 
 def test_cpu_simulation_acceptance_config(tmp_path):
     run_ranks(LAYOUTS["2+2"], _config_one, tmp_path, timeout=180)
+
+
+def _sharded_twice(rank, topology):
+    """A policy that builds its own links can be set up again on the same topology (a benchmark
+    racing policies does): the second set of links must not meet the first one's store keys."""
+    from gpubridge_b200 import policies
+    results = []
+    made = []
+    for _ in range(3):
+        policy = policies.ShardedBridge()
+        policy.setup(topology)
+        made.append(policy)
+        t = rank_tensor(rank, 1000)
+        policy.all_reduce(t, topology)
+        results.append(torch.equal(t, expected_sum(topology.world_size, 1000)))
+    for policy in made:
+        policy.close()
+    return results
+
+
+def test_a_link_building_policy_can_be_set_up_again(tmp_path):
+    for result in run_ranks(LAYOUTS["2+2"], _sharded_twice, tmp_path):
+        assert result == [True, True, True]
