@@ -11,7 +11,8 @@ Steps (what the reference spreads over ``scripts/gpu/explorer/*.sbatch`` and ``c
                        2+2+2+2 / 3+5 on eight GPUs)
     check-<policy>     the same under the pipelined and the sharded policy
     init-error         a negative step: init() must fail with the expected message
-    p2p                point-to-point checks through the torch backend
+    p2p                point-to-point checks through the torch backend, and once more with the
+                       C++ front end (GPUBRIDGE_FRONT_END=native)
     gate               the numerical gate (four ranks, both arms)
     streams            the stream-ordering mutation run (one GPU)
     sweep              a short all-reduce sweep against NCCL
@@ -77,6 +78,10 @@ def plan(out: Path, gpus: int, cpu: bool) -> list[dict]:
             expect=r"init\(\) failed")
         add("p2p", torchrun(gpus, port[0] + 1, "-m", "gpubridge_b200.kit.check", "--out", str(out / "p2p"),
                             "--p2p-only"), {"GPUBRIDGE_SPLIT_TEST": "half"})
+        # the same checks with the C++ c10d::Backend in front of the Python group
+        add("p2p-cpp-front-end", torchrun(gpus, port[0] + 1, "-m", "gpubridge_b200.kit.check", "--out",
+                                          str(out / "p2p-cpp-front-end"), "--p2p-only"),
+            {"GPUBRIDGE_SPLIT_TEST": "half", "GPUBRIDGE_FRONT_END": "native"})
     if gpus >= 4:
         for arm in ("bridged", "native"):
             add(f"gate-{arm}", torchrun(4, port[0] + 1, "-m", "gpubridge_b200.kit.numerical_gate", "--out",

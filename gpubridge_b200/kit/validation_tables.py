@@ -44,6 +44,7 @@ ITEMS = [
      ("check-pipelined-reduce-bridge-broadcast", "check-sharded-bridge"), ()),
     ("negative-init", "a configuration that cannot work fails on every rank with its reason", ("init-error",), ()),
     ("p2p", "send / recv / batched P2P through the torch backend", ("p2p",), ()),
+    ("cpp-front-end", "the same through the C++ c10d::Backend", ("p2p-cpp-front-end",), ()),
     ("numerics", "training numerics inside the gate's bounds, controls fail as they must",
      ("gate-bridged", "gate-native"), ()),
     ("performance", "all-reduce sweep against NCCL", ("sweep",), ()),
