@@ -73,6 +73,18 @@ def main(argv=None) -> int:
                 e["skipped"] = "no GPU and no built library"
         except Exception as exc:  # noqa: BLE001
             fail(e, f"{type(exc).__name__}: {exc}")
+    with journal.stage("cpp_front_end") as e:
+        try:
+            from gpubridge_b200.ops import _build_c10d
+            e["path"], e["stale"] = _build_c10d.OUT, _build_c10d.stale()
+            if e["stale"]:
+                e["skipped"] = "not built for these sources (python -m gpubridge_b200.ops._build_c10d)"
+            else:
+                e["loaded"] = hasattr(_build_c10d.load(), "GbBackend")
+                if not e["loaded"]:
+                    fail(e, "gb_c10d.so loaded without its backend class")
+        except Exception as exc:  # noqa: BLE001
+            fail(e, f"{type(exc).__name__}: {exc}")
     with journal.stage("import") as e:
         import gpubridge_b200
         here = Path(__file__).resolve().parents[1]
