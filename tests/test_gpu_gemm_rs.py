@@ -34,7 +34,9 @@ def _reference(world, rank, P, Q, R):
     return (total / world)[rank * rows:(rank + 1) * rows]
 
 
-def test_one_rank():
+def test_one_rank(monkeypatch):
+    # a first run: keep every device-side wait short, so that a mistake ends in seconds
+    monkeypatch.setenv("GPUBRIDGE_WAIT_TIMEOUT_MS", "5000")
     from gpubridge_b200.ops import fabric as fabric_mod
     from gpubridge_b200.ops.gemm import GemmReduceScatter
     dev = torch.device("cuda", 0)
@@ -87,4 +89,5 @@ def _on_a_team(rank, topology):
                     reason="needs at least two GPUs")
 def test_on_a_team_of_two(tmp_path):
     from _harness import gpu_ranks, run_ranks
-    run_ranks(gpu_ranks(2), _on_a_team, tmp_path, timeout=240)
+    run_ranks(gpu_ranks(2), _on_a_team, tmp_path, timeout=240,
+              env={"GPUBRIDGE_WAIT_TIMEOUT_MS": "10000", "NCCL_NVLS_ENABLE": "0"})
