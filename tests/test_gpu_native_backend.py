@@ -140,5 +140,5 @@ def _through_the_backend(rank, world):
 @pytest.mark.parametrize("split", [{}, {"GPUBRIDGE_SPLIT_TEST": "half"}])
 def test_backend_end_to_end(tmp_path, split):
     world = 8 if NGPU >= 8 else 4 if NGPU >= 4 else 2
-    run_ranks(gpu_ranks(world), _through_the_backend, tmp_path, mode="native-backend", env=split,
-              timeout=240)
+    run_ranks(gpu_ranks(world), _through_the_backend, tmp_path, mode="native-backend",
+              env={**split, "GPUBRIDGE_WAIT_TIMEOUT_MS": "10000"}, timeout=240)
