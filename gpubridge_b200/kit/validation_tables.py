@@ -127,8 +127,10 @@ def tables(jobs: dict[str, dict]) -> tuple[dict, str]:
         out["runs"].append(row)
         md.append(f"| {name} | {'CPU simulation' if job['simulated'] else 'GPU'} | {len(good)} | "
                   f"{', '.join(bad) or '-'} | {', '.join(job['hosts']) or '-'} | "
-                  f"{job['gpu_count'] or 0} x {', '.join(job['gpus']) or '-'} | torch {soft['torch']}, CUDA "
-                  f"{soft['torch_cuda']}, NCCL {soft['nccl']}, gpubridge_b200 {soft['gpubridge_b200']} |")
+                  f"{job['gpu_count'] or 0} x {', '.join(job['gpus']) or '-'} | "
+                  + (f"torch {soft['torch']}, CUDA {soft['torch_cuda']}, NCCL {soft['nccl']}, "
+                     f"gpubridge_b200 {soft['gpubridge_b200']}" if soft["torch"] else "- (see its steps' own rows)")
+                  + " |")
     md += ["", "## Items", "", "| item | establishes | verdict | where |", "|---|---|---|---|"]
     for key, meaning, steps, stages in ITEMS:
         where, gpu_states, sim_states = [], [], []
