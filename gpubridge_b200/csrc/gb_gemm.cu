@@ -10,8 +10,8 @@
 //   * GEMM blocks walk the output tiles shard by shard, starting with the own shard (which
 //     needs no transfer), and only wait for a shard's flag right before the first TMA load
 //     that touches it - so the tensor cores work on shard s while shard s+1 is in flight;
-//   * inside a GEMM block: warp 0 issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no
-//     multicast: every block reads this GPU's own memory) into a 4-stage shared-memory ring,
+//   * inside a GEMM block: warp 0 issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, one
+//     destination block per load: every block reads this GPU's own memory) into a 4-stage shared-memory ring,
 //     warp 1 issues tcgen05.mma (128 x 256 x 16, cta_group::1) from shared-memory descriptors
 //     into one of two 256-column accumulators in tensor memory, warps 2-5 drain the other
 //     accumulator with tcgen05.ld, convert to bf16 and store.
