@@ -45,7 +45,8 @@ struct GbTeam {
     int pad;
 };
 
-enum GbStatus { GB_OK = 0, GB_TIMEOUT_PEER = 1, GB_TIMEOUT_GRID = 2 };
+// (3 is GB_TIMEOUT_COPY, a bulk copy of the ring that never landed: gb_bulk.cuh)
+enum GbStatus { GB_OK = 0, GB_TIMEOUT_PEER = 1, GB_TIMEOUT_GRID = 2, GB_TIMEOUT_TENSOR = 4 };
 
 // ---- memory-order helpers ---------------------------------------------------------------
 __device__ __forceinline__ unsigned long long gb_now() {
@@ -138,7 +139,10 @@ __device__ __forceinline__ bool gb_sync(const GbTeam& tm, int channel, unsigned 
         const unsigned seq = s_seq;
         const int t = threadIdx.x;
         const int row = channel * GB_MAX_RANKS;
-        if (with_peers && t < tm.world && t != tm.rank) {
+        // A rank that has already given up (in this kernel or an earlier one) tells nobody that
+        // it arrived: its data may be incomplete, and the peers' own deadlines then report it.
+        const bool dead = gb_ld_volatile(&tm.ctrl->abort) != 0u;
+        if (with_peers && !dead && t < tm.world && t != tm.rank) {
             __threadfence_system();
             gb_st_release_sys(gb_flag_row(tm, t) + row + tm.rank, seq);
         }

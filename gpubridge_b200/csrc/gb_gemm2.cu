@@ -12,14 +12,16 @@
 // leader's barrier), warp 1 of the leader issues tcgen05.mma for the pair and commits to the
 // barriers of both CTAs, warps 2-5 of each CTA drain their CTA's accumulator.  No load
 // fans out to several CTAs: every CTA reads this GPU's own memory with plain tile loads.
-// Every wait has a deadline; on expiry an error word is set, the wait falls through and the
-// CTAs still meet at the cluster barrier, free their tensor memory and return.
+// Every wait has a deadline (the team's wait limit) and ends early once the error word or the
+// team's abort word is set; a role whose wait gave up leaves its tile loop, and the CTAs still
+// meet at the cluster barrier, free their tensor memory and return.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "gb_common.cuh"
+#include "gb_tc.cuh"
 
 namespace {
 
@@ -31,7 +33,6 @@ constexpr int B_BYTES = HALF * BK * 2;         // 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS2 = 192;
 constexpr int TMEM_COLS = 512;
-constexpr unsigned long long WAIT_NS = 2000000000ull;      // 2 s per wait
 
 struct Gemm2Args {
     __nv_bfloat16* y;
@@ -44,7 +45,8 @@ struct Gemm2Args {
     int shard_rows;
     int gemm_blocks;                 // even; the CTAs after the communication CTAs compute in pairs
     int comm_blocks;                 // even; CTAs [0, comm_blocks) communicate (scheduled first)
-    size_t ws_off;
+    size_t ws_off;                   // staging region inside the workspaces: two halves ...
+    size_t ws_half;                  // ... this far apart, selected by the collective counter's parity
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -73,28 +75,6 @@ __device__ __forceinline__ void bar_expect(uint64_t* bar, uint32_t bytes) {
 // One arrival on a barrier given by its address in the cluster window (own or peer CTA).
 __device__ __forceinline__ void bar_arrive_cluster(uint32_t addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(addr) : "memory");
-}
-__device__ __forceinline__ bool bar_try(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(s32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, unsigned int* error,
-                                         unsigned code) {
-    unsigned long long t0 = 0;
-    for (unsigned spins = 0; spins < 0x7fffffffu; ++spins) {
-        if (bar_try(bar, parity)) return true;
-        if ((spins & 255u) == 255u) {
-            const unsigned long long now = gb_now();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_NS) break;
-        }
-    }
-    atomicExch(error, code);
-    return false;
 }
 // Tile load of the pair: the data lands in this CTA, the bytes are counted on `bar` (an
 // address in the cluster window: the leader's barrier).
@@ -165,14 +145,17 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
         const GbLane L = gb_lane_blocks(0, comm_blocks, tm.ld_mode);
         const size_t shard_bytes = (size_t)a.shard_rows * a.K * 2;
         char* mine = reinterpret_cast<char*>(a.gathered) + (size_t)tm.rank * shard_bytes;
+        // the half of the staging region the collective before this one did not use (read
+        // before the barrier below advances the counter)
+        const size_t stage_off = a.ws_off + (size_t)(gb_ld_volatile(&tm.ctrl->epoch) & 1u) * a.ws_half;
         gb_copy_bytes(L, mine, a.shard, shard_bytes, false);
-        if (tm.world > 1) gb_copy_bytes(L, tm.ws[tm.rank] + a.ws_off, a.shard, shard_bytes, false);
+        if (tm.world > 1) gb_copy_bytes(L, tm.ws[tm.rank] + stage_off, a.shard, shard_bytes, false);
         if (!gb_sync(tm, 0, (unsigned)comm_blocks, 0, true, true)) return;
         if (L.tid == 0) gb_st_release_gpu(a.flags + tm.rank, a.epoch);
         for (int d = 1; d < tm.world; ++d) {
             const int peer = (tm.rank + d) % tm.world;
             gb_copy_bytes(L, reinterpret_cast<char*>(a.gathered) + (size_t)peer * shard_bytes,
-                          tm.ws[peer] + a.ws_off, shard_bytes, true);
+                          tm.ws[peer] + stage_off, shard_bytes, true);
             if (!gb_sync(tm, 0, (unsigned)comm_blocks, 1, false, false)) return;
             if (L.tid == 0) gb_st_release_gpu(a.flags + peer, a.epoch);
         }
@@ -186,7 +169,9 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;          // [2]
     uint64_t* acc_empty = acc_full + 2;           // [2], used on the leader
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* drained = acc_empty + 2;            // the issuer's last instructions after a failure
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
+    const TcGuard guard = {a.error, &tm.ctrl->abort, tm.timeout_ns};
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cta_rank();             // 0: the pair's leader
     const bool leader = rank == 0;
@@ -194,6 +179,7 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { bar_init(full + s, 1); bar_init(empty + s, 1); }
         for (int b = 0; b < 2; ++b) { bar_init(acc_full + b, 1); bar_init(acc_empty + b, 8); }
+        bar_init(drained, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -217,22 +203,16 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
         // ---- TMA producer of this CTA's halves ----
         uint32_t stage = 0, phase = 0;
         int ready_shard = -1;
-        for (long t = pair; t < total; t += pairs) {
+        bool alive = true;
+        for (long t = pair; alive && t < total; t += pairs) {
             const Tile2 tile = tile_of(a, tm, t);
             if (tile.shard != ready_shard) {
-                bool ok = false;
-                unsigned long long t0 = gb_now();
-                for (unsigned spins = 0; spins < 0x7fffffffu; ++spins) {
-                    if ((int)(gb_ld_acquire_gpu(a.flags + tile.shard) - a.epoch) >= 0) { ok = true; break; }
-                    __nanosleep(100);
-                    if ((spins & 63u) == 63u && gb_now() - t0 > 5ull * WAIT_NS) break;
-                }
-                if (!ok) atomicExch(a.error, 2u);
+                if (!tc_wait_flag(a.flags + tile.shard, a.epoch, guard, 2u)) { alive = false; break; }
                 asm volatile("fence.proxy.async.global;" ::: "memory");
                 ready_shard = tile.shard;
             }
             for (int kb = 0; kb < k_blocks; ++kb) {
-                bar_wait(empty + stage, phase ^ 1u, a.error, 3u);
+                if (!mbar_wait(empty + stage, phase ^ 1u, guard, 1u)) { alive = false; break; }
                 unsigned char* sa = tiles + stage * STAGE_BYTES;
                 const uint32_t leader_full = in_cta(s32(full + stage), 0);
                 if (leader) bar_expect(full + stage, 2 * STAGE_BYTES);   // both CTAs' bytes
@@ -241,17 +221,22 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
+        // Loads still in flight after a failure land in this CTA's shared memory and count on
+        // the leader's barriers; both CTAs stay until the cluster barrier at the end, which the
+        // leader reaches only after its issuer has waited (bounded) for the tensor pipe.
     } else if (warp == 1 && lane == 0 && leader) {
         // ---- MMA issuer of the pair ----
         constexpr uint32_t idesc = pair_idesc(BM, BN);
         uint32_t stage = 0, phase = 0, local = 0;
-        for (long t = pair; t < total; t += pairs, ++local) {
+        bool alive = true;
+        for (long t = pair; alive && t < total; t += pairs, ++local) {
             const uint32_t buf = local & 1u, use = local >> 1;
-            bar_wait(acc_empty + buf, (use & 1u) ^ 1u, a.error, 4u);   // both epilogues drained it
+            // both epilogues drained it
+            if (!mbar_wait(acc_empty + buf, (use & 1u) ^ 1u, guard, 3u)) { alive = false; break; }
             fence_after();
             const uint32_t tmem_d = tmem_base + buf * BN;
             for (int kb = 0; kb < k_blocks; ++kb) {
-                bar_wait(full + stage, phase, a.error, 5u);
+                if (!mbar_wait(full + stage, phase, guard, 4u)) { alive = false; break; }
                 fence_after();
                 const unsigned char* sa = tiles + stage * STAGE_BYTES;
                 const uint64_t da = tile_desc(sa), db = tile_desc(sa + A_BYTES);
@@ -262,8 +247,19 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                 pair_commit(in_cta(s32(empty + stage), 1));            // ... and in the peer
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
-            pair_commit(s32(acc_full + buf));
-            pair_commit(in_cta(s32(acc_full + buf), 1));
+            if (alive) {
+                pair_commit(s32(acc_full + buf));
+                pair_commit(in_cta(s32(acc_full + buf), 1));
+            }
+        }
+        if (!alive) {
+            // nothing of the pair's earlier instructions may be in flight when tensor memory goes
+            pair_commit(s32(drained));
+            const unsigned long long t0 = tc_now();
+            for (unsigned spins = 0; spins < (1u << 20); ++spins) {
+                if (mbar_try_wait(drained, 0u)) break;
+                if ((spins & 31u) == 31u && tc_now() - t0 > 2000000ull) break;      // 2 ms
+            }
         }
     } else if (warp >= 2) {
         // ---- epilogue of this CTA's 128 rows ----
@@ -272,7 +268,7 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
         for (long t = pair; t < total; t += pairs, ++local) {
             const Tile2 tile = tile_of(a, tm, t);
             const uint32_t buf = local & 1u, use = local >> 1;
-            bar_wait(acc_full + buf, use & 1u, a.error, 6u);
+            if (!mbar_wait_warp(acc_full + buf, use & 1u, guard, 5u)) break;
             fence_after();
             const int row = tile.m0 + (int)rank * HALF + quarter * 32 + lane;
             const int shard_end = (tile.shard + 1) * a.shard_rows;
@@ -346,7 +342,7 @@ bool make_map2(CUtensorMap* map, const void* base, int rows, int K) {
 extern "C" int gb_allgather_gemm_pair(const GbTeam* team, void* y, const void* x, const void* shard,
                                       void* gathered, unsigned int* flags, unsigned int* error,
                                       unsigned int epoch, int M, int N, int K, size_t ws_off,
-                                      int gemm_blocks, int comm_blocks, cudaStream_t stream) {
+                                      size_t ws_half, int gemm_blocks, int comm_blocks, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || N % team->world || gemm_blocks < 2 ||
         comm_blocks < 2 || (gemm_blocks & 1) || (comm_blocks & 1))
         return (int)cudaErrorInvalidValue;
@@ -360,6 +356,7 @@ extern "C" int gb_allgather_gemm_pair(const GbTeam* team, void* y, const void* x
     a.M = M; a.N = N; a.K = K;
     a.shard_rows = N / team->world;
     a.ws_off = ws_off;
+    a.ws_half = ws_half;
     const size_t smem = STAGES * STAGE_BYTES + 256 + 1024;
     static bool configured = false;
     static int resident_clusters = 0;

@@ -21,10 +21,11 @@
 // parity is the team's collective counter's, as for every region written before a kernel's
 // first barrier, and the two parities are the two halves of the region whatever the shapes - the
 // same halves the reduce-scatter kernel uses when it shares the region, so a collective never
-// writes where a slow peer may still read the one before it.  Every wait is bounded; on expiry an error word or the team's status record is
-// set, tensor memory is freed and the kernel returns.
+// writes where a slow peer may still read the one before it.  Every wait has a deadline (the
+// team's wait limit) and ends early once the error word or the team's abort word is set; the
+// role then leaves its tile loop, tensor memory is freed and the kernel returns.
 #include "gb_common.cuh"
-#include "gb_tc.cuh"
+#include "gb_tc_tile.cuh"
 
 namespace {
 
@@ -64,12 +65,15 @@ gemm_reduce_scatter_kernel(const __grid_constant__ CUtensorMap map_a,
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;          // [2]
     uint64_t* acc_empty = acc_full + 2;           // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* drained = acc_empty + 2;            // the issuer's last instructions after a failure
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
+    const TcGuard guard = {a.error, &tm.ctrl->abort, tm.timeout_ns};
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
+        mbar_init(drained, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
@@ -85,29 +89,34 @@ gemm_reduce_scatter_kernel(const __grid_constant__ CUtensorMap map_a,
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----
-        uint32_t stage = 0, phase = 0;
-        for (long t = blockIdx.x; t < total; t += stride) {
+        uint32_t stage = 0, phase = 0, issued = 0;
+        bool alive = true;
+        for (long t = blockIdx.x; alive && t < total; t += stride) {
             const RsTile tile = rs_tile_at(a, tm, t, p_tiles, q_tiles);
             for (int kb = 0; kb < k_blocks; ++kb) {
-                mbar_wait(empty + stage, phase ^ 1u, a.error);
+                if (!mbar_wait(empty + stage, phase ^ 1u, guard, 1u)) { alive = false; break; }
                 unsigned char* sa = tiles + stage * STAGE_BYTES;
                 mbar_expect_tx(full + stage, STAGE_BYTES);
                 tma_load_2d(sa, &map_a, kb * BK, tile.p0, full + stage);
                 tma_load_2d(sa + A_BYTES, &map_b, kb * BK, tile.q0, full + stage);
+                ++issued;
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
+        if (!alive) tc_drain_loads(full, issued, STAGES);
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
         constexpr uint32_t idesc = instr_desc(BM, BN);
         uint32_t stage = 0, phase = 0, local = 0;
-        for (long t = blockIdx.x; t < total; t += stride, ++local) {
+        bool alive = true;
+        for (long t = blockIdx.x; alive && t < total; t += stride, ++local) {
             const uint32_t buf = local & 1u, use = local >> 1;
-            mbar_wait(acc_empty + buf, (use & 1u) ^ 1u, a.error);   // the epilogue drained it
+            // the epilogue drained it
+            if (!mbar_wait(acc_empty + buf, (use & 1u) ^ 1u, guard, 3u)) { alive = false; break; }
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + buf * BN;
             for (int kb = 0; kb < k_blocks; ++kb) {
-                mbar_wait(full + stage, phase, a.error);
+                if (!mbar_wait(full + stage, phase, guard, 4u)) { alive = false; break; }
                 tc_fence_after();
                 const unsigned char* sa = tiles + stage * STAGE_BYTES;
                 const uint64_t da = smem_desc(sa), db = smem_desc(sa + A_BYTES);
@@ -117,8 +126,9 @@ gemm_reduce_scatter_kernel(const __grid_constant__ CUtensorMap map_a,
                 tc_commit(empty + stage);                      // frees the stage when they finish
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
-            tc_commit(acc_full + buf);
+            if (alive) tc_commit(acc_full + buf);
         }
+        if (!alive) tc_drain_mma(drained);
     } else if (warp >= 2) {
         // ---- epilogue: tensor memory -> registers -> bf16 -> the row owner's workspace ----
         const int quarter = warp & 3;                          // the lanes this warp may read
@@ -127,7 +137,7 @@ gemm_reduce_scatter_kernel(const __grid_constant__ CUtensorMap map_a,
         for (long t = blockIdx.x; t < total; t += stride, ++local) {
             const RsTile tile = rs_tile_at(a, tm, t, p_tiles, q_tiles);
             const uint32_t buf = local & 1u, use = local >> 1;
-            mbar_wait(acc_full + buf, use & 1u, a.error);
+            if (!mbar_wait_warp(acc_full + buf, use & 1u, guard, 5u)) break;
             tc_fence_after();
             const int row = tile.p0 + quarter * 32 + lane;
             const bool live = row < a.P;
@@ -170,6 +180,10 @@ gemm_reduce_scatter_kernel(const __grid_constant__ CUtensorMap map_a,
     if (warp == 1) tmem_free(tmem_base, TMEM_COLS);
 
     // ---- every rank's partial rows have been sent: meet, then add the slots of the own rows ----
+    // A block whose GEMM part gave up raises the team's abort word first, so that the barrier
+    // below ends at once on this rank and the peers' waits for it run into their deadline with
+    // a status record instead of adding slots that were never filled.
+    if (threadIdx.x == 0 && gb_ld_volatile(a.error) != 0u) gb_fail(tm, GB_TIMEOUT_TENSOR, 0u, 0u, 0u);
     if (!gb_sync_all(tm, 0, true)) return;
     const char* slots = tm.ws[tm.rank] + a.ws_off + (size_t)parity * a.half_bytes;
     const size_t nvec = a.slot_bytes >> 4;                     // vectors of eight bf16 values

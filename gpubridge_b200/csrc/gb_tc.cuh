@@ -1,7 +1,7 @@
-// tcgen05 / TMA / mbarrier wrappers and tensor-map helpers for single-CTA-group GEMM kernels
-// (bf16 operands, fp32 accumulators in tensor memory, 128 x 256 x 64 tiles, 128-byte swizzle).
-// The same sequences the all-gather GEMM (gb_gemm.cu) issues, for kernels that live in other
-// files.  Include from one translation unit per kernel file; everything has internal linkage.
+// tcgen05 / TMA / mbarrier wrappers, guarded waits and tensor-map helpers shared by the GEMM
+// kernels (bf16 operands, fp32 accumulators in tensor memory, 128-byte swizzle).  The tile
+// shape of the single-CTA kernels is in gb_tc_tile.cuh; the CTA-pair kernel has its own.
+// Include from one translation unit per kernel file; everything has internal linkage.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -9,15 +9,6 @@
 #include <stdint.h>
 
 namespace {
-
-constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB
-constexpr int B_BYTES = BN * BK * 2;                 // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int GEMM_THREADS = 192;                    // TMA warp, MMA warp, four epilogue warps
-constexpr int TMEM_COLS = 512;                       // two accumulators of 256 columns
-constexpr unsigned WAIT_LIMIT = 1u << 27;
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -41,14 +32,85 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false (and records it) when the barrier never flipped.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* error) {
-    for (unsigned spins = 0; spins < WAIT_LIMIT; ++spins) {
+// What a role needs to give up cleanly: the kernel's error word, the team's abort word (set by
+// any bounded wait of the team that ran out, in this or an earlier kernel) and the deadline of
+// one wait.  Error codes: 1 operand stage never freed, 2 shard flag never raised, 3 accumulator
+// never drained, 4 operand stage never filled, 5 accumulator never completed.
+struct TcGuard {
+    unsigned int* error;
+    const unsigned int* abort;
+    unsigned long long limit_ns;
+};
+__device__ __forceinline__ unsigned long long tc_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool tc_dead(const TcGuard& g) {
+    return *reinterpret_cast<volatile const unsigned int*>(g.error) != 0u ||
+           *reinterpret_cast<volatile const unsigned int*>(g.abort) != 0u;
+}
+// Wait until the barrier's phase `parity` has completed.  Gives up - and returns false - when
+// the deadline passes (the error word then gets `code`) or when some other wait of the kernel or
+// the team has already given up.  After a false return the caller leaves its tile loop: a role
+// that kept going would run every later wait to its deadline too.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const TcGuard& g,
+                                          unsigned code) {
+    unsigned long long t0 = 0;
+    for (unsigned spins = 0; spins < 0x40000000u; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (spins > 1024) __nanosleep(64);
+        if ((spins & 31u) == 31u) {
+            if (tc_dead(g)) return false;
+            const unsigned long long now = tc_now();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > g.limit_ns) break;
+            __nanosleep(64);
+        }
     }
-    atomicExch(error, 1u);
+    atomicCAS(g.error, 0u, code);
     return false;
+}
+// The same wait by a whole warp whose next instruction is warp-wide (tcgen05.ld): either every
+// lane goes on or none does.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const TcGuard& g,
+                                               unsigned code) {
+    const bool ok = mbar_wait(bar, parity, g, code);
+    return __all_sync(0xffffffffu, ok) != 0;
+}
+// Poll a flag in global memory (written with release semantics by another block of this GPU)
+// until it reaches `want`; same giving-up rules as mbar_wait.
+__device__ __forceinline__ bool tc_wait_flag(const unsigned int* flag, unsigned want,
+                                             const TcGuard& g, unsigned code) {
+    unsigned long long t0 = 0;
+    for (unsigned spins = 0; spins < 0x40000000u; ++spins) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int)(v - want) >= 0) return true;
+        __nanosleep(100);
+        if ((spins & 31u) == 31u) {
+            if (tc_dead(g)) return false;
+            const unsigned long long now = tc_now();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > g.limit_ns) break;
+        }
+    }
+    atomicCAS(g.error, 0u, code);
+    return false;
+}
+// After a producer gave up: the loads it already issued still write into this block's shared
+// memory, so the block may not exit before they have landed.  `issued` loads went out in ring
+// order; wait - briefly, bounded - for the last `stages` of them.
+__device__ __forceinline__ void tc_drain_loads(uint64_t* full, uint32_t issued, int stages) {
+    const uint32_t first = issued > (uint32_t)stages ? issued - (uint32_t)stages : 0u;
+    for (uint32_t i = first; i < issued; ++i) {
+        uint64_t* bar = full + (i % (uint32_t)stages);
+        const uint32_t parity = (i / (uint32_t)stages) & 1u;
+        const unsigned long long t0 = tc_now();
+        for (unsigned spins = 0; spins < (1u << 20); ++spins) {
+            if (mbar_try_wait(bar, parity)) break;
+            if ((spins & 31u) == 31u && tc_now() - t0 > 2000000ull) break;      // 2 ms
+        }
+    }
 }
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y,
                                             uint64_t* bar) {
@@ -75,6 +137,17 @@ __device__ __forceinline__ void tc_fence_after() {
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                  :: "r"(smem_u32(bar)) : "memory");
+}
+// After the issuer gave up: its earlier tcgen05.mma instructions may still be reading shared
+// memory and writing tensor memory.  Commit once more to a spare barrier and wait - briefly,
+// bounded - for that, so that nothing is in flight when the block frees its tensor memory.
+__device__ __forceinline__ void tc_drain_mma(uint64_t* spare) {
+    tc_commit(spare);
+    const unsigned long long t0 = tc_now();
+    for (unsigned spins = 0; spins < (1u << 20); ++spins) {
+        if (mbar_try_wait(spare, 0u)) break;
+        if ((spins & 31u) == 31u && tc_now() - t0 > 2000000ull) break;          // 2 ms
+    }
 }
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
                                        uint32_t idesc, uint32_t accumulate) {
@@ -131,11 +204,12 @@ EncodeTiled encoder() {
 
 // A [rows, K] row-major bf16 matrix, read in boxes of box_rows x 64 with 128-byte swizzle.
 bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    constexpr int BOX_K = 64;                        // 128 bytes: one swizzle row
     EncodeTiled encode = encoder();
     if (encode == nullptr) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)BOX_K, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

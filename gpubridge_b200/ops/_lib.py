@@ -122,7 +122,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_adamw_step.argtypes = [vp, vp, vp, vp, sz, vp] + [ctypes.c_float] * 6 + [i, vp]
     L.gb_xent_fwd_bwd.argtypes = [vp, i, vp, sz, sz, sz, vp, vp, vp, vp]
     L.gb_allgather_gemm.argtypes = [ctypes.POINTER(GbTeam), vp, vp, vp, vp, vp, vp, ctypes.c_uint,
-                                    i, i, i, sz, i, i, vp]
+                                    i, i, i, sz, sz, i, i, vp]
     L.gb_allgather_gemm_pair.argtypes = L.gb_allgather_gemm.argtypes
     L.gb_gemm_reduce_scatter_bytes.restype = sz
     L.gb_gemm_reduce_scatter_bytes.argtypes = [i, i, i]

@@ -301,7 +301,8 @@ class Fabric:
         if code == 0:
             return
         kinds = {1: "a peer never arrived at a barrier", 2: "a block of the local grid never "
-                 "arrived at a barrier"}
+                 "arrived at a barrier", 3: "a bulk copy never landed",
+                 4: "a wait inside a tensor-core pipeline ran out"}
         error = FabricError(
             f"gpubridge fused collective failed on team rank {self._status[4]}: "
             f"{kinds.get(code, f'status {code}')} (peer {self._status[1]}, barrier "

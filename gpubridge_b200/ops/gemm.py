@@ -68,7 +68,8 @@ class AllGatherLinear:
                 code = entry(
                     ctypes.byref(fabric.team), y.data_ptr(), x.data_ptr(), shard.data_ptr(),
                     self.gathered.data_ptr(), self.flags.data_ptr(), self.error.data_ptr(),
-                    self.epoch, x.shape[0], self.N, self.K, fabric.off_ag, self.gemm_blocks,
+                    self.epoch, x.shape[0], self.N, self.K, fabric.off_ag, 2 * fabric.len_ag,
+                    self.gemm_blocks,
                     self.comm_blocks, torch.cuda.current_stream(x.device).cuda_stream)
                 if code == -3:
                     raise RuntimeError("cuTensorMapEncodeTiled is unavailable or refused the shapes")

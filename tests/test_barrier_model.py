@@ -172,3 +172,66 @@ def test_a_missing_rank_ends_every_wait(missing):
                 assert rank.status[1] == missing
             # the failed barrier still publishes its number (as the kernel does); nothing follows it
             assert rank.seq <= 1 and rank.epoch <= 1
+
+
+# ---- pull-style collectives: stage the own piece, meet, read every peer's staging area ----------
+# The all-gather (csrc/gb_collectives.cu: allgather_kernel) leaves without a closing barrier, and
+# the all-gather fused into the GEMM (csrc/gb_gemm.cu) stages into the same region.  A rank that
+# has finished the all-gather may launch the GEMM and stage its weight shard while a slower peer
+# is still pulling the all-gather's piece out of that rank's memory - unless the two collectives
+# use different halves of the region, which the parity of the collective counter guarantees.
+def _pull_block(model, r, b, kernels, half_of):
+    number = 0
+    for kernel in range(kernels):
+        me = model.ranks[r]
+        half = half_of(kernel, me.epoch)                      # read at kernel start
+        if b == 0:
+            yield
+            me.buffer[half][r] = (kernel, r)                    # stage the own piece locally
+        ok = yield from model.sync(r, True, number)
+        number += 1
+        if not ok:
+            return
+        for p in range(model.world):                            # pull from every peer's memory
+            yield
+            got = model.ranks[p].buffer[half][p]
+            if got != (kernel, p):
+                model.problems.append(f"rank {r} block {b} collective {kernel}: pulled {got} from {p}")
+        if kernel % 2 == 1:                                     # the fused GEMM closes with a barrier
+            ok = yield from model.sync(r, False, number)
+            number += 1
+            if not ok:
+                return
+
+
+def _run_pull(world, blocks, seed, half_of, kernels=6):
+    model = Model(world, blocks, seed)
+    live = [_pull_block(model, r, b, kernels, half_of) for r in range(world) for b in range(blocks)]
+    while live:
+        i = model.rng.randrange(len(live))
+        for _ in range(model.rng.choice((1, 1, 2, 5, 20))):
+            try:
+                next(live[i])
+            except StopIteration:
+                live.pop(i)
+                break
+    return model.problems
+
+
+@pytest.mark.parametrize("world,blocks", [(2, 1), (3, 2), (8, 1)])
+def test_all_gather_then_fused_gemm_stage_into_different_halves(world, blocks):
+    """Collectives alternate: all-gather (even), fused all-gather GEMM (odd).  Both pick the
+    staging half from the collective counter's parity, so the GEMM's staging never lands in the
+    half a slow peer is still pulling the all-gather from."""
+    for seed in range(60):
+        problems = _run_pull(world, blocks, seed, lambda kernel, epoch: epoch & 1)
+        assert not problems, (seed, problems[:3])
+
+
+def test_fused_gemm_always_staging_into_the_first_half_is_caught():
+    """The negative control: the GEMM staging into half 0 whatever the counter says (and the
+    all-gather before it having used half 0 too) corrupts a slow peer's all-gather."""
+    def half_of(kernel, epoch):
+        return 0 if kernel % 2 == 1 else epoch & 1
+    seen = any(_run_pull(3, 1, seed, half_of, kernels=8) for seed in range(300))
+    assert seen, "the model cannot see a staging area overwritten under a slow reader"
