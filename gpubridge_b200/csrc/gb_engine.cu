@@ -6,11 +6,15 @@
 
 #include "gb_common.cuh"
 #include "gb_engine.h"
+#include "gb_switch.h"
 
 extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const GbTeam* team,
                                 const GbArgs* args, int grid, cudaStream_t stream);
 extern "C" int gb_launch_copy(int kind, const GbTeam* team, const GbArgs* args, int grid,
                               cudaStream_t stream);
+extern "C" int gb_switch_all_reduce(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
+                                    size_t n, int dtype, int divide, int max_blocks,
+                                    cudaStream_t stream);
 
 namespace {
 
@@ -23,6 +27,10 @@ constexpr int kElemSize[8] = {4, 2, 2, 8, 1, 1, 4, 8};   // GbDtype order: f32 b
 struct Engine {
     GbTeam team;
     GbEngineConfig c;
+    // in-switch all-reduce: the team's group (flat) and this rank's island's (hierarchical order)
+    GbSwitch sw_team{}, sw_island{};
+    bool has_team = false, has_island = false;
+    size_t sw_min_bytes = 0;
     std::atomic<unsigned long long> launches{0};
 };
 
@@ -130,6 +138,13 @@ extern "C" int gb_engine_prepare_all_reduce(void* engine, const void* in, void* 
     a.n = n;
     a.divide = divide > 0 ? divide : 0;
     L->family = 0;
+    if ((e.has_island || e.has_team) && op == 0 && dtype <= 2 && nbytes >= e.sw_min_bytes) {
+        L->family = 2;
+        L->kind = e.has_island ? 1 : 0;
+        L->grid = e.c.max_blocks;
+        if (grid_cap > 0 && grid_cap < L->grid) L->grid = grid_cap;
+        return GB_ENGINE_OK;
+    }
     if (nbytes <= e.c.oneshot_slot && e.c.algo != 2) {
         a.off_a = e.c.off_oneshot;
         a.len_a = e.c.len_oneshot;
@@ -225,8 +240,28 @@ extern "C" int gb_engine_prepare_broadcast(void* engine, void* buffer, size_t nb
     return GB_ENGINE_OK;
 }
 
+// The team's switch memory, once it has been bound: `team` for the flat order, `island` for the
+// hierarchical one (either may be null); SUM / AVG of floats of at least min_bytes then go
+// through the switch.  The island group wins when both are given.
+extern "C" void gb_engine_set_switch(void* engine, const GbSwitch* team, const GbSwitch* island,
+                                     size_t min_bytes) {
+    Engine& e = *static_cast<Engine*>(engine);
+    e.has_team = team != nullptr;
+    e.has_island = island != nullptr;
+    if (team) e.sw_team = *team;
+    if (island) e.sw_island = *island;
+    e.sw_min_bytes = min_bytes;
+}
+
 namespace {
 int launch(Engine& e, const GbLaunch& L, int dtype, int op, void* stream) {
+    if (L.family == 2) {
+        const int rc = gb_switch_all_reduce(&e.team, L.kind == 1 ? &e.sw_island : &e.sw_team, L.args.in,
+                                            L.args.out, L.args.n, dtype, L.args.divide, L.grid,
+                                            static_cast<cudaStream_t>(stream));
+        if (rc == 0) e.launches.fetch_add(1, std::memory_order_relaxed);
+        return rc;
+    }
     const int rc = L.family == 0
         ? gb_launch_reduce(L.kind, dtype, op, /*codec=*/0, &e.team, &L.args, L.grid, static_cast<cudaStream_t>(stream))
         : gb_launch_copy(L.kind, &e.team, &L.args, L.grid, static_cast<cudaStream_t>(stream));

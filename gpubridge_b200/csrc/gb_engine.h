@@ -27,8 +27,8 @@ struct GbEngineConfig {
 };
 
 struct GbLaunch {                       // what a prepare call decided
-    int family;                         // 0 gb_launch_reduce, 1 gb_launch_copy
-    int kind, grid;
+    int family;                         // 0 gb_launch_reduce, 1 gb_launch_copy, 2 in-switch all-reduce
+    int kind, grid;                     // family 2: kind 1 = hierarchical order, grid = block limit
     GbArgs args;
 };
 
@@ -44,6 +44,8 @@ int gb_plan_hier(size_t n, int esize, int k, int m_max, int n_islands, size_t le
 
 void* gb_engine_create(const GbTeam* team, const GbEngineConfig* config);
 void gb_engine_destroy(void* engine);
+struct GbSwitch;
+void gb_engine_set_switch(void* engine, const GbSwitch* team, const GbSwitch* island, size_t min_bytes);
 unsigned long long gb_engine_launches(void* engine);
 size_t gb_sizeof_engine_config();
 size_t gb_sizeof_launch();

@@ -1,0 +1,288 @@
+// All-reduce through the NVSwitch (NVLS) with block-level barriers: SUM / AVG of f32, bf16, f16.
+//
+// Every rank owns staging memory bound to a multicast object of its group (gb_mcast.cu).  A
+// multimem.ld_reduce on the group's multicast address returns the sum over the group, computed
+// inside the switch; a multimem.st writes every member's copy at once.  A GPU then sends and
+// receives about 9/8 of the tensor instead of the 14/8 of a reduce-scatter + all-gather over
+// peer memory, and the adding costs no SM time.
+//
+// The tensor is cut into tiles; tile j belongs to block j mod B of EVERY rank (all ranks launch
+// the same grid).  A block works through its tiles as a software pipeline over `depth` staging
+// buffers of its own, with ONE barrier per step - and that barrier joins only the blocks of the
+// same index on the other ranks (a flag row per block in the peers' workspaces), never the
+// grid.  Blocks therefore drift apart and the steps of different blocks overlap: while some
+// copy, others have their requests in the switch.  Inside a block the first half of the warps
+// does the local copies and the second half the switch step, side by side.
+//
+// One group (a team of one island, or the flat mode of a team of several), depth 3; step i:
+//     A  copy tile i from the input into the own staging buffer              (local)
+//     B  member p: ld_reduce stripe p of tile i-1, divide for AVG, multimem.st it back   (switch)
+//     C  copy tile i-2 from the own staging buffer to the output             (local)
+// Several islands (hierarchical order: island sums first, rounded to the tensor's type, then
+// the islands in island order), the group is the island, depth 4; step i:
+//     A  copy tile i in
+//     B  owner p: ld_reduce stripe p of tile i-1 over the island and store the island sum into a
+//        slot of owner p of every island                                     (switch + NVLink)
+//     C  owner p: add the islands' slots of tile i-2 in island order, divide, multimem.st to the
+//        island                                                              (switch)
+//     D  copy tile i-3 out
+// Owners: positions 0 .. k-1 of every island, k the size of the smallest island.
+//
+// Why the buffers do not collide: a buffer is rewritten `depth` steps after it was first
+// written, and every barrier in between needs every member's arrival, so nobody is ever more
+// than one step ahead of the slowest member; the proof by cases is the CPU model in
+// tests/test_switch_model.py.  Every element is reduced by exactly one rank and then
+// multicast, so all ranks end with identical bits; the order of the addends inside a group is
+// the switch's, and integer-valued data is exact.
+//
+// Every wait is bounded (gb_wait_flag: spin limit + globaltimer deadline); on expiry the block
+// records the failure in the team's status block, raises the abort word and returns.
+#include "gb_common.cuh"
+#include "gb_switch.h"
+
+namespace {
+
+constexpr int SW_THREADS = 512;
+constexpr int SW_HALF = SW_THREADS / 2;
+
+template <typename T> struct SwVec {
+    static constexpr int N = 16 / sizeof(T);
+    union { uint4 u; T e[16 / sizeof(T)]; };
+};
+
+template <typename T> struct SwitchSum;
+template <> struct SwitchSum<float> {
+    static __device__ __forceinline__ uint4 load(const char* mc) {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+template <> struct SwitchSum<__nv_bfloat16> {
+    static __device__ __forceinline__ uint4 load(const char* mc) {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+template <> struct SwitchSum<__half> {
+    static __device__ __forceinline__ uint4 load(const char* mc) {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+__device__ __forceinline__ void switch_store(char* mc, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ size_t sw_round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+
+// Barrier of block `b` with the blocks `b` of every other rank of the team.  Row b of the flag
+// area of rank q holds, at index r, the last step rank r's block b announced to q.
+__device__ __forceinline__ bool sw_block_sync(const GbTeam& tm, const GbSwitch& sw, int b,
+                                              unsigned seq) {
+    __syncthreads();                                      // this block's stores are issued
+    const int q = (int)threadIdx.x;
+    if (q < tm.world && q != tm.rank) {
+        __threadfence_system();                           // ... and ordered before the flag, everywhere
+        unsigned* theirs = reinterpret_cast<unsigned*>(tm.ws[q] + sw.off_flags) +
+                           (size_t)b * GB_MAX_RANKS + tm.rank;
+        gb_st_release_sys(theirs, seq);
+        const unsigned* mine = reinterpret_cast<const unsigned*>(tm.ws[tm.rank] + sw.off_flags) +
+                               (size_t)b * GB_MAX_RANKS + q;
+        if (!gb_wait_flag(tm, mine, seq, true, tm.timeout_ns))
+            gb_fail(tm, GB_TIMEOUT_PEER, (unsigned)q, seq, 8u + (unsigned)(b & 7));
+    }
+    __syncthreads();
+    return gb_ld_volatile(&tm.ctrl->abort) == 0u;
+}
+
+struct SwTile { size_t off, len, padded; };
+__device__ __forceinline__ SwTile sw_tile(const SwArgs& a, int owners, int b, int B, int i) {
+    SwTile t;
+    t.off = ((size_t)i * B + b) * a.tile;
+    t.len = a.nbytes - t.off < a.tile ? a.nbytes - t.off : a.tile;
+    t.padded = sw_round_up(t.len, 16 * (size_t)owners);      // stripes are whole 16-byte vectors
+    return t;
+}
+
+// Zero [lo, hi) of a staging buffer (hi - lo < 16 * owners): the padding of a short last tile.
+__device__ __forceinline__ void sw_zero(char* base, size_t lo, size_t hi, int tid, int nth) {
+    for (size_t x = lo + tid; x < hi; x += nth) base[x] = 0;
+}
+
+template <typename T, bool HIER>
+__global__ void __launch_bounds__(SW_THREADS)
+allreduce_switch_kernel(GbTeam tm, GbSwitch sw, SwArgs a) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = SwVec<T>::N;
+    constexpr int DEPTH = HIER ? 4 : 3;
+    constexpr int U = 4;                                       // switch requests in flight per thread
+    const int b = (int)blockIdx.x, B = (int)gridDim.x;
+    const int mine = (a.ntiles - b + B - 1) / B;               // tiles b, b + B, ... (b < ntiles)
+    const int steps = mine + DEPTH - 1;
+    unsigned seq = gb_ld_volatile(sw.bseq + b);
+    char* stage = sw.uc + (size_t)b * DEPTH * a.tile;          // this block's buffers, local address
+    char* stage_mc = sw.mc + (size_t)b * DEPTH * a.tile;       // the same buffers on the whole group
+    const int owners = sw.owners;
+    const bool owner = sw.group_pos < owners;
+    const bool copier = (int)threadIdx.x < SW_HALF;
+    const int tid = (int)threadIdx.x - (copier ? 0 : SW_HALF);
+    GbLane L;
+    L.tid = (size_t)tid; L.nth = SW_HALF; L.ld = tm.ld_mode;
+    // the bridge slots of this block: [2 parities][islands] of one stripe each
+    const size_t slot = a.tile / (size_t)owners;
+    const size_t bridge0 = sw.off_bridge + (size_t)b * 2 * tm.n_islands * slot;
+
+    for (int i = 0; i < steps; ++i) {
+        if (copier) {
+            if (i < mine) {                                                   // A
+                const SwTile t = sw_tile(a, owners, b, B, i);
+                char* dst = stage + (size_t)(i % DEPTH) * a.tile;
+                gb_copy_bytes(L, dst, a.in + t.off, t.len, false);
+                sw_zero(dst, t.len, t.padded, tid, SW_HALF);
+            }
+            const int c = i - (DEPTH - 1);
+            if (c >= 0) {                                                     // C (D when HIER)
+                const SwTile t = sw_tile(a, owners, b, B, c);
+                gb_copy_bytes(L, a.out + t.off, stage + (size_t)(c % DEPTH) * a.tile, t.len, true);
+            }
+        } else if (owner) {
+            const int r = i - 1;
+            if (r >= 0 && r < mine) {                                         // B
+                const SwTile t = sw_tile(a, owners, b, B, r);
+                const size_t stripe = t.padded / (size_t)owners;
+                const size_t s0 = (size_t)(r % DEPTH) * a.tile + (size_t)sw.group_pos * stripe;
+                const size_t nvec = stripe >> 4;
+                for (size_t v0 = (size_t)tid; v0 < nvec; v0 += (size_t)U * SW_HALF) {
+                    SwVec<T> w[U];
+                    #pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const size_t v = v0 + (size_t)u * SW_HALF;
+                        if (v < nvec) w[u].u = SwitchSum<T>::load(stage_mc + s0 + (v << 4));
+                    }
+                    #pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const size_t v = v0 + (size_t)u * SW_HALF;
+                        if (v >= nvec) continue;
+                        if (!HIER) {
+                            if (a.divide > 0) {
+                                #pragma unroll
+                                for (int j = 0; j < V; ++j)
+                                    w[u].e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(w[u].e[j]), a.divide));
+                            }
+                            switch_store(stage_mc + s0 + (v << 4), w[u].u);
+                        } else {
+                            // the island's sum of this stripe goes to owner p of every island
+                            const size_t at = bridge0 + ((size_t)(r & 1) * tm.n_islands + tm.my_island) * slot
+                                              + (v << 4);
+                            for (int g = 0; g < tm.n_islands; ++g) {
+                                const int peer = tm.order[tm.island_off[g] + sw.group_pos];
+                                gb_st16(tm.ws[peer] + at, w[u].u);
+                            }
+                        }
+                    }
+                }
+            }
+            const int s = i - 2;
+            if (HIER && s >= 0 && s < mine) {                                 // C
+                const SwTile t = sw_tile(a, owners, b, B, s);
+                const size_t stripe = t.padded / (size_t)owners;
+                const size_t s0 = (size_t)(s % DEPTH) * a.tile + (size_t)sw.group_pos * stripe;
+                const size_t nvec = stripe >> 4;
+                const char* slots = tm.ws[tm.rank] + bridge0 + (size_t)(s & 1) * tm.n_islands * slot;
+                for (size_t v = (size_t)tid; v < nvec; v += SW_HALF) {
+                    A acc[V];
+                    for (int g = 0; g < tm.n_islands; ++g) {                   // island order
+                        SwVec<T> w;
+                        w.u = gb_ld16(slots + (size_t)g * slot + (v << 4), tm.ld_mode);
+                        #pragma unroll
+                        for (int j = 0; j < V; ++j)
+                            acc[j] = g == 0 ? gb_up<T>(w.e[j]) : acc[j] + gb_up<T>(w.e[j]);
+                    }
+                    SwVec<T> out;
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        out.e[j] = gb_down<T>(a.divide > 0 ? gb_divide<A>(acc[j], a.divide) : acc[j]);
+                    switch_store(stage_mc + s0 + (v << 4), out.u);
+                }
+            }
+        }
+        if (i + 1 < steps && !sw_block_sync(tm, sw, b, ++seq)) return;
+    }
+    if (threadIdx.x == 0) sw.bseq[b] = seq;
+}
+
+template <typename T>
+cudaError_t launch_switch(const GbTeam& tm, const GbSwitch& sw, const SwArgs& a, int grid,
+                          cudaStream_t stream) {
+    if (sw.hier) allreduce_switch_kernel<T, true><<<grid, SW_THREADS, 0, stream>>>(tm, sw, a);
+    else allreduce_switch_kernel<T, false><<<grid, SW_THREADS, 0, stream>>>(tm, sw, a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// Tile size and grid for `nbytes` with at most `max_blocks` blocks: every rank of the team
+// computes this from values they all share.  Returns 0, or -1 when the regions are too small
+// for even one tile per block.
+extern "C" int gb_switch_plan(const GbSwitch* sw, int n_islands, size_t nbytes, int max_blocks,
+                              GbSwitchPlan* plan) {
+    const int depth = sw->hier ? 4 : 3;
+    const size_t unit = 16 * (size_t)sw->owners * 8;           // stripes of whole 128-byte lines
+    if (max_blocks > GB_SWITCH_MAX_BLOCKS) max_blocks = GB_SWITCH_MAX_BLOCKS;
+    if (max_blocks < 1 || nbytes == 0) return -1;
+    const size_t floor_tile = (8192 + unit - 1) / unit * unit;
+    // as many blocks as have at least a floor-sized tile each
+    size_t want_blocks = (nbytes + floor_tile - 1) / floor_tile;
+    int grid = (int)(want_blocks < (size_t)max_blocks ? want_blocks : (size_t)max_blocks);
+    size_t cap = sw->bytes / ((size_t)grid * depth) / unit * unit;
+    if (sw->hier) {
+        const size_t per_block = sw->len_bridge / (size_t)grid / (2 * (size_t)n_islands);   // one slot
+        const size_t by_bridge = per_block * (size_t)sw->owners / unit * unit;
+        if (by_bridge < cap) cap = by_bridge;
+    }
+    if (cap > GB_SWITCH_MAX_TILE) cap = GB_SWITCH_MAX_TILE / unit * unit;
+    if (cap < unit) return -1;
+    size_t tile = ((nbytes + grid - 1) / grid + unit - 1) / unit * unit;
+    if (tile < floor_tile) tile = floor_tile;
+    if (tile > cap) tile = cap;
+    const size_t ntiles = (nbytes + tile - 1) / tile;
+    if (ntiles > 0x7fffffffu) return -1;
+    if ((size_t)grid > ntiles) grid = (int)ntiles;
+    plan->tile = tile;
+    plan->ntiles = (int)ntiles;
+    plan->grid = grid;
+    return 0;
+}
+
+// out = sum over the team of in (divided by `divide` when > 0).  dtype: 0 f32, 1 bf16, 2 f16;
+// n elements; in / out any alignment (16-byte aligned runs fastest).  `sw`: the group's
+// switch memory (the team's, or this rank's island's with sw->hier = 1).  Every rank passes the
+// same n, dtype, divide and max_blocks.  Returns a cudaError_t, or -2 for a type the switch
+// cannot add, -1 when the plan does not fit.
+extern "C" int gb_switch_all_reduce(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
+                                    size_t n, int dtype, int divide, int max_blocks,
+                                    cudaStream_t stream) {
+    const size_t esize = dtype == 0 ? 4 : 2;
+    if (dtype < 0 || dtype > 2) return -2;
+    GbSwitchPlan plan;
+    if (gb_switch_plan(sw, team->n_islands, n * esize, max_blocks, &plan) != 0) return -1;
+    SwArgs a;
+    a.in = static_cast<const char*>(in);
+    a.out = static_cast<char*>(out);
+    a.nbytes = n * esize;
+    a.tile = plan.tile;
+    a.ntiles = plan.ntiles;
+    a.divide = divide;
+    if (dtype == 0) return (int)launch_switch<float>(*team, *sw, a, plan.grid, stream);
+    if (dtype == 1) return (int)launch_switch<__nv_bfloat16>(*team, *sw, a, plan.grid, stream);
+    return (int)launch_switch<__half>(*team, *sw, a, plan.grid, stream);
+}
+
+extern "C" size_t gb_sizeof_switch() { return sizeof(GbSwitch); }

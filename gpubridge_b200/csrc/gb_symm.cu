@@ -27,6 +27,8 @@ int gb_symm_alloc(size_t bytes, void** ptr) {
     return (int)cudaDeviceSynchronize();
 }
 
+int gb_device_synchronize() { return (int)cudaDeviceSynchronize(); }
+
 int gb_symm_free(void* ptr) { return (int)cudaFree(ptr); }
 
 int gb_symm_export(void* ptr, unsigned char* handle64) {

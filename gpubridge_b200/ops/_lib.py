@@ -18,6 +18,7 @@ from gpubridge_b200.ops import _build
 
 MAX_RANKS = 16
 STATUS_WORDS = 8
+SWITCH_MAX_BLOCKS = 160
 
 DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.float64: 3,
           torch.int8: 4, torch.uint8: 5, torch.int32: 6, torch.int64: 7}
@@ -44,6 +45,19 @@ class GbArgs(ctypes.Structure):
                 ("off_a", ctypes.c_size_t), ("off_b", ctypes.c_size_t), ("off_c", ctypes.c_size_t),
                 ("len_a", ctypes.c_size_t), ("len_b", ctypes.c_size_t), ("len_c", ctypes.c_size_t),
                 ("residual", ctypes.c_void_p), ("sym", ctypes.c_void_p), ("mc", ctypes.c_void_p)]
+
+
+class GbSwitch(ctypes.Structure):
+    """One rank's view of the switch memory of its group (csrc/gb_switch.h)."""
+    _fields_ = [("uc", ctypes.c_void_p), ("mc", ctypes.c_void_p), ("bytes", ctypes.c_size_t),
+                ("off_flags", ctypes.c_size_t), ("off_bridge", ctypes.c_size_t),
+                ("len_bridge", ctypes.c_size_t), ("bseq", ctypes.c_void_p),
+                ("group_size", ctypes.c_int), ("group_pos", ctypes.c_int),
+                ("owners", ctypes.c_int), ("hier", ctypes.c_int)]
+
+
+class GbSwitchPlan(ctypes.Structure):
+    _fields_ = [("tile", ctypes.c_size_t), ("ntiles", ctypes.c_int), ("grid", ctypes.c_int)]
 
 
 class GbEngineConfig(ctypes.Structure):
@@ -90,7 +104,8 @@ def lib() -> ctypes.CDLL:
         if loaded.gb_sizeof_team() != ctypes.sizeof(GbTeam) or \
                 loaded.gb_sizeof_args() != ctypes.sizeof(GbArgs) or \
                 loaded.gb_sizeof_engine_config() != ctypes.sizeof(GbEngineConfig) or \
-                loaded.gb_sizeof_launch() != ctypes.sizeof(GbLaunch):
+                loaded.gb_sizeof_launch() != ctypes.sizeof(GbLaunch) or \
+                loaded.gb_sizeof_switch() != ctypes.sizeof(GbSwitch):
             raise RuntimeError("the native library's structures do not match ops/_lib.py; "
                                "rebuild with python -m gpubridge_b200.ops._build --force")
         _lib = loaded
@@ -102,7 +117,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_error_string.restype = ctypes.c_char_p
     L.gb_error_string.argtypes = [i]
     for name in ("gb_sizeof_team", "gb_sizeof_args", "gb_sizeof_ctrl", "gb_sizeof_engine_config",
-                 "gb_sizeof_launch"):
+                 "gb_sizeof_launch", "gb_sizeof_switch"):
         getattr(L, name).restype = sz
         getattr(L, name).argtypes = []
     L.gb_payload_bytes.restype = sz
@@ -148,6 +163,26 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_engine_all_gather.argtypes = [vp, vp, vp, sz, i, vp]
     L.gb_engine_broadcast.argtypes = [vp, vp, sz, i, i, vp]
     L.gb_engine_barrier.argtypes = [vp, vp]
+    ull = ctypes.c_ulonglong
+    L.gb_device_synchronize.argtypes = []
+    L.gb_mc_error_string.restype = ctypes.c_char_p
+    L.gb_mc_error_string.argtypes = [i]
+    L.gb_mc_supported.argtypes = [i, ctypes.POINTER(i)]
+    L.gb_mc_granularity.argtypes = [i, i, sz, ctypes.POINTER(sz)]
+    L.gb_mc_create.argtypes = [i, sz, ctypes.POINTER(ull)]
+    L.gb_mc_add_device.argtypes = [ull, i]
+    L.gb_mc_bind.argtypes = [ull, ull, sz]
+    L.gb_mc_unbind.argtypes = [ull, i, sz]
+    L.gb_vmm_create.argtypes = [i, sz, ctypes.POINTER(ull)]
+    L.gb_vmm_release.argtypes = [ull]
+    L.gb_vmm_export.argtypes = [ull, ctypes.POINTER(i)]
+    L.gb_vmm_import.argtypes = [i, ctypes.POINTER(ull)]
+    L.gb_vmm_map.argtypes = [ull, sz, sz, i, ctypes.POINTER(vp)]
+    L.gb_vmm_unmap.argtypes = [vp, sz]
+    L.gb_switch_plan.argtypes = [ctypes.POINTER(GbSwitch), i, sz, i, ctypes.POINTER(GbSwitchPlan)]
+    L.gb_switch_all_reduce.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), vp, vp, sz,
+                                       i, i, i, vp]
+    L.gb_engine_set_switch.argtypes = [vp, ctypes.POINTER(GbSwitch), ctypes.POINTER(GbSwitch), sz]
     L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
     L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]
 

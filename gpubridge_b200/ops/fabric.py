@@ -141,6 +141,13 @@ class Fabric:
         # the rest to the compute they overlap with; reduce-scatter also reduces locally.
         self.two_shot = os.environ.get("GPUBRIDGE_BRIDGE_TWO_SHOT", "0") == "1"
         self.nvls = None        # (tensor, handle, local pointer, multicast pointer, bytes per buffer)
+        # switch memory bound by the fabric itself (enable_switch): the team's group, this
+        # rank's island's group, and the structures the kernels take
+        self._switch_groups: list = []
+        self.sw_team = self.sw_island = None
+        self._bseq = 0
+        self.switch_min_bytes = _config.size_setting("GPUBRIDGE_SWITCH_MIN_BYTES", 64 << 10, multiple=1)
+        self.switch_flat = os.environ.get("GPUBRIDGE_SWITCH_FLAT", "0") == "1"
         self.nvls_reducers = int(os.environ.get("GPUBRIDGE_NVLS_REDUCERS", "48"))
         self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "32"))
         self.overlap_blocks = int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
@@ -188,7 +195,15 @@ class Fabric:
         self.oneshot_slot = max(ONESHOT_MAX, min(8 * ONESHOT_MAX, 16 * ONESHOT_MAX // max(1, self.world)))
         self.off_oneshot, self.len_oneshot = cursor, self.world * self.oneshot_slot
         cursor += 2 * self.len_oneshot
-        rest = budget - 2 * self.len_oneshot
+        # in-switch all-reduce: one flag row per block index, and - several islands - the slots
+        # the islands' sums of a stripe are exchanged through
+        self.off_swflags = cursor
+        cursor += _align_up(_lib.SWITCH_MAX_BLOCKS * _lib.MAX_RANKS * 4, 4096)
+        self.off_swbridge = cursor
+        self.len_swbridge = (_config.size_setting("GPUBRIDGE_SWITCH_BRIDGE_BYTES", 16 * MIB, multiple=4096)
+                             if self.n_islands > 1 else 0)
+        cursor += self.len_swbridge
+        rest = self.ws_bytes - cursor
         if rest < 16 * MIB:
             raise RuntimeError(f"{_config.FABRIC_BYTES_ENV}: the fabric workspace of "
                                f"{self.ws_bytes} bytes is too small for {self.world} ranks")
@@ -268,6 +283,86 @@ class Fabric:
         self.nvls = (buffer, handle, buffer.data_ptr(), multicast, third)
         return True
 
+    def enable_switch(self, nbytes: int | None = None, timeout: timedelta | None = None) -> bool:
+        """Bind memory of every rank to NVLink multicast objects made by the fabric itself - one
+        for the team and, with several islands, one per island - so that SUM / AVG all-reduces
+        of floats run through the switch (``csrc/gb_switch.cu``).  Collective over the team.
+        Returns False - on every rank alike - when the GPUs, the driver or the team cannot."""
+        from gpubridge_b200.ops import switch as _switch
+        if self._closed or self.sw_team is not None:
+            return self.sw_team is not None
+        lib, me, device = self.lib, self.rank, self.device.index
+        members = list(range(self.world))
+        nbytes = nbytes or _config.size_setting("GPUBRIDGE_SWITCH_BYTES", _switch.DEFAULT_BYTES,
+                                                multiple=4096)
+        key = f"{self._key}/switch"
+        torch.cuda.set_device(self.device)
+
+        def everyone(step: str, ok: bool) -> bool:
+            if self.world == 1:
+                return ok
+            return all(v == "1" for v in _switch.exchange_among(
+                self._store, f"{key}/{step}", me, members, "1" if ok else "0", timeout))
+
+        try:
+            if not everyone("supported", _switch.supported(lib, device)):
+                return False
+            groups = []
+            try:
+                team_group = _switch.build_group(lib, self._store, f"{key}/team", me, members, device,
+                                                 nbytes, timeout)
+                groups.append(team_group)
+                built = True
+            except _switch.SwitchUnavailable:
+                built = False
+            if not everyone("team", built):
+                for g in groups:
+                    g.release(lib)
+                return False
+            island_group = None
+            if self.n_islands > 1 and not self.switch_flat:
+                island = self.layout.islands[self.team.my_island]
+                mine = [self.layout.index(r) for r in island.ranks]
+                try:
+                    island_group = _switch.build_group(
+                        lib, self._store, f"{key}/island{self.team.my_island}", me, mine, device,
+                        nbytes, timeout)
+                except _switch.SwitchUnavailable:
+                    island_group = None
+                if not everyone("islands", island_group is not None):
+                    if island_group is not None:
+                        island_group.release(lib)
+                    island_group = None
+                else:
+                    groups.append(island_group)
+        except _switch.SwitchUnavailable:
+            return False
+        bseq = ctypes.c_void_p()
+        _lib.check(lib.gb_symm_alloc(4096, ctypes.byref(bseq)), "cudaMalloc (switch barrier numbers)")
+        self._bseq = bseq.value
+        self._switch_groups = groups
+        self.sw_team = _switch.describe(team_group, me, self.world, False, self.off_swflags, 0, 0,
+                                        self._bseq)
+        if island_group is not None:
+            self.sw_island = _switch.describe(island_group, me, self.k, True, self.off_swflags,
+                                              self.off_swbridge, self.len_swbridge, self._bseq)
+        if self._engine:
+            self._engine_switch()
+        return True
+
+    def _engine_switch(self) -> None:
+        self.lib.gb_engine_set_switch(
+            self._engine, ctypes.byref(self.sw_team) if self.sw_team is not None else None,
+            ctypes.byref(self.sw_island) if self.sw_island is not None else None,
+            self.switch_min_bytes)
+
+    def _switch_for(self, tensor: torch.Tensor, op: str, compression) -> "_lib.GbSwitch | None":
+        """The switch group an all-reduce of ``tensor`` takes, or None for the peer-memory kernels."""
+        if (self.sw_team is None or op != "sum" or compression is not None
+                or tensor.dtype not in NVLS_DTYPES or tensor.nbytes < self.switch_min_bytes):
+            return None
+        return self.sw_island if self.sw_island is not None else self.sw_team
+
     # -- the native engine -----------------------------------------------------------------------------
     def engine_config(self) -> "_lib.GbEngineConfig":
         c = _lib.GbEngineConfig()
@@ -293,6 +388,8 @@ class Fabric:
         if self._engine is None:
             self._engine = self.lib.gb_engine_create(ctypes.byref(self.team),
                                                      ctypes.byref(self.engine_config()))
+            if self._engine and self.sw_team is not None:
+                self._engine_switch()
         return self._engine or 0
 
     # -- health --------------------------------------------------------------------------------------
@@ -368,13 +465,22 @@ class Fabric:
         algo = self.algo
         oneshot = (compression is None and nbytes <= self.oneshot_slot
                    and ((mode == "auto" and algo in ("auto", "one-shot")) or algo == "one-shot"))
+        switch = self._switch_for(tensor, op, compression) if mode == "auto" and algo == "auto" else None
         current = self._begin()
         try:
             with torch.cuda.stream(self.comm_stream):
                 args = _lib.GbArgs()
                 args.inp, args.out, args.n = tensor.data_ptr(), out.data_ptr(), n
                 args.divide = int(divide or 0)
-                if oneshot:
+                if switch is not None:
+                    limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))
+                    code = self.lib.gb_switch_all_reduce(
+                        ctypes.byref(self.team), ctypes.byref(switch), args.inp, args.out, n,
+                        _lib.DTYPES[tensor.dtype], args.divide, limit,
+                        torch.cuda.current_stream(self.device).cuda_stream)
+                    _lib.check(code, "gb_switch_all_reduce")
+                    self.launches += 1
+                elif oneshot:
                     args.off_a, args.len_a = self.off_oneshot, self.len_oneshot
                     self._launch_reduce(0, tensor.dtype, op, 0, args, self._grid(nbytes, 32))
                 elif (self.nvls is not None and op == "sum" and compression is None
@@ -572,6 +678,7 @@ class Fabric:
         self.nvls = None
         short = timedelta(seconds=20)
         if self.world == 1:
+            self._release_switch()
             self.lib.gb_symm_free(self.ws[0])
             self.lib.gb_symm_free(self.ctrl)
             self.lib.gb_status_free(self.status)
@@ -584,10 +691,24 @@ class Fabric:
             _exchange(self._store, self._key + "/unmapped", self.rank, self.world, "1", short)
         except Exception:  # noqa: BLE001 - a peer is gone: leak instead of freeing in use
             return
+        self._release_switch()
         self.lib.gb_symm_free(self.ws[self.rank])
         self.lib.gb_symm_free(self.ctrl)
         self.lib.gb_status_free(self.status)
         self._residuals.clear()
+
+
+def _release_switch_of(fabric) -> None:
+    for group in reversed(fabric._switch_groups):
+        group.release(fabric.lib)
+    fabric._switch_groups = []
+    fabric.sw_team = fabric.sw_island = None
+    if fabric._bseq:
+        fabric.lib.gb_symm_free(fabric._bseq)
+        fabric._bseq = 0
+
+
+Fabric._release_switch = _release_switch_of
 
 
 def _exchange(store, key: str, rank_index: int, world: int, value: str,

@@ -498,17 +498,23 @@ def _assemble(store, name: str, layout: Layout, rank: int, peers, cfg: Config,
 
 
 def _maybe_nvls(topology: "Topology") -> None:
-    """``GPUBRIDGE_NVLS=1``: reduce large single-island sums inside the NVSwitch.  Needs the
-    team to be the whole job (the multicast binding goes through the default process group).
-    Off by default; tests that let a rank die run with it off."""
+    """In-switch reduction for the team's SUM / AVG all-reduces of floats.  ``GPUBRIDGE_NVLS``:
+    ``1`` (the default) binds switch memory through multicast objects the fabric makes itself -
+    the team's and, with several islands, one per island; ``0`` keeps every collective on the
+    peer-memory kernels (tests that let a rank leave: a rank that exits while bound to a
+    multicast object can fault its peers' links); ``torch`` takes the binding from torch's
+    symmetric memory instead (one island, the team must be the whole job)."""
     import os
     fabric = topology.fabric
-    if fabric is None or os.environ.get("GPUBRIDGE_NVLS", "0") != "1":
+    setting = os.environ.get("GPUBRIDGE_NVLS", "1").strip().lower()
+    if fabric is None or setting in ("0", "off", "false", "no"):
         return
-    import torch.distributed as dist
-    if not dist.is_initialized() or dist.get_world_size() != topology.world_size:
+    if setting == "torch":
+        import torch.distributed as dist
+        if dist.is_initialized() and dist.get_world_size() == topology.world_size:
+            fabric.enable_nvls(dist.group.WORLD)
         return
-    fabric.enable_nvls(dist.group.WORLD)
+    fabric.enable_switch(timeout=topology.timeout)
 
 
 def close_topology(topology: Topology) -> None:

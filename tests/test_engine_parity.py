@@ -29,6 +29,8 @@ def fake_fabric(sizes, ws_bytes=384 << 20, **over):
     f.ring, f.two_shot, f.nvls, f.algo = "phased", False, None, "auto"
     f.force_chunks = f.force_channels = None
     f._caps, f._closed, f._engine, f.launches = threading.local(), False, None, 0
+    f.sw_team = f.sw_island = None
+    f.switch_min_bytes, f.switch_flat = 64 << 10, False
     f.layout = types.SimpleNamespace(index=lambda r: r)
     for name, value in over.items():
         setattr(f, name, value)

@@ -155,7 +155,7 @@ def _through_the_switch(rank, topology):
 
 @needs_two
 def test_all_reduce_through_the_switch(tmp_path):
-    out = run_ranks(gpu_ranks(WORLD), _through_the_switch, tmp_path, env={"GPUBRIDGE_NVLS": "1"},
+    out = run_ranks(gpu_ranks(WORLD), _through_the_switch, tmp_path, env={"GPUBRIDGE_NVLS": "torch"},
                     timeout=240)
     if any(o == "unavailable" for o in out):
         pytest.skip("no NVLink multicast binding on this machine")
@@ -267,7 +267,7 @@ def _late_peer(rank, topology):
 
 @needs_two
 def test_a_peer_that_never_arrives_is_reported_not_hung(tmp_path):
-    env = {"GPUBRIDGE_WAIT_TIMEOUT_MS": "300", "NCCL_NVLS_ENABLE": "0"}
+    env = {"GPUBRIDGE_WAIT_TIMEOUT_MS": "300", "NCCL_NVLS_ENABLE": "0", "GPUBRIDGE_NVLS": "0"}
     out = run_ranks(gpu_ranks(2), _late_peer, tmp_path, env=env, timeout=120)
     assert out == ["raised", "skipped"]
 

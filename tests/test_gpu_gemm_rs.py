@@ -90,4 +90,4 @@ def _on_a_team(rank, topology):
 def test_on_a_team_of_two(tmp_path):
     from _harness import gpu_ranks, run_ranks
     run_ranks(gpu_ranks(2), _on_a_team, tmp_path, timeout=240,
-              env={"GPUBRIDGE_WAIT_TIMEOUT_MS": "10000", "NCCL_NVLS_ENABLE": "0"})
+              env={"GPUBRIDGE_WAIT_TIMEOUT_MS": "10000", "NCCL_NVLS_ENABLE": "0", "GPUBRIDGE_NVLS": "0"})

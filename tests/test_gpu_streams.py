@@ -4,8 +4,8 @@ Each test writes its input only after a stretch of queued GPU work (until then t
 holds a poison value) or reads its output straight after the call, so a missing
 stream-to-stream wait shows as wrong values.  ``MUTATIONS`` names, for every switch of
 ``gpubridge_b200._mutation``, the test that must fail when the switch is on;
-``python -m gpubridge_b200.kit.stream_mutations`` runs them both ways (the reference's
-``scripts/gpu/stream_mutations.py`` does the same for its own fixes).
+``python -m gpubridge_b200.kit.stream_mutations`` runs them both ways (the reference audits
+its own stream fixes the same way: scripts/gpu/stream_mutations.py).
 """
 import pytest
 import torch

@@ -1,0 +1,99 @@
+"""The in-switch all-reduce (csrc/gb_switch.cu) on hardware.
+
+One GPU: a team of one with its own multicast object - the switch "sums" one copy, so the
+result is the input (or the input divided), which exercises the tiling, the padding of odd
+sizes, the three-buffer pipeline, the per-block barrier numbers across many launches and the
+copy stages.  Two or more GPUs: exact sums on integer-valued data for one island (flat order)
+and for several (island sums in the switch, islands added over peer memory), identical bits
+on every rank, AVG divided once.  All against plain PyTorch sums in fp32."""
+import pytest
+import torch
+
+from _harness import expected_sum, gpu_ranks, rank_tensor, run_ranks
+
+pytestmark = pytest.mark.gpu
+
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+WORLD = 8 if NGPU >= 8 else 4 if NGPU >= 4 else 2
+SIZES = (1, 17, 4099, 65536 + 3, (1 << 20) + 5, (9 << 20) + 3)
+
+
+def test_team_of_one_round_trips_through_switch_memory():
+    from gpubridge_b200.ops import fabric as fabric_mod
+    dev = torch.device("cuda", 0)
+    fabric = fabric_mod.create_single(dev)
+    try:
+        if not fabric.enable_switch():
+            pytest.skip("this GPU or driver cannot bind multicast memory")
+        fabric.switch_min_bytes = 0                       # every size takes the switch path
+        before = fabric.launches
+        for dtype in (torch.float32, torch.bfloat16, torch.float16):
+            for n in SIZES + ((40 << 20) + 1,):
+                if dtype is not torch.float32 and n > (10 << 20):
+                    continue
+                x = rank_tensor(3, n, dtype).to(dev)
+                out = torch.full_like(x, 7)
+                fabric.all_reduce(x, out=out)
+                assert torch.equal(out, x), ("sum", dtype, n)
+                fabric.all_reduce(x, divide=4, out=out)
+                assert torch.equal(out.float(), (x.float() / 4).to(dtype).float()), ("avg", dtype, n)
+        # an unaligned view: the copy stages fall back to narrower accesses
+        base = rank_tensor(5, 100_003).to(dev)
+        view = base[1:]
+        keep = view.clone()
+        fabric.all_reduce(view)
+        assert torch.equal(view, keep)
+        torch.cuda.synchronize(dev)
+        fabric.check()
+        assert fabric.launches - before >= 2 * 3 * len(SIZES)
+    finally:
+        torch.cuda.synchronize(dev)
+        fabric.close()
+
+
+def _sums(rank, topology):
+    import gpubridge_b200 as gb
+    fabric = topology.fabric
+    if fabric is None or fabric.sw_team is None:
+        return "unavailable"
+    dev, world = topology.device, topology.world_size
+    fabric.switch_min_bytes = 0
+    if fabric._engine:
+        fabric._engine_switch()
+    before = fabric.launches
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for n in SIZES:
+            t = rank_tensor(rank, n, dtype).to(dev)
+            gb.all_reduce(t)
+            assert torch.equal(t.cpu(), expected_sum(world, n, dtype)), ("sum", dtype, n)
+    for n in (33, 100_003, (3 << 20) + 7):
+        t = rank_tensor(rank, n).to(dev)
+        gb.all_reduce(t, gb.ReduceOp.AVG)
+        assert torch.equal(t.cpu(), expected_sum(world, n) / world), ("avg", n)
+    # random values: every rank must hold the same bits, close to the fp64 sum
+    g = torch.Generator().manual_seed(99 + rank)
+    t = torch.randn((2 << 20) + 11, generator=g).to(dev)
+    gb.all_reduce(t)
+    exact = sum(torch.randn((2 << 20) + 11, generator=torch.Generator().manual_seed(99 + r)).double()
+                for r in range(world))
+    assert (t.cpu().double() - exact).abs().max() < 1e-4
+    rows = torch.empty(world * t.numel(), device=dev)
+    gb.all_gather_into_tensor(rows, t)
+    rows = rows.view(world, -1)
+    assert all(torch.equal(r, rows[0]) for r in rows), "ranks disagree on the bits"
+    assert fabric.launches > before
+    gb.barrier()
+    return "hier" if fabric.sw_island is not None else "flat"
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs at least two GPUs")
+@pytest.mark.parametrize("split", [{}, {"GPUBRIDGE_SPLIT_TEST": "half"},
+                                   {"GPUBRIDGE_SPLIT_TEST": "half", "GPUBRIDGE_SWITCH_FLAT": "1"}]
+                         + ([{"GPUBRIDGE_ISLANDS": "3,5"}, {"GPUBRIDGE_ISLANDS": "2,2,2,2"}] if WORLD == 8 else []),
+                         ids=lambda s: ",".join(s.values()) or "one-island")
+def test_sums_through_the_switch(tmp_path, split):
+    out = run_ranks(gpu_ranks(WORLD), _sums, tmp_path, env={"GPUBRIDGE_NVLS": "1", **split}, timeout=240)
+    if any(o == "unavailable" for o in out):
+        pytest.skip("no NVLink multicast binding on this machine")
+    want = "hier" if split and "GPUBRIDGE_SWITCH_FLAT" not in split else "flat"
+    assert set(out) == {want}, out
