@@ -117,8 +117,8 @@ class Worker:
         if self.lib.gb_tcp_wait(self.handle, array, len(ids), left) != 0:
             raise RuntimeError(f"multitcp: {self._error()}")
 
-    # The collectives themselves, run inside the library (csrc/gb_tcp.cpp): same tags and
-    # algorithms as tagged.py, without a Python round trip per chunk.
+    # The collectives themselves run inside the library (csrc/gb_tcp.cpp): chunked, pipelined,
+    # in the reduction order tagged.py documents, without a Python round trip per chunk.
     def all_reduce(self, ptr: int, count: int, dtype: int, op: int, chunk_elems: int, seq: int,
                    deadline: float) -> None:
         left = max(0.001, deadline - time.monotonic())
@@ -156,9 +156,7 @@ class MultiTcpTransport(TaggedBridge):
             addresses = wait_for_keys(store, [f"{key}/address/{m}" for m in members], deadline,
                                       "every bridge member's multitcp address")
             worker.connect(addresses, max(0.1, deadline - time.monotonic()))
-            transport = cls(worker, members, rank, timeout, chunk)
-            transport._handshake(deadline)
-            return transport
+            return cls(worker, members, rank, timeout, chunk)
         except BaseException:
             worker.close()
             raise

@@ -1,23 +1,41 @@
-"""Cross-island point-to-point for the torch backend (host-staged route).
+"""Point-to-point between islands through host memory: one event loop, a small wire pool.
 
-On a GPU box every send/recv, same island or not, is an NCCL p2p call overlapped with
-compute (:mod:`gpubridge_b200.torch_backend`).  This engine is the other route - CPU
-simulation and the cross-node fallback - with the reference's guarantees
-(src/gpubridge/p2p.py:57-439, docs/TORCH_BACKEND.md:401-445):
+On a B200 box every send / recv is an NCCL p2p call (:mod:`gpubridge_b200.torch_backend`); this
+module is the other route - CPU simulation, and ranks on different machines - where the bytes
+travel over the job's Gloo communicator.  What a user of the reference's engine relies on
+(src/gpubridge/p2p.py, docs/TORCH_BACKEND.md "Point-to-point") holds here too, by a different
+construction:
 
-* one lane (thread, stream, FIFO) per ``(peer, tag, direction)``, a sequence number per
-  lane, so messages of one lane never overtake each other and lanes never block each other;
-* a handshake on the store (``[nbytes, dtype, chunk]`` as JSON) *before* the payload is
-  posted, because Gloo aborts the process on a size mismatch; a mismatch raises instead;
-* every operation has a deadline that includes its time in the queue;
-* a failure is published once with ``compare_set("failure", ...)``; a watcher polls it
-  every 50 ms, only while operations are pending, and fails every pending handle;
-* completion is published by the lane itself, futures are resolved by one completion
-  thread, so a callback may wait on any handle;
-* teardown is bounded (200 ms) and never waits for a missing peer.
+==============================  ===============================================================
+guarantee                        how it is kept here
+==============================  ===============================================================
+messages of one (peer, tag,      every such *lane* is a FIFO of :class:`Transfer` state
+direction) never overtake        machines; only the head of a lane is ever advanced
+lanes do not block each other    one loop thread polls the heads of all lanes round-robin and
+                                 nothing in a step blocks: stores are probed, CUDA events
+                                 queried, and a posted Gloo request - which only completes
+                                 inside its own ``wait`` - is waited for by a pool of daemon
+                                 threads that grows with the requests in flight
+a size / dtype mismatch raises   before any payload is posted the two ends swap a descriptor
+instead of aborting in Gloo      through the store and compare it
+an operation's deadline covers   the deadline is fixed at ``submit`` and checked on every step
+its time in the queue            of the machine, queued or not
+one failure fails everything,    the first error is written once to the store's ``failure``
+on both ends                     key (``compare_set``); the loop probes that key every 50 ms
+                                 while work is pending and fails all local handles
+futures resolve off the engine   a second thread runs ``set_result`` / callbacks, so a callback
+                                 may itself wait on a handle
+teardown never waits for a peer  ``close`` fails what is pending, stops the loop and joins it
+                                 for at most 200 ms
+==============================  ===============================================================
+
+CPU tensors are sent from and received into their own memory (chunks are views).  CUDA
+tensors go through pinned slots, two per transfer, with copies on the engine's own streams
+ordered by events, so a copy overlaps the wire time of the other slot.
 """
 from __future__ import annotations
 
+import collections
 import contextlib
 import json
 import os
@@ -31,343 +49,418 @@ import torch.distributed as dist
 
 from gpubridge_b200.config import parse_size
 from gpubridge_b200.groups import Comm
-from gpubridge_b200.staging import make_staging
 from gpubridge_b200.work import Work
 
 CHUNK_BYTES_ENV = "GPUBRIDGE_P2P_CHUNK_BYTES"
-MATCH_POLL_FIRST = 50e-6
-MATCH_POLL_MAX = 0.002
-WATCH_INTERVAL = 0.05
+HEALTH_PERIOD = 0.05                 # seconds between probes of the shared failure key
+IDLE_NAP = (50e-6, 2e-3)             # the loop's back-off when no head made progress
+TEARDOWN_LIMIT = 0.2
 
 
 def chunk_bytes_setting() -> int:
-    """0: one message per tensor; >0: two staging slots of that size."""
-    raw = os.environ.get(CHUNK_BYTES_ENV, "").strip()
-    if not raw:
+    """``GPUBRIDGE_P2P_CHUNK_BYTES``: 0 (unset) sends a tensor as one message; otherwise the
+    size of a piece, a positive multiple of 8 bytes."""
+    text = os.environ.get(CHUNK_BYTES_ENV, "").strip()
+    if not text:
         return 0
-    size = parse_size(raw)
-    if size < 8 or size % 8:
+    size = parse_size(text)
+    if size <= 0 or size % 8:
         raise ValueError(f"{CHUNK_BYTES_ENV} must be a positive multiple of 8 bytes")
     return size
 
 
 class TorchWork(dist.Work):
-    """A ``torch.distributed.Work`` that delegates to a library :class:`Work`, keeping the
-    Python exception and the optional host timeout of ``wait``."""
+    """Adapter: what ``torch.distributed`` hands its callers, backed by a library handle (so
+    ``wait`` raises the Python exception and honours a host timeout)."""
 
-    def __init__(self, work: Work, source: int) -> None:
+    def __init__(self, inner: Work, source_rank: int) -> None:
         super().__init__()
-        self.work, self.source = work, source
+        self._inner, self._source = inner, source_rank
 
     def wait(self, timeout=None) -> bool:
-        return self.work.wait(timeout)
-
-    def is_completed(self) -> bool:
-        return self.work.is_completed()
-
-    def is_success(self) -> bool:
-        return self.is_completed() and self.work.exception() is None
-
-    def get_future(self):
-        return self.work.get_future()
-
-    def exception(self):
-        return self.work.exception()
+        return self._inner.wait(timeout)
 
     def synchronize(self) -> None:
-        self.wait()
+        self._inner.wait()
+
+    def is_completed(self) -> bool:
+        return self._inner.is_completed()
+
+    def is_success(self) -> bool:
+        return self._inner.is_completed() and self._inner.exception() is None
+
+    def exception(self):
+        return self._inner.exception()
+
+    def get_future(self):
+        return self._inner.get_future()
 
     def _source_rank(self) -> int:
-        return self.source
+        return self._source
 
 
-class _Handle(Work):
-    """Completion is published by the lane; the future is resolved by the completer."""
+class GlooLink:
+    """Byte messages over a Gloo communicator that spans every rank of the job."""
+
+    def __init__(self, group: Comm) -> None:
+        self.group = group
+
+    def post(self, buffer: torch.Tensor, peer: int, tag: int, sending: bool):
+        return self.group.send(buffer, peer, tag) if sending else self.group.recv(buffer, peer, tag)
+
+    def close(self) -> None:
+        pass
+
+
+class _Ticket(Work):
+    """A handle whose completion and whose future are settled by different threads."""
 
     def _finish(self, error):
         self._error = error
         self._done.set()
 
 
-class GlooLink:
-    """Raw bytes over an existing Gloo communicator of every member."""
+class _Piece:
+    """One chunk of a transfer in flight: its wire request and, for CUDA, its slot and copy."""
+    __slots__ = ("view", "host", "request", "copied", "arrived", "error")
 
-    def __init__(self, group: Comm) -> None:
-        self.group = group
+    def __init__(self, view, host):
+        self.view, self.host, self.request, self.copied = view, host, None, None
+        self.arrived, self.error = False, None
 
-    def post(self, tensor: torch.Tensor, peer: int, tag: int, sending: bool):
-        return (self.group.send if sending else self.group.recv)(tensor, peer, tag)
+    def wire_done(self) -> bool:
+        if self.error is not None:
+            raise self.error
+        return self.arrived
 
-    def close(self) -> None:
-        pass
+
+class _WirePool:
+    """Daemon threads that sit in ``request.wait()`` so the loop never has to.  A Gloo send or
+    receive completes once the peer has posted the other half, which the peer does from its
+    own loop, never from its pool - so a full pool delays, but cannot deadlock."""
+
+    def __init__(self, most: int = 16) -> None:
+        self.most, self.idle, self.threads = most, 0, 0
+        self.jobs: queue.SimpleQueue = queue.SimpleQueue()
+        self.lock = threading.Lock()
+
+    def watch(self, piece: _Piece, deadline: float) -> None:
+        with self.lock:
+            if self.idle == 0 and self.threads < self.most:
+                self.threads += 1
+                threading.Thread(target=self._serve, name="gpubridge-p2p-wire", daemon=True).start()
+        self.jobs.put((piece, deadline))
+
+    def _serve(self) -> None:
+        while True:
+            with self.lock:
+                self.idle += 1
+            job = self.jobs.get()
+            with self.lock:
+                self.idle -= 1
+            if job is None:
+                return
+            piece, deadline = job
+            try:
+                piece.request.wait(timedelta(seconds=max(0.001, deadline - time.monotonic())))
+                piece.arrived = True
+            except BaseException as failure:  # noqa: BLE001 - handed to the loop
+                piece.error = failure
+
+    def stop(self) -> None:
+        with self.lock:
+            count = self.threads
+        for _ in range(count):
+            self.jobs.put(None)
+
+
+class Transfer:
+    """A send or a receive as a state machine: ``queued`` (waiting for the producer's CUDA
+    event) -> ``offered`` (descriptor published, waiting for the peer's) -> ``moving`` (pieces
+    on the wire, at most two) -> finished.  :meth:`step` never blocks and returns True when it
+    changed something."""
+
+    def __init__(self, engine: "Engine", ticket: _Ticket, tensor: torch.Tensor, peer: int, tag: int,
+                 sending: bool, number: int, deadline: float, ready) -> None:
+        self.engine, self.ticket, self.tensor = engine, ticket, tensor
+        self.peer, self.tag, self.sending, self.number = peer, tag, sending, number
+        self.deadline, self.ready = deadline, ready
+        self.state = "queued"
+        self.bytes = tensor.reshape(-1).view(torch.uint8)
+        size = engine.chunk_bytes or max(1, self.bytes.numel())
+        self.views = list(self.bytes.split(size)) if self.bytes.numel() else [self.bytes]
+        self.next_piece = 0
+        self.flying: collections.deque[_Piece] = collections.deque()
+        self.slots: list[torch.Tensor] = []
+        self.last_copy = None
+        where = (engine.rank, peer) if sending else (peer, engine.rank)
+        self.key = f"{where[0]}/{where[1]}/{tag}/{number}"
+        self.what = f"point-to-point {'send' if sending else 'recv'} with rank {peer}, tag {tag}"
+
+    # -- the machine ---------------------------------------------------------------------------------
+    def step(self) -> bool:
+        if time.monotonic() >= self.deadline:
+            waited = "in queue" if self.state == "queued" else "waiting for its peer"
+            raise TimeoutError(f"{self.what} timed out {waited}")
+        return getattr(self, "_" + self.state)()
+
+    def _queued(self) -> bool:
+        if self.ready is not None and not self.ready.query():
+            return False
+        mine = "send" if self.sending else "recv"
+        self.engine.store.set(f"{self.key}/{mine}", self._descriptor())
+        self.state = "offered"
+        return True
+
+    def _descriptor(self) -> str:
+        return json.dumps([self.bytes.numel(), str(self.tensor.dtype), self.engine.chunk_bytes])
+
+    def _offered(self) -> bool:
+        theirs = f"{self.key}/{'recv' if self.sending else 'send'}"
+        store = self.engine.store
+        if not store.check([theirs]):
+            return False
+        other = store.get(theirs).decode()
+        store.delete_key(theirs)
+        if other != self._descriptor():
+            raise ValueError(f"point-to-point payload mismatch with rank {self.peer}, tag {self.tag}: "
+                             f"local {self._descriptor()}, peer {other}")
+        if self.tensor.device.type == "cuda":
+            size = max(v.numel() for v in self.views)
+            self.slots = [torch.empty(max(1, size), dtype=torch.uint8, pin_memory=True)
+                          for _ in range(min(2, len(self.views)))]
+            self.tensor.record_stream(self.engine.copy_stream(self.tensor.device))
+        self.state = "moving"
+        return True
+
+    def _moving(self) -> bool:
+        moved = False
+        on_gpu = bool(self.slots)
+        # retire the oldest piece (pieces of one transfer complete in order on one Gloo tag)
+        while self.flying:
+            piece = self.flying[0]
+            if self.sending:
+                if piece.request is None:                       # still being copied to its slot
+                    if not piece.copied.query():
+                        break
+                    self._post(piece)
+                    moved = True
+                if not piece.wire_done():                       # raises what the wire raised
+                    break
+            else:
+                if piece.copied is None:
+                    if not piece.wire_done():
+                        break
+                    if on_gpu:
+                        piece.copied = self._copy(piece.view, piece.host)
+                        self.last_copy = piece.copied
+                        moved = True
+                if on_gpu and not piece.copied.query():
+                    break
+            self.flying.popleft()
+            moved = True
+        # launch pieces while a slot (GPU) or the two-in-flight budget (CPU) allows
+        while self.next_piece < len(self.views) and len(self.flying) < 2:
+            view = self.views[self.next_piece]
+            host = self.slots[self.next_piece % 2][:view.numel()] if on_gpu else view
+            piece = _Piece(view, host)
+            if self.sending:
+                if on_gpu:
+                    piece.copied = self._copy(host, view)
+                else:
+                    self._post(piece)
+            else:
+                self._post(piece)
+            self.flying.append(piece)
+            self.next_piece += 1
+            moved = True
+        if self.next_piece == len(self.views) and not self.flying:
+            self.state = "finished"
+        return moved
+
+    def _post(self, piece: _Piece) -> None:
+        piece.request = self.engine.link.post(piece.host, self.peer, self.tag, self.sending)
+        self.engine.wire.watch(piece, self.deadline)
+
+    def _copy(self, dst: torch.Tensor, src: torch.Tensor):
+        stream = self.engine.copy_stream(self.tensor.device)
+        with torch.cuda.stream(stream):
+            dst.copy_(src, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(stream)
+        return done
+
+    def _finished(self) -> bool:
+        return False
 
 
 class Engine:
-    def __init__(self, link, device: torch.device, rank: int, store,
-                 timeout: timedelta | None, *, pinned: bool = False, chunk_bytes: int = 0):
+    """All cross-island point-to-point traffic of one process group."""
+
+    def __init__(self, link, device: torch.device, rank: int, store, timeout: timedelta | None, *,
+                 pinned: bool = False, chunk_bytes: int = 0) -> None:
         self.link, self.device, self.rank, self.store = link, device, rank, store
-        self.timeout = (timeout or timedelta(minutes=30)).total_seconds()
-        self.pinned, self.chunk_bytes = pinned, chunk_bytes
-        self._lock = threading.RLock()
-        self._lanes: dict[tuple[int, int, bool], _Lane] = {}
-        self._next: dict[tuple[int, int, bool], int] = {}
-        self._pending: dict[_Handle, None] = {}
-        self._closed = False
-        self._failed: BaseException | None = None
-        self._resolve_queue: queue.SimpleQueue = queue.SimpleQueue()
+        self.limit = (timeout or timedelta(minutes=30)).total_seconds()
+        self.chunk_bytes = chunk_bytes
+        self.pinned = pinned                       # CUDA tensors always use pinned slots here
+        self._guard = threading.Lock()
+        self._lanes: dict[tuple[int, int, bool], collections.deque[Transfer]] = {}
+        self._numbers: collections.Counter = collections.Counter()
+        self._broken: BaseException | None = None
+        self._closing = False
+        self._work_arrived = threading.Event()
+        self._settled: queue.SimpleQueue = queue.SimpleQueue()
+        self.wire = _WirePool()
         self._streams: dict[torch.device, torch.cuda.Stream] = {}
-        self._stop, self._wake = threading.Event(), threading.Event()
-        for target, name in ((self._resolver, "gpubridge-p2p-completion"),
-                             (self._watch, "gpubridge-p2p-health")):
-            threading.Thread(target=target, name=name, daemon=True).start()
+        self._callback_streams: dict[torch.device, torch.cuda.Stream] = {}
+        self._loop_thread = threading.Thread(target=self._loop, name="gpubridge-p2p-loop", daemon=True)
+        self._callback_thread = threading.Thread(target=self._callbacks, name="gpubridge-p2p-futures",
+                                                 daemon=True)
+        self._loop_thread.start()
+        self._callback_thread.start()
 
-    # -- background threads --------------------------------------------------------------------
-    def _resolver(self) -> None:
-        while True:
-            handle = self._resolve_queue.get()
-            if handle is None:
-                return
-            scope = contextlib.nullcontext()
-            if handle._event is not None:
-                stream = self._streams.setdefault(handle._device,
-                                                  torch.cuda.Stream(handle._device))
-                stream.wait_event(handle._event)
-                scope = torch.cuda.stream(stream)
-            with scope:
-                if handle._error is None:
-                    handle._future.set_result(handle._result)
-                else:
-                    handle._future.set_exception(handle._error)
-            del handle
+    def copy_stream(self, device: torch.device) -> torch.cuda.Stream:
+        stream = self._streams.get(device)
+        if stream is None:
+            stream = self._streams[device] = torch.cuda.Stream(device)
+        return stream
 
-    def _watch(self) -> None:
-        while not self._stop.is_set():
-            with self._lock:
-                if self._closed:
-                    return
-                idle = not self._pending
-                if idle:
-                    self._wake.clear()
-            if idle:
-                self._wake.wait()
-                continue
-            if self._stop.wait(WATCH_INTERVAL - time.monotonic() % WATCH_INTERVAL):
-                return
-            try:
-                self.check()
-            except BaseException as exc:  # noqa: BLE001 - store loss fails pending handles too
-                self._fail(exc, publish=False)
-                return
-
-    # -- state -----------------------------------------------------------------------------------
+    # -- public ----------------------------------------------------------------------------------------
     def check(self) -> None:
-        with self._lock:
-            if self._closed:
+        """Raise if the group was destroyed, failed here, or failed on the other end."""
+        with self._guard:
+            if self._closing:
                 raise RuntimeError("gpubridge point-to-point group was destroyed")
-            if self._failed is not None:
-                raise RuntimeError(f"gpubridge point-to-point group failed: {self._failed}")
+            if self._broken is not None:
+                raise RuntimeError(f"gpubridge point-to-point group failed: {self._broken}")
         if self.store.check(["failure"]):
-            error = RuntimeError(self.store.get("failure").decode())
-            self._fail(error, publish=False)
-            raise error
+            remote = RuntimeError(self.store.get("failure").decode())
+            self._break(remote, announce=False)
+            raise remote
 
-    def _settle(self, handles, error) -> None:
-        for handle in handles:
-            handle._finish(error)
-            self._resolve_queue.put(handle)
-
-    def _done(self, handle, error=None) -> None:
-        with self._lock:
-            if handle not in self._pending:
-                return
-            del self._pending[handle]
-        self._settle([handle], error)
-
-    def _fail(self, error: BaseException, *, publish: bool = True) -> None:
-        with self._lock:
-            if self._failed is not None or self._closed:
-                return
-            self._failed = error
-            if publish:
-                with contextlib.suppress(Exception):
-                    self.store.compare_set("failure", "", f"rank {self.rank}: {error}")
-            pending = list(self._pending)
-            self._pending.clear()
-        self._settle(pending, error)
-
-    # -- API -------------------------------------------------------------------------------------
     def submit(self, tensor: torch.Tensor, peer: int, tag: int, sending: bool) -> Work:
         self.check()
         ready = None
         if tensor.device.type == "cuda":
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(tensor.device))
-        handle = _Handle("send" if sending else "recv", tensor.device, [tensor])
-        with self._lock:
-            self.check()
-            key = (peer, tag, sending)
-            seq = self._next.get(key, 0)
-            self._next[key] = seq + 1
-            lane = self._lanes.get(key)
-            if lane is None:
-                lane = self._lanes[key] = _Lane(self, peer, tag, sending)
-            self._pending[handle] = None
-            lane.queue.put((handle, tensor, ready, time.monotonic() + self.timeout, seq))
-        self._wake.set()
-        return handle
+        ticket = _Ticket("send" if sending else "recv", tensor.device, [tensor])
+        lane_key = (peer, tag, sending)
+        with self._guard:
+            if self._closing or self._broken is not None:
+                raise RuntimeError("gpubridge point-to-point group is not usable any more")
+            number = self._numbers[lane_key]
+            self._numbers[lane_key] += 1
+            transfer = Transfer(self, ticket, tensor, peer, tag, sending, number,
+                                time.monotonic() + self.limit, ready)
+            self._lanes.setdefault(lane_key, collections.deque()).append(transfer)
+        self._work_arrived.set()
+        return ticket
 
-    def match(self, tensor, peer, tag, seq, sending, deadline) -> None:
-        """Agree with the peer on size, dtype and chunking before any payload moves."""
-        self.check()
-        if time.monotonic() >= deadline:
-            raise TimeoutError(f"point-to-point operation with rank {peer} timed out in queue")
-        src, dst = (self.rank, peer) if sending else (peer, self.rank)
-        mine, theirs = ("send", "recv") if sending else ("recv", "send")
-        base = f"{src}/{dst}/{tag}/{seq}"
-        descriptor = json.dumps([tensor.numel() * tensor.element_size(), str(tensor.dtype),
-                                 self.chunk_bytes])
-        self.store.set(f"{base}/{mine}", descriptor)
-        key = f"{base}/{theirs}"
-        late = f"point-to-point {mine} with rank {peer}, tag {tag} timed out"
-        pause = MATCH_POLL_FIRST
-        while not self.store.check([key]):
-            self.check()
-            left = deadline - time.monotonic()
-            if left <= 0:
-                raise TimeoutError(late)
-            time.sleep(min(pause, left))
-            pause = min(2 * pause, MATCH_POLL_MAX)
-        other = self.store.get(key).decode()
-        self.store.delete_key(key)
-        if time.monotonic() >= deadline:
-            raise TimeoutError(late)
-        if other != descriptor:
-            raise ValueError(f"point-to-point payload mismatch with rank {peer}, tag {tag}: "
-                             f"local {descriptor}, peer {other}")
-
-    def close(self, timeout: float = 0.2) -> None:
-        with self._lock:
-            if self._closed:
+    def close(self, timeout: float = TEARDOWN_LIMIT) -> None:
+        with self._guard:
+            if self._closing:
                 return
-            self._closed = True
-            self._stop.set()
-            self._wake.set()
-            pending = list(self._pending)
-            self._pending.clear()
-            lanes = list(self._lanes.values())
+            self._closing = True
+            orphans = [t for lane in self._lanes.values() for t in lane]
             self._lanes.clear()
-            for lane in lanes:
-                lane.queue.put(None)
-        self._settle(pending, RuntimeError("point-to-point group was destroyed"))
-        self._resolve_queue.put(None)
-        end = time.monotonic() + timeout
-        for lane in lanes:
-            lane.thread.join(max(0.0, end - time.monotonic()))
+        self._settle(orphans, RuntimeError("point-to-point group was destroyed"))
+        self._work_arrived.set()
+        self._settled.put(None)
+        self.wire.stop()
+        self._loop_thread.join(timeout)
         self.link.close()
 
+    # -- the loop --------------------------------------------------------------------------------------
+    def _heads(self) -> list[Transfer]:
+        with self._guard:
+            return [lane[0] for lane in self._lanes.values() if lane]
 
-class _Lane:
-    def __init__(self, engine: Engine, peer: int, tag: int, sending: bool) -> None:
-        self.engine, self.peer, self.tag, self.sending = engine, peer, tag, sending
-        self.queue: queue.SimpleQueue = queue.SimpleQueue()
-        self.stream: torch.cuda.Stream | None = None
-        self.thread = threading.Thread(target=self._loop, name="gpubridge-p2p", daemon=True)
-        self.thread.start()
+    def _retire(self, transfer: Transfer) -> None:
+        key = (transfer.peer, transfer.tag, transfer.sending)
+        with self._guard:
+            lane = self._lanes.get(key)
+            if not lane or lane[0] is not transfer:
+                return                                          # already failed or closed
+            lane.popleft()
+            if not lane:
+                del self._lanes[key]
+        if transfer.last_copy is not None:
+            transfer.ticket._event = transfer.last_copy          # wait() orders the caller's stream
+        self._settle([transfer], None)
 
     def _loop(self) -> None:
+        nap, next_probe = IDLE_NAP[0], 0.0
         while True:
-            try:
-                item = self.queue.get_nowait()
-            except queue.Empty:
-                with self.engine._lock:           # the lock submit() queues under
-                    if self.queue.empty():
-                        key = (self.peer, self.tag, self.sending)
-                        if self.engine._lanes.get(key) is self:
-                            del self.engine._lanes[key]
-                        return
-                continue
-            if item is None:
+            heads = self._heads()
+            if self._closing:
                 return
-            self._one(*item)
-            del item
-
-    def _one(self, handle, tensor, ready, deadline, seq) -> None:
-        engine = self.engine
-        try:
-            engine.check()
-            stream = None
-            if tensor.device.type == "cuda":
-                torch.cuda.set_device(tensor.device)
-                if self.stream is None or self.stream.device != tensor.device:
-                    self.stream = torch.cuda.Stream(tensor.device)
-                stream = self.stream
-                stream.wait_event(ready)
-                tensor.record_stream(stream)
-            scope = torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext()
-            with scope:
-                engine.match(tensor, self.peer, self.tag, seq, self.sending, deadline)
-                self._move(tensor, deadline)
-                if stream is not None:
-                    handle._event = torch.cuda.Event()
-                    handle._event.record(stream)
-            engine._done(handle)
-        except BaseException as exc:  # noqa: BLE001 - delivered through every pending handle
-            engine._fail(exc)
-
-    def _left(self, deadline: float) -> timedelta:
-        return timedelta(seconds=max(0.001, deadline - time.monotonic()))
-
-    def _move(self, tensor: torch.Tensor, deadline: float) -> None:
-        flat = tensor.reshape(-1).view(torch.uint8)     # bytes: any dense dtype travels
-        engine = self.engine
-        if engine.pinned or engine.chunk_bytes:
-            self._chunked(flat, deadline)
-            return
-        host = flat.cpu() if self.sending else torch.empty(flat.numel(), dtype=torch.uint8)
-        engine.link.post(host, self.peer, self.tag, self.sending).wait(self._left(deadline))
-        if not self.sending:
-            flat.copy_(host)
-
-    def _chunked(self, flat: torch.Tensor, deadline: float) -> None:
-        """Two staging slots: a copy overlaps the wire transfer of the other slot."""
-        engine = self.engine
-        size = engine.chunk_bytes or max(8, flat.numel())
-        chunks = list(flat.split(size)) if flat.numel() else [flat]
-        staging = make_staging(flat.device, size, min(2, len(chunks)))
-        staging.begin(flat)
-        try:
-            if self.sending:
-                staged: dict[int, tuple] = {}
-
-                def stage(i: int) -> None:
-                    host = staging.slot(i % 2, chunks[i])
-                    staged[i] = (host, staging.to_host(host, chunks[i], None))
-
-                for i in range(min(2, len(chunks))):
-                    stage(i)
-                for i in range(len(chunks)):
-                    host, copied = staged.pop(i)
-                    staging.wait_host(copied)
-                    engine.link.post(host, self.peer, self.tag, True).wait(self._left(deadline))
-                    if i + 2 < len(chunks):
-                        stage(i + 2)
+            if not heads:
+                self._work_arrived.clear()
+                if not self._heads() and not self._closing:
+                    self._work_arrived.wait()
+                nap = IDLE_NAP[0]
+                continue
+            progressed = False
+            try:
+                now = time.monotonic()
+                if now >= next_probe:
+                    next_probe = now + HEALTH_PERIOD
+                    if self.store.check(["failure"]):
+                        raise _Remote(self.store.get("failure").decode())
+                for transfer in heads:
+                    if transfer.step():
+                        progressed = True
+                    if transfer.state == "finished":
+                        self._retire(transfer)
+            except _Remote as told:
+                self._break(RuntimeError(str(told)), announce=False)
+                return
+            except BaseException as failure:  # noqa: BLE001 - every pending handle hears of it
+                self._break(failure, announce=True)
+                return
+            if progressed:
+                nap = IDLE_NAP[0]
             else:
-                posted: dict[int, tuple] = {}
-                back = [None, None]
+                time.sleep(nap)
+                nap = min(2 * nap, IDLE_NAP[1])
 
-                def post(i: int) -> None:
-                    staging.wait_host(back[i % 2])
-                    host = staging.slot(i % 2, chunks[i])
-                    posted[i] = (host, engine.link.post(host, self.peer, self.tag, False))
+    def _break(self, error: BaseException, *, announce: bool) -> None:
+        with self._guard:
+            if self._broken is not None or self._closing:
+                return
+            self._broken = error
+            victims = [t for lane in self._lanes.values() for t in lane]
+            self._lanes.clear()
+        if announce:
+            with contextlib.suppress(Exception):
+                self.store.compare_set("failure", "", f"rank {self.rank}: {error}")
+        self._settle(victims, error)
 
-                for i in range(min(2, len(chunks))):
-                    post(i)
-                for i, chunk in enumerate(chunks):
-                    host, request = posted.pop(i)
-                    request.wait(self._left(deadline))
-                    back[i % 2] = staging.to_device(chunk, host)
-                    if i + 2 < len(chunks):
-                        post(i + 2)
-                staging.end(back[(len(chunks) - 1) % 2])
-        finally:
-            staging.close()
+    def _settle(self, transfers, error) -> None:
+        for transfer in transfers:
+            transfer.ticket._finish(error)
+            self._settled.put(transfer.ticket)
+
+    # -- futures ---------------------------------------------------------------------------------------
+    def _callbacks(self) -> None:
+        while True:
+            ticket = self._settled.get()
+            if ticket is None:
+                return
+            scope = contextlib.nullcontext()
+            if ticket._event is not None:
+                stream = self._callback_streams.get(ticket._device)
+                if stream is None:
+                    stream = self._callback_streams[ticket._device] = torch.cuda.Stream(ticket._device)
+                stream.wait_event(ticket._event)
+                scope = torch.cuda.stream(stream)
+            with scope:
+                if ticket._error is None:
+                    ticket._future.set_result(ticket._result)
+                else:
+                    ticket._future.set_exception(ticket._error)
+
+
+class _Remote(Exception):
+    """The other end published a failure."""

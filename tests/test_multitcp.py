@@ -64,22 +64,39 @@ def test_worker_reports_a_vanished_peer():
     a.close()
 
 
-def _native_equals_python(members: int):
-    """The collectives inside the library against the same algorithms in Python, thread per
-    member, every dtype and op, sizes around the chunk boundaries: bit for bit."""
+def _expected(inputs, op):
+    """What the native collectives must produce, bit for bit, rebuilt from the two rules
+    gpubridge_b200.tagged documents: two members fold the peer's values into their own; a ring
+    folds segment j starting at member j and walking upward."""
+    from gpubridge_b200.tagged import ring_order, segments
+    fold = {"sum": torch.add, "max": torch.maximum, "min": torch.minimum}[op]
+    members = len(inputs)
+    if members == 2:
+        return [fold(inputs[0], inputs[1]), fold(inputs[1], inputs[0])]
+    out = torch.empty_like(inputs[0])
+    for j, (start, length) in enumerate(segments(out.numel(), members)):
+        order = ring_order(j, members)
+        acc = inputs[order[0]][start:start + length].clone()
+        for member in order[1:]:
+            acc = fold(inputs[member][start:start + length], acc)      # own value first, as the worker folds
+        out[start:start + length] = acc
+    return [out] * members
+
+
+def _native_matches_the_documented_order(members: int):
+    """The collectives inside the library, a thread per member, every dtype and op, sizes
+    around the chunk boundaries, against :func:`_expected`."""
     import threading
-    import time
     from datetime import timedelta
     from gpubridge_b200.multitcp import MultiTcpTransport, Worker
 
-    def link():
-        workers = [Worker(i, members, 2, "127.0.0.1") for i in range(members)]
-        addresses = [w.address() for w in workers]
-        threads = [threading.Thread(target=w.connect, args=(addresses, 20.0)) for w in workers]
-        [t.start() for t in threads]
-        [t.join() for t in threads]
-        return [MultiTcpTransport(w, list(range(members)), i, timedelta(seconds=30), 4096)
-                for i, w in enumerate(workers)]
+    workers = [Worker(i, members, 2, "127.0.0.1") for i in range(members)]
+    addresses = [w.address() for w in workers]
+    joiners = [threading.Thread(target=w.connect, args=(addresses, 20.0)) for w in workers]
+    [t.start() for t in joiners]
+    [t.join() for t in joiners]
+    transports = [MultiTcpTransport(w, list(range(members)), i, timedelta(seconds=30), 4096)
+                  for i, w in enumerate(workers)]
 
     def values(rank, n, dtype):
         g = torch.Generator().manual_seed(100 * rank + n)
@@ -90,57 +107,52 @@ def _native_equals_python(members: int):
             return t
         return torch.randint(-100, 100, (n,), generator=g).to(dtype)
 
-    def run(transports, fn):
-        errors = []
+    cases = [(dtype, n, op)
+             for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.float64,
+                           torch.int8, torch.uint8, torch.int32, torch.int64)
+             for n in (1, 2, 1023, 1024, 1025, 5000) for op in ("sum", "max", "min")]
+    got, errors = {}, []
 
-        def one(tr, rank):
-            try:
-                fn(tr, rank)
-            except BaseException as exc:  # noqa: BLE001
-                errors.append(exc)
-        threads = [threading.Thread(target=one, args=(tr, r)) for r, tr in enumerate(transports)]
+    def member(rank):
+        try:
+            transports[rank].prove(__import__("time").monotonic() + 20)
+            for dtype, n, op in cases:
+                t = values(rank, n, dtype)
+                transports[rank].all_reduce(t, op)
+                got[(rank, dtype, n, op)] = t
+            t = values(rank, 3000, torch.float32)
+            transports[rank].broadcast(t, members - 1)
+            got[(rank, "bcast")] = t
+        except BaseException as exc:  # noqa: BLE001
+            errors.append(exc)
+
+    threads = [threading.Thread(target=member, args=(r,)) for r in range(members)]
+    try:
         [t.start() for t in threads]
         [t.join() for t in threads]
-        assert not errors, errors
-
-    import os
-    results = {}
-    for native in ("1", "0"):
-        os.environ["GPUBRIDGE_TAGGED_NATIVE"] = native
-        transports = link()
-        got = {}
-
-        def work(tr, rank, got=got):
-            for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.float64,
-                          torch.int8, torch.uint8, torch.int32, torch.int64):
-                for n in (1, 2, 1023, 1024, 1025, 5000):
-                    for op in ("sum", "max", "min"):
-                        t = values(rank, n, dtype)
-                        tr.all_reduce(t, op)
-                        got[(rank, str(dtype), n, op)] = t.clone()
-            t = values(rank, 3000, torch.float32)
-            tr.broadcast(t, members - 1)
-            got[(rank, "bcast")] = t.clone()
-        try:
-            run(transports, work)
-        finally:
-            for tr in transports:
-                tr.close()
-        results[native] = got
-    os.environ.pop("GPUBRIDGE_TAGGED_NATIVE", None)
-    assert results["1"].keys() == results["0"].keys()
-    for key, want in results["0"].items():
-        have = results["1"][key]
-        same = torch.equal(have.view(torch.uint8), want.view(torch.uint8)) if have.dtype != torch.bool else True
-        if not same:                      # NaN payload bits may differ; values must not
-            assert torch.equal(have.isnan(), want.isnan()), key
-            assert torch.equal(have.nan_to_num(), want.nan_to_num()), key
-    assert torch.equal(results["1"][(0, "bcast")], values(members - 1, 3000, torch.float32))
+    finally:
+        for tr in transports:
+            tr.close()
+    assert not errors, errors
+    for dtype, n, op in cases:
+        want = _expected([values(r, n, dtype) for r in range(members)], op)
+        for rank in range(members):
+            have = got[(rank, dtype, n, op)]
+            if not torch.equal(have.view(torch.uint8), want[rank].view(torch.uint8)):
+                # NaN payload bits may differ between the library and torch; values must not
+                assert torch.equal(have.isnan(), want[rank].isnan()), (dtype, n, op, rank)
+                assert torch.equal(have.nan_to_num(), want[rank].nan_to_num()), (dtype, n, op, rank)
+    for rank in range(members):
+        assert torch.equal(got[(rank, "bcast")], values(members - 1, 3000, torch.float32))
 
 
-def test_native_collectives_equal_python_two_members():
-    _native_equals_python(2)
+def test_native_collectives_two_members():
+    _native_matches_the_documented_order(2)
 
 
-def test_native_collectives_equal_python_ring():
-    _native_equals_python(3)
+def test_native_collectives_ring():
+    _native_matches_the_documented_order(3)
+
+
+def test_native_collectives_ring_of_five():
+    _native_matches_the_documented_order(5)
