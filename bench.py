@@ -12,7 +12,9 @@ network for datasets or checkpoints).  With N >= 2 GPUs the ranks are split into
 
 ``--impl ours`` (default) trains through ``gpubridge_b200.parallel.DataParallelTrainer``:
 flat buffers, bucketed all-reduce by the fused NVLink kernels overlapped with backward,
-fused AdamW, the step replayed from a CUDA graph.  ``--impl reference`` runs the unmodified
+fused AdamW, the step replayed from a CUDA graph.  The same run then measures, under
+``"hook_arm"``, the configuration a migrating user starts from: ``DistributedDataParallel`` with
+``gpubridge_b200.ddp_comm_hook`` and ``torch.optim.AdamW``, eager.  ``--impl reference`` runs the unmodified
 reference package from ``baseline/_ref`` through its public API: ``gpubridge.init()``,
 ``DistributedDataParallel`` with ``gpubridge.ddp_comm_hook``, ``torch.optim.AdamW``, on a
 plain-PyTorch model of the same architecture defined in this file.
@@ -20,7 +22,8 @@ plain-PyTorch model of the same architecture defined in this file.
 Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, barrier and
 synchronize on both sides, max over ranks) with inputs resident on the device; ``e2e`` times
 the same steps through the public API including, every step, the host-to-device copy of the
-step's tokens from pinned memory and a device-to-host read of the loss.
+step's tokens from pinned memory and a device-to-host read of the loss (every arm reads the
+previous step's loss through a pinned word once its copy has landed: the same loop for all).
 """
 from __future__ import annotations
 
@@ -124,6 +127,29 @@ def timed(run_steps, steps: int, device, barrier) -> float:
     return start.elapsed_time(end)
 
 
+def e2e_loop(step, data, host_loss, losses: list) -> "callable":
+    """The end-to-end loop every arm is timed with: each step takes its tokens from pinned host
+    memory (``step`` copies them to the device) and the loss travels back through a pinned
+    word; the host reads the PREVIOUS step's loss once its copy has landed, so no arm pays a
+    full device synchronisation per step and none is spared the read."""
+    import torch
+
+    def run(n: int) -> None:
+        copied = None
+        for i in range(n):
+            x, y = data[i % len(data)]
+            loss = step(x, y)
+            if copied is not None:
+                copied.synchronize()
+                losses.append(float(host_loss))
+            host_loss.copy_(loss.reshape(1).float(), non_blocking=True)
+            copied = torch.cuda.Event()
+            copied.record()
+        copied.synchronize()
+        losses.append(float(host_loss))
+    return run
+
+
 # ---- our arm --------------------------------------------------------------------------------------
 def run_ours(args) -> dict:
     import torch
@@ -166,20 +192,7 @@ def run_ours(args) -> dict:
 
     host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
     losses: list[float] = []
-
-    def e2e_steps(n: int) -> None:
-        copied = None
-        for i in range(n):
-            x, y = data[i % len(data)]
-            loss = trainer.step(x, y)           # host -> device copy of the tokens inside
-            if copied is not None:              # read the previous step's loss on the host
-                copied.synchronize()
-                losses.append(float(host_loss))
-            host_loss.copy_(loss.reshape(1), non_blocking=True)
-            copied = torch.cuda.Event()
-            copied.record()
-        copied.synchronize()
-        losses.append(float(host_loss))
+    e2e_steps = e2e_loop(trainer.step, data, host_loss, losses)   # the trainer copies the tokens itself
 
     device_steps(args.warmup)
     sampler = ClockSampler(local_rank)
@@ -214,8 +227,69 @@ def run_ours(args) -> dict:
         "final_loss": round(losses[-1], 4) if losses else None,
     }
     if topology is not None:
+        result["config"]["in_switch_reduction"] = bool(
+            topology.fabric is not None and topology.fabric.sw_team is not None)
+    if not args.no_hook_arm:
+        del trainer, e2e_steps
+        torch.cuda.empty_cache()
+        result["hook_arm"] = hook_arm(args, gb, gpt2, topology, device, data, resident, barrier,
+                                      max_over_ranks)
+    if topology is not None:
         gb.destroy()
     return result if rank == 0 else {}
+
+
+def hook_arm(args, gb, gpt2, topology, device, data, resident, barrier, max_over_ranks) -> dict:
+    """The configuration a user of the reference migrates to, measured beside the trainer:
+    ``DistributedDataParallel`` + ``gpubridge_b200.ddp_comm_hook`` + ``torch.optim.AdamW`` on the
+    same model, eager (no CUDA graph), bf16 autocast.  One GPU: the same loop without DDP."""
+    import torch
+    import torch.nn.functional as F
+    from torch.nn.parallel import DistributedDataParallel as DDP
+    rank, local_rank, world = env_world()
+    torch.manual_seed(0)
+    model = gpt2.build("gpt2-small").to(device)
+    net = model
+    if topology is not None:
+        net = DDP(model, device_ids=[local_rank], gradient_as_bucket_view=True)
+        net.register_comm_hook(None, gb.ddp_comm_hook)
+    optimizer = torch.optim.AdamW(net.parameters(), lr=LR, fused=True)
+    vocab = model.config.vocab
+    launches = [0]
+
+    def one_step(x, y):
+        optimizer.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = net(x)
+            loss = F.cross_entropy(logits.view(-1, vocab).float(), y.reshape(-1))
+        loss.backward()
+        optimizer.step()
+        return loss.detach()
+
+    def device_steps(n: int) -> None:
+        for i in range(n):
+            one_step(*resident[i % len(resident)])
+
+    host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
+    losses: list[float] = []
+    e2e_steps = e2e_loop(lambda x, y: one_step(x.to(device, non_blocking=True),
+                                               y.to(device, non_blocking=True)),
+                         data, host_loss, losses)
+    device_steps(args.warmup)
+    before = topology.fabric.launches if topology is not None and topology.fabric is not None else 0
+    ms = max_over_ranks(timed(device_steps, args.steps, device, barrier))
+    if topology is not None and topology.fabric is not None:
+        launches[0] = topology.fabric.launches - before
+    e2e_steps(2)
+    e2e_ms = max_over_ranks(timed(e2e_steps, args.steps, device, barrier))
+    tokens = BATCH * SEQ * world * args.steps
+    return {"what": "DistributedDataParallel + gpubridge_b200.ddp_comm_hook + torch.optim.AdamW "
+                    "(fused), eager",
+            "value": round(tokens / (ms * 1e-3), 1), "unit": "tokens/s",
+            "ms_per_step": round(ms / args.steps, 3),
+            "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "ms_per_step": round(e2e_ms / args.steps, 3)},
+            "fabric_launches": launches[0],
+            "final_loss": round(losses[-1], 4) if losses else None}
 
 
 # ---- the reference arm ---------------------------------------------------------------------------------
@@ -319,12 +393,10 @@ def run_reference(args) -> dict:
             one_step(*resident[i % len(resident)])
 
     losses: list[float] = []
-
-    def e2e_steps(n: int) -> None:
-        for i in range(n):
-            x, y = data[i % len(data)]
-            loss = one_step(x.to(device, non_blocking=True), y.to(device, non_blocking=True))
-            losses.append(loss.item())
+    host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
+    e2e_steps = e2e_loop(lambda x, y: one_step(x.to(device, non_blocking=True),
+                                               y.to(device, non_blocking=True)),
+                         data, host_loss, losses)
 
     device_steps(args.warmup)
     sampler = ClockSampler(local_rank)
@@ -361,6 +433,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly")
+    ap.add_argument("--no-hook-arm", action="store_true",
+                    help="skip the DDP + ddp_comm_hook + torch AdamW measurement beside the trainer's")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries one JSON line

@@ -8,7 +8,13 @@ it) and of ``dequantize_accumulate`` over two members.  Reported as *value* byte
 of the same tensor achieves, plus the algorithmic traffic fraction of the measured HBM peak in
 ``MEASURED_PEAKS.json`` when that file is present.
 
-    python -m gpubridge_b200.bench.bench_compression --numel 268435456
+    python -m gpubridge_b200.bench.bench_compression --numel 268435456 --triton
+
+``--triton`` adds, for every case of the reference's payload format (``ref``), the reference's
+own Triton kernels (``baseline/_ref/gpubridge/_compression_kernels.py``, unmodified, compiled by
+the Triton in this image on this GPU) timed the same way on the same tensors - the same-box
+comparison the kernels here are meant to win.  Those rows carry ``"impl": "reference-triton"``;
+when the reference is not installed or Triton cannot compile them, one row says why.
 """
 from __future__ import annotations
 
@@ -39,12 +45,29 @@ def timed(fn, trials: int) -> float:
     return statistics.median(out)
 
 
+def reference_triton():
+    """The reference's Triton codec module, or a string saying why it cannot be had."""
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    ref = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "gpubridge")):
+        return "baseline/_ref is not installed"
+    if ref not in sys.path:
+        sys.path.append(ref)
+    try:
+        from gpubridge import _compression_kernels as kernels
+    except Exception as failure:  # noqa: BLE001
+        return f"{type(failure).__name__}: {failure}"[:200]
+    return kernels
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--numel", type=int, default=1 << 28)
     ap.add_argument("--trials", type=int, default=10)
     ap.add_argument("--dtypes", default="float32,bfloat16")
     ap.add_argument("--only", default="", help="mode:format:dtype:op to run a single case")
+    ap.add_argument("--triton", action="store_true",
+                    help="also time the reference's Triton kernels on the same tensors")
     args = ap.parse_args(argv)
     n = args.numel
     peaks = {}
@@ -52,6 +75,10 @@ def main(argv=None) -> int:
     if os.path.exists(os.path.join(root, "MEASURED_PEAKS.json")):
         peaks = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
     rows = []
+    triton_kernels = reference_triton() if args.triton else None
+    if isinstance(triton_kernels, str):
+        rows.append({"impl": "reference-triton", "unavailable": triton_kernels})
+        triton_kernels = None
     for dtype_name in args.dtypes.split(","):
         dtype = getattr(torch, dtype_name)
         x = torch.randn(n, device="cuda").to(dtype)
@@ -90,6 +117,29 @@ def main(argv=None) -> int:
                     if peaks.get("hbm_gbs"):
                         row["traffic_of_measured_hbm"] = round(row["traffic_gbs"] / peaks["hbm_gbs"], 3)
                     rows.append(row)
+                if triton_kernels is not None and fmt == "ref":
+                    theirs = {
+                        "quantize": lambda: triton_kernels.quantize(mode, x, residual, payload[0]),
+                        "dequantize": lambda: triton_kernels.dequantize_accumulate(mode, payload, out),
+                    }
+                    for op, fn in theirs.items():
+                        if args.only and not args.only.endswith(op):
+                            continue
+                        try:
+                            ms = timed(fn, args.trials)
+                        except Exception as failure:  # noqa: BLE001 - e.g. Triton cannot compile here
+                            rows.append({"impl": "reference-triton", "op": op, "mode": mode,
+                                         "dtype": dtype_name,
+                                         "unavailable": f"{type(failure).__name__}: {failure}"[:200]})
+                            continue
+                        mine = next(r for r in reversed(rows) if r.get("op") == op and r.get("mode") == mode
+                                    and r.get("format") == "ref" and r.get("dtype") == dtype_name
+                                    and "impl" not in r)
+                        rows.append({"impl": "reference-triton", "op": op, "mode": mode, "format": "ref",
+                                     "dtype": dtype_name, "numel": n, "ms": round(ms, 4),
+                                     "value_gbs": round(n * esize / (ms * 1e-3) / 1e9, 1),
+                                     "of_copy_value_rate": round(copy_ms / ms, 3),
+                                     "ours_over_theirs": round(ms / mine["ms"], 3)})
     for row in rows:
         print(json.dumps(row), flush=True)
     return 0

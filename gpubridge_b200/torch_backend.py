@@ -641,14 +641,36 @@ def _teardown(group: GpubridgeProcessGroup) -> None:
         _close_subgroup(sub)
 
 
+def front_end() -> str:
+    """Which object answers ``backend="gpubridge"``: ``native`` - the C++ ``c10d::Backend`` of
+    :mod:`gpubridge_b200.native_backend`, with the Python group behind it for everything off
+    the hot path - or ``python``.  ``GPUBRIDGE_FRONT_END`` decides; unset (``auto``) it is the
+    C++ front end on GPU ranks and the Python group in CPU simulation."""
+    setting = os.environ.get("GPUBRIDGE_FRONT_END", "auto").strip().lower() or "auto"
+    if setting not in ("auto", "native", "python"):
+        raise ValueError(f"GPUBRIDGE_FRONT_END={setting!r}: expected auto, native or python")
+    if setting != "auto":
+        return setting
+    from gpubridge_b200.config import is_simulated
+    import torch
+    return "native" if torch.cuda.is_available() and not is_simulated() else "python"
+
+
 def create(options, backend_options=None):
-    """The creator torch calls (``extended_api=True``) on a group's members.  With
-    ``GPUBRIDGE_FRONT_END=native`` the group is fronted by the C++ backend of
-    :mod:`gpubridge_b200.native_backend` (the same as asking for ``backend="gpubridge_native"``);
-    otherwise it is the Python process group."""
-    if os.environ.get("GPUBRIDGE_FRONT_END", "python").strip().lower() == "native":
+    """The creator torch calls (``extended_api=True``) on a group's members: the C++ front end
+    or the Python process group, as :func:`front_end` says.  If the C++ module cannot be
+    loaded on an ``auto`` choice the Python group answers, with a warning."""
+    choice = front_end()
+    if choice == "native":
         from gpubridge_b200 import native_backend
-        return native_backend.create(options, backend_options)
+        try:
+            return native_backend.create(options, backend_options)
+        except (ImportError, OSError, RuntimeError) as failure:
+            if os.environ.get("GPUBRIDGE_FRONT_END", "auto").strip().lower() == "native":
+                raise
+            import warnings
+            warnings.warn(f"gpubridge: the C++ front end could not be loaded ({failure}); "
+                          "using the Python process group", RuntimeWarning, stacklevel=2)
     return create_python(options, backend_options)
 
 
