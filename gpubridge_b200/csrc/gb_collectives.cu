@@ -58,17 +58,41 @@ __device__ __forceinline__ size_t stripe_valid(const GbArgs& a, size_t c0, int j
     return left < a.stripe ? left : a.stripe;
 }
 
+// V results of type TO to dst: as 16-byte (or, for 8 bytes in all, one 8-byte) stores when
+// `aligned` says dst + this vector is aligned to its own size, else one by one.
+template <typename TO, int V>
+__device__ __forceinline__ void store_results(TO* dst, const TO (&vals)[V], bool aligned) {
+    constexpr int BYTES = V * (int)sizeof(TO);
+    if (aligned && BYTES >= 16) {
+        union { uint4 q[BYTES / 16 > 0 ? BYTES / 16 : 1]; TO e[V]; } pack;
+        #pragma unroll
+        for (int j = 0; j < V; ++j) pack.e[j] = vals[j];
+        #pragma unroll
+        for (int q = 0; q < BYTES / 16; ++q) gb_st16(reinterpret_cast<char*>(dst) + 16 * q, pack.q[q]);
+    } else if (aligned && BYTES == 8) {
+        union { uint2 q; TO e[V]; } pack;
+        #pragma unroll
+        for (int j = 0; j < V; ++j) pack.e[j] = vals[j];
+        *reinterpret_cast<uint2*>(dst) = pack.q;
+    } else {
+        #pragma unroll
+        for (int j = 0; j < V; ++j) dst[j] = vals[j];
+    }
+}
+
 // Reduce local slots in hierarchical order into out[0 .. count).
 //   slot s lives at slots + s * slot_bytes; island g is slot_of[bounds[g] .. bounds[g+1]).
-template <typename T, int OP>
+// TO: the type of `out`; when it differs from T (float <-> bf16) the sum - island sums rounded
+// to T, islands added in the accumulator type, divided - is rounded once, to TO.
+template <typename T, int OP, typename TO = T>
 __device__ __forceinline__ void reduce_slots(const GbLane& L, const char* slots, size_t slot_bytes,
                                              const int* slot_of, const int* bounds, int n_groups,
-                                             size_t count, T* out, int divide) {
+                                             size_t count, TO* out, int divide) {
     typedef typename GbAcc<T>::type A;
     constexpr int V = Vec<T>::N;
     const size_t tid = L.tid, nth = L.nth;
     const size_t nvec = count / V;
-    const bool out_aligned = ((uintptr_t)out & 15u) == 0;
+    const bool out_aligned = ((uintptr_t)out & (V * sizeof(TO) >= 16 ? 15u : V * sizeof(TO) - 1u)) == 0;
     // U vectors per thread and step, so U loads are in flight per slot (a single vector per
     // step leaves the loop bound by memory latency)
     constexpr int U = V >= 8 ? 4 : 8;
@@ -105,15 +129,11 @@ __device__ __forceinline__ void reduce_slots(const GbLane& L, const char* slots,
         for (int u = 0; u < U; ++u) {
             const size_t v = v0 + (size_t)u * nth;
             if (v >= nvec) continue;
-            Vec<T> r;
+            TO r[V];
             #pragma unroll
             for (int j = 0; j < V; ++j)
-                r.e[j] = gb_down<T>(divide > 0 ? gb_divide<A>(total[u][j], divide) : total[u][j]);
-            if (out_aligned) gb_st16(out + v * V, r.u);
-            else {
-                #pragma unroll
-                for (int j = 0; j < V; ++j) out[v * V + j] = r.e[j];
-            }
+                r[j] = gb_down<TO>(divide > 0 ? gb_divide<A>(total[u][j], divide) : total[u][j]);
+            store_results<TO, V>(out + v * V, r, out_aligned);
         }
     }
     // ragged tail: count is not a multiple of a 16-byte vector
@@ -133,7 +153,7 @@ __device__ __forceinline__ void reduce_slots(const GbLane& L, const char* slots,
             A rounded = gb_up<T>(gb_down<T>(part));
             total = (g == 0) ? rounded : GbFold<OP, A>::run(total, rounded);
         }
-        out[i] = gb_down<T>(divide > 0 ? gb_divide<A>(total, divide) : total);
+        out[i] = gb_down<TO>(divide > 0 ? gb_divide<A>(total, divide) : total);
     }
 }
 
@@ -1058,12 +1078,14 @@ allgather_kernel(GbTeam tm, GbArgs a) {
 // ---- reduce-scatter -------------------------------------------------------------------------------
 // Region A: [2 parities][2 chunk buffers][world slots] ; len_a = world * chunk bytes.
 // n: elements of one slice; chunk: elements per step.
-template <typename T, int OP>
+// TO: the type of the output slice (T, or the other one of float / bf16: the cast that would
+// otherwise be a separate pass over the result is the reduction's one rounding).
+template <typename T, int OP, typename TO = T>
 __global__ void __launch_bounds__(THREADS)
 reduce_scatter_kernel(GbTeam tm, GbArgs a) {
     const unsigned parity = gb_ld_volatile(&tm.ctrl->epoch) & 1u;
     const T* in = static_cast<const T*>(a.in);
-    T* out = static_cast<T*>(a.out);
+    TO* out = static_cast<TO*>(a.out);
     const size_t slot = a.chunk * sizeof(T);
     const long nchunks = (long)((a.n + a.chunk - 1) / a.chunk);
     // Roles: the blocks of role A store chunk t into its owners while the rest reduce chunk t-1.
@@ -1093,8 +1115,8 @@ reduce_scatter_kernel(GbTeam tm, GbArgs a) {
             const long c = t - 1;
             const size_t c0 = (size_t)c * a.chunk;
             const size_t len = a.n - c0 < a.chunk ? a.n - c0 : a.chunk;
-            reduce_slots<T, OP>(L, tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
-                                slot, tm.order, tm.island_off, tm.n_islands, len, out + c0, a.divide);
+            reduce_slots<T, OP, TO>(L, tm.ws[tm.rank] + a.off_a + (size_t)(parity * 2 + (c & 1)) * a.len_a,
+                                    slot, tm.order, tm.island_off, tm.n_islands, len, out + c0, a.divide);
         }
         if (t < nchunks && !gb_sync_all(tm, (unsigned)(t < 7 ? t : 7), t == 0)) return;
     }
@@ -1244,6 +1266,15 @@ cudaError_t launch_plain(int kind, const GbTeam& tm, const GbArgs& a, int grid, 
     return cudaGetLastError();
 }
 
+template <typename T, typename TO>
+cudaError_t launch_scatter_cast(const GbTeam& tm, const GbArgs& a, int grid, cudaStream_t s) {
+    static cudaError_t opted = cudaFuncSetAttribute(
+        reduce_scatter_kernel<T, GB_SUM, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, GB_RING_SMEM);
+    if (opted != cudaSuccess) return opted;
+    reduce_scatter_kernel<T, GB_SUM, TO><<<grid, THREADS, GB_RING_SMEM, s>>>(tm, a);
+    return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t launch_nvls(const GbTeam& tm, const GbArgs& a, int grid, cudaStream_t s) {
     allreduce_nvls_kernel<T><<<grid, THREADS, 0, s>>>(tm, a);
@@ -1275,7 +1306,8 @@ cudaError_t launch_coded(int codec, const GbTeam& tm, const GbArgs& a, int grid,
 
 // kind: 0 one-shot all-reduce, 1 hierarchical all-reduce, 2 reduce-scatter,
 //       3 / 4 hierarchical all-reduce through the bulk-copy ring (queue / phased; no codec),
-//       5 all-reduce through the switch (NVLS multimem).
+//       5 all-reduce through the switch (NVLS multimem),
+//       6 reduce-scatter whose output has the other float type (dtype f32: bf16 out; bf16: f32 out).
 // codec (kind 1, SUM, floating point only): GbCodec.  Returns a cudaError_t.
 extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const GbTeam* team,
                                 const GbArgs* args, int grid, cudaStream_t stream) {
@@ -1289,6 +1321,12 @@ extern "C" int gb_launch_reduce(int kind, int dtype, int op, int codec, const Gb
             case GB_BF16: return launch_coded<__nv_bfloat16>(codec, tm, a, grid, stream);
             case GB_F16: return launch_coded<__half>(codec, tm, a, grid, stream);
         }
+        return cudaErrorInvalidValue;
+    }
+    if (kind == 6) {                        // reduce-scatter that casts: float in -> bf16 out or back
+        if (op != GB_SUM) return cudaErrorInvalidValue;
+        if (dtype == GB_F32) return launch_scatter_cast<float, __nv_bfloat16>(tm, a, grid, stream);
+        if (dtype == GB_BF16) return launch_scatter_cast<__nv_bfloat16, float>(tm, a, grid, stream);
         return cudaErrorInvalidValue;
     }
     if (kind == 5) {                        // through the switch: SUM of f32, bf16, f16 only

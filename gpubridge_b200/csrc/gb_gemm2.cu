@@ -19,6 +19,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "gb_common.cuh"
 #include "gb_tc.cuh"
@@ -47,6 +48,8 @@ struct Gemm2Args {
     int comm_blocks;                 // even; CTAs [0, comm_blocks) communicate (scheduled first)
     size_t ws_off;                   // staging region inside the workspaces: two halves ...
     size_t ws_half;                  // ... this far apart, selected by the collective counter's parity
+    int group;                       // > 1: walk a shard's tiles in bands of this many n-tiles
+    int probe;                       // 1: load operands but issue no MMA (measures the ingest rate alone)
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -129,6 +132,18 @@ __device__ __forceinline__ Tile2 tile_of(const Gemm2Args& a, const GbTeam& tm, l
     const long rest = t % per_shard;
     Tile2 tile;
     tile.shard = (tm.rank + step) % tm.world;
+    if (a.group > 1) {
+        // Bands of `group` n-tiles, inside a band m outer and n inner: the pairs that run at the
+        // same time then share about sqrt(pairs) tiles of X and of W each instead of reading one
+        // tile of W and every tile of X, which keeps both operands in L2.
+        const long band_tiles = (long)a.group * m_tiles;
+        const int band = (int)(rest / band_tiles);
+        const int width = n_per_shard - band * a.group < a.group ? n_per_shard - band * a.group : a.group;
+        const long r = rest - (long)band * band_tiles;
+        tile.n0 = tile.shard * a.shard_rows + (band * a.group + (int)(r % width)) * BN;
+        tile.m0 = (int)(r / width) * BM;
+        return tile;
+    }
     tile.n0 = tile.shard * a.shard_rows + (int)(rest / m_tiles) * BN;
     tile.m0 = (int)(rest % m_tiles) * BM;
     return tile;
@@ -240,9 +255,11 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                 fence_after();
                 const unsigned char* sa = tiles + stage * STAGE_BYTES;
                 const uint64_t da = tile_desc(sa), db = tile_desc(sa + A_BYTES);
-                #pragma unroll
-                for (int kk = 0; kk < BK / 16; ++kk)
-                    pair_mma(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                if (!a.probe) {
+                    #pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk)
+                        pair_mma(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                }
                 pair_commit(s32(empty + stage));                       // frees the stage here ...
                 pair_commit(in_cta(s32(empty + stage), 1));            // ... and in the peer
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -343,6 +360,9 @@ extern "C" int gb_allgather_gemm_pair(const GbTeam* team, void* y, const void* x
                                       void* gathered, unsigned int* flags, unsigned int* error,
                                       unsigned int epoch, int M, int N, int K, size_t ws_off,
                                       size_t ws_half, int gemm_blocks, int comm_blocks, cudaStream_t stream) {
+    // tuning switches for measurements: the tile walk and the operand-ingest probe
+    static const int tile_group = []{ const char* v = getenv("GPUBRIDGE_GEMM_GROUP"); return v ? atoi(v) : 8; }();
+    static const int ingest_probe = []{ const char* v = getenv("GPUBRIDGE_GEMM_PROBE"); return v ? atoi(v) : 0; }();
     if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || N % team->world || gemm_blocks < 2 ||
         comm_blocks < 2 || (gemm_blocks & 1) || (comm_blocks & 1))
         return (int)cudaErrorInvalidValue;
@@ -357,6 +377,8 @@ extern "C" int gb_allgather_gemm_pair(const GbTeam* team, void* y, const void* x
     a.shard_rows = N / team->world;
     a.ws_off = ws_off;
     a.ws_half = ws_half;
+    a.group = tile_group;
+    a.probe = ingest_probe;
     const size_t smem = STAGES * STAGE_BYTES + 256 + 1024;
     static bool configured = false;
     static int resident_clusters = 0;

@@ -43,11 +43,22 @@ def stale() -> bool:
 
 def build(verbose: bool = False) -> str:
     """Compile when the source is newer than the module; returns the module's path."""
+    if not stale() and os.path.exists(_build.LIB):
+        return OUT                              # both libraries are there: nothing to compile
     _build.build()
     if not stale():
         return OUT
     from torch.utils import cpp_extension
     os.makedirs(WORK, exist_ok=True)
+    # torch serialises builds of one directory with a lock FILE and waits for it without a
+    # limit; a build that was killed (or a tree copied in mid-build) leaves it behind for ever
+    lock = os.path.join(WORK, "lock")
+    try:
+        import time
+        if time.time() - os.path.getmtime(lock) > 600:
+            os.remove(lock)
+    except OSError:
+        pass
     cpp_extension.load(
         name=NAME, sources=[SRC], extra_include_paths=[_build.CSRC], with_cuda=True,
         extra_cflags=["-O2", "-std=c++17"],

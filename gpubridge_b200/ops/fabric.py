@@ -581,6 +581,12 @@ class Fabric:
             output.view(-1).copy_(scratch.view(self.world, -1)[self.rank])
             return
         esize = tensor.element_size()
+        # a float input may leave as bf16 and a bf16 input as float: the cast is the sum's one
+        # rounding instead of a pass of its own over the result
+        casting = output.dtype != tensor.dtype
+        if casting and {output.dtype, tensor.dtype} != {torch.float32, torch.bfloat16}:
+            raise ValueError("reduce_scatter casts between float32 and bfloat16 only, got "
+                             f"{tensor.dtype} -> {output.dtype}")
         current = self._begin()
         try:
             with torch.cuda.stream(self.comm_stream):
@@ -593,7 +599,7 @@ class Fabric:
                 grid = self._grid(tensor.nbytes, min(self.scatter_blocks, self.max_blocks))
                 if -(-n // args.chunk) >= 4 and grid >= 8:
                     args.role_a = grid * 3 // 4
-                self._launch_reduce(2, tensor.dtype, "sum", 0, args, grid)
+                self._launch_reduce(6 if casting else 2, tensor.dtype, "sum", 0, args, grid)
         finally:
             self._end(current)
 

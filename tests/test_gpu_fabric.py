@@ -78,6 +78,13 @@ def _collectives(rank, topology, policy):
         out = torch.empty(n, device=dev)
         gb.reduce_scatter_tensor(out, rank_tensor(rank, world * n).to(dev), gb.ReduceOp.AVG)
         assert torch.equal(out.cpu(), expected_sum(world, world * n).view(world, n)[rank] / world)
+        # the cast fused into the reduction: float in -> bf16 out and back (the fabric's own call)
+        for src, dst in ((torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32)):
+            full = rank_tensor(rank, world * n, src).to(dev)
+            out = torch.full((n,), 7, dtype=dst, device=dev)
+            topology.fabric.reduce_scatter(out, full, divide=world)
+            want = (expected_sum(world, world * n, torch.float64).view(world, n)[rank] / world).to(dst)
+            assert torch.equal(out.cpu(), want), ("reduce_scatter cast", n, src, dst)
     # async handles and stream ordering: the tensor is produced by queued GPU work
     big = torch.ones(1 << 22, device=dev)
     for _ in range(20):
