@@ -26,14 +26,28 @@
 
 namespace {
 
-constexpr int BM = 256, BN = 256, BK = 64;     // per pair
-constexpr int HALF = 128;                      // rows of X and rows of W per CTA
-constexpr int STAGES = 6;
+constexpr int BM = 256, BK = 64;               // per pair
+constexpr int HALF = 128;                      // rows of X and rows of W per CTA and MMA
 constexpr int A_BYTES = HALF * BK * 2;         // 16 KiB
-constexpr int B_BYTES = HALF * BK * 2;         // 16 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int B_BYTES = HALF * BK * 2;         // 16 KiB per 256-column half of the output tile
 constexpr int THREADS2 = 192;
 constexpr int TMEM_COLS = 512;
+constexpr int SMEM_TILES = 192 << 10;          // operand ring of either shape
+
+// The output tile of a pair is 256 x (256 * NH).  NH = 1: two 256-column accumulators, so the
+// epilogue of one tile runs under the main loop of the next; 32 KB of operands per CTA and
+// step, six stages.  NH = 2: one 512-column accumulator (all of tensor memory) fed by two MMAs
+// per step that share the X tile; 48 KB per CTA and step for twice the math - a quarter less
+// operand traffic per FLOP, which is what bounds this kernel (measured: loading the operands
+// alone takes longer than cuBLAS's whole GEMM) - at the price of an epilogue that the next
+// tile's main loop has to wait for; four stages.
+template <int NH> struct Shape {
+    static constexpr int BN = 256 * NH;
+    static constexpr int STAGE_BYTES = A_BYTES + NH * B_BYTES;
+    static constexpr int STAGES = SMEM_TILES / STAGE_BYTES;
+    static constexpr int ACCS = NH == 1 ? 2 : 1;
+};
+constexpr int MAX_STAGES = 6;
 
 struct Gemm2Args {
     __nv_bfloat16* y;
@@ -124,7 +138,7 @@ __host__ __device__ constexpr uint32_t pair_idesc(int m, int n) {
 }
 
 struct Tile2 { int m0, n0, shard; };
-__device__ __forceinline__ Tile2 tile_of(const Gemm2Args& a, const GbTeam& tm, long t) {
+__device__ __forceinline__ Tile2 tile_of(const Gemm2Args& a, const GbTeam& tm, long t, int BN) {
     const int m_tiles = (a.M + BM - 1) / BM;
     const int n_per_shard = (a.shard_rows + BN - 1) / BN;
     const long per_shard = (long)m_tiles * n_per_shard;
@@ -149,9 +163,12 @@ __device__ __forceinline__ Tile2 tile_of(const Gemm2Args& a, const GbTeam& tm, l
     return tile;
 }
 
+template <int NH>
 __global__ void __launch_bounds__(THREADS2)
 allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                            const __grid_constant__ CUtensorMap map_w, GbTeam tm, Gemm2Args a) {
+    constexpr int BN = Shape<NH>::BN, STAGES = Shape<NH>::STAGES, STAGE_BYTES = Shape<NH>::STAGE_BYTES;
+    constexpr int ACCS = Shape<NH>::ACCS;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     if ((int)blockIdx.x < a.comm_blocks) {
         // ---- communication CTAs: as in the single-CTA kernel; the lowest indices, so they are
@@ -180,9 +197,9 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
     // ---- GEMM CTA pairs ---------------------------------------------------------------------
     unsigned char* tiles = reinterpret_cast<unsigned char*>(
         ((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_full = empty + STAGES;          // [2]
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + SMEM_TILES);
+    uint64_t* empty = full + MAX_STAGES;
+    uint64_t* acc_full = empty + MAX_STAGES;      // [2]
     uint64_t* acc_empty = acc_full + 2;           // [2], used on the leader
     uint64_t* drained = acc_empty + 2;            // the issuer's last instructions after a failure
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
@@ -220,7 +237,7 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
         int ready_shard = -1;
         bool alive = true;
         for (long t = pair; alive && t < total; t += pairs) {
-            const Tile2 tile = tile_of(a, tm, t);
+            const Tile2 tile = tile_of(a, tm, t, BN);
             if (tile.shard != ready_shard) {
                 if (!tc_wait_flag(a.flags + tile.shard, a.epoch, guard, 2u)) { alive = false; break; }
                 asm volatile("fence.proxy.async.global;" ::: "memory");
@@ -232,7 +249,10 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                 const uint32_t leader_full = in_cta(s32(full + stage), 0);
                 if (leader) bar_expect(full + stage, 2 * STAGE_BYTES);   // both CTAs' bytes
                 load_tile(sa, &map_x, kb * BK, tile.m0 + (int)rank * HALF, leader_full);
-                load_tile(sa + A_BYTES, &map_w, kb * BK, tile.n0 + (int)rank * HALF, leader_full);
+                #pragma unroll
+                for (int h = 0; h < NH; ++h)                     // this CTA's 128 rows of every half
+                    load_tile(sa + A_BYTES + h * B_BYTES, &map_w, kb * BK,
+                              tile.n0 + h * 256 + (int)rank * HALF, leader_full);
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
@@ -241,24 +261,29 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
         // leader reaches only after its issuer has waited (bounded) for the tensor pipe.
     } else if (warp == 1 && lane == 0 && leader) {
         // ---- MMA issuer of the pair ----
-        constexpr uint32_t idesc = pair_idesc(BM, BN);
+        constexpr uint32_t idesc = pair_idesc(BM, 256);
         uint32_t stage = 0, phase = 0, local = 0;
         bool alive = true;
         for (long t = pair; alive && t < total; t += pairs, ++local) {
-            const uint32_t buf = local & 1u, use = local >> 1;
+            const uint32_t buf = ACCS == 2 ? (local & 1u) : 0u, use = ACCS == 2 ? (local >> 1) : local;
             // both epilogues drained it
             if (!mbar_wait(acc_empty + buf, (use & 1u) ^ 1u, guard, 3u)) { alive = false; break; }
             fence_after();
-            const uint32_t tmem_d = tmem_base + buf * BN;
+            const uint32_t tmem_d = tmem_base + buf * 256;
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(full + stage, phase, guard, 4u)) { alive = false; break; }
                 fence_after();
                 const unsigned char* sa = tiles + stage * STAGE_BYTES;
-                const uint64_t da = tile_desc(sa), db = tile_desc(sa + A_BYTES);
+                const uint64_t da = tile_desc(sa);
                 if (!a.probe) {
                     #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)
-                        pair_mma(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    for (int h = 0; h < NH; ++h) {
+                        const uint64_t db = tile_desc(sa + A_BYTES + h * B_BYTES);
+                        #pragma unroll
+                        for (int kk = 0; kk < BK / 16; ++kk)
+                            pair_mma(tmem_d + h * 256, da + 2 * kk, db + 2 * kk, idesc,
+                                     (kb | kk) != 0 ? 1u : 0u);
+                    }
                 }
                 pair_commit(s32(empty + stage));                       // frees the stage here ...
                 pair_commit(in_cta(s32(empty + stage), 1));            // ... and in the peer
@@ -283,8 +308,8 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
         const int quarter = warp & 3;
         uint32_t local = 0;
         for (long t = pair; t < total; t += pairs, ++local) {
-            const Tile2 tile = tile_of(a, tm, t);
-            const uint32_t buf = local & 1u, use = local >> 1;
+            const Tile2 tile = tile_of(a, tm, t, BN);
+            const uint32_t buf = ACCS == 2 ? (local & 1u) : 0u, use = ACCS == 2 ? (local >> 1) : local;
             if (!mbar_wait_warp(acc_full + buf, use & 1u, guard, 5u)) break;
             fence_after();
             const int row = tile.m0 + (int)rank * HALF + quarter * 32 + lane;
@@ -292,7 +317,7 @@ allgather_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
             #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
-                ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c, r);
+                ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + c, r);
                 const int col = tile.n0 + c;
                 if (row < a.M && col < shard_end && col < a.N) {
                     __nv_bfloat16* dst = a.y + (size_t)row * a.N + col;
@@ -379,21 +404,24 @@ extern "C" int gb_allgather_gemm_pair(const GbTeam* team, void* y, const void* x
     a.ws_half = ws_half;
     a.group = tile_group;
     a.probe = ingest_probe;
-    const size_t smem = STAGES * STAGE_BYTES + 256 + 1024;
+    const size_t smem = SMEM_TILES + 256 + 1024;
+    // GPUBRIDGE_GEMM_WIDE: 1 = 256 x 512 tiles with one accumulator, 0 = 256 x 256 with two
+    static const int wide = []{ const char* v = getenv("GPUBRIDGE_GEMM_WIDE"); return v ? atoi(v) : 1; }();
+    typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, GbTeam, Gemm2Args);
+    Kernel kernel = wide ? allgather_gemm_pair_kernel<2> : allgather_gemm_pair_kernel<1>;
     static bool configured = false;
     static int resident_clusters = 0;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(allgather_gemm_pair_kernel,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
         // every CTA must be resident at once (pairs wait for the communication CTAs' flags)
         cudaLaunchConfig_t probe = {};
         probe.gridDim = dim3(2); probe.blockDim = dim3(THREADS2); probe.dynamicSmemBytes = smem;
         probe.attrs = attr; probe.numAttrs = 1;
-        err = cudaOccupancyMaxActiveClusters(&resident_clusters, allgather_gemm_pair_kernel, &probe);
+        err = cudaOccupancyMaxActiveClusters(&resident_clusters, kernel, &probe);
         if (err != cudaSuccess) return (int)err;
         configured = true;
     }
@@ -408,5 +436,5 @@ extern "C" int gb_allgather_gemm_pair(const GbTeam* team, void* y, const void* x
     config.stream = stream;
     config.attrs = attr;
     config.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&config, allgather_gemm_pair_kernel, map_x, map_w, *team, a);
+    return (int)cudaLaunchKernelEx(&config, kernel, map_x, map_w, *team, a);
 }

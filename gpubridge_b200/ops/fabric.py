@@ -144,6 +144,7 @@ class Fabric:
         # switch memory bound by the fabric itself (enable_switch): the team's group, this
         # rank's island's group, and the structures the kernels take
         self._switch_groups: list = []
+        self.switch_error = ""          # why enable_switch() said no, for reports
         self.sw_team = self.sw_island = None
         self._bseq = 0
         self.switch_min_bytes = _config.size_setting("GPUBRIDGE_SWITCH_MIN_BYTES", 64 << 10, multiple=1)
@@ -306,6 +307,7 @@ class Fabric:
 
         try:
             if not everyone("supported", _switch.supported(lib, device)):
+                self.switch_error = "a GPU of the team cannot join a multicast object (no NVSwitch multicast)"
                 return False
             groups = []
             try:
@@ -313,8 +315,9 @@ class Fabric:
                                                  nbytes, timeout)
                 groups.append(team_group)
                 built = True
-            except _switch.SwitchUnavailable:
+            except _switch.SwitchUnavailable as failure:
                 built = False
+                self.switch_error = str(failure)
             if not everyone("team", built):
                 for g in groups:
                     g.release(lib)
@@ -327,15 +330,17 @@ class Fabric:
                     island_group = _switch.build_group(
                         lib, self._store, f"{key}/island{self.team.my_island}", me, mine, device,
                         nbytes, timeout)
-                except _switch.SwitchUnavailable:
+                except _switch.SwitchUnavailable as failure:
                     island_group = None
+                    self.switch_error = f"island group: {failure}"
                 if not everyone("islands", island_group is not None):
                     if island_group is not None:
                         island_group.release(lib)
                     island_group = None
                 else:
                     groups.append(island_group)
-        except _switch.SwitchUnavailable:
+        except _switch.SwitchUnavailable as failure:
+            self.switch_error = str(failure)
             return False
         bseq = ctypes.c_void_p()
         _lib.check(lib.gb_symm_alloc(4096, ctypes.byref(bseq)), "cudaMalloc (switch barrier numbers)")

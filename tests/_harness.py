@@ -128,3 +128,112 @@ LAYOUTS = {
     "single-vendor": ("nvidia", "nvidia", "nvidia"),
     "single-rank": ("amd",),
 }
+
+
+# ---- a pool of ranks that stays up for a whole test module ------------------------------------------
+def _pool_entry(rank, world, vendors, path, env, mode, init, commands, results):
+    """One pooled rank: join once, then run whatever the test process sends."""
+    try:
+        os.environ.update(env)
+        if vendors[rank]:
+            os.environ["GPUBRIDGE_VENDOR"] = vendors[rank]
+            os.environ.setdefault("GPUBRIDGE_SIM_HOSTNAME", "simhost")
+        else:
+            os.environ["LOCAL_RANK"] = str(rank)
+        torch.set_num_threads(1)
+        import torch.distributed as dist
+
+        import gpubridge_b200 as gb
+        timeout = timedelta(seconds=40)
+        warnings.simplefilter("ignore", gb.SplitTestWarning)
+        if mode == "init":
+            context = gb.init(f"file://{path}", rank=rank, world_size=world, timeout=timeout, **init)
+        else:
+            dist.init_process_group("gpubridge", init_method=f"file://{path}", rank=rank,
+                                    world_size=world, timeout=timeout)
+            context = world
+        results.put((rank, "ready", None))
+        while True:
+            job = commands.get()
+            if job is None:
+                break
+            fn, args = job
+            try:
+                results.put((rank, "ok", fn(rank, context, *args)))
+            except BaseException as exc:  # noqa: BLE001
+                results.put((rank, "error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+        if mode == "init":
+            gb.destroy()
+        else:
+            dist.destroy_process_group()
+    except BaseException as exc:  # noqa: BLE001
+        results.put((rank, "error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+
+
+class RankPool:
+    """Ranks that join once and then run many scenarios: ``pool.run(fn, *args)`` calls
+    ``fn(rank, context, *args)`` on every rank (``context``: the topology in ``init`` mode, the
+    world size in ``backend`` mode) and returns the results by rank.  Starting four processes
+    and a process group costs seconds; a module of thirty scenarios pays it once.  After a
+    failed scenario the group may be out of step, so the pool is rebuilt before the next one."""
+
+    def __init__(self, vendors, directory, *, mode="backend", env=None, init=None):
+        self.vendors, self.directory = list(vendors), str(directory)
+        self.mode, self.env, self.init = mode, dict(env or {}), dict(init or {})
+        self.procs, self.generation = [], 0
+        self._start()
+
+    def _start(self):
+        global _counter
+        _counter += 1
+        self.generation += 1
+        world = len(self.vendors)
+        path = os.path.join(self.directory, f"pool-{os.getpid()}-{_counter}")
+        ctx = mp.get_context("spawn")
+        self.results = ctx.Queue()
+        self.commands = [ctx.Queue() for _ in range(world)]
+        self.procs = [ctx.Process(target=_pool_entry, args=(r, world, self.vendors, path, self.env,
+                                                            self.mode, self.init, self.commands[r],
+                                                            self.results))
+                      for r in range(world)]
+        for p in self.procs:
+            p.start()
+        self._collect(60, "ready")
+        self.healthy = True
+
+    def _collect(self, timeout, expect="ok"):
+        world, got = len(self.vendors), {}
+        try:
+            for _ in range(world):
+                rank, status, out = self.results.get(timeout=timeout)
+                got[rank] = (status, out)
+        except Exception:  # noqa: BLE001 - queue.Empty
+            pass
+        errors = [f"rank {r}: {out}" for r, (status, out) in sorted(got.items()) if status != expect]
+        missing = [r for r in range(world) if r not in got]
+        if missing:
+            errors.append(f"ranks {missing} did not answer within {timeout} s")
+        if errors:
+            self.healthy = False
+            raise AssertionError("\n".join(errors))
+        return [got[r][1] for r in range(world)]
+
+    def run(self, fn, *args, timeout=90):
+        if not self.healthy:
+            self.close(force=True)
+            self._start()
+        for queue in self.commands:
+            queue.put((fn, args))
+        return self._collect(timeout)
+
+    def close(self, force=False):
+        for queue in self.commands:
+            try:
+                queue.put(None)
+            except Exception:  # noqa: BLE001
+                pass
+        for p in self.procs:
+            p.join(1 if force else 15)
+            if p.is_alive():
+                p.kill()
+        self.procs = []

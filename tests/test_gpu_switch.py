@@ -24,7 +24,7 @@ def test_team_of_one_round_trips_through_switch_memory():
     fabric = fabric_mod.create_single(dev)
     try:
         if not fabric.enable_switch():
-            pytest.skip("this GPU or driver cannot bind multicast memory")
+            pytest.skip(f"this GPU or driver cannot bind multicast memory: {fabric.switch_error}")
         fabric.switch_min_bytes = 0                       # every size takes the switch path
         before = fabric.launches
         for dtype in (torch.float32, torch.bfloat16, torch.float16):
@@ -55,7 +55,7 @@ def _sums(rank, topology):
     import gpubridge_b200 as gb
     fabric = topology.fabric
     if fabric is None or fabric.sw_team is None:
-        return "unavailable"
+        return "unavailable: " + (fabric.switch_error if fabric is not None else "no fabric")
     dev, world = topology.device, topology.world_size
     fabric.switch_min_bytes = 0
     if fabric._engine:
@@ -93,7 +93,7 @@ def _sums(rank, topology):
                          ids=lambda s: ",".join(s.values()) or "one-island")
 def test_sums_through_the_switch(tmp_path, split):
     out = run_ranks(gpu_ranks(WORLD), _sums, tmp_path, env={"GPUBRIDGE_NVLS": "1", **split}, timeout=240)
-    if any(o == "unavailable" for o in out):
-        pytest.skip("no NVLink multicast binding on this machine")
+    if any(str(o).startswith("unavailable") for o in out):
+        pytest.skip(f"no NVLink multicast binding on this machine ({out[0]})")
     want = "hier" if split and "GPUBRIDGE_SWITCH_FLAT" not in split else "flat"
     assert set(out) == {want}, out
