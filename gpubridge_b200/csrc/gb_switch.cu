@@ -218,6 +218,53 @@ allreduce_switch_kernel(GbTeam tm, GbSwitch sw, SwArgs a) {
     if (threadIdx.x == 0) sw.bseq[b] = seq;
 }
 
+// In place, for a tensor that lives IN the group's switch memory at the same offset on every
+// rank (Fabric.switch_empty hands such tensors out; a trainer keeps its gradients there): no
+// staging and no copies.  Block b owns tiles b, b + B, ... of the tensor; it meets the same
+// block of every rank once (every rank's values are written), reduces its rank's share of
+// each of its tiles in the switch and multicasts the result back in place, and meets them
+// again (every share is written) before anybody reads.  One group, flat order.
+template <typename T>
+__global__ void __launch_bounds__(SW_THREADS)
+allreduce_switch_inplace_kernel(GbTeam tm, GbSwitch sw, SwArgs a, size_t offset) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = SwVec<T>::N;
+    constexpr int U = 4;
+    const int b = (int)blockIdx.x, B = (int)gridDim.x;
+    unsigned seq = gb_ld_volatile(sw.bseq + b);
+    if (!sw_block_sync(tm, sw, b, ++seq)) return;
+    char* everyone = sw.mc + offset;
+    for (int i = b; i < a.ntiles; i += B) {
+        const size_t t0 = (size_t)i * a.tile;
+        const size_t len = a.nbytes - t0 < a.tile ? a.nbytes - t0 : a.tile;      // a multiple of 16
+        const size_t nvec = len >> 4;
+        const size_t share = (nvec + (size_t)sw.owners - 1) / (size_t)sw.owners;
+        const size_t lo = (size_t)sw.group_pos * share;
+        const size_t hi = lo + share < nvec ? lo + share : nvec;
+        for (size_t v0 = lo + threadIdx.x; v0 < hi; v0 += (size_t)U * SW_THREADS) {
+            SwVec<T> w[U];
+            #pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t v = v0 + (size_t)u * SW_THREADS;
+                if (v < hi) w[u].u = SwitchSum<T>::load(everyone + t0 + (v << 4));
+            }
+            #pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t v = v0 + (size_t)u * SW_THREADS;
+                if (v >= hi) continue;
+                if (a.divide > 0) {
+                    #pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        w[u].e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(w[u].e[j]), a.divide));
+                }
+                switch_store(everyone + t0 + (v << 4), w[u].u);
+            }
+        }
+    }
+    if (!sw_block_sync(tm, sw, b, ++seq)) return;
+    if (threadIdx.x == 0) sw.bseq[b] = seq;
+}
+
 template <typename T>
 cudaError_t launch_switch(const GbTeam& tm, const GbSwitch& sw, const SwArgs& a, int grid,
                           cudaStream_t stream) {
@@ -283,6 +330,38 @@ extern "C" int gb_switch_all_reduce(const GbTeam* team, const GbSwitch* sw, cons
     if (dtype == 0) return (int)launch_switch<float>(*team, *sw, a, plan.grid, stream);
     if (dtype == 1) return (int)launch_switch<__nv_bfloat16>(*team, *sw, a, plan.grid, stream);
     return (int)launch_switch<__half>(*team, *sw, a, plan.grid, stream);
+}
+
+// The same sum for a tensor inside the group's switch memory, `offset` bytes from its start on
+// every rank (a multiple of 16, like the tensor's size in bytes): in place, nothing copied.
+// Returns a cudaError_t, -2 for a type the switch cannot add, -1 for a range outside the memory
+// or a group that is an island of several (the in-place form is flat).
+extern "C" int gb_switch_all_reduce_inplace(const GbTeam* team, const GbSwitch* sw, size_t offset,
+                                            size_t n, int dtype, int divide, int max_blocks,
+                                            cudaStream_t stream) {
+    if (dtype < 0 || dtype > 2) return -2;
+    const size_t nbytes = n * (dtype == 0 ? 4 : 2);
+    if (sw->hier || (offset & 15) || (nbytes & 15) || nbytes == 0 || offset + nbytes > sw->bytes) return -1;
+    if (max_blocks > GB_SWITCH_MAX_BLOCKS) max_blocks = GB_SWITCH_MAX_BLOCKS;
+    if (max_blocks < 1) return -1;
+    SwArgs a;
+    a.in = nullptr;
+    a.out = nullptr;
+    a.nbytes = nbytes;
+    a.divide = divide;
+    // tiles of at least 16 KiB per owner-share sweep, at most one per block and step
+    const size_t unit = 16 * (size_t)sw->owners * 8;
+    size_t tile = ((nbytes + max_blocks - 1) / max_blocks + unit - 1) / unit * unit;
+    const size_t floor_tile = (65536 + unit - 1) / unit * unit;
+    if (tile < floor_tile) tile = floor_tile;
+    if (tile > (4u << 20)) tile = (4u << 20) / unit * unit;
+    a.tile = tile;
+    a.ntiles = (int)((nbytes + tile - 1) / tile);
+    const int grid = a.ntiles < max_blocks ? a.ntiles : max_blocks;
+    if (dtype == 0) allreduce_switch_inplace_kernel<float><<<grid, SW_THREADS, 0, stream>>>(*team, *sw, a, offset);
+    else if (dtype == 1) allreduce_switch_inplace_kernel<__nv_bfloat16><<<grid, SW_THREADS, 0, stream>>>(*team, *sw, a, offset);
+    else allreduce_switch_inplace_kernel<__half><<<grid, SW_THREADS, 0, stream>>>(*team, *sw, a, offset);
+    return (int)cudaGetLastError();
 }
 
 extern "C" size_t gb_sizeof_switch() { return sizeof(GbSwitch); }

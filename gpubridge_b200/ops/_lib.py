@@ -182,6 +182,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_switch_plan.argtypes = [ctypes.POINTER(GbSwitch), i, sz, i, ctypes.POINTER(GbSwitchPlan)]
     L.gb_switch_all_reduce.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), vp, vp, sz,
                                        i, i, i, vp]
+    L.gb_switch_all_reduce_inplace.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), sz, sz,
+                                               i, i, i, vp]
     L.gb_engine_set_switch.argtypes = [vp, ctypes.POINTER(GbSwitch), ctypes.POINTER(GbSwitch), sz]
     L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
     L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]

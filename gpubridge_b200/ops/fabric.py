@@ -144,6 +144,7 @@ class Fabric:
         # switch memory bound by the fabric itself (enable_switch): the team's group, this
         # rank's island's group, and the structures the kernels take
         self._switch_groups: list = []
+        self._heaps: list = []          # (first address, bytes, GbSwitch) of tensors handed out by switch_empty
         self.switch_error = ""          # why enable_switch() said no, for reports
         self.sw_team = self.sw_island = None
         self._bseq = 0
@@ -355,6 +356,43 @@ class Fabric:
             self._engine_switch()
         return True
 
+    def switch_empty(self, numel: int, dtype: torch.dtype = torch.float32,
+                     timeout: timedelta | None = None) -> torch.Tensor | None:
+        """A zeroed tensor that lives in switch memory of its own - bound to a multicast object
+        of the whole team, at the same offset on every rank - so that all-reduces of it (or of
+        16-byte aligned slices of it) run IN PLACE in the switch, with no staging copies: what
+        a trainer wants for its gradient buffer.  Collective over the team: every rank calls
+        it with the same size.  None - on every rank alike - when the team has no switch
+        memory (``enable_switch`` said no, or ``GPUBRIDGE_NVLS=0``).  The memory lives until the
+        fabric closes."""
+        from gpubridge_b200.ops import switch as _switch
+        if self.sw_team is None or self._closed:
+            return None
+        esize = torch.empty(0, dtype=dtype).element_size()
+        nbytes = max(_align_up(numel * esize, 4096), 2 * MIB)
+        try:
+            group = _switch.build_group(self.lib, self._store, f"{self._key}/switch/heap{len(self._heaps)}",
+                                        self.rank, list(range(self.world)), self.device.index, nbytes,
+                                        timeout)
+        except _switch.SwitchUnavailable as failure:
+            self.switch_error = f"switch_empty: {failure}"
+            return None
+        self._switch_groups.append(group)
+        sw = _switch.describe(group, self.rank, self.world, False, self.off_swflags, 0, 0, self._bseq)
+        self._heaps.append((group.local, group.bytes, sw))
+        whole = torch.as_tensor(_Foreign(group.local, group.bytes), device=self.device)
+        return whole[:numel * esize].view(dtype)
+
+    def _heap_of(self, tensor: torch.Tensor):
+        """``(switch, offset)`` when ``tensor`` lies in memory handed out by :meth:`switch_empty`
+        and can be reduced in place there, else None."""
+        address, nbytes = tensor.data_ptr(), tensor.nbytes
+        for first, size, sw in self._heaps:
+            if first <= address and address + nbytes <= first + size:
+                offset = address - first
+                return (sw, offset) if offset % 16 == 0 and nbytes % 16 == 0 else None
+        return None
+
     def _engine_switch(self) -> None:
         self.lib.gb_engine_set_switch(
             self._engine, ctypes.byref(self.sw_team) if self.sw_team is not None else None,
@@ -477,7 +515,16 @@ class Fabric:
                 args = _lib.GbArgs()
                 args.inp, args.out, args.n = tensor.data_ptr(), out.data_ptr(), n
                 args.divide = int(divide or 0)
-                if switch is not None:
+                home = self._heap_of(tensor) if switch is not None and out is tensor and self._heaps else None
+                if home is not None:
+                    limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))
+                    code = self.lib.gb_switch_all_reduce_inplace(
+                        ctypes.byref(self.team), ctypes.byref(home[0]), home[1], n,
+                        _lib.DTYPES[tensor.dtype], args.divide, limit,
+                        torch.cuda.current_stream(self.device).cuda_stream)
+                    _lib.check(code, "gb_switch_all_reduce_inplace")
+                    self.launches += 1
+                elif switch is not None:
                     limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))
                     code = self.lib.gb_switch_all_reduce(
                         ctypes.byref(self.team), ctypes.byref(switch), args.inp, args.out, n,
@@ -709,7 +756,16 @@ class Fabric:
         self._residuals.clear()
 
 
+class _Foreign:
+    """Device memory that torch did not allocate, as ``torch.as_tensor`` takes it."""
+
+    def __init__(self, address: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "strides": None,
+                                         "data": (address, False), "version": 3}
+
+
 def _release_switch_of(fabric) -> None:
+    fabric._heaps = []
     for group in reversed(fabric._switch_groups):
         group.release(fabric.lib)
     fabric._switch_groups = []

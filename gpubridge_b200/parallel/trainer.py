@@ -73,7 +73,15 @@ class DataParallelTrainer:
         sizes = [-(-p.numel() // 64) * 64 for p in params]          # 256-byte aligned views
         total = sum(sizes)
         self.flat_param = torch.zeros(total, dtype=torch.float32, device=self.device)
-        self.flat_grad = torch.zeros(total, dtype=torch.float32, device=self.device)
+        # The gradients live in the team's switch memory when it has some: bucket all-reduces
+        # then run in place inside the NVSwitch (no staging copies, a handful of SMs), which is
+        # what lets them hide under backward.  Collective: every rank builds its trainer.
+        in_switch = None
+        if self.fabric is not None and self.world > 1 and hasattr(self.fabric, "switch_empty"):
+            in_switch = self.fabric.switch_empty(total, torch.float32)
+        self.grads_in_switch = in_switch is not None
+        self.flat_grad = in_switch if in_switch is not None else \
+            torch.zeros(total, dtype=torch.float32, device=self.device)
         # reverse registration order: the order backward fills the gradients in
         offset, self._spans = 0, []
         for p, size in zip(reversed(params), reversed(sizes)):

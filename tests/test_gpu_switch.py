@@ -37,6 +37,15 @@ def test_team_of_one_round_trips_through_switch_memory():
                 assert torch.equal(out, x), ("sum", dtype, n)
                 fabric.all_reduce(x, divide=4, out=out)
                 assert torch.equal(out.float(), (x.float() / 4).to(dtype).float()), ("avg", dtype, n)
+        # a tensor that lives in switch memory is reduced in place, slices of it too
+        home = fabric.switch_empty((3 << 20) + 64)
+        assert home is not None and float(home.abs().sum()) == 0.0
+        home.copy_(rank_tensor(2, home.numel()).to(dev))
+        keep = home.clone()
+        fabric.all_reduce(home)
+        fabric.all_reduce(home[1024:1024 + 65536], divide=2)
+        keep[1024:1024 + 65536] /= 2
+        assert torch.equal(home, keep)
         # an unaligned view: the copy stages fall back to narrower accesses
         base = rank_tensor(5, 100_003).to(dev)
         view = base[1:]
@@ -70,6 +79,21 @@ def _sums(rank, topology):
         t = rank_tensor(rank, n).to(dev)
         gb.all_reduce(t, gb.ReduceOp.AVG)
         assert torch.equal(t.cpu(), expected_sum(world, n) / world), ("avg", n)
+    # in place, inside switch memory (what the trainer does with its gradient buffer)
+    n = (5 << 20) + 256
+    home = fabric.switch_empty(n)
+    assert home is not None, fabric.switch_error
+    for lo, hi in ((0, n), (4096, 4096 + (1 << 20)), (n - 512, n)):
+        home.copy_(rank_tensor(rank, n).to(dev))
+        gb.barrier()                                  # nobody reduces while a peer still fills its copy
+        torch.cuda.synchronize()
+        topology.fabric.all_reduce(home[lo:hi], divide=world)
+        torch.cuda.current_stream().wait_stream(topology.fabric.comm_stream)
+        want = rank_tensor(rank, n)
+        want[lo:hi] = expected_sum(world, n)[lo:hi] / world
+        assert torch.equal(home.cpu(), want), ("in place", lo, hi)
+        gb.barrier()
+        torch.cuda.synchronize()
     # random values: every rank must hold the same bits, close to the fp64 sum
     g = torch.Generator().manual_seed(99 + rank)
     t = torch.randn((2 << 20) + 11, generator=g).to(dev)
