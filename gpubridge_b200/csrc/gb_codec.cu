@@ -111,14 +111,16 @@ quantize_fp8_kernel(const T* __restrict__ x, float* __restrict__ residual,
         #pragma unroll
         for (int w = 0; w < EPL / 4; ++w) words[w] = 0u;
         #pragma unroll
-        for (int j = 0; j < EPL; ++j) {
-            unsigned code = 0u;
-            if (i0 + j < n) {
-                code = fin[j] ? gb_e4m3_encode(__fmul_rn(v[j], mult)) : 0x7Fu;
-                float sent = __fmul_rn(gb_e4m3_decode(code), scale);
-                r[j] = fin[j] ? __fsub_rn(v[j], sent) : 0.0f;
-            }
-            words[j / 4] |= code << (8 * (j & 3));
+        for (int j = 0; j < EPL; j += 2) {                  // the hardware converts in pairs
+            unsigned pair = gb_e4m3_encode2(__fmul_rn(v[j], mult), __fmul_rn(v[j + 1], mult));
+            if (!fin[j]) pair = (pair & 0xFF00u) | 0x7Fu;
+            if (!fin[j + 1]) pair = (pair & 0x00FFu) | 0x7F00u;
+            if (i0 + j >= n) pair &= 0xFF00u;
+            if (i0 + j + 1 >= n) pair &= 0x00FFu;
+            const float2 sent = gb_e4m3_decode2(pair);
+            if (i0 + j < n) r[j] = fin[j] ? __fsub_rn(v[j], __fmul_rn(sent.x, scale)) : 0.0f;
+            if (i0 + j + 1 < n) r[j + 1] = fin[j + 1] ? __fsub_rn(v[j + 1], __fmul_rn(sent.y, scale)) : 0.0f;
+            words[j / 4] |= pair << (8 * (j & 3));
         }
         if (rvec) {
             #pragma unroll
@@ -163,43 +165,80 @@ quantize_bf16_kernel(const T* __restrict__ x, float* __restrict__ residual,
     }
 }
 
+// Sixteen results as vector stores (whole, aligned runs) or one by one (the tail).
+template <typename T>
+__device__ __forceinline__ void store_run16(T* out, size_t i0, size_t n, const float (&acc)[16]) {
+    const bool whole = i0 + 16 <= n;
+    if (whole && ((uintptr_t)(out + i0) & 15u) == 0 && sizeof(T) <= 4) {
+        if (sizeof(T) == 4) {
+            #pragma unroll
+            for (int g = 0; g < 4; ++g)
+                *(reinterpret_cast<float4*>(out + i0) + g) =
+                    make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+        } else {
+            union { uint4 u[2]; T e[16]; } w;
+            #pragma unroll
+            for (int j = 0; j < 16; ++j) from_float<T>(&w.e[j], acc[j]);
+            *(reinterpret_cast<uint4*>(out + i0)) = w.u[0];
+            *(reinterpret_cast<uint4*>(out + i0) + 1) = w.u[1];
+        }
+        return;
+    }
+    #pragma unroll
+    for (int j = 0; j < 16; ++j)
+        if (i0 + j < n) from_float<T>(out + i0 + j, acc[j]);
+}
+
+// Sixteen consecutive values per thread and step: a block's scale is read once per member,
+// codes arrive as four 4-byte words (rows are only 4-byte aligned) that are all in flight at
+// once, pairs of codes are decoded by one hardware conversion, and results leave as 16-byte
+// vectors.  Members are added one after the other, each sum flushed, as the oracle does.
 template <typename T, int CODEC>
 __global__ void __launch_bounds__(256)
 dequantize_kernel(const unsigned char* __restrict__ payloads, size_t row_bytes, int members,
                   T* __restrict__ out, size_t n) {
     constexpr int BS = GbBlock<CODEC>::size;
     const size_t nb = (n + BS - 1) / BS;
-    const size_t ngroups = (n + 3) / 4;
+    const size_t n4 = (n + 3) & ~(size_t)3;                  // code bytes present in a row (padded)
+    const size_t ngroups = (n + 15) / 16;
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t nth = (size_t)gridDim.x * blockDim.x;
     for (size_t g = tid; g < ngroups; g += nth) {
-        const size_t i0 = 4 * g;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const size_t i0 = 16 * g;
+        float acc[16];
+        #pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
         for (int m = 0; m < members; ++m) {
             const unsigned char* row = payloads + (size_t)m * row_bytes;
             if (CODEC == GB_C_BF16) {
-                // two 4-byte words: rows are only 4-byte aligned, and the second word lies
-                // past the row when fewer than three values remain
-                const unsigned w0 = *reinterpret_cast<const unsigned*>(row + 2 * i0);
-                const unsigned w1 = (i0 + 2 < n)
-                    ? *reinterpret_cast<const unsigned*>(row + 2 * i0 + 4) : 0u;
-                unsigned c[4] = {w0 & 0xFFFFu, w0 >> 16, w1 & 0xFFFFu, w1 >> 16};
+                // 16-bit codes: eight 4-byte words; the row holds (n + 1) / 2 of them
+                const size_t words = (n + 1) / 2;
+                unsigned w[8];
                 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    acc[j] = gb_flush(__fadd_rn(acc[j], gb_from_bf16_bits(c[j])));
+                for (int q = 0; q < 8; ++q)
+                    w[q] = (i0 / 2 + q < words) ? __ldg(reinterpret_cast<const unsigned*>(row) + i0 / 2 + q) : 0u;
+                #pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    acc[2 * q] = gb_flush(__fadd_rn(acc[2 * q], gb_from_bf16_bits(w[q] & 0xFFFFu)));
+                    acc[2 * q + 1] = gb_flush(__fadd_rn(acc[2 * q + 1], gb_from_bf16_bits(w[q] >> 16)));
+                }
             } else {
-                const float scale = reinterpret_cast<const float*>(row)[i0 / BS];
-                const unsigned w = *reinterpret_cast<const unsigned*>(row + 4 * nb + i0);
+                const float scale = __ldg(reinterpret_cast<const float*>(row) + i0 / BS);
+                const unsigned* codes = reinterpret_cast<const unsigned*>(row + 4 * nb + i0);
+                unsigned w[4];
                 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float d = __fmul_rn(gb_e4m3_decode((w >> (8 * j)) & 0xFFu), scale);
-                    acc[j] = gb_flush(__fadd_rn(acc[j], d));
+                for (int q = 0; q < 4; ++q) w[q] = (i0 + 4 * q < n4) ? __ldg(codes + q) : 0u;
+                #pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 lo = gb_e4m3_decode2(w[q] & 0xFFFFu), hi = gb_e4m3_decode2(w[q] >> 16);
+                    acc[4 * q] = gb_flush(__fadd_rn(acc[4 * q], __fmul_rn(lo.x, scale)));
+                    acc[4 * q + 1] = gb_flush(__fadd_rn(acc[4 * q + 1], __fmul_rn(lo.y, scale)));
+                    acc[4 * q + 2] = gb_flush(__fadd_rn(acc[4 * q + 2], __fmul_rn(hi.x, scale)));
+                    acc[4 * q + 3] = gb_flush(__fadd_rn(acc[4 * q + 3], __fmul_rn(hi.y, scale)));
                 }
             }
         }
-        #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (i0 + j < n) from_float<T>(out + i0 + j, acc[j]);
+        store_run16<T>(out, i0, n, acc);
     }
 }
 
@@ -233,7 +272,7 @@ cudaError_t dequantize_t(int mode, int fmt, const unsigned char* payloads, size_
                          int members, void* out, size_t n, cudaStream_t stream) {
     if (n == 0) return cudaSuccess;
     T* op = static_cast<T*>(out);
-    const int grid = grid_for((n + 3) / 4, 256 * 2);
+    const int grid = grid_for((n + 15) / 16, 256);
     if (mode == 0)
         dequantize_kernel<T, GB_C_BF16><<<grid, 256, 0, stream>>>(payloads, row_bytes, members, op, n);
     else if (fmt == 0)

@@ -53,6 +53,21 @@ __device__ __forceinline__ unsigned gb_e4m3_encode(float q) {
     return (unsigned)__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3);
 }
 
+// Two codes at once (the hardware converts e4m3 in pairs): the low byte of `pair` first.
+__device__ __forceinline__ float2 gb_e4m3_decode2(unsigned pair) {
+    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(pair & 0xFFFFu), __NV_E4M3);
+    float2 f = __half22float2(__half2(h));
+    if ((pair & 0x7Fu) == 0x7Fu) f.x = __uint_as_float(0x7FC00000u);
+    if ((pair & 0x7F00u) == 0x7F00u) f.y = __uint_as_float(0x7FC00000u);
+    return f;
+}
+// Two values to two codes (low byte = a); a zero of either sign encodes as +0.
+__device__ __forceinline__ unsigned gb_e4m3_encode2(float a, float b) {
+    a = a == 0.0f ? 0.0f : a;
+    b = b == 0.0f ? 0.0f : b;
+    return (unsigned)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+}
+
 // Scale of one block from its largest magnitude: (stored scale, multiplier).
 template <int CODEC>
 __device__ __forceinline__ void gb_block_scale(float amax, float& scale, float& mult) {
