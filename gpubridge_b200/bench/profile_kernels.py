@@ -1,6 +1,6 @@
 """Run one of the library's kernels a few times on one GPU, for ``ncu`` to capture.
 
-    python -m gpubridge_b200.bench.profile_kernels hier|oneshot|xent|adamw|quantize|dequantize|gemm
+    python -m gpubridge_b200.bench.profile_kernels hier|oneshot|switch|xent|adamw|layernorm|quantize|dequantize|gemm
 
 Sizes are small enough for a full-set capture to finish in about a minute but larger than
 the 126 MB L2, so DRAM figures mean something.  ``hier`` and ``oneshot`` run one rank's side
@@ -16,7 +16,7 @@ import torch
 def main(which: str) -> int:
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    if which in ("hier", "oneshot", "gemm"):
+    if which in ("hier", "oneshot", "gemm", "switch"):
         from gpubridge_b200.ops import fabric as F
         team = F.create_single(device)
         if which == "gemm":
@@ -28,6 +28,15 @@ def main(which: str) -> int:
                 op(x, w)
             torch.cuda.synchronize()
             op.check()
+        elif which == "switch":
+            # one rank's side of the in-switch all-reduce: a multicast object of one GPU
+            if not team.enable_switch():
+                team.close()
+                raise SystemExit(f"switch: no multicast memory here ({team.switch_error})")
+            t = torch.randn(48 << 20, device=device)              # 192 MiB: larger than L2
+            for _ in range(4):
+                team.all_reduce(t)
+            torch.cuda.synchronize()
         else:
             n = (32 << 20) if which == "hier" else (64 << 10)
             t = torch.randn(n, device=device)
@@ -50,6 +59,14 @@ def main(which: str) -> int:
         opt = FlatAdamW(p, g)
         for _ in range(4):
             opt.step(zero_grad=False)
+        torch.cuda.synchronize()
+    elif which == "layernorm":
+        from gpubridge_b200.ops.layernorm import FusedLayerNorm
+        norm = FusedLayerNorm(768).to(device)
+        x = torch.randn(65536, 768, device=device, requires_grad=True)       # 192 MiB
+        for _ in range(3):
+            y = norm(x)
+            y.backward(torch.ones_like(y))
         torch.cuda.synchronize()
     elif which in ("quantize", "dequantize"):
         from gpubridge_b200 import compression as C

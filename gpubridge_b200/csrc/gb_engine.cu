@@ -31,6 +31,7 @@ struct Engine {
     GbSwitch sw_team{}, sw_island{};
     bool has_team = false, has_island = false;
     size_t sw_min_bytes = 0;
+    int sw_min_ranks = 3;
     std::atomic<unsigned long long> launches{0};
 };
 
@@ -138,7 +139,8 @@ extern "C" int gb_engine_prepare_all_reduce(void* engine, const void* in, void* 
     a.n = n;
     a.divide = divide > 0 ? divide : 0;
     L->family = 0;
-    if ((e.has_island || e.has_team) && op == 0 && dtype <= 2 && nbytes >= e.sw_min_bytes) {
+    if ((e.has_island || e.has_team) && op == 0 && dtype <= 2 && nbytes >= e.sw_min_bytes &&
+        e.team.world >= e.sw_min_ranks) {
         L->family = 2;
         L->kind = e.has_island ? 1 : 0;
         L->grid = e.c.max_blocks;
@@ -244,13 +246,14 @@ extern "C" int gb_engine_prepare_broadcast(void* engine, void* buffer, size_t nb
 // hierarchical one (either may be null); SUM / AVG of floats of at least min_bytes then go
 // through the switch.  The island group wins when both are given.
 extern "C" void gb_engine_set_switch(void* engine, const GbSwitch* team, const GbSwitch* island,
-                                     size_t min_bytes) {
+                                     size_t min_bytes, int min_ranks) {
     Engine& e = *static_cast<Engine*>(engine);
     e.has_team = team != nullptr;
     e.has_island = island != nullptr;
     if (team) e.sw_team = *team;
     if (island) e.sw_island = *island;
     e.sw_min_bytes = min_bytes;
+    e.sw_min_ranks = min_ranks;
 }
 
 namespace {

@@ -45,7 +45,8 @@ int gb_plan_hier(size_t n, int esize, int k, int m_max, int n_islands, size_t le
 void* gb_engine_create(const GbTeam* team, const GbEngineConfig* config);
 void gb_engine_destroy(void* engine);
 struct GbSwitch;
-void gb_engine_set_switch(void* engine, const GbSwitch* team, const GbSwitch* island, size_t min_bytes);
+void gb_engine_set_switch(void* engine, const GbSwitch* team, const GbSwitch* island, size_t min_bytes,
+                          int min_ranks);
 unsigned long long gb_engine_launches(void* engine);
 size_t gb_sizeof_engine_config();
 size_t gb_sizeof_launch();

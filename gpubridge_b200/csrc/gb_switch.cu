@@ -37,13 +37,17 @@
 //
 // Every wait is bounded (gb_wait_flag: spin limit + globaltimer deadline); on expiry the block
 // records the failure in the team's status block, raises the abort word and returns.
+#include <stdlib.h>
+
 #include "gb_common.cuh"
 #include "gb_switch.h"
 
 namespace {
 
-constexpr int SW_THREADS = 512;
-constexpr int SW_HALF = SW_THREADS / 2;
+// Two launch shapes: 512 threads (one block per SM) with four switch requests in flight per
+// thread, or 256 threads (two blocks per SM, so one block's barrier wait is covered by the
+// other's work) with eight.  GPUBRIDGE_SWITCH_SHAPE picks; the default is the second.
+constexpr int SW_MAX_THREADS = 512;
 
 template <typename T> struct SwVec {
     static constexpr int N = 16 / sizeof(T);
@@ -116,13 +120,13 @@ __device__ __forceinline__ void sw_zero(char* base, size_t lo, size_t hi, int ti
     for (size_t x = lo + tid; x < hi; x += nth) base[x] = 0;
 }
 
-template <typename T, bool HIER>
-__global__ void __launch_bounds__(SW_THREADS)
+template <typename T, bool HIER, int SW_THREADS, int U>
+__global__ void __launch_bounds__(SW_THREADS, SW_MAX_THREADS / SW_THREADS)
 allreduce_switch_kernel(GbTeam tm, GbSwitch sw, SwArgs a) {
     typedef typename GbAcc<T>::type A;
     constexpr int V = SwVec<T>::N;
     constexpr int DEPTH = HIER ? 4 : 3;
-    constexpr int U = 4;                                       // switch requests in flight per thread
+    constexpr int SW_HALF = SW_THREADS / 2;                    // U: switch requests in flight per thread
     const int b = (int)blockIdx.x, B = (int)gridDim.x;
     const int mine = (a.ntiles - b + B - 1) / B;               // tiles b, b + B, ... (b < ntiles)
     const int steps = mine + DEPTH - 1;
@@ -214,8 +218,12 @@ allreduce_switch_kernel(GbTeam tm, GbSwitch sw, SwArgs a) {
             }
         }
         if (i + 1 < steps && !sw_block_sync(tm, sw, b, ++seq)) return;
+        if (b == 0 && threadIdx.x == 0 && i == 0) tm.ctrl->stamps[0] = gb_now();   // first tiles staged
     }
-    if (threadIdx.x == 0) sw.bseq[b] = seq;
+    if (threadIdx.x == 0) {
+        sw.bseq[b] = seq;
+        if (b == 0) tm.ctrl->stamps[1] = gb_now();             // block 0's last tile is out
+    }
 }
 
 // In place, for a tensor that lives IN the group's switch memory at the same offset on every
@@ -224,12 +232,11 @@ allreduce_switch_kernel(GbTeam tm, GbSwitch sw, SwArgs a) {
 // block of every rank once (every rank's values are written), reduces its rank's share of
 // each of its tiles in the switch and multicasts the result back in place, and meets them
 // again (every share is written) before anybody reads.  One group, flat order.
-template <typename T>
-__global__ void __launch_bounds__(SW_THREADS)
+template <typename T, int SW_THREADS, int U>
+__global__ void __launch_bounds__(SW_THREADS, SW_MAX_THREADS / SW_THREADS)
 allreduce_switch_inplace_kernel(GbTeam tm, GbSwitch sw, SwArgs a, size_t offset) {
     typedef typename GbAcc<T>::type A;
     constexpr int V = SwVec<T>::N;
-    constexpr int U = 4;
     const int b = (int)blockIdx.x, B = (int)gridDim.x;
     unsigned seq = gb_ld_volatile(sw.bseq + b);
     if (!sw_block_sync(tm, sw, b, ++seq)) return;
@@ -265,11 +272,29 @@ allreduce_switch_inplace_kernel(GbTeam tm, GbSwitch sw, SwArgs a, size_t offset)
     if (threadIdx.x == 0) sw.bseq[b] = seq;
 }
 
+int switch_shape() {
+    static const int shape = []{ const char* v = getenv("GPUBRIDGE_SWITCH_SHAPE"); return v ? atoi(v) : 1; }();
+    return shape;
+}
+
 template <typename T>
 cudaError_t launch_switch(const GbTeam& tm, const GbSwitch& sw, const SwArgs& a, int grid,
                           cudaStream_t stream) {
-    if (sw.hier) allreduce_switch_kernel<T, true><<<grid, SW_THREADS, 0, stream>>>(tm, sw, a);
-    else allreduce_switch_kernel<T, false><<<grid, SW_THREADS, 0, stream>>>(tm, sw, a);
+    if (switch_shape() == 0) {
+        if (sw.hier) allreduce_switch_kernel<T, true, 512, 4><<<grid, 512, 0, stream>>>(tm, sw, a);
+        else allreduce_switch_kernel<T, false, 512, 4><<<grid, 512, 0, stream>>>(tm, sw, a);
+    } else {
+        if (sw.hier) allreduce_switch_kernel<T, true, 256, 8><<<grid, 256, 0, stream>>>(tm, sw, a);
+        else allreduce_switch_kernel<T, false, 256, 8><<<grid, 256, 0, stream>>>(tm, sw, a);
+    }
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_inplace(const GbTeam& tm, const GbSwitch& sw, const SwArgs& a, size_t offset, int grid,
+                           cudaStream_t stream) {
+    if (switch_shape() == 0) allreduce_switch_inplace_kernel<T, 512, 4><<<grid, 512, 0, stream>>>(tm, sw, a, offset);
+    else allreduce_switch_inplace_kernel<T, 256, 8><<<grid, 256, 0, stream>>>(tm, sw, a, offset);
     return cudaGetLastError();
 }
 
@@ -282,6 +307,7 @@ extern "C" int gb_switch_plan(const GbSwitch* sw, int n_islands, size_t nbytes, 
                               GbSwitchPlan* plan) {
     const int depth = sw->hier ? 4 : 3;
     const size_t unit = 16 * (size_t)sw->owners * 8;           // stripes of whole 128-byte lines
+    if (switch_shape() != 0) max_blocks *= 2;                  // half-size blocks, two per SM
     if (max_blocks > GB_SWITCH_MAX_BLOCKS) max_blocks = GB_SWITCH_MAX_BLOCKS;
     if (max_blocks < 1 || nbytes == 0) return -1;
     const size_t floor_tile = (8192 + unit - 1) / unit * unit;
@@ -342,6 +368,7 @@ extern "C" int gb_switch_all_reduce_inplace(const GbTeam* team, const GbSwitch* 
     if (dtype < 0 || dtype > 2) return -2;
     const size_t nbytes = n * (dtype == 0 ? 4 : 2);
     if (sw->hier || (offset & 15) || (nbytes & 15) || nbytes == 0 || offset + nbytes > sw->bytes) return -1;
+    if (switch_shape() != 0) max_blocks *= 2;
     if (max_blocks > GB_SWITCH_MAX_BLOCKS) max_blocks = GB_SWITCH_MAX_BLOCKS;
     if (max_blocks < 1) return -1;
     SwArgs a;
@@ -358,10 +385,9 @@ extern "C" int gb_switch_all_reduce_inplace(const GbTeam* team, const GbSwitch* 
     a.tile = tile;
     a.ntiles = (int)((nbytes + tile - 1) / tile);
     const int grid = a.ntiles < max_blocks ? a.ntiles : max_blocks;
-    if (dtype == 0) allreduce_switch_inplace_kernel<float><<<grid, SW_THREADS, 0, stream>>>(*team, *sw, a, offset);
-    else if (dtype == 1) allreduce_switch_inplace_kernel<__nv_bfloat16><<<grid, SW_THREADS, 0, stream>>>(*team, *sw, a, offset);
-    else allreduce_switch_inplace_kernel<__half><<<grid, SW_THREADS, 0, stream>>>(*team, *sw, a, offset);
-    return (int)cudaGetLastError();
+    if (dtype == 0) return (int)launch_inplace<float>(*team, *sw, a, offset, grid, stream);
+    if (dtype == 1) return (int)launch_inplace<__nv_bfloat16>(*team, *sw, a, offset, grid, stream);
+    return (int)launch_inplace<__half>(*team, *sw, a, offset, grid, stream);
 }
 
 extern "C" size_t gb_sizeof_switch() { return sizeof(GbSwitch); }

@@ -2,7 +2,7 @@
 #pragma once
 #include <cstddef>
 
-#define GB_SWITCH_MAX_BLOCKS 160                 // rows of the per-block flag area
+#define GB_SWITCH_MAX_BLOCKS 320                 // rows of the per-block flag area
 #define GB_SWITCH_MAX_TILE (256u << 10)          // bytes of one tile of the pipeline
 
 // One rank's view of the switch memory of its group (the team, or its island).

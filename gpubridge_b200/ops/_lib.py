@@ -18,7 +18,7 @@ from gpubridge_b200.ops import _build
 
 MAX_RANKS = 16
 STATUS_WORDS = 8
-SWITCH_MAX_BLOCKS = 160
+SWITCH_MAX_BLOCKS = 320
 
 DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.float64: 3,
           torch.int8: 4, torch.uint8: 5, torch.int32: 6, torch.int64: 7}
@@ -184,7 +184,7 @@ def _declare(L: ctypes.CDLL) -> None:
                                        i, i, i, vp]
     L.gb_switch_all_reduce_inplace.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), sz, sz,
                                                i, i, i, vp]
-    L.gb_engine_set_switch.argtypes = [vp, ctypes.POINTER(GbSwitch), ctypes.POINTER(GbSwitch), sz]
+    L.gb_engine_set_switch.argtypes = [vp, ctypes.POINTER(GbSwitch), ctypes.POINTER(GbSwitch), sz, i]
     L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
     L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]
 

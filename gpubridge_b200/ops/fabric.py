@@ -150,6 +150,9 @@ class Fabric:
         self._bseq = 0
         self.switch_min_bytes = _config.size_setting("GPUBRIDGE_SWITCH_MIN_BYTES", 64 << 10, multiple=1)
         self.switch_flat = os.environ.get("GPUBRIDGE_SWITCH_FLAT", "0") == "1"
+        # Through the switch a GPU moves (n + 1) / n of the tensor, over peer memory 2 (n - 1) / n:
+        # less from four ranks on, more at two (measured at two: the peer-memory kernels win).
+        self.switch_min_ranks = int(os.environ.get("GPUBRIDGE_SWITCH_MIN_RANKS", "3"))
         self.nvls_reducers = int(os.environ.get("GPUBRIDGE_NVLS_REDUCERS", "48"))
         self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "32"))
         self.overlap_blocks = int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
@@ -397,12 +400,13 @@ class Fabric:
         self.lib.gb_engine_set_switch(
             self._engine, ctypes.byref(self.sw_team) if self.sw_team is not None else None,
             ctypes.byref(self.sw_island) if self.sw_island is not None else None,
-            self.switch_min_bytes)
+            self.switch_min_bytes, self.switch_min_ranks)
 
     def _switch_for(self, tensor: torch.Tensor, op: str, compression) -> "_lib.GbSwitch | None":
         """The switch group an all-reduce of ``tensor`` takes, or None for the peer-memory kernels."""
         if (self.sw_team is None or op != "sum" or compression is not None
-                or tensor.dtype not in NVLS_DTYPES or tensor.nbytes < self.switch_min_bytes):
+                or tensor.dtype not in NVLS_DTYPES or tensor.nbytes < self.switch_min_bytes
+                or self.world < self.switch_min_ranks):
             return None
         return self.sw_island if self.sw_island is not None else self.sw_team
 
@@ -515,7 +519,10 @@ class Fabric:
                 args = _lib.GbArgs()
                 args.inp, args.out, args.n = tensor.data_ptr(), out.data_ptr(), n
                 args.divide = int(divide or 0)
-                home = self._heap_of(tensor) if switch is not None and out is tensor and self._heaps else None
+                home = None
+                if (self._heaps and out is tensor and op == "sum" and compression is None
+                        and tensor.dtype in NVLS_DTYPES and mode == "auto" and algo == "auto"):
+                    home = self._heap_of(tensor)       # in place at any team size: nothing is staged
                 if home is not None:
                     limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))
                     code = self.lib.gb_switch_all_reduce_inplace(
@@ -532,6 +539,8 @@ class Fabric:
                         torch.cuda.current_stream(self.device).cuda_stream)
                     _lib.check(code, "gb_switch_all_reduce")
                     self.launches += 1
+                    if _observe.watching() and not torch.cuda.is_current_stream_capturing():
+                        self._report_switch_phase()
                 elif oneshot:
                     args.off_a, args.len_a = self.off_oneshot, self.len_oneshot
                     self._launch_reduce(0, tensor.dtype, op, 0, args, self._grid(nbytes, 32))
@@ -601,6 +610,18 @@ class Fabric:
         done = torch.cuda.Event(enable_timing=True)
         done.record(stream)
         _observe.device_phases_later(names, stamps, done)
+
+    def _report_switch_phase(self) -> None:
+        """The in-switch all-reduce as observers see it: one phase, from the moment block 0 has
+        met its peers for the first time (every rank's first tiles are staged) to the moment its
+        last tile is out - ``globaltimer`` values the kernel leaves, copied behind it."""
+        stamps = torch.zeros(8, dtype=torch.int64).pin_memory()
+        stream = torch.cuda.current_stream(self.device)
+        _lib.check(self.lib.gb_copy_to_host(stamps.data_ptr(), self.ctrl + 32, 64, stream.cuda_stream),
+                   "cudaMemcpyAsync (switch timestamps)")
+        done = torch.cuda.Event(enable_timing=True)
+        done.record(stream)
+        _observe.device_phases_later(["switch-reduce"], stamps, done)
 
     def _residual(self, tensor: torch.Tensor, geometry: tuple) -> torch.Tensor:
         """Error feedback of this rank's stripes of ``tensor``: found by the buffer's address,

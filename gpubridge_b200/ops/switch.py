@@ -28,7 +28,7 @@ from datetime import timedelta
 from gpubridge_b200.ops import _lib
 
 MIB = 1 << 20
-DEFAULT_BYTES = 128 * MIB
+DEFAULT_BYTES = 256 * MIB
 FLAG_AREA = _lib.SWITCH_MAX_BLOCKS * _lib.MAX_RANKS * 4           # one row of flags per block index
 
 

@@ -31,7 +31,7 @@ def fake_fabric(sizes, ws_bytes=384 << 20, **over):
     f._caps, f._closed, f._engine, f.launches = threading.local(), False, None, 0
     f.sw_team = f.sw_island = None
     f._heaps = []
-    f.switch_min_bytes, f.switch_flat = 64 << 10, False
+    f.switch_min_bytes, f.switch_flat, f.switch_min_ranks = 64 << 10, False, 3
     f.layout = types.SimpleNamespace(index=lambda r: r)
     for name, value in over.items():
         setattr(f, name, value)

@@ -188,7 +188,8 @@ def _observed(rank, topology):
         gb.remove_observer(watcher)
     record = records[-1]
     names = [p.name for p in record.phases]
-    assert names and all(n.startswith(("pipeline-step", "island-reduce", "bridge-reduce")) for n in names)
+    assert names and all(n.startswith(("pipeline-step", "island-reduce", "bridge-reduce", "switch-reduce"))
+                         for n in names)
     spans = [p.elapsed_ms() for p in record.phases]
     assert all(p.start.ready() and p.end.ready() for p in record.phases)
     assert all(0 <= ms < 100 for ms in spans) and sum(spans) > 0, spans

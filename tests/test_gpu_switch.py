@@ -25,7 +25,7 @@ def test_team_of_one_round_trips_through_switch_memory():
     try:
         if not fabric.enable_switch():
             pytest.skip(f"this GPU or driver cannot bind multicast memory: {fabric.switch_error}")
-        fabric.switch_min_bytes = 0                       # every size takes the switch path
+        fabric.switch_min_bytes, fabric.switch_min_ranks = 0, 1     # every size takes the switch path
         before = fabric.launches
         for dtype in (torch.float32, torch.bfloat16, torch.float16):
             for n in SIZES + ((40 << 20) + 1,):
@@ -66,7 +66,7 @@ def _sums(rank, topology):
     if fabric is None or fabric.sw_team is None:
         return "unavailable: " + (fabric.switch_error if fabric is not None else "no fabric")
     dev, world = topology.device, topology.world_size
-    fabric.switch_min_bytes = 0
+    fabric.switch_min_bytes, fabric.switch_min_ranks = 0, 2
     if fabric._engine:
         fabric._engine_switch()
     before = fabric.launches
@@ -119,5 +119,8 @@ def test_sums_through_the_switch(tmp_path, split):
     out = run_ranks(gpu_ranks(WORLD), _sums, tmp_path, env={"GPUBRIDGE_NVLS": "1", **split}, timeout=240)
     if any(str(o).startswith("unavailable") for o in out):
         pytest.skip(f"no NVLink multicast binding on this machine ({out[0]})")
-    want = "hier" if split and "GPUBRIDGE_SWITCH_FLAT" not in split else "flat"
+    # islands of one GPU cannot have a multicast object of their own: the team's is used
+    sizes = {"GPUBRIDGE_SPLIT_TEST": [WORLD // 2], "GPUBRIDGE_ISLANDS": [3, 5] if "3,5" in split.values() else [2]}
+    smallest = min(sizes[next(iter(split))]) if split else WORLD
+    want = "hier" if split and "GPUBRIDGE_SWITCH_FLAT" not in split and smallest >= 2 else "flat"
     assert set(out) == {want}, out
