@@ -229,6 +229,7 @@ def run_ours(args) -> dict:
     if topology is not None:
         result["config"]["in_switch_reduction"] = bool(
             topology.fabric is not None and topology.fabric.sw_team is not None)
+        result["config"]["gradients_in_switch_memory"] = bool(getattr(trainer, "grads_in_switch", False))
     if not args.no_hook_arm:
         del trainer, e2e_steps
         torch.cuda.empty_cache()

@@ -1,0 +1,174 @@
+"""The RDMA-style tagged endpoint (``csrc/gb_rdma.cpp``) from Python, and ``bridge="verbs"``.
+
+The endpoint is the host-staged bridge for links made of reliable connected queue pairs
+(InfiniBand / RoCE): eager messages through pre-posted, credit-controlled receive slots,
+large ones by rendezvous - the receiver registers the user's buffer (an LRU cache of
+registrations), grants it, the sender writes into it and says when it is done.  It is written
+against a provider interface.  Two things can be had here:
+
+* :class:`MockFabric` / :class:`Endpoint`: the whole protocol over an in-process fabric that can
+  be told to fail, drop, delay or corrupt an operation or kill a member - how the protocol,
+  its flow control and its failure rule are tested, without a NIC;
+* the name ``bridge="verbs"``.  A provider over libibverbs needs headers this image does not
+  have, so none is built, and resolving the name raises - on every rank alike, before anything
+  is connected - an error that says so: the behaviour the reference has where its shim cannot
+  be built (src/gpubridge/verbs/__init__.py:63-64).
+
+Settings an endpoint takes (0 keeps the default): ``eager_max`` (16 KiB; larger messages go by
+rendezvous), ``data_slots`` / ``ctrl_slots`` (16 / 8 receive slots per peer and class),
+``max_write`` (1 MiB per one-sided write), ``unexpected_max`` (64 MiB of early eager messages),
+``mr_cache`` (64 registrations).  :meth:`Endpoint.telemetry` returns the counters as a dict.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import time
+
+
+FAULTS = {"error": 1, "drop": 2, "delay": 3, "corrupt": 4, "kill": 5}
+OPCODES = {"send": 0, "write": 2, "any": -1}
+
+
+def _library():
+    from gpubridge_b200.ops import _lib
+    L = _lib.lib()
+    if not getattr(L, "_rdma_declared", False):
+        vp, i, u64, u = ctypes.c_void_p, ctypes.c_int, ctypes.c_ulonglong, ctypes.c_uint
+        L.gb_rdma_mock_fabric.restype = vp
+        L.gb_rdma_mock_fabric.argtypes = [i]
+        L.gb_rdma_mock_free.restype = None
+        L.gb_rdma_mock_free.argtypes = [vp]
+        L.gb_rdma_mock_inject.restype = None
+        L.gb_rdma_mock_inject.argtypes = [vp, i, i, i, i, ctypes.c_long, i]
+        L.gb_rdma_mock_stats.restype = ctypes.c_char_p
+        L.gb_rdma_mock_stats.argtypes = [vp]
+        L.gb_rdma_create.restype = vp
+        L.gb_rdma_create.argtypes = [vp, i, u, u, u, u, u64, u]
+        for name in ("gb_rdma_send", "gb_rdma_recv"):
+            getattr(L, name).restype = ctypes.c_long
+            getattr(L, name).argtypes = [vp, i, vp, u64, u64]
+        L.gb_rdma_wait.argtypes = [vp, ctypes.POINTER(ctypes.c_long), i, ctypes.c_double]
+        L.gb_rdma_all_reduce.argtypes = [vp, vp, u64, i, i, u64, u64, ctypes.c_double]
+        L.gb_rdma_broadcast.argtypes = [vp, vp, u64, i, u64, u64, ctypes.c_double]
+        L.gb_rdma_invalidate.argtypes = [vp, vp, u64]
+        for name in ("gb_rdma_last_error", "gb_rdma_telemetry"):
+            getattr(L, name).restype = ctypes.c_char_p
+            getattr(L, name).argtypes = [vp]
+        L.gb_rdma_abort.restype = L.gb_rdma_close.restype = None
+        L.gb_rdma_abort.argtypes = L.gb_rdma_close.argtypes = [vp]
+        L._rdma_declared = True
+    return L
+
+
+def protocol_version() -> int:
+    return _library().gb_rdma_protocol()
+
+
+class MockFabric:
+    """``members`` connected members inside this process."""
+
+    def __init__(self, members: int) -> None:
+        self.lib, self.members = _library(), members
+        self.handle = self.lib.gb_rdma_mock_fabric(members)
+        if not self.handle:
+            raise ValueError("a mock fabric has 1 to 64 members")
+        self.endpoints: list[Endpoint] = []
+
+    def endpoint(self, index: int, **settings) -> "Endpoint":
+        made = Endpoint(self, index, **settings)
+        self.endpoints.append(made)
+        return made
+
+    def inject(self, fault: str, *, src: int = -1, dst: int = -1, on: str = "any", nth: int = 1,
+               milliseconds: int = 0) -> None:
+        """The ``nth`` next operation of kind ``on`` (send / write / any) from ``src`` to ``dst``
+        (-1: any) will ``error``, ``drop``, ``delay``, be ``corrupt`` or ``kill`` its destination."""
+        self.lib.gb_rdma_mock_inject(self.handle, FAULTS[fault], src, dst, OPCODES[on], nth, milliseconds)
+
+    def stats(self) -> dict:
+        return json.loads(self.lib.gb_rdma_mock_stats(self.handle).decode())
+
+    def close(self) -> None:
+        for endpoint in self.endpoints:
+            endpoint.close()
+        handle, self.handle = self.handle, None
+        if handle:
+            self.lib.gb_rdma_mock_free(handle)
+
+
+class Endpoint:
+    """One member's endpoint; the worker interface :class:`~gpubridge_b200.tagged.TaggedBridge`
+    expects (``all_reduce`` / ``broadcast`` / ``abort`` / ``close``) plus send / recv / wait."""
+
+    def __init__(self, fabric: MockFabric, index: int, *, eager_max: int = 0, data_slots: int = 0,
+                 ctrl_slots: int = 0, max_write: int = 0, unexpected_max: int = 0, mr_cache: int = 0) -> None:
+        self.lib, self.index = fabric.lib, index
+        self.handle = self.lib.gb_rdma_create(fabric.handle, index, eager_max, data_slots, ctrl_slots,
+                                              max_write, unexpected_max, mr_cache)
+        if not self.handle:
+            raise ValueError(f"member {index} is not on this fabric")
+
+    def _error(self) -> str:
+        return self.lib.gb_rdma_last_error(self.handle).decode()
+
+    def send(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
+        op = self.lib.gb_rdma_send(self.handle, peer, ptr, nbytes, tag)
+        if op < 0:
+            raise RuntimeError(f"rdma endpoint: {self._error() or 'no such peer'}")
+        return op
+
+    def recv(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
+        op = self.lib.gb_rdma_recv(self.handle, peer, ptr, nbytes, tag)
+        if op < 0:
+            raise RuntimeError(f"rdma endpoint: {self._error() or 'no such peer'}")
+        return op
+
+    def wait(self, ids: list[int], deadline: float) -> None:
+        array = (ctypes.c_long * len(ids))(*ids)
+        if self.lib.gb_rdma_wait(self.handle, array, len(ids), max(0.001, deadline - time.monotonic())) != 0:
+            raise RuntimeError(f"rdma endpoint: {self._error()}")
+
+    def all_reduce(self, ptr: int, count: int, dtype: int, op: int, chunk_elems: int, seq: int,
+                   deadline: float) -> None:
+        left = max(0.001, deadline - time.monotonic())
+        if self.lib.gb_rdma_all_reduce(self.handle, ptr, count, dtype, op, chunk_elems, seq, left) != 0:
+            raise RuntimeError(f"rdma endpoint: {self._error()}")
+
+    def broadcast(self, ptr: int, nbytes: int, root: int, chunk_bytes: int, seq: int, deadline: float) -> None:
+        left = max(0.001, deadline - time.monotonic())
+        if self.lib.gb_rdma_broadcast(self.handle, ptr, nbytes, root, chunk_bytes, seq, left) != 0:
+            raise RuntimeError(f"rdma endpoint: {self._error()}")
+
+    def invalidate(self, ptr: int, nbytes: int) -> int:
+        """Forget cached registrations overlapping the range (call before freeing memory that
+        large messages were received into); returns how many were dropped."""
+        return self.lib.gb_rdma_invalidate(self.handle, ptr, nbytes)
+
+    def telemetry(self) -> dict:
+        return json.loads(self.lib.gb_rdma_telemetry(self.handle).decode())
+
+    def abort(self) -> None:
+        if self.handle:
+            self.lib.gb_rdma_abort(self.handle)
+
+    def close(self) -> None:
+        handle, self.handle = self.handle, None
+        if handle:
+            self.lib.gb_rdma_close(handle)
+
+
+def provider_available() -> bool:
+    """Whether a provider over real queue pairs is part of this build (none is: see the module
+    text)."""
+    return False
+
+
+def load(name: str) -> None:
+    """Called when ``bridge="verbs"`` is resolved: says, on every rank alike and before anything
+    is connected, why the bridge cannot be used here."""
+    raise ImportError(
+        "the verbs bridge needs a provider over libibverbs, and this build has none: the "
+        "infiniband/verbs.h header is not installed here.  The endpoint itself - wire protocol, "
+        "flow control, registration cache, failure rule - is built and runs over an in-process "
+        "fabric (gpubridge_b200.rdma.MockFabric); across machines use bridge='multitcp' or 'gloo'")

@@ -132,7 +132,7 @@ _TRANSPORTS: dict[str, type[BridgeTransport]] = {
     GlooTransport.name: GlooTransport, NvlinkTransport.name: NvlinkTransport}
 #: Opt-in transports, imported at first use.
 _BUILT_IN = {"multitcp": "gpubridge_b200.multitcp", "ucx": "gpubridge_b200.unavailable",
-             "verbs": "gpubridge_b200.unavailable"}
+             "verbs": "gpubridge_b200.rdma"}
 
 
 def _load_built_in(name: str) -> None:
