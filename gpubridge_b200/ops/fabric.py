@@ -355,9 +355,56 @@ class Fabric:
         if island_group is not None:
             self.sw_island = _switch.describe(island_group, me, self.k, True, self.off_swflags,
                                               self.off_swbridge, self.len_swbridge, self._bseq)
+        # Commissioning: one small all-reduce with a known answer through every group, with a
+        # short wait limit.  A group that answers wrongly or not at all is given up by every
+        # rank alike, and the team stays on the peer-memory kernels.
+        if self.world > 1:
+            flat_ok = everyone("check-team", self._commission(self.sw_team))
+            hier_ok = self.sw_island is None or everyone("check-islands", self._commission(self.sw_island))
+            if not hier_ok:
+                self.switch_error = "the island groups failed their first sum; using the team's group"
+                self.sw_island = None
+                # the failed kernel left the per-block barrier numbers out of step: start them over
+                self.lib.gb_memset_async(self._bseq, 0, 4096, None)
+                self.lib.gb_memset_async(self.ws[self.rank] + self.off_swflags, 0,
+                                         _lib.SWITCH_MAX_BLOCKS * _lib.MAX_RANKS * 4, None)
+                self.lib.gb_device_synchronize()
+                everyone("flags-reset", True)
+            if not flat_ok:
+                self.switch_error = "the team's group failed its first sum; in-switch reduction is off"
+                self._release_switch()
+                return False
         if self._engine:
             self._engine_switch()
         return True
+
+    def _commission(self, switch) -> bool:
+        """One all-reduce of 96 Ki integer-valued floats through ``switch``; True when this rank
+        got the exact sum in time.  Never raises; clears a timeout it caused."""
+        n, world = 96 << 10, self.world
+        ramp = (torch.arange(n, device=self.device) % 13).float()
+        mine, out = ramp + self.rank, torch.full((n,), -1.0, device=self.device)
+        want = ramp * world + world * (world - 1) / 2
+        saved = self.team.timeout_ns
+        self.team.timeout_ns = 3_000_000_000
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+                code = self.lib.gb_switch_all_reduce(ctypes.byref(self.team), ctypes.byref(switch),
+                                                     mine.data_ptr(), out.data_ptr(), n, 0, 0, 16,
+                                                     self.comm_stream.cuda_stream)
+            self.comm_stream.synchronize()
+            good = code == 0 and self._status[0] == 0 and bool(torch.equal(out, want))
+        except Exception:  # noqa: BLE001 - any failure means "not this way"
+            good = False
+        finally:
+            self.team.timeout_ns = saved
+        if self._status[0] != 0:                     # a wait ran out: forget it, the group is dropped
+            for word in range(_lib.STATUS_WORDS):
+                self._status[word] = 0
+            self.lib.gb_memset_async(self.ctrl + 16, 0, 4, None)
+            self.lib.gb_device_synchronize()
+        return good
 
     def switch_empty(self, numel: int, dtype: torch.dtype = torch.float32,
                      timeout: timedelta | None = None) -> torch.Tensor | None:
@@ -382,8 +429,34 @@ class Fabric:
             return None
         self._switch_groups.append(group)
         sw = _switch.describe(group, self.rank, self.world, False, self.off_swflags, 0, 0, self._bseq)
-        self._heaps.append((group.local, group.bytes, sw))
         whole = torch.as_tensor(_Foreign(group.local, group.bytes), device=self.device)
+        # commissioning, as for the staged groups: a known sum in place, then zeros again
+        n, world = min(96 << 10, group.bytes // 4), self.world
+        probe = whole[:4 * n].view(torch.float32)
+        ramp = (torch.arange(n, device=self.device) % 13).float()
+        probe.copy_(ramp + self.rank)
+        saved, self.team.timeout_ns = self.team.timeout_ns, 3_000_000_000
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+            code = self.lib.gb_switch_all_reduce_inplace(ctypes.byref(self.team), ctypes.byref(sw), 0, n, 0, 0,
+                                                         16, self.comm_stream.cuda_stream)
+        self.comm_stream.synchronize()
+        self.team.timeout_ns = saved
+        good = code == 0 and self._status[0] == 0 and bool(
+            torch.equal(probe, ramp * world + world * (world - 1) / 2))
+        verdicts = _switch.exchange_among(self._store, f"{self._key}/switch/heap{len(self._heaps)}/check",
+                                          self.rank, list(range(self.world)), "1" if good else "0", timeout)
+        probe.zero_()
+        torch.cuda.synchronize(self.device)
+        if "0" in verdicts:
+            self.switch_error = "switch_empty: the first in-place sum failed"
+            if self._status[0] != 0:
+                for word in range(_lib.STATUS_WORDS):
+                    self._status[word] = 0
+                self.lib.gb_memset_async(self.ctrl + 16, 0, 4, None)
+                self.lib.gb_device_synchronize()
+            return None
+        self._heaps.append((group.local, group.bytes, sw))
         return whole[:numel * esize].view(dtype)
 
     def _heap_of(self, tensor: torch.Tensor):
