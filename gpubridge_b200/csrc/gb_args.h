@@ -19,4 +19,6 @@ struct GbArgs {
     float* residual;          // error feedback of this rank's stripes (compressed all-reduce)
     char* sym;                // NVLS all-reduce: this rank's multicast-bound buffer ...
     char* mc;                 // ... and the multicast address of the same buffer on every rank
+    size_t keep_lo, keep_n;   // hierarchical all-reduce: the element range this rank wants in `out`
+                              // (out[0] is element keep_lo); keep_n = 0: the whole tensor
 };

@@ -524,10 +524,18 @@ allreduce_hier_kernel(GbTeam tm, GbArgs a) {
                 const int j = (tm.my_pos + dj) % a.k;
                 const int own = tm.order[tm.island_off[tm.my_island] + j];
                 const size_t valid = stripe_valid(a, c0, j);
-                if (valid)
-                    gb_copy_bytes(L, out + c0 + (size_t)j * a.stripe,
-                                  tm.ws[own] + off_c + (size_t)((i - depth) & 1) * a.len_c,
-                                  valid * sizeof(T), true);
+                if (!valid) continue;
+                // A reduce-scatter keeps only its own slice of the result: the part of this
+                // stripe inside [keep_lo, keep_lo + keep_n) goes to out[element - keep_lo].
+                const size_t s0 = c0 + (size_t)j * a.stripe;
+                const size_t keep_hi = a.keep_n ? a.keep_lo + a.keep_n : a.n;
+                const size_t lo = s0 > a.keep_lo ? s0 : a.keep_lo;
+                const size_t hi = s0 + valid < keep_hi ? s0 + valid : keep_hi;
+                if (lo < hi)
+                    gb_copy_bytes(L, out + (lo - a.keep_lo),
+                                  tm.ws[own] + off_c + (size_t)((i - depth) & 1) * a.len_c
+                                  + (lo - s0) * sizeof(T),
+                                  (hi - lo) * sizeof(T), true);
             }
         }
         if (i + 1 < iters &&

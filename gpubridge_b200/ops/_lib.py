@@ -44,7 +44,8 @@ class GbArgs(ctypes.Structure):
                 ("role_b", ctypes.c_int), ("pad", ctypes.c_int),
                 ("off_a", ctypes.c_size_t), ("off_b", ctypes.c_size_t), ("off_c", ctypes.c_size_t),
                 ("len_a", ctypes.c_size_t), ("len_b", ctypes.c_size_t), ("len_c", ctypes.c_size_t),
-                ("residual", ctypes.c_void_p), ("sym", ctypes.c_void_p), ("mc", ctypes.c_void_p)]
+                ("residual", ctypes.c_void_p), ("sym", ctypes.c_void_p), ("mc", ctypes.c_void_p),
+                ("keep_lo", ctypes.c_size_t), ("keep_n", ctypes.c_size_t)]
 
 
 class GbSwitch(ctypes.Structure):

@@ -568,8 +568,11 @@ class Fabric:
     # -- collectives -----------------------------------------------------------------------------------
     def all_reduce(self, tensor: torch.Tensor, op: str = "sum", divide: int | None = None,
                    mode: str = "auto", compression=None, chunk_bytes: int | None = None,
-                   out: torch.Tensor | None = None) -> None:
-        """Reduce ``tensor`` over the team into ``out`` (default: in place).
+                   out: torch.Tensor | None = None, keep: tuple[int, int] | None = None) -> None:
+        """Reduce ``tensor`` over the team into ``out`` (default: in place).  ``keep = (first
+        element, count)``: only that range of the result is wanted, and ``out`` holds just it (the
+        compressed reduce-scatter: the register-load hierarchical kernel, whose last step then
+        fetches one slice instead of the whole tensor).
 
         ``mode``: ``auto`` (one-shot up to 256 KiB, else hierarchical), ``striped``
         (hierarchical always), ``chunked`` (hierarchical, ``chunk_bytes`` per pipeline step).
@@ -583,17 +586,20 @@ class Fabric:
         if compression is not None and (op != "sum" or self.n_islands < 2):
             compression = None
         algo = self.algo
-        oneshot = (compression is None and nbytes <= self.oneshot_slot
+        oneshot = (compression is None and nbytes <= self.oneshot_slot and keep is None
                    and ((mode == "auto" and algo in ("auto", "one-shot")) or algo == "one-shot"))
-        switch = self._switch_for(tensor, op, compression) if mode == "auto" and algo == "auto" else None
+        switch = (self._switch_for(tensor, op, compression)
+                  if mode == "auto" and algo == "auto" and keep is None else None)
         current = self._begin()
         try:
             with torch.cuda.stream(self.comm_stream):
                 args = _lib.GbArgs()
                 args.inp, args.out, args.n = tensor.data_ptr(), out.data_ptr(), n
                 args.divide = int(divide or 0)
+                if keep is not None:
+                    args.keep_lo, args.keep_n = keep
                 home = None
-                if (self._heaps and out is tensor and op == "sum" and compression is None
+                if (self._heaps and out is tensor and op == "sum" and compression is None and keep is None
                         and tensor.dtype in NVLS_DTYPES and mode == "auto" and algo == "auto"):
                     home = self._heap_of(tensor)       # in place at any team size: nothing is staged
                 if home is not None:
@@ -638,7 +644,7 @@ class Fabric:
 
     def _hier(self, tensor, args, op, compression, chunk_bytes) -> None:
         aligned = (args.inp | args.out) % 16 == 0
-        ring = bool(self.ring) and compression is None and aligned
+        ring = bool(self.ring) and compression is None and aligned and not args.keep_n
         # more than two islands: the bridge can move 2 (I - 1) / I stripes per owner instead of
         # I - 1 (GPUBRIDGE_BRIDGE_TWO_SHOT=1; the phased ring kernel only)
         two_shot = (ring and self.ring == "phased" and self.n_islands >= 3 and self.two_shot)
@@ -721,10 +727,11 @@ class Fabric:
         if n == 0:
             return
         if compression is not None and self.n_islands > 1:
-            # compressed bridge leg: the hierarchical all-reduce into scratch, then the slice
-            scratch = torch.empty_like(tensor)
-            self.all_reduce(tensor, "sum", divide, "striped", compression, out=scratch)
-            output.view(-1).copy_(scratch.view(self.world, -1)[self.rank])
+            # compressed bridge leg: the hierarchical all-reduce - island sums, quantised, across
+            # the bridge, added in island order - whose last step fetches this rank's slice only,
+            # straight into `output`: the same bits as the compressed all-reduce's slice
+            self.all_reduce(tensor, "sum", divide, "striped", compression, out=output,
+                            keep=(self.rank * n, n))
             return
         esize = tensor.element_size()
         # a float input may leave as bf16 and a bf16 input as float: the cast is the sum's one

@@ -239,6 +239,34 @@ def _compressed(rank, topology, mode, fmt):
     return True
 
 
+def _compressed_scatter(rank, topology, mode, fmt):
+    """The compressed reduce-scatter is the compressed all-reduce's slice, bit for bit: the same
+    island sums, the same quantisation, the same order - only the last step fetches one slice."""
+    import gpubridge_b200 as gb
+    dev, world = topology.device, topology.world_size
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (256, 70_001, (1 << 20) + 3):
+            g = torch.Generator().manual_seed(77 + rank)
+            full = torch.randn(world * n, generator=g).to(dtype).to(dev)
+            whole = full.clone()
+            gb.reset_error_feedback()
+            gb.all_reduce(whole)
+            out = torch.full((n,), 9, dtype=dtype, device=dev)
+            gb.reset_error_feedback()
+            gb.reduce_scatter_tensor(out, full)
+            want = whole.view(world, n)[rank]
+            assert torch.equal(out.view(torch.uint8), want.contiguous().view(torch.uint8)), (mode, dtype, n)
+    return True
+
+
+@needs_two
+@pytest.mark.parametrize("mode,fmt", [("fp8", "b200"), ("bf16", "ref")])
+def test_compressed_reduce_scatter_is_the_all_reduces_slice(tmp_path, mode, fmt):
+    env = {"GPUBRIDGE_SPLIT_TEST": "half", "GPUBRIDGE_BRIDGE_COMPRESSION": mode,
+           "GPUBRIDGE_CODEC_FORMAT": fmt}
+    run_ranks(gpu_ranks(WORLD), _compressed_scatter, tmp_path, mode, fmt, env=env, timeout=240)
+
+
 @needs_two
 @pytest.mark.parametrize("mode,fmt", [("fp8", "ref"), ("fp8", "b200"), ("bf16", "ref")])
 def test_compressed_bridge_matches_codec(tmp_path, mode, fmt):
