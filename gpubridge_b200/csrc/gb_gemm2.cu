@@ -405,26 +405,30 @@ extern "C" int gb_allgather_gemm_pair(const GbTeam* team, void* y, const void* x
     a.group = tile_group;
     a.probe = ingest_probe;
     const size_t smem = SMEM_TILES + 256 + 1024;
-    // GPUBRIDGE_GEMM_WIDE: 1 = 256 x 512 tiles with one accumulator, 0 = 256 x 256 with two
-    static const int wide = []{ const char* v = getenv("GPUBRIDGE_GEMM_WIDE"); return v ? atoi(v) : 1; }();
+    // 256 x 512 tiles have one accumulator, so their epilogue does not overlap the next tile's
+    // products: they pay off for a long K only (measured: 8192 wins, 2048 and 4096 lose).
+    // GPUBRIDGE_GEMM_WIDE: 1 = always wide, 0 = always 256 x 256 with two accumulators, unset = by K
+    static const int wide_choice = []{ const char* v = getenv("GPUBRIDGE_GEMM_WIDE"); return v ? atoi(v) : -1; }();
+    const int wide = wide_choice >= 0 ? (wide_choice != 0) : (K >= 8192 && N % 512 == 0);
     typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, GbTeam, Gemm2Args);
     Kernel kernel = wide ? allgather_gemm_pair_kernel<2> : allgather_gemm_pair_kernel<1>;
-    static bool configured = false;
-    static int resident_clusters = 0;
+    static bool configured[2] = {false, false};
+    static int resident[2] = {0, 0};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    if (!configured) {
+    if (!configured[wide]) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
         // every CTA must be resident at once (pairs wait for the communication CTAs' flags)
         cudaLaunchConfig_t probe = {};
         probe.gridDim = dim3(2); probe.blockDim = dim3(THREADS2); probe.dynamicSmemBytes = smem;
         probe.attrs = attr; probe.numAttrs = 1;
-        err = cudaOccupancyMaxActiveClusters(&resident_clusters, kernel, &probe);
+        err = cudaOccupancyMaxActiveClusters(&resident[wide], kernel, &probe);
         if (err != cudaSuccess) return (int)err;
-        configured = true;
+        configured[wide] = true;
     }
+    const int resident_clusters = resident[wide];
     if (gemm_blocks + comm_blocks > 2 * resident_clusters) gemm_blocks = 2 * resident_clusters - comm_blocks;
     if (gemm_blocks < 2) return (int)cudaErrorInvalidConfiguration;
     a.gemm_blocks = gemm_blocks;
