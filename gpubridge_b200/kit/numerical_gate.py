@@ -62,8 +62,8 @@ def flat(tensors) -> torch.Tensor:
 
 
 def compare(actual, expected, *, exact=False, update=False) -> dict:
-    a = torch.as_tensor(actual, dtype=torch.float64).reshape(-1)
-    b = torch.as_tensor(expected, dtype=torch.float64).reshape(-1)
+    a = torch.as_tensor(actual).detach().cpu().to(torch.float64).reshape(-1)
+    b = torch.as_tensor(expected).detach().cpu().to(torch.float64).reshape(-1)
     if a.shape != b.shape:
         return {"violations": max(a.numel(), b.numel()), "shape_mismatch": True}
     delta = (a - b).abs()
