@@ -151,3 +151,67 @@ def test_plan_function_matches_and_refuses_small_workspaces():
         assert rc == 0
         assert (out.channels, out.grid, out.stripe, out.nchunks, out.len_a, out.len_b, out.len_c) == (
             want.channels, want.grid, want.stripe, want.nchunks, want.len_a, want.len_b, want.len_c)
+
+
+class _RecordingLib:
+    """The native library with the in-switch launch recorded instead of made (it needs a GPU)."""
+
+    def __init__(self, real, seen) -> None:
+        self._real, self._seen = real, seen
+
+    def __getattr__(self, name):
+        return getattr(self._real, name)
+
+    def gb_switch_all_reduce(self, team, switch, inp, out, n, dtype, divide, limit, stream):
+        self._seen.append((2, switch._obj.hier, limit, inp, out, n, divide))
+        return 0
+
+
+@pytest.mark.parametrize("sizes", [(2,), (3,), (4,), (8,), (4, 4), (2, 2, 2, 2), (1, 1, 1)])
+@pytest.mark.parametrize("islands_have_groups", [False, True])
+def test_the_in_switch_all_reduce_is_chosen_alike(sizes, islands_have_groups, monkeypatch):
+    """Both planners send the same tensors through the switch (sum of floats, from the size and
+    team size on), with the same group (the island's when there is one) and the same grid limit;
+    everything else takes the kernels it took before."""
+    monkeypatch.setattr(torch.cuda, "current_stream",
+                        lambda device=None: types.SimpleNamespace(cuda_stream=0))
+    monkeypatch.setattr(torch.cuda, "stream", lambda s: __import__("contextlib").nullcontext())
+    rng = random.Random(len(sizes) * 131 + sum(sizes))
+    f = fake_fabric(sizes)
+    f.lib = _RecordingLib(f.lib, f.seen)
+    f.sw_team = _lib.GbSwitch()
+    f.sw_team.hier = 0
+    if islands_have_groups and len(sizes) > 1:
+        f.sw_island = _lib.GbSwitch()
+        f.sw_island.hier = 1
+    engine = f.engine()
+    assert engine
+    through_switch = 0
+    for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int64):
+        esize = torch.empty(0, dtype=dtype).element_size()
+        for op in ("sum", "max"):
+            for _ in range(10):
+                n = rng.choice([256, (64 << 10) // esize - 1, (64 << 10) // esize, 1 << 20,
+                                rng.randrange(1, 1 << 24)])
+                inp = 1 << 30
+                fake = types.SimpleNamespace(
+                    numel=lambda n=n: n, nbytes=n * esize, dtype=dtype, data_ptr=lambda: inp,
+                    element_size=lambda esize=esize: esize)
+                cap = rng.choice([0, 32, 7])
+                divide = f.world if op == "sum" else 0
+                with f.grid_cap(cap or None):
+                    f.all_reduce(fake, op, divide=divide)
+                launch = _lib.GbLaunch()
+                rc = f.lib.gb_engine_prepare_all_reduce(engine, inp, inp, n, _lib.DTYPES[dtype],
+                                                        _lib.OPS[op], divide, cap, ctypes.byref(launch))
+                assert rc == 0
+                seen = f.seen.pop()
+                if seen[0] == 2:
+                    through_switch += 1
+                    _, hier, limit, _, _, count, div = seen
+                    assert (launch.family, launch.kind, launch.grid) == (2, hier, limit)
+                    assert (launch.args.n, launch.args.divide) == (count, div)
+                else:
+                    same(launch, seen)
+    assert (through_switch > 0) == (sum(sizes) >= f.switch_min_ranks)
+    f.lib.gb_engine_destroy(engine)
