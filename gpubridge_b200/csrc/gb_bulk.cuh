@@ -89,10 +89,15 @@ __device__ __forceinline__ void gb_ring_issue(const GbRing& R, unsigned use, con
     const unsigned dst = gb_smem_u32(R.buf + (size_t)stage * GB_RING_STAGE_BYTES);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
                  :: "r"(bar), "r"(len * (unsigned)m) : "memory");
-    for (int p = 0; p < m; ++p)
+    for (int p = 0; p < m; ++p) {
+        const char* from = src + (size_t)p * src_stride + off;
+#ifdef GB_BOUNDS
+        from = gb_bounds_source(from, len);
+#endif
         asm volatile(
             "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-            :: "r"(dst + (unsigned)p * pitch), "l"(src + (size_t)p * src_stride + off), "r"(len), "r"(bar) : "memory");
+            :: "r"(dst + (unsigned)p * pitch), "l"(from), "r"(len), "r"(bar) : "memory");
+    }
 }
 
 // The tile size a transfer of `bytes` per source is cut into when `nblocks` blocks share it

@@ -1394,3 +1394,5 @@ extern "C" size_t gb_payload_bytes(int codec, int elem_size, size_t stripe) {
     const size_t bs = codec == GB_C_FP8_B200 ? 128 : 256;
     return (stripe + 4 * (stripe / bs) + 15) / 16 * 16;
 }
+
+GB_BOUNDS_HOST(collectives)

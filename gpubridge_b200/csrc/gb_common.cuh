@@ -71,7 +71,52 @@ __device__ __forceinline__ unsigned int gb_ld_volatile(const unsigned int* p) {
 // Mode 1 (the default) is a weak load that bypasses L1 (ld.global.cg): L2 is a memory-side
 // cache, so it is coherent for local memory and not involved for a peer's; the barrier that
 // precedes every such load orders it.  Mode 0 is a system-scope relaxed load.
+#ifdef GB_BOUNDS
+// The checked build (-DGB_BOUNDS, a library of its own): every 16-byte access of the fabric
+// kernels and every source of a bulk copy is compared with the address ranges the host allowed
+// for the launch (the workspaces of all ranks as mapped here, switch memory, the caller's
+// tensors).  An access outside them is not made: the first one is recorded (address, kind,
+// block, thread) and counted, a load returns zeros, a bulk copy reads the start of the first
+// range instead.  One table per translation unit; the host fills and reads each through the
+// functions GB_BOUNDS_HOST defines.  An empty table allows everything.
+#define GB_BOUNDS_RANGES 40
+struct GbBoundsTable {
+    unsigned long long lo[GB_BOUNDS_RANGES], hi[GB_BOUNDS_RANGES];
+    int n, pad;
+    unsigned long long first[4];    // address, kind (0 load, 1 store, 2 bulk copy), block, thread
+    unsigned int violations, pad2;
+};
+static __device__ GbBoundsTable gb_bounds_table;
+__device__ __forceinline__ bool gb_in_bounds(const void* p, unsigned bytes, unsigned kind) {
+    const unsigned long long a = reinterpret_cast<unsigned long long>(p);
+    const int n = gb_bounds_table.n;
+    if (n == 0) return true;
+    for (int i = 0; i < n; ++i)
+        if (a >= gb_bounds_table.lo[i] && a + bytes <= gb_bounds_table.hi[i]) return true;
+    if (atomicAdd(&gb_bounds_table.violations, 1u) == 0) {
+        gb_bounds_table.first[0] = a; gb_bounds_table.first[1] = kind;
+        gb_bounds_table.first[2] = blockIdx.x; gb_bounds_table.first[3] = threadIdx.x;
+    }
+    return false;
+}
+__device__ __forceinline__ const char* gb_bounds_source(const char* p, unsigned bytes) {
+    return gb_in_bounds(p, bytes, 2) ? p : reinterpret_cast<const char*>(gb_bounds_table.lo[0]);
+}
+#define GB_BOUNDS_HOST(unit)                                                                    \
+    extern "C" int gb_bounds_set_##unit(const GbBoundsTable* t) {                               \
+        return (int)cudaMemcpyToSymbol(gb_bounds_table, t, sizeof(GbBoundsTable));              \
+    }                                                                                           \
+    extern "C" int gb_bounds_get_##unit(GbBoundsTable* t) {                                     \
+        return (int)cudaMemcpyFromSymbol(t, gb_bounds_table, sizeof(GbBoundsTable));            \
+    }
+#else
+#define GB_BOUNDS_HOST(unit)
+#endif
+
 __device__ __forceinline__ uint4 gb_ld16(const void* p, int mode = 1) {
+#ifdef GB_BOUNDS
+    if (!gb_in_bounds(p, 16, 0)) return make_uint4(0u, 0u, 0u, 0u);
+#endif
     if (mode == 0) {
         uint4 v;
         asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -81,6 +126,9 @@ __device__ __forceinline__ uint4 gb_ld16(const void* p, int mode = 1) {
     return __ldcg(reinterpret_cast<const uint4*>(p));      // ld.global.cg.v4: schedulable
 }
 __device__ __forceinline__ void gb_st16(void* p, uint4 v) {
+#ifdef GB_BOUNDS
+    if (!gb_in_bounds(p, 16, 1)) return;
+#endif
     *reinterpret_cast<uint4*>(p) = v;
 }
 

@@ -257,3 +257,5 @@ extern "C" int gb_allgather_gemm(const GbTeam* team, void* y, const void* x, con
                                                                                    *team, a);
     return (int)cudaGetLastError();
 }
+
+GB_BOUNDS_HOST(gemm)

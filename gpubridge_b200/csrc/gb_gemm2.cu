@@ -442,3 +442,5 @@ extern "C" int gb_allgather_gemm_pair(const GbTeam* team, void* y, const void* x
     config.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&config, kernel, map_x, map_w, *team, a);
 }
+
+GB_BOUNDS_HOST(gemm2)

@@ -278,3 +278,5 @@ extern "C" int gb_gemm_reduce_scatter(const GbTeam* team, void* out, const void*
     gemm_reduce_scatter_kernel<<<grid, GEMM_THREADS, smem, stream>>>(map_a, map_b, *team, args);
     return (int)cudaGetLastError();
 }
+
+GB_BOUNDS_HOST(gemm_rs)

@@ -22,7 +22,8 @@ struct AdamState {
 __global__ void __launch_bounds__(256)
 adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
              float* __restrict__ v, size_t n, AdamState* state, float lr, float beta1,
-             float beta2, float eps, float weight_decay, float grad_scale, int zero_grad) {
+             float beta2, float eps, float weight_decay, float grad_scale, int zero_grad,
+             int advance) {
     __shared__ float s_step;
     if (threadIdx.x == 0) {
         s_step = *reinterpret_cast<volatile float*>(&state->step) + 1.0f;
@@ -30,7 +31,7 @@ adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m
         // the last block to have read the old value publishes the new one
         if (atomicAdd(&state->arrived, 1u) + 1u == gridDim.x) {
             state->arrived = 0u;
-            *reinterpret_cast<volatile float*>(&state->step) = s_step;
+            if (advance) *reinterpret_cast<volatile float*>(&state->step) = s_step;
         }
     }
     __syncthreads();
@@ -76,16 +77,26 @@ adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m
 }  // namespace
 
 // All pointers are 16-byte aligned device memory; `state` is 16 zeroed bytes that persist
-// across steps.  Returns a cudaError_t.
-extern "C" int gb_adamw_step(float* p, float* g, float* m, float* v, size_t n, void* state,
+// across steps.  `advance` = 0 updates a part of the buffers as a part of the step in progress
+// (the step count is read but left as it is); the launch for the last part passes 1.  The parts
+// of one step run one after another (one stream, or events between them).  Returns a cudaError_t.
+extern "C" int gb_adamw_span(float* p, float* g, float* m, float* v, size_t n, void* state,
                              float lr, float beta1, float beta2, float eps, float weight_decay,
-                             float grad_scale, int zero_grad, cudaStream_t stream) {
-    if (n == 0) return 0;
+                             float grad_scale, int zero_grad, int advance, cudaStream_t stream) {
+    if (n == 0 && !advance) return 0;
     size_t blocks = (n / 4 + 256 * 4 - 1) / (256 * 4);
     if (blocks < 1) blocks = 1;
     if (blocks > 148 * 8) blocks = 148 * 8;
     adamw_kernel<<<(int)blocks, 256, 0, stream>>>(p, g, m, v, n, static_cast<AdamState*>(state),
                                                   lr, beta1, beta2, eps, weight_decay, grad_scale,
-                                                  zero_grad);
+                                                  zero_grad, advance);
     return (int)cudaGetLastError();
+}
+
+extern "C" int gb_adamw_step(float* p, float* g, float* m, float* v, size_t n, void* state,
+                             float lr, float beta1, float beta2, float eps, float weight_decay,
+                             float grad_scale, int zero_grad, cudaStream_t stream) {
+    if (n == 0) return 0;
+    return gb_adamw_span(p, g, m, v, n, state, lr, beta1, beta2, eps, weight_decay, grad_scale,
+                         zero_grad, 1, stream);
 }

@@ -391,3 +391,5 @@ extern "C" int gb_switch_all_reduce_inplace(const GbTeam* team, const GbSwitch* 
 }
 
 extern "C" size_t gb_sizeof_switch() { return sizeof(GbSwitch); }
+
+GB_BOUNDS_HOST(switch)

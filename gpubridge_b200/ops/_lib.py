@@ -73,6 +73,22 @@ class GbEngineConfig(ctypes.Structure):
                     "len_ag", "ag_chunk_bytes", "off_bc", "len_bc", "bc_stripe_bytes")])
 
 
+BOUNDS = os.environ.get("GPUBRIDGE_BOUNDS", "0") == "1"
+"""The checked library (``-DGB_BOUNDS``) is the one loaded: a debugging run."""
+BOUNDS_RANGES = 40
+BOUNDS_UNITS = ("collectives", "switch", "gemm", "gemm2", "gemm_rs")
+
+
+class GbBoundsTable(ctypes.Structure):
+    _fields_ = [("lo", ctypes.c_ulonglong * BOUNDS_RANGES), ("hi", ctypes.c_ulonglong * BOUNDS_RANGES),
+                ("n", ctypes.c_int), ("pad", ctypes.c_int), ("first", ctypes.c_ulonglong * 4),
+                ("violations", ctypes.c_uint), ("pad2", ctypes.c_uint)]
+
+
+def path() -> str:
+    return _build.LIB_BOUNDS if BOUNDS else _build.LIB
+
+
 class GbLaunch(ctypes.Structure):
     _fields_ = [("family", ctypes.c_int), ("kind", ctypes.c_int), ("grid", ctypes.c_int),
                 ("args", GbArgs)]
@@ -89,7 +105,7 @@ _lib: ctypes.CDLL | None = None
 
 
 def available() -> bool:
-    return os.path.exists(_build.LIB)
+    return os.path.exists(path())
 
 
 def lib() -> ctypes.CDLL:
@@ -98,9 +114,9 @@ def lib() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        if not os.path.exists(_build.LIB):
-            _build.build()
-        loaded = ctypes.CDLL(_build.LIB)
+        if not os.path.exists(path()):
+            _build.build(bounds=BOUNDS)
+        loaded = ctypes.CDLL(path())
         _declare(loaded)
         if loaded.gb_sizeof_team() != ctypes.sizeof(GbTeam) or \
                 loaded.gb_sizeof_args() != ctypes.sizeof(GbArgs) or \
@@ -115,6 +131,10 @@ def lib() -> ctypes.CDLL:
 
 def _declare(L: ctypes.CDLL) -> None:
     vp, sz, i = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    if BOUNDS:
+        for unit in BOUNDS_UNITS:
+            for verb in ("set", "get"):
+                getattr(L, f"gb_bounds_{verb}_{unit}").argtypes = [ctypes.POINTER(GbBoundsTable)]
     L.gb_error_string.restype = ctypes.c_char_p
     L.gb_error_string.argtypes = [i]
     for name in ("gb_sizeof_team", "gb_sizeof_args", "gb_sizeof_ctrl", "gb_sizeof_engine_config",
@@ -136,6 +156,7 @@ def _declare(L: ctypes.CDLL) -> None:
                                    i, vp]
     L.gb_launch_copy.argtypes = [i, ctypes.POINTER(GbTeam), ctypes.POINTER(GbArgs), i, vp]
     L.gb_adamw_step.argtypes = [vp, vp, vp, vp, sz, vp] + [ctypes.c_float] * 6 + [i, vp]
+    L.gb_adamw_span.argtypes = [vp, vp, vp, vp, sz, vp] + [ctypes.c_float] * 6 + [i, i, vp]
     L.gb_xent_fwd_bwd.argtypes = [vp, i, vp, sz, sz, sz, vp, vp, vp, vp]
     L.gb_allgather_gemm.argtypes = [ctypes.POINTER(GbTeam), vp, vp, vp, vp, vp, vp, ctypes.c_uint,
                                     i, i, i, sz, sz, i, i, vp]

@@ -108,6 +108,26 @@ def plan_hier(n: int, esize: int, *, k: int, m_max: int, n_islands: int, len_ha:
     return HierPlan(channels, grid, stripe, -(-n // (stripe * k)), len_a, len_b, len_c)
 
 
+def _bounds_checked(method):
+    """With the checked library loaded (``GPUBRIDGE_BOUNDS=1``): allow the launch the
+    workspaces, switch memory and the call's own tensors, wait for it, and raise if a kernel
+    tried to touch anything else.  Otherwise the method as it is."""
+    if not _lib.BOUNDS:
+        return method
+
+    import functools
+
+    @functools.wraps(method)
+    def run(self, *args, **kwargs):
+        tensors = [a for a in (*args, *kwargs.values()) if isinstance(a, torch.Tensor)]
+        self._bounds_allow(tensors)
+        try:
+            return method(self, *args, **kwargs)
+        finally:
+            self._bounds_verdict(method.__name__)
+    return run
+
+
 class FabricError(RuntimeError):
     """A device-side wait of a fused collective ran out, or the team was poisoned."""
 
@@ -565,7 +585,38 @@ class Fabric:
         _lib.check(code, "gb_launch_copy")
         self.launches += 1
 
+    # -- the checked build ------------------------------------------------------------------------------
+    def _bounds_allow(self, tensors) -> None:
+        self._bounds_tensors = tensors
+        table = _lib.GbBoundsTable()
+        ranges = [(int(self.team.ws[r]), int(self.team.ws[r]) + self.ws_bytes) for r in range(self.world)]
+        for sw in [self.sw_team, self.sw_island] + [heap[2] for heap in self._heaps]:
+            if sw is not None:
+                ranges += [(int(sw.uc), int(sw.uc) + sw.bytes), (int(sw.mc), int(sw.mc) + sw.bytes)]
+        ranges += [(t.data_ptr(), t.data_ptr() + t.nbytes) for t in tensors if t.numel()]
+        for residual in self._residuals.values():
+            ranges.append((residual[0].data_ptr(), residual[0].data_ptr() + residual[0].nbytes))
+        ranges = ranges[:_lib.BOUNDS_RANGES]
+        for i, (lo, hi) in enumerate(ranges):
+            table.lo[i], table.hi[i] = lo, hi
+        table.n = len(ranges)
+        for unit in ("collectives", "switch"):
+            _lib.check(getattr(self.lib, f"gb_bounds_set_{unit}")(ctypes.byref(table)), "bounds table")
+
+    def _bounds_verdict(self, what: str) -> None:
+        torch.cuda.synchronize(self.device)
+        for unit in ("collectives", "switch"):
+            table = _lib.GbBoundsTable()
+            _lib.check(getattr(self.lib, f"gb_bounds_get_{unit}")(ctypes.byref(table)), "bounds table")
+            if table.violations:
+                kind = {0: "load", 1: "store", 2: "bulk copy"}.get(int(table.first[1]), "access")
+                raise FabricError(
+                    f"{what}: {table.violations} accesses outside the allowed memory; the first: a "
+                    f"{kind} at {int(table.first[0]):#x} by thread {int(table.first[3])} of block "
+                    f"{int(table.first[2])} ({unit} kernels, team rank {self.rank})")
+
     # -- collectives -----------------------------------------------------------------------------------
+    @_bounds_checked
     def all_reduce(self, tensor: torch.Tensor, op: str = "sum", divide: int | None = None,
                    mode: str = "auto", compression=None, chunk_bytes: int | None = None,
                    out: torch.Tensor | None = None, keep: tuple[int, int] | None = None) -> None:
@@ -714,12 +765,15 @@ class Fabric:
                 size = stripe * nchunks if self.my_pos < self.k else 256
                 kept = (torch.zeros(size, dtype=torch.float32, device=self.device), geometry)
                 self._residuals[key] = kept
+                if _lib.BOUNDS:
+                    self._bounds_allow(getattr(self, "_bounds_tensors", []))
             return kept[0]
 
     def reset_error_feedback(self) -> None:
         with self._lock:
             self._residuals.clear()
 
+    @_bounds_checked
     def reduce_scatter(self, output: torch.Tensor, tensor: torch.Tensor, divide: int | None = None,
                        compression=None) -> None:
         """``output`` = slice ``rank`` of the sum of every rank's ``tensor``."""
@@ -756,6 +810,7 @@ class Fabric:
         finally:
             self._end(current)
 
+    @_bounds_checked
     def all_gather(self, output: torch.Tensor, tensor: torch.Tensor) -> None:
         nbytes = tensor.nbytes
         if nbytes == 0:
@@ -771,6 +826,7 @@ class Fabric:
         finally:
             self._end(current)
 
+    @_bounds_checked
     def broadcast(self, tensor: torch.Tensor, src: int) -> None:
         """Copy ``tensor`` from global rank ``src`` to every rank of the team."""
         nbytes = tensor.nbytes

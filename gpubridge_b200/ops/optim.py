@@ -27,28 +27,40 @@ class FlatAdamW:
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
 
     def step(self, grad_scale: float = 1.0, zero_grad: bool = True) -> None:
+        self.step_span(0, self.p.numel(), last=True, grad_scale=grad_scale, zero_grad=zero_grad)
+
+    def step_span(self, lo: int, hi: int, last: bool, grad_scale: float = 1.0,
+                  zero_grad: bool = True) -> None:
+        """Update elements ``[lo, hi)`` (``lo`` a multiple of 4) as a part of the step in
+        progress.  The parts of a step are launched in stream order; the one launched last
+        passes ``last=True`` and advances the step count."""
         global launches
         if self.p.device.type != "cuda":
-            self._reference_step(grad_scale, zero_grad)
+            self._reference_step(grad_scale, zero_grad, lo, hi, last)
             return
-        code = _lib.lib().gb_adamw_step(
-            self.p.data_ptr(), self.g.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
-            self.p.numel(), self.state.data_ptr(), self.lr, self.betas[0], self.betas[1],
-            self.eps, self.weight_decay, grad_scale, int(zero_grad),
+        assert lo % 4 == 0
+        code = _lib.lib().gb_adamw_span(
+            self.p.data_ptr() + 4 * lo, self.g.data_ptr() + 4 * lo, self.m.data_ptr() + 4 * lo,
+            self.v.data_ptr() + 4 * lo, hi - lo, self.state.data_ptr(), self.lr, self.betas[0],
+            self.betas[1], self.eps, self.weight_decay, grad_scale, int(zero_grad), int(last),
             _lib.stream_ptr(self.p.device))
-        _lib.check(code, "gb_adamw_step")
+        _lib.check(code, "gb_adamw_span")
         launches += 1
 
-    def _reference_step(self, grad_scale: float, zero_grad: bool) -> None:
+    def _reference_step(self, grad_scale: float, zero_grad: bool, lo: int = 0, hi: int | None = None,
+                        last: bool = True) -> None:
         """The same update in plain PyTorch (CPU runs and the oracle of the kernel test)."""
-        self.state[2] += 1
-        step = float(self.state[2])
+        hi = self.p.numel() if hi is None else hi
+        step = float(self.state[2]) + 1
+        if last:
+            self.state[2] += 1
         b1, b2 = self.betas
-        g = self.g * grad_scale
-        self.p.mul_(1 - self.lr * self.weight_decay)
-        self.m.mul_(b1).add_(g, alpha=1 - b1)
-        self.v.mul_(b2).addcmul_(g, g, value=1 - b2)
-        denom = (self.v.sqrt() / (1 - b2 ** step) ** 0.5).add_(self.eps)
-        self.p.addcdiv_(self.m, denom, value=-self.lr / (1 - b1 ** step))
+        p, m, v = self.p[lo:hi], self.m[lo:hi], self.v[lo:hi]
+        g = self.g[lo:hi] * grad_scale
+        p.mul_(1 - self.lr * self.weight_decay)
+        m.mul_(b1).add_(g, alpha=1 - b1)
+        v.mul_(b2).addcmul_(g, g, value=1 - b2)
+        denom = (v.sqrt() / (1 - b2 ** step) ** 0.5).add_(self.eps)
+        p.addcdiv_(m, denom, value=-self.lr / (1 - b1 ** step))
         if zero_grad:
-            self.g.zero_()
+            self.g[lo:hi].zero_()

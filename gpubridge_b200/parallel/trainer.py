@@ -47,6 +47,12 @@ class DataParallelTrainer:
             ``loss_fn`` scales the model's loss.
         exchange: False trains this rank alone even inside an initialised job (the
             compute-only phase of a benchmark).
+        optimizer_in_backward: update a bucket's parameters as soon as its averaged gradients
+            are there, on a side stream beside the rest of backward (the layers a bucket
+            belongs to have finished their backward by then, so nothing reads those
+            parameters again before the next forward); only the last bucket's update is left
+            for after backward.  The arithmetic and its result are those of one optimizer
+            call after backward.  ``GPUBRIDGE_OPTIMIZER_IN_BACKWARD`` (default 1).
     """
 
     def __init__(self, model: nn.Module, loss_fn, *, topology: Topology | None = None,
@@ -54,10 +60,14 @@ class DataParallelTrainer:
                  weight_decay: float = 1e-2, bucket_mb: float = 25.0,
                  autocast: torch.dtype | None = torch.bfloat16, graph: bool = False,
                  graph_warmup: int = 3, overlap_blocks: int | None = None,
-                 unit_grad: bool = True, exchange: bool = True) -> None:
+                 unit_grad: bool = True, exchange: bool = True,
+                 optimizer_in_backward: bool | None = None) -> None:
         self.model, self.loss_fn = model, loss_fn
         import os
         self.overlap_blocks = overlap_blocks or int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
+        if optimizer_in_backward is None:
+            optimizer_in_backward = os.environ.get("GPUBRIDGE_OPTIMIZER_IN_BACKWARD", "1") == "1"
+        self.optimizer_in_backward = optimizer_in_backward
         if hasattr(model, "unit_grad"):
             model.unit_grad = unit_grad     # backward always starts at the loss here
         if not exchange:
@@ -97,7 +107,10 @@ class DataParallelTrainer:
         self._sent = 0
         self._syncing = True
         self._comm_events: list[torch.cuda.Event] = []
-        if self.world > 1:
+        # the bucket updates of an optimizer that runs inside backward get a stream of their own
+        self._opt_stream = (torch.cuda.Stream(self.device)
+                            if self.optimizer_in_backward and self.device.type == "cuda" else None)
+        if self.world > 1 or self.optimizer_in_backward:
             for index, (lo, hi, members) in enumerate(self._buckets):
                 for p in members:
                     p.register_post_accumulate_grad_hook(self._make_hook(index))
@@ -133,8 +146,25 @@ class DataParallelTrainer:
         """Launch, in bucket order, every bucket whose gradients are all in."""
         while self._sent < len(self._buckets) and self._pending[self._sent] == 0:
             lo, hi, _ = self._buckets[self._sent]
-            self._all_reduce(self.flat_grad[lo:hi], tail=self._sent == len(self._buckets) - 1)
+            tail = self._sent == len(self._buckets) - 1
+            if self.world > 1:
+                self._all_reduce(self.flat_grad[lo:hi], tail=tail)
+            if self.optimizer_in_backward:
+                self._update(lo, hi, tail)
             self._sent += 1
+
+    def _update(self, lo: int, hi: int, last: bool) -> None:
+        """The optimizer on one bucket, ordered after the bucket's all-reduce (or, alone, after
+        the backward so far) and beside whatever backward still has to do."""
+        side = self._opt_stream
+        if side is None:
+            self.optimizer.step_span(lo, hi, last=last, zero_grad=True)
+            return
+        after = self.fabric.comm_stream if self.world > 1 and self.fabric is not None \
+            else torch.cuda.current_stream(self.device)
+        side.wait_stream(after)
+        with torch.cuda.stream(side):
+            self.optimizer.step_span(lo, hi, last=last, zero_grad=True)
 
     def _all_reduce(self, grads: torch.Tensor, tail: bool = False) -> None:
         topology, fabric = self.topology, self.fabric
@@ -177,13 +207,16 @@ class DataParallelTrainer:
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
         loss = total
-        if self.world > 1:
+        if self.world > 1 or self.optimizer_in_backward:
             # parameters that received no gradient still belong to their bucket
             self._pending = [0] * len(self._buckets)
             self._reduce_ready()
-            if self.fabric is not None:
+            if self.world > 1 and self.fabric is not None:
                 torch.cuda.current_stream(self.device).wait_stream(self.fabric.comm_stream)
-        self.optimizer.step(zero_grad=True)
+        if not self.optimizer_in_backward:
+            self.optimizer.step(zero_grad=True)
+        elif self._opt_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._opt_stream)
         self.launches += self._own_kernels() - own_before
         return loss
 

@@ -653,6 +653,8 @@ def front_end() -> str:
         return setting
     from gpubridge_b200.config import is_simulated
     import torch
+    if os.environ.get("GPUBRIDGE_BOUNDS", "0") == "1":
+        return "python"         # the C++ front end is linked against the unchecked library
     return "native" if torch.cuda.is_available() and not is_simulated() else "python"
 
 
