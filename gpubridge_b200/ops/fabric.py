@@ -169,7 +169,11 @@ class Fabric:
         self.sw_team = self.sw_island = None
         self._bseq = 0
         self.switch_min_bytes = _config.size_setting("GPUBRIDGE_SWITCH_MIN_BYTES", 64 << 10, multiple=1)
-        self.switch_flat = os.environ.get("GPUBRIDGE_SWITCH_FLAT", "0") == "1"
+        # One NVSwitch joins every GPU of the team, so an uncompressed sum over several islands is
+        # reduced in the switch across the whole team (one step, about (n + 1) / n of the tensor
+        # per GPU); "0" keeps the hierarchical order in the switch (a group per island, the
+        # islands' sums exchanged over peer memory), which moves more and is about half as fast.
+        self.switch_flat = os.environ.get("GPUBRIDGE_SWITCH_FLAT", "1") == "1"
         # Through the switch a GPU moves (n + 1) / n of the tensor, over peer memory 2 (n - 1) / n:
         # less from four ranks on, more at two (measured at two: the peer-memory kernels win).
         self.switch_min_ranks = int(os.environ.get("GPUBRIDGE_SWITCH_MIN_RANKS", "3"))

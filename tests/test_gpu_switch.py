@@ -112,8 +112,9 @@ def _sums(rank, topology):
 
 @pytest.mark.skipif(NGPU < 2, reason="needs at least two GPUs")
 @pytest.mark.parametrize("split", [{}, {"GPUBRIDGE_SPLIT_TEST": "half"},
-                                   {"GPUBRIDGE_SPLIT_TEST": "half", "GPUBRIDGE_SWITCH_FLAT": "1"}]
-                         + ([{"GPUBRIDGE_ISLANDS": "3,5"}, {"GPUBRIDGE_ISLANDS": "2,2,2,2"}] if WORLD == 8 else []),
+                                   {"GPUBRIDGE_SPLIT_TEST": "half", "GPUBRIDGE_SWITCH_FLAT": "0"}]
+                         + ([{"GPUBRIDGE_ISLANDS": "3,5", "GPUBRIDGE_SWITCH_FLAT": "0"},
+                             {"GPUBRIDGE_ISLANDS": "2,2,2,2", "GPUBRIDGE_SWITCH_FLAT": "0"}] if WORLD == 8 else []),
                          ids=lambda s: ",".join(s.values()) or "one-island")
 def test_sums_through_the_switch(tmp_path, split):
     out = run_ranks(gpu_ranks(WORLD), _sums, tmp_path, env={"GPUBRIDGE_NVLS": "1", **split}, timeout=240)
@@ -122,5 +123,5 @@ def test_sums_through_the_switch(tmp_path, split):
     # islands of one GPU cannot have a multicast object of their own: the team's is used
     sizes = {"GPUBRIDGE_SPLIT_TEST": [WORLD // 2], "GPUBRIDGE_ISLANDS": [3, 5] if "3,5" in split.values() else [2]}
     smallest = min(sizes[next(iter(split))]) if split else WORLD
-    want = "hier" if split and "GPUBRIDGE_SWITCH_FLAT" not in split and smallest >= 2 else "flat"
+    want = "hier" if split.get("GPUBRIDGE_SWITCH_FLAT") == "0" and smallest >= 2 else "flat"
     assert set(out) == {want}, out
