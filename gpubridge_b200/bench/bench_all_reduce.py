@@ -111,6 +111,10 @@ def close_targets(topology) -> None:
     _made.clear()
 
 
+_heap = None
+_heap_bytes = 0
+
+
 def make_target(name: str, op: str, topology, dtype, nbytes: int):
     """A zero-argument callable running ``op`` once on ``nbytes`` of ``dtype``."""
     dev, world = topology.device, topology.world_size
@@ -130,6 +134,21 @@ def make_target(name: str, op: str, topology, dtype, nbytes: int):
         out = torch.empty(n // world, dtype=dtype, device=dev)
         src = full[: out.numel() * world]
         return lambda: comm.reduce_scatter_into(out, src), src.nbytes
+    if name == "ours-inplace":
+        # the tensor lives in the team's switch memory (what the data-parallel trainer does
+        # with its gradients): the all-reduce runs in place inside the NVSwitch, nothing staged
+        fabric = topology.fabric
+        if op != "all_reduce" or fabric is None or not hasattr(fabric, "switch_empty"):
+            return None, nbytes
+        global _heap
+        if _heap is None or _heap.numel() * _heap.element_size() < nbytes:
+            _heap = fabric.switch_empty(max(nbytes, _heap_bytes) // 4, torch.float32)
+        if _heap is None:
+            return None, nbytes
+        home = _heap.view(torch.uint8)[:nbytes].view(dtype)
+        home.copy_(full)
+        policy = topology.policy
+        return lambda: policy.all_reduce(home, topology), nbytes
     policy = target_policy(name, topology)
     if op == "all_reduce":
         return lambda: policy.all_reduce(full, topology), nbytes
@@ -155,6 +174,8 @@ def main(argv=None) -> int:
     ap.add_argument("--seconds", type=float, default=20.0)
     ap.add_argument("--inner", type=int, default=1, help="back-to-back calls per trial")
     ap.add_argument("--json", default="")
+    ap.add_argument("--blocks", type=int, default=0, help="cap the grid of this library's kernels "
+                    "(what a collective that runs beside compute gets)")
     ap.add_argument("--bridge", default=os.environ.get("GPUBRIDGE_BRIDGE", "").strip() or None,
                     help="bridge transport between islands (default: GPUBRIDGE_BRIDGE, else init()'s choice)")
     ap.add_argument("--write-thresholds", default="")
@@ -174,6 +195,11 @@ def main(argv=None) -> int:
         topology = gb.init(**({"bridge": args.bridge} if args.bridge else {}))
     rank, world = topology.rank, topology.world_size
     rows = []
+    global _heap_bytes
+    _heap_bytes = parse_size(args.largest)
+    import contextlib
+    capped = (lambda: topology.fabric.grid_cap(args.blocks)) if args.blocks and topology.fabric is not None \
+        else contextlib.nullcontext
     try:
         for op in args.ops.split(","):
             for dtype_name in args.dtypes.split(","):
@@ -183,13 +209,15 @@ def main(argv=None) -> int:
                         if target == "nccl" and topology.p2p_group is None:
                             continue
                         fn, moved = make_target(target, op, topology, dtype, nbytes)
+                        if fn is None:
+                            continue
                         # the fused kernels are timed on the stream they run on, as the async
                         # (DDP / FSDP) path uses them; NCCL is timed on the current stream
                         fused = target != "nccl" and topology.fabric is not None
                         if topology.device.type == "cuda":
                             stream = (topology.fabric.comm_stream if fused
                                       else torch.cuda.current_stream(topology.device))
-                            with torch.cuda.stream(stream):
+                            with torch.cuda.stream(stream), (capped() if fused else contextlib.nullcontext()):
                                 ms = time_calls(fn, topology, args.trials, args.seconds,
                                                 inner=args.inner)
                         else:
@@ -200,6 +228,8 @@ def main(argv=None) -> int:
                                "busbw_gbs": round(algbw * BUS[op](world), 3), "world": world,
                                "islands": [len(i.ranks) for i in topology.layout.islands],
                                "policy": topology.policy_name, "inner": args.inner}
+                        if args.blocks and fused:
+                            row["blocks"] = args.blocks
                         if target.startswith("compression:") and op == "all_reduce":
                             row.update(compression_check(target, topology, dtype, nbytes))
                         if args.phases and target == "ours" and op == "all_reduce":

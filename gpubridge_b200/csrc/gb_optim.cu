@@ -79,14 +79,18 @@ adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m
 // All pointers are 16-byte aligned device memory; `state` is 16 zeroed bytes that persist
 // across steps.  `advance` = 0 updates a part of the buffers as a part of the step in progress
 // (the step count is read but left as it is); the launch for the last part passes 1.  The parts
-// of one step run one after another (one stream, or events between them).  Returns a cudaError_t.
+// of one step run one after another (one stream, or events between them).  `max_blocks` > 0
+// caps the grid.  Returns a cudaError_t.
 extern "C" int gb_adamw_span(float* p, float* g, float* m, float* v, size_t n, void* state,
                              float lr, float beta1, float beta2, float eps, float weight_decay,
-                             float grad_scale, int zero_grad, int advance, cudaStream_t stream) {
+                             float grad_scale, int zero_grad, int advance, int max_blocks,
+                             cudaStream_t stream) {
     if (n == 0 && !advance) return 0;
     size_t blocks = (n / 4 + 256 * 4 - 1) / (256 * 4);
     if (blocks < 1) blocks = 1;
     if (blocks > 148 * 8) blocks = 148 * 8;
+    // a part that runs beside other kernels can be told to leave them the SMs
+    if (max_blocks > 0 && blocks > (size_t)max_blocks) blocks = (size_t)max_blocks;
     adamw_kernel<<<(int)blocks, 256, 0, stream>>>(p, g, m, v, n, static_cast<AdamState*>(state),
                                                   lr, beta1, beta2, eps, weight_decay, grad_scale,
                                                   zero_grad, advance);
@@ -98,5 +102,5 @@ extern "C" int gb_adamw_step(float* p, float* g, float* m, float* v, size_t n, v
                              float grad_scale, int zero_grad, cudaStream_t stream) {
     if (n == 0) return 0;
     return gb_adamw_span(p, g, m, v, n, state, lr, beta1, beta2, eps, weight_decay, grad_scale,
-                         zero_grad, 1, stream);
+                         zero_grad, 1, 0, stream);
 }

@@ -156,7 +156,7 @@ def _declare(L: ctypes.CDLL) -> None:
                                    i, vp]
     L.gb_launch_copy.argtypes = [i, ctypes.POINTER(GbTeam), ctypes.POINTER(GbArgs), i, vp]
     L.gb_adamw_step.argtypes = [vp, vp, vp, vp, sz, vp] + [ctypes.c_float] * 6 + [i, vp]
-    L.gb_adamw_span.argtypes = [vp, vp, vp, vp, sz, vp] + [ctypes.c_float] * 6 + [i, i, vp]
+    L.gb_adamw_span.argtypes = [vp, vp, vp, vp, sz, vp] + [ctypes.c_float] * 6 + [i, i, i, vp]
     L.gb_xent_fwd_bwd.argtypes = [vp, i, vp, sz, sz, sz, vp, vp, vp, vp]
     L.gb_allgather_gemm.argtypes = [ctypes.POINTER(GbTeam), vp, vp, vp, vp, vp, vp, ctypes.c_uint,
                                     i, i, i, sz, sz, i, i, vp]

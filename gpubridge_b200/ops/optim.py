@@ -30,10 +30,11 @@ class FlatAdamW:
         self.step_span(0, self.p.numel(), last=True, grad_scale=grad_scale, zero_grad=zero_grad)
 
     def step_span(self, lo: int, hi: int, last: bool, grad_scale: float = 1.0,
-                  zero_grad: bool = True) -> None:
+                  zero_grad: bool = True, max_blocks: int = 0) -> None:
         """Update elements ``[lo, hi)`` (``lo`` a multiple of 4) as a part of the step in
         progress.  The parts of a step are launched in stream order; the one launched last
-        passes ``last=True`` and advances the step count."""
+        passes ``last=True`` and advances the step count.  ``max_blocks`` caps the grid of a
+        part that runs beside other kernels."""
         global launches
         if self.p.device.type != "cuda":
             self._reference_step(grad_scale, zero_grad, lo, hi, last)
@@ -43,7 +44,7 @@ class FlatAdamW:
             self.p.data_ptr() + 4 * lo, self.g.data_ptr() + 4 * lo, self.m.data_ptr() + 4 * lo,
             self.v.data_ptr() + 4 * lo, hi - lo, self.state.data_ptr(), self.lr, self.betas[0],
             self.betas[1], self.eps, self.weight_decay, grad_scale, int(zero_grad), int(last),
-            _lib.stream_ptr(self.p.device))
+            int(max_blocks), _lib.stream_ptr(self.p.device))
         _lib.check(code, "gb_adamw_span")
         launches += 1
 

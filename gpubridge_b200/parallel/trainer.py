@@ -41,7 +41,8 @@ class DataParallelTrainer:
         autocast: dtype of ``torch.autocast`` around forward, or None.
         graph: capture the step in a CUDA graph after ``graph_warmup`` eager steps.
         overlap_blocks: CTAs of a bucket all-reduce that runs beside backward
-            (``GPUBRIDGE_OVERLAP_BLOCKS``, default 32); the last bucket uses the full grid.
+            (``GPUBRIDGE_OVERLAP_BLOCKS``; default 8 when the gradients live in switch memory,
+            else 32); the last bucket uses the full grid.
         unit_grad: tell a model that has a ``unit_grad`` switch that backward starts at its
             loss with gradient 1 (its fused loss then skips the multiply); pass False when
             ``loss_fn`` scales the model's loss.
@@ -52,7 +53,8 @@ class DataParallelTrainer:
             belongs to have finished their backward by then, so nothing reads those
             parameters again before the next forward); only the last bucket's update is left
             for after backward.  The arithmetic and its result are those of one optimizer
-            call after backward.  ``GPUBRIDGE_OPTIMIZER_IN_BACKWARD`` (default 1).
+            call after backward.  ``GPUBRIDGE_OPTIMIZER_IN_BACKWARD``: ``1``, ``0``, or unset =
+            on a team of two or more only (alone it costs more than it hides).
     """
 
     def __init__(self, model: nn.Module, loss_fn, *, topology: Topology | None = None,
@@ -64,10 +66,10 @@ class DataParallelTrainer:
                  optimizer_in_backward: bool | None = None) -> None:
         self.model, self.loss_fn = model, loss_fn
         import os
-        self.overlap_blocks = overlap_blocks or int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
-        if optimizer_in_backward is None:
-            optimizer_in_backward = os.environ.get("GPUBRIDGE_OPTIMIZER_IN_BACKWARD", "1") == "1"
-        self.optimizer_in_backward = optimizer_in_backward
+        self.overlap_blocks = overlap_blocks or int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "0"))
+        self._in_backward_wanted = optimizer_in_backward
+        # grid of an update that runs beside backward (the last bucket's takes what it wants)
+        self.update_blocks = int(os.environ.get("GPUBRIDGE_UPDATE_BLOCKS", "0"))
         if hasattr(model, "unit_grad"):
             model.unit_grad = unit_grad     # backward always starts at the loss here
         if not exchange:
@@ -90,6 +92,20 @@ class DataParallelTrainer:
         if self.fabric is not None and self.world > 1 and hasattr(self.fabric, "switch_empty"):
             in_switch = self.fabric.switch_empty(total, torch.float32)
         self.grads_in_switch = in_switch is not None
+        if not self.overlap_blocks:
+            # measured on four B200s: in place in the switch 8 CTAs keep up with the buckets
+            # and cost backward the least (14.67 ms a step against 14.80 with 32); the
+            # peer-memory kernels need their 32
+            self.overlap_blocks = 8 if self.grads_in_switch else 32
+        # Alone, an update beside backward costs more than it hides (13.7 ms a step after
+        # backward, 14.3-14.9 inside it: every kernel that shares the GPU delays cuBLAS's
+        # persistent GEMMs); on a team the updates follow the bucket all-reduces, which are
+        # there anyway, and the step gets about 0.1 ms shorter.
+        wanted = self._in_backward_wanted
+        if wanted is None:
+            wanted = os.environ.get("GPUBRIDGE_OPTIMIZER_IN_BACKWARD", "auto")
+            wanted = self.world > 1 if wanted == "auto" else wanted == "1"
+        self.optimizer_in_backward = bool(wanted)
         self.flat_grad = in_switch if in_switch is not None else \
             torch.zeros(total, dtype=torch.float32, device=self.device)
         # reverse registration order: the order backward fills the gradients in
@@ -164,7 +180,8 @@ class DataParallelTrainer:
             else torch.cuda.current_stream(self.device)
         side.wait_stream(after)
         with torch.cuda.stream(side):
-            self.optimizer.step_span(lo, hi, last=last, zero_grad=True)
+            self.optimizer.step_span(lo, hi, last=last, zero_grad=True,
+                                     max_blocks=0 if last else self.update_blocks)
 
     def _all_reduce(self, grads: torch.Tensor, tail: bool = False) -> None:
         topology, fabric = self.topology, self.fabric
