@@ -43,10 +43,13 @@ def sizes(lo: int, hi: int) -> list[int]:
     return out
 
 
-def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5, inner: int = 1) -> float:
+def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5, inner: int = 1,
+               graph: bool = False) -> float:
     """Median over trials of the slowest rank's device time per call, in milliseconds.  With
     ``inner`` > 1 a trial is that many back-to-back calls (what a training step issues), which
-    takes the launch and host jitter of a lone call out of small-message latencies."""
+    takes the launch and host jitter of a lone call out of small-message latencies.  With
+    ``graph`` the ``inner`` calls are captured once in a CUDA graph and a trial is one replay:
+    what the device needs, with no host work between the calls."""
     dev = topology.device
     on_gpu = dev.type == "cuda"
     for _ in range(warmup):
@@ -54,13 +57,24 @@ def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5, inner
     if on_gpu:
         torch.cuda.synchronize(dev)
     topology.world_group.barrier()
+    if graph and on_gpu:
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured, stream=torch.cuda.current_stream(dev)):
+            for _ in range(inner):
+                fn()
+        torch.cuda.synchronize(dev)
+        topology.world_group.barrier()
+        run_trial = captured.replay
+    else:
+        def run_trial():
+            for _ in range(inner):
+                fn()
     times, started = [], time.monotonic()
     for _ in range(trials):
         if on_gpu:
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-            for _ in range(inner):
-                fn()
+            run_trial()
             end.record()
             end.synchronize()
             took = start.elapsed_time(end)
@@ -174,6 +188,8 @@ def main(argv=None) -> int:
     ap.add_argument("--seconds", type=float, default=20.0)
     ap.add_argument("--inner", type=int, default=1, help="back-to-back calls per trial")
     ap.add_argument("--json", default="")
+    ap.add_argument("--graph", action="store_true", help="capture the --inner calls of a trial in "
+                    "a CUDA graph and time its replay (device time without host work between calls)")
     ap.add_argument("--blocks", type=int, default=0, help="cap the grid of this library's kernels "
                     "(what a collective that runs beside compute gets)")
     ap.add_argument("--bridge", default=os.environ.get("GPUBRIDGE_BRIDGE", "").strip() or None,
@@ -219,7 +235,7 @@ def main(argv=None) -> int:
                                       else torch.cuda.current_stream(topology.device))
                             with torch.cuda.stream(stream), (capped() if fused else contextlib.nullcontext()):
                                 ms = time_calls(fn, topology, args.trials, args.seconds,
-                                                inner=args.inner)
+                                                inner=args.inner, graph=args.graph)
                         else:
                             ms = time_calls(fn, topology, args.trials, args.seconds, inner=args.inner)
                         algbw = moved / (ms * 1e-3) / 1e9
@@ -230,6 +246,8 @@ def main(argv=None) -> int:
                                "policy": topology.policy_name, "inner": args.inner}
                         if args.blocks and fused:
                             row["blocks"] = args.blocks
+                        if args.graph:
+                            row["graph"] = True
                         if target.startswith("compression:") and op == "all_reduce":
                             row.update(compression_check(target, topology, dtype, nbytes))
                         if args.phases and target == "ours" and op == "all_reduce":
