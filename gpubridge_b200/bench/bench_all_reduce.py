@@ -30,6 +30,7 @@ import torch
 import gpubridge_b200 as gb
 from gpubridge_b200 import policies as _policies
 from gpubridge_b200.config import parse_size
+from gpubridge_b200.ops import _lib as _native
 
 BUS = {"all_reduce": lambda n: 2 * (n - 1) / n, "all_gather": lambda n: (n - 1) / n,
        "reduce_scatter": lambda n: (n - 1) / n, "broadcast": lambda n: 1.0}
@@ -148,6 +149,21 @@ def make_target(name: str, op: str, topology, dtype, nbytes: int):
         out = torch.empty(n // world, dtype=dtype, device=dev)
         src = full[: out.numel() * world]
         return lambda: comm.reduce_scatter_into(out, src), src.nbytes
+    if name == "ours-native":
+        # the native engine's own entry point, as the C++ front end calls it (planner and launch
+        # in C++, no Python policy layer): what DDP's hook and FSDP2 get per call
+        fabric = topology.fabric
+        engine = fabric.engine() if fabric is not None and op == "all_reduce" else 0
+        if not engine or dtype not in _native.DTYPES:
+            return None, nbytes
+        lib, code = fabric.lib, _native.DTYPES[dtype]
+        ptr, count = full.data_ptr(), full.numel()
+
+        def native_call():
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            _native.check(lib.gb_engine_all_reduce(engine, ptr, ptr, count, code, 0, 0, 0, stream),
+                          "gb_engine_all_reduce")
+        return native_call, nbytes
     if name == "ours-inplace":
         # the tensor lives in the team's switch memory (what the data-parallel trainer does
         # with its gradients): the all-reduce runs in place inside the NVSwitch, nothing staged
