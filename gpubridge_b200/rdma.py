@@ -167,6 +167,10 @@ def provider_available() -> bool:
 def load(name: str) -> None:
     """Called when ``bridge="verbs"`` is resolved: says, on every rank alike and before anything
     is connected, why the bridge cannot be used here."""
+    if provider_available():
+        from gpubridge_b200 import rdma_transport, transport
+        transport.register_transport(rdma_transport.RdmaTransport)
+        return
     raise ImportError(
         "the verbs bridge needs a provider over libibverbs, and this build has none: the "
         "infiniband/verbs.h header is not installed here.  The endpoint itself - wire protocol, "
