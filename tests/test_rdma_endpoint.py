@@ -102,6 +102,8 @@ def test_early_messages_wait_for_their_receives_in_any_tag_order(fabric):
 
 def test_credits_hold_back_a_flood_and_every_message_still_arrives(fabric):
     f, (a, b) = fabric(data_slots=4, ctrl_slots=3)
+    # the first credit message back to the sender is late, so the sender is certain to run dry
+    f.inject("delay", src=1, dst=0, on="send", nth=1, milliseconds=200)
     payloads = [torch.full((64,), float(i)) for i in range(200)]
     sends = [a.send(1, p.data_ptr(), p.nbytes, 1) for p in payloads]  # far more than four slots
     outs = [torch.zeros(64) for _ in range(200)]
