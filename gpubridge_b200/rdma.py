@@ -176,3 +176,34 @@ def load(name: str) -> None:
         "infiniband/verbs.h header is not installed here.  The endpoint itself - wire protocol, "
         "flow control, registration cache, failure rule - is built and runs over an in-process "
         "fabric (gpubridge_b200.rdma.MockFabric); across machines use bridge='multitcp' or 'gloo'")
+
+
+def info() -> dict:
+    """What this build has of the verbs bridge (``python -m gpubridge_b200.rdma info``)."""
+    import ctypes.util
+    import os
+    return {"protocol": protocol_version(), "provider": "libibverbs" if provider_available() else None,
+            "libibverbs_found": ctypes.util.find_library("ibverbs") is not None,
+            "verbs_header": os.path.exists("/usr/include/infiniband/verbs.h"),
+            "in_process_fabric": True,
+            "defaults": {"eager_max": 16 << 10, "data_slots": 16, "ctrl_slots": 8, "max_write": 1 << 20,
+                         "unexpected_max": 64 << 20, "mr_cache": 64}}
+
+
+def main(argv: list[str]) -> int:
+    import sys
+    command = argv[0] if argv else "info"
+    if command == "build":
+        from gpubridge_b200.ops import _build
+        print(_build.build())
+        return 0
+    if command == "info":
+        print(json.dumps(info()))
+        return 0
+    print("usage: python -m gpubridge_b200.rdma [build|info]", file=sys.stderr)
+    return 2
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(main(sys.argv[1:]))

@@ -19,3 +19,35 @@ def load(name: str) -> None:
     raise ImportError(
         f"{label} {'was found but its headers are not part of this build' if found else 'is not installed'}; "
         "use bridge='nvlink' on one NVSwitch box, or 'multitcp' / 'gloo' across nodes")
+
+
+def info() -> dict:
+    """What is known about each unavailable transport (``python -m gpubridge_b200.unavailable info``)."""
+    import os
+    out = {}
+    for name, (lib, label) in _NEEDS.items():
+        out[name] = {"needs": label, "library_found": ctypes.util.find_library(lib) is not None,
+                     "header_found": os.path.exists("/usr/include/ucp/api/ucp.h")}
+    return out
+
+
+def main(argv: list[str]) -> int:
+    import json
+    import sys
+    command = argv[0] if argv else "info"
+    if command == "info":
+        print(json.dumps(info()))
+        return 0
+    if command == "build":
+        try:
+            load("ucx")
+        except ImportError as failure:
+            print(f"nothing to build: {failure}", file=sys.stderr)
+            return 1
+    print("usage: python -m gpubridge_b200.unavailable [build|info]", file=sys.stderr)
+    return 2
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(main(sys.argv[1:]))

@@ -215,3 +215,16 @@ def test_the_name_still_says_why_it_cannot_load():
     from gpubridge_b200 import transport
     with pytest.raises(ValueError, match="provider"):
         transport.resolve_transport("verbs")
+
+
+def test_the_command_lines_say_what_this_build_has():
+    import json
+    import subprocess
+    import sys
+    done = subprocess.run([sys.executable, "-m", "gpubridge_b200.rdma", "info"], capture_output=True, text=True)
+    told = json.loads(done.stdout)
+    assert told["protocol"] >= 1 and told["in_process_fabric"] and told["provider"] is None
+    done = subprocess.run([sys.executable, "-m", "gpubridge_b200.unavailable", "info"], capture_output=True, text=True)
+    assert "ucx" in json.loads(done.stdout)
+    done = subprocess.run([sys.executable, "-m", "gpubridge_b200.unavailable", "build"], capture_output=True, text=True)
+    assert done.returncode == 1 and "nothing to build" in done.stderr
