@@ -337,6 +337,7 @@ def main(argv=None) -> int:
     slowest = torch.tensor([ms], dtype=torch.float64, device=device)
     dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
     tokens = args.batch * args.seq * world * args.steps
+    front_end = _front_end_calls(device, locals().get("mesh"))
     if rank == 0:
         topology = gb.get_topology() if gb.is_initialized() else None
         print(json.dumps({
@@ -348,10 +349,34 @@ def main(argv=None) -> int:
             "loss": round(float(loss), 4),
             "compression": os.environ.get("GPUBRIDGE_BRIDGE_COMPRESSION", ""),
             "parameters": sum(p.numel() for p in core.parameters()),
-            "clocks": clocks,
+            "clocks": clocks, "front_end": front_end,
         }), flush=True)
     dist.destroy_process_group()
     return 0
+
+
+def _front_end_calls(device, mesh) -> dict | None:
+    """How many collective calls the C++ front end launched itself and how many it handed to
+    the Python group, summed over the world group and the mesh's groups (None when another
+    backend, or the Python group, answers)."""
+    groups = [dist.group.WORLD]
+    if mesh is not None:
+        try:
+            groups += list(mesh.get_all_groups())
+        except Exception:  # noqa: BLE001 - a mesh without groups of its own
+            pass
+    native = fallback = 0
+    seen = False
+    for group in groups:
+        try:
+            backend = group._get_backend(device)
+        except Exception:  # noqa: BLE001
+            continue
+        if hasattr(backend, "native_calls"):
+            seen = True
+            native += int(backend.native_calls)
+            fallback += int(backend.fallback_calls)
+    return {"native_calls": native, "fallback_calls": fallback} if seen else None
 
 
 if __name__ == "__main__":
