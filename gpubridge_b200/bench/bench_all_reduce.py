@@ -159,7 +159,7 @@ def make_target(name: str, op: str, topology, dtype, nbytes: int):
         lib, code = fabric.lib, _native.DTYPES[dtype]
         ptr, count = full.data_ptr(), full.numel()
 
-        def native_call():
+        def native_call(keep=full):            # the closure owns the tensor: only its address is used
             stream = torch.cuda.current_stream(dev).cuda_stream
             _native.check(lib.gb_engine_all_reduce(engine, ptr, ptr, count, code, 0, 0, 0, stream),
                           "gb_engine_all_reduce")
