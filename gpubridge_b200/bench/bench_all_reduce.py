@@ -60,7 +60,9 @@ def time_calls(fn, topology, trials: int, seconds: float, warmup: int = 5, inner
     topology.world_group.barrier()
     if graph and on_gpu:
         captured = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(captured, stream=torch.cuda.current_stream(dev)):
+        here = torch.cuda.current_stream(dev)
+        side = here if here != torch.cuda.default_stream(dev) else torch.cuda.Stream(dev)
+        with torch.cuda.graph(captured, stream=side):       # never the default stream
             for _ in range(inner):
                 fn()
         torch.cuda.synchronize(dev)

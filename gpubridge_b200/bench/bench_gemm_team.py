@@ -116,7 +116,7 @@ def main(argv=None) -> int:
 
             def cublas_then_nccl():
                 full = dy_t @ x_t.t()
-                nccl.reduce_scatter_into(out.view(-1), full.view(-1), "avg")
+                nccl.reduce_scatter_into(out.view(-1), full.view(-1), dist.ReduceOp.AVG)
             try:
                 row["cublas_then_nccl_reduce_scatter_us"] = slowest_us(cublas_then_nccl)
             except Exception as failure:  # noqa: BLE001

@@ -15,6 +15,13 @@ extern "C" int gb_launch_copy(int kind, const GbTeam* team, const GbArgs* args, 
 extern "C" int gb_switch_all_reduce(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
                                     size_t n, int dtype, int divide, int max_blocks,
                                     cudaStream_t stream);
+extern "C" int gb_switch_reduce_scatter(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
+                                        size_t n_out, int dtype, int divide, int max_blocks,
+                                        cudaStream_t stream);
+extern "C" int gb_switch_all_gather(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
+                                    size_t in_bytes, int max_blocks, cudaStream_t stream);
+extern "C" int gb_switch_broadcast(const GbTeam* team, const GbSwitch* sw, void* buffer, size_t nbytes,
+                                   int root, int max_blocks, cudaStream_t stream);
 
 namespace {
 
@@ -32,12 +39,29 @@ struct Engine {
     bool has_team = false, has_island = false;
     size_t sw_min_bytes = 0;
     int sw_min_ranks = 3;
+    size_t sw_copy_min_bytes = ~size_t(0);      // reduce-scatter, all-gather, broadcast through the switch
     std::atomic<unsigned long long> launches{0};
 };
 
 inline size_t down(size_t v, size_t m) { return v / m * m; }
 inline size_t up(size_t v, size_t m) { return (v + m - 1) / m * m; }
 inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Whether a copy-shaped collective of `total` bytes in pieces of `piece` bytes takes the switch
+// (the team's group; pieces and pointers in multiples of 16 bytes): the same rule as
+// Fabric._switch_copy.
+bool switch_copy(const Engine& e, size_t total, size_t piece, const void* p0, const void* p1) {
+    return e.has_team && e.team.world >= e.sw_min_ranks && e.c.algo == 0 && total >= e.sw_copy_min_bytes &&
+           (piece & 15) == 0 &&
+           ((reinterpret_cast<uintptr_t>(p0) | reinterpret_cast<uintptr_t>(p1)) & 15) == 0;
+}
+
+void switch_grid(const Engine& e, int grid_cap, GbLaunch* L, int kind) {
+    L->family = 2;
+    L->kind = kind;
+    L->grid = e.c.max_blocks;
+    if (grid_cap > 0 && grid_cap < L->grid) L->grid = grid_cap;
+}
 
 int grid_for(const Engine& e, size_t nbytes, int cap, int grid_cap) {
     const size_t blocks = ceil_div(nbytes, size_t(kThreads) * 16 * 4);
@@ -186,6 +210,10 @@ extern "C" int gb_engine_prepare_reduce_scatter(void* engine, const void* in, vo
     a.out = out;
     a.n = n_out;
     a.divide = divide > 0 ? divide : 0;
+    if (dtype <= 2 && switch_copy(e, n_out * size_t(esize) * e.team.world, n_out * size_t(esize), in, out)) {
+        switch_grid(e, grid_cap, L, 2);
+        return GB_ENGINE_OK;
+    }
     const size_t cap = down(e.c.rs_chunk_bytes / esize, 256), whole = up(n_out, 256);
     a.chunk = cap < whole ? cap : whole;
     if (a.chunk == 0) return GB_ENGINE_WORKSPACE;
@@ -209,6 +237,10 @@ extern "C" int gb_engine_prepare_all_gather(void* engine, const void* in, void* 
     a.in = in;
     a.out = out;
     a.n = in_bytes;
+    if (switch_copy(e, in_bytes * size_t(e.team.world), in_bytes, in, out)) {
+        switch_grid(e, grid_cap, L, 3);
+        return GB_ENGINE_OK;
+    }
     const size_t whole = up(in_bytes, 16);
     a.chunk = e.c.ag_chunk_bytes < whole ? e.c.ag_chunk_bytes : whole;
     a.off_a = e.c.off_ag;
@@ -229,6 +261,10 @@ extern "C" int gb_engine_prepare_broadcast(void* engine, void* buffer, size_t nb
     a.out = buffer;
     a.n = nbytes;
     a.root = root;
+    if (switch_copy(e, nbytes, nbytes, buffer, buffer)) {
+        switch_grid(e, grid_cap, L, 4);
+        return GB_ENGINE_OK;
+    }
     const size_t share = up(ceil_div(nbytes, size_t(e.team.world)), 16);
     const size_t stripe = e.c.bc_stripe_bytes < share ? e.c.bc_stripe_bytes : share;
     a.stripe = stripe;
@@ -256,8 +292,25 @@ extern "C" void gb_engine_set_switch(void* engine, const GbSwitch* team, const G
     e.sw_min_ranks = min_ranks;
 }
 
+// From how many bytes on reduce-scatter, all-gather and broadcast go through the team's switch
+// group (never, until this is called).
+extern "C" void gb_engine_set_switch_copy(void* engine, size_t min_bytes) {
+    static_cast<Engine*>(engine)->sw_copy_min_bytes = min_bytes;
+}
+
 namespace {
 int launch(Engine& e, const GbLaunch& L, int dtype, int op, void* stream) {
+    if (L.family == 2 && L.kind >= 2) {
+        cudaStream_t on = static_cast<cudaStream_t>(stream);
+        const int rc = L.kind == 2
+            ? gb_switch_reduce_scatter(&e.team, &e.sw_team, L.args.in, L.args.out, L.args.n, dtype,
+                                       L.args.divide, L.grid, on)
+            : L.kind == 3
+            ? gb_switch_all_gather(&e.team, &e.sw_team, L.args.in, L.args.out, L.args.n, L.grid, on)
+            : gb_switch_broadcast(&e.team, &e.sw_team, L.args.out, L.args.n, L.args.root, L.grid, on);
+        if (rc == 0) e.launches.fetch_add(1, std::memory_order_relaxed);
+        return rc;
+    }
     if (L.family == 2) {
         const int rc = gb_switch_all_reduce(&e.team, L.kind == 1 ? &e.sw_island : &e.sw_team, L.args.in,
                                             L.args.out, L.args.n, dtype, L.args.divide, L.grid,

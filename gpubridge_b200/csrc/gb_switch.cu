@@ -42,6 +42,9 @@
 #include "gb_common.cuh"
 #include "gb_switch.h"
 
+extern "C" int gb_switch_plan_copy(const GbSwitch* sw, int nsub, size_t piece, int max_blocks,
+                                   GbSwitchPlan* plan);
+
 namespace {
 
 // Two launch shapes: 512 threads (one block per SM) with four switch requests in flight per
@@ -298,6 +301,167 @@ cudaError_t launch_inplace(const GbTeam& tm, const GbSwitch& sw, const SwArgs& a
     return cudaGetLastError();
 }
 
+
+// ---- reduce-scatter, all-gather and broadcast through the switch -----------------------------------
+//
+// The same staging memory, block-level barriers and tile ownership as the all-reduce (one group:
+// the team), depth 3, every step ends with the barrier - the last one too, so that when a block
+// leaves nobody reads or writes its staging buffers any more and the next kernel may start with
+// a remote write.  A staging buffer holds `nsub` sub-tiles, one per member's piece.
+//   reduce-scatter  A  copy tile i of every member's piece of the input into the own buffer (local)
+//                   B  ld_reduce the own piece's sub-tile of tile i-1 over the team, divide for AVG,
+//                      store it straight into the output                       (switch; no copy out)
+//   all-gather      A  multimem.st tile i of the own input into the own sub-tile of every
+//                      member's buffer                                          (switch; no copy in)
+//                   B  copy every sub-tile of tile i-1 from the own buffer to the output   (local)
+//   broadcast       A  root: multimem.st tile i of the tensor into every member's buffer
+//                   B  the others: copy tile i-1 from the own buffer into the tensor
+// Traffic per GPU: what the collective has to move and no more - a reduce-scatter receives 1/n
+// of the input instead of (n-1)/n of it, an all-gather and a broadcast send one copy instead of
+// n-1 - and the local copies run at memory speed beside the switch requests.
+// All pointers and the piece size are multiples of 16 bytes (the host checks).
+template <typename T, int MODE, int SW_THREADS, int U>
+__global__ void __launch_bounds__(SW_THREADS, SW_MAX_THREADS / SW_THREADS)
+switch_copy_kernel(GbTeam tm, GbSwitch sw, SwCopyArgs a) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = SwVec<T>::N;
+    constexpr int DEPTH = 3;
+    constexpr int SW_HALF = SW_THREADS / 2;
+    const int b = (int)blockIdx.x, B = (int)gridDim.x;
+    const int mine = (a.ntiles - b + B - 1) / B;
+    unsigned seq = gb_ld_volatile(sw.bseq + b);
+    const size_t buf = (size_t)a.nsub * a.tile;
+    char* stage = sw.uc + (size_t)b * DEPTH * buf;
+    char* stage_mc = sw.mc + (size_t)b * DEPTH * buf;
+    const int n = tm.world, me = tm.rank;
+    const bool front = (int)threadIdx.x < SW_HALF;
+    const int tid = (int)threadIdx.x - (front ? 0 : SW_HALF);
+    GbLane half;
+    half.tid = (size_t)tid; half.nth = SW_HALF; half.ld = tm.ld_mode;
+    GbLane whole;
+    whole.tid = threadIdx.x; whole.nth = SW_THREADS; whole.ld = tm.ld_mode;
+
+    for (int s = 0; s <= mine; ++s) {
+        const size_t off = ((size_t)s * B + b) * a.tile;                       // tile s, inside a piece
+        const size_t len = s < mine ? (a.piece - off < a.tile ? a.piece - off : a.tile) : 0;
+        const size_t poff = ((size_t)(s - 1) * B + b) * a.tile;                // tile s - 1
+        const size_t plen = s >= 1 ? (a.piece - poff < a.tile ? a.piece - poff : a.tile) : 0;
+        char* now = stage + (size_t)(s % DEPTH) * buf;
+        char* now_mc = stage_mc + (size_t)(s % DEPTH) * buf;
+        char* before = stage + (size_t)((s + DEPTH - 1) % DEPTH) * buf;
+        char* before_mc = stage_mc + (size_t)((s + DEPTH - 1) % DEPTH) * buf;
+        if (MODE == 0) {
+            if (front) {
+                if (len)
+                    for (int q = 0; q < n; ++q)
+                        gb_copy_bytes(half, now + (size_t)q * a.tile, a.in + (size_t)q * a.piece + off, len, false);
+            } else if (plen) {
+                const char* src = before_mc + (size_t)me * a.tile;
+                const size_t nvec = plen >> 4;
+                for (size_t v0 = (size_t)tid; v0 < nvec; v0 += (size_t)U * SW_HALF) {
+                    SwVec<T> w[U];
+                    #pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const size_t v = v0 + (size_t)u * SW_HALF;
+                        if (v < nvec) w[u].u = SwitchSum<T>::load(src + (v << 4));
+                    }
+                    #pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const size_t v = v0 + (size_t)u * SW_HALF;
+                        if (v >= nvec) continue;
+                        if (a.divide > 0) {
+                            #pragma unroll
+                            for (int j = 0; j < V; ++j)
+                                w[u].e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(w[u].e[j]), a.divide));
+                        }
+                        gb_st16(a.out + poff + (v << 4), w[u].u);
+                    }
+                }
+            }
+        } else if (MODE == 1) {
+            if (!front) {
+                if (len) {
+                    const char* src = a.in + off;
+                    char* dst = now_mc + (size_t)me * a.tile;
+                    const size_t nvec = len >> 4;
+                    for (size_t v0 = (size_t)tid; v0 < nvec; v0 += (size_t)U * SW_HALF) {
+                        uint4 w[U];
+                        #pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            const size_t v = v0 + (size_t)u * SW_HALF;
+                            if (v < nvec) w[u] = __ldg(reinterpret_cast<const uint4*>(src + (v << 4)));
+                        }
+                        #pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            const size_t v = v0 + (size_t)u * SW_HALF;
+                            if (v < nvec) switch_store(dst + (v << 4), w[u]);
+                        }
+                    }
+                }
+            } else if (plen) {
+                for (int q = 0; q < n; ++q)
+                    gb_copy_bytes(half, a.out + (size_t)q * a.piece + poff, before + (size_t)q * a.tile, plen, true);
+            }
+        } else {
+            if (me == a.root) {
+                if (len) {
+                    const size_t nvec = len >> 4;
+                    for (size_t v0 = threadIdx.x; v0 < nvec; v0 += (size_t)U * SW_THREADS) {
+                        uint4 w[U];
+                        #pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            const size_t v = v0 + (size_t)u * SW_THREADS;
+                            if (v < nvec) w[u] = __ldg(reinterpret_cast<const uint4*>(a.in + off + (v << 4)));
+                        }
+                        #pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            const size_t v = v0 + (size_t)u * SW_THREADS;
+                            if (v < nvec) switch_store(now_mc + (v << 4), w[u]);
+                        }
+                    }
+                }
+            } else if (plen) {
+                gb_copy_bytes(whole, a.out + poff, before, plen, true);
+            }
+        }
+        if (!sw_block_sync(tm, sw, b, ++seq)) return;
+        if (b == 0 && threadIdx.x == 0 && s == 0) tm.ctrl->stamps[0] = gb_now();
+    }
+    if (threadIdx.x == 0) {
+        sw.bseq[b] = seq;
+        if (b == 0) tm.ctrl->stamps[1] = gb_now();
+    }
+}
+
+template <typename T, int MODE>
+cudaError_t launch_copy(const GbTeam& tm, const GbSwitch& sw, const SwCopyArgs& a, int grid,
+                        cudaStream_t stream) {
+    if (switch_shape() == 0) switch_copy_kernel<T, MODE, 512, 4><<<grid, 512, 0, stream>>>(tm, sw, a);
+    else switch_copy_kernel<T, MODE, 256, 8><<<grid, 256, 0, stream>>>(tm, sw, a);
+    return cudaGetLastError();
+}
+
+// Shared preparation of the three: checks, plan, arguments.  Returns 0, -1 (does not fit) or -3
+// (alignment: the caller takes the peer-memory kernel).
+int prepare_copy(const GbTeam* team, const GbSwitch* sw, const void* in, void* out, size_t piece,
+                 int nsub, int max_blocks, SwCopyArgs* a, int* grid) {
+    if (sw->hier || sw->group_size != team->world) return -1;
+    if (piece == 0 || (piece & 15) || ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15))
+        return -3;
+    GbSwitchPlan plan;
+    if (gb_switch_plan_copy(sw, nsub, piece, max_blocks, &plan) != 0) return -1;
+    a->in = static_cast<const char*>(in);
+    a->out = static_cast<char*>(out);
+    a->piece = piece;
+    a->tile = plan.tile;
+    a->ntiles = plan.ntiles;
+    a->nsub = nsub;
+    a->divide = 0;
+    a->root = 0;
+    *grid = plan.grid;
+    return 0;
+}
+
 }  // namespace
 
 // Tile size and grid for `nbytes` with at most `max_blocks` blocks: every rank of the team
@@ -388,6 +552,72 @@ extern "C" int gb_switch_all_reduce_inplace(const GbTeam* team, const GbSwitch* 
     if (dtype == 0) return (int)launch_inplace<float>(*team, *sw, a, offset, grid, stream);
     if (dtype == 1) return (int)launch_inplace<__nv_bfloat16>(*team, *sw, a, offset, grid, stream);
     return (int)launch_inplace<__half>(*team, *sw, a, offset, grid, stream);
+}
+
+// Tiles and grid of a copy-shaped collective: `nsub` sub-tiles per staging buffer, pieces of
+// `piece` bytes.  Every rank computes this from values they all share.
+extern "C" int gb_switch_plan_copy(const GbSwitch* sw, int nsub, size_t piece, int max_blocks,
+                                   GbSwitchPlan* plan) {
+    const size_t unit = 128;
+    if (switch_shape() != 0) max_blocks *= 2;
+    if (max_blocks > GB_SWITCH_MAX_BLOCKS) max_blocks = GB_SWITCH_MAX_BLOCKS;
+    if (max_blocks < 1 || piece == 0 || nsub < 1) return -1;
+    const size_t floor_tile = nsub > 1 ? 4096 : 16384;
+    const size_t want_blocks = (piece + floor_tile - 1) / floor_tile;
+    int grid = (int)(want_blocks < (size_t)max_blocks ? want_blocks : (size_t)max_blocks);
+    size_t cap = sw->bytes / ((size_t)grid * 3 * (size_t)nsub) / unit * unit;
+    const size_t most = (size_t)(2 * GB_SWITCH_MAX_TILE) / (size_t)nsub / unit * unit;   // 512 KiB per buffer
+    if (cap > most) cap = most;
+    if (cap < unit) return -1;
+    size_t tile = ((piece + grid - 1) / grid + unit - 1) / unit * unit;
+    if (tile < floor_tile) tile = floor_tile;
+    if (tile > cap) tile = cap;
+    const size_t ntiles = (piece + tile - 1) / tile;
+    if (ntiles > 0x7fffffffu) return -1;
+    if ((size_t)grid > ntiles) grid = (int)ntiles;
+    plan->tile = tile;
+    plan->ntiles = (int)ntiles;
+    plan->grid = grid;
+    return 0;
+}
+
+// out = this rank's piece (n_out elements) of the sum over the team of in (world pieces back to
+// back), divided by `divide` when > 0.  dtype: 0 f32, 1 bf16, 2 f16.  Returns a cudaError_t, -2
+// for a type the switch cannot add, -1 when it does not fit, -3 for pointers or a piece size
+// that are not multiples of 16 bytes (take the peer-memory kernel then).
+extern "C" int gb_switch_reduce_scatter(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
+                                        size_t n_out, int dtype, int divide, int max_blocks,
+                                        cudaStream_t stream) {
+    if (dtype < 0 || dtype > 2) return -2;
+    SwCopyArgs a;
+    int grid = 0;
+    const int rc = prepare_copy(team, sw, in, out, n_out * (dtype == 0 ? 4 : 2), team->world, max_blocks, &a, &grid);
+    if (rc != 0) return rc;
+    a.divide = divide;
+    if (dtype == 0) return (int)launch_copy<float, 0>(*team, *sw, a, grid, stream);
+    if (dtype == 1) return (int)launch_copy<__nv_bfloat16, 0>(*team, *sw, a, grid, stream);
+    return (int)launch_copy<__half, 0>(*team, *sw, a, grid, stream);
+}
+
+// out = every rank's `in` (in_bytes each) back to back in team order.
+extern "C" int gb_switch_all_gather(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
+                                    size_t in_bytes, int max_blocks, cudaStream_t stream) {
+    SwCopyArgs a;
+    int grid = 0;
+    const int rc = prepare_copy(team, sw, in, out, in_bytes, team->world, max_blocks, &a, &grid);
+    if (rc != 0) return rc;
+    return (int)launch_copy<float, 1>(*team, *sw, a, grid, stream);
+}
+
+// Every rank's `buffer` becomes the root's.
+extern "C" int gb_switch_broadcast(const GbTeam* team, const GbSwitch* sw, void* buffer, size_t nbytes,
+                                   int root, int max_blocks, cudaStream_t stream) {
+    SwCopyArgs a;
+    int grid = 0;
+    const int rc = prepare_copy(team, sw, buffer, buffer, nbytes, 1, max_blocks, &a, &grid);
+    if (rc != 0) return rc;
+    a.root = root;
+    return (int)launch_copy<float, 2>(*team, *sw, a, grid, stream);
 }
 
 extern "C" size_t gb_sizeof_switch() { return sizeof(GbSwitch); }

@@ -34,3 +34,15 @@ struct SwArgs {
     int ntiles;
     int divide;
 };
+
+// The copy-shaped collectives through the switch (reduce-scatter, all-gather, broadcast).
+struct SwCopyArgs {
+    const char* in;
+    char* out;
+    size_t piece;             // bytes of one member's piece (broadcast: of the whole tensor)
+    size_t tile;              // bytes of one piece's share of a staging buffer; a multiple of 128
+    int ntiles;               // tiles per piece
+    int nsub;                 // pieces per staging buffer: the team size (broadcast: 1)
+    int divide;               // reduce-scatter: > 0 divides the sum
+    int root;                 // broadcast: the team rank that has the data
+};

@@ -207,6 +207,13 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_switch_all_reduce_inplace.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), sz, sz,
                                                i, i, i, vp]
     L.gb_engine_set_switch.argtypes = [vp, ctypes.POINTER(GbSwitch), ctypes.POINTER(GbSwitch), sz, i]
+    L.gb_engine_set_switch_copy.argtypes = [vp, sz]
+    L.gb_engine_set_switch_copy.restype = None
+    L.gb_switch_plan_copy.argtypes = [ctypes.POINTER(GbSwitch), i, sz, i, ctypes.POINTER(GbSwitchPlan)]
+    L.gb_switch_reduce_scatter.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), vp, vp, sz,
+                                           i, i, i, vp]
+    L.gb_switch_all_gather.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), vp, vp, sz, i, vp]
+    L.gb_switch_broadcast.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), vp, sz, i, i, vp]
     L.gb_codec_quantize.argtypes = [i, i, i, vp, vp, vp, sz, vp]
     L.gb_codec_dequantize.argtypes = [i, i, i, vp, sz, i, vp, sz, vp]
 

@@ -177,6 +177,11 @@ class Fabric:
         # Through the switch a GPU moves (n + 1) / n of the tensor, over peer memory 2 (n - 1) / n:
         # less from four ranks on, more at two (measured at two: the peer-memory kernels win).
         self.switch_min_ranks = int(os.environ.get("GPUBRIDGE_SWITCH_MIN_RANKS", "3"))
+        # reduce-scatter, all-gather and broadcast take the switch from this many bytes on (the
+        # whole tensor: input of a reduce-scatter, output of an all-gather); below it the
+        # peer-memory kernels are as fast and need no staging
+        self.switch_copy_min_bytes = _config.size_setting("GPUBRIDGE_SWITCH_COPY_MIN_BYTES", 32 << 20,
+                                                          multiple=1)
         self.nvls_reducers = int(os.environ.get("GPUBRIDGE_NVLS_REDUCERS", "48"))
         self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "32"))
         self.overlap_blocks = int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
@@ -498,6 +503,8 @@ class Fabric:
             self._engine, ctypes.byref(self.sw_team) if self.sw_team is not None else None,
             ctypes.byref(self.sw_island) if self.sw_island is not None else None,
             self.switch_min_bytes, self.switch_min_ranks)
+        if self.sw_team is not None:
+            self.lib.gb_engine_set_switch_copy(self._engine, self.switch_copy_min_bytes)
 
     def _switch_for(self, tensor: torch.Tensor, op: str, compression) -> "_lib.GbSwitch | None":
         """The switch group an all-reduce of ``tensor`` takes, or None for the peer-memory kernels."""
@@ -506,6 +513,20 @@ class Fabric:
                 or self.world < self.switch_min_ranks):
             return None
         return self.sw_island if self.sw_island is not None else self.sw_team
+
+    def _switch_copy(self, total_bytes: int, *pointers: int, piece: int) -> "_lib.GbSwitch | None":
+        """The team's switch group when a copy-shaped collective of ``total_bytes`` should take
+        it (pieces and pointers in multiples of 16 bytes), else None."""
+        if (self.sw_team is None or self.world < self.switch_min_ranks or self.algo != "auto"
+                or total_bytes < self.switch_copy_min_bytes or piece % 16
+                or any(p % 16 for p in pointers)):
+            return None
+        return self.sw_team
+
+    def _launch_switch_copy(self, call, what: str) -> None:
+        limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))
+        _lib.check(call(limit, torch.cuda.current_stream(self.device).cuda_stream), what)
+        self.launches += 1
 
     # -- the native engine -----------------------------------------------------------------------------
     def engine_config(self) -> "_lib.GbEngineConfig":
@@ -798,9 +819,17 @@ class Fabric:
         if casting and {output.dtype, tensor.dtype} != {torch.float32, torch.bfloat16}:
             raise ValueError("reduce_scatter casts between float32 and bfloat16 only, got "
                              f"{tensor.dtype} -> {output.dtype}")
+        switch = None if casting or tensor.dtype not in NVLS_DTYPES else self._switch_copy(
+            tensor.nbytes, tensor.data_ptr(), output.data_ptr(), piece=n * esize)
         current = self._begin()
         try:
             with torch.cuda.stream(self.comm_stream):
+                if switch is not None:
+                    self._launch_switch_copy(lambda limit, stream: self.lib.gb_switch_reduce_scatter(
+                        ctypes.byref(self.team), ctypes.byref(switch), tensor.data_ptr(), output.data_ptr(),
+                        n, _lib.DTYPES[tensor.dtype], int(divide or 0), limit, stream),
+                        "gb_switch_reduce_scatter")
+                    return
                 args = _lib.GbArgs()
                 args.inp, args.out, args.n = tensor.data_ptr(), output.data_ptr(), n
                 args.divide = int(divide or 0)
@@ -819,9 +848,15 @@ class Fabric:
         nbytes = tensor.nbytes
         if nbytes == 0:
             return
+        switch = self._switch_copy(output.nbytes, tensor.data_ptr(), output.data_ptr(), piece=nbytes)
         current = self._begin()
         try:
             with torch.cuda.stream(self.comm_stream):
+                if switch is not None:
+                    self._launch_switch_copy(lambda limit, stream: self.lib.gb_switch_all_gather(
+                        ctypes.byref(self.team), ctypes.byref(switch), tensor.data_ptr(), output.data_ptr(),
+                        nbytes, limit, stream), "gb_switch_all_gather")
+                    return
                 args = _lib.GbArgs()
                 args.inp, args.out, args.n = tensor.data_ptr(), output.data_ptr(), nbytes
                 args.chunk = min(self.ag_chunk_bytes, _align_up(nbytes, 16))
@@ -836,9 +871,16 @@ class Fabric:
         nbytes = tensor.nbytes
         if nbytes == 0:
             return
+        switch = self._switch_copy(nbytes, tensor.data_ptr(), piece=nbytes)
         current = self._begin()
         try:
             with torch.cuda.stream(self.comm_stream):
+                if switch is not None:
+                    root = self.layout.index(src)
+                    self._launch_switch_copy(lambda limit, stream: self.lib.gb_switch_broadcast(
+                        ctypes.byref(self.team), ctypes.byref(switch), tensor.data_ptr(), nbytes, root,
+                        limit, stream), "gb_switch_broadcast")
+                    return
                 args = _lib.GbArgs()
                 args.out, args.n = tensor.data_ptr(), nbytes
                 args.root = self.layout.index(src)

@@ -32,6 +32,7 @@ def fake_fabric(sizes, ws_bytes=384 << 20, **over):
     f.sw_team = f.sw_island = None
     f._heaps = []
     f.switch_min_bytes, f.switch_flat, f.switch_min_ranks = 64 << 10, False, 3
+    f.switch_copy_min_bytes = 32 << 20
     f.layout = types.SimpleNamespace(index=lambda r: r)
     for name, value in over.items():
         setattr(f, name, value)
@@ -166,6 +167,18 @@ class _RecordingLib:
         self._seen.append((2, switch._obj.hier, limit, inp, out, n, divide))
         return 0
 
+    def gb_switch_reduce_scatter(self, team, switch, inp, out, n, dtype, divide, limit, stream):
+        self._seen.append((2, 2, limit, inp, out, n, divide))
+        return 0
+
+    def gb_switch_all_gather(self, team, switch, inp, out, nbytes, limit, stream):
+        self._seen.append((2, 3, limit, inp, out, nbytes, 0))
+        return 0
+
+    def gb_switch_broadcast(self, team, switch, buffer, nbytes, root, limit, stream):
+        self._seen.append((2, 4, limit, None, buffer, nbytes, root))
+        return 0
+
 
 @pytest.mark.parametrize("sizes", [(2,), (3,), (4,), (8,), (4, 4), (2, 2, 2, 2), (1, 1, 1)])
 @pytest.mark.parametrize("islands_have_groups", [False, True])
@@ -215,3 +228,84 @@ def test_the_in_switch_all_reduce_is_chosen_alike(sizes, islands_have_groups, mo
                     same(launch, seen)
     assert (through_switch > 0) == (sum(sizes) >= f.switch_min_ranks)
     f.lib.gb_engine_destroy(engine)
+
+
+@pytest.mark.parametrize("sizes", [(2,), (4,), (8,), (4, 4)])
+def test_copy_shaped_collectives_take_the_switch_alike(sizes, monkeypatch):
+    """Reduce-scatter, all-gather and broadcast go through the team's switch group from the same
+    size on in both planners, only with pieces and pointers in multiples of 16 bytes, with the
+    same grid limit; below it the peer-memory plans still agree field by field."""
+    monkeypatch.setattr(torch.cuda, "current_stream",
+                        lambda device=None: types.SimpleNamespace(cuda_stream=0))
+    monkeypatch.setattr(torch.cuda, "stream", lambda s: __import__("contextlib").nullcontext())
+    rng = random.Random(sum(sizes))
+    f = fake_fabric(sizes, ws_bytes=1 << 30)
+    f.lib = _RecordingLib(f.lib, f.seen)
+    f.sw_team = _lib.GbSwitch()
+    engine = f.engine()
+    assert engine
+    world, through = f.world, 0
+
+    def tensor(nbytes, dtype, ptr):
+        esize = torch.empty(0, dtype=dtype).element_size()
+        return types.SimpleNamespace(numel=lambda: nbytes // esize, nbytes=nbytes, dtype=dtype,
+                                     data_ptr=lambda: ptr, element_size=lambda: esize)
+
+    for _ in range(40):
+        dtype = rng.choice([torch.float32, torch.bfloat16])
+        esize = torch.empty(0, dtype=dtype).element_size()
+        piece = rng.choice([4096, (8 << 20) // world, (32 << 20) // world, (64 << 20) // world,
+                            (64 << 20) // world + 4, (256 << 20) // world]) // esize * esize
+        base = (1 << 30) + rng.choice([0, 0, 0, 4])
+        cap = rng.choice([0, 0, 16])
+        whole, part = tensor(piece * world, dtype, base), tensor(piece, dtype, (1 << 32) + 256)
+        launch = _lib.GbLaunch()
+        with f.grid_cap(cap or None):
+            f.reduce_scatter(part, whole, divide=world)
+        assert f.lib.gb_engine_prepare_reduce_scatter(engine, base, part.data_ptr(), piece // esize,
+                                                      _lib.DTYPES[dtype], world, cap, ctypes.byref(launch)) == 0
+        seen = f.seen.pop()
+        if seen[0] == 2:
+            through += 1
+            assert (launch.family, launch.kind, launch.grid) == seen[:3] and launch.args.n == seen[5]
+        else:
+            same(launch, seen)
+        with f.grid_cap(cap or None):
+            f.all_gather(whole, part)
+        assert f.lib.gb_engine_prepare_all_gather(engine, part.data_ptr(), base, piece, cap,
+                                                  ctypes.byref(launch)) == 0
+        seen = f.seen.pop()
+        if seen[0] == 2:
+            through += 1
+            assert (launch.family, launch.kind, launch.grid) == seen[:3] and launch.args.n == seen[5]
+        else:
+            same(launch, seen)
+        f.layout = types.SimpleNamespace(index=lambda r: r)
+        with f.grid_cap(cap or None):
+            f.broadcast(whole, 1)
+        assert f.lib.gb_engine_prepare_broadcast(engine, base, piece * world, 1, cap, ctypes.byref(launch)) == 0
+        seen = f.seen.pop()
+        if seen[0] == 2:
+            through += 1
+            assert (launch.family, launch.kind, launch.grid, launch.args.root) == (*seen[:3], seen[6])
+        else:
+            same(launch, seen)
+    assert (through > 0) == (world >= 3)
+    f.lib.gb_engine_destroy(engine)
+
+
+def test_the_copy_plan_fits_the_switch_memory():
+    lib = _lib.lib()
+    sw = _lib.GbSwitch()
+    sw.bytes = 256 << 20
+    for nsub in (1, 3, 4, 8, 16):
+        for piece in (16, 4096, 100_000 * 16, 8 << 20, 1 << 30):
+            for blocks in (1, 8, 32, 128):
+                plan = _lib.GbSwitchPlan()
+                assert lib.gb_switch_plan_copy(ctypes.byref(sw), nsub, piece, blocks, ctypes.byref(plan)) == 0
+                assert plan.tile % 128 == 0 and plan.tile > 0
+                assert 1 <= plan.grid <= min(2 * blocks, _lib.SWITCH_MAX_BLOCKS, plan.ntiles)
+                assert plan.grid * 3 * nsub * plan.tile <= sw.bytes
+                assert (plan.ntiles - 1) * plan.tile < piece <= plan.ntiles * plan.tile
+    sw.bytes = 1 << 16
+    assert lib.gb_switch_plan_copy(ctypes.byref(sw), 8, 1 << 20, 128, ctypes.byref(_lib.GbSwitchPlan())) == -1

@@ -125,3 +125,53 @@ def test_sums_through_the_switch(tmp_path, split):
     smallest = min(sizes[next(iter(split))]) if split else WORLD
     want = "hier" if split.get("GPUBRIDGE_SWITCH_FLAT") == "0" and smallest >= 2 else "flat"
     assert set(out) == {want}, out
+
+
+def _copies(rank, topology):
+    """Reduce-scatter, all-gather and broadcast through the switch (pieces in multiples of 16
+    bytes), every size twice in a row, against the values the collective must produce; sizes
+    whose pieces are not multiples of 16 bytes take the peer-memory kernels and must still be
+    right."""
+    import gpubridge_b200 as gb
+    fabric = topology.fabric
+    if fabric is None or fabric.sw_team is None:
+        return f"unavailable: {getattr(fabric, 'switch_error', 'no fabric')}"
+    dev, world = topology.device, topology.world_size
+    assert fabric.switch_copy_min_bytes == 0
+    before = fabric.launches
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (8, 1024, 70_000, (3 << 20) + 8, 6_000_000, 4099):
+            for _ in range(2):
+                full = rank_tensor(rank, world * n, dtype).to(dev)
+                keep = full.clone()
+                out = torch.full((n,), 9, dtype=dtype, device=dev)
+                gb.reduce_scatter_tensor(out, full)
+                want = expected_sum(world, world * n, dtype).view(world, n)[rank]
+                assert torch.equal(out.cpu(), want), ("reduce_scatter", n, dtype)
+                assert torch.equal(full, keep), "reduce_scatter must not modify its input"
+                if dtype is torch.float32:
+                    gb.reduce_scatter_tensor(out, full, gb.ReduceOp.AVG)
+                    assert torch.equal(out.cpu(), want / world), ("reduce_scatter avg", n)
+                gathered = torch.full((world * n,), 9, dtype=dtype, device=dev)
+                gb.all_gather_into_tensor(gathered, rank_tensor(rank, n, dtype).to(dev))
+                want = torch.cat([rank_tensor(r, n, dtype) for r in range(world)])
+                assert torch.equal(gathered.cpu(), want), ("all_gather", n, dtype)
+                for src in (0, world - 1):
+                    t = rank_tensor(rank, n, dtype).to(dev)
+                    gb.broadcast(t, src)
+                    assert torch.equal(t.cpu(), rank_tensor(src, n, dtype)), ("broadcast", n, src)
+    torch.cuda.synchronize(dev)
+    fabric.check()
+    assert fabric.launches > before
+    gb.barrier()
+    return "ok"
+
+
+@pytest.mark.skipif(NGPU < 3, reason="the switch path starts at three ranks")
+@pytest.mark.parametrize("split", [{}, {"GPUBRIDGE_SPLIT_TEST": "half"}], ids=["one-island", "half"])
+def test_copy_shaped_collectives_through_the_switch(tmp_path, split):
+    env = {"GPUBRIDGE_NVLS": "1", "GPUBRIDGE_SWITCH_COPY_MIN_BYTES": "0", **split}
+    out = run_ranks(gpu_ranks(WORLD), _copies, tmp_path, env=env, timeout=240)
+    if any(str(o).startswith("unavailable") for o in out):
+        pytest.skip(f"no NVLink multicast binding on this machine ({out[0]})")
+    assert set(out) == {"ok"}
