@@ -94,7 +94,7 @@ class Runner:
         if step == "fetch":
             if Path(self.source).exists():
                 return [[py, "-c", "import shutil, sys; shutil.copytree(sys.argv[1], sys.argv[2], "
-                         "dirs_exist_ok=True, ignore=shutil.ignore_patterns('.git', 'gpurun_out', '_work'))",
+                         "dirs_exist_ok=True, ignore=shutil.ignore_patterns('.git', '__pycache__', '*.o'))",
                          self.source, str(self.src)]]
             return [["git", "clone", "--depth", "1", *(["--branch", self.ref] if self.ref else []),
                      self.source, str(self.src)]]
