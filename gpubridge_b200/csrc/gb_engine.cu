@@ -39,7 +39,8 @@ struct Engine {
     bool has_team = false, has_island = false;
     size_t sw_min_bytes = 0;
     int sw_min_ranks = 3;
-    size_t sw_copy_min_bytes = ~size_t(0);      // reduce-scatter, all-gather, broadcast through the switch
+    size_t sw_copy_min_bytes = ~size_t(0);      // broadcast through the switch from this size on
+    size_t sw_gather_min_bytes = ~size_t(0);    // reduce-scatter and all-gather
     std::atomic<unsigned long long> launches{0};
 };
 
@@ -50,8 +51,10 @@ inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
 // Whether a copy-shaped collective of `total` bytes in pieces of `piece` bytes takes the switch
 // (the team's group; pieces and pointers in multiples of 16 bytes): the same rule as
 // Fabric._switch_copy.
-bool switch_copy(const Engine& e, size_t total, size_t piece, const void* p0, const void* p1) {
-    return e.has_team && e.team.world >= e.sw_min_ranks && e.c.algo == 0 && total >= e.sw_copy_min_bytes &&
+bool switch_copy(const Engine& e, size_t total, size_t piece, const void* p0, const void* p1,
+                 bool gather = true) {
+    const size_t least = gather ? e.sw_gather_min_bytes : e.sw_copy_min_bytes;
+    return e.has_team && e.team.world >= e.sw_min_ranks && e.c.algo == 0 && total >= least &&
            (piece & 15) == 0 &&
            ((reinterpret_cast<uintptr_t>(p0) | reinterpret_cast<uintptr_t>(p1)) & 15) == 0;
 }
@@ -261,7 +264,7 @@ extern "C" int gb_engine_prepare_broadcast(void* engine, void* buffer, size_t nb
     a.out = buffer;
     a.n = nbytes;
     a.root = root;
-    if (switch_copy(e, nbytes, nbytes, buffer, buffer)) {
+    if (switch_copy(e, nbytes, nbytes, buffer, buffer, /*gather=*/false)) {
         switch_grid(e, grid_cap, L, 4);
         return GB_ENGINE_OK;
     }
@@ -292,10 +295,11 @@ extern "C" void gb_engine_set_switch(void* engine, const GbSwitch* team, const G
     e.sw_min_ranks = min_ranks;
 }
 
-// From how many bytes on reduce-scatter, all-gather and broadcast go through the team's switch
-// group (never, until this is called).
-extern "C" void gb_engine_set_switch_copy(void* engine, size_t min_bytes) {
-    static_cast<Engine*>(engine)->sw_copy_min_bytes = min_bytes;
+// From how many bytes on a broadcast, and a reduce-scatter or all-gather, go through the team's
+// switch group (never, until this is called).
+extern "C" void gb_engine_set_switch_copy(void* engine, size_t broadcast_min_bytes, size_t gather_min_bytes) {
+    static_cast<Engine*>(engine)->sw_copy_min_bytes = broadcast_min_bytes;
+    static_cast<Engine*>(engine)->sw_gather_min_bytes = gather_min_bytes;
 }
 
 namespace {

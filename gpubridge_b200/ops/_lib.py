@@ -207,7 +207,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.gb_switch_all_reduce_inplace.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), sz, sz,
                                                i, i, i, vp]
     L.gb_engine_set_switch.argtypes = [vp, ctypes.POINTER(GbSwitch), ctypes.POINTER(GbSwitch), sz, i]
-    L.gb_engine_set_switch_copy.argtypes = [vp, sz]
+    L.gb_engine_set_switch_copy.argtypes = [vp, sz, sz]
     L.gb_engine_set_switch_copy.restype = None
     L.gb_switch_plan_copy.argtypes = [ctypes.POINTER(GbSwitch), i, sz, i, ctypes.POINTER(GbSwitchPlan)]
     L.gb_switch_reduce_scatter.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), vp, vp, sz,

@@ -177,15 +177,20 @@ class Fabric:
         # Through the switch a GPU moves (n + 1) / n of the tensor, over peer memory 2 (n - 1) / n:
         # less from four ranks on, more at two (measured at two: the peer-memory kernels win).
         self.switch_min_ranks = int(os.environ.get("GPUBRIDGE_SWITCH_MIN_RANKS", "3"))
-        # reduce-scatter, all-gather and broadcast take the switch from this many bytes on (the
-        # whole tensor: input of a reduce-scatter, output of an all-gather); below it the
-        # peer-memory kernels are as fast and need no staging
+        # A broadcast takes the switch from this many bytes on (measured on four B200s: 548 us
+        # against 795 us at 256 MiB, the same at 32 MiB).  Reduce-scatter and all-gather through
+        # the switch ran no faster than the peer-memory kernels there (483 against 467 us, 472
+        # against 422 us at 256 MiB), so they take it only when asked to
+        # (GPUBRIDGE_SWITCH_GATHER_MIN_BYTES; the sizes are the whole tensor: input of a
+        # reduce-scatter, output of an all-gather).
         self.switch_copy_min_bytes = _config.size_setting("GPUBRIDGE_SWITCH_COPY_MIN_BYTES", 32 << 20,
                                                           multiple=1)
+        self.switch_gather_min_bytes = _config.size_setting("GPUBRIDGE_SWITCH_GATHER_MIN_BYTES", 1 << 62,
+                                                            multiple=1)
         self.nvls_reducers = int(os.environ.get("GPUBRIDGE_NVLS_REDUCERS", "48"))
-        self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "32"))
+        self.copy_blocks = int(os.environ.get("GPUBRIDGE_COPY_BLOCKS", "128"))
         self.overlap_blocks = int(os.environ.get("GPUBRIDGE_OVERLAP_BLOCKS", "32"))
-        self.scatter_blocks = int(os.environ.get("GPUBRIDGE_SCATTER_BLOCKS", "64"))
+        self.scatter_blocks = int(os.environ.get("GPUBRIDGE_SCATTER_BLOCKS", "128"))
         # reads through the bulk-copy ring (TMA into shared memory) instead of register loads
         # ("phased": one ring run per step instead of one queue per iteration)
         ring = os.environ.get("GPUBRIDGE_RING", "phased")
@@ -504,7 +509,8 @@ class Fabric:
             ctypes.byref(self.sw_island) if self.sw_island is not None else None,
             self.switch_min_bytes, self.switch_min_ranks)
         if self.sw_team is not None:
-            self.lib.gb_engine_set_switch_copy(self._engine, self.switch_copy_min_bytes)
+            self.lib.gb_engine_set_switch_copy(self._engine, self.switch_copy_min_bytes,
+                                               self.switch_gather_min_bytes)
 
     def _switch_for(self, tensor: torch.Tensor, op: str, compression) -> "_lib.GbSwitch | None":
         """The switch group an all-reduce of ``tensor`` takes, or None for the peer-memory kernels."""
@@ -514,11 +520,14 @@ class Fabric:
             return None
         return self.sw_island if self.sw_island is not None else self.sw_team
 
-    def _switch_copy(self, total_bytes: int, *pointers: int, piece: int) -> "_lib.GbSwitch | None":
+    def _switch_copy(self, total_bytes: int, *pointers: int, piece: int,
+                     gather: bool = True) -> "_lib.GbSwitch | None":
         """The team's switch group when a copy-shaped collective of ``total_bytes`` should take
-        it (pieces and pointers in multiples of 16 bytes), else None."""
+        it (pieces and pointers in multiples of 16 bytes), else None.  ``gather``: a
+        reduce-scatter or all-gather (their own threshold) rather than a broadcast."""
+        least = self.switch_gather_min_bytes if gather else self.switch_copy_min_bytes
         if (self.sw_team is None or self.world < self.switch_min_ranks or self.algo != "auto"
-                or total_bytes < self.switch_copy_min_bytes or piece % 16
+                or total_bytes < least or piece % 16
                 or any(p % 16 for p in pointers)):
             return None
         return self.sw_team
@@ -871,7 +880,7 @@ class Fabric:
         nbytes = tensor.nbytes
         if nbytes == 0:
             return
-        switch = self._switch_copy(nbytes, tensor.data_ptr(), piece=nbytes)
+        switch = self._switch_copy(nbytes, tensor.data_ptr(), piece=nbytes, gather=False)
         current = self._begin()
         try:
             with torch.cuda.stream(self.comm_stream):

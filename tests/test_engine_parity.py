@@ -32,7 +32,7 @@ def fake_fabric(sizes, ws_bytes=384 << 20, **over):
     f.sw_team = f.sw_island = None
     f._heaps = []
     f.switch_min_bytes, f.switch_flat, f.switch_min_ranks = 64 << 10, False, 3
-    f.switch_copy_min_bytes = 32 << 20
+    f.switch_copy_min_bytes, f.switch_gather_min_bytes = 32 << 20, 1 << 62
     f.layout = types.SimpleNamespace(index=lambda r: r)
     for name, value in over.items():
         setattr(f, name, value)
@@ -239,7 +239,7 @@ def test_copy_shaped_collectives_take_the_switch_alike(sizes, monkeypatch):
                         lambda device=None: types.SimpleNamespace(cuda_stream=0))
     monkeypatch.setattr(torch.cuda, "stream", lambda s: __import__("contextlib").nullcontext())
     rng = random.Random(sum(sizes))
-    f = fake_fabric(sizes, ws_bytes=1 << 30)
+    f = fake_fabric(sizes, ws_bytes=1 << 30, switch_gather_min_bytes=rng.choice([32 << 20, 1 << 62]))
     f.lib = _RecordingLib(f.lib, f.seen)
     f.sw_team = _lib.GbSwitch()
     engine = f.engine()

@@ -137,7 +137,7 @@ def _copies(rank, topology):
     if fabric is None or fabric.sw_team is None:
         return f"unavailable: {getattr(fabric, 'switch_error', 'no fabric')}"
     dev, world = topology.device, topology.world_size
-    assert fabric.switch_copy_min_bytes == 0
+    assert fabric.switch_copy_min_bytes == fabric.switch_gather_min_bytes == 16
     before = fabric.launches
     for dtype in (torch.float32, torch.bfloat16):
         for n in (8, 1024, 70_000, (3 << 20) + 8, 6_000_000, 4099):
@@ -170,7 +170,8 @@ def _copies(rank, topology):
 @pytest.mark.skipif(NGPU < 3, reason="the switch path starts at three ranks")
 @pytest.mark.parametrize("split", [{}, {"GPUBRIDGE_SPLIT_TEST": "half"}], ids=["one-island", "half"])
 def test_copy_shaped_collectives_through_the_switch(tmp_path, split):
-    env = {"GPUBRIDGE_NVLS": "1", "GPUBRIDGE_SWITCH_COPY_MIN_BYTES": "0", **split}
+    env = {"GPUBRIDGE_NVLS": "1", "GPUBRIDGE_SWITCH_COPY_MIN_BYTES": "16",
+           "GPUBRIDGE_SWITCH_GATHER_MIN_BYTES": "16", **split}
     out = run_ranks(gpu_ranks(WORLD), _copies, tmp_path, env=env, timeout=240)
     if any(str(o).startswith("unavailable") for o in out):
         pytest.skip(f"no NVLink multicast binding on this machine ({out[0]})")
