@@ -1,6 +1,6 @@
 """Run one of the library's kernels a few times on one GPU, for ``ncu`` to capture.
 
-    python -m gpubridge_b200.bench.profile_kernels hier|oneshot|switch|xent|adamw|layernorm|quantize|dequantize|gemm
+    python -m gpubridge_b200.bench.profile_kernels hier|oneshot|switch|allgather|reducescatter|broadcast|xent|adamw|layernorm|quantize|dequantize|gemm
 
 Sizes are small enough for a full-set capture to finish in about a minute but larger than
 the 126 MB L2, so DRAM figures mean something.  ``hier`` and ``oneshot`` run one rank's side
@@ -16,7 +16,7 @@ import torch
 def main(which: str) -> int:
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    if which in ("hier", "oneshot", "gemm", "switch"):
+    if which in ("hier", "oneshot", "gemm", "switch", "allgather", "reducescatter", "broadcast"):
         from gpubridge_b200.ops import fabric as F
         team = F.create_single(device)
         if which == "gemm":
@@ -36,6 +36,18 @@ def main(which: str) -> int:
             t = torch.randn(48 << 20, device=device)              # 192 MiB: larger than L2
             for _ in range(4):
                 team.all_reduce(t)
+            torch.cuda.synchronize()
+        elif which in ("allgather", "reducescatter", "broadcast"):
+            # one rank's side of the copy-shaped collectives (stage, barrier, pull): 192 MiB
+            t = torch.randn(48 << 20, device=device)
+            out = torch.empty_like(t)
+            for _ in range(4):
+                if which == "allgather":
+                    team.all_gather(out, t)
+                elif which == "reducescatter":
+                    team.reduce_scatter(out, t)
+                else:
+                    team.broadcast(t, 0)
             torch.cuda.synchronize()
         else:
             n = (32 << 20) if which == "hier" else (64 << 10)
