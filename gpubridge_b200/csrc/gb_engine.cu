@@ -15,6 +15,9 @@ extern "C" int gb_launch_copy(int kind, const GbTeam* team, const GbArgs* args, 
 extern "C" int gb_switch_all_reduce(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
                                     size_t n, int dtype, int divide, int max_blocks,
                                     cudaStream_t stream);
+extern "C" int gb_switch_all_reduce_oneshot(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
+                                            size_t n, int dtype, int divide, int max_blocks,
+                                            cudaStream_t stream);
 extern "C" int gb_switch_reduce_scatter(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
                                         size_t n_out, int dtype, int divide, int max_blocks,
                                         cudaStream_t stream);
@@ -41,6 +44,7 @@ struct Engine {
     int sw_min_ranks = 3;
     size_t sw_copy_min_bytes = ~size_t(0);      // broadcast through the switch from this size on
     size_t sw_gather_min_bytes = ~size_t(0);    // reduce-scatter and all-gather
+    size_t sw_oneshot_max = 0;                  // the one-step all-reduce up to this size
     std::atomic<unsigned long long> launches{0};
 };
 
@@ -172,6 +176,11 @@ extern "C" int gb_engine_prepare_all_reduce(void* engine, const void* in, void* 
         L->kind = e.has_island ? 1 : 0;
         L->grid = e.c.max_blocks;
         if (grid_cap > 0 && grid_cap < L->grid) L->grid = grid_cap;
+        // one step (kind 5): the flat group, small enough, inside the slots this grid has
+        size_t blocks = 2 * size_t(L->grid);
+        if (blocks > GB_SWITCH_ONESHOT_BLOCKS) blocks = GB_SWITCH_ONESHOT_BLOCKS;
+        if (!e.has_island && nbytes <= e.sw_oneshot_max && nbytes <= blocks * GB_SWITCH_ONESHOT_SLOT)
+            L->kind = 5;
         return GB_ENGINE_OK;
     }
     if (nbytes <= e.c.oneshot_slot && e.c.algo != 2) {
@@ -295,6 +304,11 @@ extern "C" void gb_engine_set_switch(void* engine, const GbSwitch* team, const G
     e.sw_min_ranks = min_ranks;
 }
 
+// Up to how many bytes an all-reduce through the flat group takes the one-step kernel (0: never).
+extern "C" void gb_engine_set_switch_oneshot(void* engine, size_t max_bytes) {
+    static_cast<Engine*>(engine)->sw_oneshot_max = max_bytes;
+}
+
 // From how many bytes on a broadcast, and a reduce-scatter or all-gather, go through the team's
 // switch group (never, until this is called).
 extern "C" void gb_engine_set_switch_copy(void* engine, size_t broadcast_min_bytes, size_t gather_min_bytes) {
@@ -306,7 +320,10 @@ namespace {
 int launch(Engine& e, const GbLaunch& L, int dtype, int op, void* stream) {
     if (L.family == 2 && L.kind >= 2) {
         cudaStream_t on = static_cast<cudaStream_t>(stream);
-        const int rc = L.kind == 2
+        const int rc = L.kind == 5
+            ? gb_switch_all_reduce_oneshot(&e.team, &e.sw_team, L.args.in, L.args.out, L.args.n, dtype,
+                                           L.args.divide, L.grid, on)
+            : L.kind == 2
             ? gb_switch_reduce_scatter(&e.team, &e.sw_team, L.args.in, L.args.out, L.args.n, dtype,
                                        L.args.divide, L.grid, on)
             : L.kind == 3

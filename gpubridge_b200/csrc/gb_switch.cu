@@ -302,6 +302,72 @@ cudaError_t launch_inplace(const GbTeam& tm, const GbSwitch& sw, const SwArgs& a
 }
 
 
+// ---- all-reduce in one step, for small and medium tensors -------------------------------------------
+//
+// Block b copies its tile of the input into ITS slot of the reserved tail of the switch memory,
+// meets block b of every other rank once, and then ld_reduces the whole tile - not a share of
+// it - straight into the output: one barrier instead of two, no copy out, at the price of every
+// rank pulling every byte through the switch (n times the traffic of the two-step form, which
+// is why this is for a few MiB at most).  Every rank adds the same values in the switch's order,
+// so all ranks still end with identical bits.
+// A slot has two halves; a block uses half (its barrier number & 1).  Two calls in a row
+// therefore use different halves, and by the time a half comes round again the block has been
+// through a barrier that every peer joined after finishing the earlier call - so nobody still
+// reads what is overwritten.  Any other kernel in between only adds barriers.  The slots are
+// per block index and fixed in place, whatever the tile size of a call.
+template <typename T, int SW_THREADS, int U>
+__global__ void __launch_bounds__(SW_THREADS, SW_MAX_THREADS / SW_THREADS)
+allreduce_switch_oneshot_kernel(GbTeam tm, GbSwitch sw, SwArgs a) {
+    typedef typename GbAcc<T>::type A;
+    constexpr int V = SwVec<T>::N;
+    const int b = (int)blockIdx.x;
+    unsigned seq = gb_ld_volatile(sw.bseq + b) + 1u;
+    const size_t slot = sw.bytes + (size_t)(seq & 1u) * GB_SWITCH_ONESHOT_SLOT * GB_SWITCH_ONESHOT_BLOCKS +
+                        (size_t)b * GB_SWITCH_ONESHOT_SLOT;
+    char* mine = sw.uc + slot;
+    const char* everyone = sw.mc + slot;
+    const size_t off = (size_t)b * a.tile;
+    const size_t len = a.nbytes - off < a.tile ? a.nbytes - off : a.tile;
+    const size_t padded = sw_round_up(len, 16);
+    GbLane whole;
+    whole.tid = threadIdx.x; whole.nth = SW_THREADS; whole.ld = tm.ld_mode;
+    gb_copy_bytes(whole, mine, a.in + off, len, false);
+    sw_zero(mine, len, padded, (int)threadIdx.x, SW_THREADS);
+    if (!sw_block_sync(tm, sw, b, seq)) return;
+    if (b == 0 && threadIdx.x == 0) tm.ctrl->stamps[0] = gb_now();
+    char* out = a.out + off;
+    const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+    const size_t nvec = padded >> 4;
+    for (size_t v0 = threadIdx.x; v0 < nvec; v0 += (size_t)U * SW_THREADS) {
+        SwVec<T> w[U];
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const size_t v = v0 + (size_t)u * SW_THREADS;
+            if (v < nvec) w[u].u = SwitchSum<T>::load(everyone + (v << 4));
+        }
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const size_t v = v0 + (size_t)u * SW_THREADS;
+            if (v >= nvec) continue;
+            if (a.divide > 0) {
+                #pragma unroll
+                for (int j = 0; j < V; ++j)
+                    w[u].e[j] = gb_down<T>(gb_divide<A>(gb_up<T>(w[u].e[j]), a.divide));
+            }
+            if (aligned && ((v + 1) << 4) <= len) {
+                gb_st16(out + (v << 4), w[u].u);
+            } else {                                                   // a ragged end or an odd address
+                const unsigned char* bytes = reinterpret_cast<const unsigned char*>(&w[u].u);
+                for (size_t j = 0; j < 16 && (v << 4) + j < len; ++j) out[(v << 4) + j] = (char)bytes[j];
+            }
+        }
+    }
+    if (threadIdx.x == 0) {
+        sw.bseq[b] = seq;
+        if (b == 0) tm.ctrl->stamps[1] = gb_now();
+    }
+}
+
 // ---- reduce-scatter, all-gather and broadcast through the switch -----------------------------------
 //
 // The same staging memory, block-level barriers and tile ownership as the all-reduce (one group:
@@ -520,6 +586,43 @@ extern "C" int gb_switch_all_reduce(const GbTeam* team, const GbSwitch* sw, cons
     if (dtype == 0) return (int)launch_switch<float>(*team, *sw, a, plan.grid, stream);
     if (dtype == 1) return (int)launch_switch<__nv_bfloat16>(*team, *sw, a, plan.grid, stream);
     return (int)launch_switch<__half>(*team, *sw, a, plan.grid, stream);
+}
+
+// The same sum in one step (see allreduce_switch_oneshot_kernel): for tensors of at most
+// max_blocks x 16 KiB (max_blocks doubled for the half-size launch shape, 256 at most), one
+// group, flat order.  The group's memory must have GB_SWITCH_ONESHOT_RESERVE bytes behind
+// sw->bytes.  Returns a cudaError_t, -2 for a type the switch cannot add, -1 when it does not fit.
+extern "C" int gb_switch_all_reduce_oneshot(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,
+                                            size_t n, int dtype, int divide, int max_blocks,
+                                            cudaStream_t stream) {
+    if (dtype < 0 || dtype > 2) return -2;
+    const size_t nbytes = n * (dtype == 0 ? 4 : 2);
+    if (switch_shape() != 0) max_blocks *= 2;
+    if (max_blocks > GB_SWITCH_ONESHOT_BLOCKS) max_blocks = GB_SWITCH_ONESHOT_BLOCKS;
+    if (sw->hier || nbytes == 0 || max_blocks < 1 || nbytes > (size_t)max_blocks * GB_SWITCH_ONESHOT_SLOT)
+        return -1;
+    SwArgs a;
+    a.in = static_cast<const char*>(in);
+    a.out = static_cast<char*>(out);
+    a.nbytes = nbytes;
+    a.divide = divide;
+    size_t tile = ((nbytes + max_blocks - 1) / max_blocks + 127) / 128 * 128;
+    if (tile < 2048) tile = 2048;
+    a.tile = tile;
+    a.ntiles = (int)((nbytes + tile - 1) / tile);
+    const int grid = a.ntiles;
+    cudaError_t err;
+    if (switch_shape() == 0) {
+        if (dtype == 0) allreduce_switch_oneshot_kernel<float, 512, 4><<<grid, 512, 0, stream>>>(*team, *sw, a);
+        else if (dtype == 1) allreduce_switch_oneshot_kernel<__nv_bfloat16, 512, 4><<<grid, 512, 0, stream>>>(*team, *sw, a);
+        else allreduce_switch_oneshot_kernel<__half, 512, 4><<<grid, 512, 0, stream>>>(*team, *sw, a);
+    } else {
+        if (dtype == 0) allreduce_switch_oneshot_kernel<float, 256, 8><<<grid, 256, 0, stream>>>(*team, *sw, a);
+        else if (dtype == 1) allreduce_switch_oneshot_kernel<__nv_bfloat16, 256, 8><<<grid, 256, 0, stream>>>(*team, *sw, a);
+        else allreduce_switch_oneshot_kernel<__half, 256, 8><<<grid, 256, 0, stream>>>(*team, *sw, a);
+    }
+    err = cudaGetLastError();
+    return (int)err;
 }
 
 // The same sum for a tensor inside the group's switch memory, `offset` bytes from its start on

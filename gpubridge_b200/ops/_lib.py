@@ -19,6 +19,8 @@ from gpubridge_b200.ops import _build
 MAX_RANKS = 16
 STATUS_WORDS = 8
 SWITCH_MAX_BLOCKS = 320
+SWITCH_ONESHOT_SLOT, SWITCH_ONESHOT_BLOCKS = 16 << 10, 256
+SWITCH_ONESHOT_RESERVE = 2 * SWITCH_ONESHOT_SLOT * SWITCH_ONESHOT_BLOCKS
 
 DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.float64: 3,
           torch.int8: 4, torch.uint8: 5, torch.int32: 6, torch.int64: 7}
@@ -208,6 +210,10 @@ def _declare(L: ctypes.CDLL) -> None:
                                                i, i, i, vp]
     L.gb_engine_set_switch.argtypes = [vp, ctypes.POINTER(GbSwitch), ctypes.POINTER(GbSwitch), sz, i]
     L.gb_engine_set_switch_copy.argtypes = [vp, sz, sz]
+    L.gb_engine_set_switch_oneshot.argtypes = [vp, sz]
+    L.gb_engine_set_switch_oneshot.restype = None
+    L.gb_switch_all_reduce_oneshot.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), vp, vp, sz,
+                                               i, i, i, vp]
     L.gb_engine_set_switch_copy.restype = None
     L.gb_switch_plan_copy.argtypes = [ctypes.POINTER(GbSwitch), i, sz, i, ctypes.POINTER(GbSwitchPlan)]
     L.gb_switch_reduce_scatter.argtypes = [ctypes.POINTER(GbTeam), ctypes.POINTER(GbSwitch), vp, vp, sz,

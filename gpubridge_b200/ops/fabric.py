@@ -177,6 +177,12 @@ class Fabric:
         # Through the switch a GPU moves (n + 1) / n of the tensor, over peer memory 2 (n - 1) / n:
         # less from four ranks on, more at two (measured at two: the peer-memory kernels win).
         self.switch_min_ranks = int(os.environ.get("GPUBRIDGE_SWITCH_MIN_RANKS", "3"))
+        # The one-step form (copy in, one barrier, every rank reduces the whole tensor in the
+        # switch) for tensors up to this size: n times the two-step form's traffic, one barrier
+        # and two copies less.  16 MiB / world, at most 4 MiB; 0 turns it off.
+        self.switch_oneshot_max = _config.size_setting(
+            "GPUBRIDGE_SWITCH_ONESHOT_MAX_BYTES", max(1, min(4 << 20, (16 << 20) // max(1, layout.world_size))),
+            multiple=1)
         # A broadcast takes the switch from this many bytes on (measured on four B200s: 548 us
         # against 795 us at 256 MiB, the same at 32 MiB).  Reduce-scatter and all-gather through
         # the switch ran no faster than the peer-memory kernels there (483 against 467 us, 472
@@ -386,8 +392,12 @@ class Fabric:
         _lib.check(lib.gb_symm_alloc(4096, ctypes.byref(bseq)), "cudaMalloc (switch barrier numbers)")
         self._bseq = bseq.value
         self._switch_groups = groups
+        # the one-step all-reduce's slots sit behind what the staging kernels may use
+        reserve = _lib.SWITCH_ONESHOT_RESERVE if team_group.bytes >= 4 * _lib.SWITCH_ONESHOT_RESERVE else 0
+        if not reserve:
+            self.switch_oneshot_max = 0
         self.sw_team = _switch.describe(team_group, me, self.world, False, self.off_swflags, 0, 0,
-                                        self._bseq)
+                                        self._bseq, reserve)
         if island_group is not None:
             self.sw_island = _switch.describe(island_group, me, self.k, True, self.off_swflags,
                                               self.off_swbridge, self.len_swbridge, self._bseq)
@@ -410,13 +420,22 @@ class Fabric:
                 self.switch_error = "the team's group failed its first sum; in-switch reduction is off"
                 self._release_switch()
                 return False
+            if self.switch_oneshot_max and not everyone("check-one-step", self._commission(self.sw_team, True)):
+                self.switch_error = "the one-step all-reduce failed its first sum; it stays off"
+                self.switch_oneshot_max = 0
+                self.lib.gb_memset_async(self._bseq, 0, 4096, None)
+                self.lib.gb_memset_async(self.ws[self.rank] + self.off_swflags, 0,
+                                         _lib.SWITCH_MAX_BLOCKS * _lib.MAX_RANKS * 4, None)
+                self.lib.gb_device_synchronize()
+                everyone("flags-reset-2", True)
         if self._engine:
             self._engine_switch()
         return True
 
-    def _commission(self, switch) -> bool:
-        """One all-reduce of 96 Ki integer-valued floats through ``switch``; True when this rank
-        got the exact sum in time.  Never raises; clears a timeout it caused."""
+    def _commission(self, switch, one_step: bool = False) -> bool:
+        """One all-reduce of 96 Ki integer-valued floats through ``switch`` (``one_step``: by the
+        one-step kernel); True when this rank got the exact sum in time.  Never raises; clears
+        a timeout it caused."""
         n, world = 96 << 10, self.world
         ramp = (torch.arange(n, device=self.device) % 13).float()
         mine, out = ramp + self.rank, torch.full((n,), -1.0, device=self.device)
@@ -426,9 +445,9 @@ class Fabric:
         try:
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
-                code = self.lib.gb_switch_all_reduce(ctypes.byref(self.team), ctypes.byref(switch),
-                                                     mine.data_ptr(), out.data_ptr(), n, 0, 0, 16,
-                                                     self.comm_stream.cuda_stream)
+                entry = self.lib.gb_switch_all_reduce_oneshot if one_step else self.lib.gb_switch_all_reduce
+                code = entry(ctypes.byref(self.team), ctypes.byref(switch), mine.data_ptr(),
+                             out.data_ptr(), n, 0, 0, 16, self.comm_stream.cuda_stream)
             self.comm_stream.synchronize()
             good = code == 0 and self._status[0] == 0 and bool(torch.equal(out, want))
         except Exception:  # noqa: BLE001 - any failure means "not this way"
@@ -513,6 +532,7 @@ class Fabric:
         if self.sw_team is not None:
             self.lib.gb_engine_set_switch_copy(self._engine, self.switch_copy_min_bytes,
                                                self.switch_gather_min_bytes)
+            self.lib.gb_engine_set_switch_oneshot(self._engine, self.switch_oneshot_max)
 
     def _switch_for(self, tensor: torch.Tensor, op: str, compression) -> "_lib.GbSwitch | None":
         """The switch group an all-reduce of ``tensor`` takes, or None for the peer-memory kernels."""
@@ -533,6 +553,14 @@ class Fabric:
                 or any(p % 16 for p in pointers)):
             return None
         return self.sw_team
+
+    def _one_step(self, switch, nbytes: int) -> bool:
+        """Whether an all-reduce of ``nbytes`` through ``switch`` takes the one-step kernel: the
+        flat group only, small enough, and inside the slots the calling thread's grid has."""
+        limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))
+        blocks = min(2 * limit, _lib.SWITCH_ONESHOT_BLOCKS)
+        return (not switch.hier and nbytes <= self.switch_oneshot_max
+                and nbytes <= blocks * _lib.SWITCH_ONESHOT_SLOT)
 
     def _launch_switch_copy(self, call, what: str) -> None:
         limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))
@@ -696,6 +724,14 @@ class Fabric:
                         _lib.DTYPES[tensor.dtype], args.divide, limit,
                         torch.cuda.current_stream(self.device).cuda_stream)
                     _lib.check(code, "gb_switch_all_reduce_inplace")
+                    self.launches += 1
+                elif switch is not None and self._one_step(switch, nbytes):
+                    limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))
+                    code = self.lib.gb_switch_all_reduce_oneshot(
+                        ctypes.byref(self.team), ctypes.byref(switch), args.inp, args.out, n,
+                        _lib.DTYPES[tensor.dtype], args.divide, limit,
+                        torch.cuda.current_stream(self.device).cuda_stream)
+                    _lib.check(code, "gb_switch_all_reduce_oneshot")
                     self.launches += 1
                 elif switch is not None:
                     limit = min(self.max_blocks, getattr(self._caps, "value", 1 << 30))

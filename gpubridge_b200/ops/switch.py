@@ -202,10 +202,11 @@ def supported(lib, device: int) -> bool:
 
 
 def describe(group: Group, me: int, owners: int, hier: bool, off_flags: int, off_bridge: int,
-             len_bridge: int, bseq: int) -> "_lib.GbSwitch":
-    """The structure the kernels take."""
+             len_bridge: int, bseq: int, reserve: int = 0) -> "_lib.GbSwitch":
+    """The structure the kernels take.  ``reserve``: bytes at the end of the group's memory that
+    the staging kernels must leave alone (the one-step all-reduce's slots live there)."""
     sw = _lib.GbSwitch()
-    sw.uc, sw.mc, sw.bytes = group.local, group.multicast, group.bytes
+    sw.uc, sw.mc, sw.bytes = group.local, group.multicast, group.bytes - reserve
     sw.off_flags, sw.off_bridge, sw.len_bridge = off_flags, off_bridge, len_bridge
     sw.bseq = bseq
     sw.group_size, sw.group_pos = len(group.members), group.members.index(me)

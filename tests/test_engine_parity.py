@@ -33,6 +33,7 @@ def fake_fabric(sizes, ws_bytes=384 << 20, **over):
     f._heaps = []
     f.switch_min_bytes, f.switch_flat, f.switch_min_ranks = 64 << 10, False, 3
     f.switch_copy_min_bytes, f.switch_gather_min_bytes = 32 << 20, 1 << 62
+    f.switch_oneshot_max = min(4 << 20, (16 << 20) // f.world)
     f.layout = types.SimpleNamespace(index=lambda r: r)
     for name, value in over.items():
         setattr(f, name, value)
@@ -167,6 +168,10 @@ class _RecordingLib:
         self._seen.append((2, switch._obj.hier, limit, inp, out, n, divide))
         return 0
 
+    def gb_switch_all_reduce_oneshot(self, team, switch, inp, out, n, dtype, divide, limit, stream):
+        self._seen.append((2, 5, limit, inp, out, n, divide))
+        return 0
+
     def gb_switch_reduce_scatter(self, team, switch, inp, out, n, dtype, divide, limit, stream):
         self._seen.append((2, 2, limit, inp, out, n, divide))
         return 0
@@ -205,7 +210,8 @@ def test_the_in_switch_all_reduce_is_chosen_alike(sizes, islands_have_groups, mo
         for op in ("sum", "max"):
             for _ in range(10):
                 n = rng.choice([256, (64 << 10) // esize - 1, (64 << 10) // esize, 1 << 20,
-                                rng.randrange(1, 1 << 24)])
+                                (512 << 10) // esize, (512 << 10) // esize + 1, (2 << 20) // esize,
+                                (4 << 20) // esize, rng.randrange(1, 1 << 24)])
                 inp = 1 << 30
                 fake = types.SimpleNamespace(
                     numel=lambda n=n: n, nbytes=n * esize, dtype=dtype, data_ptr=lambda: inp,
