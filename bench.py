@@ -230,6 +230,8 @@ def run_ours(args) -> dict:
         result["config"]["in_switch_reduction"] = bool(
             topology.fabric is not None and topology.fabric.sw_team is not None)
         result["config"]["gradients_in_switch_memory"] = bool(getattr(trainer, "grads_in_switch", False))
+        result["config"]["bucket_ctas"] = trainer.overlap_blocks
+        result["config"]["updates_inside_backward"] = bool(trainer.optimizer_in_backward)
     if not args.no_hook_arm:
         del trainer, e2e_steps
         torch.cuda.empty_cache()
