@@ -54,7 +54,7 @@ class DataParallelTrainer:
             parameters again before the next forward); only the last bucket's update is left
             for after backward.  The arithmetic and its result are those of one optimizer
             call after backward.  ``GPUBRIDGE_OPTIMIZER_IN_BACKWARD``: ``1``, ``0``, or unset =
-            on teams whose gradients live in switch memory (three ranks or more on an NVSwitch).
+            on a team of two or more only (alone it costs more than it hides).
     """
 
     def __init__(self, model: nn.Module, loss_fn, *, topology: Topology | None = None,
@@ -89,11 +89,7 @@ class DataParallelTrainer:
         # then run in place inside the NVSwitch (no staging copies, a handful of SMs), which is
         # what lets them hide under backward.  Collective: every rank builds its trainer.
         in_switch = None
-        # With two ranks the switch saves no traffic (measured: 15.0 ms a step with the gradients in
-        # switch memory against 14.4 ms with the peer-memory kernels), so only teams that take the
-        # switch path for their all-reduces keep their gradients there.
-        if (self.fabric is not None and self.world >= max(2, getattr(self.fabric, "switch_min_ranks", 3))
-                and hasattr(self.fabric, "switch_empty")):
+        if self.fabric is not None and self.world > 1 and hasattr(self.fabric, "switch_empty"):
             in_switch = self.fabric.switch_empty(total, torch.float32)
         self.grads_in_switch = in_switch is not None
         if not self.overlap_blocks:
@@ -103,14 +99,12 @@ class DataParallelTrainer:
             self.overlap_blocks = 8 if self.grads_in_switch else 32
         # Alone, an update beside backward costs more than it hides (13.7 ms a step after
         # backward, 14.3-14.9 inside it: every kernel that shares the GPU delays cuBLAS's
-        # persistent GEMMs); on a team whose buckets are reduced in the switch the updates follow
-        # the bucket all-reduces, which are there anyway, and the step gets about 0.1 ms shorter
-        # (measured on four GPUs).  Teams on the peer-memory kernels keep the one update after
-        # backward they were measured with.
+        # persistent GEMMs); on a team the updates follow the bucket all-reduces, which are
+        # there anyway, and the step gets about 0.1 ms shorter.
         wanted = self._in_backward_wanted
         if wanted is None:
             wanted = os.environ.get("GPUBRIDGE_OPTIMIZER_IN_BACKWARD", "auto")
-            wanted = self.grads_in_switch if wanted == "auto" else wanted == "1"
+            wanted = self.world > 1 if wanted == "auto" else wanted == "1"
         self.optimizer_in_backward = bool(wanted)
         self.flat_grad = in_switch if in_switch is not None else \
             torch.zeros(total, dtype=torch.float32, device=self.device)
