@@ -41,7 +41,7 @@ class DataParallelTrainer:
         autocast: dtype of ``torch.autocast`` around forward, or None.
         graph: capture the step in a CUDA graph after ``graph_warmup`` eager steps.
         overlap_blocks: CTAs of a bucket all-reduce that runs beside backward
-            (``GPUBRIDGE_OVERLAP_BLOCKS``; default 8 when the gradients live in switch memory,
+            (``GPUBRIDGE_OVERLAP_BLOCKS``; default 16 when the gradients live in switch memory,
             else 32); the last bucket uses the full grid.
         unit_grad: tell a model that has a ``unit_grad`` switch that backward starts at its
             loss with gradient 1 (its fused loss then skips the multiply); pass False when
@@ -93,10 +93,10 @@ class DataParallelTrainer:
             in_switch = self.fabric.switch_empty(total, torch.float32)
         self.grads_in_switch = in_switch is not None
         if not self.overlap_blocks:
-            # measured on four B200s: in place in the switch 8 CTAs keep up with the buckets
-            # and cost backward the least (14.67 ms a step against 14.80 with 32); the
-            # peer-memory kernels need their 32
-            self.overlap_blocks = 8 if self.grads_in_switch else 32
+            # measured: in place in the switch 8-16 CTAs keep up with the buckets and cost
+            # backward the least (four B200s: 14.67 / 14.69 ms a step with 8 / 16 against 14.80
+            # with 32; two: 14.88 / 14.67 with 8 / 16); the peer-memory kernels need their 32
+            self.overlap_blocks = 16 if self.grads_in_switch else 32
         # Alone, an update beside backward costs more than it hides (13.7 ms a step after
         # backward, 14.3-14.9 inside it: every kernel that shares the GPU delays cuBLAS's
         # persistent GEMMs); on a team the updates follow the bucket all-reduces, which are
