@@ -589,7 +589,7 @@ extern "C" int gb_switch_all_reduce(const GbTeam* team, const GbSwitch* sw, cons
 }
 
 // The same sum in one step (see allreduce_switch_oneshot_kernel): for tensors of at most
-// max_blocks x 16 KiB (max_blocks doubled for the half-size launch shape, 256 at most), one
+// max_blocks x 32 KiB (max_blocks doubled for the half-size launch shape, 128 at most), one
 // group, flat order.  The group's memory must have GB_SWITCH_ONESHOT_RESERVE bytes behind
 // sw->bytes.  Returns a cudaError_t, -2 for a type the switch cannot add, -1 when it does not fit.
 extern "C" int gb_switch_all_reduce_oneshot(const GbTeam* team, const GbSwitch* sw, const void* in, void* out,

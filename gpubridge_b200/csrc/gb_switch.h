@@ -7,8 +7,8 @@
 
 // The one-step all-reduce keeps two halves of fixed per-block slots BEHIND `bytes` of a group's
 // switch memory (the host reserves them: GbSwitch::bytes excludes this tail).
-#define GB_SWITCH_ONESHOT_SLOT (16u << 10)       // bytes of one block's slot
-#define GB_SWITCH_ONESHOT_BLOCKS 256             // slots per half
+#define GB_SWITCH_ONESHOT_SLOT (32u << 10)       // bytes of one block's slot
+#define GB_SWITCH_ONESHOT_BLOCKS 128             // slots per half (more blocks cost more at the barrier than they gain)
 #define GB_SWITCH_ONESHOT_RESERVE (2u * GB_SWITCH_ONESHOT_SLOT * GB_SWITCH_ONESHOT_BLOCKS)   // 8 MiB
 
 // One rank's view of the switch memory of its group (the team, or its island).

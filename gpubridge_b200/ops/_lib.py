@@ -19,7 +19,7 @@ from gpubridge_b200.ops import _build
 MAX_RANKS = 16
 STATUS_WORDS = 8
 SWITCH_MAX_BLOCKS = 320
-SWITCH_ONESHOT_SLOT, SWITCH_ONESHOT_BLOCKS = 16 << 10, 256
+SWITCH_ONESHOT_SLOT, SWITCH_ONESHOT_BLOCKS = 32 << 10, 128
 SWITCH_ONESHOT_RESERVE = 2 * SWITCH_ONESHOT_SLOT * SWITCH_ONESHOT_BLOCKS
 
 DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.float64: 3,
