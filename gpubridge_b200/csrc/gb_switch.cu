@@ -537,7 +537,11 @@ extern "C" int gb_switch_plan(const GbSwitch* sw, int n_islands, size_t nbytes, 
                               GbSwitchPlan* plan) {
     const int depth = sw->hier ? 4 : 3;
     const size_t unit = 16 * (size_t)sw->owners * 8;           // stripes of whole 128-byte lines
-    if (switch_shape() != 0) max_blocks *= 2;                  // half-size blocks, two per SM
+    // half-size blocks, two per SM - from 64 MiB on: below that the barrier (whose cost grows with
+    // the number of blocks) weighs more than the second block per SM gains (measured on four
+    // B200s: 8 / 16 / 32 MiB in 58 / 84 / 128 us on 128 blocks against 69 / 90 / 137 us on 256;
+    // 256 MiB in 707 us on 256 against 765 us on 128)
+    if (switch_shape() != 0 && nbytes >= ((size_t)64 << 20)) max_blocks *= 2;
     if (max_blocks > GB_SWITCH_MAX_BLOCKS) max_blocks = GB_SWITCH_MAX_BLOCKS;
     if (max_blocks < 1 || nbytes == 0) return -1;
     const size_t floor_tile = (8192 + unit - 1) / unit * unit;
