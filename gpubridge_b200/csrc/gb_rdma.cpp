@@ -54,6 +54,12 @@
 #include <thread>
 #include <vector>
 
+#include <cerrno>
+#include <poll.h>
+#include <sys/socket.h>
+#include <sys/un.h>
+#include <unistd.h>
+
 #include "gb_tagged.h"
 
 namespace {
@@ -274,6 +280,311 @@ int MockProvider::post_write(int peer, uint64_t wr_id, const void* local, uint64
     return 0;
 }
 
+// ---- a provider over Unix-domain sockets: members in different processes of one host ------------------
+//
+// The same queue-pair semantics as the in-process fabric, carried over one stream socket per
+// pair of members (abstract socket names, so nothing is left in the file system): a SEND is
+// matched to the receive posted for (source, lane) and completes at both ends; a WRITE names a
+// registered region of the destination and lands there without the destination's endpoint
+// taking part, completing at the source when the destination has acknowledged it (refused, with
+// "remote access", when the key or the range is not registered any more).  A reader and a
+// writer thread per connection: posting never blocks the caller, and a reader never waits for
+// the endpoint above it (credits guarantee a posted receive for every SEND), so the sockets
+// always drain.  A peer that goes away flushes everything posted for it.  This is what lets the
+// whole bridge run between processes where no adapter exists; it is not a fast path.
+struct SocketProvider : Provider {
+    enum Frame : uint32_t { FR_SEND = 1, FR_WRITE = 2, FR_ACK = 3 };
+    struct Wire { uint32_t type, lane; uint64_t wr_id, remote; uint32_t rkey, len; };   // 32 bytes
+    struct Out { Wire w; const char* data; int opcode; };
+    struct Link {
+        int fd = -1;
+        std::thread reader, writer;
+        std::mutex mu;
+        std::condition_variable cv;
+        std::deque<Out> queue;
+        bool gone = false;
+    };
+    int index, count;
+    int listener = -1;
+    std::vector<std::unique_ptr<Link>> links;
+    std::mutex mu;
+    std::condition_variable cv, posted_cv;
+    std::deque<Completion> cq;
+    struct Posted { uint64_t wr_id; char* buf; uint32_t len; };
+    std::map<std::pair<int, int>, std::deque<Posted>> recvs;
+    struct Region { char* base; size_t len; };
+    std::map<uint32_t, Region> regions;
+    uint32_t next_key = 0x2000;
+    bool woken = false, closing = false;
+
+    SocketProvider(int i, int n) : index(i), count(n) {
+        for (int p = 0; p < n; ++p) links.emplace_back(new Link());
+    }
+    ~SocketProvider() override { shutdown_all(); }
+
+    static sockaddr_un address(const std::string& name, socklen_t* len) {
+        sockaddr_un a;
+        std::memset(&a, 0, sizeof(a));
+        a.sun_family = AF_UNIX;
+        const size_t n = name.size() < sizeof(a.sun_path) - 2 ? name.size() : sizeof(a.sun_path) - 2;
+        std::memcpy(a.sun_path + 1, name.data(), n);            // leading NUL: the abstract namespace
+        *len = (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + n);
+        return a;
+    }
+    bool listen_on(const std::string& name) {
+        listener = ::socket(AF_UNIX, SOCK_STREAM, 0);
+        if (listener < 0) return false;
+        socklen_t len;
+        sockaddr_un a = address(name, &len);
+        return ::bind(listener, reinterpret_cast<sockaddr*>(&a), len) == 0 && ::listen(listener, 64) == 0;
+    }
+    static bool write_all(int fd, const void* data, size_t n) {
+        const char* p = static_cast<const char*>(data);
+        while (n) {
+            const ssize_t k = ::send(fd, p, n, MSG_NOSIGNAL);
+            if (k <= 0) { if (k < 0 && errno == EINTR) continue; return false; }
+            p += k; n -= (size_t)k;
+        }
+        return true;
+    }
+    static bool read_all(int fd, void* data, size_t n) {
+        char* p = static_cast<char*>(data);
+        while (n) {
+            const ssize_t k = ::recv(fd, p, n, 0);
+            if (k <= 0) { if (k < 0 && errno == EINTR) continue; return false; }
+            p += k; n -= (size_t)k;
+        }
+        return true;
+    }
+    // Members with a lower index dial; every connection opens with the dialler's index.
+    bool connect_all(const std::vector<std::string>& names, double timeout_s, std::string* why) {
+        const auto deadline = Clock::now() + std::chrono::duration<double>(timeout_s);
+        for (int p = index + 1; p < count; ++p) {
+            socklen_t len;
+            sockaddr_un a = address(names[p], &len);
+            int fd = -1;
+            for (;;) {
+                fd = ::socket(AF_UNIX, SOCK_STREAM, 0);
+                if (fd >= 0 && ::connect(fd, reinterpret_cast<sockaddr*>(&a), len) == 0) break;
+                if (fd >= 0) ::close(fd);
+                if (Clock::now() > deadline) { *why = "member " + std::to_string(p) + " never listened"; return false; }
+                std::this_thread::sleep_for(std::chrono::milliseconds(20));
+            }
+            const uint32_t me = (uint32_t)index;
+            if (!write_all(fd, &me, 4)) { *why = "handshake failed"; ::close(fd); return false; }
+            links[p]->fd = fd;
+        }
+        for (int got = 0; got < index; ++got) {
+            pollfd wait{listener, POLLIN, 0};
+            const auto left = std::chrono::duration_cast<std::chrono::milliseconds>(deadline - Clock::now()).count();
+            if (left <= 0 || ::poll(&wait, 1, (int)left) <= 0) { *why = "a lower member never dialled"; return false; }
+            const int fd = ::accept(listener, nullptr, nullptr);
+            uint32_t who = 0;
+            if (fd < 0 || !read_all(fd, &who, 4) || (int)who >= index || links[who]->fd >= 0) {
+                if (fd >= 0) ::close(fd);
+                *why = "a connection with no valid member index";
+                return false;
+            }
+            links[who]->fd = fd;
+        }
+        ::close(listener);
+        listener = -1;
+        for (int p = 0; p < count; ++p) {
+            if (p == index) continue;
+            Link* l = links[p].get();
+            l->reader = std::thread([this, p] { read_loop(p); });
+            l->writer = std::thread([this, p] { write_loop(p); });
+        }
+        return true;
+    }
+    void complete(const Completion& c) {
+        { std::lock_guard<std::mutex> hold(mu); cq.push_back(c); }
+        cv.notify_all();
+    }
+    void flush_peer(int peer) {
+        std::deque<Posted> lost;
+        {
+            std::lock_guard<std::mutex> hold(mu);
+            for (int lane = 0; lane < 2; ++lane) {
+                auto& q = recvs[{peer, lane}];
+                while (!q.empty()) { lost.push_back(q.front()); q.pop_front(); }
+            }
+        }
+        for (const Posted& r : lost) {
+            Completion c; c.wr_id = r.wr_id; c.status = ST_FLUSHED; c.opcode = OC_RECV; c.peer = peer;
+            complete(c);
+        }
+        Link& l = *links[peer];
+        std::deque<Out> unsent;
+        { std::lock_guard<std::mutex> hold(l.mu); l.gone = true; unsent.swap(l.queue); }
+        l.cv.notify_all();
+        posted_cv.notify_all();
+        for (const Out& o : unsent) {
+            Completion c; c.wr_id = o.w.wr_id; c.status = ST_FLUSHED; c.opcode = o.opcode; c.peer = peer;
+            complete(c);
+        }
+    }
+    void write_loop(int peer) {
+        Link& l = *links[peer];
+        for (;;) {
+            Out o;
+            {
+                std::unique_lock<std::mutex> hold(l.mu);
+                l.cv.wait(hold, [&] { return l.gone || !l.queue.empty(); });
+                if (l.gone) return;
+                o = l.queue.front();
+                l.queue.pop_front();
+            }
+            const bool ok = write_all(l.fd, &o.w, sizeof(Wire)) && (o.w.len == 0 || o.data == nullptr ||
+                                                                    write_all(l.fd, o.data, o.w.len));
+            if (o.w.type == FR_ACK) { if (!ok) { flush_peer(peer); return; } continue; }
+            if (!ok) {
+                Completion c; c.wr_id = o.w.wr_id; c.status = ST_FLUSHED; c.opcode = o.opcode; c.peer = peer;
+                complete(c);
+                flush_peer(peer);
+                return;
+            }
+            if (o.w.type == FR_SEND) {                 // a WRITE completes when its acknowledgement arrives
+                Completion c; c.wr_id = o.w.wr_id; c.opcode = OC_SEND; c.peer = peer;
+                complete(c);
+            }
+        }
+    }
+    void read_loop(int peer) {
+        Link& l = *links[peer];
+        std::vector<char> sink;
+        for (;;) {
+            Wire w;
+            if (!read_all(l.fd, &w, sizeof(Wire))) break;
+            if (w.type == FR_SEND) {
+                Posted slot{0, nullptr, 0};
+                {
+                    std::unique_lock<std::mutex> hold(mu);
+                    posted_cv.wait(hold, [&] { return closing || !recvs[{peer, (int)w.lane}].empty(); });
+                    if (closing) return;
+                    slot = recvs[{peer, (int)w.lane}].front();
+                    recvs[{peer, (int)w.lane}].pop_front();
+                }
+                Completion c; c.wr_id = slot.wr_id; c.opcode = OC_RECV; c.peer = peer;
+                if (w.len > slot.len) {
+                    sink.resize(w.len);
+                    if (!read_all(l.fd, sink.data(), w.len)) break;
+                    c.status = ST_LENGTH;
+                } else {
+                    if (w.len && !read_all(l.fd, slot.buf, w.len)) { c.status = ST_FLUSHED; complete(c); break; }
+                    c.bytes = w.len;
+                }
+                complete(c);
+            } else if (w.type == FR_WRITE) {
+                char* at = reinterpret_cast<char*>(w.remote);
+                bool allowed;
+                {
+                    // the registration is held for the length of the copy: a region that is
+                    // dropped while data lands would be memory the caller already reuses
+                    std::unique_lock<std::mutex> hold(mu);
+                    auto it = regions.find(w.rkey);
+                    allowed = it != regions.end() && at >= it->second.base &&
+                              at + w.len <= it->second.base + it->second.len;
+                    if (allowed) {
+                        if (w.len && !read_all(l.fd, at, w.len)) { hold.unlock(); goto out; }
+                    }
+                }
+                if (!allowed) {
+                    sink.resize(w.len);
+                    if (w.len && !read_all(l.fd, sink.data(), w.len)) break;
+                }
+                Out ack;
+                ack.w = Wire{FR_ACK, (uint32_t)(allowed ? ST_OK : ST_REMOTE_ACCESS), w.wr_id, 0, 0, 0};
+                ack.data = nullptr; ack.opcode = OC_WRITE;
+                { std::lock_guard<std::mutex> hold(l.mu); if (!l.gone) l.queue.push_back(ack); }
+                l.cv.notify_all();
+            } else if (w.type == FR_ACK) {
+                Completion c; c.wr_id = w.wr_id; c.opcode = OC_WRITE; c.peer = peer; c.status = (int)w.lane;
+                complete(c);
+            } else {
+                break;                                 // not this protocol
+            }
+        }
+    out:
+        if (!closing) flush_peer(peer);
+    }
+    int enqueue(int peer, const Out& o) {
+        Link& l = *links[peer];
+        bool gone;
+        { std::lock_guard<std::mutex> hold(l.mu); gone = l.gone || l.fd < 0; if (!gone) l.queue.push_back(o); }
+        if (gone) {
+            Completion c; c.wr_id = o.w.wr_id; c.status = ST_FLUSHED; c.opcode = o.opcode; c.peer = peer;
+            complete(c);
+        } else {
+            l.cv.notify_all();
+        }
+        return 0;
+    }
+    int post_recv(int peer, int lane, uint64_t wr_id, void* buf, uint32_t len) override {
+        bool gone;
+        { std::lock_guard<std::mutex> hold(links[peer]->mu); gone = links[peer]->gone; }
+        if (gone) {
+            Completion c; c.wr_id = wr_id; c.status = ST_FLUSHED; c.opcode = OC_RECV; c.peer = peer;
+            complete(c);
+            return 0;
+        }
+        { std::lock_guard<std::mutex> hold(mu); recvs[{peer, lane}].push_back(Posted{wr_id, static_cast<char*>(buf), len}); }
+        posted_cv.notify_all();
+        return 0;
+    }
+    int post_send(int peer, int lane, uint64_t wr_id, const void* buf, uint32_t len) override {
+        Out o;
+        o.w = Wire{FR_SEND, (uint32_t)lane, wr_id, 0, 0, len};
+        o.data = static_cast<const char*>(buf); o.opcode = OC_SEND;
+        return enqueue(peer, o);
+    }
+    int post_write(int peer, uint64_t wr_id, const void* local, uint64_t remote, uint32_t rkey,
+                   uint32_t len) override {
+        Out o;
+        o.w = Wire{FR_WRITE, 0, wr_id, remote, rkey, len};
+        o.data = static_cast<const char*>(local); o.opcode = OC_WRITE;
+        return enqueue(peer, o);
+    }
+    int poll(Completion* out, int max, int timeout_ms) override {
+        std::unique_lock<std::mutex> hold(mu);
+        if (cq.empty() && timeout_ms > 0)
+            cv.wait_for(hold, std::chrono::milliseconds(timeout_ms), [&] { return !cq.empty() || woken; });
+        woken = false;
+        int n = 0;
+        while (n < max && !cq.empty()) { out[n++] = cq.front(); cq.pop_front(); }
+        return n;
+    }
+    int reg(void* addr, size_t len, uint32_t* rkey) override {
+        std::lock_guard<std::mutex> hold(mu);
+        *rkey = next_key++;
+        regions[*rkey] = Region{static_cast<char*>(addr), len};
+        return 0;
+    }
+    int dereg(uint32_t rkey) override {
+        std::lock_guard<std::mutex> hold(mu);              // waits for a copy into the region to end
+        return regions.erase(rkey) ? 0 : -1;
+    }
+    void wake() override {
+        { std::lock_guard<std::mutex> hold(mu); woken = true; }
+        cv.notify_all();
+    }
+    void shutdown_all() {
+        { std::lock_guard<std::mutex> hold(mu); if (closing) return; closing = true; regions.clear(); recvs.clear(); }
+        posted_cv.notify_all();
+        if (listener >= 0) { ::close(listener); listener = -1; }
+        for (auto& l : links) {
+            if (l->fd >= 0) ::shutdown(l->fd, SHUT_RDWR);
+            { std::lock_guard<std::mutex> hold(l->mu); l->gone = true; }
+            l->cv.notify_all();
+        }
+        for (auto& l : links) {
+            if (l->reader.joinable()) l->reader.join();
+            if (l->writer.joinable()) l->writer.join();
+            if (l->fd >= 0) { ::close(l->fd); l->fd = -1; }
+        }
+    }
+};
+
 // ---- registrations of user memory, cached ---------------------------------------------------------------
 struct MrCache {
     struct Entry { char* base; size_t len; uint32_t rkey; };
@@ -399,6 +710,7 @@ struct Op {
 struct Endpoint : GbTaggedWorker {
     Provider* provider = nullptr;
     MockFabric* mock = nullptr;
+    std::unique_ptr<Provider> owned;               // a provider that lives and dies with this endpoint
     int me = 0, count = 0;
     Config cfg;
     std::mutex mu;
@@ -815,16 +1127,66 @@ const char* gb_rdma_mock_stats(void* fabric) {
     return g_text.c_str();
 }
 
+// A provider over Unix-domain sockets for member `index` of `members`, listening under `name`
+// (an abstract socket name; every member publishes its own and connects with all of them).
+void* gb_rdma_socket_provider(int index, int members, const char* name) {
+    if (members < 1 || members > 64 || index < 0 || index >= members || name == nullptr) return nullptr;
+    SocketProvider* p = new SocketProvider(index, members);
+    if (!p->listen_on(name)) { delete p; return nullptr; }
+    return p;
+}
+
+// Connect with every member (names[i]: member i's socket name).  0, or -1 with the reason in
+// gb_rdma_socket_error().
+int gb_rdma_socket_connect(void* provider, const char* const* names, double timeout_s) {
+    SocketProvider* p = static_cast<SocketProvider*>(provider);
+    std::vector<std::string> all;
+    for (int i = 0; i < p->count; ++i) all.push_back(names[i] ? names[i] : "");
+    std::string why;
+    if (p->connect_all(all, timeout_s, &why)) return 0;
+    g_text = why;
+    return -1;
+}
+const char* gb_rdma_socket_error() { return g_text.c_str(); }
+void gb_rdma_socket_free(void* provider) { delete static_cast<SocketProvider*>(provider); }
+
+namespace {
+Endpoint* make_endpoint(Provider* provider, MockFabric* fabric, int index, int count, unsigned eager_max,
+                        unsigned data_slots, unsigned ctrl_slots, unsigned max_write,
+                        unsigned long long unexpected_max, unsigned mr_cache);
+}
+
+// An endpoint over a connected socket provider; it owns the provider from here on.
+void* gb_rdma_create_on(void* provider, unsigned eager_max, unsigned data_slots, unsigned ctrl_slots,
+                        unsigned max_write, unsigned long long unexpected_max, unsigned mr_cache) {
+    SocketProvider* p = static_cast<SocketProvider*>(provider);
+    if (p == nullptr) return nullptr;
+    Endpoint* e = make_endpoint(p, nullptr, p->index, p->count, eager_max, data_slots, ctrl_slots, max_write,
+                                unexpected_max, mr_cache);
+    e->owned.reset(p);
+    return e;
+}
+
 // Member `index` of the fabric.  Zero for a setting keeps its default.
 void* gb_rdma_create(void* fabric, int index, unsigned eager_max, unsigned data_slots, unsigned ctrl_slots,
                      unsigned max_write, unsigned long long unexpected_max, unsigned mr_cache) {
     MockFabric* f = static_cast<MockFabric*>(fabric);
     if (f == nullptr || index < 0 || index >= (int)f->members.size()) return nullptr;
+    return make_endpoint(f->members[index].get(), f, index, (int)f->members.size(), eager_max, data_slots,
+                         ctrl_slots, max_write, unexpected_max, mr_cache);
+}
+
+}  // extern "C"
+
+namespace {
+Endpoint* make_endpoint(Provider* provider, MockFabric* fabric, int index, int count, unsigned eager_max,
+                        unsigned data_slots, unsigned ctrl_slots, unsigned max_write,
+                        unsigned long long unexpected_max, unsigned mr_cache) {
     Endpoint* e = new Endpoint();
-    e->provider = f->members[index].get();
-    e->mock = f;
+    e->provider = provider;
+    e->mock = fabric;
     e->me = index;
-    e->count = (int)f->members.size();
+    e->count = count;
     if (eager_max) e->cfg.eager_max = eager_max;
     if (data_slots) e->cfg.data_slots = data_slots;
     if (ctrl_slots) e->cfg.ctrl_slots = ctrl_slots < 2 ? 2 : ctrl_slots;
@@ -844,6 +1206,9 @@ void* gb_rdma_create(void* fabric, int index, unsigned eager_max, unsigned data_
     e->progress = std::thread([e] { e->loop(); });
     return e;
 }
+}  // namespace
+
+extern "C" {
 
 long gb_rdma_send(void* ep, int peer, const void* data, unsigned long long length, unsigned long long tag) {
     return static_cast<Endpoint*>(ep)->send(peer, data, length, tag);
@@ -891,6 +1256,7 @@ void gb_rdma_close(void* ep) {
     e->provider->wake();
     if (e->progress.joinable()) e->progress.join();
     e->mrs->clear();
+    if (e->owned) static_cast<SocketProvider*>(e->owned.get())->shutdown_all();   // nothing lands any more
     if (e->mock != nullptr) {                              // nothing may land in this member's buffers any more
         std::lock_guard<std::mutex> order(e->mock->mu);
         e->mock->dead[e->me] = true;

@@ -57,6 +57,14 @@ def _library():
             getattr(L, name).argtypes = [vp]
         L.gb_rdma_abort.restype = L.gb_rdma_close.restype = None
         L.gb_rdma_abort.argtypes = L.gb_rdma_close.argtypes = [vp]
+        L.gb_rdma_socket_provider.restype = vp
+        L.gb_rdma_socket_provider.argtypes = [i, i, ctypes.c_char_p]
+        L.gb_rdma_socket_connect.argtypes = [vp, ctypes.POINTER(ctypes.c_char_p), ctypes.c_double]
+        L.gb_rdma_socket_error.restype = ctypes.c_char_p
+        L.gb_rdma_socket_free.restype = None
+        L.gb_rdma_socket_free.argtypes = [vp]
+        L.gb_rdma_create_on.restype = vp
+        L.gb_rdma_create_on.argtypes = [vp, u, u, u, u, u64, u]
         L._rdma_declared = True
     return L
 
@@ -101,13 +109,45 @@ class Endpoint:
     """One member's endpoint; the worker interface :class:`~gpubridge_b200.tagged.TaggedBridge`
     expects (``all_reduce`` / ``broadcast`` / ``abort`` / ``close``) plus send / recv / wait."""
 
-    def __init__(self, fabric: MockFabric, index: int, *, eager_max: int = 0, data_slots: int = 0,
-                 ctrl_slots: int = 0, max_write: int = 0, unexpected_max: int = 0, mr_cache: int = 0) -> None:
+    def __init__(self, fabric: "MockFabric | None", index: int, *, eager_max: int = 0, data_slots: int = 0,
+                 ctrl_slots: int = 0, max_write: int = 0, unexpected_max: int = 0, mr_cache: int = 0,
+                 _handle: int | None = None) -> None:
+        if _handle is not None:                           # an endpoint made elsewhere (over_sockets)
+            self.lib, self.index, self.handle = _library(), index, _handle
+            return
         self.lib, self.index = fabric.lib, index
         self.handle = self.lib.gb_rdma_create(fabric.handle, index, eager_max, data_slots, ctrl_slots,
                                               max_write, unexpected_max, mr_cache)
         if not self.handle:
             raise ValueError(f"member {index} is not on this fabric")
+
+    @classmethod
+    def over_sockets(cls, index: int, members: int, publish, collect, timeout: float = 60.0, *,
+                     eager_max: int = 0, data_slots: int = 0, ctrl_slots: int = 0, max_write: int = 0,
+                     unexpected_max: int = 0, mr_cache: int = 0) -> "Endpoint":
+        """Member ``index`` of ``members`` processes on one host, joined by Unix-domain sockets
+        (the socket provider of ``csrc/gb_rdma.cpp``: the endpoint's whole protocol between
+        processes, where no adapter exists).  ``publish(name)`` makes this member's socket name
+        known; ``collect()`` returns every member's, in member order (a store does both)."""
+        import os
+        import uuid
+        lib = _library()
+        name = f"gpubridge-rdma-{os.getpid()}-{uuid.uuid4().hex[:12]}-{index}"
+        provider = lib.gb_rdma_socket_provider(index, members, name.encode())
+        if not provider:
+            raise RuntimeError("rdma endpoint: could not listen on a Unix-domain socket")
+        try:
+            publish(name)
+            names = collect()
+            array = (ctypes.c_char_p * members)(*[n.encode() for n in names])
+            if lib.gb_rdma_socket_connect(provider, array, timeout) != 0:
+                raise RuntimeError(f"rdma endpoint: {lib.gb_rdma_socket_error().decode()}")
+        except BaseException:
+            lib.gb_rdma_socket_free(provider)
+            raise
+        handle = lib.gb_rdma_create_on(provider, eager_max, data_slots, ctrl_slots, max_write,
+                                       unexpected_max, mr_cache)
+        return cls(None, index, _handle=handle)
 
     def _error(self) -> str:
         return self.lib.gb_rdma_last_error(self.handle).decode()
@@ -158,10 +198,16 @@ class Endpoint:
             self.lib.gb_rdma_close(handle)
 
 
+PROVIDER_ENV = "GPUBRIDGE_VERBS_PROVIDER"
+
+
 def provider_available() -> bool:
-    """Whether a provider over real queue pairs is part of this build (none is: see the module
-    text)."""
-    return False
+    """Whether ``bridge="verbs"`` can connect members here.  No provider over real queue pairs
+    is part of this build (see the module text); ``GPUBRIDGE_VERBS_PROVIDER=sockets`` selects
+    the Unix-domain socket provider, which joins the processes of ONE host - the bridge's whole
+    protocol end to end in CPU simulation and on one box, not a fast path."""
+    import os
+    return os.environ.get(PROVIDER_ENV, "").strip().lower() == "sockets"
 
 
 def load(name: str) -> None:
@@ -175,7 +221,9 @@ def load(name: str) -> None:
         "the verbs bridge needs a provider over libibverbs, and this build has none: the "
         "infiniband/verbs.h header is not installed here.  The endpoint itself - wire protocol, "
         "flow control, registration cache, failure rule - is built and runs over an in-process "
-        "fabric (gpubridge_b200.rdma.MockFabric); across machines use bridge='multitcp' or 'gloo'")
+        "fabric (gpubridge_b200.rdma.MockFabric) and, between the processes of one host, over "
+        "Unix-domain sockets (GPUBRIDGE_VERBS_PROVIDER=sockets); across machines use "
+        "bridge='multitcp' or 'gloo'")
 
 
 def info() -> dict:

@@ -137,8 +137,19 @@ class RdmaTransport(TaggedBridge):
 
     @classmethod
     def _connect(cls, store, key, members, rank, timeout, deadline):
-        _rdma.load(cls.name)                   # raises: no provider over real queue pairs here
-        raise AssertionError("unreachable")
+        if not _rdma.provider_available():
+            _rdma.load(cls.name)               # raises: no provider over real queue pairs here
+        # the socket provider: every member publishes its socket name on the store
+        from gpubridge_b200.tagged import wait_for_keys
+        index = list(members).index(rank)
+        endpoint = _rdma.Endpoint.over_sockets(
+            index, len(members),
+            publish=lambda name: store.set(f"{key}/socket/{rank}", name),
+            collect=lambda: wait_for_keys(store, [f"{key}/socket/{m}" for m in members], deadline,
+                                          "every bridge member's socket name"),
+            timeout=max(0.1, deadline - time.monotonic()))
+        chunk = _config.size_setting("GPUBRIDGE_VERBS_CHUNK_BYTES", 4 << 20)
+        return cls(endpoint, members, rank, timeout, chunk)
 
     @classmethod
     def over_fabric(cls, fabric: "_rdma.MockFabric", members: Sequence[int], rank: int, *,
