@@ -55,7 +55,10 @@
 #include <vector>
 
 #include <cerrno>
+#include <cstdlib>
 #include <poll.h>
+#include <pthread.h>
+#include <sched.h>
 #include <sys/socket.h>
 #include <sys/un.h>
 #include <unistd.h>
@@ -694,6 +697,9 @@ struct Config {
     uint64_t unexpected_max = 64ull << 20;
     uint32_t mr_cache = 64;
     int poll_ms = 5;                     // how long the progress thread sleeps in poll
+    int spin = 0;                        // "latency" progress: poll without sleeping, this many
+                                         // empty rounds before a short sleep is allowed again
+    int cpu = -1;                        // pin the progress thread to this CPU (-1: leave it)
 };
 
 struct Op {
@@ -1037,10 +1043,24 @@ void Endpoint::on_completion(const Completion& c) {
     in_flight.erase(c.wr_id);                             // a send buffer is free again
 }
 
+// How the progress thread waits for completions - GPUBRIDGE_VERBS_PROGRESS, read once per
+// endpoint: "economy" sleeps up to 50 ms in poll (an idle bridge costs nothing), "balanced" (the
+// default) up to 5 ms, "latency" polls without sleeping while completions keep coming and
+// only sleeps 1 ms after 2000 empty rounds.  GPUBRIDGE_VERBS_PROGRESS_CPU pins the thread.
 void Endpoint::loop() {
     Completion batch[32];
+    if (cfg.cpu >= 0) {
+        cpu_set_t set;
+        CPU_ZERO(&set);
+        CPU_SET(cfg.cpu, &set);
+        pthread_setaffinity_np(pthread_self(), sizeof(set), &set);       // best effort
+    }
+    int empty = 0;
     for (;;) {
-        const int got = provider->poll(batch, 32, cfg.poll_ms);
+        const int sleep_ms = cfg.spin > 0 ? (empty < cfg.spin ? 0 : 1) : cfg.poll_ms;
+        const int got = provider->poll(batch, 32, sleep_ms);
+        empty = got ? 0 : empty + 1;
+        if (cfg.spin > 0 && !got && sleep_ms == 0) std::this_thread::yield();
         std::unique_lock<std::mutex> hold(mu);
         if (closing) return;
         for (int i = 0; i < got && !broken; ++i) on_completion(batch[i]);
@@ -1082,10 +1102,11 @@ std::string Endpoint::telemetry() {
         "\"eager_recv\": %ld, \"rndv_recv\": %ld, \"bytes_sent\": %ld, \"bytes_recv\": %ld, \"unexpected\": %ld, "
         "\"unexpected_bytes_now\": %llu, \"credit_msgs\": %ld, \"credit_stalls\": %ld, \"completions\": %ld, "
         "\"errors\": %ld, \"writes\": %ld, \"mr_hits\": %ld, \"mr_misses\": %ld, \"mr_evictions\": %ld, "
-        "\"mr_entries\": %zu, \"pending_ops\": %zu}",
+        "\"mr_entries\": %zu, \"pending_ops\": %zu, \"progress\": \"%s\", \"progress_cpu\": %d}",
         me, count, broken ? "true" : "false", n.eager_sent, n.rndv_sent, n.eager_recv, n.rndv_recv, n.bytes_sent,
         n.bytes_recv, n.unexpected, (unsigned long long)unexpected_bytes, n.credit_msgs, n.credit_stalls,
-        n.completions, n.errors, n.writes, mrs->hits, mrs->misses, mrs->evictions, mrs->lru.size(), ops.size());
+        n.completions, n.errors, n.writes, mrs->hits, mrs->misses, mrs->evictions, mrs->lru.size(), ops.size(),
+        cfg.spin > 0 ? "latency" : cfg.poll_ms >= 50 ? "economy" : "balanced", cfg.cpu);
     return text;
 }
 
@@ -1193,6 +1214,12 @@ Endpoint* make_endpoint(Provider* provider, MockFabric* fabric, int index, int c
     if (max_write) e->cfg.max_write = max_write;
     if (unexpected_max) e->cfg.unexpected_max = unexpected_max;
     if (mr_cache) e->cfg.mr_cache = mr_cache;
+    if (const char* mode = std::getenv("GPUBRIDGE_VERBS_PROGRESS")) {
+        const std::string m(mode);
+        if (m == "economy") e->cfg.poll_ms = 50;
+        else if (m == "latency") e->cfg.spin = 2000;
+    }
+    if (const char* cpu = std::getenv("GPUBRIDGE_VERBS_PROGRESS_CPU")) e->cfg.cpu = std::atoi(cpu);
     e->mrs.reset(new MrCache(e->provider, e->cfg.mr_cache));
     e->peers.resize(e->count);
     for (int p = 0; p < e->count; ++p) {

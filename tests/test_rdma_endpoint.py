@@ -308,3 +308,25 @@ def test_the_verbs_bridge_says_why_it_cannot_load():
     with pytest.raises(ValueError, match="libibverbs"):
         resolve_transport("verbs")
     assert rdma.provider_available() is False
+
+
+@pytest.mark.parametrize("mode", ["economy", "balanced", "latency"])
+def test_progress_modes_deliver_the_same_messages(monkeypatch, mode):
+    """How the progress thread waits (sleeping long, sleeping briefly, polling) is a setting of
+    the process; every mode delivers, and the endpoint says which one it runs."""
+    monkeypatch.setenv("GPUBRIDGE_VERBS_PROGRESS", mode)
+    monkeypatch.setenv("GPUBRIDGE_VERBS_PROGRESS_CPU", "0")
+    f = rdma.MockFabric(2)
+    a, b = f.endpoint(0), f.endpoint(1)
+    try:
+        small, large = torch.arange(100, dtype=torch.float32), torch.arange(300_000, dtype=torch.float32)
+        got_small, got_large = torch.zeros(100), torch.zeros(300_000)
+        sends = [a.send(1, small.data_ptr(), small.nbytes, 1), a.send(1, large.data_ptr(), large.nbytes, 2)]
+        recvs = [b.recv(0, got_small.data_ptr(), got_small.nbytes, 1), b.recv(0, got_large.data_ptr(), got_large.nbytes, 2)]
+        b.wait(recvs, time.monotonic() + 10)
+        a.wait(sends, time.monotonic() + 10)
+        assert torch.equal(got_small, small) and torch.equal(got_large, large)
+        told = a.telemetry()
+        assert told["progress"] == mode and told["progress_cpu"] == 0
+    finally:
+        f.close()
