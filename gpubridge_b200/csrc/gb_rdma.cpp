@@ -23,7 +23,9 @@
 //    24  u64 tag            32  u64 length of the whole message
 //    40  u64 GRANT: address to write to   (the remote key travels in the first payload word)
 // Kinds: EAGER (header + the whole message, up to eager_max bytes), RTS (a large message is
-// ready), GRANT (the receiver matched it: write here), FIN (written), CREDIT (counters only).
+// ready), GRANT (the receiver matched it: write here), FIN (written), CREDIT (counters only),
+// BYE (the sender leaves in good order: it has sent what it owed, nothing more goes to it, and
+// the end of its link is no failure; a member that vanishes without it breaks its peers).
 // Flow control: every member pre-posts `data_slots` receive buffers per peer for EAGER and RTS
 // and `ctrl_slots` for GRANT, FIN and CREDIT; a sender may only have as many unreturned
 // messages of a class in flight as the peer has slots, and learns of re-posted slots from the
@@ -305,7 +307,9 @@ struct SocketProvider : Provider {
         std::mutex mu;
         std::condition_variable cv;
         std::deque<Out> queue;
-        bool gone = false;
+        bool gone = false;                 // nothing can be sent on this link any more
+        bool eof = false;                  // ... and nothing will arrive on it: the reader has ended
+        bool busy = false;                 // the writer is putting a frame on the wire
     };
     int index, count;
     int listener = -1;
@@ -417,12 +421,20 @@ struct SocketProvider : Provider {
             Completion c; c.wr_id = r.wr_id; c.status = ST_FLUSHED; c.opcode = OC_RECV; c.peer = peer;
             complete(c);
         }
+        { std::lock_guard<std::mutex> hold(links[peer]->mu); links[peer]->eof = true; }
+        send_side_dead(peer);
+        posted_cv.notify_all();
+    }
+    // Nothing more can be sent to `peer` (a write failed, or its stream ended): what is queued
+    // fails.  What the peer sent before it went may still be unread - the reader decides when
+    // the receives are lost, not the writer.
+    void send_side_dead(int peer) {
         Link& l = *links[peer];
         std::deque<Out> unsent;
         { std::lock_guard<std::mutex> hold(l.mu); l.gone = true; unsent.swap(l.queue); }
         l.cv.notify_all();
-        posted_cv.notify_all();
         for (const Out& o : unsent) {
+            if (o.w.type == FR_ACK) continue;
             Completion c; c.wr_id = o.w.wr_id; c.status = ST_FLUSHED; c.opcode = o.opcode; c.peer = peer;
             complete(c);
         }
@@ -437,14 +449,17 @@ struct SocketProvider : Provider {
                 if (l.gone) return;
                 o = l.queue.front();
                 l.queue.pop_front();
+                l.busy = true;
             }
             const bool ok = write_all(l.fd, &o.w, sizeof(Wire)) && (o.w.len == 0 || o.data == nullptr ||
                                                                     write_all(l.fd, o.data, o.w.len));
-            if (o.w.type == FR_ACK) { if (!ok) { flush_peer(peer); return; } continue; }
+            { std::lock_guard<std::mutex> hold(l.mu); l.busy = false; }
+            l.cv.notify_all();
+            if (o.w.type == FR_ACK) { if (!ok) { send_side_dead(peer); return; } continue; }
             if (!ok) {
                 Completion c; c.wr_id = o.w.wr_id; c.status = ST_FLUSHED; c.opcode = o.opcode; c.peer = peer;
                 complete(c);
-                flush_peer(peer);
+                send_side_dead(peer);
                 return;
             }
             if (o.w.type == FR_SEND) {                 // a WRITE completes when its acknowledgement arrives
@@ -525,7 +540,7 @@ struct SocketProvider : Provider {
     }
     int post_recv(int peer, int lane, uint64_t wr_id, void* buf, uint32_t len) override {
         bool gone;
-        { std::lock_guard<std::mutex> hold(links[peer]->mu); gone = links[peer]->gone; }
+        { std::lock_guard<std::mutex> hold(links[peer]->mu); gone = links[peer]->eof; }
         if (gone) {
             Completion c; c.wr_id = wr_id; c.status = ST_FLUSHED; c.opcode = OC_RECV; c.peer = peer;
             complete(c);
@@ -570,6 +585,16 @@ struct SocketProvider : Provider {
     void wake() override {
         { std::lock_guard<std::mutex> hold(mu); woken = true; }
         cv.notify_all();
+    }
+    // Give what is queued for the wire (acknowledgements of the peers' last writes among it)
+    // the time to leave: a member that closes right after its last operation completed must
+    // not take its peers' last messages with it.
+    void drain(double seconds) {
+        const auto until = Clock::now() + std::chrono::duration<double>(seconds);
+        for (auto& l : links) {
+            std::unique_lock<std::mutex> hold(l->mu);
+            l->cv.wait_until(hold, until, [&] { return l->gone || (l->queue.empty() && !l->busy); });
+        }
     }
     void shutdown_all() {
         { std::lock_guard<std::mutex> hold(mu); if (closing) return; closing = true; regions.clear(); recvs.clear(); }
@@ -642,7 +667,7 @@ struct MrCache {
 // ---- the protocol ---------------------------------------------------------------------------------------------
 constexpr uint32_t MAGIC = 0x31524247u;          // "GBR1"
 constexpr int HEADER_BYTES = 48;
-enum Kind { K_EAGER = 1, K_RTS = 2, K_GRANT = 3, K_FIN = 4, K_CREDIT = 5 };
+enum Kind { K_EAGER = 1, K_RTS = 2, K_GRANT = 3, K_FIN = 4, K_CREDIT = 5, K_BYE = 6 };
 
 struct Header {
     uint8_t kind = 0;
@@ -680,7 +705,7 @@ std::string decode(const char* in, uint32_t received, Header* h) {
     std::memcpy(&h->tag, in + 24, 8);
     std::memcpy(&h->length, in + 32, 8);
     std::memcpy(&h->address, in + 40, 8);
-    if (h->kind < K_EAGER || h->kind > K_CREDIT) return "a message of unknown kind " + std::to_string(h->kind);
+    if (h->kind < K_EAGER || h->kind > K_BYE) return "a message of unknown kind " + std::to_string(h->kind);
     if (received != HEADER_BYTES + h->payload) return "a message whose length disagrees with its header";
     if (h->kind == K_EAGER && h->payload != h->length) return "an eager message that is not whole";
     if (h->kind == K_GRANT && (h->payload != 4 || h->address == 0)) return "a write grant without key or address";
@@ -735,6 +760,7 @@ struct Endpoint : GbTaggedWorker {
         uint32_t freed_data = 0, freed_ctrl = 0;                      // slots re-posted here, cumulative
         uint32_t reported_data = 0, reported_ctrl = 0;                // ... and last told to the peer
         uint32_t next_seq = 1;
+        bool departed = false;                                        // it said goodbye: nothing more goes to it
         std::deque<long> posted;                                      // receives waiting, in order
         struct Early { Header h; std::vector<char> bytes; };
         std::deque<Early> early;                                      // messages waiting for a receive
@@ -743,6 +769,7 @@ struct Endpoint : GbTaggedWorker {
     };
     std::vector<Peer> peers;
     std::map<uint64_t, std::vector<char>> in_flight;                  // send buffers until completed
+    std::map<uint64_t, bool> reports;                                 // sends that carry counters only
     uint64_t next_wr = 1;
     uint64_t unexpected_bytes = 0;
     // wr_id layout: bit 63 receive, bit 62 control class, bits 32-47 peer, low 32 slot / serial
@@ -784,6 +811,10 @@ struct Endpoint : GbTaggedWorker {
     // Put an encoded message on the wire, or queue it until the peer has a slot for its class.
     void transmit(int peer, bool ctrl, std::vector<char>&& bytes, bool is_credit = false) {
         Peer& p = peers[peer];
+        if (p.departed) {
+            if (!ctrl || !is_credit) break_locked("member " + std::to_string(peer) + " has left the bridge");
+            return;
+        }
         std::deque<std::vector<char>>& backlog = ctrl ? p.backlog_ctrl : p.backlog_data;
         const uint32_t have = ctrl ? ctrl_credits(p) : data_credits(p);
         const uint32_t need = ctrl && !is_credit ? 2u : 1u;             // the last control slot is CREDIT's
@@ -795,7 +826,7 @@ struct Endpoint : GbTaggedWorker {
         }
         put(peer, ctrl, std::move(bytes));
     }
-    void put(int peer, bool ctrl, std::vector<char>&& bytes) {
+    uint64_t put(int peer, bool ctrl, std::vector<char>&& bytes) {
         Peer& p = peers[peer];
         // every header carries the latest counters
         std::memcpy(bytes.data() + 16, &p.freed_data, 4);
@@ -806,6 +837,7 @@ struct Endpoint : GbTaggedWorker {
         const uint64_t wr = next_wr++;
         auto& kept = in_flight[wr] = std::move(bytes);
         provider->post_send(peer, ctrl ? 1 : 0, wr, kept.data(), (uint32_t)kept.size());
+        return wr;
     }
     void drain_backlogs(int peer) {
         Peer& p = peers[peer];
@@ -824,13 +856,27 @@ struct Endpoint : GbTaggedWorker {
         Peer& p = peers[peer];
         const bool due = p.freed_data - p.reported_data >= (cfg.data_slots + 1) / 2 ||
                          p.freed_ctrl - p.reported_ctrl >= (cfg.ctrl_slots + 1) / 2;
-        if (!due || ctrl_credits(p) < 1 || !p.backlog_ctrl.empty()) return;
+        if (!due || p.departed || ctrl_credits(p) < 1 || !p.backlog_ctrl.empty()) return;
         Header h;
         h.kind = K_CREDIT; h.sender = (uint16_t)me;
         std::vector<char> bytes(HEADER_BYTES);
         encode(h, bytes.data());
         ++n.credit_msgs;
-        put(peer, true, std::move(bytes));
+        reports[put(peer, true, std::move(bytes))] = true;
+    }
+    // Leaving in good order: tell every peer that nothing more comes from here and that nothing
+    // more should be sent here.  A peer that has read this neither reports to this member any
+    // more nor takes the end of its stream for a failure.
+    void say_goodbye() {
+        for (int peer = 0; peer < count; ++peer) {
+            Peer& p = peers[peer];
+            if (peer == me || p.departed || ctrl_credits(p) < 1) continue;
+            Header h;
+            h.kind = K_BYE; h.sender = (uint16_t)me;
+            std::vector<char> bytes(HEADER_BYTES);
+            encode(h, bytes.data());
+            reports[put(peer, true, std::move(bytes))] = true;
+        }
     }
     void send_control(int peer, const Header& h, const char* payload = nullptr, uint32_t payload_len = 0) {
         std::vector<char> bytes(HEADER_BYTES + payload_len);
@@ -903,6 +949,10 @@ long Endpoint::recv(int peer, void* data, uint64_t length, uint64_t tag) {
     Op& op = ops[id];
     op.sending = false; op.peer = peer; op.tag = tag; op.data = static_cast<char*>(data); op.length = length;
     Peer& p = peers[peer];
+    if (p.departed && p.early.empty()) {
+        break_locked("member " + std::to_string(peer) + " has left the bridge");
+        return id;
+    }
     for (auto it = p.early.begin(); it != p.early.end(); ++it) {       // did it arrive first?
         if (it->h.tag != tag) continue;
         Peer::Early early = std::move(*it);
@@ -992,6 +1042,16 @@ void Endpoint::on_message(int peer, const Header& h, const char* payload) {
         p.recvs_by_seq.erase(it);
         break;
     }
+    case K_BYE: {
+        // The peer leaves in good order.  It owes this member nothing (it sent what it had
+        // first); anything this member still expects of it can never come.
+        p.departed = true;
+        p.backlog_data.clear();
+        p.backlog_ctrl.clear();
+        if (!p.posted.empty() || !p.sends_by_seq.empty() || !p.recvs_by_seq.empty())
+            break_locked("member " + std::to_string(peer) + " left the bridge with operations pending");
+        break;
+    }
     default: break;                                       // CREDIT: the counters were all it carried
     }
 }
@@ -999,6 +1059,16 @@ void Endpoint::on_message(int peer, const Header& h, const char* payload) {
 void Endpoint::on_completion(const Completion& c) {
     ++n.completions;
     if (c.status != ST_OK) {
+        // After a goodbye the link's end is no failure, and a report (counters only, or this
+        // member's own goodbye) that could not be delivered costs nothing: if its peer is really
+        // dead, the end of that peer's stream will say so.
+        const bool receive = (c.wr_id >> 63) & 1, piece = (c.wr_id >> 61) & 1;
+        const int about = receive || piece ? (int)((c.wr_id >> 32) & 0xFFFF) : c.peer;
+        const bool report = !receive && !piece && reports.count(c.wr_id) != 0;
+        if (closing || report || (about >= 0 && about < count && peers[about].departed)) {
+            if (!receive && !piece) { in_flight.erase(c.wr_id); reports.erase(c.wr_id); }
+            return;
+        }
         static const char* names[] = {"ok", "a transport error", "a refused remote access", "a flushed connection",
                                       "a message longer than its receive buffer"};
         break_locked(std::string("the link to member ") + std::to_string(c.peer) + " reported " +
@@ -1017,7 +1087,7 @@ void Endpoint::on_completion(const Completion& c) {
         const bool control_kind = h.kind >= K_GRANT;
         if (control_kind != ctrl || h.sender != peer) { break_locked("a message in the wrong class of slot"); return; }
         on_message(peer, h, buf.data() + HEADER_BYTES);
-        if (broken) return;
+        if (broken || p.departed) return;
         post_slot(peer, ctrl, slot);
         (ctrl ? p.freed_ctrl : p.freed_data)++;
         drain_backlogs(peer);
@@ -1041,6 +1111,7 @@ void Endpoint::on_completion(const Completion& c) {
         return;
     }
     in_flight.erase(c.wr_id);                             // a send buffer is free again
+    reports.erase(c.wr_id);
 }
 
 // How the progress thread waits for completions - GPUBRIDGE_VERBS_PROGRESS, read once per
@@ -1276,7 +1347,26 @@ void gb_rdma_close(void* ep) {
     Endpoint* e = static_cast<Endpoint*>(ep);
     if (e == nullptr) return;
     {
+        // Leave in good order: messages this member still owes its peers (queued for a credit,
+        // or handed to the provider and not yet completed) go out first, for a bounded time.
         std::unique_lock<std::mutex> hold(e->mu);
+        const auto until = Clock::now() + std::chrono::seconds(5);
+        while (!e->broken && Clock::now() < until) {
+            bool owed = !e->in_flight.empty();
+            for (const Endpoint::Peer& p : e->peers) owed = owed || !p.backlog_data.empty() || !p.backlog_ctrl.empty();
+            if (!owed) break;
+            e->done.wait_for(hold, std::chrono::milliseconds(5));
+        }
+        const bool clean = !e->broken;
+        if (clean) {
+            e->say_goodbye();
+            const auto last = Clock::now() + std::chrono::seconds(2);
+            while (!e->broken && !e->in_flight.empty() && Clock::now() < last)
+                e->done.wait_for(hold, std::chrono::milliseconds(5));
+        }
+        hold.unlock();
+        if (clean && e->owned) static_cast<SocketProvider*>(e->owned.get())->drain(5.0);
+        hold.lock();
         e->closing = true;
         e->break_locked("the endpoint was closed");
     }

@@ -330,3 +330,48 @@ def test_progress_modes_deliver_the_same_messages(monkeypatch, mode):
         assert told["progress"] == mode and told["progress_cpu"] == 0
     finally:
         f.close()
+
+
+def test_a_member_that_leaves_in_good_order_does_not_break_the_others():
+    """Closing says goodbye first: the others stop reporting to the member that left, do not take
+    the end of its link for a failure, and go on working among themselves; an operation that
+    still expects something of it fails with the reason."""
+    f = rdma.MockFabric(3)
+    a, b, c = (f.endpoint(i, data_slots=4, ctrl_slots=3) for i in range(3))
+    try:
+        deadline = time.monotonic() + 10
+        # enough traffic from a to b that b owes a credit reports
+        payloads = [torch.full((64,), float(k)) for k in range(20)]
+        outs = [torch.zeros(64) for _ in range(20)]
+        recvs = [b.recv(0, o.data_ptr(), o.nbytes, 4) for o in outs]
+        a.wait([a.send(1, p.data_ptr(), p.nbytes, 4) for p in payloads], deadline)
+        b.wait(recvs, deadline)
+        a.close()                                           # leaves while b and c go on
+        f.endpoints.remove(a)
+        time.sleep(0.2)
+        big = torch.arange(200_000, dtype=torch.float32)
+        got = torch.zeros(200_000)
+        r = c.recv(1, got.data_ptr(), got.nbytes, 8)
+        b.wait([b.send(2, big.data_ptr(), big.nbytes, 8)], deadline)
+        c.wait([r], deadline)
+        assert torch.equal(got, big)
+        assert not b.telemetry()["broken"] and not c.telemetry()["broken"]
+        # ... but nothing can be had from the member that left
+        lost = torch.zeros(8)
+        with pytest.raises(RuntimeError, match="left the bridge"):
+            b.wait([b.recv(0, lost.data_ptr(), lost.nbytes, 9)], time.monotonic() + 5)
+    finally:
+        f.close()
+
+
+def test_a_member_that_dies_without_a_word_still_breaks_its_peers():
+    f = rdma.MockFabric(2)
+    a, b = f.endpoint(0), f.endpoint(1)
+    try:
+        f.inject("kill", dst=1, nth=1)
+        t = torch.ones(64)
+        with pytest.raises(RuntimeError):
+            a.wait([a.send(1, t.data_ptr(), t.nbytes, 1)], time.monotonic() + 5)
+        assert a.telemetry()["broken"]
+    finally:
+        f.close()
