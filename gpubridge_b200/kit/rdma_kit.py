@@ -136,11 +136,34 @@ def check(out: Path) -> int:
 
 
 # ---- perf -------------------------------------------------------------------------------------------
-def perf(out: Path, sizes: list[int], trials: int) -> int:
+def _socket_pair() -> list:
+    """Two endpoints joined by the Unix-domain socket provider, made in two threads."""
+    names, ready, ends = [None, None], threading.Barrier(2), [None, None]
+
+    def make(i: int) -> None:
+        def publish(name: str) -> None:
+            names[i] = name
+            ready.wait(20)
+        ends[i] = rdma.Endpoint.over_sockets(i, 2, publish, lambda: list(names), 20.0)
+
+    workers = [threading.Thread(target=make, args=(i,)) for i in range(2)]
+    for w in workers:
+        w.start()
+    for w in workers:
+        w.join(30)
+    if None in ends:
+        raise RuntimeError("the socket provider did not connect")
+    return ends
+
+
+def perf(out: Path, sizes: list[int], trials: int, fabric_kind: str = "memory") -> int:
     rows = []
     for nbytes in sizes:
-        fabric = rdma.MockFabric(2)
-        ends = [fabric.endpoint(i) for i in range(2)]
+        if fabric_kind == "sockets":
+            fabric, ends = None, _socket_pair()
+        else:
+            fabric = rdma.MockFabric(2)
+            ends = [fabric.endpoint(i) for i in range(2)]
         # every member has its own pair of buffers (real pages, not the zero page)
         pairs = [[torch.randint(0, 255, (nbytes,), dtype=torch.uint8) for _ in range(2)] for _ in range(2)]
         laps: list[float] = []
@@ -160,12 +183,19 @@ def perf(out: Path, sizes: list[int], trials: int) -> int:
                     ends[1].wait([ends[1].send(0, back.data_ptr(), nbytes, lap)], deadline)
 
         result = _threads(2, body)
-        fabric.close()
+        if fabric is not None:
+            fabric.close()
+        else:
+            closers = [threading.Thread(target=e.close) for e in ends]      # they say goodbye to each other
+            for c in closers:
+                c.start()
+            for c in closers:
+                c.join(15)
         if any(r["error"] for r in result) or not laps:
             rows.append({"bytes": nbytes, "error": [r["error"] for r in result if r["error"]]})
             continue
         half = statistics.median(laps) / 2
-        rows.append({"bytes": nbytes, "one_way_us": round(half * 1e6, 1),
+        rows.append({"bytes": nbytes, "fabric": fabric_kind, "one_way_us": round(half * 1e6, 1),
                      "gbs": round(nbytes / half / 1e9, 3)})
         print(json.dumps(rows[-1]), flush=True)
     out.mkdir(parents=True, exist_ok=True)
@@ -222,11 +252,13 @@ def main(argv=None) -> int:
     ap.add_argument("--trials", type=int, default=20)
     ap.add_argument("--sizes", default="64,4096,65536,1048576,16777216")
     ap.add_argument("--numel", type=int, default=1 << 22)
+    ap.add_argument("--fabric", default="memory", choices=("memory", "sockets"),
+                    help="perf: the in-process fabric, or the Unix-domain socket provider")
     args = ap.parse_args(argv)
     if args.what == "check":
         return check(args.out)
     if args.what == "perf":
-        return perf(args.out, [int(s) for s in args.sizes.split(",")], args.trials)
+        return perf(args.out, [int(s) for s in args.sizes.split(",")], args.trials, args.fabric)
     return ab(args.out, args.numel, args.trials)
 
 

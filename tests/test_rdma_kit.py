@@ -27,3 +27,10 @@ def test_perf_and_ab_write_their_tables(tmp_path):
     ab = json.loads((tmp_path / "rdma_ab.json").read_text())["rows"]
     assert len(ab) == len(rdma_kit.ARMS) and ab[0]["against_first"] == 1.0
     assert all(r["routes"] == {"bounce": 3} for r in ab)
+
+
+def test_perf_over_the_socket_provider(tmp_path):
+    assert rdma_kit.main(["perf", "--out", str(tmp_path), "--trials", "2", "--sizes", "64,100000",
+                          "--fabric", "sockets"]) == 0
+    rows = json.loads((tmp_path / "rdma_perf.json").read_text())["rows"]
+    assert [r["fabric"] for r in rows] == ["sockets", "sockets"] and all(r["one_way_us"] > 0 for r in rows)
