@@ -15,6 +15,7 @@ Steps (what the reference spreads over ``scripts/gpu/explorer/*.sbatch`` and ``c
                        C++ front end (GPUBRIDGE_FRONT_END=native)
     gate               the numerical gate (four ranks, both arms)
     streams            the stream-ordering mutation run (one GPU)
+    rdma-check         the RDMA-style endpoint's protocol scenarios with injected faults
     sweep              a short all-reduce sweep against NCCL
     scaling            train_synthetic at 1, 2, 4, ... ranks and the weak-scaling table
 
@@ -88,6 +89,8 @@ def plan(out: Path, gpus: int, cpu: bool) -> list[dict]:
                                         str(out / "gate"), "--arm", arm) + (["--software-only"] if cpu else []))
     if not cpu:
         add("streams", [PY, "-m", "gpubridge_b200.kit.stream_mutations", "--out", str(out / "streams")])
+    # the RDMA-style endpoint's protocol scenarios (in-process fabric: needs no adapter and no GPU)
+    add("rdma-check", [PY, "-m", "gpubridge_b200.kit.rdma_kit", "check", "--out", str(out / "rdma")])
     if gpus >= 2:
         add("sweep", torchrun(gpus, port[0] + 1, "-m", "gpubridge_b200.bench.bench_all_reduce", "--smallest",
                               "64K", "--largest", "4M" if cpu else "256M", "--trials", "5", "--seconds", "2",
