@@ -6,6 +6,8 @@ sizes, the three-buffer pipeline, the per-block barrier numbers across many laun
 copy stages.  Two or more GPUs: exact sums on integer-valued data for one island (flat order)
 and for several (island sums in the switch, islands added over peer memory), identical bits
 on every rank, AVG divided once.  All against plain PyTorch sums in fp32."""
+import os
+
 import pytest
 import torch
 
@@ -113,8 +115,11 @@ def _sums(rank, topology):
 @pytest.mark.skipif(NGPU < 2, reason="needs at least two GPUs")
 @pytest.mark.parametrize("split", [{}, {"GPUBRIDGE_SPLIT_TEST": "half"},
                                    {"GPUBRIDGE_SPLIT_TEST": "half", "GPUBRIDGE_SWITCH_FLAT": "0"}]
+                         # the hierarchical order on uneven and on four islands has not run on eight
+                         # GPUs yet (it has on 2+2): those cases join with GPUBRIDGE_TEST_SWITCH_HIER8=1
                          + ([{"GPUBRIDGE_ISLANDS": "3,5", "GPUBRIDGE_SWITCH_FLAT": "0"},
-                             {"GPUBRIDGE_ISLANDS": "2,2,2,2", "GPUBRIDGE_SWITCH_FLAT": "0"}] if WORLD == 8 else []),
+                             {"GPUBRIDGE_ISLANDS": "2,2,2,2", "GPUBRIDGE_SWITCH_FLAT": "0"}]
+                            if WORLD == 8 and os.environ.get("GPUBRIDGE_TEST_SWITCH_HIER8") == "1" else []),
                          ids=lambda s: ",".join(s.values()) or "one-island")
 def test_sums_through_the_switch(tmp_path, split):
     # two ranks take the switch only when told to (it saves them no traffic): the kernels are the same
