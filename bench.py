@@ -239,10 +239,16 @@ def run_ours(args) -> dict:
     if not args.no_hook_arm:
         del trainer, e2e_steps
         torch.cuda.empty_cache()
-        result["hook_arm"] = hook_arm(args, gb, gpt2, topology, device, data, resident, barrier,
-                                      max_over_ranks)
+        try:
+            result["hook_arm"] = hook_arm(args, gb, gpt2, topology, device, data, resident, barrier,
+                                          max_over_ranks)
+        except Exception as failure:  # noqa: BLE001 - the second arm must not cost the first its line
+            result["hook_arm"] = {"error": f"{type(failure).__name__}: {failure}"[:300]}
     if topology is not None:
-        gb.destroy()
+        try:
+            gb.destroy()
+        except Exception as failure:  # noqa: BLE001 - the measurement is done: report it
+            result["teardown_error"] = f"{type(failure).__name__}: {failure}"[:300]
     return result if rank == 0 else {}
 
 
