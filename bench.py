@@ -466,9 +466,21 @@ def main() -> int:
                       "unavailable": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]}
             if int(os.environ.get("RANK", "0")) != 0:
                 result = {}
+        elif (world > 1 and os.environ.get("GPUBRIDGE_NVLS", "1") != "0"
+              and not os.environ.get("GPUBRIDGE_BENCH_SECOND_TRY")):
+            # A wait inside an in-switch kernel ran out, or its set-up failed half-way: every
+            # rank ends up here (the others' waits are bounded too).  Run the measurement once
+            # more on the peer-memory kernels, and say so in the result.
+            print(f"[bench] {type(exc).__name__}: {exc}\n[bench] second try without in-switch "
+                  "reduction (GPUBRIDGE_NVLS=0)", file=sys.stderr, flush=True)
+            os.environ["GPUBRIDGE_NVLS"] = "0"
+            os.environ["GPUBRIDGE_BENCH_SECOND_TRY"] = "1"
+            os.execv(sys.executable, [sys.executable, *sys.argv])
         else:
             raise
     if result:
+        if os.environ.get("GPUBRIDGE_BENCH_SECOND_TRY") and isinstance(result.get("config"), dict):
+            result["config"]["second_try_without_in_switch_reduction"] = True
         print(json.dumps(result), flush=True)
     return 0
 
