@@ -476,6 +476,7 @@ def main() -> int:
             os.environ["GPUBRIDGE_NVLS"] = "0"
             os.environ["GPUBRIDGE_BENCH_SECOND_TRY"] = "1"
             os.execv(sys.executable, [sys.executable, *sys.argv])
+            raise                                   # not reached: the process image was replaced
         else:
             raise
     if result:
