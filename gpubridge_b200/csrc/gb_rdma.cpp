@@ -58,6 +58,9 @@
 
 #include <cerrno>
 #include <cstdlib>
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
 #include <poll.h>
 #include <pthread.h>
 #include <sched.h>
@@ -285,7 +288,12 @@ int MockProvider::post_write(int peer, uint64_t wr_id, const void* local, uint64
     return 0;
 }
 
-// ---- a provider over Unix-domain sockets: members in different processes of one host ------------------
+// ---- a provider over stream sockets: members in different processes ----------------------------------
+//
+// Names: a plain string is an abstract Unix-domain socket name (the processes of one host);
+// "tcp://a.b.c.d:port" is a TCP address (port 0 when listening: the system picks one, and
+// bound_name() says which), so the same provider also joins processes on different hosts -
+// the endpoint's protocol over an ordinary network, where no adapter exists.
 //
 // The same queue-pair semantics as the in-process fabric, carried over one stream socket per
 // pair of members (abstract socket names, so nothing is left in the file system): a SEND is
@@ -329,6 +337,17 @@ struct SocketProvider : Provider {
     }
     ~SocketProvider() override { shutdown_all(); }
 
+    std::string bound;                                 // the name peers can reach this member under
+    static bool is_tcp(const std::string& name) { return name.rfind("tcp://", 0) == 0; }
+    static bool tcp_address(const std::string& name, sockaddr_in* a) {
+        const std::string rest = name.substr(6);
+        const size_t colon = rest.rfind(':');
+        if (colon == std::string::npos) return false;
+        std::memset(a, 0, sizeof(*a));
+        a->sin_family = AF_INET;
+        a->sin_port = htons((uint16_t)std::atoi(rest.c_str() + colon + 1));
+        return ::inet_pton(AF_INET, rest.substr(0, colon).c_str(), &a->sin_addr) == 1;
+    }
     static sockaddr_un address(const std::string& name, socklen_t* len) {
         sockaddr_un a;
         std::memset(&a, 0, sizeof(a));
@@ -339,11 +358,49 @@ struct SocketProvider : Provider {
         return a;
     }
     bool listen_on(const std::string& name) {
+        bound = name;
+        if (is_tcp(name)) {
+            sockaddr_in a;
+            if (!tcp_address(name, &a)) return false;
+            listener = ::socket(AF_INET, SOCK_STREAM, 0);
+            if (listener < 0) return false;
+            const int yes = 1;
+            ::setsockopt(listener, SOL_SOCKET, SO_REUSEADDR, &yes, sizeof(yes));
+            if (::bind(listener, reinterpret_cast<sockaddr*>(&a), sizeof(a)) != 0 || ::listen(listener, 64) != 0)
+                return false;
+            socklen_t len = sizeof(a);
+            ::getsockname(listener, reinterpret_cast<sockaddr*>(&a), &len);     // the port the system chose
+            char ip[INET_ADDRSTRLEN];
+            ::inet_ntop(AF_INET, &a.sin_addr, ip, sizeof(ip));
+            bound = std::string("tcp://") + ip + ":" + std::to_string(ntohs(a.sin_port));
+            return true;
+        }
         listener = ::socket(AF_UNIX, SOCK_STREAM, 0);
         if (listener < 0) return false;
         socklen_t len;
         sockaddr_un a = address(name, &len);
         return ::bind(listener, reinterpret_cast<sockaddr*>(&a), len) == 0 && ::listen(listener, 64) == 0;
+    }
+    // A connected socket to `name`, or -1.
+    static int dial(const std::string& name) {
+        if (is_tcp(name)) {
+            sockaddr_in a;
+            if (!tcp_address(name, &a)) return -1;
+            const int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+            if (fd >= 0 && ::connect(fd, reinterpret_cast<sockaddr*>(&a), sizeof(a)) == 0) {
+                const int yes = 1;
+                ::setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &yes, sizeof(yes));
+                return fd;
+            }
+            if (fd >= 0) ::close(fd);
+            return -1;
+        }
+        socklen_t len;
+        sockaddr_un a = address(name, &len);
+        const int fd = ::socket(AF_UNIX, SOCK_STREAM, 0);
+        if (fd >= 0 && ::connect(fd, reinterpret_cast<sockaddr*>(&a), len) == 0) return fd;
+        if (fd >= 0) ::close(fd);
+        return -1;
     }
     static bool write_all(int fd, const void* data, size_t n) {
         const char* p = static_cast<const char*>(data);
@@ -367,13 +424,10 @@ struct SocketProvider : Provider {
     bool connect_all(const std::vector<std::string>& names, double timeout_s, std::string* why) {
         const auto deadline = Clock::now() + std::chrono::duration<double>(timeout_s);
         for (int p = index + 1; p < count; ++p) {
-            socklen_t len;
-            sockaddr_un a = address(names[p], &len);
             int fd = -1;
             for (;;) {
-                fd = ::socket(AF_UNIX, SOCK_STREAM, 0);
-                if (fd >= 0 && ::connect(fd, reinterpret_cast<sockaddr*>(&a), len) == 0) break;
-                if (fd >= 0) ::close(fd);
+                fd = dial(names[p]);
+                if (fd >= 0) break;
                 if (Clock::now() > deadline) { *why = "member " + std::to_string(p) + " never listened"; return false; }
                 std::this_thread::sleep_for(std::chrono::milliseconds(20));
             }
@@ -386,6 +440,10 @@ struct SocketProvider : Provider {
             const auto left = std::chrono::duration_cast<std::chrono::milliseconds>(deadline - Clock::now()).count();
             if (left <= 0 || ::poll(&wait, 1, (int)left) <= 0) { *why = "a lower member never dialled"; return false; }
             const int fd = ::accept(listener, nullptr, nullptr);
+            if (fd >= 0 && is_tcp(bound)) {
+                const int yes = 1;
+                ::setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &yes, sizeof(yes));
+            }
             uint32_t who = 0;
             if (fd < 0 || !read_all(fd, &who, 4) || (int)who >= index || links[who]->fd >= 0) {
                 if (fd >= 0) ::close(fd);
@@ -1240,6 +1298,11 @@ int gb_rdma_socket_connect(void* provider, const char* const* names, double time
     return -1;
 }
 const char* gb_rdma_socket_error() { return g_text.c_str(); }
+// The name peers reach this member under (for "tcp://host:0": with the port the system chose).
+const char* gb_rdma_socket_name(void* provider) {
+    g_text = static_cast<SocketProvider*>(provider)->bound;
+    return g_text.c_str();
+}
 void gb_rdma_socket_free(void* provider) { delete static_cast<SocketProvider*>(provider); }
 
 namespace {

@@ -61,6 +61,8 @@ def _library():
         L.gb_rdma_socket_provider.argtypes = [i, i, ctypes.c_char_p]
         L.gb_rdma_socket_connect.argtypes = [vp, ctypes.POINTER(ctypes.c_char_p), ctypes.c_double]
         L.gb_rdma_socket_error.restype = ctypes.c_char_p
+        L.gb_rdma_socket_name.restype = ctypes.c_char_p
+        L.gb_rdma_socket_name.argtypes = [vp]
         L.gb_rdma_socket_free.restype = None
         L.gb_rdma_socket_free.argtypes = [vp]
         L.gb_rdma_create_on.restype = vp
@@ -123,20 +125,24 @@ class Endpoint:
 
     @classmethod
     def over_sockets(cls, index: int, members: int, publish, collect, timeout: float = 60.0, *,
-                     eager_max: int = 0, data_slots: int = 0, ctrl_slots: int = 0, max_write: int = 0,
+                     tcp_host: str | None = None, eager_max: int = 0, data_slots: int = 0, ctrl_slots: int = 0, max_write: int = 0,
                      unexpected_max: int = 0, mr_cache: int = 0) -> "Endpoint":
         """Member ``index`` of ``members`` processes on one host, joined by Unix-domain sockets
         (the socket provider of ``csrc/gb_rdma.cpp``: the endpoint's whole protocol between
         processes, where no adapter exists).  ``publish(name)`` makes this member's socket name
-        known; ``collect()`` returns every member's, in member order (a store does both)."""
+        known; ``collect()`` returns every member's, in member order (a store does both).
+        ``tcp_host``: listen on that IPv4 address with TCP instead (a port the system picks), so
+        the members may sit on different hosts."""
         import os
         import uuid
         lib = _library()
-        name = f"gpubridge-rdma-{os.getpid()}-{uuid.uuid4().hex[:12]}-{index}"
+        name = (f"tcp://{tcp_host}:0" if tcp_host else
+                f"gpubridge-rdma-{os.getpid()}-{uuid.uuid4().hex[:12]}-{index}")
         provider = lib.gb_rdma_socket_provider(index, members, name.encode())
         if not provider:
-            raise RuntimeError("rdma endpoint: could not listen on a Unix-domain socket")
+            raise RuntimeError(f"rdma endpoint: could not listen on {name}")
         try:
+            name = lib.gb_rdma_socket_name(provider).decode()
             publish(name)
             names = collect()
             array = (ctypes.c_char_p * members)(*[n.encode() for n in names])
@@ -204,10 +210,16 @@ PROVIDER_ENV = "GPUBRIDGE_VERBS_PROVIDER"
 def provider_available() -> bool:
     """Whether ``bridge="verbs"`` can connect members here.  No provider over real queue pairs
     is part of this build (see the module text); ``GPUBRIDGE_VERBS_PROVIDER=sockets`` selects
-    the Unix-domain socket provider, which joins the processes of ONE host - the bridge's whole
-    protocol end to end in CPU simulation and on one box, not a fast path."""
+    the socket provider over Unix-domain sockets, which joins the processes of ONE host, and
+    ``=tcp`` the same provider over TCP (listening where ``GPUBRIDGE_MULTITCP_IFADDR`` /
+    ``GPUBRIDGE_MULTITCP_IFNAME`` say, loopback otherwise), which joins hosts - the bridge's
+    whole protocol end to end without an adapter, not a fast path."""
+    return provider_kind() in ("sockets", "tcp")
+
+
+def provider_kind() -> str:
     import os
-    return os.environ.get(PROVIDER_ENV, "").strip().lower() == "sockets"
+    return os.environ.get(PROVIDER_ENV, "").strip().lower()
 
 
 def load(name: str) -> None:

@@ -142,12 +142,16 @@ class RdmaTransport(TaggedBridge):
         # the socket provider: every member publishes its socket name on the store
         from gpubridge_b200.tagged import wait_for_keys
         index = list(members).index(rank)
+        tcp_host = None
+        if _rdma.provider_kind() == "tcp":
+            from gpubridge_b200.multitcp import listen_address
+            tcp_host = listen_address()
         endpoint = _rdma.Endpoint.over_sockets(
             index, len(members),
             publish=lambda name: store.set(f"{key}/socket/{rank}", name),
             collect=lambda: wait_for_keys(store, [f"{key}/socket/{m}" for m in members], deadline,
                                           "every bridge member's socket name"),
-            timeout=max(0.1, deadline - time.monotonic()))
+            timeout=max(0.1, deadline - time.monotonic()), tcp_host=tcp_host)
         chunk = _config.size_setting("GPUBRIDGE_VERBS_CHUNK_BYTES", 4 << 20)
         return cls(endpoint, members, rank, timeout, chunk)
 

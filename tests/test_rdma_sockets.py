@@ -15,7 +15,7 @@ from gpubridge_b200.ops import _lib
 pytestmark = pytest.mark.skipif(not _lib.available(), reason="the native library is not built")
 
 
-def _members(count, body, leave_together=True, **settings):
+def _members(count, body, leave_together=True, tcp=False, **settings):
     """``body(endpoint, index)`` on ``count`` members.  They close together unless told not to: a
     member that closes is a member that went away, and its peers' endpoints break."""
     names, ready, finished = [None] * count, threading.Barrier(count), threading.Barrier(count)
@@ -27,7 +27,8 @@ def _members(count, body, leave_together=True, **settings):
             def publish(name):
                 names[i] = name
                 ready.wait(20)
-            endpoint = rdma.Endpoint.over_sockets(i, count, publish, lambda: list(names), 20.0, **settings)
+            endpoint = rdma.Endpoint.over_sockets(i, count, publish, lambda: list(names), 20.0,
+                                                  tcp_host="127.0.0.1" if tcp else None, **settings)
             out[i] = body(endpoint, i)
             if leave_together:
                 finished.wait(30)
@@ -66,8 +67,9 @@ def test_eager_and_rendezvous_messages_cross_the_sockets():
     assert receiver["mr_misses"] == 1 and not receiver["broken"]
 
 
+@pytest.mark.parametrize("tcp", [False, True], ids=["unix", "tcp"])
 @pytest.mark.parametrize("count", [2, 3, 4])
-def test_tagged_collectives_over_sockets(count):
+def test_tagged_collectives_over_sockets(count, tcp):
     def body(ep, i):
         deadline = time.monotonic() + 30
         t = torch.arange(200_000, dtype=torch.float32) + i
@@ -77,7 +79,7 @@ def test_tagged_collectives_over_sockets(count):
         return t, b
 
     want = count * torch.arange(200_000, dtype=torch.float32) + sum(range(count))
-    for t, b in _members(count, body):
+    for t, b in _members(count, body, tcp=tcp):
         assert torch.equal(t, want) and torch.equal(b, torch.full((70_000,), float(count - 1)))
 
 
@@ -124,11 +126,12 @@ def _through_sockets(rank, topology, policy):
     return topology.policy_name
 
 
-@pytest.mark.parametrize("policy", ["auto", "pipelined-reduce-bridge-broadcast", "sharded-bridge"])
-def test_policies_over_the_verbs_bridge_between_processes(tmp_path, policy):
+@pytest.mark.parametrize("policy, provider", [("auto", "sockets"), ("pipelined-reduce-bridge-broadcast", "sockets"),
+                                              ("sharded-bridge", "sockets"), ("auto", "tcp")])
+def test_policies_over_the_verbs_bridge_between_processes(tmp_path, policy, provider):
     out = run_ranks(LAYOUTS["2+2"], _through_sockets, tmp_path, policy,
                     init={"bridge": "verbs", "policy": policy},
-                    env={"GPUBRIDGE_VERBS_PROVIDER": "sockets"}, timeout=120)
+                    env={"GPUBRIDGE_VERBS_PROVIDER": provider}, timeout=120)
     assert len(set(out)) == 1
 
 
