@@ -79,7 +79,13 @@ def plan_hier(n: int, esize: int, *, k: int, m_max: int, n_islands: int, len_ha:
     line up.  Every channel owns two buffers of each region; a stripe fits the smallest slot
     (``m_max`` slots in region A, ``n_islands`` in region B, one in region C).  ``stripe_multiple``:
     the stripe length is a multiple of it (256 values; 256 * islands for the two-shot bridge,
-    whose sub-stripes must be whole quantisation-block multiples too)."""
+    whose sub-stripes must be whole quantisation-block multiples too).
+
+    ``grid`` is one of those shared values too, although it comes from the calling thread's
+    grid cap (``Fabric.grid_cap``): a collective is one call on every rank, made from the same
+    place in the program - inside the same ``grid_cap`` block or on the same async path - so
+    the cap is the same everywhere; a program that caps one rank's call and not its peers' is
+    as wrong as one that passes them different sizes."""
     nbytes = n * esize
     # Channels: independent pipelines that hide each other's barriers and local phases.
     # One for small tensors (a barrier costs more than the data), up to four for large.
