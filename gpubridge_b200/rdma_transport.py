@@ -34,7 +34,7 @@ import torch
 from gpubridge_b200 import config as _config
 from gpubridge_b200 import gdr as _gdr
 from gpubridge_b200 import rdma as _rdma
-from gpubridge_b200.tagged import DTYPE_CODES, OP_CODES, TaggedBridge
+from gpubridge_b200.tagged import DTYPE_CODES, OP_CODES, OnDevice, TaggedBridge
 
 DIRECT_MIN_ENV = "GPUBRIDGE_VERBS_DIRECT_MIN_BYTES"
 STAGING_ENV = "GPUBRIDGE_VERBS_STAGING_BYTES"
@@ -58,6 +58,10 @@ class Router:
                            if direct_min_bytes is None else direct_min_bytes)
         self._plans = flush_plans or _gdr.plan
         self.counts = collections.Counter()
+
+    def plan(self, device: int):
+        """The flush plan of ``device`` this router decides by."""
+        return self._plans(device)
 
     def route(self, tensor: torch.Tensor) -> Route:
         chosen = self._route(tensor)
@@ -134,6 +138,7 @@ class RdmaTransport(TaggedBridge):
         self.piece_bytes = (_config.size_setting(PIECE_ENV, 8 << 20, multiple=256)
                             if piece_bytes is None else piece_bytes)
         self._copy_stream = None
+        self.last_route: Route | None = None
 
     @classmethod
     def _connect(cls, store, key, members, rank, timeout, deadline):
@@ -150,7 +155,8 @@ class RdmaTransport(TaggedBridge):
             index, len(members),
             publish=lambda name: store.set(f"{key}/socket/{rank}", name),
             collect=lambda: wait_for_keys(store, [f"{key}/socket/{m}" for m in members], deadline,
-                                          "every bridge member's socket name"),
+                                          "every bridge member's socket name",
+                                          verdicts=[f"{key}/status/{m}" for m in members if m != rank]),
             timeout=max(0.1, deadline - time.monotonic()), tcp_host=tcp_host)
         chunk = _config.size_setting("GPUBRIDGE_VERBS_CHUNK_BYTES", 4 << 20)
         return cls(endpoint, members, rank, timeout, chunk)
@@ -171,7 +177,9 @@ class RdmaTransport(TaggedBridge):
             return
         self._carry(tensor, lambda view, number, deadline: self.worker.all_reduce(
             view.data_ptr(), view.numel(), DTYPE_CODES[view.dtype], OP_CODES[op],
-            max(1, self.chunk_bytes // view.element_size()), number, deadline))
+            max(1, self.chunk_bytes // view.element_size()), number, deadline),
+            where_it_lies=lambda flat, number, deadline: self._on_device(flat).all_reduce(
+                flat, op, max(1, self.chunk_bytes // flat.element_size()), number, deadline))
 
     def broadcast(self, tensor: torch.Tensor, src: int) -> None:
         if len(self.members) == 1 or tensor.numel() == 0:
@@ -179,24 +187,43 @@ class RdmaTransport(TaggedBridge):
         root = self.members.index(src)
         self._carry(tensor, lambda view, number, deadline: self.worker.broadcast(
             view.data_ptr(), view.numel() * view.element_size(), root, max(1, self.chunk_bytes),
-            number, deadline), only_out=self.index != root, only_in=self.index == root)
+            number, deadline), only_out=self.index != root, only_in=self.index == root,
+            where_it_lies=lambda flat, number, deadline: self._on_device(flat).broadcast(
+                flat, root, self.chunk_bytes, number, deadline))
 
-    def _carry(self, tensor: torch.Tensor, run, only_out: bool = False, only_in: bool = False) -> None:
+    def _on_device(self, flat: torch.Tensor) -> OnDevice:
+        """Message by message, reductions where the tensor lives: before every post the
+        tensor's stream has finished its producers, after every receive the device's flush
+        plan has run."""
+        if flat.device.type != "cuda":
+            return OnDevice(self.worker, len(self.members), self.index)
+        stream = torch.cuda.current_stream(flat.device)
+        flush = self.router.plan(flat.device.index or 0)
+        return OnDevice(self.worker, len(self.members), self.index, settle=stream.synchronize,
+                        landed=flush.after_receive)
+
+    def _carry(self, tensor: torch.Tensor, run, only_out: bool = False, only_in: bool = False,
+               where_it_lies=None) -> None:
         if tensor.dtype not in DTYPE_CODES:
             raise ValueError(f"the {self.name} bridge cannot carry {tensor.dtype}")
         route = self.router.route(tensor)
+        self.last_route = route
         deadline = time.monotonic() + self.timeout
         try:
-            if route.how != "bounce":
+            if route.how == "in-place":
+                self._calls += 1
+                self._in_place(tensor.view(-1), self._calls, deadline, where_it_lies)
+            elif route.how == "plain":
                 self._calls += 1
                 run(tensor, self._calls, deadline)
-                if route.how == "in-place":
-                    _gdr.plan(tensor.device.index or 0).after_receive()
-                return
-            self._bounce(tensor, run, deadline, only_out, only_in)
+            else:
+                self._bounce(tensor, run, deadline, only_out, only_in)
         except BaseException:
             self.worker.abort()
             raise
+
+    def _in_place(self, flat: torch.Tensor, number: int, deadline: float, where_it_lies) -> None:
+        where_it_lies(flat, number, deadline)
 
     def _bounce(self, tensor: torch.Tensor, run, deadline: float, only_out: bool, only_in: bool) -> None:
         """Through registered host memory, in pieces: while the network works on piece ``i``

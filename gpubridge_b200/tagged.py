@@ -56,15 +56,116 @@ def ring_order(segment: int, members: int) -> list[int]:
     return [(segment + hop) % members for hop in range(members)]
 
 
-def wait_for_keys(store, keys: Sequence[str], deadline: float, what: str) -> list[str]:
+def message_tag(number: int, step: int, sender: int, chunk: int) -> int:
+    """The 64-bit tag of one message, as the native collectives number them: call (24 bits),
+    step (12), sending member (8), chunk (20)."""
+    return ((number & 0xFFFFFF) << 40) | ((step & 0xFFF) << 28) | ((sender & 0xFF) << 20) | (chunk & 0xFFFFF)
+
+
+_FOLDS = {"sum": lambda mine, theirs: mine.add_(theirs),
+          "max": lambda mine, theirs: torch.maximum(mine, theirs, out=mine),
+          "min": lambda mine, theirs: torch.minimum(mine, theirs, out=mine)}
+
+
+class OnDevice:
+    """The collectives of the native workers, message by message from Python, for tensors whose
+    reduction has to run where they live: a worker that reads and writes device memory itself
+    (GPUDirect) cannot fold on the host.  Same cuts, order and tags as ``csrc/gb_tagged.cpp``;
+    the worker only needs ``send(peer, pointer, nbytes, tag)``, ``recv(...)`` and
+    ``wait(ids, deadline)``.
+
+    ``settle`` runs before messages are posted (the producer of the bytes must have finished:
+    a stream synchronise for device tensors) and ``landed`` after receives completed and before
+    anything reads them (the flush of direct writes, where the device needs one).
+    """
+
+    def __init__(self, worker: Any, members: int, index: int, settle=None, landed=None) -> None:
+        self.worker, self.members, self.index = worker, members, index
+        self.settle = settle or (lambda: None)
+        self.landed = landed or (lambda: None)
+
+    def _post(self, sending: bool, peer: int, flat: torch.Tensor, chunk: int, number: int, step: int,
+              sender: int, ids: list[int]) -> None:
+        esize, base, count = flat.element_size(), flat.data_ptr(), flat.numel()
+        starts = range(0, count, chunk) if count else [0]
+        for index, start in enumerate(starts):
+            n = min(chunk, count - start)
+            call = self.worker.send if sending else self.worker.recv
+            ids.append(call(peer, base + start * esize, n * esize, message_tag(number, step, sender, index)))
+
+    def all_reduce(self, flat: torch.Tensor, op: str, chunk_elems: int, number: int, deadline: float) -> None:
+        size, me, fold = self.members, self.index, _FOLDS[op]
+        if size == 1 or flat.numel() == 0:
+            return
+        chunk = max(1, chunk_elems)
+        if size == 2:
+            scratch = torch.empty_like(flat)
+            ids: list[int] = []
+            self.settle()
+            self._post(False, 1 - me, scratch, chunk, number, 0, 1 - me, ids)
+            self._post(True, 1 - me, flat, chunk, number, 0, me, ids)
+            self.worker.wait(ids, deadline)
+            self.landed()
+            fold(flat, scratch)
+            return
+        cuts = segments(flat.numel(), size)
+        piece = lambda i: flat.narrow(0, *cuts[i % size])                      # noqa: E731
+        scratch = torch.empty(cuts[0][1], dtype=flat.dtype, device=flat.device)
+        right, left = (me + 1) % size, (me - 1) % size
+        for step in range(size - 1):                                           # reduce-scatter
+            arriving, leaving = piece(me - step - 1), piece(me - step)
+            ids = []
+            self.settle()
+            self._post(False, left, scratch[:arriving.numel()], chunk, number, step, left, ids)
+            self._post(True, right, leaving, chunk, number, step, me, ids)
+            self.worker.wait(ids, deadline)
+            self.landed()
+            fold(arriving, scratch[:arriving.numel()])
+        for step in range(size - 1):                                           # all-gather
+            ids = []
+            self.settle()
+            self._post(False, left, piece(me - step), chunk, number, size + step, left, ids)
+            self._post(True, right, piece(me + 1 - step), chunk, number, size + step, me, ids)
+            self.worker.wait(ids, deadline)
+        self.landed()
+
+    def broadcast(self, flat: torch.Tensor, root: int, chunk_bytes: int, number: int, deadline: float) -> None:
+        if self.members == 1 or flat.numel() == 0:
+            return
+        raw = flat.view(torch.uint8)
+        ids: list[int] = []
+        self.settle()
+        if self.index == root:
+            for peer in range(self.members):
+                if peer != root:
+                    self._post(True, peer, raw, max(1, chunk_bytes), number, 0, root, ids)
+        else:
+            self._post(False, root, raw, max(1, chunk_bytes), number, 0, root, ids)
+        self.worker.wait(ids, deadline)
+        if self.index != root:
+            self.landed()
+
+
+def wait_for_keys(store, keys: Sequence[str], deadline: float, what: str,
+                  verdicts: Sequence[str] = ()) -> list[str]:
     """Values of ``keys`` once all exist; polls in short slices so the deadline is honoured
-    whatever timeout type the store raises."""
+    whatever timeout type the store raises.  ``verdicts`` are keys under which members publish
+    how their set-up ended: as soon as one of them holds anything but ``ok`` the wait is over -
+    that member will never publish what is waited for."""
     wanted = list(keys)
     while True:
-        slice_s = max(0.05, min(2.0, deadline - time.monotonic()))
+        slice_s = max(0.05, min(0.5 if verdicts else 2.0, deadline - time.monotonic()))
         try:
             store.wait(wanted, timedelta(seconds=slice_s))
         except Exception:  # noqa: BLE001
+            for key in verdicts:
+                try:
+                    store.wait([key], timedelta(milliseconds=1))
+                    said = store.get(key).decode()
+                except Exception:  # noqa: BLE001 - not published yet
+                    continue
+                if said != "ok":
+                    raise RuntimeError(f"gave up waiting for {what}: another member's set-up failed") from None
             if time.monotonic() >= deadline:
                 raise RuntimeError(f"timed out waiting for {what}") from None
             continue

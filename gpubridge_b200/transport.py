@@ -5,8 +5,9 @@ leaders' data, this class only carries the name, the reductions and a device fal
 The host-staged transports of the reference survive as the cross-node fallback and as
 what CPU simulation runs: ``gloo`` (a Gloo group of the leaders; reference:
 src/gpubridge/transport.py:127-153) and ``multitcp`` (native multi-stream TCP worker,
-:mod:`gpubridge_b200.multitcp`).  ``ucx`` and ``verbs`` are known names that report why
-they are unavailable when their system headers are missing, as the reference's loaders do
+:mod:`gpubridge_b200.multitcp`).  ``ucx`` (:mod:`gpubridge_b200.ucx`: a worker compiled at first
+use against the machine's UCX) and ``verbs`` (:mod:`gpubridge_b200.rdma`) load when what they need
+is there and otherwise say, on every rank alike, what is missing, as the reference's loaders do
 (src/gpubridge/ucx/__init__.py:45-46).
 """
 from __future__ import annotations
@@ -131,7 +132,7 @@ DEFAULT_TRANSPORT = GlooTransport.name
 _TRANSPORTS: dict[str, type[BridgeTransport]] = {
     GlooTransport.name: GlooTransport, NvlinkTransport.name: NvlinkTransport}
 #: Opt-in transports, imported at first use.
-_BUILT_IN = {"multitcp": "gpubridge_b200.multitcp", "ucx": "gpubridge_b200.unavailable",
+_BUILT_IN = {"multitcp": "gpubridge_b200.multitcp", "ucx": "gpubridge_b200.ucx.transport",
              "verbs": "gpubridge_b200.rdma"}
 
 

@@ -224,7 +224,3 @@ def test_the_command_lines_say_what_this_build_has():
     done = subprocess.run([sys.executable, "-m", "gpubridge_b200.rdma", "info"], capture_output=True, text=True)
     told = json.loads(done.stdout)
     assert told["protocol"] >= 1 and told["in_process_fabric"] and told["provider"] is None
-    done = subprocess.run([sys.executable, "-m", "gpubridge_b200.unavailable", "info"], capture_output=True, text=True)
-    assert "ucx" in json.loads(done.stdout)
-    done = subprocess.run([sys.executable, "-m", "gpubridge_b200.unavailable", "build"], capture_output=True, text=True)
-    assert done.returncode == 1 and "nothing to build" in done.stderr
