@@ -193,46 +193,66 @@ struct UcxWorker final : GbTaggedWorker {
         (void)peer;
         return post(true, -1, data, length, tag);
     }
+    // Collect what has completed among `ids`; `open` says whether any is still in flight.
+    // < 0: one of them failed (the worker is broken and has let go of everything).
+    int sweep(const long* ids, int n, bool* open) {
+        *open = false;
+        for (int i = 0; i < n; ++i) {
+            auto found = table.find(ids[i]);
+            if (found == table.end()) continue;                  // completed and collected before
+            Operation* op = found->second;
+            if (!op->done) { *open = true; continue; }
+            if (op->status != UCS_OK) {
+                const std::string why = std::string(op->receive ? "a receive" : "a send") + " failed: " +
+                                        ucs_status_string(op->status);
+                retire(op);
+                wreck(GB_UCX_PEER_FAILED, why);
+                let_go(2.0);
+                return broken_code;
+            }
+            if (op->receive && op->arrived != op->posted) {
+                const std::string why = "a message of " + std::to_string(op->arrived) + " bytes arrived for a "
+                    "receive of " + std::to_string(op->posted) + ": the members disagree about the call";
+                retire(op);
+                wreck(GB_UCX_FAILED, why);
+                let_go(2.0);
+                return broken_code;
+            }
+            retire(op);
+        }
+        if (*open && check_links() != 0) { let_go(2.0); return broken_code; }
+        return 0;
+    }
+
     int wait(const long* ids, int n, double timeout_s) override {
         if (broken) return broken_code;
         const double until = seconds_now() + (timeout_s > 0 ? timeout_s : 0);
         unsigned spins = 0;
         for (;;) {
             bool open = false;
-            for (int i = 0; i < n; ++i) {
-                auto found = table.find(ids[i]);
-                if (found == table.end()) continue;                  // completed and collected before
-                Operation* op = found->second;
-                if (!op->done) { open = true; continue; }
-                if (op->status != UCS_OK) {
-                    const std::string why = std::string(op->receive ? "a receive" : "a send") + " failed: " +
-                                            ucs_status_string(op->status);
-                    retire(op);
-                    wreck(GB_UCX_PEER_FAILED, why);
-                    let_go(2.0);
-                    return broken_code;
-                }
-                if (op->receive && op->arrived != op->posted) {
-                    const std::string why = "a message of " + std::to_string(op->arrived) + " bytes arrived for a "
-                        "receive of " + std::to_string(op->posted) + ": the members disagree about the call";
-                    retire(op);
-                    wreck(GB_UCX_FAILED, why);
-                    let_go(2.0);
-                    return broken_code;
-                }
-                retire(op);
-            }
+            const int rc = sweep(ids, n, &open);
+            if (rc != 0) return rc;
             if (!open) return 0;
-            if (check_links() != 0) { let_go(2.0); return broken_code; }
             if (seconds_now() > until) {
                 wreck(GB_UCX_TIMED_OUT, "operations were still outstanding at the deadline "
-                        "(a member that never joined, or a slower link than the timeout allows)");
+                      "(a member that never joined, or a slower link than the timeout allows)");
                 let_go(2.0);
                 return broken_code;
             }
             ++progress_calls;
             if (ucp_worker_progress(worker) == 0 && ++spins > 2000) { sched_yield(); spins = 0; }
         }
+    }
+    // Without waiting: progress a little, then 0 (all complete), 1 (some in flight) or < 0.
+    int poll(const long* ids, int n) {
+        if (broken) return broken_code;
+        for (int round = 0; round < 8; ++round) {
+            ++progress_calls;
+            if (ucp_worker_progress(worker) == 0) break;
+        }
+        bool open = false;
+        const int rc = sweep(ids, n, &open);
+        return rc != 0 ? rc : (open ? 1 : 0);
     }
     void stop() override {
         wreck(GB_UCX_FAILED, reason.empty() ? "stopped after a failed call" : reason);
@@ -396,6 +416,15 @@ int gb_ucx_wait(void* handle, const long long* ids, int count, double timeout_s)
     std::lock_guard<std::mutex> hold(w->gate);
     std::vector<long> own(ids, ids + count);
     return w->wait(own.data(), count, timeout_s);
+}
+
+// The same without waiting: 0 all complete, 1 some still in flight, < 0 failed.  Lets several
+// threads share one worker without one of them holding it for the length of a wait.
+int gb_ucx_poll(void* handle, const long long* ids, int count) {
+    auto* w = static_cast<UcxWorker*>(handle);
+    std::lock_guard<std::mutex> hold(w->gate);
+    std::vector<long> own(ids, ids + count);
+    return w->poll(own.data(), count);
 }
 
 int gb_ucx_all_reduce(void* handle, void* data, unsigned long long count, int dtype, int op,

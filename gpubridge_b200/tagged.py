@@ -222,6 +222,13 @@ class TaggedBridge(BridgeTransport):
     def _connect(cls, store, key, members, rank, timeout, deadline) -> "TaggedBridge":
         raise NotImplementedError
 
+    @classmethod
+    def create_p2p(cls, group, *, store=None, timeout=None):
+        """Cross-island point-to-point of a bridge without a wire of its own for it: the job's
+        Gloo group carries the engine's host buffers (a subclass may bring its own link)."""
+        from gpubridge_b200.p2p import GlooLink
+        return GlooLink(group)
+
     def prove(self, deadline: float) -> None:
         """One all-reduce of the members' indices: the sum is known in advance."""
         count = len(self.members)

@@ -147,6 +147,7 @@ def _declare(lib: ctypes.CDLL) -> ctypes.CDLL:
         "gb_ucx_send": (c.c_longlong, [ptr, c.c_int, ptr, u64, u64]),
         "gb_ucx_recv": (c.c_longlong, [ptr, ptr, u64, u64]),
         "gb_ucx_wait": (c.c_int, [ptr, c.POINTER(c.c_longlong), c.c_int, c.c_double]),
+        "gb_ucx_poll": (c.c_int, [ptr, c.POINTER(c.c_longlong), c.c_int]),
         "gb_ucx_all_reduce": (c.c_int, [ptr, ptr, u64, c.c_int, c.c_int, u64, u64, c.c_double]),
         "gb_ucx_broadcast": (c.c_int, [ptr, ptr, u64, c.c_int, u64, u64, c.c_double]),
         "gb_ucx_abort": (None, [ptr]),
@@ -269,6 +270,13 @@ class Worker:
             array = (ctypes.c_longlong * len(ids))(*ids)
             self._check(self.lib.gb_ucx_wait(self._live(), array, len(ids),
                                              max(0.0, deadline - time.monotonic())))
+
+    def poll(self, ids: Sequence[int]) -> bool:
+        """Progress a little without waiting; True once every operation of ``ids`` is complete."""
+        if not ids:
+            return True
+        array = (ctypes.c_longlong * len(ids))(*ids)
+        return self._check(self.lib.gb_ucx_poll(self._live(), array, len(ids))) == 0
 
     # -- the interface of a tagged bridge's worker
     def all_reduce(self, pointer: int, count: int, dtype: int, op: int, chunk_elems: int, number: int,

@@ -115,6 +115,13 @@ class UcxTransport(RdmaTransport):
             if self.worker is not None and self.worker.handle:
                 self.worker.memory(_ucx.HOST)
 
+    @classmethod
+    def create_p2p(cls, group, *, store=None, timeout=None):
+        """The wire of the cross-island point-to-point engine: workers of its own, one per peer."""
+        from gpubridge_b200.tagged import DEFAULT_TIMEOUT
+        from gpubridge_b200.ucx.p2p import UcxLink
+        return UcxLink(group.rank, store, timeout or DEFAULT_TIMEOUT)
+
     def describe(self) -> dict:
         told = super().describe()
         told["paths"] = {PATHS[how]: count for how, count in self.router.counts.items()}

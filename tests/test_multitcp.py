@@ -156,3 +156,32 @@ def test_native_collectives_ring():
 
 def test_native_collectives_ring_of_five():
     _native_matches_the_documented_order(5)
+
+
+def _p2p_beside_a_tagged_bridge(rank, world):
+    import torch.distributed as dist
+    from gpubridge_b200.p2p import GlooLink
+    dist.barrier()
+    peer = {0: 2, 2: 0}.get(rank)
+    if peer is not None:
+        data = torch.arange(70_001, dtype=torch.float32)
+        if rank == 0:
+            dist.send(data, peer, tag=4)
+        else:
+            got = torch.zeros(70_001)
+            dist.recv(got, peer, tag=4)
+            assert torch.equal(got, data)
+        assert isinstance(dist.distributed_c10d._get_default_group()._engine.link, GlooLink)
+    t = torch.ones(100) * rank
+    dist.all_reduce(t)
+    assert float(t[0]) == 6.0
+    dist.barrier()
+    return True
+
+
+def test_cross_island_point_to_point_with_the_multitcp_bridge(tmp_path):
+    """A bridge that brings no point-to-point wire of its own leaves that traffic to the job's
+    Gloo group instead of refusing it."""
+    from _harness import TWO_BY_TWO, run_ranks
+    run_ranks(TWO_BY_TWO, _p2p_beside_a_tagged_bridge, tmp_path, mode="backend", timeout=120,
+              env={"GPUBRIDGE_BRIDGE": "multitcp"})

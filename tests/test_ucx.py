@@ -533,3 +533,100 @@ def _vanish_entry(rank, path, env, results):
     results.close()
     results.join_thread()                                        # the message is out before the process is
     os._exit(0)                                                  # nobody waits for a group that lost a member
+
+
+# ---- point-to-point between islands over UCX ---------------------------------------------------------
+def test_the_point_to_point_link_in_threads(fake_ucx):
+    """Two ranks, one link each, a store that is a dict: several tags in flight at once, received
+    in another order than sent, while a request that nobody answers does not keep the rest back."""
+    from gpubridge_b200.ucx.p2p import UcxLink
+
+    class Store:
+        def __init__(self):
+            self.items, self.ready = {}, threading.Condition()
+
+        def set(self, key, value):
+            with self.ready:
+                self.items[key] = value.encode() if isinstance(value, str) else value
+                self.ready.notify_all()
+
+        def get(self, key):
+            return self.items[key]
+
+        def wait(self, keys, timeout):
+            with self.ready:
+                if not self.ready.wait_for(lambda: all(k in self.items for k in keys), timeout.total_seconds()):
+                    raise TimeoutError(keys)
+
+    store, out, errors = Store(), {}, []
+    payloads = {tag: torch.full((50_000,), float(tag)) for tag in (3, 4, 5)}
+
+    def run(rank):
+        link = UcxLink(rank, store, timedelta(seconds=20))
+        try:
+            peer = 1 - rank
+            if rank == 0:
+                lonely = link.post(torch.zeros(8), peer, 99, False)          # never answered
+                requests = [link.post(payloads[tag], peer, tag, True) for tag in (3, 4, 5)]
+                for r in requests:
+                    r.wait(timedelta(seconds=20))
+                with pytest.raises(TimeoutError):
+                    lonely.wait(timedelta(seconds=0.3))
+                with pytest.raises(ValueError, match="host buffers"):
+                    link.post(torch.zeros(1, device="meta"), peer, 1, True)
+            else:
+                rooms = {tag: torch.zeros(50_000) for tag in (5, 3, 4)}
+                requests = [link.post(rooms[tag], peer, tag, False) for tag in (5, 3, 4)]
+                for r in requests:
+                    r.wait(timedelta(seconds=20))
+                out[rank] = {tag: float(room[0]) for tag, room in rooms.items()}
+        except BaseException as failure:  # noqa: BLE001
+            errors.append((rank, repr(failure)))
+        finally:
+            link.close()
+            with pytest.raises(RuntimeError, match="closed"):
+                link.post(torch.zeros(1), 1 - rank, 1, True)
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in (0, 1)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    assert not errors, errors
+    assert out[1] == {3: 3.0, 4: 4.0, 5: 5.0}
+
+
+def _p2p_over_ucx(rank, world):
+    import torch.distributed as dist
+    dist.barrier()
+    peer = {0: 2, 2: 0, 1: 3, 3: 1}[rank]                           # every pair crosses the islands
+    lower = rank < peer
+    for n in (0, 1, 4099, 300_001):
+        data = (torch.arange(n) % 13).to(torch.float32) + min(rank, peer)
+        if lower:
+            dist.send(data, peer, tag=7)
+        else:
+            got = torch.full((n,), 99.0)
+            dist.recv(got, peer, tag=7)
+            assert torch.equal(got, data), n
+    # both directions at once, batched
+    mine, theirs = torch.full((10_000,), float(rank)), torch.empty(10_000)
+    ops = [dist.P2POp(dist.isend, mine, peer, tag=3), dist.P2POp(dist.irecv, theirs, peer, tag=3)]
+    for work in dist.batch_isend_irecv(ops):
+        work.wait()
+    assert float(theirs[0]) == float(peer)
+    t = torch.ones(1000) * rank                                    # and the bridged collectives still work
+    dist.all_reduce(t)
+    assert float(t[0]) == 6.0
+    from gpubridge_b200.topology import get_topology
+    from gpubridge_b200.ucx.p2p import UcxLink
+    backend = dist.distributed_c10d._get_default_group()
+    assert get_topology().transport.name == "ucx" and isinstance(backend._engine.link, UcxLink)
+    assert sorted(backend._engine.link.pairs) == [peer]
+    dist.barrier()
+    return True
+
+
+def test_cross_island_point_to_point_over_ucx_through_the_backend(fake_ucx, tmp_path):
+    run_ranks(LAYOUTS["2+2"], _p2p_over_ucx, tmp_path, mode="backend", timeout=180,
+              env=dict(fake_ucx, GPUBRIDGE_BRIDGE="ucx", GPUBRIDGE_P2P_CHUNK_BYTES="64K"))
