@@ -237,3 +237,20 @@ class RankPool:
             if p.is_alive():
                 p.kill()
         self.procs = []
+
+
+def per_rank(rank, world, path, envs, init, fn=None, *args):
+    """For ``run_ranks(..., mode="plain")``: set THIS rank's environment (``envs[rank]``), join
+    with ``init`` and run ``fn(rank, topology, *args)`` - what a common ``env`` cannot express:
+    ranks that were started with different settings."""
+    import gpubridge_b200 as gb
+    os.environ.update(envs.get(rank, {}))
+    init = dict(init)
+    seconds = init.pop("seconds", 40)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", gb.SplitTestWarning)
+        topology = gb.init(f"file://{path}", rank=rank, world_size=world, timeout=timedelta(seconds=seconds), **init)
+        try:
+            return fn(rank, topology, *args) if fn is not None else "up"
+        finally:
+            gb.destroy()
