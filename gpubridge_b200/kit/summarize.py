@@ -52,6 +52,22 @@ def summarize(directory: Path, partial: bool = False) -> tuple[dict[str, Any], s
                     {k: v for k, v in s.items() if k not in ("name", "ok")}, default=str)
             elif s["ok"] is None:
                 problems[where] = "the rank was left inside this stage"
+    if not split:
+        # two ranks on one physical GPU is a mistake of the launch unless the run relabels on purpose
+        holders: dict[tuple, list[int]] = {}
+        for rank, j in sorted(journals.items()):
+            device = (j.get("run") or {}).get("device") or ""
+            if not device.startswith("cuda"):
+                continue
+            index = int(device.split(":")[1]) if ":" in device else 0
+            devices = (j.get("environment") or {}).get("devices") or []
+            bus = next((d.get("pci_bus_id") for d in devices if d and d.get("index") == index), None)
+            if bus:
+                holders.setdefault(((j.get("environment") or {}).get("hostname"), bus), []).append(rank)
+        for (host, bus), ranks in holders.items():
+            if len(ranks) > 1:
+                problems[f"ranks {ranks}"] = (f"share one GPU (PCI {bus} on {host}) outside a split test: "
+                                              "give every rank its own device")
     table = {name: {rank: next((s["ok"] for s in j["stages"] if s["name"] == name), None)
                     for rank, j in sorted(journals.items())} for name in stage_names}
     ok = (bool(journals) and (partial or not missing) and not problems
