@@ -51,6 +51,8 @@ class Plan:
 
 def in_flight(schedule: str, stages: int, microbatches: int) -> list[int]:
     """Microbatches whose activations each stage holds at once."""
+    if stages < 1 or microbatches < 1:
+        raise ValueError(f"a schedule needs at least one stage and one microbatch, got {stages} and {microbatches}")
     if schedule == "gpipe":
         return [microbatches] * stages
     if schedule == "1f1b":
