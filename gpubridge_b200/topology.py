@@ -154,7 +154,6 @@ def describe_local(bridge: str, policy: "str | type[CollectivePolicy]" = AUTO
     joining becomes an entry of :attr:`PeerInfo.problems` instead of an exception, so that
     discovery fails every rank with one message."""
     import os
-    split = _config.split_test_mode() or ""
     problems: list[str] = []
 
     def setting(read, default):
@@ -164,6 +163,7 @@ def describe_local(bridge: str, policy: "str | type[CollectivePolicy]" = AUTO
             problems.append(str(exc))
             return default
 
+    split = setting(_config.split_test_mode, None) or ""
     pinned = setting(_config.pinned_staging_setting, False)
     compression = setting(_config.bridge_compression_setting, "")
     islands = setting(_config.islands_setting, ())
