@@ -1,6 +1,7 @@
 """The UCX worker behind ``bridge="ucx"``: build it, load it, call it.
 
-``csrc/gb_ucx.cpp`` is a C++ worker over UCX's UCP tagged messages.  UCX is a system library,
+``gb_ucx.cpp`` beside this file is a C++ worker over UCX's UCP tagged messages (it is kept out of
+``csrc/``, whose every file is part of the package's own library).  UCX is a system library,
 so nothing of it is compiled with the package: ``python -m gpubridge_b200.ucx build`` compiles
 the worker against the UCX of this machine, and :func:`load` does so at first use - with the
 system C++ compiler, UCX found through ``UCX_HOME``, ``pkg-config ucx`` or the default include
@@ -11,7 +12,7 @@ that do not share one UCX.  Without a compiler or UCX, :class:`Unavailable` says
 missing; nothing else in the package needs this module.
 
 The collectives (two-member exchange, ring, broadcast; chunked, with a deadline) run inside the
-worker (``csrc/gb_tagged.cpp``); :class:`Worker` also gives the single messages, which the
+worker (``csrc/gb_tagged.cpp``, compiled in); :class:`Worker` also gives the single messages, which the
 bridge uses where the reduction has to run on a device.
 (Reference: src/gpubridge/ucx/__init__.py, whose collectives run in Python.)
 """
@@ -32,7 +33,7 @@ from collections.abc import Sequence
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
-SOURCES = (CSRC / "gb_ucx.cpp", CSRC / "gb_tagged.cpp")
+SOURCES = (Path(__file__).resolve().parent / "gb_ucx.cpp", CSRC / "gb_tagged.cpp")
 HEADERS = (CSRC / "gb_tagged.h",)
 LIB_DIR_ENV = "GPUBRIDGE_UCX_LIB_DIR"
 UCX_HOME_ENV = "UCX_HOME"

@@ -1,4 +1,4 @@
-"""``bridge="ucx"``: the worker of ``csrc/gb_ucx.cpp`` compiled against the stand-in UCP library of
+"""``bridge="ucx"``: the worker of ``ucx/gb_ucx.cpp`` compiled against the stand-in UCP library of
 ``tests/fake_ucx`` (same API, Unix-domain sockets underneath), which lets tests make UCX
 misbehave: members in threads for the worker itself, ranks in processes for the bridge of the
 policies and for what init promises when one leader's UCX is different or does not start.
@@ -630,3 +630,15 @@ def _p2p_over_ucx(rank, world):
 def test_cross_island_point_to_point_over_ucx_through_the_backend(fake_ucx, tmp_path):
     run_ranks(LAYOUTS["2+2"], _p2p_over_ucx, tmp_path, mode="backend", timeout=180,
               env=dict(fake_ucx, GPUBRIDGE_BRIDGE="ucx", GPUBRIDGE_P2P_CHUNK_BYTES="64K"))
+
+
+def test_the_workers_source_is_not_part_of_the_packages_own_library():
+    """Everything under ``csrc/`` is compiled into the package's library on every machine; a file
+    that needs UCX's headers there would break that build wherever UCX is absent."""
+    from gpubridge_b200 import ucx
+    from gpubridge_b200.ops import _build
+    assert ucx.SOURCES[0].exists() and ucx.SOURCES[0].parent != ucx.CSRC
+    for path in _build.sources():
+        with open(path) as fh:
+            text = fh.read()
+        assert "#include <ucp/" not in text and "#include <infiniband/" not in text, path
