@@ -52,8 +52,11 @@ class Router:
     give the same route on every member, so both ends of a link agree without talking."""
 
     def __init__(self, *, device_registration: bool = False, direct_min_bytes: int | None = None,
-                 flush_plans=None) -> None:
-        self.device_registration = device_registration
+                 flush_plans=None, registrar=None) -> None:
+        self.device_registration = device_registration or registrar is not None
+        #: a :class:`gpubridge_b200.rdma_direct.Registrar`: asked whether THIS range can be
+        #: registered (dma-buf or peer memory); its reasons become the route's when it cannot
+        self.registrar = registrar
         self.direct_min = (_config.size_setting(DIRECT_MIN_ENV, 64 << 10, multiple=1)
                            if direct_min_bytes is None else direct_min_bytes)
         self._plans = flush_plans or _gdr.plan
@@ -80,6 +83,14 @@ class Router:
         plan = self._plans(tensor.device.index or 0)
         if not plan.direct_ok:
             return Route("bounce", plan.reason)
+        if self.registrar is not None:
+            from gpubridge_b200.rdma_direct import NotDirect
+            try:
+                region = self.registrar.take(tensor.data_ptr(), tensor.nbytes)
+            except NotDirect as reasons:
+                return Route("bounce", f"the range cannot be registered ({reasons})")
+            self.registrar.give_back(region)               # stays cached for the call that follows
+            return Route("in-place", f"registered through {region.method}; {plan.reason}")
         return Route("in-place", plan.reason)
 
 
