@@ -10,6 +10,7 @@ import sys
 from pathlib import Path
 
 import pytest
+import torch
 
 from gpubridge_b200 import kit
 from gpubridge_b200.kit import baseline_identity, preflight, probe, report, stream_mutations, summarize
@@ -290,3 +291,45 @@ def test_the_probes_child_reports_its_pci_address():
     assert probe.child_pci("3", run=fake) == "1b:00" and seen["visible"] == "3"
     with pytest.raises(RuntimeError, match="no address.*exit code 1"):
         probe.child_pci("0", run=lambda *a, **k: Done(stdout="", stderr="boom", returncode=1))
+
+
+# ---- the small diagnosis programs -----------------------------------------------------------------------
+def test_the_supported_types_table_holds_for_gloo_in_this_torch(tmp_path):
+    from gpubridge_b200.kit import gloo_dtypes
+    found = gloo_dtypes.survey()
+    assert gloo_dtypes.verdict(found) == []                        # every promised type sums and broadcasts exactly
+    rows = found["rows"]
+    assert all(rows[name] == {"all_reduce": "ok", "broadcast": "ok"} for name in ("float32", "bfloat16", "int64", "uint8"))
+    # what the table leaves out is left out for a reason that still holds
+    left_out = [name for name in gloo_dtypes.EXTRAS if name in rows and name != "bool"]
+    assert any(rows[name]["all_reduce"] != "ok" for name in left_out)
+    broken = dict(found, rows=dict(rows, float16={"all_reduce": "refused: x", "broadcast": "ok"}))
+    assert gloo_dtypes.verdict(broken) == ["float16"]
+
+
+def test_the_codec_diagnosis_finds_nothing_where_the_bits_match_and_explains_where_they_do_not(capsys):
+    from gpubridge_b200 import compression as C
+    from gpubridge_b200.kit import codec_diagnosis
+    for mode, fmt in (("fp8", "ref"), ("fp8", "b200"), ("bf16", "ref")):
+        assert codec_diagnosis.diagnose(mode, fmt, 5000, "cpu") == []
+    assert codec_diagnosis.main(["--numel", "3000", "--device", "cpu"]) == 0
+    assert "identical to the oracle" in capsys.readouterr().out
+
+    def contracted(mode, x, residual, payload, fmt="ref"):
+        """An implementation whose residual is rounded once (as a fused multiply-add would) and
+        whose code of one value is off by one."""
+        C.quantize_reference(mode, x, residual, payload, fmt)
+        residual[100] = residual[100] + residual[100].abs() * 2.0 ** -22 + 1e-12
+        head = 4 * C.n_blocks(x.numel(), fmt)
+        payload[head + 200] ^= 1
+
+    found = codec_diagnosis.diagnose("fp8", "ref", 5000, "cpu", quantize=contracted)
+    text = "\n".join(found)
+    assert len(found) == 2 and "value 100 (block 0)" in text and "value 200 (block 0)" in text
+    assert "a fused multiply-add would leave" in text and "oracle 0x" in text and "residual" in text
+
+    def other_scale(mode, x, residual, payload, fmt="ref"):
+        C.quantize_reference(mode, x, residual, payload, fmt)
+        payload[:4].view(torch.float32).mul_(2)
+
+    assert any(line.startswith("block 0: scale") for line in codec_diagnosis.diagnose("fp8", "ref", 1000, "cpu", quantize=other_scale))
