@@ -10,7 +10,8 @@ message in the unexpected queue, a sender out of credits stalls and resumes, reg
 cached and dropped on invalidate, tagged collectives give the known sums, and each injected
 fault (an operation that fails, is dropped, delayed or corrupted; a member that dies) ends the
 waits of everybody involved with an error inside the time limit and leaves the endpoints
-broken.  ``perf`` times ping-pong latency and one-way bandwidth by message size.  ``ab`` runs
+broken; three more rows come from the registrar of device memory (which method it picks,
+every reason when none works, a reused address as another owner).  ``perf`` times ping-pong latency and one-way bandwidth by message size.  ``ab`` runs
 the bridge's all-reduce of one tensor under several settings (eager limit, write size, piece
 size of the bounce path) and reports each against the first.  Numbers from the in-process
 fabric measure this library's own work per message - queueing, matching, copying - not a
@@ -96,6 +97,52 @@ def _fault(kind: str, members: int = 2) -> dict:
     return {"ok": ok, "seconds": round(took, 2), "members_failed": failed, "broken": broken}
 
 
+def _registration() -> list[tuple[str, dict]]:
+    """The registrar of device memory on pretend device memory and a pretend adapter: the method
+    it picks, what it says when no method works, and that a stale address is another owner."""
+    import tempfile
+
+    from gpubridge_b200 import rdma_direct
+    found = []
+    with tempfile.TemporaryDirectory() as root:
+        Path(root, "proc").mkdir()
+        Path(root, "proc", "modules").write_text("nvidia_peermem 16384 0 - Live 0x0\n")
+        registrar = rdma_direct.Registrar.pretend(root)
+        try:
+            a = registrar.alloc(8 << 20)
+            with registrar.acquire(a, 1 << 20) as first:
+                pass
+            registrar.invalidate(a, 8 << 20)
+            registrar.fail("device dma-buf", "not exported")
+            with registrar.acquire(a, 1 << 20) as second:
+                pass
+            found.append(("device registration: dma-buf first, then peer memory",
+                          {"ok": (first.method, second.method) == ("dma-buf", "peer memory"),
+                           "methods": [first.method, second.method]}))
+            registrar.invalidate(a, 8 << 20)
+            registrar.fail("device peer memory", "not allowed")
+            try:
+                registrar.take(a, 1 << 20)
+                reasons = None
+            except rdma_direct.NotDirect as why:
+                reasons = str(why)
+            found.append(("device registration: every reason when nothing works",
+                          {"ok": reasons == "dma-buf: not exported; peer memory: not allowed", "reasons": reasons}))
+            registrar.fail("device dma-buf")
+            with registrar.acquire(a, 1 << 20) as old:
+                pass
+            registrar.free(a)
+            registrar.alloc(8 << 20, at=a)
+            with registrar.acquire(a, 1 << 20) as new:
+                pass
+            told = registrar.telemetry()
+            found.append(("device registration: the same address later is another owner",
+                          {"ok": new.key != old.key and told["stale_dropped"] == 1, "telemetry": told}))
+        finally:
+            registrar.close()
+    return found
+
+
 def check(out: Path) -> int:
     rows = []
 
@@ -128,6 +175,8 @@ def check(out: Path) -> int:
                                                  "errors": [r["error"] for r in result if r["error"]]})
     for kind in ("error", "drop", "delay", "corrupt", "kill"):
         row(f"fault: {kind}", _fault(kind, 3 if kind == "kill" else 2))
+    for name, result in _registration():
+        row(name, result)
     out.mkdir(parents=True, exist_ok=True)
     (out / "rdma_check.json").write_text(json.dumps({"schema": "gpubridge_b200.rdma_kit/1", "rows": rows}, indent=1))
     failed = [r["scenario"] for r in rows if not r["ok"]]
