@@ -4,10 +4,16 @@
 // Contract (the reference's multi-stream TCP worker, written there in Rust:
 // src/gpubridge/multitcp/crate/src/lib.rs:656-840): a worker listens on one port; for every
 // pair of members the lower index dials `streams` connections to the higher; a message is a
-// 16-byte header {tag, length} followed by its bytes and travels on one connection, chosen
-// round robin; every connection has a sender thread (fed by a queue) and a receiver thread;
+// 16-byte header {tag, length} followed by its bytes and travels on one connection, chosen by
+// its tag (the chunk number sits in the tag's low bits, so the chunks of a message fan out over
+// the connections like a round robin would, while messages that share a tag share a connection
+// and so arrive in the order sent); every connection has a sender thread (fed by a queue) and
+// a receiver thread;
 // a receive is matched by (peer, tag), and a message that arrives before its receive is
-// posted is buffered; send() and recv() return operation ids at once and wait() blocks until
+// posted is buffered - and stays receivable after its sender has closed: a member that ends
+// its connections between two messages has left, which fails what still waits for it and what
+// is posted towards it later, but is not a wreck of the whole worker (a connection that ends
+// in the middle of a message is); send() and recv() return operation ids at once and wait() blocks until
 // the listed operations are done or a deadline passes.  A failed wait stops every thread
 // before it returns, so no thread touches the caller's memory afterwards.
 #include <arpa/inet.h>
@@ -66,12 +72,13 @@ struct Worker {
     long next_id = 1;
     std::vector<std::unique_ptr<Conn>> conns;
     std::vector<std::vector<int>> by_peer;         // connection indices of each peer
-    std::vector<size_t> round_robin;
     std::map<std::pair<int, uint64_t>, long> posted;                  // receives waiting
     std::map<std::pair<int, uint64_t>, std::deque<std::vector<char>>> early;   // unexpected messages
+    std::vector<int> open_conns;                   // per peer: connections that have not ended
     std::atomic<bool> stopping{false};
     bool broken = false;
     std::string error;
+    bool gone(int peer) const { return !by_peer[peer].empty() && open_conns[peer] == 0; }
 };
 
 thread_local std::string g_error;
@@ -81,7 +88,9 @@ void set_error(Worker* w, const std::string& text) {
     g_error = text;
 }
 
-bool read_all(int fd, char* p, uint64_t n, std::atomic<bool>& stop) {
+bool read_all(int fd, char* p, uint64_t n, std::atomic<bool>& stop, bool* ended_cleanly = nullptr) {
+    const uint64_t wanted = n;
+    if (ended_cleanly != nullptr) *ended_cleanly = false;
     while (n > 0) {
         pollfd pfd{fd, POLLIN, 0};
         int ready = poll(&pfd, 1, 100);
@@ -89,7 +98,11 @@ bool read_all(int fd, char* p, uint64_t n, std::atomic<bool>& stop) {
         if (ready == 0) continue;
         if (ready < 0) { if (errno == EINTR) continue; return false; }
         ssize_t got = ::recv(fd, p, n > (1u << 30) ? (1u << 30) : n, 0);
-        if (got <= 0) { if (got < 0 && (errno == EINTR || errno == EAGAIN)) continue; return false; }
+        if (got <= 0) {
+            if (got < 0 && (errno == EINTR || errno == EAGAIN)) continue;
+            if (got == 0 && n == wanted && ended_cleanly != nullptr) *ended_cleanly = true;
+            return false;
+        }
         p += got; n -= (uint64_t)got;
     }
     return true;
@@ -141,10 +154,37 @@ void sender_loop(Worker* w, Conn* c) {
     }
 }
 
+// The member at the other end of `c` closed it between two messages.  What it sent before is
+// still here and can be received; when its last connection has ended, receives that wait for
+// more from it fail, and so does everything posted towards it later.  Called with w->mu held.
+void member_left(Worker* w, Conn* c) {
+    if (--w->open_conns[c->peer] > 0) return;
+    const std::string why = "member " + std::to_string(c->peer) + " closed its connections";
+    if (w->error.empty()) w->error = why;
+    for (auto it = w->posted.begin(); it != w->posted.end();) {
+        if (it->first.first == c->peer) {
+            auto op = w->ops.find(it->second);
+            if (op != w->ops.end() && op->second.state == 0) op->second.state = 2;
+            it = w->posted.erase(it);
+        } else ++it;
+    }
+    for (auto& entry : w->ops)
+        if (entry.second.sending && entry.second.peer == c->peer && entry.second.state == 0) entry.second.state = 2;
+    w->done.notify_all();
+}
+
 void receiver_loop(Worker* w, Conn* c) {
     for (;;) {
         Header h{};
-        if (!read_all(c->fd, reinterpret_cast<char*>(&h), sizeof(h), w->stopping)) break;
+        bool ended_cleanly = false;
+        if (!read_all(c->fd, reinterpret_cast<char*>(&h), sizeof(h), w->stopping, &ended_cleanly)) {
+            if (ended_cleanly && !w->stopping.load()) {
+                std::lock_guard<std::mutex> lock(w->mu);
+                member_left(w, c);
+                return;
+            }
+            break;
+        }
         long id = 0;
         char* target = nullptr;
         {
@@ -199,6 +239,8 @@ void stop_threads(Worker* w) {
     w->stopping.store(true);
     {
         std::lock_guard<std::mutex> lock(w->mu);
+        w->broken = true;                              // nothing can be posted on a stopped worker
+        if (w->error.empty()) w->error = "the worker was stopped";
         for (auto& c : w->conns) {
             if (c->fd >= 0) ::shutdown(c->fd, SHUT_RDWR);
             c->wake.notify_all();
@@ -246,7 +288,7 @@ void* gb_tcp_create(int index, int members, int streams, const char* host) {
     w->index = index; w->members = members; w->streams = streams < 1 ? 1 : streams;
     if (host != nullptr && host[0] != 0) w->host = host;
     w->by_peer.resize(members);
-    w->round_robin.assign(members, 0);
+    w->open_conns.assign(members, 0);
     w->listener = ::socket(AF_INET, SOCK_STREAM, 0);
     if (w->listener < 0) { set_error(nullptr, "socket() failed"); return nullptr; }
     int one = 1;
@@ -336,6 +378,8 @@ int gb_tcp_connect(void* handle, const char** addresses, double timeout_s) {
         w->conns.push_back(std::move(c));
         --expected;
     }
+    w->open_conns.assign(w->members, 0);
+    for (auto& c : w->conns) ++w->open_conns[c->peer];
     for (auto& c : w->conns) {
         Conn* raw = c.get();
         raw->sender = std::thread(sender_loop, w, raw);
@@ -347,7 +391,7 @@ int gb_tcp_connect(void* handle, const char** addresses, double timeout_s) {
 long gb_tcp_send(void* handle, int peer, const void* data, uint64_t length, uint64_t tag) {
     Worker* w = static_cast<Worker*>(handle);
     std::lock_guard<std::mutex> lock(w->mu);
-    if (w->broken || peer < 0 || peer >= w->members || w->by_peer[peer].empty()) {
+    if (w->broken || peer < 0 || peer >= w->members || w->by_peer[peer].empty() || w->gone(peer)) {
         set_error(w, "send: the worker is broken or has no connection to that member");
         return -1;
     }
@@ -357,7 +401,7 @@ long gb_tcp_send(void* handle, int peer, const void* data, uint64_t length, uint
     op.data = const_cast<char*>(static_cast<const char*>(data)); op.length = length;
     w->ops[id] = op;
     auto& list = w->by_peer[peer];
-    Conn* c = w->conns[list[w->round_robin[peer]++ % list.size()]].get();
+    Conn* c = w->conns[list[(size_t)((tag ^ (tag >> 28)) % list.size())]].get();
     c->queue.push_back(id);
     c->wake.notify_one();
     return id;
@@ -380,6 +424,9 @@ long gb_tcp_recv(void* handle, int peer, void* data, uint64_t length, uint64_t t
         else { op.state = 2; w->error = "length mismatch on a buffered message"; }
         found->second.pop_front();
         if (found->second.empty()) w->early.erase(found);
+    } else if (w->gone(peer)) {
+        set_error(w, "recv: member " + std::to_string(peer) + " closed its connections and sent nothing more");
+        return -1;
     } else {
         w->posted[{peer, tag}] = id;
     }

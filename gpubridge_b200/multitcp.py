@@ -88,25 +88,31 @@ class Worker:
 
     def address(self) -> str:
         buf = ctypes.create_string_buffer(128)
-        self.lib.gb_tcp_address(self.handle, buf, 128)
+        self.lib.gb_tcp_address(self._live(), buf, 128)
         return buf.value.decode()
 
     def connect(self, addresses: list[str], timeout_s: float) -> None:
         array = (ctypes.c_char_p * len(addresses))(*[a.encode() for a in addresses])
-        if self.lib.gb_tcp_connect(self.handle, array, timeout_s) != 0:
+        if self.lib.gb_tcp_connect(self._live(), array, timeout_s) != 0:
             raise RuntimeError(f"multitcp: {self._error()}")
 
     def _error(self) -> str:
         return self.lib.gb_tcp_last_error(self.handle).decode()
 
+    def _live(self) -> int:
+        """The native handle; a closed worker refuses calls instead of handing the library nothing."""
+        if not self.handle:
+            raise RuntimeError("multitcp: the worker is closed")
+        return self.handle
+
     def send(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
-        op = self.lib.gb_tcp_send(self.handle, peer, ptr, nbytes, tag)
+        op = self.lib.gb_tcp_send(self._live(), peer, ptr, nbytes, tag)
         if op < 0:
             raise RuntimeError(f"multitcp: {self._error()}")
         return op
 
     def recv(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
-        op = self.lib.gb_tcp_recv(self.handle, peer, ptr, nbytes, tag)
+        op = self.lib.gb_tcp_recv(self._live(), peer, ptr, nbytes, tag)
         if op < 0:
             raise RuntimeError(f"multitcp: {self._error()}")
         return op
@@ -114,7 +120,7 @@ class Worker:
     def wait(self, ids: list[int], deadline: float) -> None:
         array = (ctypes.c_long * len(ids))(*ids)
         left = max(0.001, deadline - time.monotonic())
-        if self.lib.gb_tcp_wait(self.handle, array, len(ids), left) != 0:
+        if self.lib.gb_tcp_wait(self._live(), array, len(ids), left) != 0:
             raise RuntimeError(f"multitcp: {self._error()}")
 
     # The collectives themselves run inside the library (csrc/gb_tcp.cpp): chunked, pipelined,
@@ -122,13 +128,13 @@ class Worker:
     def all_reduce(self, ptr: int, count: int, dtype: int, op: int, chunk_elems: int, seq: int,
                    deadline: float) -> None:
         left = max(0.001, deadline - time.monotonic())
-        if self.lib.gb_tcp_all_reduce(self.handle, ptr, count, dtype, op, chunk_elems, seq, left) != 0:
+        if self.lib.gb_tcp_all_reduce(self._live(), ptr, count, dtype, op, chunk_elems, seq, left) != 0:
             raise RuntimeError(f"multitcp: {self._error()}")
 
     def broadcast(self, ptr: int, nbytes: int, root: int, chunk_bytes: int, seq: int,
                   deadline: float) -> None:
         left = max(0.001, deadline - time.monotonic())
-        if self.lib.gb_tcp_broadcast(self.handle, ptr, nbytes, root, chunk_bytes, seq, left) != 0:
+        if self.lib.gb_tcp_broadcast(self._live(), ptr, nbytes, root, chunk_bytes, seq, left) != 0:
             raise RuntimeError(f"multitcp: {self._error()}")
 
     def abort(self) -> None:
@@ -154,7 +160,8 @@ class MultiTcpTransport(TaggedBridge):
         try:
             store.set(f"{key}/address/{rank}", worker.address())
             addresses = wait_for_keys(store, [f"{key}/address/{m}" for m in members], deadline,
-                                      "every bridge member's multitcp address")
+                                      "every bridge member's multitcp address",
+                                      verdicts=[f"{key}/status/{m}" for m in members if m != rank])
             worker.connect(addresses, max(0.1, deadline - time.monotonic()))
             return cls(worker, members, rank, timeout, chunk)
         except BaseException:
