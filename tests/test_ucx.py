@@ -642,3 +642,22 @@ def test_the_workers_source_is_not_part_of_the_packages_own_library():
         with open(path) as fh:
             text = fh.read()
         assert "#include <ucp/" not in text and "#include <infiniband/" not in text, path
+
+
+def _three_leaders(rank, topology):
+    import gpubridge_b200 as gb
+    assert len(topology.layout.islands) == 3 and topology.peers[rank].bridge == "ucx"
+    for n, dtype in ((300_001, torch.float32), (7, torch.int64), (50_000, torch.bfloat16)):
+        t = rank_tensor(rank, n, dtype)
+        gb.all_reduce(t)
+        assert torch.equal(t, expected_sum(3, n, dtype)), (n, dtype)
+    t = rank_tensor(rank, 999)
+    gb.broadcast(t, 2)
+    assert torch.equal(t, rank_tensor(2, 999))
+    return topology.bridge.describe()["endpoint"]["sends"]
+
+
+def test_three_leaders_run_the_workers_ring_between_processes(fake_ucx, tmp_path):
+    sends = run_ranks(("nvidia",) * 3, _three_leaders, tmp_path, init={"bridge": "ucx"}, timeout=120,
+                      env=dict(fake_ucx, GPUBRIDGE_ISLANDS="1,1,1", GPUBRIDGE_UCX_CHUNK_BYTES="64K"))
+    assert all(count > 10 for count in sends)                      # a ring in chunks, on every leader
