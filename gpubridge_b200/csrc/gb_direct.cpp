@@ -148,7 +148,11 @@ struct DriverGpu final : GpuMemory {
         pointer_attr = reinterpret_cast<PointerAttr>(dlsym(lib, "cuPointerGetAttribute"));
         device_attr = reinterpret_cast<DeviceAttr>(dlsym(lib, "cuDeviceGetAttribute"));
         handle_for_range = reinterpret_cast<HandleForRange>(dlsym(lib, "cuMemGetHandleForAddressRange"));
-        if (pointer_attr == nullptr || device_attr == nullptr) problem = "the driver lacks the pointer attribute calls";
+        if (pointer_attr == nullptr || device_attr == nullptr) { problem = "the driver lacks the pointer attribute calls"; return; }
+        typedef int (*Init)(unsigned);
+        Init init = reinterpret_cast<Init>(dlsym(lib, "cuInit"));
+        const int rc = init != nullptr ? init(0) : -1;            // attribute queries need an initialised driver
+        if (rc != 0) problem = "the CUDA driver did not initialise (cuInit: code " + std::to_string(rc) + ")";
     }
     ~DriverGpu() override { if (lib != nullptr) dlclose(lib); }
     bool ready(std::string* why) { if (!problem.empty()) { *why = problem; return false; } return true; }

@@ -238,6 +238,19 @@ def load(name: str) -> None:
         "bridge='multitcp' or 'gloo'")
 
 
+def _device_registration() -> str:
+    """What the registrar of device memory finds on this machine (device 0), in its own words."""
+    try:
+        from gpubridge_b200.rdma_direct import Registrar
+        registrar = Registrar.on_this_machine()
+        try:
+            return registrar.capabilities(0)
+        finally:
+            registrar.close()
+    except Exception as failure:  # noqa: BLE001 - informational
+        return f"unknown ({type(failure).__name__}: {failure})"
+
+
 def info() -> dict:
     """What this build has of the verbs bridge (``python -m gpubridge_b200.rdma info``)."""
     import ctypes.util
@@ -245,7 +258,7 @@ def info() -> dict:
     return {"protocol": protocol_version(), "provider": "libibverbs" if provider_available() else None,
             "libibverbs_found": ctypes.util.find_library("ibverbs") is not None,
             "verbs_header": os.path.exists("/usr/include/infiniband/verbs.h"),
-            "in_process_fabric": True,
+            "in_process_fabric": True, "device_registration": _device_registration(),
             "defaults": {"eager_max": 16 << 10, "data_slots": 16, "ctrl_slots": 8, "max_write": 1 << 20,
                          "unexpected_max": 64 << 20, "mr_cache": 64}}
 

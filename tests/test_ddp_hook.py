@@ -60,11 +60,10 @@ def _train(rank, topology, cap_mb):
     return len(buckets), sum(n for _, _, n in buckets)
 
 
-@pytest.mark.parametrize("layout", ["2+2", "interleaved", "3+1", "single-vendor"])
-@pytest.mark.parametrize("policy", ["auto", "pipelined-reduce-bridge-broadcast", "sharded-bridge", "flat-gloo"])
+@pytest.mark.parametrize("layout, policy", [
+    ("2+2", "auto"), ("interleaved", "pipelined-reduce-bridge-broadcast"), ("3+1", "sharded-bridge"),
+    ("2+2", "sharded-bridge"), ("3+1", "flat-gloo"), ("single-vendor", "auto")])
 def test_ddp_with_the_hook_averages_gradients_exactly(tmp_path, layout, policy):
-    if layout == "single-vendor" and policy not in ("auto", "flat-gloo"):
-        pytest.skip("a bridged policy does not apply to one island")
     out = run_ranks(LAYOUTS[layout], _train, tmp_path, 25, init={"policy": policy}, timeout=120)
     parameter_bytes = sum(p.numel() for p in _net().parameters()) * 8
     assert all(total == 2 * parameter_bytes for _, total in out)   # every gradient went through once per step
