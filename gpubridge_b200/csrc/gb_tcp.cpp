@@ -76,6 +76,7 @@ struct Worker {
     std::map<std::pair<int, uint64_t>, std::deque<std::vector<char>>> early;   // unexpected messages
     std::vector<int> open_conns;                   // per peer: connections that have not ended
     std::atomic<bool> stopping{false};
+    std::mutex stop_mu;                            // one thread at a time stops (and joins) the others
     bool broken = false;
     std::string error;
     bool gone(int peer) const { return !by_peer[peer].empty() && open_conns[peer] == 0; }
@@ -236,6 +237,9 @@ void receiver_loop(Worker* w, Conn* c) {
 }
 
 void stop_threads(Worker* w) {
+    // A failed wait stops the worker, and so may an abort or a close from another thread at the
+    // same moment: the second one waits here and then finds nothing left to join.
+    std::lock_guard<std::mutex> one_at_a_time(w->stop_mu);
     w->stopping.store(true);
     {
         std::lock_guard<std::mutex> lock(w->mu);

@@ -18,7 +18,7 @@ import sys
 import time
 
 from gpubridge_b200 import config as _config
-from gpubridge_b200.tagged import TaggedBridge, wait_for_keys
+from gpubridge_b200.tagged import Guarded, TaggedBridge, wait_for_keys
 from gpubridge_b200.transport import register_transport
 
 STREAMS_ENV = "GPUBRIDGE_MULTITCP_STREAMS"
@@ -77,74 +77,80 @@ def streams_setting() -> int:
     return value
 
 
-class Worker:
-    """One member's native worker."""
+class Worker(Guarded):
+    """One member's native worker.  Calls from several threads are counted, so that ``close``
+    frees the worker only after every one of them has left the library."""
+
+    _what = "multitcp"
 
     def __init__(self, index: int, members: int, streams: int, host: str) -> None:
+        self._guard()
         self.lib = _library()
         self.handle = self.lib.gb_tcp_create(index, members, streams, host.encode())
         if not self.handle:
             raise RuntimeError(f"multitcp: {self.lib.gb_tcp_last_error(None).decode()}")
 
+    def _fail(self, handle: int):
+        raise RuntimeError(f"multitcp: {self.lib.gb_tcp_last_error(handle).decode()}")
+
     def address(self) -> str:
         buf = ctypes.create_string_buffer(128)
-        self.lib.gb_tcp_address(self._live(), buf, 128)
+        with self._inside() as handle:
+            self.lib.gb_tcp_address(handle, buf, 128)
         return buf.value.decode()
 
     def connect(self, addresses: list[str], timeout_s: float) -> None:
         array = (ctypes.c_char_p * len(addresses))(*[a.encode() for a in addresses])
-        if self.lib.gb_tcp_connect(self._live(), array, timeout_s) != 0:
-            raise RuntimeError(f"multitcp: {self._error()}")
-
-    def _error(self) -> str:
-        return self.lib.gb_tcp_last_error(self.handle).decode()
-
-    def _live(self) -> int:
-        """The native handle; a closed worker refuses calls instead of handing the library nothing."""
-        if not self.handle:
-            raise RuntimeError("multitcp: the worker is closed")
-        return self.handle
+        with self._inside() as handle:
+            if self.lib.gb_tcp_connect(handle, array, timeout_s) != 0:
+                self._fail(handle)
 
     def send(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
-        op = self.lib.gb_tcp_send(self._live(), peer, ptr, nbytes, tag)
-        if op < 0:
-            raise RuntimeError(f"multitcp: {self._error()}")
-        return op
+        with self._inside() as handle:
+            op = self.lib.gb_tcp_send(handle, peer, ptr, nbytes, tag)
+            if op < 0:
+                self._fail(handle)
+            return op
 
     def recv(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
-        op = self.lib.gb_tcp_recv(self._live(), peer, ptr, nbytes, tag)
-        if op < 0:
-            raise RuntimeError(f"multitcp: {self._error()}")
-        return op
+        with self._inside() as handle:
+            op = self.lib.gb_tcp_recv(handle, peer, ptr, nbytes, tag)
+            if op < 0:
+                self._fail(handle)
+            return op
 
     def wait(self, ids: list[int], deadline: float) -> None:
         array = (ctypes.c_long * len(ids))(*ids)
         left = max(0.001, deadline - time.monotonic())
-        if self.lib.gb_tcp_wait(self._live(), array, len(ids), left) != 0:
-            raise RuntimeError(f"multitcp: {self._error()}")
+        with self._inside() as handle:
+            if self.lib.gb_tcp_wait(handle, array, len(ids), left) != 0:
+                self._fail(handle)
 
     # The collectives themselves run inside the library (csrc/gb_tcp.cpp): chunked, pipelined,
     # in the reduction order tagged.py documents, without a Python round trip per chunk.
     def all_reduce(self, ptr: int, count: int, dtype: int, op: int, chunk_elems: int, seq: int,
                    deadline: float) -> None:
         left = max(0.001, deadline - time.monotonic())
-        if self.lib.gb_tcp_all_reduce(self._live(), ptr, count, dtype, op, chunk_elems, seq, left) != 0:
-            raise RuntimeError(f"multitcp: {self._error()}")
+        with self._inside() as handle:
+            if self.lib.gb_tcp_all_reduce(handle, ptr, count, dtype, op, chunk_elems, seq, left) != 0:
+                self._fail(handle)
 
     def broadcast(self, ptr: int, nbytes: int, root: int, chunk_bytes: int, seq: int,
                   deadline: float) -> None:
         left = max(0.001, deadline - time.monotonic())
-        if self.lib.gb_tcp_broadcast(self._live(), ptr, nbytes, root, chunk_bytes, seq, left) != 0:
-            raise RuntimeError(f"multitcp: {self._error()}")
+        with self._inside() as handle:
+            if self.lib.gb_tcp_broadcast(handle, ptr, nbytes, root, chunk_bytes, seq, left) != 0:
+                self._fail(handle)
 
     def abort(self) -> None:
-        if self.handle:
-            self.lib.gb_tcp_abort(self.handle)
+        try:
+            with self._inside() as handle:
+                self.lib.gb_tcp_abort(handle)
+        except RuntimeError:
+            pass                                           # closed already
 
     def close(self) -> None:
-        handle, self.handle = self.handle, None
-        if handle:
-            self.lib.gb_tcp_close(handle)
+        self._retire(self.lib.gb_tcp_abort, self.lib.gb_tcp_close)
 
 
 @register_transport

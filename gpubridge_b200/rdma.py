@@ -75,6 +75,9 @@ def protocol_version() -> int:
     return _library().gb_rdma_protocol()
 
 
+from gpubridge_b200.tagged import Guarded as _Guarded  # noqa: E402
+
+
 class MockFabric:
     """``members`` connected members inside this process."""
 
@@ -107,13 +110,14 @@ class MockFabric:
             self.lib.gb_rdma_mock_free(handle)
 
 
-class Endpoint:
+class Endpoint(_Guarded):
     """One member's endpoint; the worker interface :class:`~gpubridge_b200.tagged.TaggedBridge`
     expects (``all_reduce`` / ``broadcast`` / ``abort`` / ``close``) plus send / recv / wait."""
 
     def __init__(self, fabric: "MockFabric | None", index: int, *, eager_max: int = 0, data_slots: int = 0,
                  ctrl_slots: int = 0, max_write: int = 0, unexpected_max: int = 0, mr_cache: int = 0,
                  _handle: int | None = None) -> None:
+        self._guard()
         if _handle is not None:                           # an endpoint made elsewhere (over_sockets)
             self.lib, self.index, self.handle = _library(), index, _handle
             return
@@ -155,53 +159,74 @@ class Endpoint:
                                        unexpected_max, mr_cache)
         return cls(None, index, _handle=handle)
 
-    def _error(self) -> str:
-        return self.lib.gb_rdma_last_error(self.handle).decode()
+    _what = "rdma endpoint"
+
+    def _error(self, handle: int) -> str:
+        return self.lib.gb_rdma_last_error(handle).decode()
+
+    def last_error(self) -> str:
+        """Why the endpoint broke (empty while it has not)."""
+        with self._inside() as handle:
+            return self._error(handle)
 
     def send(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
-        op = self.lib.gb_rdma_send(self.handle, peer, ptr, nbytes, tag)
-        if op < 0:
-            raise RuntimeError(f"rdma endpoint: {self._error() or 'no such peer'}")
-        return op
+        with self._inside() as handle:
+            op = self.lib.gb_rdma_send(handle, peer, ptr, nbytes, tag)
+            if op < 0:
+                raise RuntimeError(f"rdma endpoint: {self._error(handle) or 'no such peer'}")
+            return op
 
     def recv(self, peer: int, ptr: int, nbytes: int, tag: int) -> int:
-        op = self.lib.gb_rdma_recv(self.handle, peer, ptr, nbytes, tag)
-        if op < 0:
-            raise RuntimeError(f"rdma endpoint: {self._error() or 'no such peer'}")
-        return op
+        with self._inside() as handle:
+            op = self.lib.gb_rdma_recv(handle, peer, ptr, nbytes, tag)
+            if op < 0:
+                raise RuntimeError(f"rdma endpoint: {self._error(handle) or 'no such peer'}")
+            return op
 
     def wait(self, ids: list[int], deadline: float) -> None:
         array = (ctypes.c_long * len(ids))(*ids)
-        if self.lib.gb_rdma_wait(self.handle, array, len(ids), max(0.001, deadline - time.monotonic())) != 0:
-            raise RuntimeError(f"rdma endpoint: {self._error()}")
+        with self._inside() as handle:
+            if self.lib.gb_rdma_wait(handle, array, len(ids), max(0.001, deadline - time.monotonic())) != 0:
+                raise RuntimeError(f"rdma endpoint: {self._error(handle)}")
 
     def all_reduce(self, ptr: int, count: int, dtype: int, op: int, chunk_elems: int, seq: int,
                    deadline: float) -> None:
         left = max(0.001, deadline - time.monotonic())
-        if self.lib.gb_rdma_all_reduce(self.handle, ptr, count, dtype, op, chunk_elems, seq, left) != 0:
-            raise RuntimeError(f"rdma endpoint: {self._error()}")
+        with self._inside() as handle:
+            if self.lib.gb_rdma_all_reduce(handle, ptr, count, dtype, op, chunk_elems, seq, left) != 0:
+                raise RuntimeError(f"rdma endpoint: {self._error(handle)}")
 
     def broadcast(self, ptr: int, nbytes: int, root: int, chunk_bytes: int, seq: int, deadline: float) -> None:
         left = max(0.001, deadline - time.monotonic())
-        if self.lib.gb_rdma_broadcast(self.handle, ptr, nbytes, root, chunk_bytes, seq, left) != 0:
-            raise RuntimeError(f"rdma endpoint: {self._error()}")
+        with self._inside() as handle:
+            if self.lib.gb_rdma_broadcast(handle, ptr, nbytes, root, chunk_bytes, seq, left) != 0:
+                raise RuntimeError(f"rdma endpoint: {self._error(handle)}")
 
     def invalidate(self, ptr: int, nbytes: int) -> int:
         """Forget cached registrations overlapping the range (call before freeing memory that
-        large messages were received into); returns how many were dropped."""
-        return self.lib.gb_rdma_invalidate(self.handle, ptr, nbytes)
+        large messages were received into); returns how many were dropped.  Nothing to forget
+        on an endpoint that is closed already."""
+        try:
+            with self._inside() as handle:
+                return self.lib.gb_rdma_invalidate(handle, ptr, nbytes)
+        except RuntimeError:
+            return 0
 
     def telemetry(self) -> dict:
-        return json.loads(self.lib.gb_rdma_telemetry(self.handle).decode())
+        with self._inside() as handle:
+            return json.loads(self.lib.gb_rdma_telemetry(handle).decode())
 
     def abort(self) -> None:
-        if self.handle:
-            self.lib.gb_rdma_abort(self.handle)
+        try:
+            with self._inside() as handle:
+                self.lib.gb_rdma_abort(handle)
+        except RuntimeError:
+            pass                                           # closed already: nothing left to stop
 
     def close(self) -> None:
-        handle, self.handle = self.handle, None
-        if handle:
-            self.lib.gb_rdma_close(handle)
+        """Leave in good order - unless other threads are still inside calls: those are ended
+        first (their waits return with an error) and the endpoint is freed once they have left."""
+        self._retire(self.lib.gb_rdma_abort, self.lib.gb_rdma_close)
 
 
 PROVIDER_ENV = "GPUBRIDGE_VERBS_PROVIDER"

@@ -56,6 +56,55 @@ def ring_order(segment: int, members: int) -> list[int]:
     return [(segment + hop) % members for hop in range(members)]
 
 
+class Guarded:
+    """Lifetime of a native worker's handle when several threads use it.
+
+    Every call into the library goes through :meth:`_inside`, which counts the calls that are
+    in there; :meth:`_retire` (from ``close``) refuses new calls, asks the library to end the
+    ones inside (``stop``: the native abort, after which their waits return with an error),
+    waits - for a bounded time - until they have left, and only then hands the handle to
+    ``free``.  A call on a closed worker raises instead of handing the library nothing.
+    """
+
+    _what = "worker"
+
+    def _guard(self) -> None:
+        import threading
+        self._gate = threading.Condition()
+        self._calls_inside = 0
+        self._closing = False
+
+    @contextlib.contextmanager
+    def _inside(self):
+        with self._gate:
+            if self._closing or not getattr(self, "handle", None):
+                raise RuntimeError(f"{self._what}: the worker is closed")
+            self._calls_inside += 1
+        try:
+            yield self.handle
+        finally:
+            with self._gate:
+                self._calls_inside -= 1
+                self._gate.notify_all()
+
+    def _retire(self, stop, free, limit: float = 10.0) -> bool:
+        """True when the handle was freed now; False when it was closed before or calls were
+        still inside at the limit (the handle is then leaked rather than freed under them)."""
+        with self._gate:
+            if self._closing or not getattr(self, "handle", None):
+                return False
+            self._closing = True
+            handle = self.handle
+            if self._calls_inside:
+                stop(handle)
+                if not self._gate.wait_for(lambda: self._calls_inside == 0, limit):
+                    self.handle = None
+                    return False
+            self.handle = None
+        free(handle)
+        return True
+
+
 def message_tag(number: int, step: int, sender: int, chunk: int) -> int:
     """The 64-bit tag of one message, as the native collectives number them: call (24 bits),
     step (12), sending member (8), chunk (20)."""

@@ -18,6 +18,7 @@ bridge uses where the reduction has to run on a device.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import hashlib
 import logging
@@ -31,6 +32,8 @@ import threading
 import time
 from collections.abc import Sequence
 from pathlib import Path
+
+from gpubridge_b200.tagged import Guarded
 
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
 SOURCES = (Path(__file__).resolve().parent / "gb_ucx.cpp", CSRC / "gb_tagged.cpp")
@@ -204,11 +207,16 @@ def info() -> dict:
 
 
 # ---- the worker -------------------------------------------------------------------------------------
-class Worker:
+class Worker(Guarded):
     """One UCP context and worker with an endpoint per other member.  Calls are serialised
-    inside the library; the object is the ``worker`` of a :class:`~gpubridge_b200.tagged.TaggedBridge`."""
+    inside the library and counted here, so that ``close`` frees the worker only after every
+    thread has left it; the object is the ``worker`` of a
+    :class:`~gpubridge_b200.tagged.TaggedBridge`."""
+
+    _what = "UCX"
 
     def __init__(self, members: int, index: int) -> None:
+        self._guard()
         self.lib = load()
         self.members, self.index = members, index
         text = ctypes.create_string_buffer(512)
@@ -219,92 +227,116 @@ class Worker:
                 "cannot really be used (common on cloud machines), name the ones to use with "
                 "UCX_TLS (tcp,self; rc,self on InfiniBand) or UCX_NET_DEVICES")
 
+    @contextlib.contextmanager
+    def _inside(self):
+        try:
+            with super()._inside() as handle:
+                yield handle
+        except RuntimeError as failure:
+            if isinstance(failure, UcxError) or "is closed" not in str(failure):
+                raise
+            raise UcxError("the UCX worker is closed") from None
+
     # -- errors
-    def last_error(self) -> str:
+    def _text(self, handle: int) -> str:
         text = ctypes.create_string_buffer(1024)
-        self.lib.gb_ucx_last_error(self._live(), text, len(text))
+        self.lib.gb_ucx_last_error(handle, text, len(text))
         return text.value.decode(errors="replace")
 
-    def _live(self) -> int:
-        if not self.handle:
-            raise UcxError("the UCX worker is closed")
-        return self.handle
+    def last_error(self) -> str:
+        with self._inside() as handle:
+            return self._text(handle)
 
-    def _check(self, code: int) -> int:
+    def _check(self, handle: int, code: int) -> int:
         if code < 0:
             kind = {TIMED_OUT: "timed out", PEER_FAILED: "lost a peer"}.get(code, "failed")
-            raise UcxError(f"UCX {kind}: {self.last_error()}", code)
+            raise UcxError(f"UCX {kind}: {self._text(handle)}", code)
         return code
 
     # -- set-up
     def memory_types(self) -> set[str]:
         bits = ctypes.c_ulonglong()
-        self._check(self.lib.gb_ucx_memory_types(self._live(), ctypes.byref(bits)))
+        with self._inside() as handle:
+            self._check(handle, self.lib.gb_ucx_memory_types(handle, ctypes.byref(bits)))
         return {name for name, bit in (("host", 1), ("cuda", 2)) if bits.value & bit}
 
     def address(self) -> bytes:
         room = 1024
         while True:
             buffer, length = ctypes.create_string_buffer(room), ctypes.c_size_t()
-            code = self._check(self.lib.gb_ucx_address(self._live(), buffer, room, ctypes.byref(length)))
+            with self._inside() as handle:
+                code = self._check(handle, self.lib.gb_ucx_address(handle, buffer, room, ctypes.byref(length)))
             if code == 0:
                 return buffer.raw[:length.value]
             room = length.value
 
     def connect(self, member: int, address: bytes) -> None:
-        self._check(self.lib.gb_ucx_connect(self._live(), member, address))
+        with self._inside() as handle:
+            self._check(handle, self.lib.gb_ucx_connect(handle, member, address))
 
     # -- single messages
     def memory(self, kind: int) -> None:
         """Memory type of the buffers of the posts that follow (:data:`HOST`, :data:`CUDA`)."""
-        self.lib.gb_ucx_set_memory(self._live(), kind)
+        with self._inside() as handle:
+            self.lib.gb_ucx_set_memory(handle, kind)
 
     def send(self, member: int, pointer: int, nbytes: int, tag: int) -> int:
-        return self._check(self.lib.gb_ucx_send(self._live(), member, pointer, nbytes, tag))
+        with self._inside() as handle:
+            return self._check(handle, self.lib.gb_ucx_send(handle, member, pointer, nbytes, tag))
 
     def recv(self, member: int, pointer: int, nbytes: int, tag: int) -> int:
         """``member`` is for the reader: a UCX receive names no peer, the tag says whose message it is."""
-        return self._check(self.lib.gb_ucx_recv(self._live(), pointer, nbytes, tag))
+        with self._inside() as handle:
+            return self._check(handle, self.lib.gb_ucx_recv(handle, pointer, nbytes, tag))
 
     def wait(self, ids: Sequence[int], deadline: float) -> None:
         if ids:
             array = (ctypes.c_longlong * len(ids))(*ids)
-            self._check(self.lib.gb_ucx_wait(self._live(), array, len(ids),
-                                             max(0.0, deadline - time.monotonic())))
+            with self._inside() as handle:
+                self._check(handle, self.lib.gb_ucx_wait(handle, array, len(ids),
+                                                         max(0.0, deadline - time.monotonic())))
 
     def poll(self, ids: Sequence[int]) -> bool:
         """Progress a little without waiting; True once every operation of ``ids`` is complete."""
         if not ids:
             return True
         array = (ctypes.c_longlong * len(ids))(*ids)
-        return self._check(self.lib.gb_ucx_poll(self._live(), array, len(ids))) == 0
+        with self._inside() as handle:
+            return self._check(handle, self.lib.gb_ucx_poll(handle, array, len(ids))) == 0
 
     # -- the interface of a tagged bridge's worker
     def all_reduce(self, pointer: int, count: int, dtype: int, op: int, chunk_elems: int, number: int,
                    deadline: float) -> None:
-        self._check(self.lib.gb_ucx_all_reduce(self._live(), pointer, count, dtype, op, chunk_elems, number,
-                                               max(0.0, deadline - time.monotonic())))
+        with self._inside() as handle:
+            self._check(handle, self.lib.gb_ucx_all_reduce(handle, pointer, count, dtype, op, chunk_elems, number,
+                                                           max(0.0, deadline - time.monotonic())))
 
     def broadcast(self, pointer: int, nbytes: int, root: int, chunk_bytes: int, number: int,
                   deadline: float) -> None:
-        self._check(self.lib.gb_ucx_broadcast(self._live(), pointer, nbytes, root, chunk_bytes, number,
-                                              max(0.0, deadline - time.monotonic())))
+        with self._inside() as handle:
+            self._check(handle, self.lib.gb_ucx_broadcast(handle, pointer, nbytes, root, chunk_bytes, number,
+                                                          max(0.0, deadline - time.monotonic())))
 
     def abort(self) -> None:
-        if self.handle:
-            self.lib.gb_ucx_abort(self.handle)
+        try:
+            with self._inside() as handle:
+                self.lib.gb_ucx_abort(handle)
+        except UcxError:
+            pass                                           # closed already
 
     def invalidate(self, pointer: int, nbytes: int) -> None:
         """UCX keeps its own registration cache; a staging buffer needs no word from us."""
 
     def telemetry(self) -> dict:
         seven = (ctypes.c_ulonglong * 7)()
-        self.lib.gb_ucx_counters(self._live(), seven)
+        with self._inside() as handle:
+            self.lib.gb_ucx_counters(handle, seven)
         names = ("sends", "receives", "bytes_out", "bytes_in", "progress_calls", "open_operations", "broken")
         return dict(zip(names, (int(v) for v in seven)))
 
     def close(self, limit: float = 10.0) -> None:
-        handle, self.handle = self.handle, None
-        if handle and self.lib.gb_ucx_close(handle, limit) != 0:
-            log.warning("gpubridge_b200: UCX endpoints were still flushing after %g s; the worker was "
-                        "torn down anyway", limit)
+        def free(handle: int) -> None:
+            if self.lib.gb_ucx_close(handle, limit) != 0:
+                log.warning("gpubridge_b200: UCX endpoints were still flushing after %g s; the worker was "
+                            "torn down anyway", limit)
+        self._retire(self.lib.gb_ucx_abort, free)

@@ -19,6 +19,8 @@
 //  * After a timeout, a peer failure or stop() the worker is broken: outstanding operations are
 //    cancelled and progressed until UCX has let go of the caller's buffers (bounded), and every
 //    later call fails with the first reason.
+//  * abort() may come from another thread while one is inside wait(): a flag read without the
+//    mutex ends that wait, then the worker is stopped.
 //  * close() closes the endpoints with a flush first and by force when that takes longer than
 //    the limit; it never blocks past the limit.
 // (Role of the reference's src/gpubridge/ucx/bridge.cpp, whose collectives run in Python.)
@@ -26,6 +28,7 @@
 
 #include <sched.h>
 
+#include <atomic>
 #include <chrono>
 #include <cstdint>
 #include <cstdio>
@@ -77,6 +80,7 @@ struct UcxWorker final : GbTaggedWorker {
     int broken_code = 0;
     std::string reason;
     std::mutex gate;
+    std::atomic<bool> asked_to_stop{false};    // set without the gate, so that it reaches a thread inside wait()
     unsigned long long sends = 0, receives = 0, bytes_out = 0, bytes_in = 0, progress_calls = 0;
 
     int members() const override { return count; }
@@ -233,6 +237,11 @@ struct UcxWorker final : GbTaggedWorker {
             const int rc = sweep(ids, n, &open);
             if (rc != 0) return rc;
             if (!open) return 0;
+            if (asked_to_stop.load()) {
+                wreck(GB_UCX_FAILED, "stopped from another thread while operations were outstanding");
+                let_go(2.0);
+                return broken_code;
+            }
             if (seconds_now() > until) {
                 wreck(GB_UCX_TIMED_OUT, "operations were still outstanding at the deadline "
                       "(a member that never joined, or a slower link than the timeout allows)");
@@ -445,8 +454,11 @@ int gb_ucx_broadcast(void* handle, void* data, unsigned long long nbytes, int ro
     return rc == 0 ? 0 : (w->broken ? w->broken_code : GB_UCX_FAILED);
 }
 
+// May be called while another thread is inside a wait: the flag ends that wait, which frees
+// the gate for the rest.
 void gb_ucx_abort(void* handle) {
     auto* w = static_cast<UcxWorker*>(handle);
+    w->asked_to_stop.store(true);
     std::lock_guard<std::mutex> hold(w->gate);
     w->stop();
 }

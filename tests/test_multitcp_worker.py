@@ -237,3 +237,30 @@ def test_one_leaders_trouble_fails_init_on_every_rank(tmp_path, what, envs, mess
     errors = run_ranks(LAYOUTS["2+2"], per_rank, tmp_path, envs, {"bridge": "multitcp"}, mode="plain",
                        expect_error=message, timeout=90)
     assert len(errors) == 4 and all("could not be set up" in e for e in errors)
+
+
+def test_close_from_another_thread_ends_a_blocked_wait_before_the_worker_is_freed():
+    a, b = connected(2)
+    room = torch.zeros(64)
+    seen = {}
+
+    def waits():
+        try:
+            a.wait([a.recv(1, room.data_ptr(), room.nbytes, 3)], soon(30))
+            seen["wait"] = "returned"
+        except RuntimeError as failure:
+            seen["wait"] = str(failure)
+
+    thread = threading.Thread(target=waits)
+    thread.start()
+    time.sleep(0.3)
+    started = time.monotonic()
+    a.close()
+    thread.join(10)
+    assert not thread.is_alive() and time.monotonic() - started < 8
+    assert seen["wait"].startswith("multitcp")
+    with pytest.raises(RuntimeError, match="closed"):
+        a.address()
+    a.abort()
+    a.close()
+    b.close()

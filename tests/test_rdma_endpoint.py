@@ -237,7 +237,7 @@ def test_a_broken_receiver_revokes_its_registrations(fabric):
     sender.join(5)
     time.sleep(0.5)
     assert a.telemetry()["broken"], "the late writes must have been refused"
-    assert "refused remote access" in a._error()
+    assert "refused remote access" in a.last_error()
 
 
 def test_telemetry_counts_what_happened(fabric):
@@ -375,3 +375,35 @@ def test_a_member_that_dies_without_a_word_still_breaks_its_peers():
         assert a.telemetry()["broken"]
     finally:
         f.close()
+
+
+def test_close_waits_for_calls_that_are_inside_and_later_calls_are_refused(fabric):
+    """Another thread is blocked in a wait when the endpoint is closed: the wait is ended with an
+    error, the endpoint is freed only after that thread has left the library, and whatever is
+    called afterwards raises instead of reaching freed memory."""
+    f, (a, b) = fabric()
+    room = torch.zeros(100)
+    seen = {}
+
+    def waits():
+        try:
+            a.wait([a.recv(1, room.data_ptr(), room.nbytes, 9)], soon(30))
+            seen["wait"] = "returned"
+        except RuntimeError as failure:
+            seen["wait"] = str(failure)
+
+    thread = threading.Thread(target=waits)
+    thread.start()
+    time.sleep(0.3)                                                 # it is inside the library now
+    started = time.monotonic()
+    a.close()
+    thread.join(10)
+    assert not thread.is_alive() and time.monotonic() - started < 8
+    assert seen["wait"] != "returned" and "rdma endpoint" in seen["wait"]
+    for call in (lambda: a.send(1, room.data_ptr(), 8, 1), lambda: a.recv(1, room.data_ptr(), 8, 1),
+                 lambda: a.wait([1], soon(1)), a.telemetry, a.last_error):
+        with pytest.raises(RuntimeError, match="closed"):
+            call()
+    a.abort()                                                       # harmless on a closed endpoint
+    a.close()
+    assert a.invalidate(room.data_ptr(), 8) == 0

@@ -661,3 +661,34 @@ def test_three_leaders_run_the_workers_ring_between_processes(fake_ucx, tmp_path
     sends = run_ranks(("nvidia",) * 3, _three_leaders, tmp_path, init={"bridge": "ucx"}, timeout=120,
                       env=dict(fake_ucx, GPUBRIDGE_ISLANDS="1,1,1", GPUBRIDGE_UCX_CHUNK_BYTES="64K"))
     assert all(count > 10 for count in sends)                      # a ring in chunks, on every leader
+
+
+def test_close_from_another_thread_ends_a_blocked_wait_before_the_worker_is_freed(fake_ucx):
+    from gpubridge_b200 import ucx
+    seen = {}
+
+    def body(worker, i):
+        if i == 1:
+            return None
+        room = torch.zeros(64)
+
+        def waits():
+            try:
+                worker.wait([worker.recv(1, room.data_ptr(), room.nbytes, 3)], time.monotonic() + 30)
+                seen["wait"] = "returned"
+            except ucx.UcxError as failure:
+                seen["wait"] = str(failure)
+
+        thread = threading.Thread(target=waits)
+        thread.start()
+        time.sleep(0.3)
+        started = time.monotonic()
+        worker.close(2.0)
+        thread.join(10)
+        assert not thread.is_alive() and time.monotonic() - started < 8
+        with pytest.raises(ucx.UcxError, match="closed"):
+            worker.memory_types()
+        worker.abort()
+        return seen["wait"]
+
+    assert "UCX" in _workers(2, body)[0]
