@@ -76,7 +76,8 @@ def build(verbose: bool = False, force: bool = False, bounds: bool = False) -> s
     extra = ("-DGB_BOUNDS",) if bounds else ()
     if force:
         for name in os.listdir(OBJ):
-            os.remove(os.path.join(OBJ, name))
+            if os.path.isfile(os.path.join(OBJ, name)):        # the front end's objects have a folder of their own
+                os.remove(os.path.join(OBJ, name))
     with ThreadPoolExecutor(max_workers=4) as pool:
         objects = list(pool.map(lambda p: _compile(p, verbose, extra), sources()))
     stamp = os.path.join(OBJ, "linked_bounds.txt" if bounds else "linked.txt")
