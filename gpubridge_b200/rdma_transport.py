@@ -36,6 +36,18 @@ from gpubridge_b200 import gdr as _gdr
 from gpubridge_b200 import rdma as _rdma
 from gpubridge_b200.tagged import DTYPE_CODES, OP_CODES, OnDevice, TaggedBridge
 
+#: endpoint settings of ``bridge="verbs"``: variable -> (endpoint argument, default, must be a multiple of)
+ENDPOINT_SETTINGS = {
+    "GPUBRIDGE_VERBS_SLOT_BYTES": ("eager_max", 16 << 10, 8),          # largest message that travels in a receive slot
+    "GPUBRIDGE_VERBS_CREDITS": ("data_slots", 16, 1),                  # receive slots (= send credits) per peer
+    "GPUBRIDGE_VERBS_WRITE_BYTES": ("max_write", 1 << 20, 8),          # size of one remote write of a large message
+    "GPUBRIDGE_VERBS_UNEXPECTED_BYTES": ("unexpected_max", 64 << 20, 1),   # early messages kept per endpoint
+    "GPUBRIDGE_VERBS_MR_CACHE": ("mr_cache", 64, 1),                   # registrations kept, least recently used out
+}
+GPU_PATH_ENV = "GPUBRIDGE_VERBS_GPU_PATH"          # auto | staged: staged keeps device tensors off the direct path
+OBSERVE_ENV = "GPUBRIDGE_VERBS_OBSERVE"            # a file: one JSON line per bridge call, the counters at close
+OBSERVE_QUEUE_ENV = "GPUBRIDGE_VERBS_OBSERVE_QUEUE"
+JOB_ENV = "GPUBRIDGE_JOB_ID"
 DIRECT_MIN_ENV = "GPUBRIDGE_VERBS_DIRECT_MIN_BYTES"
 STAGING_ENV = "GPUBRIDGE_VERBS_STAGING_BYTES"
 PIECE_ENV = "GPUBRIDGE_VERBS_PIECE_BYTES"
@@ -60,6 +72,7 @@ class Router:
         self.direct_min = (_config.size_setting(DIRECT_MIN_ENV, 64 << 10, multiple=1)
                            if direct_min_bytes is None else direct_min_bytes)
         self._plans = flush_plans or _gdr.plan
+        self.gpu_path = _config.choice(GPU_PATH_ENV, ("auto", "staged"), "auto")
         self.counts = collections.Counter()
 
     def plan(self, device: int):
@@ -76,6 +89,8 @@ class Router:
             return Route("bounce", "the tensor is not contiguous")
         if tensor.device.type == "cpu":
             return Route("plain", "contiguous host memory is registered where it lies")
+        if self.gpu_path == "staged":
+            return Route("bounce", f"{GPU_PATH_ENV}=staged keeps device tensors off the direct path")
         if not self.device_registration:
             return Route("bounce", "the provider cannot register device memory")
         if tensor.nbytes < self.direct_min:
@@ -132,6 +147,36 @@ class RegisteredStaging:
         self._buffers.clear()
 
 
+def endpoint_settings() -> dict[str, int]:
+    """The endpoint arguments the ``GPUBRIDGE_VERBS_*`` variables ask for (defaults where unset)."""
+    return {argument: _config.size_setting(name, default, multiple=multiple)
+            for name, (argument, default, multiple) in ENDPOINT_SETTINGS.items()}
+
+
+_emitters: dict[str, object] = {}
+
+
+def observations(rank: int | None = None):
+    """The process's emitter of bridge observations (``GPUBRIDGE_VERBS_OBSERVE=FILE``; ``%r`` in the
+    name becomes the rank, so that ranks do not share a file), or None.  One JSON line per bridge
+    call - bridge, member, bytes, route, milliseconds or the failure - and the endpoint's counters
+    when a bridge closes; written behind a bounded queue (``GPUBRIDGE_VERBS_OBSERVE_QUEUE``
+    records) by :class:`gpubridge_b200.telemetry.Emitter`, labelled with ``GPUBRIDGE_JOB_ID``."""
+    import atexit
+    import os
+    path = os.environ.get(OBSERVE_ENV, "").strip()
+    if not path:
+        return None
+    path = path.replace("%r", str(rank) if rank is not None else os.environ.get("RANK", "0"))
+    if path not in _emitters:
+        from gpubridge_b200.telemetry import Emitter
+        capacity = _config.size_setting(OBSERVE_QUEUE_ENV, 4096, multiple=1)
+        made = Emitter(path, capacity=capacity, job=os.environ.get(JOB_ENV, "").strip() or None, pid=os.getpid())
+        atexit.register(made.close)
+        _emitters[path] = made
+    return _emitters[path]
+
+
 class RdmaTransport(TaggedBridge):
     """Registered under its name by ``rdma.load`` once a provider over real queue pairs is
     part of the build; until then resolving ``bridge="verbs"`` says why it cannot load."""
@@ -150,6 +195,7 @@ class RdmaTransport(TaggedBridge):
                             if piece_bytes is None else piece_bytes)
         self._copy_stream = None
         self.last_route: Route | None = None
+        self.observations = observations(rank)
 
     @classmethod
     def _connect(cls, store, key, members, rank, timeout, deadline):
@@ -162,14 +208,25 @@ class RdmaTransport(TaggedBridge):
         if _rdma.provider_kind() == "tcp":
             from gpubridge_b200.multitcp import listen_address
             tcp_host = listen_address()
+        settings = endpoint_settings()              # a bad value fails here, on this leader
+        chunk = _config.size_setting("GPUBRIDGE_VERBS_CHUNK_BYTES", 4 << 20)
+        # both ends of a link must cut messages alike and offer the slots the other end counts on
+        import json
+        store.set(f"{key}/settings/{rank}", json.dumps(dict(settings, chunk_bytes=chunk), sort_keys=True))
+        said = wait_for_keys(store, [f"{key}/settings/{m}" for m in members], deadline,
+                             "every bridge member's endpoint settings",
+                             verdicts=[f"{key}/status/{m}" for m in members if m != rank])
+        if len(set(said)) > 1:
+            listed = "; ".join(f"rank {m}: {text}" for m, text in zip(members, said))
+            raise ValueError(f"the leaders' verbs settings differ ({listed}); set the same GPUBRIDGE_VERBS_* "
+                             "values on every leader")
         endpoint = _rdma.Endpoint.over_sockets(
             index, len(members),
             publish=lambda name: store.set(f"{key}/socket/{rank}", name),
             collect=lambda: wait_for_keys(store, [f"{key}/socket/{m}" for m in members], deadline,
                                           "every bridge member's socket name",
                                           verdicts=[f"{key}/status/{m}" for m in members if m != rank]),
-            timeout=max(0.1, deadline - time.monotonic()), tcp_host=tcp_host)
-        chunk = _config.size_setting("GPUBRIDGE_VERBS_CHUNK_BYTES", 4 << 20)
+            timeout=max(0.1, deadline - time.monotonic()), tcp_host=tcp_host, **settings)
         return cls(endpoint, members, rank, timeout, chunk)
 
     @classmethod
@@ -220,6 +277,7 @@ class RdmaTransport(TaggedBridge):
         route = self.router.route(tensor)
         self.last_route = route
         deadline = time.monotonic() + self.timeout
+        began = time.perf_counter()
         try:
             if route.how == "in-place":
                 self._calls += 1
@@ -229,9 +287,15 @@ class RdmaTransport(TaggedBridge):
                 run(tensor, self._calls, deadline)
             else:
                 self._bounce(tensor, run, deadline, only_out, only_in)
-        except BaseException:
+        except BaseException as failure:
             self.worker.abort()
+            if self.observations is not None:
+                self.observations.emit("bridge_call", bridge=self.name, member=self.index, nbytes=tensor.nbytes,
+                                       route=route.how, failed=type(failure).__name__)
             raise
+        if self.observations is not None:
+            self.observations.emit("bridge_call", bridge=self.name, member=self.index, nbytes=tensor.nbytes,
+                                   route=route.how, ms=round((time.perf_counter() - began) * 1e3, 4))
 
     def _in_place(self, flat: torch.Tensor, number: int, deadline: float, where_it_lies) -> None:
         where_it_lies(flat, number, deadline)
@@ -302,5 +366,10 @@ class RdmaTransport(TaggedBridge):
 
     def close(self) -> None:
         if self.worker is not None:
+            if self.observations is not None:
+                try:
+                    self.observations.emit("endpoint", **dict(self.worker.telemetry(), bridge=self.name, member=self.index))
+                except Exception:  # noqa: BLE001 - a record less, never a failed close
+                    pass
             self.staging.close()
         super().close()

@@ -138,3 +138,73 @@ def test_policies_over_the_verbs_bridge_between_processes(tmp_path, policy, prov
 def test_without_a_provider_the_name_still_refuses(tmp_path):
     run_ranks(LAYOUTS["2+2"], _through_sockets, tmp_path, "auto", init={"bridge": "verbs"},
               expect_error="provider", timeout=60)
+
+
+# ---- settings of the verbs bridge ---------------------------------------------------------------------
+def test_endpoint_settings_parse_and_refuse_bad_values(monkeypatch):
+    from gpubridge_b200 import rdma_transport
+    for name in rdma_transport.ENDPOINT_SETTINGS:
+        monkeypatch.delenv(name, raising=False)
+    assert rdma_transport.endpoint_settings() == {"eager_max": 16 << 10, "data_slots": 16, "max_write": 1 << 20,
+                                                  "unexpected_max": 64 << 20, "mr_cache": 64}
+    monkeypatch.setenv("GPUBRIDGE_VERBS_SLOT_BYTES", "64K")
+    monkeypatch.setenv("GPUBRIDGE_VERBS_CREDITS", "4")
+    told = rdma_transport.endpoint_settings()
+    assert told["eager_max"] == 65536 and told["data_slots"] == 4
+    monkeypatch.setenv("GPUBRIDGE_VERBS_SLOT_BYTES", "1001")
+    with pytest.raises(ValueError, match="GPUBRIDGE_VERBS_SLOT_BYTES.*multiple of 8"):
+        rdma_transport.endpoint_settings()
+    monkeypatch.setenv("GPUBRIDGE_VERBS_SLOT_BYTES", "64K")
+    monkeypatch.setenv("GPUBRIDGE_VERBS_GPU_PATH", "staged")
+    router = rdma_transport.Router(device_registration=True)
+    from types import SimpleNamespace
+    device_tensor = SimpleNamespace(device=SimpleNamespace(type="cuda", index=0), nbytes=1 << 20,
+                                    is_contiguous=lambda: True, data_ptr=lambda: 0x1000)
+    route = router.route(device_tensor)
+    assert route.how == "bounce" and "GPUBRIDGE_VERBS_GPU_PATH=staged" in route.why
+    monkeypatch.setenv("GPUBRIDGE_VERBS_GPU_PATH", "sideways")
+    with pytest.raises(ValueError, match="GPUBRIDGE_VERBS_GPU_PATH"):
+        rdma_transport.Router()
+
+
+def _observed(rank, topology, out_dir):
+    import gpubridge_b200 as gb
+    t = rank_tensor(rank, 70_001)
+    gb.all_reduce(t)
+    assert torch.equal(t, expected_sum(topology.world_size, 70_001))
+    gb.broadcast(t, 0)
+    told = None if topology.bridge is None else topology.bridge.describe()["endpoint"]
+    return told
+
+
+def test_the_bridge_honours_its_settings_and_writes_its_observations(tmp_path):
+    import json
+    out = run_ranks(LAYOUTS["2+2"], _observed, tmp_path, str(tmp_path), init={"bridge": "verbs"}, timeout=120,
+                    env={"GPUBRIDGE_VERBS_PROVIDER": "sockets", "GPUBRIDGE_VERBS_SLOT_BYTES": "1K",
+                         "GPUBRIDGE_VERBS_CREDITS": "2", "GPUBRIDGE_VERBS_WRITE_BYTES": "8K",
+                         "GPUBRIDGE_VERBS_OBSERVE": str(tmp_path / "observed-%r.jsonl"), "GPUBRIDGE_JOB_ID": "job-77"})
+    leaders = [told for told in out if told is not None]
+    assert len(leaders) == 2
+    # 280 KB above a 1 KB slot: everything went by rendezvous, in writes of 8 KB
+    assert all(told["rndv_sent"] >= 1 and told["writes"] >= 280_004 // 8192 for told in leaders)
+    files = sorted(tmp_path.glob("observed-*.jsonl"))
+    assert [f.name for f in files] == ["observed-0.jsonl", "observed-2.jsonl"]          # the leaders' files, finished
+    records = [json.loads(line) for line in files[0].read_text().splitlines()]
+    calls = [r for r in records if r["kind"] == "bridge_call"]
+    assert len(calls) == 2 and all(r["job"] == "job-77" and r["bridge"] == "verbs" and r["route"] == "plain" for r in calls)
+    assert any(r["nbytes"] == 280_004 and r["ms"] > 0 for r in calls)
+    assert [r["kind"] for r in records][-2:] == ["endpoint", "closed"]
+    assert not any("rkey" in json.dumps(r) or "key" in " ".join(r) for r in records)
+
+
+@pytest.mark.parametrize("envs, message", [
+    ({2: {"GPUBRIDGE_VERBS_SLOT_BYTES": "2K"}}, "verbs settings differ"),
+    ({0: {"GPUBRIDGE_VERBS_CREDITS": "0"}}, "GPUBRIDGE_VERBS_CREDITS"),
+])
+def test_leaders_whose_settings_differ_or_are_bad_fail_init_on_every_rank(tmp_path, envs, message):
+    from _harness import per_rank
+    common = {"GPUBRIDGE_VERBS_PROVIDER": "sockets"}
+    per = {r: dict(common, **envs.get(r, {})) for r in range(4)}
+    errors = run_ranks(LAYOUTS["2+2"], per_rank, tmp_path, per, {"bridge": "verbs"}, mode="plain",
+                       expect_error=message, timeout=90)
+    assert len(errors) == 4 and all("could not be set up" in e for e in errors)
