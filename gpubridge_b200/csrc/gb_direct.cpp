@@ -268,6 +268,7 @@ struct Registrar {
     uint64_t next_window = 1;
     uint64_t hits = 0, misses = 0, evictions = 0, stale = 0, refusals = 0;
     uint64_t windows_made = 0, window_register_ns = 0, window_release_ns = 0;
+    std::string dmabuf_off, peer_off;                  // a method the user switched off, with the reason to give
 
     void drop(const std::shared_ptr<Region>& r) {
         adapter->dereg(r->key);
@@ -278,9 +279,9 @@ struct Registrar {
     // Register [lo, hi) of allocation `a` with `access`; which method worked, or every reason.
     bool make(const Allocation& a, uint64_t lo, uint64_t hi, int access, Region* out, std::string* reasons) {
         std::string why, all;
-        bool tried_dmabuf = false;
-        if (gpu->dmabuf_support(a.device, &why)) {
-            tried_dmabuf = true;
+        if (!dmabuf_off.empty()) {
+            why = dmabuf_off;
+        } else if (gpu->dmabuf_support(a.device, &why)) {
             const uint64_t page = gpu->page();
             const uint64_t from = lo / page * page, to = std::min(a.base + a.size, (hi + page - 1) / page * page);
             const int fd = gpu->export_dmabuf(from, to - from, &why);
@@ -294,10 +295,11 @@ struct Registrar {
             }
         }
         all += "dma-buf: " + why;
-        (void)tried_dmabuf;
         why.clear();
         std::string module;
-        if (!peer_module(modules_root, &module)) {
+        if (!peer_off.empty()) {
+            why = peer_off;
+        } else if (!peer_module(modules_root, &module)) {
             why = "neither nvidia_peermem nor nv_peer_mem is loaded";
         } else if (gpu->peer_support(a.device, &why)) {
             uint32_t key = 0;
@@ -425,10 +427,12 @@ struct Registrar {
     }
     std::string capabilities(int device) {
         std::string why, module, out = "dma-buf: ";
-        out += gpu->dmabuf_support(device, &why) ? "yes" : "no (" + why + ")";
+        if (!dmabuf_off.empty()) out += "no (" + dmabuf_off + ")";
+        else out += gpu->dmabuf_support(device, &why) ? "yes" : "no (" + why + ")";
         why.clear();
         out += "; peer memory: ";
-        if (!peer_module(modules_root, &module)) out += "no (no peer-memory module is loaded)";
+        if (!peer_off.empty()) out += "no (" + peer_off + ")";
+        else if (!peer_module(modules_root, &module)) out += "no (no peer-memory module is loaded)";
         else out += gpu->peer_support(device, &why) ? "yes (" + module + ")" : "no (" + why + ")";
         return out;
     }
@@ -521,6 +525,14 @@ void gb_direct_mock_counts(void* handle, unsigned long long* six) {
         std::lock_guard<std::mutex> hold(adapter->mu);
         six[3] = adapter->live.size(); six[4] = adapter->registrations; six[5] = adapter->deregistrations;
     }
+}
+
+// Switch a method off for this registrar (1 dma-buf, 2 peer memory), with the reason to report;
+// an empty reason switches it back on.
+void gb_direct_switch_off(void* handle, int method, const char* reason) {
+    auto* r = static_cast<Handle*>(handle)->registrar.get();
+    std::lock_guard<std::mutex> hold(r->mu);
+    (method == M_DMABUF ? r->dmabuf_off : r->peer_off) = reason ? reason : "";
 }
 
 // -- registrations.  Returns a ticket (> 0) and fills method (1 dma-buf, 2 peer memory), key and the

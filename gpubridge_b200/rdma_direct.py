@@ -25,6 +25,8 @@ import json
 from gpubridge_b200.ops import _lib
 
 METHODS = {1: "dma-buf", 2: "peer memory"}
+DMABUF_ENV = "GPUBRIDGE_VERBS_DMABUF"              # 0: never register through a dma-buf
+PEER_MEMORY_ENV = "GPUBRIDGE_VERBS_PEER_MEMORY"    # 0: never register through a peer-memory module
 #: what a pretend device or adapter can be told to refuse (``Registrar.fail``)
 FAILURES = {"device dma-buf": 0, "device peer memory": 1, "export": 2, "adapter dma-buf": 3, "adapter pointer": 4}
 
@@ -59,6 +61,7 @@ def _declare(lib) -> None:
         "gb_direct_invalidate": (c.c_int, [ptr, u64, u64]),
         "gb_direct_expose": (u64, [ptr, u64, u64, c.POINTER(c.c_uint), c.c_char_p, c.c_size_t]),
         "gb_direct_close_window": (c.c_int, [ptr, u64]),
+        "gb_direct_switch_off": (None, [ptr, c.c_int, c.c_char_p]),
         "gb_direct_capabilities": (None, [ptr, c.c_int, c.c_char_p, c.c_size_t]),
         "gb_direct_telemetry": (None, [ptr, c.c_char_p, c.c_size_t]),
     }
@@ -74,6 +77,15 @@ class Registrar:
         _declare(self.lib)
         self.real = real
         self.handle = self.lib.gb_direct_new(1 if real else 0, modules_root.encode(), capacity)
+        from gpubridge_b200 import config
+        for method, name in ((1, DMABUF_ENV), (2, PEER_MEMORY_ENV)):      # GPUBRIDGE_VERBS_DMABUF=0 and the like
+            if config._raw(name) and not config.flag(name):
+                self.switch_off(METHODS[method], f"switched off by {name}")
+
+    def switch_off(self, method: str, reason: str = "switched off") -> None:
+        """Never try ``method`` ("dma-buf" or "peer memory"); an empty reason switches it back on."""
+        code = {name: number for number, name in METHODS.items()}[method]
+        self.lib.gb_direct_switch_off(self.handle, code, reason.encode())
 
     @classmethod
     def pretend(cls, modules_root: str = "", capacity: int = 64) -> "Registrar":

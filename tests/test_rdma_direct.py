@@ -247,3 +247,27 @@ def test_the_router_asks_the_registrar_and_passes_its_reasons_on(registrar):
     assert refused.how == "bounce" and "dma-buf: closed driver; peer memory: not allowed" in refused.why
     assert router.counts == {"in-place": 1, "bounce": 4}
     assert registrar.telemetry()["held"] == 0                                      # deciding holds nothing
+
+
+def test_a_method_can_be_switched_off_by_the_user(modules, monkeypatch):
+    from gpubridge_b200.rdma_direct import NotDirect, Registrar
+    monkeypatch.setenv("GPUBRIDGE_VERBS_DMABUF", "0")
+    registrar = Registrar.pretend(modules("nvidia_peermem"))
+    try:
+        a = registrar.alloc(4 * MB)
+        with registrar.acquire(a, MB) as region:
+            assert region.method == "peer memory"
+        assert registrar.capabilities().startswith("dma-buf: no (switched off by GPUBRIDGE_VERBS_DMABUF)")
+        assert registrar.counts()["exports"] == 0                  # not even tried
+        registrar.invalidate(a, 4 * MB)
+        registrar.switch_off("peer memory", "not on this cluster")
+        with pytest.raises(NotDirect, match="dma-buf: switched off by GPUBRIDGE_VERBS_DMABUF; peer memory: not on this cluster"):
+            registrar.take(a, MB)
+        registrar.switch_off("dma-buf", "")                         # back on
+        with registrar.acquire(a, MB) as region:
+            assert region.method == "dma-buf"
+    finally:
+        registrar.close()
+    monkeypatch.setenv("GPUBRIDGE_VERBS_DMABUF", "perhaps")
+    with pytest.raises(ValueError, match="GPUBRIDGE_VERBS_DMABUF"):
+        Registrar.pretend(modules("nvidia_peermem"))
