@@ -162,13 +162,22 @@ class MultiTcpTransport(TaggedBridge):
         index = members.index(rank)
         host = listen_address()
         chunk = _config.size_setting(CHUNK_ENV, 4 << 20)
-        worker = Worker(index, len(members), streams_setting(), host)
+        streams = streams_setting()
+        worker = Worker(index, len(members), streams, host)
         try:
-            store.set(f"{key}/address/{rank}", worker.address())
-            addresses = wait_for_keys(store, [f"{key}/address/{m}" for m in members], deadline,
-                                      "every bridge member's multitcp address",
-                                      verdicts=[f"{key}/status/{m}" for m in members if m != rank])
-            worker.connect(addresses, max(0.1, deadline - time.monotonic()))
+            # the address travels with the settings both ends of a link must share: the lower
+            # member dials `streams` connections and the higher one waits for exactly as many
+            mine = json.dumps({"address": worker.address(), "streams": streams, "chunk_bytes": chunk})
+            store.set(f"{key}/address/{rank}", mine)
+            said = [json.loads(text) for text in wait_for_keys(
+                store, [f"{key}/address/{m}" for m in members], deadline, "every bridge member's multitcp address",
+                verdicts=[f"{key}/status/{m}" for m in members if m != rank])]
+            for name, variable in (("streams", STREAMS_ENV), ("chunk_bytes", CHUNK_ENV)):
+                values = {m: told[name] for m, told in zip(members, said)}
+                if len(set(values.values())) > 1:
+                    listed = ", ".join(f"rank {m}: {v}" for m, v in values.items())
+                    raise ValueError(f"{variable} differs between the leaders ({listed}); set the same value on each")
+            worker.connect([told["address"] for told in said], max(0.1, deadline - time.monotonic()))
             return cls(worker, members, rank, timeout, chunk)
         except BaseException:
             worker.close()

@@ -232,6 +232,8 @@ def test_bad_arguments_are_refused():
     ("a bad stream count on one leader", {2: {"GPUBRIDGE_MULTITCP_STREAMS": "0"}}, "between 1 and 64"),
     ("a bad chunk size on one leader", {0: {"GPUBRIDGE_MULTITCP_CHUNK_BYTES": "13"}}, "multiple of 8"),
     ("an interface that is not there", {0: {"GPUBRIDGE_MULTITCP_IFNAME": "nosuch0"}}, "no such interface"),
+    ("another stream count on one leader", {2: {"GPUBRIDGE_MULTITCP_STREAMS": "7"}}, "GPUBRIDGE_MULTITCP_STREAMS differs"),
+    ("another chunk size on one leader", {0: {"GPUBRIDGE_MULTITCP_CHUNK_BYTES": "64K"}}, "GPUBRIDGE_MULTITCP_CHUNK_BYTES differs"),
 ])
 def test_one_leaders_trouble_fails_init_on_every_rank(tmp_path, what, envs, message):
     errors = run_ranks(LAYOUTS["2+2"], per_rank, tmp_path, envs, {"bridge": "multitcp"}, mode="plain",
