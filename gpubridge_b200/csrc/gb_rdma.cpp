@@ -98,7 +98,11 @@ struct Provider {
 };
 
 // ---- the in-process fabric ---------------------------------------------------------------------------
-enum FaultKind { F_NONE = 0, F_ERROR = 1, F_DROP = 2, F_DELAY = 3, F_CORRUPT = 4, F_KILL = 5 };
+// F_SPURIOUS: both ends' polls are woken with nothing to report, `arg` times, and the operation
+// goes through.  F_LATE: the operation is carried out at once but its completion reaches the
+// poster `arg` milliseconds later - so the peer's answer may come back before it.
+enum FaultKind { F_NONE = 0, F_ERROR = 1, F_DROP = 2, F_DELAY = 3, F_CORRUPT = 4, F_KILL = 5, F_SPURIOUS = 6,
+                 F_LATE = 7 };
 
 struct Fault {
     int kind = F_NONE, src = -1, dst = -1, opcode = -1;
@@ -114,6 +118,7 @@ struct MockProvider : Provider {
     std::mutex mu;
     std::condition_variable cv;
     std::deque<Completion> cq;
+    std::deque<std::pair<Clock::time_point, Completion>> late;    // completions held back by F_LATE
     struct Posted { uint64_t wr_id; char* buf; uint32_t len; };
     std::map<std::pair<int, int>, std::deque<Posted>> recvs; // by (source, lane)
     struct Region { char* base; size_t len; };
@@ -126,14 +131,30 @@ struct MockProvider : Provider {
         { std::lock_guard<std::mutex> hold(mu); cq.push_back(c); }
         cv.notify_all();
     }
+    void complete_later(const Completion& c, int milliseconds) {
+        std::lock_guard<std::mutex> hold(mu);
+        late.emplace_back(Clock::now() + std::chrono::milliseconds(milliseconds), c);
+    }
     int post_recv(int peer, int lane, uint64_t wr_id, void* buf, uint32_t len) override;
     int post_send(int peer, int lane, uint64_t wr_id, const void* buf, uint32_t len) override;
     int post_write(int peer, uint64_t wr_id, const void* local, uint64_t remote, uint32_t rkey,
                    uint32_t len) override;
+    // mu held.  Completions that were held back and are due now join the queue.
+    void release_due() {
+        const auto now = Clock::now();
+        for (auto it = late.begin(); it != late.end();) {
+            if (it->first <= now) { cq.push_back(it->second); it = late.erase(it); } else ++it;
+        }
+    }
     int poll(Completion* out, int max, int timeout_ms) override {
         std::unique_lock<std::mutex> hold(mu);
-        if (cq.empty() && timeout_ms > 0)
-            cv.wait_for(hold, std::chrono::milliseconds(timeout_ms), [&] { return !cq.empty() || woken; });
+        release_due();
+        if (cq.empty() && timeout_ms > 0) {
+            auto until = Clock::now() + std::chrono::milliseconds(timeout_ms);
+            for (auto& held : late) until = std::min(until, held.first);       // wake for the next one that falls due
+            cv.wait_until(hold, until, [&] { return !cq.empty() || woken; });
+            release_due();
+        }
         woken = false;
         int n = 0;
         while (n < max && !cq.empty()) { out[n++] = cq.front(); cq.pop_front(); }
@@ -181,7 +202,8 @@ struct MockFabric {
         return Fault();
     }
     // mu held.
-    void deliver(int src, int dst, int lane, uint64_t wr_id, const char* bytes, uint32_t len, bool corrupt) {
+    void deliver(int src, int dst, int lane, uint64_t wr_id, const char* bytes, uint32_t len, bool corrupt,
+                 int late_ms = 0) {
         MockProvider& to = *members[dst];
         MockProvider::Posted slot;
         {
@@ -199,8 +221,11 @@ struct MockFabric {
             if (corrupt && len > 0) slot.buf[0] ^= 0x5A;
             r.bytes = len;
         }
-        members[src]->complete(s);
+        if (late_ms > 0) members[src]->complete_later(s, late_ms); else members[src]->complete(s);
         to.complete(r);
+    }
+    void spurious(int a, int b, int times) {
+        for (int i = 0; i < (times > 0 ? times : 1); ++i) { members[a]->wake(); members[b]->wake(); }
     }
 };
 
@@ -243,6 +268,7 @@ int MockProvider::post_send(int peer, int lane, uint64_t wr_id, const void* buf,
         std::this_thread::sleep_for(std::chrono::milliseconds(f.arg));
         order.lock();
     }
+    if (f.kind == F_SPURIOUS) fabric->spurious(index, peer, f.arg);
     bool posted;
     {
         std::lock_guard<std::mutex> hold(fabric->members[peer]->mu);
@@ -254,7 +280,8 @@ int MockProvider::post_send(int peer, int lane, uint64_t wr_id, const void* buf,
         fabric->waiting.push_back(std::move(held));
         return 0;
     }
-    fabric->deliver(index, peer, lane, wr_id, static_cast<const char*>(buf), len, f.kind == F_CORRUPT);
+    fabric->deliver(index, peer, lane, wr_id, static_cast<const char*>(buf), len, f.kind == F_CORRUPT,
+                    f.kind == F_LATE ? f.arg : 0);
     return 0;
 }
 
@@ -273,6 +300,7 @@ int MockProvider::post_write(int peer, uint64_t wr_id, const void* local, uint64
         std::this_thread::sleep_for(std::chrono::milliseconds(f.arg));
         order.lock();
     }
+    if (f.kind == F_SPURIOUS) fabric->spurious(index, peer, f.arg);
     MockProvider& to = *fabric->members[peer];
     {
         std::lock_guard<std::mutex> hold(to.mu);
@@ -284,7 +312,7 @@ int MockProvider::post_write(int peer, uint64_t wr_id, const void* local, uint64
             std::memcpy(const_cast<char*>(at), local, len);
         }
     }
-    complete(c);
+    if (f.kind == F_LATE) complete_later(c, f.arg); else complete(c);
     return 0;
 }
 
@@ -325,6 +353,7 @@ struct SocketProvider : Provider {
     std::mutex mu;
     std::condition_variable cv, posted_cv;
     std::deque<Completion> cq;
+    std::deque<std::pair<Clock::time_point, Completion>> late;    // completions held back by F_LATE
     struct Posted { uint64_t wr_id; char* buf; uint32_t len; };
     std::map<std::pair<int, int>, std::deque<Posted>> recvs;
     struct Region { char* base; size_t len; };
@@ -465,6 +494,10 @@ struct SocketProvider : Provider {
     void complete(const Completion& c) {
         { std::lock_guard<std::mutex> hold(mu); cq.push_back(c); }
         cv.notify_all();
+    }
+    void complete_later(const Completion& c, int milliseconds) {
+        std::lock_guard<std::mutex> hold(mu);
+        late.emplace_back(Clock::now() + std::chrono::milliseconds(milliseconds), c);
     }
     void flush_peer(int peer) {
         std::deque<Posted> lost;
@@ -621,10 +654,22 @@ struct SocketProvider : Provider {
         o.data = static_cast<const char*>(local); o.opcode = OC_WRITE;
         return enqueue(peer, o);
     }
+    // mu held.  Completions that were held back and are due now join the queue.
+    void release_due() {
+        const auto now = Clock::now();
+        for (auto it = late.begin(); it != late.end();) {
+            if (it->first <= now) { cq.push_back(it->second); it = late.erase(it); } else ++it;
+        }
+    }
     int poll(Completion* out, int max, int timeout_ms) override {
         std::unique_lock<std::mutex> hold(mu);
-        if (cq.empty() && timeout_ms > 0)
-            cv.wait_for(hold, std::chrono::milliseconds(timeout_ms), [&] { return !cq.empty() || woken; });
+        release_due();
+        if (cq.empty() && timeout_ms > 0) {
+            auto until = Clock::now() + std::chrono::milliseconds(timeout_ms);
+            for (auto& held : late) until = std::min(until, held.first);       // wake for the next one that falls due
+            cv.wait_until(hold, until, [&] { return !cq.empty() || woken; });
+            release_due();
+        }
         woken = false;
         int n = 0;
         while (n < max && !cq.empty()) { out[n++] = cq.front(); cq.pop_front(); }

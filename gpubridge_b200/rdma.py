@@ -26,7 +26,7 @@ import json
 import time
 
 
-FAULTS = {"error": 1, "drop": 2, "delay": 3, "corrupt": 4, "kill": 5}
+FAULTS = {"error": 1, "drop": 2, "delay": 3, "corrupt": 4, "kill": 5, "spurious": 6, "late": 7}
 OPCODES = {"send": 0, "write": 2, "any": -1}
 
 
@@ -96,7 +96,10 @@ class MockFabric:
     def inject(self, fault: str, *, src: int = -1, dst: int = -1, on: str = "any", nth: int = 1,
                milliseconds: int = 0) -> None:
         """The ``nth`` next operation of kind ``on`` (send / write / any) from ``src`` to ``dst``
-        (-1: any) will ``error``, ``drop``, ``delay``, be ``corrupt`` or ``kill`` its destination."""
+        (-1: any) will ``error``, ``drop``, ``delay``, be ``corrupt`` or ``kill`` its destination;
+        ``spurious``: both ends' polls wake ``milliseconds`` times with nothing to report and the
+        operation goes through; ``late``: it is carried out at once but its completion reaches
+        the poster ``milliseconds`` later, so the peer's answer may overtake it."""
         self.lib.gb_rdma_mock_inject(self.handle, FAULTS[fault], src, dst, OPCODES[on], nth, milliseconds)
 
     def stats(self) -> dict:

@@ -407,3 +407,50 @@ def test_close_waits_for_calls_that_are_inside_and_later_calls_are_refused(fabri
     a.abort()                                                       # harmless on a closed endpoint
     a.close()
     assert a.invalidate(room.data_ptr(), 8) == 0
+
+
+@pytest.mark.parametrize("on", ["send", "write"])
+def test_spurious_wake_ups_are_harmless(fabric, on):
+    f, (a, b) = fabric(eager_max=1024, max_write=4096)
+    for nth in (1, 2, 3, 5):
+        f.inject("spurious", src=0, dst=1, on=on, nth=nth, milliseconds=7)          # seven empty wake-ups each
+    small, large = torch.arange(100, dtype=torch.float32), torch.arange(50_000, dtype=torch.float32)
+    for data in (small, large, small, large):
+        out = torch.zeros_like(data)
+        r = b.recv(0, out.data_ptr(), out.nbytes, 4)
+        s = a.send(1, data.data_ptr(), data.nbytes, 4)
+        a.wait([s], soon())
+        b.wait([r], soon())
+        assert torch.equal(out, data)
+    assert not a.telemetry()["broken"] and not b.telemetry()["broken"]
+    assert a.telemetry()["errors"] == 0 and b.telemetry()["pending_ops"] == 0
+
+
+def test_a_completion_that_comes_after_the_peers_answer(fabric):
+    """The send is delivered at once but the sender learns of it 300 ms later: by then the receiver
+    has consumed the message and its credit (and, for a large message, its write grant) is back.
+    Nothing may depend on the local completion coming first."""
+    f, (a, b) = fabric(eager_max=1024, data_slots=2, max_write=4096)
+    f.inject("late", src=0, dst=1, on="send", nth=1, milliseconds=300)
+    data, out = torch.arange(200, dtype=torch.float32), torch.zeros(200)
+    r = b.recv(0, out.data_ptr(), out.nbytes, 1)
+    started = time.monotonic()
+    s = a.send(1, data.data_ptr(), data.nbytes, 1)
+    b.wait([r], soon())
+    assert torch.equal(out, data) and time.monotonic() - started < 0.25              # the receiver did not wait for it
+    a.wait([s], soon())                                # a small message is the endpoint's own copy: done for the caller
+    before = a.telemetry()["completions"]
+    time.sleep(0.45)
+    assert a.telemetry()["completions"] == before + 1                                 # the held-back completion came in
+    # and a large message whose request-to-send completes late still goes through, writes and all
+    f.inject("late", src=0, dst=1, on="send", nth=1, milliseconds=200)
+    f.inject("late", src=0, dst=1, on="write", nth=2, milliseconds=200)
+    big, room = torch.arange(30_000, dtype=torch.float32), torch.zeros(30_000)
+    r = b.recv(0, room.data_ptr(), room.nbytes, 2)
+    s = a.send(1, big.data_ptr(), big.nbytes, 2)
+    a.wait([s], soon())
+    b.wait([r], soon())
+    assert torch.equal(room, big)
+    for _ in range(6):                                                                # credits are all back: a burst fits
+        exchange(a, b, torch.ones(50))
+    assert not a.telemetry()["broken"] and not b.telemetry()["broken"] and a.telemetry()["pending_ops"] == 0
