@@ -97,6 +97,27 @@ def _fault(kind: str, members: int = 2) -> dict:
     return {"ok": ok, "seconds": round(took, 2), "members_failed": failed, "broken": broken}
 
 
+def _harmless(kind: str) -> dict:
+    """Faults the protocol has to shrug off: the all-reduce still gives the known sum, nothing breaks."""
+    fabric = rdma.MockFabric(2)
+    bridges = [RdmaTransport.over_fabric(fabric, [0, 1], m, timeout=timedelta(seconds=10)) for m in (0, 1)]
+    for nth in (1, 2, 4):
+        fabric.inject(kind, src=0, dst=1, nth=nth, milliseconds=5 if kind == "spurious" else 150)
+
+    def body(i: int):
+        t = torch.arange(300_000, dtype=torch.float32) + i
+        bridges[i].all_reduce(t)
+        return bool(torch.equal(t, 2 * torch.arange(300_000, dtype=torch.float32) + 1))
+
+    result = _threads(2, body)
+    broken = [b.worker.telemetry()["broken"] for b in bridges]
+    for b in bridges:
+        b.close()
+    fabric.close()
+    return {"ok": all(r["value"] is True for r in result) and not any(broken), "broken": broken,
+            "errors": [r["error"] for r in result if r["error"]]}
+
+
 def _registration() -> list[tuple[str, dict]]:
     """The registrar of device memory on pretend device memory and a pretend adapter: the method
     it picks, what it says when no method works, and that a stale address is another owner."""
@@ -175,6 +196,8 @@ def check(out: Path) -> int:
                                                  "errors": [r["error"] for r in result if r["error"]]})
     for kind in ("error", "drop", "delay", "corrupt", "kill"):
         row(f"fault: {kind}", _fault(kind, 3 if kind == "kill" else 2))
+    row("spurious wake-ups are harmless", _harmless("spurious"))
+    row("a completion that comes after the peer's answer is harmless", _harmless("late"))
     for name, result in _registration():
         row(name, result)
     out.mkdir(parents=True, exist_ok=True)

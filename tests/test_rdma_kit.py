@@ -13,7 +13,7 @@ def test_check_passes_every_scenario_and_records_them(tmp_path):
     assert rdma_kit.main(["check", "--out", str(tmp_path)]) == 0
     rows = json.loads((tmp_path / "rdma_check.json").read_text())["rows"]
     names = [r["scenario"] for r in rows]
-    assert "rendezvous message" in names and "fault: kill" in names and len(rows) >= 15
+    assert "rendezvous message" in names and "fault: kill" in names and len(rows) >= 17
     assert sum(name.startswith("device registration") for name in names) == 3
     assert all(r["ok"] for r in rows)
     kill = next(r for r in rows if r["scenario"] == "fault: kill")
