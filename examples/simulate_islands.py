@@ -5,7 +5,9 @@ election and the bridged all-reduce run exactly as on a mixed machine, with Gloo
 for the island library.  Pass the vendors on the command line to try other shapes:
 
     python examples/simulate_islands.py                       # nvidia nvidia amd amd
-    python examples/simulate_islands.py nvidia amd amd amd intel
+    python examples/simulate_islands.py nvidia amd amd amd nvidia
+    GPUBRIDGE_BRIDGE_COMPRESSION=fp8 python examples/simulate_islands.py
+    python examples/simulate_islands.py --bridge multitcp     # the native TCP worker between the leaders
 """
 from __future__ import annotations
 
@@ -21,13 +23,13 @@ _sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__)
 import gpubridge_b200 as gb
 
 
-def worker(rank: int, vendors: list[str], rendezvous: str) -> None:
+def worker(rank: int, vendors: list[str], rendezvous: str, bridge: str | None) -> None:
     os.environ["GPUBRIDGE_VENDOR"] = vendors[rank]
-    topo = gb.init(init_method=f"file://{rendezvous}", rank=rank, world_size=len(vendors))
+    topo = gb.init(init_method=f"file://{rendezvous}", rank=rank, world_size=len(vendors), bridge=bridge)
     if rank == 0:
         for island in topo.layout.islands:
             print(f"island {island.vendor:<8} ranks {list(island.ranks)}  leader {island.leader}")
-        print(f"bridge link between leaders {list(topo.layout.bridge_ranks)}, "
+        print(f"bridge link between leaders {list(topo.layout.bridge_ranks)} over {topo.peers[0].bridge}, "
               f"policy {topo.policy_name}\n", flush=True)
     gb.barrier()
     t = torch.full((4,), float(rank + 1))
@@ -48,6 +50,12 @@ def worker(rank: int, vendors: list[str], rendezvous: str) -> None:
 
 
 if __name__ == "__main__":
-    vendors = sys.argv[1:] or ["nvidia", "nvidia", "amd", "amd"]
+    words = sys.argv[1:]
+    bridge = None
+    if "--bridge" in words:
+        at = words.index("--bridge")
+        bridge = words[at + 1]
+        del words[at:at + 2]
+    vendors = words or ["nvidia", "nvidia", "amd", "amd"]
     with tempfile.TemporaryDirectory() as tmp:
-        mp.spawn(worker, args=(vendors, os.path.join(tmp, "rendezvous")), nprocs=len(vendors))
+        mp.spawn(worker, args=(vendors, os.path.join(tmp, "rendezvous"), bridge), nprocs=len(vendors))
