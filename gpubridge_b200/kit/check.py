@@ -209,7 +209,13 @@ def main(argv=None) -> int:
             gb.barrier()
             sync(device)
 
-        with journal.stage("destroy"):
+        with journal.stage("destroy") as e:
+            describe = getattr(topology.bridge, "describe", None)
+            if describe is not None:               # a leader whose bridge keeps counts: routes, staging, counters
+                try:
+                    e["bridge"] = describe()
+                except Exception as failure:  # noqa: BLE001 - a record less, never a failed stage
+                    e["bridge"] = f"no report: {type(failure).__name__}: {failure}"
             gb.destroy()
     except BaseException:
         traceback.print_exc()

@@ -692,3 +692,22 @@ def test_close_from_another_thread_ends_a_blocked_wait_before_the_worker_is_free
         return seen["wait"]
 
     assert "UCX" in _workers(2, body)[0]
+
+
+def test_the_kits_check_program_runs_over_the_ucx_bridge_and_records_its_report(fake_ucx, tmp_path):
+    """The 13-stage per-rank check with ``GPUBRIDGE_BRIDGE=ucx``: every stage passes on both leaders
+    and the last stage carries the bridge's own report (paths, staging, the worker's counters)."""
+    out = tmp_path / "check"
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), OMP_NUM_THREADS="1",
+               GPUBRIDGE_VENDOR="nvidia", GPUBRIDGE_SPLIT_TEST="half", GPUBRIDGE_BRIDGE="ucx", **fake_ucx)
+    done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                           "--master-addr", "127.0.0.1", "--master-port", "29733", "-m", "gpubridge_b200.kit.check",
+                           "--out", str(out), "--in-flight-settle", "0.2", "--timeout", "120"],
+                          env=env, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr[-3000:]
+    for rank in (0, 1):
+        record = json.loads((out / f"rank{rank}.json").read_text())
+        assert record["ok"] and record["run"]["bridge"] == "ucx"
+        last = record["stages"][-1]
+        assert last["name"] == "destroy" and last["bridge"]["paths"].get("host", 0) > 0
+        assert last["bridge"]["endpoint"]["sends"] > 0 and not last["bridge"]["endpoint"]["broken"]
