@@ -15,7 +15,10 @@ _SETTINGS = ("GPUBRIDGE_BRIDGE_COMPRESSION", "GPUBRIDGE_PINNED_STAGING", "GPUBRI
              "GPUBRIDGE_BRIDGE", "GPUBRIDGE_THRESHOLDS", "GPUBRIDGE_CHUNK_BYTES",
              "GPUBRIDGE_SPLIT_TEST", "GPUBRIDGE_ISLANDS", "GPUBRIDGE_VENDOR",
              "GPUBRIDGE_CPU_ONLY", "GPUBRIDGE_CODEC_FORMAT", "GPUBRIDGE_FABRIC",
-             "GPUBRIDGE_ALGO", "GPUBRIDGE_ASYNC_QUEUE")
+             "GPUBRIDGE_ALGO", "GPUBRIDGE_ASYNC_QUEUE", "GPUBRIDGE_P2P_CHUNK_BYTES",
+             "GPUBRIDGE_UCX_CHUNK_BYTES", "GPUBRIDGE_UCX_DIRECT_MIN_BYTES", "GPUBRIDGE_JOB_ID")
+#: every setting of the host-staged bridges (a shell that exports one must not change what a test means)
+_SETTING_PREFIXES = ("GPUBRIDGE_VERBS_", "GPUBRIDGE_MULTITCP_")
 
 
 def pytest_configure(config):
@@ -51,4 +54,6 @@ def pytest_collection_modifyitems(config, items):
 def _clean_settings(monkeypatch):
     """Bit-exact tests must not inherit compression or policy settings from the shell."""
     for name in _SETTINGS:
+        monkeypatch.delenv(name, raising=False)
+    for name in [n for n in os.environ if n.startswith(_SETTING_PREFIXES)]:
         monkeypatch.delenv(name, raising=False)
