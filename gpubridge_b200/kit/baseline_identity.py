@@ -107,7 +107,10 @@ def identity() -> dict:
 
 def main(argv: list[str] | None = None) -> int:
     argv = sys.argv[1:] if argv is None else argv
-    if len(argv) != 1:
+    if argv and argv[0] in ("-h", "--help"):
+        print(__doc__)
+        return 0
+    if len(argv) != 1 or argv[0].startswith("-"):
         print("usage: python -m gpubridge_b200.kit.baseline_identity OUT.json", file=sys.stderr)
         return 2
     out = Path(argv[0])

@@ -90,6 +90,9 @@ def verdict(found: dict) -> list[str]:
 
 def main(argv=None) -> int:
     argv = sys.argv[1:] if argv is None else argv
+    if argv and argv[0].startswith("-"):
+        print(__doc__)
+        return 0 if argv[0] in ("-h", "--help") else 2
     found = survey()
     width = max(len(n) for n in found["rows"])
     print(f"torch {found['torch']}")

@@ -136,8 +136,11 @@ def summarize_scaling(directory: Path) -> tuple[dict[str, Any], str]:
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     partial = "--partial" in argv
+    if "-h" in argv or "--help" in argv:
+        print(__doc__)
+        return 0
     dirs = [Path(a) for a in argv if a != "--partial"]
-    if not dirs:
+    if not dirs or any(str(d).startswith("-") for d in dirs):
         print(__doc__, file=sys.stderr)
         return 2
     failed = False
