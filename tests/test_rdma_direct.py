@@ -271,3 +271,46 @@ def test_a_method_can_be_switched_off_by_the_user(modules, monkeypatch):
     monkeypatch.setenv("GPUBRIDGE_VERBS_DMABUF", "perhaps")
     with pytest.raises(ValueError, match="GPUBRIDGE_VERBS_DMABUF"):
         Registrar.pretend(modules("nvidia_peermem"))
+
+
+def test_many_threads_share_the_registrar(modules):
+    """Acquire, expose, invalidate and release from eight threads at once: every registration that
+    was made is released again, no descriptor is closed twice and the counts add up."""
+    import threading
+
+    from gpubridge_b200.rdma_direct import NotDirect, Registrar
+    registrar = Registrar.pretend(modules("nvidia_peermem"), capacity=4)
+    allocations = [registrar.alloc(8 * MB) for _ in range(6)]
+    errors = []
+
+    def work(seed):
+        try:
+            for step in range(300):
+                a = allocations[(seed + step) % len(allocations)]
+                offset = ((seed * 7 + step) % 4) * 2 * MB
+                try:
+                    with registrar.acquire(a + offset, 1000) as region:
+                        assert region.lo <= a + offset and a + offset + 1000 <= region.hi
+                        if step % 5 == 0:
+                            window, _ = registrar.expose(a + offset, 512)
+                            registrar.close_window(window)
+                except NotDirect as refused:
+                    assert "still held" in str(refused)
+                if step % 37 == 0:
+                    registrar.invalidate(a, 8 * MB)
+        except BaseException as failure:  # noqa: BLE001
+            errors.append(repr(failure))
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(8)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    assert not errors, errors[:3]
+    told, counts = registrar.telemetry(), registrar.counts()
+    assert told["held"] == 0 and told["windows_open"] == 0 and told["cached"] <= 4
+    assert told["hits"] + told["misses"] + told["refusals"] == 8 * 300
+    assert counts["descriptors_closed_twice"] == 0 and counts["registrations_alive"] == told["cached"]
+    assert counts["descriptors_open"] == told["cached"]
+    assert counts["registrations_made"] - counts["registrations_released"] == told["cached"]
+    registrar.close()
