@@ -711,3 +711,27 @@ def test_the_kits_check_program_runs_over_the_ucx_bridge_and_records_its_report(
         last = record["stages"][-1]
         assert last["name"] == "destroy" and last["bridge"]["paths"].get("host", 0) > 0
         assert last["bridge"]["endpoint"]["sends"] > 0 and not last["bridge"]["endpoint"]["broken"]
+
+
+@pytest.mark.parametrize("dtype, code", [(torch.bfloat16, 1), (torch.float16, 2), (torch.int64, 7), (torch.float64, 3)])
+def test_message_by_message_and_native_agree_for_every_element_type(fake_ucx, dtype, code):
+    """Sixteen-bit floats are folded through float32 and rounded once per addition on both paths:
+    three members, values that do not sum exactly, identical bits."""
+    torch.manual_seed(11)
+    if dtype.is_floating_point:
+        values = [(torch.randn(20_011) * 3 ** i).to(dtype) for i in range(3)]
+    else:
+        values = [torch.randint(-1000, 1000, (20_011,), dtype=dtype) * (i + 1) for i in range(3)]
+
+    def body(worker, i):
+        deadline = time.monotonic() + 30
+        native, stepwise = values[i].clone(), values[i].clone()
+        worker.all_reduce(native.data_ptr(), native.numel(), code, 0, 3_000, 1, deadline)
+        tagged.OnDevice(worker, 3, i).all_reduce(stepwise, "sum", 3_000, 2, deadline)
+        empty = torch.zeros(0, dtype=dtype)
+        tagged.OnDevice(worker, 3, i).all_reduce(empty, "sum", 3_000, 3, deadline)      # nothing to do, nothing posted
+        return native.view(torch.uint8).clone(), stepwise.view(torch.uint8).clone()
+
+    out = _workers(3, body)
+    for native, stepwise in out:
+        assert torch.equal(native, stepwise) and torch.equal(native, out[0][0])
