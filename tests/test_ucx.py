@@ -735,3 +735,30 @@ def test_message_by_message_and_native_agree_for_every_element_type(fake_ucx, dt
     out = _workers(3, body)
     for native, stepwise in out:
         assert torch.equal(native, stepwise) and torch.equal(native, out[0][0])
+
+
+def test_a_ucx_built_for_cuda_memory_opens_the_direct_path_only_where_the_device_allows_it(fake_ucx, monkeypatch):
+    from types import SimpleNamespace
+
+    from gpubridge_b200 import gdr
+    from gpubridge_b200.rdma_transport import Router
+    from gpubridge_b200.ucx.transport import UcxTransport
+    monkeypatch.setenv("FAKE_UCP_MEMORY_TYPES", "host,cuda")
+    device_tensor = SimpleNamespace(device=SimpleNamespace(type="cuda", index=0), nbytes=1 << 20,
+                                    is_contiguous=lambda: True, data_ptr=lambda: 0x1000)
+
+    def body(worker, i):
+        assert worker.memory_types() == {"host", "cuda"}
+        bridge = UcxTransport(worker, [0, 1], i, timedelta(seconds=5), 1 << 16)
+        assert bridge.router.device_registration
+        here = bridge.router.route(device_tensor)                   # this machine: whatever its driver says
+        ordered = Router(device_registration=True, direct_min_bytes=0,
+                         flush_plans=lambda d: gdr.FlushPlan(d, True, False, "ordered"))
+        refused = Router(device_registration=True, direct_min_bytes=0,
+                         flush_plans=lambda d: gdr.FlushPlan(d, False, False, "unordered writes, no host flush"))
+        bridge.worker = None
+        return here.how, ordered.route(device_tensor).how, refused.route(device_tensor)
+
+    for here, allowed, refused in _workers(2, body):
+        assert here in ("bounce", "in-place") and allowed == "in-place"
+        assert refused.how == "bounce" and refused.why == "unordered writes, no host flush"
