@@ -369,9 +369,12 @@ def test_a_member_that_dies_without_a_word_still_breaks_its_peers():
     a, b = f.endpoint(0), f.endpoint(1)
     try:
         f.inject("kill", dst=1, nth=1)
-        t = torch.ones(64)
+        t, room = torch.ones(64), torch.zeros(64)
+        # a small send is done for its caller once it is copied into a slot, so the wait also
+        # covers a receive that only the dead member could have answered
+        answer = a.recv(1, room.data_ptr(), room.nbytes, 2)
         with pytest.raises(RuntimeError):
-            a.wait([a.send(1, t.data_ptr(), t.nbytes, 1)], time.monotonic() + 5)
+            a.wait([a.send(1, t.data_ptr(), t.nbytes, 1), answer], time.monotonic() + 5)
         assert a.telemetry()["broken"]
     finally:
         f.close()
